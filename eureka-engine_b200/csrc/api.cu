@@ -1,0 +1,191 @@
+// api.cu -- the C ABI of include/llb_b200.h: backend primitives and operator entry points.
+#include "../../include/llb_b200.h"
+#include "host.cuh"
+
+LlbCtx g_llb;
+
+struct llb_xp {
+  XPlanes p;
+  int T, planes;
+  void *base;
+};
+
+// K-slice partial sums of the operator entry points (the engine owns its own scratch)
+static float *g_parts = nullptr;
+static size_t g_parts_floats = 0;
+
+extern "C" {
+
+int llb_b200_init(int device) {
+  if (g_llb.device == device && g_llb.stream) return 0;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n < 1) return llb_fail("no CUDA device: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= n) return llb_fail("device %d out of range (%d visible)", device, n);
+  CU_OK(cudaSetDevice(device));
+  cudaDeviceProp pr;
+  CU_OK(cudaGetDeviceProperties(&pr, device));
+  if (pr.major < 10) return llb_fail("device %d is sm_%d%d; this library is built for sm_100a only", device, pr.major, pr.minor);
+  g_llb.device = device;
+  g_llb.sms = pr.multiProcessorCount;
+  CU_OK(cudaStreamCreateWithFlags(&g_llb.stream, cudaStreamNonBlocking));
+  if (gemm_setup()) return -1;
+  return 0;
+}
+const char *llb_b200_last_error(void) { return g_llb.err; }
+int llb_b200_sm_count(void) { return g_llb.sms; }
+
+#define NEED_INIT(ret) \
+  if (!g_llb.stream) { llb_fail("llb_b200_init has not been called"); return ret; }
+
+llb_dptr llb_alloc_zero(size_t bytes) {
+  NEED_INIT(0)
+  void *p = nullptr;
+  if (cudaMalloc(&p, bytes ? bytes : 4) != cudaSuccess) { llb_fail("cudaMalloc(%zu) failed", bytes); cudaGetLastError(); return 0; }
+  if (cudaMemsetAsync(p, 0, bytes, g_llb.stream) != cudaSuccess) { cudaFree(p); llb_fail("memset failed"); return 0; }
+  return (llb_dptr)(uintptr_t)p;
+}
+int llb_free(llb_dptr p) {
+  NEED_INIT(-1)
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  CU_OK(cudaFree((void *)(uintptr_t)p));
+  return 0;
+}
+int llb_zero(llb_dptr p, size_t bytes) {
+  NEED_INIT(-1)
+  CU_OK(cudaMemsetAsync((void *)(uintptr_t)p, 0, bytes, g_llb.stream));
+  return 0;
+}
+int llb_copy(llb_dptr d, llb_dptr s, size_t bytes) {
+  NEED_INIT(-1)
+  CU_OK(cudaMemcpyAsync((void *)(uintptr_t)d, (const void *)(uintptr_t)s, bytes, cudaMemcpyDeviceToDevice, g_llb.stream));
+  return 0;
+}
+int llb_write(llb_dptr d, const void *h, size_t bytes) {
+  NEED_INIT(-1)
+  CU_OK(cudaMemcpyAsync((void *)(uintptr_t)d, h, bytes, cudaMemcpyHostToDevice, g_llb.stream));
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  return 0;
+}
+int llb_read(void *h, llb_dptr p, size_t bytes) {
+  NEED_INIT(-1)
+  CU_OK(cudaMemcpyAsync(h, (const void *)(uintptr_t)p, bytes, cudaMemcpyDeviceToHost, g_llb.stream));
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  return 0;
+}
+int llb_sync(void) {
+  NEED_INIT(-1)
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+llb_dptr llb_stream(void) { return (llb_dptr)(uintptr_t)g_llb.stream; }
+
+size_t llb_b200_weight_bytes(int fmt, int rows, int cols) { return (size_t)rows * dev_row_bytes(fmt, cols); }
+
+int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src_on_device, llb_dptr dst) {
+  NEED_INIT(-1)
+  const size_t pb = (size_t)rows * pack_row_bytes(fmt, cols);
+  if (!pack_row_bytes(fmt, cols)) return llb_fail("weight_upload: format %d / cols %d", fmt, cols);
+  if (fmt != LLB_FM_Q6_K) {
+    CU_OK(cudaMemcpyAsync((void *)(uintptr_t)dst, src, pb, src_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                          g_llb.stream));
+    if (!src_on_device) CU_OK(cudaStreamSynchronize(g_llb.stream));
+    return 0;
+  }
+  const uint8_t *s = (const uint8_t *)src;
+  void *tmp = nullptr;
+  if (!src_on_device) {
+    CU_OK(cudaMalloc(&tmp, pb));
+    CU_OK(cudaMemcpyAsync(tmp, src, pb, cudaMemcpyHostToDevice, g_llb.stream));
+    s = (const uint8_t *)tmp;
+  }
+  int rc = ops_repack_q6k(g_llb.stream, s, (uint8_t *)(uintptr_t)dst, (size_t)rows * (cols / 256));
+  if (tmp) {
+    cudaStreamSynchronize(g_llb.stream);
+    cudaFree(tmp);
+  }
+  return rc;
+}
+
+int llb_b200_dequant(int fmt, int rows, int cols, llb_dptr w, llb_dptr row_ids, int nrows, llb_dptr out) {
+  NEED_INIT(-1)
+  return ops_dequant_rows(g_llb.stream, fmt, (const uint8_t *)(uintptr_t)w, rows, cols, (const int *)(uintptr_t)row_ids, nrows,
+                          (float *)(uintptr_t)out);
+}
+
+llb_xp *llb_b200_xp_new(int K, int T, int planes) {
+  NEED_INIT(nullptr)
+  if (K % 256 || T < 1 || (planes != 1 && planes != 2) || T * planes > 16) { llb_fail("xp_new: K %d T %d planes %d", K, T, planes); return nullptr; }
+  llb_xp *x = new llb_xp();
+  x->T = T; x->planes = planes;
+  const int NC = T * planes <= 8 ? 8 : 16;
+  size_t bh = (size_t)NC * K * 2, b16 = (size_t)(K / 16) * NC * 4, b32 = (size_t)(K / 32) * NC * 4;
+  if (cudaMalloc(&x->base, bh + b16 + b32) != cudaSuccess) { llb_fail("xp_new: out of memory"); delete x; return nullptr; }
+  cudaMemsetAsync(x->base, 0, bh + b16 + b32, g_llb.stream);
+  x->p.xh = (__half *)x->base;
+  x->p.xs16 = (float *)((char *)x->base + bh);
+  x->p.xs32 = (float *)((char *)x->base + bh + b16);
+  x->p.K = K; x->p.NC = NC;
+  return x;
+}
+void llb_b200_xp_free(llb_xp *xp) {
+  if (!xp) return;
+  cudaStreamSynchronize(g_llb.stream);
+  cudaFree(xp->base);
+  delete xp;
+}
+int llb_b200_xp_set_f32(llb_xp *xp, llb_dptr x) {
+  NEED_INIT(-1)
+  return ops_xp_from_f32(g_llb.stream, (const float *)(uintptr_t)x, xp->T, xp->planes, xp->p);
+}
+int llb_b200_xp_set_bf16(llb_xp *xp, llb_dptr x) {
+  NEED_INIT(-1)
+  if (xp->planes != 1) return llb_fail("xp_set_bf16 needs planes == 1");
+  return ops_xp_from_bf16(g_llb.stream, (const void *)(uintptr_t)x, xp->T, xp->p);
+}
+
+int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const llb_dptr *out, int K, const llb_xp *xp, int ksplit) {
+  NEED_INIT(-1)
+  if (nmat < 1 || nmat > GEMM_MAXMAT) return llb_fail("gemm: nmat %d", nmat);
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.nmat = nmat; a.K = K; a.xp = xp->p; a.planes = xp->planes; a.T = xp->T;
+  int ntiles = 0, total_rows = 0;
+  for (int i = 0; i < nmat; i++) { ntiles += (rows[i] + 15) / 16; total_rows += rows[i]; }
+  a.ksplit = ksplit > 0 ? ksplit : gemm_pick_ksplit(ntiles, K / 256, g_llb.sms);
+  if (a.ksplit > K / 256) a.ksplit = K / 256;
+  const size_t per_split = (size_t)xp->T * total_rows;
+  if (a.ksplit > 1 && per_split * a.ksplit > g_parts_floats) {
+    if (g_parts) { CU_OK(cudaStreamSynchronize(g_llb.stream)); CU_OK(cudaFree(g_parts)); }
+    g_parts_floats = per_split * GEMM_MAXSPLIT;
+    CU_OK(cudaMalloc(&g_parts, g_parts_floats * 4));
+  }
+  size_t off = 0;
+  for (int i = 0; i < nmat; i++) {
+    a.m[i].W = (const uint8_t *)(uintptr_t)w[i];
+    a.m[i].rows = rows[i];
+    a.m[i].ostride = rows[i];
+    a.m[i].tok_slot = nullptr;
+    if (a.ksplit == 1) { a.m[i].out = (float *)(uintptr_t)out[i]; a.m[i].split_stride = 0; }
+    else { a.m[i].out = g_parts + off; a.m[i].split_stride = (long long)per_split; off += (size_t)xp->T * rows[i]; }
+  }
+  if (gemm_launch(g_llb.stream, fmt, a)) return -1;
+  if (a.ksplit > 1)
+    for (int i = 0; i < nmat; i++)
+      if (ops_sum_parts(g_llb.stream, a.m[i].out, a.ksplit, a.m[i].split_stride, xp->T * rows[i], (float *)(uintptr_t)out[i])) return -1;
+  return 0;
+}
+
+int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp, llb_dptr x_dev,
+                       llb_dptr y_dev) {
+  NEED_INIT(-1)
+  CU_OK(cudaMemcpyAsync((void *)(uintptr_t)x_dev, x_bf16, (size_t)T * K * 2, cudaMemcpyHostToDevice, g_llb.stream));
+  if (llb_b200_xp_set_bf16(xp, x_dev)) return -1;
+  if (llb_b200_gemm(fmt, 1, &w, &rows, &y_dev, K, xp, 0)) return -1;
+  CU_OK(cudaMemcpyAsync(y, (const void *)(uintptr_t)y_dev, (size_t)T * rows * 4, cudaMemcpyDeviceToHost, g_llb.stream));
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,144 @@
+// common.cuh -- shared device helpers of the B200 speculative-decoding library.
+//
+// Weight formats are the reference's (host/llb_formats.h:4-15).  Device layouts:
+//   Q8_0  as stored in a pack: row = [cols x int8][cols/32 x f16]          (tools/q8_pack.py:7-10)
+//   Q4_K  as stored: 144-byte super-blocks                                  (tools/qwen35_engine.c:258-272)
+//   Q5_K  as stored: 176-byte super-blocks                                  (tools/qwen35_engine.c:273-289)
+//   Q6_K  re-sliced at load: each 210-byte super-block is padded to 224 bytes
+//         [ql 128 | qh 64 | scales 16 | d 2 | zero 14] so that every super-block starts on a
+//         16-byte boundary (the stored 210-byte stride does not); values are unchanged.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LLB_FM_F32 0
+#define LLB_FM_Q8_0 1
+#define LLB_FM_Q4_K 3
+#define LLB_FM_Q6_K 4
+#define LLB_FM_Q5_K 9
+
+// bytes of one row in the DEVICE layout
+__host__ __device__ inline size_t dev_row_bytes(int fmt, int cols) {
+  switch (fmt) {
+    case LLB_FM_F32: return (size_t)cols * 4;
+    case LLB_FM_Q8_0: return (size_t)cols / 32 * 34;
+    case LLB_FM_Q4_K: return (size_t)cols / 256 * 144;
+    case LLB_FM_Q5_K: return (size_t)cols / 256 * 176;
+    case LLB_FM_Q6_K: return (size_t)cols / 256 * 224;
+  }
+  return 0;
+}
+// bytes of one row as stored in a pack (host/llb_formats.h:17)
+__host__ __device__ inline size_t pack_row_bytes(int fmt, int cols) {
+  return fmt == LLB_FM_Q6_K ? (size_t)cols / 256 * 210 : dev_row_bytes(fmt, cols);
+}
+
+// ---- activation planes -------------------------------------------------------------------------
+// A GEMM reads its T <= 8 activation rows as fp16 "planes": column t (< NH) holds hi = fp16(x),
+// column NH + t holds lo = fp16((x - hi) * 2048), NH = NC / 2, so hi + lo/2048 carries about 22
+// bits of x.  NC is 8 (T <= 4) or 16 (T <= 8).  With planes == 1 all NC columns are independent
+// rows (bf16/fp16 inputs that need no second plane).
+//   xh   [NC][K]    fp16, K-index permuted inside every aligned group of 8: stored order
+//                   0 2 1 3 4 6 5 7, which is the order the tensor-core B fragments consume
+//   xs16 [K/16][NC] f32 sums of the fp16 values over 16 consecutive columns
+//   xs32 [K/32][NC] f32 sums over 32 consecutive columns
+struct XPlanes {
+  __half *xh;
+  float *xs16;
+  float *xs32;
+  int K;
+  int NC;
+};
+#define XP_LO_SCALE 2048.0f
+#define XP_LO_INV (1.0f / 2048.0f)
+
+__host__ __device__ inline int xp_perm(int c) { return (c & ~7) | ((c & 4) | ((c & 1) << 1) | ((c & 2) >> 1)); }
+
+// Warp-cooperative store of 32 consecutive columns (lane = column c0 + lane) of row t.
+__device__ __forceinline__ void xp_store32(const XPlanes &xp, int t, int planes, int c0, float v, int lane) {
+  int c = c0 + lane, NH = xp.NC >> 1;
+  __half hi = __float2half_rn(v);
+  float hif = __half2float(hi);
+  float lof = 0.0f;
+  xp.xh[(size_t)t * xp.K + xp_perm(c)] = hi;
+  if (planes == 2) {
+    __half lo = __float2half_rn((v - hif) * XP_LO_SCALE);
+    lof = __half2float(lo);
+    xp.xh[(size_t)(NH + t) * xp.K + xp_perm(c)] = lo;
+  }
+#pragma unroll
+  for (int m = 1; m < 16; m <<= 1) {
+    hif += __shfl_xor_sync(0xffffffffu, hif, m);
+    lof += __shfl_xor_sync(0xffffffffu, lof, m);
+  }
+  float hi32 = hif + __shfl_xor_sync(0xffffffffu, hif, 16);
+  float lo32 = lof + __shfl_xor_sync(0xffffffffu, lof, 16);
+  if ((lane & 15) == 0) {
+    xp.xs16[(size_t)(c >> 4) * xp.NC + t] = hif;
+    if (planes == 2) xp.xs16[(size_t)(c >> 4) * xp.NC + NH + t] = lof;
+  }
+  if (lane == 0) {
+    xp.xs32[(size_t)(c >> 5) * xp.NC + t] = hi32;
+    if (planes == 2) xp.xs32[(size_t)(c >> 5) * xp.NC + NH + t] = lo32;
+  }
+}
+
+// ---- small PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+// D += A(16x16, row) * B(16x8, col), fp16 inputs, fp32 accumulate
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ldg128(const void *p) { return __ldg((const uint4 *)p); }
+__device__ __forceinline__ uint2 ldg64(const void *p) { return __ldg((const uint2 *)p); }
+__device__ __forceinline__ float2 ldg_f2(const void *p) { return __ldg((const float2 *)p); }
+
+__device__ __forceinline__ float h2f_bits(uint32_t h16) { return __half2float(__ushort_as_half((unsigned short)h16)); }
+
+// ---- per-format scalar dequantisers (bit-exact with tools/qwen35_engine.c:233-307) -------------
+// Each returns weight (row, c) of a matrix in DEVICE layout.  __fmul_rn/__fsub_rn keep the
+// reference's one-rounding-per-operation arithmetic (no FMA contraction).
+__device__ __forceinline__ void q4k_scale_min(const uint8_t *s, int j, int &sc, int &mn) {
+  if (j < 4) { sc = s[j] & 63; mn = s[j + 4] & 63; }
+  else { sc = (s[j + 4] & 15) | ((s[j - 4] >> 6) << 4); mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4); }
+}
+__device__ __forceinline__ float deq_elem(int fmt, const uint8_t *row, int cols, int c) {
+  if (fmt == LLB_FM_F32) return ((const float *)row)[c];
+  if (fmt == LLB_FM_Q8_0) {
+    float d = h2f_bits(((const unsigned short *)(row + cols))[c >> 5]);
+    return __fmul_rn((float)((const int8_t *)row)[c], d);
+  }
+  int b = c >> 8, i = c & 255;
+  if (fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K) {
+    const uint8_t *blk = row + (size_t)b * (fmt == LLB_FM_Q4_K ? 144 : 176);
+    float d = h2f_bits(blk[0] | (blk[1] << 8)), dm = h2f_bits(blk[2] | (blk[3] << 8));
+    int g = i >> 6, hi = (i >> 5) & 1, l = i & 31, sc, mn;
+    q4k_scale_min(blk + 4, 2 * g + hi, sc, mn);
+    const uint8_t *qs = blk + (fmt == LLB_FM_Q4_K ? 16 : 48);
+    int q = hi ? (qs[32 * g + l] >> 4) : (qs[32 * g + l] & 15);
+    if (fmt == LLB_FM_Q5_K) q += ((blk[16 + l] >> (2 * g + hi)) & 1) * 16;
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dm, (float)mn));
+  }
+  if (fmt == LLB_FM_Q6_K) {
+    const uint8_t *blk = row + (size_t)b * 224;
+    int hf = i >> 7, qd = (i >> 5) & 3, l = i & 31;
+    uint8_t lq = blk[64 * hf + 32 * (qd & 1) + l];
+    int nib = qd < 2 ? (lq & 15) : (lq >> 4);
+    int code = (nib | (((blk[128 + 32 * hf + l] >> (2 * qd)) & 3) << 4)) - 32;
+    float d = h2f_bits(blk[208] | (blk[209] << 8));
+    float sc = (float)((const int8_t *)(blk + 192))[8 * hf + 2 * qd + (l >> 4)];
+    return __fmul_rn(__fmul_rn(d, sc), (float)code);
+  }
+  return 0.0f;
+}

@@ -1,0 +1,42 @@
+// host.cuh -- host-side state shared by the translation units of libllb_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "gemm.cuh"
+
+struct LlbCtx {
+  int device = -1;
+  int sms = 0;
+  cudaStream_t stream = nullptr;
+  char err[512] = {0};
+};
+extern LlbCtx g_llb;
+
+inline int llb_fail(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_llb.err, sizeof g_llb.err, fmt, ap);
+  va_end(ap);
+  return -1;
+}
+#define CU_OK(call)                                                                              \
+  do {                                                                                           \
+    cudaError_t e_ = (call);                                                                     \
+    if (e_ != cudaSuccess) return llb_fail("%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+  } while (0)
+
+// gemm.cu
+int gemm_pick_ksplit(int ntiles, int nsb, int sms);
+int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
+int gemm_setup(void);
+
+// ops.cu
+int ops_xp_from_f32(cudaStream_t s, const float *x, int T, int planes, XPlanes xp);
+int ops_xp_from_bf16(cudaStream_t s, const void *x, int T, XPlanes xp);
+int ops_dequant_rows(cudaStream_t s, int fmt, const uint8_t *W, int rows, int cols, const int *row_ids, int nrows, float *out);
+int ops_repack_q6k(cudaStream_t s, const uint8_t *src210, uint8_t *dst224, size_t nblocks);
+int ops_sum_parts(cudaStream_t s, const float *parts, int nsplit, long long split_stride, int n, float *out);

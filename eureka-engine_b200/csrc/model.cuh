@@ -1,0 +1,76 @@
+// model.cuh -- device-side control block and kernel launchers of the verify / draft passes.
+#pragma once
+#include "host.cuh"
+
+#define SPEC_MAXT 8      // rows per pass (k + 1 <= 8, host/llb_host.c:1608 limits k to 0..7)
+#define CONV_RING 16     // conv history slots, indexed by position & 15 (host/llb_host.c:1630)
+#define TOP2_NB 64       // blocks of the first argmax stage
+
+// A set of rows a pass works on: n rows at positions pos0 .. pos0+n-1 with input tokens tok[].
+struct RowSet {
+  int n;
+  int pos0;
+  int tok[SPEC_MAXT];
+  int slot[SPEC_MAXT];   // conv ring slot of each row, (pos0 + t) & 15
+};
+
+// Everything a cycle needs lives on the device, so a cycle is one CUDA graph replay with no host
+// decision inside (the reference makes them on the host: host/llb_host.c:1902-1950).
+struct SpecCtl {
+  RowSet verify;         // rows of the (k+1)-token verify pass
+  RowSet catchup;        // drafter rows over the positions the last cycle served (host/llb_host.c:1815)
+  RowSet chain;          // the drafter's single chained row (host/llb_host.c:1824-1827)
+  int sc;                // DeltaNet state-ring slot holding the committed state
+  int R;                 // ring slots, k + 2 (host/llb_host.c:1621)
+  int k;                 // drafts per cycle
+  int forced;            // > 0: a prompt chunk; the rows and their successors are given, all are served
+  int next_tok[SPEC_MAXT];
+  int max_pos;           // exclusive bound on positions (context capacity)
+  int err;               // sticky device-side error word (0 = none)
+  unsigned long long seq;
+};
+
+// What one cycle reports to the host (written to a pinned ring by the accept kernel).
+struct SpecResult {
+  unsigned long long seq;
+  int p0, T, served, pad;
+  int tin[SPEC_MAXT];            // verify inputs: tin[0] the committed token, then the drafts
+  int ids[SPEC_MAXT];            // argmax of each row; ids[0..served-1] are emitted
+  unsigned int top2[SPEC_MAXT][4];  // id1, bits(v1), id2, bits(v2) per row (tools/qwen35_engine.c:985)
+};
+
+// a tensor that may be split into K-slice partial sums: value(i) = sum_k p[k*stride + i]
+struct PartIn {
+  const float *p;
+  int ns;
+  long long stride;
+};
+__device__ __forceinline__ float part_get(const PartIn &a, size_t i) {
+  float v = a.p[i];
+  for (int k = 1; k < a.ns; k++) v += a.p[(size_t)k * a.stride + i];
+  return v;
+}
+
+struct AttnShape { int H, KV, hd, rope_dim; float eps; };
+struct DeltaShape { int TR, GK, SZ, KC, convd, kdc, vdc; float eps; };
+
+// launchers (ops_model.cu); every kernel covers SPEC_MAXT rows at most and ignores rows >= rs->n
+int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs, int Tmax, float *x);
+int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
+               int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0);
+int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax);
+int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
+              AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax);
+int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
+                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax);
+int op_delta_conv(cudaStream_t s, const float *ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
+                  DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax);
+int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,
+                  DeltaShape sh, float *o, const RowSet *rs, int Tmax);
+int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs,
+                int Tmax);
+int op_top2_part(cudaStream_t s, const float *logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
+int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax);
+int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
+                  float *chain_h, int d);
+int ops_model_setup(void);

@@ -1,0 +1,81 @@
+/* llb_b200.h -- C ABI of libllb_b200.so, a B200 (sm_100a) implementation of the
+ * speculative-decoding path of phenomenon0/eureka-engine.
+ *
+ * Plain C: integers, sizes, device addresses as 64-bit integers (the reference's llb_dptr,
+ * host/llb_backend.h:7-9) and host pointers.  Every call returns 0 / a handle on success and
+ * -1 / 0 on failure with llb_b200_last_error() holding the reason; nothing falls back to the CPU.
+ * All work is queued on one in-order stream per process (the reference's null-stream contract,
+ * host/llb_backend.h:15-18): each call sees the effects of every earlier one.
+ *
+ * Three layers, bottom up:
+ *   1. backend primitives      -- what host/llb_backend.h:7-34 asks of a backend
+ *   2. operator entry points   -- the T-row leaves of tools/payload-spec*.patch, one call each
+ *   3. llb_spec_*              -- the whole draft -> verify -> accept -> commit cycle of
+ *                                 host/llb_host.c:1902-1950 on the device
+ */
+#ifndef LLB_B200_H
+#define LLB_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint64_t llb_dptr; /* host/llb_backend_cuda.h:5 */
+
+#if defined(__GNUC__)
+#define LLB_API __attribute__((visibility("default")))
+#else
+#define LLB_API
+#endif
+
+/* weight formats: the reference registry, host/llb_formats.h:4-15 */
+enum { LLB_F32 = 0, LLB_Q8_0 = 1, LLB_Q4_K = 3, LLB_Q6_K = 4, LLB_Q5_K = 9 };
+
+/* ---- 1. backend primitives ------------------------------------------------------------------ */
+LLB_API int llb_b200_init(int device);              /* binds the process to a GPU; creates the stream     */
+LLB_API const char *llb_b200_last_error(void);
+LLB_API int llb_b200_sm_count(void);
+LLB_API llb_dptr llb_alloc_zero(size_t bytes);      /* host/llb_backend.h:27   (0 on failure)            */
+LLB_API int llb_free(llb_dptr p);
+LLB_API int llb_zero(llb_dptr p, size_t bytes);     /* host/llb_backend.h:29                              */
+LLB_API int llb_copy(llb_dptr d, llb_dptr s, size_t bytes);        /* host/llb_backend.h:30 (device to device, in order) */
+LLB_API int llb_write(llb_dptr d, const void *h, size_t bytes);    /* host/llb_backend.h:31 */
+LLB_API int llb_read(void *h, llb_dptr p, size_t bytes);           /* host/llb_backend.h:32 (synchronises) */
+LLB_API int llb_sync(void);                                        /* host/llb_backend_cuda.h:216-219 */
+LLB_API llb_dptr llb_stream(void);                  /* the cudaStream_t all calls queue on, for event timing */
+
+/* ---- 2. operator entry points --------------------------------------------------------------- */
+/* Bytes of a [rows x cols] matrix in the device layout (Q6_K super-blocks are padded from 210 to
+ * 224 bytes at upload; every other format is stored as in a pack). */
+LLB_API size_t llb_b200_weight_bytes(int fmt, int rows, int cols);
+/* Pack bytes (host pointer, or device address when src_on_device) -> device layout at dst. */
+LLB_API int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src_on_device, llb_dptr dst);
+/* Bit-exact dequantisation of `nrows` rows (row_ids on the device, or 0 for rows 0..nrows-1) into
+ * f32 [nrows][cols].  Replaces llb_embedk / deq_row (tools/payload-kpair.patch:526,
+ * tools/qwen35_engine.c:233-327). */
+LLB_API int llb_b200_dequant(int fmt, int rows, int cols, llb_dptr w, llb_dptr row_ids, int nrows, llb_dptr out_f32);
+
+/* Activation planes of a T-row GEMM input (replaces the two-plane int8 quantiser llb_t_q8x2,
+ * tools/payload-spec2.patch:126-145).  `planes` = 2 keeps about 22 bits of each f32 value in two
+ * fp16 columns (T <= 8); `planes` = 1 takes bf16 rows as they are (T <= 16 rows... T <= 8 used). */
+typedef struct llb_xp llb_xp;
+LLB_API llb_xp *llb_b200_xp_new(int K, int T, int planes);
+LLB_API void llb_b200_xp_free(llb_xp *xp);
+LLB_API int llb_b200_xp_set_f32(llb_xp *xp, llb_dptr x_f32 /* [T][K] */);
+LLB_API int llb_b200_xp_set_bf16(llb_xp *xp, llb_dptr x_bf16 /* [T][K] */);
+
+/* Y_i[t][r] = sum_c W_i[r][c] x[t][c] for up to four matrices of one format sharing x
+ * (replaces llb_spec_gu / _re / _q8 / _q6, tools/payload-spec.patch:226-236).
+ * out_i: f32 [T][rows_i].  ksplit = 0 picks the K-split; scratch for the partial sums is internal. */
+LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const llb_dptr *out, int K, const llb_xp *xp,
+                  int ksplit);
+/* The same through HOST buffers: bf16 x [T][K] in, f32 y [T][rows] out, copies included. */
+LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
+                       llb_dptr x_dev, llb_dptr y_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
