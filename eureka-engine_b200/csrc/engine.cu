@@ -1,0 +1,674 @@
+// engine.cu -- the speculative-decoding engine: weights on the device, per-sequence state, and the
+// draft -> verify -> accept -> commit cycle as one CUDA graph.
+//
+// It replaces, for this path, the reference's host chain host/llb_host.c:1474-1950 (spec_init,
+// mtp_load, spec_mdraft / mtp_rows, spec_rows, spec_attn, spec_ffn, spec_pass).  Differences that
+// are design, not omission:
+//   * every decision of a cycle (argmax, accept length, ring advance, the drafter's catch-up rows,
+//     the next cycle's inputs) is taken on the device (k_accept / k_draft_pick), so a cycle is one
+//     graph launch and one small result record, instead of k blocking reads plus one host round
+//     trip per served row;
+//   * the prompt is fed through the same T-row pass in chunks of k+1 given tokens.
+#include <math.h>
+#include <stdlib.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/llb_b200.h"
+#include "model.cuh"
+
+struct DevMat { uint8_t *w = nullptr; int rows = 0, cols = 0, fmt = -1; };
+struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; };   // K-slice partial sums of one matrix
+static PartIn as_in(const OutBuf &o) { return PartIn{o.p, o.ns, o.stride}; }
+
+struct AttnW { DevMat q, k, v, o; float *qn = nullptr, *kn = nullptr; };
+struct FfnW { DevMat gate, up, down; float *post = nullptr; };
+struct DeltaW { DevMat qkv, z, beta, alpha, out; float *dt = nullptr, *a = nullptr, *conv = nullptr, *norm = nullptr; };
+struct LayerW { bool full = false; float *attn_norm = nullptr; AttnW at; DeltaW dn; FfnW ffn; };
+
+struct TensorRec { uint64_t off, bytes; int rows, cols, fmt; };
+
+struct llb_spec {
+  // configuration (index.tsv #cfg keys, tools/qwen35_engine.c:386-409)
+  int L = 0, d = 0, H = 0, KV = 0, hd = 0, f = 0, V = 0, interval = 4, KC = 4, SZ = 128, GK = 0, TR = 0, vdc = 0, kdc = 0,
+      convd = 0, rope_dim = 64;
+  float rope_base = 1e7f, eps = 1e-6f;
+  int k = 0, Tmax = 1, R = 2, max_ctx = 0, NC = 8;
+  // weights
+  std::vector<void *> allocs;
+  std::vector<LayerW> layer;
+  DevMat embd, head;
+  float *out_norm = nullptr;
+  double *invfreq = nullptr;
+  // drafter
+  bool has_mtp = false;
+  float *mt_enorm = nullptr, *mt_hnorm = nullptr, *mt_attn_norm = nullptr, *mt_shn = nullptr;
+  DevMat mt_eh, mt_head;
+  AttnW mt_at;
+  FfnW mt_ffn;
+  int *mt_ids = nullptr;
+  int mt_nv = 0;
+  // per-sequence state
+  std::vector<float *> Kc, Vc, ring, S;   // per layer (null where not applicable)
+  float *mt_Kc = nullptr, *mt_Vc = nullptr;
+  SpecCtl *ctl = nullptr;
+  SpecResult *res_host = nullptr, *res_dev = nullptr;
+  int res_n = 64;
+  // activations
+  float *x = nullptr, *x1 = nullptr, *hn = nullptr, *e = nullptr, *qn = nullptr, *y = nullptr, *beta = nullptr, *decay = nullptr,
+        *o = nullptr, *logits = nullptr, *t2part = nullptr, *pm = nullptr, *pl = nullptr, *po = nullptr;
+  float *mt_x = nullptr, *mt_hn = nullptr, *chain_h = nullptr, *mt_logits = nullptr;
+  XPlanes xp_d, xp_f, xp_qa, xp_v, xp_2d;
+  OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg;
+  int att_split = 1;
+  // graphs
+  cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr;
+  // host mirror
+  unsigned long long seq = 0;
+  int pos = 0;            // position of the next cycle's row 0
+  bool primed = false;    // prefill done
+  // reference-shaped row serving (llb_spec_pass)
+  SpecResult last;
+  int last_served_idx = 0;
+  bool have_last = false;
+  // statistics, as the reference's "spec:" line (host/llb_host.c:1513-1523)
+  unsigned long long cycles = 0, rows = 0, served = 0, drafted[8] = {0}, accepted[8] = {0};
+};
+
+#define CK(call) do { if ((call)) return -1; } while (0)
+static float bits_float(unsigned int u) { float f; memcpy(&f, &u, 4); return f; }
+
+static void *dalloc(llb_spec *m, size_t bytes) {
+  void *p = nullptr;
+  if (cudaMalloc(&p, bytes ? bytes : 256) != cudaSuccess) { llb_fail("out of device memory (%zu bytes)", bytes); cudaGetLastError(); return nullptr; }
+  cudaMemsetAsync(p, 0, bytes, g_llb.stream);
+  m->allocs.push_back(p);
+  return p;
+}
+static float *falloc(llb_spec *m, size_t n) { return (float *)dalloc(m, n * 4); }
+static int xp_alloc(llb_spec *m, XPlanes &xp, int K) {
+  const int NC = m->NC;
+  size_t bh = (size_t)NC * K * 2, b16 = (size_t)(K / 16) * NC * 4, b32 = (size_t)(K / 32) * NC * 4;
+  char *b = (char *)dalloc(m, bh + b16 + b32);
+  if (!b) return -1;
+  xp.xh = (__half *)b; xp.xs16 = (float *)(b + bh); xp.xs32 = (float *)(b + bh + b16); xp.K = K; xp.NC = NC;
+  return 0;
+}
+
+static int fmt_of(const std::string &ty) {
+  if (ty == "F32") return LLB_FM_F32;
+  if (ty == "Q8_0") return LLB_FM_Q8_0;
+  if (ty == "Q4_K") return LLB_FM_Q4_K;
+  if (ty == "Q6_K") return LLB_FM_Q6_K;
+  if (ty == "Q5_K") return LLB_FM_Q5_K;
+  return -1;
+}
+
+// index.tsv: "#cfg\tKEY\tVALUE" lines, then name off bytes rows cols TYPE [row_bytes fmt]
+// (tools/qwen35_engine.c:379-433)
+static int parse_index(llb_spec *m, const char *text, std::unordered_map<std::string, TensorRec> &tab) {
+  const char *p = text;
+  while (*p) {
+    const char *e = strchr(p, '\n');
+    std::string line(p, e ? (size_t)(e - p) : strlen(p));
+    p = e ? e + 1 : p + line.size();
+    if (line.rfind("#cfg\t", 0) == 0) {
+      size_t t = line.find('\t', 5);
+      if (t == std::string::npos) continue;
+      std::string key = line.substr(5, t - 5), val = line.substr(t + 1);
+      struct { const char *k; int *v; } im[] = {
+        {"n_layers", &m->L}, {"n_heads", &m->H}, {"n_kv_heads", &m->KV}, {"d_model", &m->d}, {"head_dim", &m->hd},
+        {"d_ff", &m->f}, {"vocab_size", &m->V}, {"full_attention_interval", &m->interval}, {"ssm_conv_kernel", &m->KC},
+        {"ssm_state_size", &m->SZ}, {"ssm_group_count", &m->GK}, {"ssm_time_step_rank", &m->TR}, {"ssm_inner_size", &m->vdc},
+        {"linear_key_dim", &m->kdc}, {"linear_conv_dim", &m->convd}, {"rope_dim", &m->rope_dim}};
+      for (auto &kv : im) if (key == kv.k) *kv.v = atoi(val.c_str());
+      if (key == "rope_freq_base") m->rope_base = strtof(val.c_str(), nullptr);
+      if (key == "rms_norm_eps") m->eps = strtof(val.c_str(), nullptr);
+      continue;
+    }
+    if (line.empty() || line[0] == '#') continue;
+    char name[128], ty[32];
+    unsigned long long off, nb;
+    int rows, cols;
+    if (sscanf(line.c_str(), "%127[^\t]\t%llu\t%llu\t%d\t%d\t%31[^\t\n]", name, &off, &nb, &rows, &cols, ty) != 6) continue;
+    int fm = fmt_of(ty);
+    if (fm < 0) return llb_fail("index: tensor %s has unsupported type %s", name, ty);
+    tab[name] = TensorRec{off, nb, rows, cols, fm};
+  }
+  return 0;
+}
+
+// one tensor from pack bytes into its device layout; `dedupe` shares the copy of aliased tensors
+static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, int on_device, void **out,
+                       std::unordered_map<uint64_t, void *> &dedupe) {
+  auto it = dedupe.find(t.off);
+  if (it != dedupe.end()) { *out = it->second; return 0; }
+  const size_t want = (size_t)t.rows * pack_row_bytes(t.fmt, t.cols);
+  if (want != t.bytes) return llb_fail("index: tensor at %llu has %llu bytes, its shape needs %zu", (unsigned long long)t.off,
+                                       (unsigned long long)t.bytes, want);
+  void *dst = dalloc(m, (size_t)t.rows * dev_row_bytes(t.fmt, t.cols));
+  if (!dst) return -1;
+  CK(llb_b200_weight_upload(t.fmt, t.rows, t.cols, pack + t.off, on_device, (llb_dptr)(uintptr_t)dst));
+  dedupe[t.off] = dst;
+  *out = dst;
+  return 0;
+}
+
+static int check_k(const DevMat &w, int rows, int cols, const char *what) {
+  if (w.rows != rows || w.cols != cols) return llb_fail("%s is [%d x %d], the configuration needs [%d x %d]", what, w.rows, w.cols, rows, cols);
+  if (w.fmt == LLB_FM_F32) return llb_fail("%s: F32 matrices have no GEMM kernel", what);
+  if (cols % 256) return llb_fail("%s: %d columns is not a multiple of 256", what, cols);
+  return 0;
+}
+
+// ---- GEMM sites ---------------------------------------------------------------------------------
+struct SiteMat { const DevMat *w; OutBuf *out; const int *tok_slot; float *direct; int direct_stride; };
+
+// Allocate (at init) or reuse the partial-sum buffer of one matrix and record its split.
+static int out_prepare(llb_spec *m, OutBuf &o, int rows, int ks) {
+  if (o.p && o.ns == ks && o.stride == (long long)m->Tmax * rows) return 0;
+  if (o.p && o.ns * o.stride >= (long long)ks * m->Tmax * rows) { o.ns = ks; o.stride = (long long)m->Tmax * rows; return 0; }
+  o.p = falloc(m, (size_t)ks * m->Tmax * rows);
+  if (!o.p) return -1;
+  o.ns = ks; o.stride = (long long)m->Tmax * rows;
+  return 0;
+}
+
+// Enqueue the GEMMs of one site: matrices sharing the activation planes, grouped by format.
+static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, int force_ks) {
+  std::vector<bool> done(mats.size(), false);
+  for (size_t i = 0; i < mats.size(); i++) {
+    if (done[i]) continue;
+    GemmArgs a;
+    memset(&a, 0, sizeof a);
+    a.K = mats[i].w->cols; a.xp = xp; a.planes = 2; a.T = m->Tmax;
+    int ntiles = 0;
+    std::vector<size_t> grp;
+    for (size_t j = i; j < mats.size() && grp.size() < GEMM_MAXMAT; j++)
+      if (!done[j] && mats[j].w->fmt == mats[i].w->fmt) { grp.push_back(j); ntiles += (mats[j].w->rows + 15) / 16; }
+    bool direct = false;
+    for (size_t j : grp) direct = direct || mats[j].direct;
+    int ks = direct ? 1 : force_ks > 0 ? force_ks : gemm_pick_ksplit(ntiles, a.K / 256, g_llb.sms);
+    if (ks > a.K / 256) ks = a.K / 256;
+    a.ksplit = ks;
+    a.nmat = (int)grp.size();
+    for (size_t g = 0; g < grp.size(); g++) {
+      SiteMat &sm = mats[grp[g]];
+      a.m[g].W = sm.w->w; a.m[g].rows = sm.w->rows; a.m[g].tok_slot = sm.tok_slot;
+      if (sm.direct) { a.m[g].out = sm.direct; a.m[g].ostride = sm.direct_stride; a.m[g].split_stride = 0; }
+      else {
+        CK(out_prepare(m, *sm.out, sm.w->rows, ks));
+        a.m[g].out = sm.out->p; a.m[g].ostride = sm.w->rows; a.m[g].split_stride = sm.out->stride;
+      }
+      done[grp[g]] = true;
+    }
+    CK(gemm_launch(g_llb.stream, mats[i].w->fmt, a));
+  }
+  return 0;
+}
+
+// ---- blocks -------------------------------------------------------------------------------------
+// full attention block on rows `rs`: planes xp_d hold the normed input; result partial sums in b_a
+static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const RowSet *rs) {
+  cudaStream_t s = g_llb.stream;
+  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps};
+  CK(site_gemm(m, {{&w.q, &m->b_q, nullptr, nullptr, 0}, {&w.k, &m->b_k, nullptr, nullptr, 0}, {&w.v, &m->b_v, nullptr, nullptr, 0}}, m->xp_d, 0));
+  CK(op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
+  CK(op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
+  CK(site_gemm(m, {{&w.o, &m->b_a, nullptr, nullptr, 0}}, m->xp_qa, 0));
+  return 0;
+}
+
+// x1 = xin + sum(b_a); h = rms(x1) * post -> planes; x1 + down(silu(gate h) * up h) stays split in b_dn
+static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
+  cudaStream_t s = g_llb.stream;
+  CK(op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
+  CK(site_gemm(m, {{&w.gate, &m->b_g, nullptr, nullptr, 0}, {&w.up, &m->b_u, nullptr, nullptr, 0}}, m->xp_d, 0));
+  CK(op_silu_xp(s, as_in(m->b_g), as_in(m->b_u), m->f, m->xp_f, rs, m->Tmax));
+  CK(site_gemm(m, {{&w.down, &m->b_dn, nullptr, nullptr, 0}}, m->xp_f, 0));
+  return 0;
+}
+
+static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const RowSet *rs) {
+  cudaStream_t s = g_llb.stream;
+  DeltaShape sh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
+  // raw qkv rows go straight into the conv ring slot of their position (host/llb_host.c:1747-1749)
+  CK(site_gemm(m, {{&w.qkv, nullptr, &m->ctl->verify.slot[0], ring, m->convd}, {&w.z, &m->b_z, nullptr, nullptr, 0},
+                   {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}}, m->xp_d, 1));
+  CK(op_delta_conv(s, ring, w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
+  CK(op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
+  CK(op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
+  CK(site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
+  return 0;
+}
+
+// the (k+1)-row verify pass (spec_rows, host/llb_host.c:1714-1769)
+static int enq_verify(llb_spec *m) {
+  cudaStream_t s = g_llb.stream;
+  const RowSet *rs = &m->ctl->verify;
+  CK(op_embed(s, m->embd.fmt, m->embd.w, m->d, rs, m->Tmax, m->x));
+  PartIn none{nullptr, 0, 0};
+  for (int il = 0; il < m->L; il++) {
+    const LayerW &l = m->layer[il];
+    // x += previous layer's FFN output (kept as partial sums), h = rms(x) * attn_norm
+    CK(op_norm_xp(s, il ? m->x1 : m->x, il ? as_in(m->b_dn) : none, l.attn_norm, m->eps, m->d, m->x, m->xp_d, 0, nullptr, rs,
+                  m->Tmax, 0));
+    if (l.full) CK(enq_attn(m, l.at, m->Kc[il], m->Vc[il], rs));
+    else CK(enq_delta(m, l.dn, m->ring[il], m->S[il], rs));
+    CK(enq_ffn(m, l.ffn, m->x, m->x1, rs));
+  }
+  CK(op_norm_xp(s, m->x1, as_in(m->b_dn), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
+  CK(site_gemm(m, {{&m->head, &m->b_lg, nullptr, nullptr, 0}}, m->xp_d, 1));
+  CK(op_top2_part(s, m->b_lg.p, m->V, m->V, m->t2part, rs, m->Tmax));
+  return 0;
+}
+
+// the drafter's NextN block over rows `rs` with hidden rows `h` (mtp_rows, host/llb_host.c:1775-1808)
+static int enq_mtp(llb_spec *m, const RowSet *rs, const float *h, bool with_head, int zero_h_at_pos0) {
+  cudaStream_t s = g_llb.stream;
+  PartIn none{nullptr, 0, 0};
+  CK(op_embed(s, m->embd.fmt, m->embd.w, m->d, rs, m->Tmax, m->e));
+  CK(op_norm_xp(s, m->e, none, m->mt_enorm, m->eps, m->d, nullptr, m->xp_2d, 0, nullptr, rs, m->Tmax, 0));
+  CK(op_norm_xp(s, h, none, m->mt_hnorm, m->eps, m->d, nullptr, m->xp_2d, m->d, nullptr, rs, m->Tmax, zero_h_at_pos0));
+  CK(site_gemm(m, {{&m->mt_eh, &m->b_eh, nullptr, nullptr, 0}}, m->xp_2d, 0));
+  // x = eh_proj [e ; h]; normed by attn_norm into the planes; x itself kept in mt_x
+  CK(op_norm_xp(s, nullptr, as_in(m->b_eh), m->mt_attn_norm, m->eps, m->d, m->mt_x, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
+  CK(enq_attn(m, m->mt_at, m->mt_Kc, m->mt_Vc, rs));
+  CK(enq_ffn(m, m->mt_ffn, m->mt_x, m->x1, rs));
+  CK(op_norm_xp(s, m->x1, as_in(m->b_dn), m->mt_shn, m->eps, m->d, nullptr, m->xp_d, 0, m->mt_hn, rs, m->Tmax, 0));
+  if (with_head) {
+    CK(site_gemm(m, {{&m->mt_head, &m->b_mlg, nullptr, nullptr, 0}}, m->xp_d, 1));
+    CK(op_top2_part(s, m->b_mlg.p, m->mt_nv, m->mt_nv, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, rs, m->Tmax));
+  }
+  return 0;
+}
+
+static int enq_cycle(llb_spec *m, bool spec) {
+  cudaStream_t s = g_llb.stream;
+  if (m->has_mtp) {
+    // catch-up over the rows the previous cycle served; the hidden at position 0 is zero
+    // (host/llb_host.c:1815-1817); in a speculative cycle its last row's head gives draft 1
+    CK(enq_mtp(m, &m->ctl->catchup, m->hn, spec && m->k > 0, 0));
+    if (spec) {
+      for (int j = 1; j <= m->k; j++) {
+        CK(op_draft_pick(s, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, m->mt_ids, m->ctl, j > 1, j, m->mt_hn, m->chain_h, m->d));
+        if (j < m->k) CK(enq_mtp(m, &m->ctl->chain, m->chain_h, true, 0));
+      }
+    }
+  }
+  CK(enq_verify(m));
+  CK(op_accept(s, m->t2part, m->ctl, m->res_dev, m->res_n, m->Tmax));
+  return 0;
+}
+
+static int capture(llb_spec *m, bool spec, cudaGraphExec_t *out) {
+  cudaStream_t s = g_llb.stream;
+  cudaGraph_t g = nullptr;
+  CU_OK(cudaStreamSynchronize(s));
+  CU_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  int rc = enq_cycle(m, spec);
+  cudaError_t e = cudaStreamEndCapture(s, &g);
+  if (rc) { if (g) cudaGraphDestroy(g); return -1; }
+  if (e != cudaSuccess) return llb_fail("graph capture: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(out, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return llb_fail("graph instantiate: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// ---- open ---------------------------------------------------------------------------------------
+static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, int on_device, const uint8_t *mtp, size_t mtp_bytes,
+                     int mtp_on_device, int k, int max_ctx, int layers) {
+  std::unordered_map<std::string, TensorRec> tab;
+  CK(parse_index(m, index_text, tab));
+  if (layers > 0 && layers < m->L) m->L = layers;
+  if (k < 0 || k > 7) return llb_fail("k = %d: the path takes 0..7 drafts (host/llb_host.c:1608)", k);
+  if (m->SZ != 128 || m->KC < 2) return llb_fail("ssm_state_size %d / conv kernel %d unsupported", m->SZ, m->KC);
+  if (m->hd != 128 && m->hd != 256) return llb_fail("head_dim %d unsupported", m->hd);
+  if (m->d % 256 || m->f % 256 || m->vdc % 256 || (m->H * m->hd) % 256) return llb_fail("model widths must be multiples of 256");
+  if (m->TR % m->GK || m->H % m->KV) return llb_fail("head counts do not divide");
+  m->k = k; m->Tmax = k + 1; m->R = k + 2; m->max_ctx = max_ctx;
+  m->NC = m->Tmax <= 4 ? 8 : 16;
+  const int d = m->d, qa = m->H * m->hd, kvd = m->KV * m->hd, T = m->Tmax;
+  std::unordered_map<uint64_t, void *> dedupe;
+  auto mat = [&](const std::string &name, DevMat &w) -> int {
+    auto it = tab.find(name);
+    if (it == tab.end()) return llb_fail("pack has no tensor %s", name.c_str());
+    void *p;
+    CK(load_tensor(m, it->second, pack, on_device, &p, dedupe));
+    w.w = (uint8_t *)p; w.rows = it->second.rows; w.cols = it->second.cols; w.fmt = it->second.fmt;
+    return 0;
+  };
+  auto vec = [&](const std::string &name, float **v, int n) -> int {
+    DevMat w;
+    CK(mat(name, w));
+    if (w.fmt != LLB_FM_F32 || w.rows * w.cols != n) return llb_fail("%s must be %d F32 values", name.c_str(), n);
+    *v = (float *)w.w;
+    return 0;
+  };
+  CK(mat("token_embd.weight", m->embd));
+  CK(mat("output.weight", m->head));
+  CK(check_k(m->head, m->V, d, "output.weight"));
+  if (m->embd.rows != m->V || m->embd.cols != d) return llb_fail("token_embd.weight shape");
+  CK(vec("output_norm.weight", &m->out_norm, d));
+  m->layer.resize(m->L);
+  m->Kc.assign(m->L, nullptr); m->Vc.assign(m->L, nullptr); m->ring.assign(m->L, nullptr); m->S.assign(m->L, nullptr);
+  for (int il = 0; il < m->L; il++) {
+    LayerW &l = m->layer[il];
+    std::string p = "blk." + std::to_string(il) + ".";
+    l.full = (il + 1) % m->interval == 0;
+    CK(vec(p + "attn_norm.weight", &l.attn_norm, d));
+    if (l.full) {
+      CK(mat(p + "attn_q.weight", l.at.q)); CK(check_k(l.at.q, 2 * qa, d, "attn_q"));
+      CK(mat(p + "attn_k.weight", l.at.k)); CK(check_k(l.at.k, kvd, d, "attn_k"));
+      CK(mat(p + "attn_v.weight", l.at.v)); CK(check_k(l.at.v, kvd, d, "attn_v"));
+      CK(mat(p + "attn_output.weight", l.at.o)); CK(check_k(l.at.o, d, qa, "attn_output"));
+      CK(vec(p + "attn_q_norm.weight", &l.at.qn, m->hd));
+      CK(vec(p + "attn_k_norm.weight", &l.at.kn, m->hd));
+      m->Kc[il] = falloc(m, (size_t)max_ctx * kvd); m->Vc[il] = falloc(m, (size_t)max_ctx * kvd);
+      if (!m->Kc[il] || !m->Vc[il]) return -1;
+    } else {
+      CK(mat(p + "attn_qkv.weight", l.dn.qkv)); CK(check_k(l.dn.qkv, m->convd, d, "attn_qkv"));
+      CK(mat(p + "attn_gate.weight", l.dn.z)); CK(check_k(l.dn.z, m->vdc, d, "attn_gate"));
+      CK(mat(p + "ssm_beta.weight", l.dn.beta)); CK(check_k(l.dn.beta, m->TR, d, "ssm_beta"));
+      CK(mat(p + "ssm_alpha.weight", l.dn.alpha)); CK(check_k(l.dn.alpha, m->TR, d, "ssm_alpha"));
+      CK(mat(p + "ssm_out.weight", l.dn.out)); CK(check_k(l.dn.out, d, m->vdc, "ssm_out"));
+      CK(vec(p + "ssm_dt.bias", &l.dn.dt, m->TR));
+      CK(vec(p + "ssm_a", &l.dn.a, m->TR));
+      CK(vec(p + "ssm_conv1d.weight", &l.dn.conv, m->convd * m->KC));
+      CK(vec(p + "ssm_norm.weight", &l.dn.norm, m->SZ));
+      m->ring[il] = falloc(m, (size_t)CONV_RING * m->convd);
+      m->S[il] = falloc(m, (size_t)m->R * m->TR * m->SZ * m->SZ);
+      if (!m->ring[il] || !m->S[il]) return -1;
+    }
+    CK(vec(p + "post_attention_norm.weight", &l.ffn.post, d));
+    CK(mat(p + "ffn_gate.weight", l.ffn.gate)); CK(check_k(l.ffn.gate, m->f, d, "ffn_gate"));
+    CK(mat(p + "ffn_up.weight", l.ffn.up)); CK(check_k(l.ffn.up, m->f, d, "ffn_up"));
+    CK(mat(p + "ffn_down.weight", l.ffn.down)); CK(check_k(l.ffn.down, d, m->f, "ffn_down"));
+  }
+  // rope inverse frequencies in double, as the reference computes the angle (tools/qwen35_engine.c:527)
+  {
+    std::vector<double> f(m->rope_dim / 2);
+    for (int i = 0; i < m->rope_dim / 2; i++) f[i] = pow((double)m->rope_base, -2.0 * i / m->rope_dim);
+    m->invfreq = (double *)dalloc(m, f.size() * 8);
+    if (!m->invfreq) return -1;
+    CU_OK(cudaMemcpyAsync(m->invfreq, f.data(), f.size() * 8, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaStreamSynchronize(g_llb.stream));
+  }
+  // drafter: AUX1 named container (host/llb_host.c:1543-1570) or positional MTP1 (:1539-1542)
+  if (mtp && mtp_bytes >= 16) {
+    static const char *names[17] = {"nextn.enorm", "nextn.hnorm", "nextn.eh_proj", "attn_norm", "attn_q", "attn_k", "attn_v",
+                                    "attn_q_norm", "attn_k_norm", "attn_output", "post_attention_norm", "ffn_gate", "ffn_up", "ffn_down",
+                                    "nextn.shared_head_norm", "mtp.head_slice", "mtp.ids"};
+    std::vector<uint8_t> hdr(16 + 72 * 64);
+    size_t hb = mtp_bytes < hdr.size() ? mtp_bytes : hdr.size();
+    if (mtp_on_device) CU_OK(cudaMemcpy(hdr.data(), mtp, hb, cudaMemcpyDeviceToHost)); else memcpy(hdr.data(), mtp, hb);
+    uint64_t off[17], nb[17];
+    int fm[17];
+    bool got[17] = {false};
+    const int mtp1_fmt[17] = {0, 0, LLB_FM_Q4_K, 0, LLB_FM_Q6_K, LLB_FM_Q6_K, LLB_FM_Q6_K, 0, 0, LLB_FM_Q6_K, 0, LLB_FM_Q4_K, LLB_FM_Q4_K,
+                              LLB_FM_Q4_K, 0, LLB_FM_Q6_K, 0};
+    if (!memcmp(hdr.data(), "MTP1", 4)) {
+      uint32_t n; memcpy(&n, hdr.data() + 4, 4);
+      if (n != 17) return llb_fail("MTP1: %u entries, 17 expected", n);
+      for (int j = 0; j < 17; j++) { memcpy(&off[j], hdr.data() + 8 + 16 * j, 8); memcpy(&nb[j], hdr.data() + 16 + 16 * j, 8); fm[j] = mtp1_fmt[j]; got[j] = true; }
+    } else if (!memcmp(hdr.data(), "AUX1", 4)) {
+      uint32_t n; memcpy(&n, hdr.data() + 8, 4);
+      if (n < 17 || n > 64) return llb_fail("AUX1: %u entries", n);
+      for (uint32_t i = 0; i < n; i++) {
+        const uint8_t *e = hdr.data() + 16 + 72 * (size_t)i;
+        char nm[33]; memcpy(nm, e, 32); nm[32] = 0;
+        for (int j = 0; j < 17; j++) if (!strcmp(nm, names[j])) {
+          if (got[j]) return llb_fail("AUX1: duplicate entry %s", nm);
+          uint32_t dt; memcpy(&dt, e + 32, 4); memcpy(&off[j], e + 56, 8); memcpy(&nb[j], e + 64, 8);
+          fm[j] = dt == 0 ? LLB_FM_F32 : dt == 2 ? LLB_FM_Q8_0 : dt == 3 ? LLB_FM_Q4_K : dt == 4 ? LLB_FM_Q6_K : dt == 7 ? LLB_FM_Q5_K : j == 16 ? 0 : -1;
+          got[j] = true;
+        }
+      }
+    } else return llb_fail("drafter image is neither AUX1 nor MTP1");
+    for (int j = 0; j < 17; j++) if (!got[j] || fm[j] < 0 || off[j] + nb[j] > mtp_bytes) return llb_fail("drafter image: entry %s missing or out of range", names[j]);
+    const int nv = (int)(nb[16] / 4);
+    const int rows[17] = {1, 1, d, 1, 2 * qa, kvd, kvd, 1, 1, d, 1, m->f, m->f, d, 1, nv, 1};
+    const int cols[17] = {d, d, 2 * d, d, d, d, d, m->hd, m->hd, qa, d, d, d, m->f, d, d, nv};
+    std::unordered_map<uint64_t, void *> dd;
+    void *ptr[17];
+    for (int j = 0; j < 17; j++) {
+      TensorRec t{off[j], nb[j], rows[j], cols[j], j == 16 ? LLB_FM_F32 : fm[j]};
+      CK(load_tensor(m, t, mtp, mtp_on_device, &ptr[j], dd));
+    }
+    auto MM = [&](int j) { DevMat w; w.w = (uint8_t *)ptr[j]; w.rows = rows[j]; w.cols = cols[j]; w.fmt = fm[j]; return w; };
+    m->mt_enorm = (float *)ptr[0]; m->mt_hnorm = (float *)ptr[1]; m->mt_eh = MM(2); m->mt_attn_norm = (float *)ptr[3];
+    m->mt_at.q = MM(4); m->mt_at.k = MM(5); m->mt_at.v = MM(6); m->mt_at.qn = (float *)ptr[7]; m->mt_at.kn = (float *)ptr[8];
+    m->mt_at.o = MM(9); m->mt_ffn.post = (float *)ptr[10]; m->mt_ffn.gate = MM(11); m->mt_ffn.up = MM(12); m->mt_ffn.down = MM(13);
+    m->mt_shn = (float *)ptr[14]; m->mt_head = MM(15); m->mt_ids = (int *)ptr[16]; m->mt_nv = nv;
+    CK(check_k(m->mt_eh, d, 2 * d, "nextn.eh_proj")); CK(check_k(m->mt_head, nv, d, "mtp.head_slice"));
+    m->mt_Kc = falloc(m, (size_t)max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)max_ctx * kvd);
+    if (!m->mt_Kc || !m->mt_Vc) return -1;
+    m->has_mtp = true;
+  } else if (k > 0) return llb_fail("k = %d drafts need a drafter image", k);
+
+  // activations
+  int big = m->f > m->convd ? m->f : m->convd;
+  m->x = falloc(m, (size_t)T * d); m->x1 = falloc(m, (size_t)T * d); m->hn = falloc(m, (size_t)SPEC_MAXT * d); m->e = falloc(m, (size_t)T * d);
+  m->qn = falloc(m, (size_t)T * qa); m->y = falloc(m, (size_t)T * big); m->beta = falloc(m, (size_t)T * m->TR); m->decay = falloc(m, (size_t)T * m->TR);
+  m->o = falloc(m, (size_t)T * m->vdc); m->t2part = falloc(m, (size_t)2 * SPEC_MAXT * TOP2_NB * 4);
+  m->mt_x = falloc(m, (size_t)T * d); m->mt_hn = falloc(m, (size_t)T * d); m->chain_h = falloc(m, d);
+  m->att_split = (2 * g_llb.sms) / m->KV;
+  if (m->att_split < 1) m->att_split = 1;
+  if (m->att_split > 128) m->att_split = 128;
+  m->pm = falloc(m, (size_t)m->H * T * m->att_split); m->pl = falloc(m, (size_t)m->H * T * m->att_split);
+  m->po = falloc(m, (size_t)m->H * T * m->att_split * m->hd);
+  CK(xp_alloc(m, m->xp_d, d)); CK(xp_alloc(m, m->xp_f, m->f)); CK(xp_alloc(m, m->xp_qa, qa)); CK(xp_alloc(m, m->xp_v, m->vdc));
+  CK(xp_alloc(m, m->xp_2d, 2 * d));
+  m->ctl = (SpecCtl *)dalloc(m, sizeof(SpecCtl));
+  if (!m->x || !m->po || !m->ctl) return -1;
+  CU_OK(cudaHostAlloc((void **)&m->res_host, sizeof(SpecResult) * m->res_n, cudaHostAllocMapped));
+  memset(m->res_host, 0, sizeof(SpecResult) * m->res_n);
+  CU_OK(cudaHostGetDevicePointer((void **)&m->res_dev, m->res_host, 0));
+  CK(ops_model_setup());
+  return 0;
+}
+
+static int ctl_write(llb_spec *m, const SpecCtl &c) {
+  CU_OK(cudaMemcpyAsync(m->ctl, &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  return 0;
+}
+
+static int wait_result(llb_spec *m, SpecResult *out) {
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  const SpecResult *r = &m->res_host[m->seq % (unsigned long long)m->res_n];
+  if (r->seq != m->seq + 1) return llb_fail("cycle %llu did not report (device error word set?)", m->seq);
+  *out = *r;
+  m->seq += 1;
+  return 0;
+}
+
+extern "C" {
+
+LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
+                                size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers) {
+  (void)pack_bytes;
+  if (!g_llb.stream) { llb_fail("llb_b200_init has not been called"); return nullptr; }
+  llb_spec *m = new llb_spec();
+  if (open_impl(m, index_text, (const uint8_t *)pack, pack_on_device, (const uint8_t *)mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers)) {
+    llb_spec_close(m);
+    return nullptr;
+  }
+  // One eager pass with empty row sets sizes and allocates every partial-sum buffer, so that the
+  // captures below allocate nothing.  Then the graphs are captured once; everything that changes
+  // between cycles lives in device memory.
+  if (llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m) || capture(m, true, &m->g_spec) ||
+      capture(m, false, &m->g_prefill) || llb_spec_reset(m)) {
+    llb_spec_close(m);
+    return nullptr;
+  }
+  return m;
+}
+
+LLB_API void llb_spec_close(llb_spec *m) {
+  if (!m) return;
+  cudaStreamSynchronize(g_llb.stream);
+  if (m->g_spec) cudaGraphExecDestroy(m->g_spec);
+  if (m->g_prefill) cudaGraphExecDestroy(m->g_prefill);
+  for (void *p : m->allocs) cudaFree(p);
+  if (m->res_host) cudaFreeHost(m->res_host);
+  delete m;
+}
+
+// zero the sequence state (host/llb_host.c:1915-1928): KV rows are overwritten before they are
+// read, so only the conv rings and the committed DeltaNet slot need clearing
+LLB_API int llb_spec_reset(llb_spec *m) {
+  for (int il = 0; il < m->L; il++) {
+    if (m->ring[il]) CU_OK(cudaMemsetAsync(m->ring[il], 0, (size_t)CONV_RING * m->convd * 4, g_llb.stream));
+    if (m->S[il]) CU_OK(cudaMemsetAsync(m->S[il], 0, (size_t)m->R * m->TR * m->SZ * m->SZ * 4, g_llb.stream));
+  }
+  CU_OK(cudaMemsetAsync(m->hn, 0, (size_t)SPEC_MAXT * m->d * 4, g_llb.stream));
+  SpecCtl c;
+  memset(&c, 0, sizeof c);
+  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq;
+  CK(ctl_write(m, c));
+  m->pos = 0; m->primed = false; m->have_last = false;
+  m->cycles = m->rows = m->served = 0;
+  memset(m->drafted, 0, sizeof m->drafted); memset(m->accepted, 0, sizeof m->accepted);
+  return 0;
+}
+
+// Feed the prompt.  Positions 0 .. n-2 run through the verify pass in chunks of k+1 given rows;
+// the last prompt token becomes the first speculative cycle's committed input, exactly where the
+// reference's first cycle after a prompt starts (host/llb_host.c:1911, pos = n-1).
+LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
+  if (n < 1) return llb_fail("prefill: empty prompt");
+  if (n + m->Tmax + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
+  for (int i = 0; i < n; i++) if (ids[i] < 0 || ids[i] >= m->V) return llb_fail("prefill: token %d out of range", ids[i]);
+  CK(llb_spec_reset(m));
+  SpecCtl c;
+  memset(&c, 0, sizeof c);
+  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq;
+  // the drafter's row for position 0 pairs token 0 with a zero hidden (host/llb_host.c:1815-1817)
+  c.catchup.n = 1; c.catchup.pos0 = 0; c.catchup.tok[0] = ids[0];
+  c.verify.n = m->Tmax; c.verify.pos0 = 0; c.verify.tok[0] = ids[0];
+  for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
+  CK(ctl_write(m, c));
+  int p = 0;
+  while (p < n - 1) {
+    const int rows = (n - 1 - p) < m->Tmax ? (n - 1 - p) : m->Tmax;
+    // rows and their successors are given; only these fields of the control block change
+    struct { int n, pos0, tok[SPEC_MAXT], slot[SPEC_MAXT]; } v;
+    v.n = rows; v.pos0 = p;
+    for (int r = 0; r < SPEC_MAXT; r++) { v.tok[r] = r < rows ? ids[p + r] : 0; v.slot[r] = (p + r) & (CONV_RING - 1); }
+    int tail[1 + SPEC_MAXT];
+    tail[0] = rows;  // forced
+    for (int r = 0; r < SPEC_MAXT; r++) tail[1 + r] = r < rows ? ids[p + r + 1] : 0;
+    CU_OK(cudaMemcpyAsync(&m->ctl->verify, &v, sizeof v, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaMemcpyAsync(&m->ctl->forced, tail, sizeof tail, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaGraphLaunch(m->g_prefill, g_llb.stream));
+    SpecResult r;
+    CK(wait_result(m, &r));
+    if (r.served != rows) return llb_fail("prefill: chunk at %d served %d of %d rows", p, r.served, rows);
+    p += rows;
+  }
+  if (n == 1) {
+    // nothing ran: the first cycle starts at position 0 with the single prompt token
+  }
+  m->pos = n - 1;
+  m->primed = true;
+  return 0;
+}
+
+// One speculative cycle.  ids_out[0..*n_out-1] are the emitted tokens; top2_out (may be null) gets
+// [id1, bits1, id2, bits2] of each emitted row.
+LLB_API int llb_spec_cycle(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2_out) {
+  if (!m->primed) return llb_fail("llb_spec_cycle before llb_spec_prefill");
+  // every row of the cycle, and the drafter's chained rows, must fit: no clipped cycles
+  if (m->pos + m->Tmax >= m->max_ctx) return llb_fail("context of %d positions is full", m->max_ctx);
+  CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
+  SpecResult r;
+  CK(wait_result(m, &r));
+  if (r.p0 != m->pos) return llb_fail("cycle ran at position %d, host expected %d", r.p0, m->pos);
+  for (int i = 0; i < r.served; i++) {
+    ids_out[i] = r.ids[i];
+    if (top2_out) memcpy(top2_out + 4 * i, r.top2[i], 16);
+  }
+  *n_out = r.served;
+  m->pos += r.served;
+  m->cycles += 1; m->rows += (unsigned long long)r.T; m->served += (unsigned long long)r.served;
+  for (int j = 1; j < r.T; j++) { m->drafted[j] += 1; m->accepted[j] += r.served > j; }
+  m->last = r; m->have_last = true; m->last_served_idx = 0;
+  return 0;
+}
+
+// Generate `steps` tokens after the prompt (greedy).  Returns the number written (== steps).
+LLB_API int llb_spec_generate(llb_spec *m, int steps, int *ids, uint32_t *top2) {
+  int out = 0;
+  while (out < steps) {
+    int got[SPEC_MAXT], n = 0;
+    uint32_t t2[SPEC_MAXT * 4];
+    CK(llb_spec_cycle(m, got, &n, t2));
+    for (int i = 0; i < n && out < steps; i++, out++) {
+      ids[out] = got[i];
+      if (top2) memcpy(top2 + 4 * out, t2 + 4 * i, 16);
+    }
+  }
+  return out;
+}
+
+// The reference's per-token entry (spec_pass, host/llb_host.c:1902-1950): the caller hands in
+// (pos, tok) and gets the row's four words y = [v1, id1, v2, id2] (ids as floats, as the device
+// argmax writes them).  Rows of the running cycle are served while (pos, tok) follows the cycle;
+// otherwise a new cycle starts there.  Because acceptance is committed on the device under the
+// greedy rule, a caller that leaves the greedy stream gets "a step out of order", the reference's
+// own error for that case (host/llb_host.c:1929-1930).
+LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y) {
+  if (m->have_last && m->last_served_idx < m->last.served && pos == m->last.p0 + m->last_served_idx &&
+      (m->last_served_idx == 0 || tok == m->last.ids[m->last_served_idx - 1])) {
+    const int r = m->last_served_idx++;
+    y[0] = bits_float(m->last.top2[r][1]); y[1] = (float)m->last.top2[r][0];
+    y[2] = bits_float(m->last.top2[r][3]); y[3] = (float)m->last.top2[r][2];
+    return 0;
+  }
+  return llb_fail("LLB_SPEC: a step out of order");
+}
+
+LLB_API int llb_spec_position(const llb_spec *m) { return m->pos; }
+
+LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out /* cycles, rows, served, drafted[8], accepted[8] */) {
+  out[0] = m->cycles; out[1] = m->rows; out[2] = m->served;
+  for (int j = 0; j < 8; j++) { out[3 + j] = m->drafted[j]; out[11 + j] = m->accepted[j]; }
+  return 0;
+}
+
+// State read-back for parity checks: what = 0 committed DeltaNet state of layer il [TR][128][128],
+// 1 the K row and 2 the V row of position `pos` in layer il, 3 the conv ring row of position `pos`,
+// 4 the trunk's output-normed hidden row `pos` (0..k) of the last pass, 5 the drafter's K row.
+LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n) {
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  const float *src = nullptr;
+  size_t have = 0;
+  const int kvd = m->KV * m->hd;
+  if (what == 0 && il < m->L && m->S[il]) {
+    SpecCtl c;
+    CU_OK(cudaMemcpy(&c, m->ctl, sizeof c, cudaMemcpyDeviceToHost));
+    have = (size_t)m->TR * m->SZ * m->SZ; src = m->S[il] + (size_t)c.sc * have;
+  } else if (what == 1 && il < m->L && m->Kc[il]) { have = kvd; src = m->Kc[il] + (size_t)pos * kvd; }
+  else if (what == 2 && il < m->L && m->Vc[il]) { have = kvd; src = m->Vc[il] + (size_t)pos * kvd; }
+  else if (what == 3 && il < m->L && m->ring[il]) { have = m->convd; src = m->ring[il] + (size_t)(pos & (CONV_RING - 1)) * m->convd; }
+  else if (what == 4) { have = m->d; src = m->hn + (size_t)pos * m->d; }
+  else if (what == 5 && m->mt_Kc) { have = kvd; src = m->mt_Kc + (size_t)pos * kvd; }
+  else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
+  if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
+  CU_OK(cudaMemcpy(out, src, have * 4, cudaMemcpyDeviceToHost));
+  return (int)have;
+}
+
+// The logits of verify row r of the last pass (f32 [V]), for the logit-tolerance parity check.
+LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out) {
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  if (m->b_lg.ns != 1) return llb_fail("logits are split");
+  CU_OK(cudaMemcpy(out, m->b_lg.p + (size_t)r * m->V, (size_t)m->V * 4, cudaMemcpyDeviceToHost));
+  return 0;
+}
+
+}  // extern "C"

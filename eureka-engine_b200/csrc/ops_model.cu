@@ -1,0 +1,574 @@
+// ops_model.cu -- the non-GEMM device ops of the verify / draft passes, T rows per launch.
+// Each kernel restates one or more of the reference's llb_t_* row kernels
+// (tools/payload-spec2.patch:35-483); the arithmetic follows the CPU engine
+// (tools/qwen35_engine.c:510-778), which is what parity is judged against.
+#include "model.cuh"
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+// sum over the block; every thread gets the result (red: >= 32 floats of shared memory)
+__device__ __forceinline__ float block_sum(float v, float *red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.0f;
+  for (int i = 0; i < nw; i++) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ---- embedding rows (llb_embedk, tools/payload-kpair.patch:526) ---------------------------------
+__global__ void k_embed(int fmt, const uint8_t *__restrict__ W, int d, const RowSet *__restrict__ rs, float *__restrict__ x) {
+  const int t = blockIdx.y;
+  if (t >= rs->n) return;
+  const uint8_t *row = W + (size_t)rs->tok[t] * dev_row_bytes(fmt, d);
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < d; c += gridDim.x * blockDim.x) x[(size_t)t * d + c] = deq_elem(fmt, row, d, c);
+}
+int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs, int Tmax, float *x) {
+  k_embed<<<dim3((d + 255) / 256, Tmax), 256, 0, s>>>(fmt, W, d, rs, x);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- residual add + RMSNorm -> activation planes (llb_t_rnaddq / llb_t_rnormq,
+// tools/payload-spec2.patch:35-112; rms_norm tools/qwen35_engine.c:510-515) ----------------------
+// v = xin + sum(partials); xout = v (optional); h = (v * s) * w, s = 1/sqrt(mean(v^2) + eps);
+// h goes to the planes at column offset xp_col0 and, optionally, to hn_out as f32.
+__global__ void k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
+                          float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
+                          const RowSet *__restrict__ rs, int zero_if_pos0) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  if (t >= rs->n) return;
+  const bool zero = zero_if_pos0 && (rs->pos0 + t == 0);
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float v = (zero || !xin) ? 0.0f : xin[(size_t)t * d + c];
+    if (add.p && !zero) v += part_get(add, (size_t)t * d + c);
+    rowbuf[c] = v;
+    if (xout) xout[(size_t)t * d + c] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float sc = 1.0f / sqrtf(ss / (float)d + eps);
+  const int lane = threadIdx.x & 31;
+  for (int c0 = (threadIdx.x & ~31); c0 < d; c0 += blockDim.x) {
+    float h = rowbuf[c0 + lane] * sc * w[c0 + lane];
+    if (hn_out) hn_out[(size_t)t * d + c0 + lane] = h;
+    xp_store32(xp, t, 2, xp_col0 + c0, h, lane);
+  }
+}
+int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
+               int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0) {
+  if (d % 32) return llb_fail("norm: d %d", d);
+  k_norm_xp<<<Tmax, 512, (size_t)d * 4, s>>>(xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- silu(gate) * up -> planes (llb_t_siluq, tools/payload-spec2.patch:114-124) -----------------
+__global__ void k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *__restrict__ rs) {
+  const int t = blockIdx.y, lane = threadIdx.x & 31;
+  if (t >= rs->n) return;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31;
+  if (c0 >= f) return;
+  const size_t i = (size_t)t * f + c0 + lane;
+  xp_store32(xp, t, 2, c0, silu_f(part_get(g, i)) * part_get(u, i), lane);
+}
+int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax) {
+  if (f % 32) return llb_fail("silu: f %d", f);
+  k_silu_xp<<<dim3((f + 255) / 256, Tmax), 256, 0, s>>>(g, u, f, xp, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- per-head QK RMSNorm + partial NEOX RoPE; K and V rows straight into their cache slots
+// (llb_t_qkr, tools/payload-spec2.patch:159-204; tools/qwen35_engine.c:523-533, 667-690) ----------
+// grid (H + 2 KV, Tmax), block hd.  q input rows are [H][q(hd) | gate(hd)].
+__global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__ qn_w, const float *__restrict__ kn_w,
+                         const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, float *__restrict__ Kc,
+                         float *__restrict__ Vc, const RowSet *__restrict__ rs) {
+  extern __shared__ float hv[];
+  __shared__ float red[32];
+  const int t = blockIdx.y, b = blockIdx.x, i = threadIdx.x, hd = sh.hd;
+  if (t >= rs->n) return;
+  const int pos = rs->pos0 + t, kvd = sh.KV * hd;
+  if (b >= sh.H + sh.KV) {  // V row: copied
+    const int g = b - sh.H - sh.KV;
+    Vc[(size_t)pos * kvd + g * hd + i] = part_get(v, (size_t)t * kvd + g * hd + i);
+    return;
+  }
+  float x;
+  const float *nw;
+  float *dst;
+  if (b < sh.H) {
+    x = part_get(q, (size_t)t * 2 * sh.H * hd + (size_t)b * 2 * hd + i);
+    nw = qn_w;
+    dst = qout + ((size_t)t * sh.H + b) * hd;
+  } else {
+    const int g = b - sh.H;
+    x = part_get(k, (size_t)t * kvd + g * hd + i);
+    nw = kn_w;
+    dst = Kc + (size_t)pos * kvd + g * hd;
+  }
+  const float ss = block_sum(x * x, red);
+  const float sc = 1.0f / sqrtf(ss / (float)hd + sh.eps);
+  const float y = x * sc * nw[i];
+  hv[i] = y;
+  __syncthreads();
+  float out = y;
+  const int half = sh.rope_dim >> 1;
+  if (i < sh.rope_dim) {
+    const int pi = i < half ? i : i - half;
+    const float th = (float)((double)pos * invfreq[pi]);
+    const float c = (float)cos((double)th), sn = (float)sin((double)th);
+    const float a = hv[pi], bb = hv[pi + half];
+    out = i < half ? __fsub_rn(__fmul_rn(a, c), __fmul_rn(bb, sn)) : __fadd_rn(__fmul_rn(a, sn), __fmul_rn(bb, c));
+  }
+  dst[i] = out;
+}
+int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
+              AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax) {
+  k_qkrope<<<dim3(sh.H + 2 * sh.KV, Tmax), sh.hd, (size_t)sh.hd * 4, s>>>(q, k, v, qn_w, kn_w, invfreq, sh, qout, Kc, Vc, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- split-K GQA attention of the T query rows over the KV cache --------------------------------
+// (llb_t_attn4 computes one block per (head, row) with no split, tools/payload-spec2.patch:208-315;
+// the reference's own split-K form is llb_attn4_sk8, tools/payload-sk8add.patch:16-93.)
+// grid (KV, nsplit), 8 warps.  One block streams a slice of one kv head's K and V rows ONCE through
+// shared memory for all G = H/KV query heads x T rows; warp w owns queries w*QW .. w*QW+QW-1.
+// Output: per (query, split) a running max m, a sum l and an unnormalised accumulator o[hd].
+#define ATT_PT 32
+template <int HD, int QW>
+__global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, const float *__restrict__ Kc,
+                                                   const float *__restrict__ Vc, AttnShape sh, int Tmax, float *__restrict__ pm,
+                                                   float *__restrict__ pl, float *__restrict__ po, const RowSet *__restrict__ rs) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int KS = HD + 4, DPL = HD / 32;
+  const int G = sh.H / sh.KV, NQ = G * Tmax, nsplit = gridDim.y;
+  float *qs = sm;                         // [NQ][HD]
+  float *Ks = qs + (size_t)NQ * HD;       // [PT][HD + 4]
+  float *Vs = Ks + ATT_PT * KS;           // [PT][HD]
+  const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = rs->n, pos0 = rs->pos0, total = pos0 + n, kvd = sh.KV * HD;
+  // slices of at least 64 positions: short contexts use the first few blocks only
+  const int per = max(64, (total + nsplit - 1) / nsplit), s0 = split * per, s1 = min(total, s0 + per);
+  // query (g, r) -> local index g * Tmax + r; global head h = kvh * G + g
+  for (int i = threadIdx.x; i < NQ * HD; i += blockDim.x) {
+    int ql = i / HD, dd = i - ql * HD, g = ql / Tmax, r = ql - g * Tmax;
+    qs[i] = r < n ? q[((size_t)r * sh.H + kvh * G + g) * HD + dd] : 0.0f;
+  }
+  float m[QW], l[QW], acc[QW][DPL];
+#pragma unroll
+  for (int a = 0; a < QW; a++) {
+    m[a] = -INFINITY; l[a] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DPL; i++) acc[a][i] = 0.0f;
+  }
+  const float scale = 1.0f / sqrtf((float)HD);
+  for (int p0 = s0; p0 < s1; p0 += ATT_PT) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < ATT_PT * (HD / 4); i += blockDim.x) {
+      int pp = i / (HD / 4), c4 = i - pp * (HD / 4), p = p0 + pp;
+      float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+      if (p < s1) {
+        kk = *(const float4 *)(Kc + (size_t)p * kvd + kvh * HD + 4 * c4);
+        vv = *(const float4 *)(Vc + (size_t)p * kvd + kvh * HD + 4 * c4);
+      }
+      *(float4 *)(Ks + pp * KS + 4 * c4) = kk;
+      *(float4 *)(Vs + pp * HD + 4 * c4) = vv;
+    }
+    __syncthreads();
+    float pr[QW];
+    bool any = false;
+#pragma unroll
+    for (int a = 0; a < QW; a++) {
+      const int ql = warp * QW + a;
+      pr[a] = 0.0f;
+      if (ql >= NQ) continue;
+      const int r = ql % Tmax;
+      if (r >= n) continue;
+      // lane <-> position p0 + lane
+      const float4 *kr = (const float4 *)(Ks + lane * KS);
+      const float4 *qr = (const float4 *)(qs + (size_t)ql * HD);
+      float sdot = 0.0f;
+#pragma unroll 8
+      for (int i = 0; i < HD / 4; i++) {
+        float4 kk = kr[i], qq = qr[i];
+        sdot += kk.x * qq.x + kk.y * qq.y + kk.z * qq.z + kk.w * qq.w;
+      }
+      const int p = p0 + lane;
+      float sc = (p < s1 && p <= pos0 + r) ? sdot * scale : -INFINITY;
+      const float mt = warp_max(sc);
+      if (mt == -INFINITY) continue;      // the whole tile is masked for this query
+      const float mn = fmaxf(m[a], mt);
+      const float corr = expf(m[a] - mn);  // exp(-inf) = 0 on the first tile
+      const float e = expf(sc - mn);
+      l[a] = l[a] * corr + warp_sum(e);
+      m[a] = mn;
+#pragma unroll
+      for (int i = 0; i < DPL; i++) acc[a][i] *= corr;
+      pr[a] = e;
+      any = true;
+    }
+    if (any) {
+      for (int pp = 0; pp < ATT_PT; pp++) {
+        float vv[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; i++) vv[i] = Vs[pp * HD + lane + 32 * i];
+#pragma unroll
+        for (int a = 0; a < QW; a++) {
+          const float e = __shfl_sync(0xffffffffu, pr[a], pp);
+#pragma unroll
+          for (int i = 0; i < DPL; i++) acc[a][i] += e * vv[i];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < QW; a++) {
+    const int ql = warp * QW + a;
+    if (ql >= NQ) continue;
+    const int g = ql / Tmax, r = ql - g * Tmax;
+    if (r >= n) continue;
+    const size_t qi = ((size_t)(kvh * G + g) * Tmax + r) * nsplit + split;
+    if (lane == 0) { pm[qi] = m[a]; pl[qi] = l[a]; }
+    if (m[a] == -INFINITY) continue;   // an empty slice: the merge skips it on m alone
+#pragma unroll
+    for (int i = 0; i < DPL; i++) po[qi * HD + lane + 32 * i] = acc[a][i];
+  }
+}
+
+// merge the splits, normalise, apply the sigmoid output gate, write the planes of attn_output's input
+// (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
+__global__ void k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
+                            AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *__restrict__ rs) {
+  const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = sh.hd, lane = threadIdx.x & 31;
+  if (t >= rs->n) return;
+  const size_t qb = ((size_t)h * Tmax + t) * nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; s++) M = fmaxf(M, pm[qb + s]);
+  float L = 0.0f, o = 0.0f;
+  for (int s = 0; s < nsplit; s++) {
+    const float ms = pm[qb + s];
+    if (ms == -INFINITY) continue;
+    const float w = expf(ms - M);
+    L += pl[qb + s] * w;
+    o += po[(qb + s) * hd + i] * w;
+  }
+  const float gate = part_get(qg, (size_t)t * 2 * sh.H * hd + (size_t)h * 2 * hd + hd + i);
+  xp_store32(xp, t, 2, h * hd + (i & ~31), (o / L) * sigmoid_f(gate), lane);
+}
+
+template <int HD> static int attn_launch(cudaStream_t s, int QW, dim3 grid, size_t smem, const float *q, const float *Kc,
+                                         const float *Vc, AttnShape sh, int Tmax, float *pm, float *pl, float *po, const RowSet *rs) {
+#define ATT(Q) case Q: k_attn_part<HD, Q><<<grid, 256, smem, s>>>(q, Kc, Vc, sh, Tmax, pm, pl, po, rs); break;
+  switch (QW) { ATT(1) ATT(2) ATT(3) ATT(4) ATT(6) default: return llb_fail("attention: %d queries per warp", QW); }
+#undef ATT
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+static size_t attn_smem(int hd, int NQ) { return ((size_t)NQ * hd + ATT_PT * (hd + 4) + ATT_PT * hd) * 4; }
+static int attn_qw(int NQ) { int q = (NQ + 7) / 8; return q == 5 ? 6 : q; }
+
+int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
+                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax) {
+  const int G = sh.H / sh.KV, NQ = G * Tmax, QW = attn_qw(NQ);
+  if (QW > 6) return llb_fail("attention: %d queries per kv head", NQ);
+  const size_t smem = attn_smem(sh.hd, NQ);
+  dim3 grid(sh.KV, nsplit);
+  int rc;
+  if (sh.hd == 128) rc = attn_launch<128>(s, QW, grid, smem, q, Kc, Vc, sh, Tmax, pm, pl, po, rs);
+  else if (sh.hd == 256) rc = attn_launch<256>(s, QW, grid, smem, q, Kc, Vc, sh, Tmax, pm, pl, po, rs);
+  else return llb_fail("attention: head_dim %d", sh.hd);
+  if (rc) return rc;
+  k_attn_comb<<<dim3(sh.H, Tmax), sh.hd, 0, s>>>(pm, pl, po, qg, sh, nsplit, Tmax, xp, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int HD> static int attn_setup_hd() {
+  const int mx = (int)attn_smem(HD, 48);
+#define ATT(Q) CU_OK(cudaFuncSetAttribute(k_attn_part<HD, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx));
+  ATT(1) ATT(2) ATT(3) ATT(4) ATT(6)
+#undef ATT
+  return 0;
+}
+int ops_model_setup(void) {
+  if (attn_setup_hd<128>() || attn_setup_hd<256>()) return -1;
+  return 0;
+}
+
+// ---- gated DeltaNet ------------------------------------------------------------------------------
+// conv1d + SiLU over the position-indexed ring, and the per-head gates
+// (llb_t_midconv, tools/payload-spec2.patch:319-350; tools/qwen35_engine.c:589-602).
+// grid (ceil(convd/256) + 1, Tmax): the last block computes beta = sigmoid(b), decay = exp(softplus(a + dt) * ssm_a).
+__global__ void k_delta_conv(const float *__restrict__ ring, const float *__restrict__ cw, PartIn bp, PartIn ap,
+                             const float *__restrict__ dt, const float *__restrict__ sa, DeltaShape sh, float *__restrict__ y,
+                             float *__restrict__ beta, float *__restrict__ decay, const RowSet *__restrict__ rs) {
+  const int t = blockIdx.y;
+  if (t >= rs->n) return;
+  if (blockIdx.x == gridDim.x - 1) {
+    for (int h = threadIdx.x; h < sh.TR; h += blockDim.x) {
+      const float b = part_get(bp, (size_t)t * sh.TR + h), a = part_get(ap, (size_t)t * sh.TR + h);
+      beta[t * sh.TR + h] = 1.0f / (1.0f + (float)exp((double)-b));
+      const float x = a + dt[h];
+      const float sp = x > 20.0f ? x : (float)log1p((double)(float)exp((double)(x < 88.0f ? x : 88.0f)));
+      decay[t * sh.TR + h] = (float)exp((double)(sp * sa[h]));
+    }
+    return;
+  }
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= sh.convd) return;
+  const int pos = rs->pos0 + t;
+  float acc = 0.0f;
+  for (int k = 0; k < sh.KC; k++) {  // tap KC-1 is the current token (tools/qwen35_engine.c:599-600)
+    const int slot = (pos - (sh.KC - 1) + k) & (CONV_RING - 1);
+    acc = __fadd_rn(acc, __fmul_rn(ring[(size_t)slot * sh.convd + c], cw[c * sh.KC + k]));
+  }
+  y[(size_t)t * sh.convd + c] = silu_f(acc);
+}
+int op_delta_conv(cudaStream_t s, const float *ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
+                  DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax) {
+  if (sh.KC > CONV_RING / 2) return llb_fail("conv kernel %d", sh.KC);
+  k_delta_conv<<<dim3((sh.convd + 255) / 256 + 1, Tmax), 256, 0, s>>>(ring, cw, bp, ap, dt, sa, sh, y, beta, decay, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// The recurrent scan over the T rows with per-row state checkpoints
+// (llb_t_l2qk + llb_t_gdl, tools/payload-spec2.patch:353-410; tools/qwen35_engine.c:610-646).
+// grid (TR, 4), 128 threads: block (hh, jq) owns state rows j = 32 jq .. 32 jq + 31 of head hh, 32
+// registers of state per thread (thread = row jr, column quarter cq).  The state is read from ring
+// slot sc and the state after row r is written to slot (sc + r + 1) % R, so rejecting rows costs
+// nothing: the next cycle simply starts from the slot of the last served row.
+__global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const SpecCtl *__restrict__ ctl,
+                                                    const float *__restrict__ y, const float *__restrict__ beta,
+                                                    const float *__restrict__ decay, DeltaShape sh, float *__restrict__ o,
+                                                    const RowSet *__restrict__ rs) {
+  __shared__ float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128], vs[SPEC_MAXT][32];
+  __shared__ float red[32];
+  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs->n;
+  const int g = hh % sh.GK;   // value head hh reads q/k group hh % GK (tile, tools/qwen35_engine.c:621-626)
+  for (int t = 0; t < n; t++) {
+    const float qv = y[(size_t)t * sh.convd + g * 128 + tid], kv = y[(size_t)t * sh.convd + sh.kdc + g * 128 + tid];
+    const float sq = block_sum(qv * qv, red), sk = block_sum(kv * kv, red);
+    const float nq = sqrtf(sq), nk = sqrtf(sk);
+    const float iq = (1.0f / (nq > sh.eps ? nq : sh.eps)) / sqrtf(128.0f), ik = 1.0f / (nk > sh.eps ? nk : sh.eps);
+    qs[t][tid] = qv * iq;
+    ks[t][tid] = kv * ik;
+    if (tid < 32) vs[t][tid] = y[(size_t)t * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + tid];
+  }
+  __syncthreads();
+  const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
+  const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
+  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 32 * cq;
+  float st[32];
+  {
+    const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { float4 v = src[i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
+  }
+  for (int t = 0; t < n; t++) {
+    const float dec = decay[t * sh.TR + hh], bt = beta[t * sh.TR + hh];
+    float kvacc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) { st[i] *= dec; kvacc += st[i] * ks[t][32 * cq + i]; }
+    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 1);
+    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 2);
+    const float delta = (vs[t][jr] - kvacc) * bt;
+    float oacc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) { st[i] += ks[t][32 * cq + i] * delta; oacc += st[i] * qs[t][32 * cq + i]; }
+    oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
+    oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
+    if (cq == 0) o[(size_t)t * sh.vdc + hh * 128 + 32 * jq + jr] = oacc;
+    float4 *dst = (float4 *)(S + (size_t)((sc + t + 1) % R) * slot_sz + off);
+#pragma unroll
+    for (int i = 0; i < 8; i++) dst[i] = make_float4(st[4 * i], st[4 * i + 1], st[4 * i + 2], st[4 * i + 3]);
+  }
+}
+int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,
+                  DeltaShape sh, float *o, const RowSet *rs, int Tmax) {
+  (void)Tmax;
+  if (sh.SZ != 128) return llb_fail("DeltaNet state size %d (only 128, as host/llb_host.c:1608)", sh.SZ);
+  k_delta_scan<<<dim3(sh.TR, 4), 128, 0, s>>>(S, ctl, y, beta, decay, sh, o, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// gated RMSNorm of each head's output -> planes of ssm_out's input
+// (llb_t_grn, tools/payload-spec2.patch:413-447; tools/qwen35_engine.c:648-654)
+__global__ void __launch_bounds__(128) k_gnorm_xp(const float *__restrict__ o, PartIn z, const float *__restrict__ nw,
+                                                  DeltaShape sh, XPlanes xp, const RowSet *__restrict__ rs) {
+  __shared__ float red[32];
+  const int hh = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
+  if (t >= rs->n) return;
+  const size_t idx = (size_t)t * sh.vdc + hh * 128 + i;
+  const float v = o[idx];
+  const float ss = block_sum(v * v, red);
+  const float r = 1.0f / sqrtf(ss / 128.0f + sh.eps);
+  xp_store32(xp, t, 2, hh * 128 + (i & ~31), v * r * nw[i] * silu_f(part_get(z, idx)), i & 31);
+}
+int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs, int Tmax) {
+  k_gnorm_xp<<<dim3(sh.TR, Tmax), 128, 0, s>>>(o, z, nw, sh, xp, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- top-2 over the logits (llb_t_amaxp / llb_t_amax, tools/payload-spec2.patch:450-483) ---------
+// Order: larger value first, lower id on equal values (tools/qwen35_engine.c:763-778).
+struct Top2 { float v1; int i1; float v2; int i2; };
+__device__ __forceinline__ bool t2_before(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+__device__ __forceinline__ void t2_push(Top2 &a, float v, int i) {
+  if (i < 0) return;
+  if (a.i1 < 0 || t2_before(v, i, a.v1, a.i1)) { a.v2 = a.v1; a.i2 = a.i1; a.v1 = v; a.i1 = i; }
+  else if (a.i2 < 0 || t2_before(v, i, a.v2, a.i2)) { a.v2 = v; a.i2 = i; }
+}
+__device__ __forceinline__ Top2 t2_warp(Top2 a) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) {
+    float v1 = __shfl_xor_sync(0xffffffffu, a.v1, m), v2 = __shfl_xor_sync(0xffffffffu, a.v2, m);
+    int i1 = __shfl_xor_sync(0xffffffffu, a.i1, m), i2 = __shfl_xor_sync(0xffffffffu, a.i2, m);
+    t2_push(a, v1, i1);
+    t2_push(a, v2, i2);
+  }
+  return a;
+}
+__global__ void __launch_bounds__(256) k_top2_part(const float *__restrict__ logits, int V, long long row_stride,
+                                                   float *__restrict__ part, const RowSet *__restrict__ rs) {
+  __shared__ Top2 sh[8];
+  const int t = blockIdx.y;
+  if (t >= rs->n) return;
+  const float *z = logits + (size_t)t * row_stride;
+  const int per = (V + gridDim.x - 1) / gridDim.x, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
+  Top2 a = {0.f, -1, 0.f, -1};
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) t2_push(a, z[i], i);
+  a = t2_warp(a);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = a;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    Top2 b = threadIdx.x < 8 ? sh[threadIdx.x] : Top2{0.f, -1, 0.f, -1};
+    b = t2_warp(b);
+    if (threadIdx.x == 0) {
+      float *p = part + ((size_t)t * gridDim.x + blockIdx.x) * 4;
+      p[0] = b.v1; p[1] = __int_as_float(b.i1); p[2] = b.v2; p[3] = __int_as_float(b.i2);
+    }
+  }
+}
+int op_top2_part(cudaStream_t s, const float *logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax) {
+  k_top2_part<<<dim3(TOP2_NB, Tmax), 256, 0, s>>>(logits, V, row_stride, part, rs);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+__device__ __forceinline__ Top2 t2_final(const float *part, int t, int lane) {
+  Top2 a = {0.f, -1, 0.f, -1};
+  for (int b = lane; b < TOP2_NB; b += 32) {
+    const float *p = part + ((size_t)t * TOP2_NB + b) * 4;
+    t2_push(a, p[0], __float_as_int(p[1]));
+    t2_push(a, p[2], __float_as_int(p[3]));
+  }
+  return t2_warp(a);
+}
+
+// ---- fused argmax + accept/reject + commit -------------------------------------------------------
+// The reference serves row r while the caller's next token equals the row's input
+// (host/llb_host.c:1911) and advances the state ring by the rows served (:1932); under greedy
+// sampling that is "accept while argmax(row j) == draft j+1" (host/llb_sampler_impl.h:400-405).
+// Here the whole decision runs on the device and also prepares the next cycle: new p0, ring slot,
+// committed token, and the drafter's catch-up rows (host/llb_host.c:1815).
+__global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ ctl, SpecResult *__restrict__ ring, int ring_n) {
+  __shared__ Top2 rows[SPEC_MAXT];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T = ctl->verify.n;
+  if (T < 1) return;   // an empty pass (the sizing run at open) decides nothing
+  if (warp < T) {
+    Top2 a = t2_final(part, warp, lane);
+    if (lane == 0) rows[warp] = a;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  const int p0 = ctl->verify.pos0;
+  SpecResult *res = ring + (ctl->seq % (unsigned long long)ring_n);
+  int served = 1;
+  if (ctl->forced > 0) served = T;
+  else while (served < T && rows[served - 1].i1 == ctl->verify.tok[served]) served++;
+  res->p0 = p0; res->T = T; res->served = served; res->pad = 0;
+  for (int r = 0; r < SPEC_MAXT; r++) {
+    res->tin[r] = r < T ? ctl->verify.tok[r] : -1;
+    res->ids[r] = r < T ? rows[r].i1 : -1;
+    res->top2[r][0] = r < T ? (unsigned)rows[r].i1 : 0u;
+    res->top2[r][1] = r < T ? __float_as_uint(rows[r].v1) : 0u;
+    res->top2[r][2] = r < T ? (unsigned)rows[r].i2 : 0u;
+    res->top2[r][3] = r < T ? __float_as_uint(rows[r].v2) : 0u;
+  }
+  // commit: the state after the last served row becomes the committed state
+  ctl->sc = (ctl->sc + served) % ctl->R;
+  const int np0 = p0 + served;
+  // the drafter catches up over the served positions p0+1 .. p0+served, whose tokens are the
+  // emitted ids (or the given prompt tokens), paired with the trunk's normed hidden rows 0..served-1
+  ctl->catchup.n = served;
+  ctl->catchup.pos0 = p0 + 1;
+  for (int r = 0; r < served; r++) ctl->catchup.tok[r] = ctl->forced > 0 ? ctl->next_tok[r] : rows[r].i1;
+  const int tok0 = ctl->catchup.tok[served - 1];
+  int Tn = ctl->k + 1;
+  if (np0 + Tn > ctl->max_pos) Tn = ctl->max_pos - np0 > 0 ? ctl->max_pos - np0 : 1;
+  ctl->verify.n = Tn;
+  ctl->verify.pos0 = np0;
+  ctl->verify.tok[0] = tok0;
+  for (int r = 0; r < SPEC_MAXT; r++) ctl->verify.slot[r] = (np0 + r) & (CONV_RING - 1);
+  ctl->forced = 0;
+  __threadfence_system();
+  res->seq = ctl->seq + 1;   // written last: the host polls it
+  ctl->seq += 1;
+}
+int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax) {
+  k_accept<<<1, 32 * Tmax, 0, s>>>(part, ctl, ring, ring_n);
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// After a drafter pass: the head argmax of its last row is draft j (mapped through the draft-vocab ids,
+// host/llb_host.c:1800-1807); it becomes verify input j and the token of the next chained row, whose hidden
+// is the drafter's own normed hidden of that last row (host/llb_host.c:1824-1827).
+__global__ void k_draft_pick(const float *__restrict__ part, const int *__restrict__ ids, SpecCtl *__restrict__ ctl,
+                             int from_chain, int j, const float *__restrict__ mt_hn, float *__restrict__ chain_h, int d) {
+  __shared__ int s_tok;
+  const RowSet *rs = from_chain ? &ctl->chain : &ctl->catchup;
+  const int last = rs->n - 1;
+  if (last < 0) return;
+  if (threadIdx.x < 32) {
+    Top2 a = t2_final(part, last, threadIdx.x);
+    if (threadIdx.x == 0) s_tok = a.i1 < 0 ? 0 : ids ? ids[a.i1] : a.i1;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) chain_h[c] = mt_hn[(size_t)last * d + c];
+  if (threadIdx.x == 0) {
+    const int p = ctl->verify.pos0;
+    if (j < ctl->verify.n) ctl->verify.tok[j] = s_tok;
+    ctl->chain.n = 1;
+    ctl->chain.pos0 = p + j;
+    ctl->chain.tok[0] = s_tok;
+    ctl->chain.slot[0] = 0;
+  }
+}
+int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
+                  float *chain_h, int d) {
+  k_draft_pick<<<1, 256, 0, s>>>(part, ids, ctl, from_chain, j, mt_hn, chain_h, d);
+  CU_OK(cudaGetLastError());
+  return 0;
+}

@@ -53,6 +53,12 @@ def lib() -> C.CDLL:
             "llb_b200_xp_set_f32": (i32, [vp, u64]), "llb_b200_xp_set_bf16": (i32, [vp, u64]),
             "llb_b200_gemm": (i32, [i32, i32, C.POINTER(u64), C.POINTER(i32), C.POINTER(u64), i32, vp, i32]),
             "llb_b200_gemm_host": (i32, [i32, u64, i32, i32, vp, i32, vp, vp, u64, u64]),
+            "llb_spec_open": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32]),
+            "llb_spec_close": (None, [vp]), "llb_spec_reset": (i32, [vp]),
+            "llb_spec_prefill": (i32, [vp, vp, i32]), "llb_spec_cycle": (i32, [vp, vp, vp, vp]),
+            "llb_spec_generate": (i32, [vp, i32, vp, vp]), "llb_spec_pass": (i32, [vp, i32, i32, vp]),
+            "llb_spec_position": (i32, [vp]), "llb_spec_stats": (i32, [vp, vp]),
+            "llb_spec_read_state": (i32, [vp, i32, i32, i32, vp, sz]), "llb_spec_read_logits": (i32, [vp, i32, vp]),
         }
         for name, (res, args) in sig.items():
             f = getattr(L, name)
@@ -94,3 +100,89 @@ def gemm(fmt: int, ws, rows, outs, K: int, xp, ksplit: int = 0):
     n = len(ws)
     check(lib().llb_b200_gemm(fmt, n, arr(C.c_uint64, ws), arr(C.c_int, rows), arr(C.c_uint64, outs), K, xp, ksplit),
           "llb_b200_gemm")
+
+
+class SpecEngine:
+    """The speculative-decoding engine behind llb_spec_* (one sequence, greedy, MTP drafter).
+
+    `pack` is a packs.Pack whose bytes live on the host (numpy / CPU tensor) or on the GPU (CUDA
+    tensor); `mtp` the drafter image as bytes (host) or a CUDA uint8 tensor.
+    """
+
+    def __init__(self, pack, mtp=None, k: int = 3, max_ctx: int = 4096, layers: int = 0):
+        import numpy as np
+        import torch
+        L = lib()
+        self.L = L
+        data = pack.data
+        on_dev = bool(isinstance(data, torch.Tensor) and data.is_cuda)
+        ptr = data.data_ptr() if isinstance(data, torch.Tensor) else data.ctypes.data
+        nbytes = data.numel() if isinstance(data, torch.Tensor) else data.size
+        if mtp is None:
+            mptr, mbytes, mdev = None, 0, 0
+        elif isinstance(mtp, (bytes, bytearray)):
+            self._mtp_keep = np.frombuffer(mtp, dtype=np.uint8)
+            mptr, mbytes, mdev = self._mtp_keep.ctypes.data, len(mtp), 0
+        else:
+            self._mtp_keep = mtp
+            mptr, mbytes, mdev = mtp.data_ptr(), mtp.numel(), int(mtp.is_cuda)
+        self.h = handle(L.llb_spec_open(pack.index_text().encode(), ptr, nbytes, int(on_dev), mptr, mbytes, mdev, k, max_ctx,
+                                        layers), "llb_spec_open")
+        self.k, self.vocab, self.d = k, pack.cfg.vocab_size, pack.cfg.d_model
+        self.cfg = pack.cfg
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.llb_spec_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def prefill(self, ids):
+        import numpy as np
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        check(self.L.llb_spec_prefill(self.h, ids.ctypes.data, len(ids)), "llb_spec_prefill")
+
+    def cycle(self):
+        import numpy as np
+        ids = np.zeros(8, np.int32)
+        n = C.c_int(0)
+        t2 = np.zeros((8, 4), np.uint32)
+        check(self.L.llb_spec_cycle(self.h, ids.ctypes.data, C.addressof(n), t2.ctypes.data), "llb_spec_cycle")
+        return ids[: n.value].copy(), t2[: n.value].copy()
+
+    def generate(self, steps: int):
+        import numpy as np
+        ids = np.zeros(steps, np.int32)
+        t2 = np.zeros((steps, 4), np.uint32)
+        n = check(self.L.llb_spec_generate(self.h, steps, ids.ctypes.data, t2.ctypes.data), "llb_spec_generate")
+        assert n == steps
+        return ids, t2
+
+    def stats(self):
+        import numpy as np
+        out = np.zeros(19, np.uint64)
+        check(self.L.llb_spec_stats(self.h, out.ctypes.data), "llb_spec_stats")
+        return {"cycles": int(out[0]), "rows": int(out[1]), "served": int(out[2]),
+                "drafted": [int(v) for v in out[3:11]], "accepted": [int(v) for v in out[11:19]]}
+
+    def position(self) -> int:
+        return self.L.llb_spec_position(self.h)
+
+    def read_state(self, what: int, il: int = 0, pos: int = 0):
+        import numpy as np
+        c = self.cfg
+        n = max(c.ssm_heads * c.ssm_state * c.ssm_state, c.convd, c.d_model, c.n_kv_heads * c.head_dim)
+        out = np.zeros(n, np.float32)
+        got = check(self.L.llb_spec_read_state(self.h, what, il, pos, out.ctypes.data, n), "llb_spec_read_state")
+        return out[:got].copy()
+
+    def read_logits(self, r: int):
+        import numpy as np
+        out = np.zeros(self.vocab, np.float32)
+        check(self.L.llb_spec_read_logits(self.h, r, out.ctypes.data), "llb_spec_read_logits")
+        return out

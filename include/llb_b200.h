@@ -75,6 +75,31 @@ LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows,
 LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
                        llb_dptr x_dev, llb_dptr y_dev);
 
+/* ---- 3. the speculative cycle ----------------------------------------------------------------- */
+/* Replaces host/llb_host.c:1474-1950 for greedy decoding with the MTP drafter.
+ * index_text: the pack's index.tsv (tools/qwen35_engine.c:379-433); pack: pack.bin bytes (host, or a
+ * device address when pack_on_device); mtp: the drafter as an AUX1 or MTP1 image
+ * (host/llb_host.c:1525-1603), required when k > 0; k: drafts per cycle (0..7, LLB_SPEC);
+ * max_ctx: positions of KV kept per full-attention layer; layers: > 0 truncates the model like the
+ * reference engine's --layers. */
+typedef struct llb_spec llb_spec;
+LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
+                                size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers);
+LLB_API void llb_spec_close(llb_spec *m);
+LLB_API int llb_spec_reset(llb_spec *m);                       /* host/llb_host.c:1915-1928 */
+LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n);
+/* one cycle: ids_out[0 .. *n_out-1] emitted; top2_out[i] = id1, bits(v1), id2, bits(v2) of row i
+ * (the reference's "logits" line, tools/qwen35_engine.c:985) */
+LLB_API int llb_spec_cycle(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2_out);
+LLB_API int llb_spec_generate(llb_spec *m, int steps, int *ids, uint32_t *top2);
+/* the reference's per-token operator (spec_pass, host/llb_host.c:1902-1950): y = [v1, id1, v2, id2] */
+LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y);
+LLB_API int llb_spec_position(const llb_spec *m);
+/* out[19] = cycles, rows, served, drafted[8], accepted[8] by draft position (host/llb_host.c:1513-1523) */
+LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out);
+LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n);
+LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out);
+
 #ifdef __cplusplus
 }
 #endif

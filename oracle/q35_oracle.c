@@ -723,8 +723,7 @@ API int q35_spec_greedy(Q35 *m, const int *prompt, int np, int steps, int k, int
         if (top2) memcpy(top2 + 4 * out, w, 16);
         out++;
       }
-      if (r + 1 < T && (int)w[0] != tin[r + 1]) break;
-      if (out >= steps) break;
+      if (r + 1 < T && (int)w[0] != tin[r + 1]) break;   /* a cycle always runs to its own end */
     }
     for (int j = 1; j < T; j++) { z.drafted[j]++; z.accepted[j] += nv > j; }
     z.served += (uint64_t)nv;
