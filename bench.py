@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""Benchmark of the speculative-decoding path on the 27B-shape Q4_K_M model, MTP k = 3.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one speculative cycle (MTP drafts -> 4-row verify -> accept -> commit) of one request
+stream on one GPU.  The synthetic 27B-shape pack (seed 3) is drawn and quantised on the GPU, the
+3011-token prompt is fed through the engine, then W warm-up and K timed cycles run.
+
+  value     emitted tokens / s over all GPUs, cycles enqueued back to back, timed with CUDA events
+            on the library's stream (inputs resident in HBM)
+  e2e       the same through the reference-shaped per-token call llb_spec_pass(pos, tok) -> y with
+            host buffers: (pos, tok) crosses to the device and the result record comes back every cycle
+  roofline  the largest launch (FFN gate|up GEMM), event-timed over cold weights, against the
+            measured HBM copy peak; verify_step = weight + KV bytes of one verify pass / its time
+  cpu_baseline  the reference CPU engine (oracle/_ref, built from the reference's own sources) on the
+            same pack on this box's host cores, a bounded sample
+
+With N > 1 (torchrun) every rank runs its own stream on its own replica: no collective on the data
+path, weak scaling.  `--impl reference` times the reference CPU engine alone (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "spec-decode tok/s per B200, 27B-shape Q4_K_M MTP k=3; verify-step HBM GB/s"
+WORKLOAD = "config 2: 27B-shape hybrid (d 5120, 64 layers, f 17408, V 151936), Q4_K_M, batch 1, MTP k=3 greedy, prompt 3011"
+PROMPT, GEN_CAP, K_DRAFT = 3011, 1200, 3
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 8 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 8 and r[4 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def verify_bytes(pack, pos: int, T: int) -> float:
+    """Algorithmic bytes of one verify pass: every trunk matrix and the head once, T embedding rows,
+    and the K/V rows of positions 0 .. pos+T-1 of every full-attention layer (f32)."""
+    from __graft_entry__ import load_package
+    packs = load_package().packs
+    c = pack.cfg
+    b = 0.0
+    for e in pack.entries:
+        if e.name == "token_embd.weight":
+            b += T * packs.row_bytes(e.ty, e.cols)
+        elif e.name == "output.weight" or (e.name.startswith("blk.") and e.rows > 1 and e.ty != "F32"):
+            b += e.nbytes
+    n_full = sum(1 for i in range(c.n_layers) if c.is_full(i))
+    b += n_full * 2.0 * (pos + T) * c.n_kv_heads * c.head_dim * 4
+    return b
+
+
+def build_model(device, layers=None):
+    from __graft_entry__ import load_package
+    packs = load_package().packs
+    cfg = packs.cfg_c2()
+    pack = packs.build_pack(cfg, device=device, layers=layers)
+    mtp = packs.aux1_bytes(packs.build_mtp(pack))
+    prompt = packs.synth_prompt(3, PROMPT, cfg.vocab_size)
+    return packs, pack, mtp, prompt
+
+
+def cpu_reference_run(pack, prompt, n_prompt: int, n_gen: int, threads: int):
+    """The reference CPU engine on the same pack: teacher-forces `n_prompt` prompt tokens, then decodes
+    `n_gen` tokens greedily.  Returns (tok/s over the generated tokens, ids, seconds)."""
+    from oracle.bindings import RefTwin
+    host = pack.data.cpu().numpy()
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "index.tsv"), "w") as f:
+            f.write(pack.index_text())
+        ref = RefTwin(d, cap=n_prompt + n_gen + 4, pack=host, threads=threads)
+        for t in range(n_prompt):
+            ref.forward(int(prompt[t]), t)
+        ids = []
+        t0 = time.perf_counter()
+        for s in range(n_gen):
+            ref.logits()
+            (i1, _), _ = ref.top2()
+            ids.append(i1)
+            ref.forward(i1, n_prompt + s)
+        dt = time.perf_counter() - t0
+    return n_gen / dt, ids, dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    import torch
+    cores = os.cpu_count() or 1
+    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+    packs, pack, mtp, prompt = build_model(dev)
+    n_prompt = 4
+    tps, ids, dt = cpu_reference_run(pack, prompt, n_prompt, args.steps + args.warmup, cores)
+    # warm-up tokens are part of the loop above; report the rate over all of them
+    line = {"metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": WORKLOAD, "note": "reference CPU engine (tools/qwen35_engine.c), plain greedy: it has no speculative path; "
+                       "a step is one decoded token at a context of %d" % n_prompt},
+            "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "reference",
+                             "sample": f"full-depth pack, {n_prompt} prompt tokens then {args.steps + args.warmup} greedy tokens"},
+            "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model (debugging only; the number is then not the headline)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if args.steps > 24:
+            args.steps = 24        # a 27B-shape token costs seconds on the host cores
+        run_reference(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    llb = pkg.llb
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    llb.init(local)
+    t_build = time.time()
+    packs, pack, mtp, prompt = build_model(f"cuda:{local}", layers=args.layers or None)
+    max_ctx = PROMPT + GEN_CAP + 64
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()   # the quantisers' temporaries go back to the driver before the engine allocates
+    eng = llb.SpecEngine(pack, mtp, k=K_DRAFT, max_ctx=max_ctx)
+    t_build = time.time() - t_build
+    t_pre = time.time()
+    eng.prefill(prompt)
+    t_pre = time.time() - t_pre
+
+    steps, warm = args.steps, max(args.warmup, 3)
+    if (steps + warm) * 2 * (K_DRAFT + 1) + 16 > GEN_CAP:
+        raise SystemExit("--steps too large for the context this benchmark allocates")
+    st = torch.cuda.ExternalStream(llb.lib().llb_stream())
+    sampler = ClockSampler(local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident arm: K cycles enqueued back to back ------------------------------------
+    sampler.start()          # nvidia-smi needs a second to come up: started before the warm-up
+    eng.run_cycles(warm)
+    t_w = time.time()
+    while not sampler.rows and time.time() - t_w < 5.0:
+        eng.run_cycles(1)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    _, toks = eng.run_cycles(steps)
+    e1.record(st)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    pos_mid = eng.position()
+
+    # ---- end to end: the per-token operator with host buffers -----------------------------------
+    barrier()
+    # continue from the engine's committed token: the last id of one more cycle's record
+    ids_w, _ = eng.cycle()
+    pos, tok = eng.position(), int(ids_w[-1])
+    t0 = time.perf_counter()
+    n_e2e, c0 = 0, eng.stats()["cycles"]
+    while eng.stats()["cycles"] - c0 < steps:
+        y = eng.step(pos, tok)
+        tok, pos, n_e2e = int(y[1]), pos + 1, n_e2e + 1
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop()
+
+    # ---- roofline legs ---------------------------------------------------------------------------
+    ver_ms = eng.time_verify(10)
+    gemm_us, gemm_bytes = eng.time_gemm(48)
+    vbytes = verify_bytes(pack, pos_mid, K_DRAFT + 1)
+    peak, peak_src = peaks()
+    stats = eng.stats()
+    launches = eng.graph_nodes(0)
+
+    if world > 1:
+        t = torch.tensor([ms, float(toks), e2e_s, float(n_e2e)], device=f"cuda:{local}", dtype=torch.float64)
+        tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, toks, e2e_s, n_e2e = tmax[0].item(), tsum[1].item(), tmax[2].item(), tsum[3].item()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        try:
+            cores = os.cpu_count() or 1
+            tps, cids, dt = cpu_reference_run(pack, prompt, 4, 4, cores)
+            # the same 4 + 4 tokens on the device (k = 0 engine on the same weights would be another
+            # load; the speculative engine is lossless, so its ids are the plain greedy ids)
+            eng2 = llb.SpecEngine(pack, mtp, k=K_DRAFT, max_ctx=128)
+            eng2.prefill(prompt[:4])
+            gids, _ = eng2.generate(4)
+            eng2.close()
+            cpu = {"value": tps, "unit": "tok/s", "cores": cores, "kind": "reference",
+                   "sample": "full-depth pack, 4 prompt tokens then 4 greedy tokens (context 8, not 3011); plain greedy, "
+                             "the reference CPU engine has no speculative path",
+                   "ids_equal_device": bool(list(gids) == list(cids))}
+        except Exception as ex:  # the checker must not take the measurement down
+            cpu = {"value": None, "unit": "tok/s", "cores": os.cpu_count(), "kind": "reference", "sample": f"failed: {ex}"}
+
+    if rank == 0:
+        value = toks / (ms / 1000.0)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "streams_per_gpu": 1, "parallelism": f"stream-dp{world}",
+                       "layers": args.layers or 64, "l2": "inputs larger than L2: a cycle streams >14 GB of weights",
+                       "tokens_per_cycle": toks / (steps * world),
+                       "accepted_by_position": [round(a / d, 4) if d else None for a, d in zip(stats["accepted"][1:4], stats["drafted"][1:4])],
+                       "prefill_s": round(t_pre, 2), "build_s": round(t_build, 2)},
+            "clocks": clocks,
+            "e2e": {"value": n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 216,
+                    "api": "llb_spec_pass(pos, tok) -> y[4], one call per token"},
+            "gpu_launches": launches * steps,
+            "roofline": {"bound": "hbm", "kernel": "k_gemm<Q4_K> ffn_gate|ffn_up [2 x 17408 x 5120], T=4", "achieved": gemm_bytes / gemm_us / 1e3,
+                         "peak": peak, "unit": "GB/s", "frac": gemm_bytes / gemm_us / 1e3 / peak, "traffic": None, "peak_source": peak_src,
+                         "us_per_launch": gemm_us, "bytes_per_launch": gemm_bytes},
+            "verify_step": {"bytes": vbytes, "ms": ver_ms, "GBs": vbytes / ver_ms / 1e6, "frac": vbytes / ver_ms / 1e6 / peak,
+                            "kernels": eng.graph_nodes(2)},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -28,7 +28,9 @@ int llb_b200_init(int device) {
   if (pr.major < 10) return llb_fail("device %d is sm_%d%d; this library is built for sm_100a only", device, pr.major, pr.minor);
   g_llb.device = device;
   g_llb.sms = pr.multiProcessorCount;
-  CU_OK(cudaStreamCreateWithFlags(&g_llb.stream, cudaStreamNonBlocking));
+  // a blocking stream: ordered after work a caller queued on the legacy default stream (torch's), so
+  // device buffers produced there can be handed in without an explicit synchronisation
+  CU_OK(cudaStreamCreate(&g_llb.stream));
   if (gemm_setup()) return -1;
   return 0;
 }

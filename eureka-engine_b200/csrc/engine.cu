@@ -20,7 +20,7 @@
 #include "model.cuh"
 
 struct DevMat { uint8_t *w = nullptr; int rows = 0, cols = 0, fmt = -1; };
-struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; };   // K-slice partial sums of one matrix
+struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; size_t cap = 0; };   // K-slice partial sums of one matrix (cap: floats allocated)
 static PartIn as_in(const OutBuf &o) { return PartIn{o.p, o.ns, o.stride}; }
 
 struct AttnW { DevMat q, k, v, o; float *qn = nullptr, *kn = nullptr; };
@@ -55,7 +55,7 @@ struct llb_spec {
   float *mt_Kc = nullptr, *mt_Vc = nullptr;
   SpecCtl *ctl = nullptr;
   SpecResult *res_host = nullptr, *res_dev = nullptr;
-  int res_n = 64;
+  int res_n = 256;
   // activations
   float *x = nullptr, *x1 = nullptr, *hn = nullptr, *e = nullptr, *qn = nullptr, *y = nullptr, *beta = nullptr, *decay = nullptr,
         *o = nullptr, *logits = nullptr, *t2part = nullptr, *pm = nullptr, *pl = nullptr, *po = nullptr;
@@ -64,7 +64,9 @@ struct llb_spec {
   OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg;
   int att_split = 1;
   // graphs
-  cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr;
+  cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
+  size_t n_spec_nodes = 0, n_verify_nodes = 0;
+  int last_tok = -1;      // the committed token of the next cycle (host mirror)
   // host mirror
   unsigned long long seq = 0;
   int pos = 0;            // position of the next cycle's row 0
@@ -82,7 +84,8 @@ static float bits_float(unsigned int u) { float f; memcpy(&f, &u, 4); return f; 
 
 static void *dalloc(llb_spec *m, size_t bytes) {
   void *p = nullptr;
-  if (cudaMalloc(&p, bytes ? bytes : 256) != cudaSuccess) { llb_fail("out of device memory (%zu bytes)", bytes); cudaGetLastError(); return nullptr; }
+  cudaError_t e = cudaMalloc(&p, bytes ? bytes : 256);
+  if (e != cudaSuccess) { llb_fail("cudaMalloc(%zu bytes): %s", bytes, cudaGetErrorString(e)); cudaGetLastError(); return nullptr; }
   cudaMemsetAsync(p, 0, bytes, g_llb.stream);
   m->allocs.push_back(p);
   return p;
@@ -168,10 +171,12 @@ struct SiteMat { const DevMat *w; OutBuf *out; const int *tok_slot; float *direc
 
 // Allocate (at init) or reuse the partial-sum buffer of one matrix and record its split.
 static int out_prepare(llb_spec *m, OutBuf &o, int rows, int ks) {
-  if (o.p && o.ns == ks && o.stride == (long long)m->Tmax * rows) return 0;
-  if (o.p && o.ns * o.stride >= (long long)ks * m->Tmax * rows) { o.ns = ks; o.stride = (long long)m->Tmax * rows; return 0; }
-  o.p = falloc(m, (size_t)ks * m->Tmax * rows);
-  if (!o.p) return -1;
+  const size_t need = (size_t)ks * m->Tmax * rows;
+  if (!o.p || o.cap < need) {
+    o.p = falloc(m, need);
+    if (!o.p) return -1;
+    o.cap = need;
+  }
   o.ns = ks; o.stride = (long long)m->Tmax * rows;
   return 0;
 }
@@ -303,15 +308,18 @@ static int enq_cycle(llb_spec *m, bool spec) {
   return 0;
 }
 
-static int capture(llb_spec *m, bool spec, cudaGraphExec_t *out) {
+// which: 0 the speculative cycle, 1 a prompt chunk, 2 the verify pass alone (no accept: replaying
+// it changes nothing that is committed, so it can be timed in place)
+static int capture(llb_spec *m, int which, cudaGraphExec_t *out, size_t *nodes) {
   cudaStream_t s = g_llb.stream;
   cudaGraph_t g = nullptr;
   CU_OK(cudaStreamSynchronize(s));
   CU_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-  int rc = enq_cycle(m, spec);
+  int rc = which == 2 ? enq_verify(m) : enq_cycle(m, which == 0);
   cudaError_t e = cudaStreamEndCapture(s, &g);
   if (rc) { if (g) cudaGraphDestroy(g); return -1; }
   if (e != cudaSuccess) return llb_fail("graph capture: %s", cudaGetErrorString(e));
+  if (nodes) cudaGraphGetNodes(g, nullptr, nodes);
   e = cudaGraphInstantiate(out, g, 0);
   cudaGraphDestroy(g);
   if (e != cudaSuccess) return llb_fail("graph instantiate: %s", cudaGetErrorString(e));
@@ -500,8 +508,8 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
   // One eager pass with empty row sets sizes and allocates every partial-sum buffer, so that the
   // captures below allocate nothing.  Then the graphs are captured once; everything that changes
   // between cycles lives in device memory.
-  if (llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m) || capture(m, true, &m->g_spec) ||
-      capture(m, false, &m->g_prefill) || llb_spec_reset(m)) {
+  if (llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m) || capture(m, 0, &m->g_spec, &m->n_spec_nodes) ||
+      capture(m, 1, &m->g_prefill, nullptr) || capture(m, 2, &m->g_verify, &m->n_verify_nodes) || llb_spec_reset(m)) {
     llb_spec_close(m);
     return nullptr;
   }
@@ -513,6 +521,7 @@ LLB_API void llb_spec_close(llb_spec *m) {
   cudaStreamSynchronize(g_llb.stream);
   if (m->g_spec) cudaGraphExecDestroy(m->g_spec);
   if (m->g_prefill) cudaGraphExecDestroy(m->g_prefill);
+  if (m->g_verify) cudaGraphExecDestroy(m->g_verify);
   for (void *p : m->allocs) cudaFree(p);
   if (m->res_host) cudaFreeHost(m->res_host);
   delete m;
@@ -574,7 +583,9 @@ LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
     // nothing ran: the first cycle starts at position 0 with the single prompt token
   }
   m->pos = n - 1;
+  m->last_tok = ids[n - 1];
   m->primed = true;
+  m->have_last = false;
   return 0;
 }
 
@@ -594,6 +605,7 @@ LLB_API int llb_spec_cycle(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2
   }
   *n_out = r.served;
   m->pos += r.served;
+  m->last_tok = r.ids[r.served - 1];
   m->cycles += 1; m->rows += (unsigned long long)r.T; m->served += (unsigned long long)r.served;
   for (int j = 1; j < r.T; j++) { m->drafted[j] += 1; m->accepted[j] += r.served > j; }
   m->last = r; m->have_last = true; m->last_served_idx = 0;
@@ -629,8 +641,84 @@ LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y) {
     y[2] = bits_float(m->last.top2[r][3]); y[3] = (float)m->last.top2[r][2];
     return 0;
   }
+  if (m->primed && pos == m->pos && tok == m->last_tok) {
+    // a new cycle at (pos, tok): the pair crosses to the device and the accept kernel checks it
+    // against the state it committed itself
+    int chk[3] = {1, pos, tok};
+    CU_OK(cudaMemcpyAsync(&m->ctl->chk_on, chk, sizeof chk, cudaMemcpyHostToDevice, g_llb.stream));
+    int ids[SPEC_MAXT], n = 0;
+    CK(llb_spec_cycle(m, ids, &n, nullptr));
+    if (m->last.pad) return llb_fail("LLB_SPEC: the device's committed (pos, tok) differs from the caller's");
+    return llb_spec_pass(m, pos, tok, y);
+  }
   return llb_fail("LLB_SPEC: a step out of order");
 }
+
+// Enqueue `n` cycles back to back with no host round trip between them (nothing a cycle needs comes
+// from the host), then collect what they emitted.  ids (may be null) receives the tokens in order,
+// at most cap of them; returns the number of tokens emitted by the n cycles.
+LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap) {
+  if (!m->primed) return llb_fail("llb_spec_run_cycles before llb_spec_prefill");
+  if (n > m->res_n) return llb_fail("at most %d cycles per call", m->res_n);
+  if (m->pos + n * m->Tmax >= m->max_ctx) return llb_fail("context of %d positions cannot take %d more cycles", m->max_ctx, n);
+  for (int i = 0; i < n; i++) CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
+  int total = 0;
+  for (int i = 0; i < n; i++) {
+    SpecResult r;
+    CK(wait_result(m, &r));
+    if (r.p0 != m->pos) return llb_fail("cycle ran at position %d, host expected %d", r.p0, m->pos);
+    for (int j = 0; j < r.served; j++, total++) if (ids && total < cap) ids[total] = r.ids[j];
+    m->pos += r.served;
+    m->last_tok = r.ids[r.served - 1];
+    m->cycles += 1; m->rows += (unsigned long long)r.T; m->served += (unsigned long long)r.served;
+    for (int j = 1; j < r.T; j++) { m->drafted[j] += 1; m->accepted[j] += r.served > j; }
+    m->last = r; m->have_last = true; m->last_served_idx = r.served;
+  }
+  return total;
+}
+
+// Device time of the verify pass alone at the current position: `iters` replays, CUDA events on the
+// library's stream.  Replaying commits nothing (no accept kernel), so the sequence is unchanged.
+LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass) {
+  cudaEvent_t a, b;
+  CU_OK(cudaEventCreate(&a)); CU_OK(cudaEventCreate(&b));
+  CU_OK(cudaGraphLaunch(m->g_verify, g_llb.stream));
+  CU_OK(cudaEventRecord(a, g_llb.stream));
+  for (int i = 0; i < iters; i++) CU_OK(cudaGraphLaunch(m->g_verify, g_llb.stream));
+  CU_OK(cudaEventRecord(b, g_llb.stream));
+  CU_OK(cudaEventSynchronize(b));
+  float ms = 0;
+  CU_OK(cudaEventElapsedTime(&ms, a, b));
+  *ms_per_pass = ms / iters;
+  cudaEventDestroy(a); cudaEventDestroy(b);
+  return 0;
+}
+
+// Device time per launch of the FFN gate|up GEMM (the largest launch of the pass), cycling over the
+// layers so that every launch streams weights that are not in L2.  bytes_per_launch = the two
+// matrices' stored bytes plus the activation planes and the outputs.
+LLB_API int llb_spec_time_gemm(llb_spec *m, int iters, float *us_per_launch, double *bytes_per_launch) {
+  cudaEvent_t a, b;
+  CU_OK(cudaEventCreate(&a)); CU_OK(cudaEventCreate(&b));
+  auto go = [&](int il) { const FfnW &w = m->layer[il % m->L].ffn;
+    return site_gemm(m, {{&w.gate, &m->b_g, nullptr, nullptr, 0}, {&w.up, &m->b_u, nullptr, nullptr, 0}}, m->xp_d, 0); };
+  for (int i = 0; i < 4; i++) CK(go(i));
+  CU_OK(cudaEventRecord(a, g_llb.stream));
+  for (int i = 0; i < iters; i++) CK(go(4 + i));
+  CU_OK(cudaEventRecord(b, g_llb.stream));
+  CU_OK(cudaEventSynchronize(b));
+  float ms = 0;
+  CU_OK(cudaEventElapsedTime(&ms, a, b));
+  *us_per_launch = ms * 1000.0f / iters;
+  const FfnW &w0 = m->layer[0].ffn;
+  *bytes_per_launch = (double)w0.gate.rows * pack_row_bytes(w0.gate.fmt, m->d) + (double)w0.up.rows * pack_row_bytes(w0.up.fmt, m->d) +
+                      (double)m->NC * m->d * 2 + 2.0 * m->Tmax * m->f * 4;
+  cudaEventDestroy(a); cudaEventDestroy(b);
+  return 0;
+}
+
+// kernels per replay of the cycle graph (which = 0) or of the verify pass (which = 2)
+LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which) { return (int)(which == 2 ? m->n_verify_nodes : m->n_spec_nodes); }
 
 LLB_API int llb_spec_position(const llb_spec *m) { return m->pos; }
 

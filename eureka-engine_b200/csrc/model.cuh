@@ -26,6 +26,7 @@ struct SpecCtl {
   int forced;            // > 0: a prompt chunk; the rows and their successors are given, all are served
   int next_tok[SPEC_MAXT];
   int max_pos;           // exclusive bound on positions (context capacity)
+  int chk_on, chk_pos, chk_tok;   // the caller's (pos, tok) for this cycle, checked against the committed state
   int err;               // sticky device-side error word (0 = none)
   unsigned long long seq;
 };

@@ -507,7 +507,9 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
   int served = 1;
   if (ctl->forced > 0) served = T;
   else while (served < T && rows[served - 1].i1 == ctl->verify.tok[served]) served++;
-  res->p0 = p0; res->T = T; res->served = served; res->pad = 0;
+  res->p0 = p0; res->T = T; res->served = served;
+  res->pad = (ctl->chk_on && (ctl->chk_pos != p0 || ctl->chk_tok != ctl->verify.tok[0])) ? 1 : 0;
+  ctl->chk_on = 0;
   for (int r = 0; r < SPEC_MAXT; r++) {
     res->tin[r] = r < T ? ctl->verify.tok[r] : -1;
     res->ids[r] = r < T ? rows[r].i1 : -1;

@@ -59,6 +59,8 @@ def lib() -> C.CDLL:
             "llb_spec_generate": (i32, [vp, i32, vp, vp]), "llb_spec_pass": (i32, [vp, i32, i32, vp]),
             "llb_spec_position": (i32, [vp]), "llb_spec_stats": (i32, [vp, vp]),
             "llb_spec_read_state": (i32, [vp, i32, i32, i32, vp, sz]), "llb_spec_read_logits": (i32, [vp, i32, vp]),
+            "llb_spec_run_cycles": (i32, [vp, i32, vp, i32]), "llb_spec_time_verify": (i32, [vp, i32, vp]),
+            "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
         }
         for name, (res, args) in sig.items():
             f = getattr(L, name)
@@ -172,6 +174,32 @@ class SpecEngine:
 
     def position(self) -> int:
         return self.L.llb_spec_position(self.h)
+
+    def run_cycles(self, n: int, cap: int = 4096):
+        import numpy as np
+        ids = np.zeros(cap, np.int32)
+        got = check(self.L.llb_spec_run_cycles(self.h, n, ids.ctypes.data, cap), "llb_spec_run_cycles")
+        return ids[: min(got, cap)].copy(), got
+
+    def step(self, pos: int, tok: int):
+        """The reference's per-token operator: (pos, tok) in, [v1, id1, v2, id2] out."""
+        import numpy as np
+        y = np.zeros(4, np.float32)
+        check(self.L.llb_spec_pass(self.h, int(pos), int(tok), y.ctypes.data), "llb_spec_pass")
+        return y
+
+    def time_verify(self, iters: int) -> float:
+        ms = C.c_float(0)
+        check(self.L.llb_spec_time_verify(self.h, iters, C.addressof(ms)), "llb_spec_time_verify")
+        return ms.value
+
+    def time_gemm(self, iters: int):
+        us, nb = C.c_float(0), C.c_double(0)
+        check(self.L.llb_spec_time_gemm(self.h, iters, C.addressof(us), C.addressof(nb)), "llb_spec_time_gemm")
+        return us.value, nb.value
+
+    def graph_nodes(self, which: int = 0) -> int:
+        return self.L.llb_spec_graph_nodes(self.h, which)
 
     def read_state(self, what: int, il: int = 0, pos: int = 0):
         import numpy as np

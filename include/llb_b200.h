@@ -95,6 +95,13 @@ LLB_API int llb_spec_generate(llb_spec *m, int steps, int *ids, uint32_t *top2);
 /* the reference's per-token operator (spec_pass, host/llb_host.c:1902-1950): y = [v1, id1, v2, id2] */
 LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y);
 LLB_API int llb_spec_position(const llb_spec *m);
+/* n cycles enqueued back to back, no host round trip between them; returns the tokens emitted */
+LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap);
+/* measurement helpers: device time (CUDA events on the library's stream) of the verify pass alone and
+ * of the largest GEMM launch; kernels per graph replay (which: 0 cycle, 2 verify pass) */
+LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass);
+LLB_API int llb_spec_time_gemm(llb_spec *m, int iters, float *us_per_launch, double *bytes_per_launch);
+LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which);
 /* out[19] = cycles, rows, served, drafted[8], accepted[8] by draft position (host/llb_host.c:1513-1523) */
 LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out);
 LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n);

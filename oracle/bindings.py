@@ -199,7 +199,7 @@ class Oracle:
 class RefTwin:
     """The reference CPU engine (one model per process: it keeps its state in globals)."""
 
-    def __init__(self, pack_dir: str, cap: int, layers: int = 0):
+    def __init__(self, pack_dir: str, cap: int, layers: int = 0, pack: "np.ndarray | None" = None, threads: int = 0):
         if not os.path.exists(REF_SO):
             raise FileNotFoundError(REF_SO)
         self.L = L = C.CDLL(REF_SO)
@@ -221,7 +221,14 @@ class RefTwin:
         for n in ("q35ref_silu", "q35ref_sigmoid", "q35ref_softplus"):
             getattr(L, n).restype = _f
             getattr(L, n).argtypes = [_f]
-        if L.q35ref_open(pack_dir.encode(), layers, cap):
+        L.q35ref_open_mem.argtypes = [C.c_char_p, _vp, _i, _i]
+        L.q35ref_threads(threads)
+        if pack is not None:
+            self._pack = np.ascontiguousarray(pack, dtype=np.uint8)
+            rc = L.q35ref_open_mem(pack_dir.encode(), _p(self._pack), layers, cap)
+        else:
+            rc = L.q35ref_open(pack_dir.encode(), layers, cap)
+        if rc:
             raise RuntimeError("q35ref_open failed")
         cfg = (C.c_int * 19)()
         L.q35ref_cfg(cfg)
@@ -234,6 +241,29 @@ class RefTwin:
 
     def logits(self):
         return np.ctypeslib.as_array(self.L.q35ref_logits(), shape=(self.vocab,)).copy()
+
+    def top2(self):
+        """ids, values of the top two logits of the last q35ref_logits call"""
+        ids = (C.c_int * 2)()
+        vals = (C.c_float * 2)()
+        self.L.q35ref_top2(ids, vals)
+        return [ids[0], ids[1]], [vals[0], vals[1]]
+
+    def greedy(self, prompt, steps):
+        """Plain greedy decoding as the reference CLI does it (tools/qwen35_engine.c:981-1007):
+        ids[steps], top2[steps][4] = id1, bits1, id2, bits2."""
+        ids = np.zeros(steps, np.int32)
+        t2 = np.zeros((steps, 4), np.uint32)
+        for t, tok in enumerate(prompt):
+            self.forward(tok, t)
+        for s in range(steps):
+            self.logits()
+            (i1, i2), (v1, v2) = self.top2()
+            ids[s] = i1
+            t2[s] = [i1, np.float32(v1).view(np.uint32), i2, np.float32(v2).view(np.uint32)]
+            if s + 1 < steps:
+                self.forward(i1, len(prompt) + s)
+        return ids, t2
 
     def residual(self):
         return np.ctypeslib.as_array(self.L.q35ref_x(), shape=(self.d_model,)).copy()

@@ -82,6 +82,18 @@ API int q35ref_open(const char *dir, int layers, int cap) {
   return 0;
 }
 
+/* The same with the pack bytes already in memory (borrowed): only index.tsv is read from `dir`. */
+API int q35ref_open_mem(const char *dir, const uint8_t *pack, int layers, int cap) {
+  gNT = 0;
+  load_index(dir);
+  if (layers > 0 && layers < L) L = layers;
+  gPack = pack;
+  gMapSz = 0;
+  state_alloc(cap);
+  buf_alloc();
+  return 0;
+}
+
 /* cfg[0..18] = L D H KV HDIM dff V INTERVAL KC SZ GK TR VHD KDC VDC CONVD ROPEDIM, then
  * ROPE_BASE and EPS as float bits. */
 API void q35ref_cfg(int *cfg) {
