@@ -122,13 +122,9 @@ llb_xp *llb_b200_xp_new(int K, int T, int planes) {
   llb_xp *x = new llb_xp();
   x->T = T; x->planes = planes;
   const int NC = T * planes <= 8 ? 8 : 16;
-  size_t bh = (size_t)NC * K * 2, b16 = (size_t)(K / 16) * NC * 4, b32 = (size_t)(K / 32) * NC * 4;
-  if (cudaMalloc(&x->base, bh + b16 + b32) != cudaSuccess) { llb_fail("xp_new: out of memory"); delete x; return nullptr; }
-  cudaMemsetAsync(x->base, 0, bh + b16 + b32, g_llb.stream);
-  x->p.xh = (__half *)x->base;
-  x->p.xs16 = (float *)((char *)x->base + bh);
-  x->p.xs32 = (float *)((char *)x->base + bh + b16);
-  x->p.K = K; x->p.NC = NC;
+  if (cudaMalloc(&x->base, xp_bytes(K, NC)) != cudaSuccess) { llb_fail("xp_new: out of memory"); delete x; return nullptr; }
+  cudaMemsetAsync(x->base, 0, xp_bytes(K, NC), g_llb.stream);
+  x->p = xp_carve(x->base, K, NC);
   return x;
 }
 void llb_b200_xp_free(llb_xp *xp) {
@@ -155,8 +151,7 @@ int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const l
   a.nmat = nmat; a.K = K; a.xp = xp->p; a.planes = xp->planes; a.T = xp->T;
   int ntiles = 0, total_rows = 0;
   for (int i = 0; i < nmat; i++) { ntiles += (rows[i] + 15) / 16; total_rows += rows[i]; }
-  a.ksplit = ksplit > 0 ? ksplit : gemm_pick_ksplit(ntiles, K / 256, g_llb.sms);
-  if (a.ksplit > K / 256) a.ksplit = K / 256;
+  a.ksplit = gemm_fix_ksplit(fmt, xp->p.NC, K / 256, ksplit > 0 ? ksplit : gemm_pick_ksplit(fmt, xp->p.NC, ntiles, K / 256, g_llb.sms));
   const size_t per_split = (size_t)xp->T * total_rows;
   if (a.ksplit > 1 && per_split * a.ksplit > g_parts_floats) {
     if (g_parts) { CU_OK(cudaStreamSynchronize(g_llb.stream)); CU_OK(cudaFree(g_parts)); }

@@ -43,13 +43,29 @@ __host__ __device__ inline size_t pack_row_bytes(int fmt, int cols) {
 //                   0 2 1 3 4 6 5 7, which is the order the tensor-core B fragments consume
 //   xs16 [K/16][NC] f32 sums of the fp16 values over 16 consecutive columns
 //   xs32 [K/32][NC] f32 sums over 32 consecutive columns
+//   xsf  [K/256][NC][16] fp16: the eight 32-column MEANS of a super-block as hi/lo pairs, in the order
+//                   the min-term MMA's B fragment reads them: for j = 0..3: hi(2j) hi(2j+1) lo(2j) lo(2j+1)
 struct XPlanes {
   __half *xh;
   float *xs16;
   float *xs32;
+  __half *xsf;
   int K;
   int NC;
 };
+__host__ __device__ inline size_t xp_bytes(int K, int NC) {
+  return (size_t)NC * K * 2 + (size_t)(K / 16) * NC * 4 + (size_t)(K / 32) * NC * 4 + (size_t)(K / 256) * NC * 32;
+}
+__host__ __device__ inline XPlanes xp_carve(void *base, int K, int NC) {
+  char *b = (char *)base;
+  XPlanes xp;
+  xp.xh = (__half *)b; b += (size_t)NC * K * 2;
+  xp.xs16 = (float *)b; b += (size_t)(K / 16) * NC * 4;
+  xp.xs32 = (float *)b; b += (size_t)(K / 32) * NC * 4;
+  xp.xsf = (__half *)b;
+  xp.K = K; xp.NC = NC;
+  return xp;
+}
 #define XP_LO_SCALE 2048.0f
 #define XP_LO_INV (1.0f / 2048.0f)
 
@@ -81,6 +97,17 @@ __device__ __forceinline__ void xp_store32(const XPlanes &xp, int t, int planes,
   if (lane == 0) {
     xp.xs32[(size_t)(c >> 5) * xp.NC + t] = hi32;
     if (planes == 2) xp.xs32[(size_t)(c >> 5) * xp.NC + NH + t] = lo32;
+    const int b = (c >> 5) & 7;
+    __half *f = xp.xsf + ((size_t)(c >> 8) * xp.NC + t) * 16 + 4 * (b >> 1) + (b & 1);
+    float v = hi32 * 0.03125f;
+    __half h1 = __float2half_rn(v);
+    f[0] = h1; f[2] = __float2half_rn(v - __half2float(h1));
+    if (planes == 2) {
+      f += (size_t)NH * 16;
+      v = lo32 * 0.03125f;
+      h1 = __float2half_rn(v);
+      f[0] = h1; f[2] = __float2half_rn(v - __half2float(h1));
+    }
   }
 }
 

@@ -61,7 +61,7 @@ struct llb_spec {
         *o = nullptr, *logits = nullptr, *t2part = nullptr, *pm = nullptr, *pl = nullptr, *po = nullptr;
   float *mt_x = nullptr, *mt_hn = nullptr, *chain_h = nullptr, *mt_logits = nullptr;
   XPlanes xp_d, xp_f, xp_qa, xp_v, xp_2d;
-  OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg;
+  OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg, b_ring;
   int att_split = 1;
   // graphs
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
@@ -80,6 +80,7 @@ struct llb_spec {
 };
 
 #define CK(call) do { if ((call)) return -1; } while (0)
+#define RING_SPLITS 4   // K-slices the conv ring can hold per row
 static float bits_float(unsigned int u) { float f; memcpy(&f, &u, 4); return f; }
 
 static void *dalloc(llb_spec *m, size_t bytes) {
@@ -92,11 +93,9 @@ static void *dalloc(llb_spec *m, size_t bytes) {
 }
 static float *falloc(llb_spec *m, size_t n) { return (float *)dalloc(m, n * 4); }
 static int xp_alloc(llb_spec *m, XPlanes &xp, int K) {
-  const int NC = m->NC;
-  size_t bh = (size_t)NC * K * 2, b16 = (size_t)(K / 16) * NC * 4, b32 = (size_t)(K / 32) * NC * 4;
-  char *b = (char *)dalloc(m, bh + b16 + b32);
+  void *b = dalloc(m, xp_bytes(K, m->NC));
   if (!b) return -1;
-  xp.xh = (__half *)b; xp.xs16 = (float *)(b + bh); xp.xs32 = (float *)(b + bh + b16); xp.K = K; xp.NC = NC;
+  xp = xp_carve(b, K, m->NC);
   return 0;
 }
 
@@ -167,7 +166,9 @@ static int check_k(const DevMat &w, int rows, int cols, const char *what) {
 }
 
 // ---- GEMM sites ---------------------------------------------------------------------------------
-struct SiteMat { const DevMat *w; OutBuf *out; const int *tok_slot; float *direct; int direct_stride; };
+// direct: the matrix writes into caller-owned storage (the conv ring) laid out [direct_splits][slots][direct_stride];
+// `out` then only records how many K-slices the launch used
+struct SiteMat { const DevMat *w; OutBuf *out; const int *tok_slot; float *direct; int direct_stride; long long direct_split_stride = 0; int direct_splits = 1; };
 
 // Allocate (at init) or reuse the partial-sum buffer of one matrix and record its split.
 static int out_prepare(llb_spec *m, OutBuf &o, int rows, int ks) {
@@ -195,14 +196,19 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
       if (!done[j] && mats[j].w->fmt == mats[i].w->fmt) { grp.push_back(j); ntiles += (mats[j].w->rows + 15) / 16; }
     bool direct = false;
     for (size_t j : grp) direct = direct || mats[j].direct;
-    int ks = direct ? 1 : force_ks > 0 ? force_ks : gemm_pick_ksplit(ntiles, a.K / 256, g_llb.sms);
-    if (ks > a.K / 256) ks = a.K / 256;
+    int ks = gemm_fix_ksplit(mats[i].w->fmt, xp.NC, a.K / 256,
+                             force_ks > 0 ? force_ks : gemm_pick_ksplit(mats[i].w->fmt, xp.NC, ntiles, a.K / 256, g_llb.sms));
+    (void)direct;
     a.ksplit = ks;
     a.nmat = (int)grp.size();
     for (size_t g = 0; g < grp.size(); g++) {
       SiteMat &sm = mats[grp[g]];
       a.m[g].W = sm.w->w; a.m[g].rows = sm.w->rows; a.m[g].tok_slot = sm.tok_slot;
-      if (sm.direct) { a.m[g].out = sm.direct; a.m[g].ostride = sm.direct_stride; a.m[g].split_stride = 0; }
+      if (sm.direct) {
+        if (ks > sm.direct_splits) return llb_fail("gemm site: %d K-slices, the direct output holds %d", ks, sm.direct_splits);
+        a.m[g].out = sm.direct; a.m[g].ostride = sm.direct_stride; a.m[g].split_stride = sm.direct_split_stride;
+        if (sm.out) { sm.out->p = sm.direct; sm.out->ns = ks; sm.out->stride = sm.direct_split_stride; }
+      }
       else {
         CK(out_prepare(m, *sm.out, sm.w->rows, ks));
         a.m[g].out = sm.out->p; a.m[g].ostride = sm.w->rows; a.m[g].split_stride = sm.out->stride;
@@ -240,9 +246,11 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const 
   cudaStream_t s = g_llb.stream;
   DeltaShape sh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
   // raw qkv rows go straight into the conv ring slot of their position (host/llb_host.c:1747-1749)
-  CK(site_gemm(m, {{&w.qkv, nullptr, &m->ctl->verify.slot[0], ring, m->convd}, {&w.z, &m->b_z, nullptr, nullptr, 0},
-                   {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}}, m->xp_d, 1));
-  CK(op_delta_conv(s, ring, w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
+  // (the ring keeps the K-slice partial sums of each row; the conv kernel adds them as it reads)
+  CK(site_gemm(m, {{&w.qkv, &m->b_ring, &m->ctl->verify.slot[0], ring, m->convd, (long long)CONV_RING * m->convd, RING_SPLITS},
+                   {&w.z, &m->b_z, nullptr, nullptr, 0}, {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}},
+               m->xp_d, 0));
+  CK(op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
   CK(op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
   CK(op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
   CK(site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
@@ -265,8 +273,8 @@ static int enq_verify(llb_spec *m) {
     CK(enq_ffn(m, l.ffn, m->x, m->x1, rs));
   }
   CK(op_norm_xp(s, m->x1, as_in(m->b_dn), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
-  CK(site_gemm(m, {{&m->head, &m->b_lg, nullptr, nullptr, 0}}, m->xp_d, 1));
-  CK(op_top2_part(s, m->b_lg.p, m->V, m->V, m->t2part, rs, m->Tmax));
+  CK(site_gemm(m, {{&m->head, &m->b_lg, nullptr, nullptr, 0}}, m->xp_d, 0));
+  CK(op_top2_part(s, as_in(m->b_lg), m->V, m->V, m->t2part, rs, m->Tmax));
   return 0;
 }
 
@@ -284,8 +292,8 @@ static int enq_mtp(llb_spec *m, const RowSet *rs, const float *h, bool with_head
   CK(enq_ffn(m, m->mt_ffn, m->mt_x, m->x1, rs));
   CK(op_norm_xp(s, m->x1, as_in(m->b_dn), m->mt_shn, m->eps, m->d, nullptr, m->xp_d, 0, m->mt_hn, rs, m->Tmax, 0));
   if (with_head) {
-    CK(site_gemm(m, {{&m->mt_head, &m->b_mlg, nullptr, nullptr, 0}}, m->xp_d, 1));
-    CK(op_top2_part(s, m->b_mlg.p, m->mt_nv, m->mt_nv, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, rs, m->Tmax));
+    CK(site_gemm(m, {{&m->mt_head, &m->b_mlg, nullptr, nullptr, 0}}, m->xp_d, 0));
+    CK(op_top2_part(s, as_in(m->b_mlg), m->mt_nv, m->mt_nv, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, rs, m->Tmax));
   }
   return 0;
 }
@@ -387,7 +395,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
       CK(vec(p + "ssm_a", &l.dn.a, m->TR));
       CK(vec(p + "ssm_conv1d.weight", &l.dn.conv, m->convd * m->KC));
       CK(vec(p + "ssm_norm.weight", &l.dn.norm, m->SZ));
-      m->ring[il] = falloc(m, (size_t)CONV_RING * m->convd);
+      m->ring[il] = falloc(m, (size_t)RING_SPLITS * CONV_RING * m->convd);
       m->S[il] = falloc(m, (size_t)m->R * m->TR * m->SZ * m->SZ);
       if (!m->ring[il] || !m->S[il]) return -1;
     }
@@ -531,7 +539,7 @@ LLB_API void llb_spec_close(llb_spec *m) {
 // read, so only the conv rings and the committed DeltaNet slot need clearing
 LLB_API int llb_spec_reset(llb_spec *m) {
   for (int il = 0; il < m->L; il++) {
-    if (m->ring[il]) CU_OK(cudaMemsetAsync(m->ring[il], 0, (size_t)CONV_RING * m->convd * 4, g_llb.stream));
+    if (m->ring[il]) CU_OK(cudaMemsetAsync(m->ring[il], 0, (size_t)RING_SPLITS * CONV_RING * m->convd * 4, g_llb.stream));
     if (m->S[il]) CU_OK(cudaMemsetAsync(m->S[il], 0, (size_t)m->R * m->TR * m->SZ * m->SZ * 4, g_llb.stream));
   }
   CU_OK(cudaMemsetAsync(m->hn, 0, (size_t)SPEC_MAXT * m->d * 4, g_llb.stream));
@@ -742,7 +750,18 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
     have = (size_t)m->TR * m->SZ * m->SZ; src = m->S[il] + (size_t)c.sc * have;
   } else if (what == 1 && il < m->L && m->Kc[il]) { have = kvd; src = m->Kc[il] + (size_t)pos * kvd; }
   else if (what == 2 && il < m->L && m->Vc[il]) { have = kvd; src = m->Vc[il] + (size_t)pos * kvd; }
-  else if (what == 3 && il < m->L && m->ring[il]) { have = m->convd; src = m->ring[il] + (size_t)(pos & (CONV_RING - 1)) * m->convd; }
+  else if (what == 3 && il < m->L && m->ring[il]) {
+    have = m->convd;
+    if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
+    std::vector<float> tmp(have);
+    for (size_t i = 0; i < have; i++) out[i] = 0.0f;
+    for (int k = 0; k < m->b_ring.ns; k++) {
+      CU_OK(cudaMemcpy(tmp.data(), m->ring[il] + (size_t)k * CONV_RING * m->convd + (size_t)(pos & (CONV_RING - 1)) * m->convd, have * 4,
+                       cudaMemcpyDeviceToHost));
+      for (size_t i = 0; i < have; i++) out[i] += tmp[i];
+    }
+    return (int)have;
+  }
   else if (what == 4) { have = m->d; src = m->hn + (size_t)pos * m->d; }
   else if (what == 5 && m->mt_Kc) { have = kvd; src = m->mt_Kc + (size_t)pos * kvd; }
   else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
@@ -754,8 +773,12 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
 // The logits of verify row r of the last pass (f32 [V]), for the logit-tolerance parity check.
 LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out) {
   CU_OK(cudaStreamSynchronize(g_llb.stream));
-  if (m->b_lg.ns != 1) return llb_fail("logits are split");
-  CU_OK(cudaMemcpy(out, m->b_lg.p + (size_t)r * m->V, (size_t)m->V * 4, cudaMemcpyDeviceToHost));
+  std::vector<float> tmp(m->V);
+  for (int i = 0; i < m->V; i++) out[i] = 0.0f;
+  for (int k = 0; k < m->b_lg.ns; k++) {
+    CU_OK(cudaMemcpy(tmp.data(), m->b_lg.p + (size_t)k * m->b_lg.stride + (size_t)r * m->V, (size_t)m->V * 4, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < m->V; i++) out[i] += tmp[i];
+  }
   return 0;
 }
 

@@ -1,10 +1,28 @@
-// gemm.cu -- host side of the dequant-fused skinny GEMM (kernel in gemm.cuh).
+// gemm.cu -- host side of the dequant-fused skinny GEMMs (kernels in gemm.cuh and gemm2.cuh).
+#include "gemm2.cuh"
 #include "host.cuh"
+
+static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K; }
+static int g2_max_sb(int fmt, int NC) { return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : g2_max_slice_sb<LLB_FM_Q5_K>(NC); }
 
 template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs &a, int grid) {
   k_gemm<FMT, NT><<<grid, GEMM_WARPS * 32, gemm_smem_bytes<FMT>(), s>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return llb_fail("k_gemm launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs &a) {
+  const int NC = 8 * NT, nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
+  int cps = g_llb.sms / a.ksplit;
+  if (cps < 1) cps = 1;
+  // no more CTAs per slice than there are 16-tile groups to hand out
+  const int need = (a.tile0[a.nmat] + G2_WARPS - 1) / G2_WARPS;
+  if (cps > need) cps = need;
+  const size_t smem = (size_t)g2_xp_bytes(nsl, NC) + g2_ring_bytes<FMT>();
+  if (smem > G2_SMEM_MAX) return llb_fail("k_gemm2: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
+  k_gemm2<FMT, NT><<<cps * a.ksplit, G2_WARPS * 32, smem, s>>>(a, cps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return llb_fail("k_gemm2 launch: %s", cudaGetErrorString(e));
   return 0;
 }
 
@@ -13,25 +31,50 @@ template <int FMT> static int setup_fmt() {
   CU_OK(cudaFuncSetAttribute(k_gemm<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem_bytes<FMT>()));
   return 0;
 }
-
-int gemm_setup(void) {
-  if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
+template <int FMT> static int setup_fmt2() {
+  CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   return 0;
 }
 
-// K-slices per row tile: balance (tiles * slices) over the resident warps against the length of the
-// longest slice, with a small charge per slice for the partial sums the consumer has to add.
-int gemm_pick_ksplit(int ntiles, int nsb, int sms) {
-  const long long nw = (long long)sms * GEMM_WARPS;
+int gemm_setup(void) {
+  if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
+  if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>()) return -1;
+  return 0;
+}
+
+int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks) {
+  if (ks < 1) ks = 1;
+  if (is_g2(fmt)) {
+    const int mx = g2_max_sb(fmt, NC);
+    const int lo = (nsb + mx - 1) / mx;       // the activation slice of a CTA has to fit in shared memory
+    if (ks < lo) ks = lo;
+  }
+  if (ks > GEMM_MAXSPLIT) ks = GEMM_MAXSPLIT;
+  if (ks > nsb) ks = nsb;
+  return ks;
+}
+
+// K-slices per row tile: the longest chain of work of any warp (tiles per warp x super-blocks per
+// slice), with a small charge per slice for the partial sums the consumer has to add.
+int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
   int best = 1;
   double best_cost = 1e30;
   for (int ks = 1; ks <= GEMM_MAXSPLIT && ks <= nsb; ks++) {
-    long long rounds = ((long long)ntiles * ks + nw - 1) / nw;
-    int slice = (nsb + ks - 1) / ks;
-    double cost = (double)rounds * slice * (1.0 + 0.02 * (ks - 1));
+    if (gemm_fix_ksplit(fmt, NC, nsb, ks) != ks) continue;
+    long long rounds;
+    if (is_g2(fmt)) {
+      const int cps = sms / ks > 0 ? sms / ks : 1;
+      rounds = (ntiles + (long long)cps * G2_WARPS - 1) / ((long long)cps * G2_WARPS);
+    } else {
+      const long long nw = (long long)sms * GEMM_WARPS;
+      rounds = ((long long)ntiles * ks + nw - 1) / nw;
+    }
+    const int slice = (nsb + ks - 1) / ks;
+    const double cost = (double)rounds * slice * (1.0 + 0.02 * (ks - 1));
     if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
   }
-  return best;
+  return gemm_fix_ksplit(fmt, NC, nsb, best);
 }
 
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
@@ -43,20 +86,15 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   a.tile0[0] = 0;
   for (int i = 0; i < a.nmat; i++) a.tile0[i + 1] = a.tile0[i] + (a.m[i].rows + 15) / 16;
   for (int i = a.nmat; i < GEMM_MAXMAT; i++) a.tile0[i + 1] = a.tile0[a.nmat];
-  if (a.ksplit < 1 || a.ksplit > GEMM_MAXSPLIT || a.ksplit > a.nsb) return llb_fail("gemm: ksplit %d", a.ksplit);
+  if (a.ksplit != gemm_fix_ksplit(fmt, a.xp.NC, a.nsb, a.ksplit)) return llb_fail("gemm: ksplit %d is not valid for this shape", a.ksplit);
+  if (a.tile0[a.nmat] < 1) return 0;
+  const int NT = a.xp.NC / 8;
+  if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : launch_two<LLB_FM_Q4_K, 2>(s, a);
+  if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : launch_two<LLB_FM_Q5_K, 2>(s, a);
   const int nunits = a.tile0[a.nmat] * a.ksplit;
   int grid = (nunits + GEMM_WARPS - 1) / GEMM_WARPS;
   if (grid > g_llb.sms) grid = g_llb.sms;
-  if (grid < 1) return 0;
-  const int NT = a.xp.NC / 8;
-#define GO(F)                                                                     \
-  case F: return NT == 1 ? launch_one<F, 1>(s, a, grid) : launch_one<F, 2>(s, a, grid);
-  switch (fmt) {
-    GO(LLB_FM_Q4_K)
-    GO(LLB_FM_Q5_K)
-    GO(LLB_FM_Q6_K)
-    GO(LLB_FM_Q8_0)
-  }
-#undef GO
+  if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_one<LLB_FM_Q6_K, 1>(s, a, grid) : launch_one<LLB_FM_Q6_K, 2>(s, a, grid);
+  if (fmt == LLB_FM_Q8_0) return NT == 1 ? launch_one<LLB_FM_Q8_0, 1>(s, a, grid) : launch_one<LLB_FM_Q8_0, 2>(s, a, grid);
   return llb_fail("gemm: format %d has no kernel", fmt);
 }

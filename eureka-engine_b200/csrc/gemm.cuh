@@ -60,7 +60,15 @@ __device__ __forceinline__ void k4_scales(uint32_t u0, uint32_t u1, uint32_t u2,
   scB = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
   mnB = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
 }
-__device__ __forceinline__ float byte_f(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
+// byte i of w as a float without the conversion pipe: 0x4B0000bb is 2^23 + bb exactly
+__device__ __forceinline__ float byte_f(uint32_t w, int i) {
+  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u | (uint32_t)i)) - 8388608.0f;
+}
+
+// the same times a power of two, in one FMA: (2^23 + bb) * s - 2^23 * s is exact
+__device__ __forceinline__ float byte_f_scaled(uint32_t w, int i, float s) {
+  return fmaf(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u | (uint32_t)i)), s, -8388608.0f * s);
+}
 
 #define TWO24 16777216.0f
 

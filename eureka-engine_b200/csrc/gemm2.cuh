@@ -1,0 +1,221 @@
+// gemm2.cuh -- second-generation skinny GEMM for the 4/5-bit K-quants (Q4_K, Q5_K), the formats that
+// carry most of a Q4_K_M model's bytes.  Same arithmetic as gemm.cuh (integer codes as fp16
+// subnormals into mma.m16n8k16, scales applied to fp32 partial sums); what changes is everything
+// around the MMAs, driven by the first kernel's profile (issue-bound at 670 instructions per
+// 16-row x 256-column tile-super-block, activation loads waiting on L1/L2):
+//
+//  * a CTA owns ONE K-slice and stages that slice of the activation planes in shared memory once;
+//    all B-fragment reads are then conflict-free LDS.128 (column stride = 64 mod 128 bytes);
+//  * 16 warps per SM, one-super-block stages, three-deep private cp.async rings
+//    (row stride 160 / 224 bytes = 32 / 96 mod 128: conflict-free 8-byte A-fragment reads);
+//  * the copy issue loop has no division and no per-piece address arithmetic beyond one add;
+//  * the Q4_K "min" term  dmin * sum_b m_b * sum(x in sub-block b)  is ONE extra MMA per
+//    tile-super-block: A = the eight 6-bit mins (fp16 subnormal integers, twice), B = the
+//    sub-block activation means as fp16 hi/lo pairs prepared with the planes;
+//  * first MMAs of a sub-block take a zero C operand instead of zeroing registers.
+#pragma once
+#include "gemm.cuh"
+
+#define G2_WARPS 16
+#define G2_STAGES 3
+#define G2_SMEM_MAX 232448   // 227 KB per CTA on sm_100
+
+template <int FMT> struct G2Traits;
+template <> struct G2Traits<LLB_FM_Q4_K> { enum { SB = 144, RS = 160, P = 9, QOFF = 16 }; };
+template <> struct G2Traits<LLB_FM_Q5_K> { enum { SB = 176, RS = 224, P = 11, QOFF = 48 }; };
+
+template <int FMT> constexpr int g2_ring_bytes() { return G2_WARPS * G2_STAGES * 16 * G2Traits<FMT>::RS; }
+// bytes of shared memory a K-slice of nsl super-blocks needs for NC activation columns
+__host__ __device__ inline int g2_xp_bytes(int nsl, int NC) { return NC * (nsl * 512 + 64) + nsl * NC * 32; }
+template <int FMT> inline int g2_max_slice_sb(int NC) {
+  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>() - NC * 64;
+  return left / (NC * 512 + NC * 32);
+}
+
+// D = A*B with a zero C operand
+__device__ __forceinline__ void mma16816_z(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+template <int FMT, int NT>
+__global__ void __launch_bounds__(G2_WARPS * 32, 1) k_gemm2(const GemmArgs a, const int cps) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using TR = G2Traits<FMT>;
+  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
+  const int ks = blockIdx.x % a.ksplit, ci = blockIdx.x / a.ksplit;
+  const int sb0 = (int)(((long long)ks * a.nsb) / a.ksplit), nsl = (int)(((long long)(ks + 1) * a.nsb) / a.ksplit) - sb0;
+  const int CS = nsl * 512 + 64;
+  uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * 32 + (size_t)warp * G2_STAGES * 16 * RS;
+  const uint32_t ring_s = smem_u32(ring);
+  const int ntiles = a.tile0[a.nmat], nws = cps * G2_WARPS;
+  const size_t rb = dev_row_bytes(FMT, a.K);
+
+  // per-lane copy plan: piece i = lane + 32*it of the 16 x P sixteen-byte pieces of a stage
+  uint32_t dst_rel[NIT], row_of[NIT], pc_of[NIT];
+#pragma unroll
+  for (int it = 0; it < NIT; it++) {
+    const int i = lane + 32 * it, r = i / P, p = i - r * P;
+    row_of[it] = r; pc_of[it] = p * 16; dst_rel[it] = i < 16 * P ? r * RS + p * 16 : 0xffffffffu;
+  }
+  // producer cursor
+  int p_tile = ci * G2_WARPS + warp, p_c = 0;
+  const uint8_t *p_W = nullptr;
+  uint32_t p_off[NIT];
+  auto plan_tile = [&](int tile) {
+    if (tile >= ntiles) return;
+    int m = 0;
+    while (m + 1 < a.nmat && tile >= a.tile0[m + 1]) m++;
+    const int row0 = (tile - a.tile0[m]) * 16, rows = a.m[m].rows;
+    p_W = a.m[m].W + (size_t)sb0 * SB;
+#pragma unroll
+    for (int it = 0; it < NIT; it++) p_off[it] = (uint32_t)min(row0 + (int)row_of[it], rows - 1) * (uint32_t)rb + pc_of[it];
+  };
+  auto issue = [&](int stage) {
+    if (p_tile < ntiles) {
+      const uint8_t *src = p_W + (size_t)p_c * SB;
+      const uint32_t dst = ring_s + stage * 16 * RS;
+#pragma unroll
+      for (int it = 0; it < NIT; it++)
+        if (dst_rel[it] != 0xffffffffu) cp_async16(dst + dst_rel[it], src + p_off[it]);
+      if (++p_c == nsl) { p_c = 0; p_tile += nws; plan_tile(p_tile); }
+    }
+    cp_async_commit();
+  };
+  plan_tile(p_tile);
+  // weights first: the ring's prologue is in flight while the activation slice is staged
+#pragma unroll 1
+  for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
+  {
+    const int per_col = nsl * 32;   // 16-byte pieces of one column's slice
+    for (int i = threadIdx.x; i < NC * per_col; i += blockDim.x) {
+      const int c = i / per_col, p = i - c * per_col;
+      cp_async16(smem_u32(xh_s + c * CS + p * 16), (const uint8_t *)(a.xp.xh + (size_t)c * a.K + (size_t)sb0 * 256) + p * 16);
+    }
+    const uint8_t *xf = (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
+    for (int i = threadIdx.x; i < nsl * NC * 2; i += blockDim.x) cp_async16(smem_u32(xsf_s + i * 16), xf + i * 16);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+  // the XP group sits between prologue groups and later ones; from here on group accounting is per
+  // warp again: G2_STAGES-1 chunks are complete, none pending
+  int pstage = G2_STAGES - 1, cstage = 0;
+  int c_tile = ci * G2_WARPS + warp, c_c = 0;
+  float acc[NT][4];
+  const uint8_t *xb = xh_s + gid * CS + 16 * j;          // B fragments of column gid (n-tile 0)
+  const uint8_t *xfb = xsf_s + gid * 32 + 8 * j;
+  const uint32_t mn_sel = (j & 1) ? 0x4342u : 0x4140u;
+#pragma unroll 1
+  while (c_tile < ntiles) {
+    if (c_c == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    }
+    issue(pstage);                       // refill the stage consumed last iteration
+    pstage = pstage + 1 == G2_STAGES ? 0 : pstage + 1;
+    cp_async_wait<G2_STAGES - 1>();      // all but the newest G2_STAGES-1 groups: the stage to consume is in
+    __syncwarp();
+    {
+      const uint8_t *b0 = ring + cstage * 16 * RS + gid * RS, *b1 = b0 + 8 * RS;
+      const uint4 h0 = *(const uint4 *)b0, h1 = *(const uint4 *)b1;
+      uint32_t scA0, scB0, mnA0, mnB0, scA1, scB1, mnA1, mnB1;
+      k4_scales(h0.y, h0.z, h0.w, scA0, scB0, mnA0, mnB0);
+      k4_scales(h1.y, h1.z, h1.w, scA1, scB1, mnA1, mnB1);
+      const uint32_t am0 = __byte_perm(j < 2 ? mnA0 : mnB0, 0, mn_sel), am1 = __byte_perm(j < 2 ? mnA1 : mnB1, 0, mn_sel);
+      uint32_t qh0 = 0, qh0b = 0, qh1 = 0, qh1b = 0;
+      if constexpr (FMT == LLB_FM_Q5_K) {
+        const uint2 t0 = *(const uint2 *)(b0 + 16 + 8 * j), t1 = *(const uint2 *)(b1 + 16 + 8 * j);
+        qh0 = t0.x; qh0b = t0.y; qh1 = t1.x; qh1b = t1.y;
+      }
+      float sS[NT][4], pm[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        const uint2 xf = *(const uint2 *)(xfb + (size_t)c_c * NC * 32 + nt * 8 * 32);
+        mma16816_z(pm[nt], am0, am1, am0, am1, xf.x, xf.y);
+        sS[nt][0] = sS[nt][1] = sS[nt][2] = sS[nt][3] = 0.0f;
+      }
+#pragma unroll
+      for (int g = 0; g < 4; g++) {
+        const uint2 a0 = *(const uint2 *)(b0 + TR::QOFF + 32 * g + 8 * j), a1 = *(const uint2 *)(b1 + TR::QOFF + 32 * g + 8 * j);
+        uint32_t f0l = 0, f0h = 0, f1l = 0, f1h = 0, f0lb = 0, f0hb = 0, f1lb = 0, f1hb = 0;
+        if constexpr (FMT == LLB_FM_Q5_K) {
+          f0l = (qh0 >> (2 * g)) & 0x01010101u; f0h = (qh0 >> (2 * g + 1)) & 0x01010101u;
+          f1l = (qh1 >> (2 * g)) & 0x01010101u; f1h = (qh1 >> (2 * g + 1)) & 0x01010101u;
+          f0lb = (qh0b >> (2 * g)) & 0x01010101u; f0hb = (qh0b >> (2 * g + 1)) & 0x01010101u;
+          f1lb = (qh1b >> (2 * g)) & 0x01010101u; f1hb = (qh1b >> (2 * g + 1)) & 0x01010101u;
+        }
+        const uint32_t s0 = g < 2 ? scA0 : scB0, s1 = g < 2 ? scA1 : scB1;
+        const float sc0l = byte_f(s0, (2 * g) & 3), sc0h = byte_f_scaled(s0, (2 * g + 1) & 3, 0.0625f);
+        const float sc1l = byte_f(s1, (2 * g) & 3), sc1h = byte_f_scaled(s1, (2 * g + 1) & 3, 0.0625f);
+        const uint32_t a0x8 = a0.x >> 8, a0y8 = a0.y >> 8, a1x8 = a1.x >> 8, a1y8 = a1.y >> 8;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const uint8_t *xr = xb + (size_t)nt * 8 * CS + ((size_t)c_c * 256 + 64 * g) * 2;
+          const uint4 bl = *(const uint4 *)xr, bh = *(const uint4 *)(xr + 64);
+          float pl[4], ph[4];
+          mma16816_z(pl, (a0.x & 0x000f000fu) | ((f0l & 0x00010001u) << 4), (a1.x & 0x000f000fu) | ((f1l & 0x00010001u) << 4),
+                     (a0x8 & 0x000f000fu) | (((f0l >> 8) & 0x00010001u) << 4), (a1x8 & 0x000f000fu) | (((f1l >> 8) & 0x00010001u) << 4), bl.x, bl.y);
+          mma16816(pl, (a0.y & 0x000f000fu) | ((f0lb & 0x00010001u) << 4), (a1.y & 0x000f000fu) | ((f1lb & 0x00010001u) << 4),
+                   (a0y8 & 0x000f000fu) | (((f0lb >> 8) & 0x00010001u) << 4), (a1y8 & 0x000f000fu) | (((f1lb >> 8) & 0x00010001u) << 4), bl.z, bl.w);
+          mma16816_z(ph, (a0.x & 0x00f000f0u) | ((f0h & 0x00010001u) << 8), (a1.x & 0x00f000f0u) | ((f1h & 0x00010001u) << 8),
+                     (a0x8 & 0x00f000f0u) | (((f0h >> 8) & 0x00010001u) << 8), (a1x8 & 0x00f000f0u) | (((f1h >> 8) & 0x00010001u) << 8), bh.x, bh.y);
+          mma16816(ph, (a0.y & 0x00f000f0u) | ((f0hb & 0x00010001u) << 8), (a1.y & 0x00f000f0u) | ((f1hb & 0x00010001u) << 8),
+                   (a0y8 & 0x00f000f0u) | (((f0hb >> 8) & 0x00010001u) << 8), (a1y8 & 0x00f000f0u) | (((f1hb >> 8) & 0x00010001u) << 8), bh.z, bh.w);
+          sS[nt][0] += sc0l * pl[0] + sc0h * ph[0];
+          sS[nt][1] += sc0l * pl[1] + sc0h * ph[1];
+          sS[nt][2] += sc1l * pl[2] + sc1h * ph[2];
+          sS[nt][3] += sc1l * pl[3] + sc1h * ph[3];
+        }
+      }
+      const float d0 = h2f_bits(h0.x & 0xffffu) * TWO24, dm0 = h2f_bits(h0.x >> 16) * (TWO24 * 32.0f);
+      const float d1 = h2f_bits(h1.x & 0xffffu) * TWO24, dm1 = h2f_bits(h1.x >> 16) * (TWO24 * 32.0f);
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        acc[nt][0] += d0 * sS[nt][0] - dm0 * pm[nt][0];
+        acc[nt][1] += d0 * sS[nt][1] - dm0 * pm[nt][1];
+        acc[nt][2] += d1 * sS[nt][2] - dm1 * pm[nt][2];
+        acc[nt][3] += d1 * sS[nt][3] - dm1 * pm[nt][3];
+      }
+    }
+    __syncwarp();
+    cstage = cstage + 1 == G2_STAGES ? 0 : cstage + 1;
+    if (++c_c == nsl) {
+      int m = 0;
+      while (m + 1 < a.nmat && c_tile >= a.tile0[m + 1]) m++;
+      const GemmMat &M = a.m[m];
+      const int row0 = (c_tile - a.tile0[m]) * 16;
+      float *out = M.out + (size_t)ks * M.split_stride;
+      if (a.planes == 2) {
+        float lo[4];
+        if constexpr (NT == 1) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) lo[i] = __shfl_xor_sync(0xffffffffu, acc[0][i], 2);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; i++) lo[i] = acc[NT - 1][i];
+        }
+        if (NT == 2 || j < 2) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const int t = 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
+            if (t < a.T && r < M.rows) out[(size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r] = acc[0][i] + lo[i] * XP_LO_INV;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const int t = nt * 8 + 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
+            if (t < a.T && r < M.rows) out[(size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r] = acc[nt][i];
+          }
+      }
+      c_c = 0;
+      c_tile += nws;
+    }
+  }
+  cp_async_wait<0>();
+}

@@ -30,7 +30,8 @@ inline int llb_fail(const char *fmt, ...) {
   } while (0)
 
 // gemm.cu
-int gemm_pick_ksplit(int ntiles, int nsb, int sms);
+int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms);
+int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks);   // clamps a requested K-split to what the format's kernel can take
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
 int gemm_setup(void);
 

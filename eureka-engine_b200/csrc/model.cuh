@@ -64,13 +64,13 @@ int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, c
               AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax);
 int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
                  float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax);
-int op_delta_conv(cudaStream_t s, const float *ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
+int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax);
 int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,
                   DeltaShape sh, float *o, const RowSet *rs, int Tmax);
 int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs,
                 int Tmax);
-int op_top2_part(cudaStream_t s, const float *logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
+int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
 int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax);
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
                   float *chain_h, int d);

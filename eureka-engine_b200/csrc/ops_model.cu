@@ -45,35 +45,59 @@ int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs,
 // tools/payload-spec2.patch:35-112; rms_norm tools/qwen35_engine.c:510-515) ----------------------
 // v = xin + sum(partials); xout = v (optional); h = (v * s) * w, s = 1/sqrt(mean(v^2) + eps);
 // h goes to the planes at column offset xp_col0 and, optionally, to hn_out as f32.
-__global__ void k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
-                          float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
-                          const RowSet *__restrict__ rs, int zero_if_pos0) {
-  extern __shared__ float rowbuf[];
+#define NORM_THREADS 1024
+#define NORM_MAXI 8   // columns per thread: d <= 8192
+__global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
+                                                          float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
+                                                          const RowSet *__restrict__ rs, int zero_if_pos0) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   if (t >= rs->n) return;
   const bool zero = zero_if_pos0 && (rs->pos0 + t == 0);
+  const size_t row = (size_t)t * d;
+  // every load of the row is issued before the first use: one round trip to L2, not one per element
+  float v[NORM_MAXI];
+#pragma unroll
+  for (int i = 0; i < NORM_MAXI; i++) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    v[i] = (c < d && xin && !zero) ? xin[row + c] : 0.0f;
+  }
+  if (add.p && !zero) {
+    for (int k = 0; k < add.ns; k++) {
+      const float *pk = add.p + (size_t)k * add.stride + row;
+#pragma unroll
+      for (int i = 0; i < NORM_MAXI; i++) {
+        const int c = threadIdx.x + i * NORM_THREADS;
+        if (c < d) v[i] += pk[c];
+      }
+    }
+  }
   float ss = 0.0f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float v = (zero || !xin) ? 0.0f : xin[(size_t)t * d + c];
-    if (add.p && !zero) v += part_get(add, (size_t)t * d + c);
-    rowbuf[c] = v;
-    if (xout) xout[(size_t)t * d + c] = v;
-    ss += v * v;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXI; i++) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < d) {
+      if (xout) xout[row + c] = v[i];
+      ss += v[i] * v[i];
+    }
   }
   ss = block_sum(ss, red);
   const float sc = 1.0f / sqrtf(ss / (float)d + eps);
   const int lane = threadIdx.x & 31;
-  for (int c0 = (threadIdx.x & ~31); c0 < d; c0 += blockDim.x) {
-    float h = rowbuf[c0 + lane] * sc * w[c0 + lane];
-    if (hn_out) hn_out[(size_t)t * d + c0 + lane] = h;
-    xp_store32(xp, t, 2, xp_col0 + c0, h, lane);
+#pragma unroll
+  for (int i = 0; i < NORM_MAXI; i++) {
+    const int c = threadIdx.x + i * NORM_THREADS;   // a warp's 32 lanes hold 32 consecutive columns
+    if (c < d) {
+      const float h = v[i] * sc * w[c];
+      if (hn_out) hn_out[row + c] = h;
+      xp_store32(xp, t, 2, xp_col0 + (c & ~31), h, lane);
+    }
   }
 }
 int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
                int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0) {
-  if (d % 32) return llb_fail("norm: d %d", d);
-  k_norm_xp<<<Tmax, 512, (size_t)d * 4, s>>>(xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0);
+  if (d % 32 || d > NORM_THREADS * NORM_MAXI) return llb_fail("norm: d %d", d);
+  k_norm_xp<<<Tmax, NORM_THREADS, 0, s>>>(xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0);
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -257,18 +281,30 @@ __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, 
 // (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
 __global__ void k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
                             AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *__restrict__ rs) {
+  __shared__ float wsm[128];
+  __shared__ float red[32];
   const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = sh.hd, lane = threadIdx.x & 31;
   if (t >= rs->n) return;
   const size_t qb = ((size_t)h * Tmax + t) * nsplit;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; s++) M = fmaxf(M, pm[qb + s]);
-  float L = 0.0f, o = 0.0f;
-  for (int s = 0; s < nsplit; s++) {
-    const float ms = pm[qb + s];
-    if (ms == -INFINITY) continue;
-    const float w = expf(ms - M);
-    L += pl[qb + s] * w;
-    o += po[(qb + s) * hd + i] * w;
+  // slices in use at this context length (the partial kernel's split rule)
+  const int total = rs->pos0 + rs->n;
+  const int per = max(64, (total + nsplit - 1) / nsplit), nact = min(nsplit, (total + per - 1) / per);
+  float m = -INFINITY, l = 0.0f;
+  if (i < nact) { m = pm[qb + i]; l = pl[qb + i]; }
+  float M = warp_max(m);
+  __syncthreads();
+  if (lane == 0) red[i >> 5] = M;
+  __syncthreads();
+  M = red[0];
+  for (int k = 1; k < (blockDim.x >> 5); k++) M = fmaxf(M, red[k]);
+  const float wgt = (i < nact && m != -INFINITY) ? expf(m - M) : 0.0f;
+  if (i < 128) wsm[i] = wgt;
+  const float L = block_sum(l * wgt, red);   // (block_sum synchronises: wsm is visible after it)
+  float o = 0.0f;
+#pragma unroll 4
+  for (int s = 0; s < nact; s++) {
+    const float ws = wsm[s];
+    if (ws != 0.0f) o += po[(qb + s) * hd + i] * ws;
   }
   const float gate = part_get(qg, (size_t)t * 2 * sh.H * hd + (size_t)h * 2 * hd + hd + i);
   xp_store32(xp, t, 2, h * hd + (i & ~31), (o / L) * sigmoid_f(gate), lane);
@@ -317,7 +353,7 @@ int ops_model_setup(void) {
 // conv1d + SiLU over the position-indexed ring, and the per-head gates
 // (llb_t_midconv, tools/payload-spec2.patch:319-350; tools/qwen35_engine.c:589-602).
 // grid (ceil(convd/256) + 1, Tmax): the last block computes beta = sigmoid(b), decay = exp(softplus(a + dt) * ssm_a).
-__global__ void k_delta_conv(const float *__restrict__ ring, const float *__restrict__ cw, PartIn bp, PartIn ap,
+__global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn bp, PartIn ap,
                              const float *__restrict__ dt, const float *__restrict__ sa, DeltaShape sh, float *__restrict__ y,
                              float *__restrict__ beta, float *__restrict__ decay, const RowSet *__restrict__ rs) {
   const int t = blockIdx.y;
@@ -338,11 +374,11 @@ __global__ void k_delta_conv(const float *__restrict__ ring, const float *__rest
   float acc = 0.0f;
   for (int k = 0; k < sh.KC; k++) {  // tap KC-1 is the current token (tools/qwen35_engine.c:599-600)
     const int slot = (pos - (sh.KC - 1) + k) & (CONV_RING - 1);
-    acc = __fadd_rn(acc, __fmul_rn(ring[(size_t)slot * sh.convd + c], cw[c * sh.KC + k]));
+    acc = __fadd_rn(acc, __fmul_rn(part_get(ring, (size_t)slot * sh.convd + c), cw[c * sh.KC + k]));
   }
   y[(size_t)t * sh.convd + c] = silu_f(acc);
 }
-int op_delta_conv(cudaStream_t s, const float *ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
+int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax) {
   if (sh.KC > CONV_RING / 2) return llb_fail("conv kernel %d", sh.KC);
   k_delta_conv<<<dim3((sh.convd + 255) / 256 + 1, Tmax), 256, 0, s>>>(ring, cw, bp, ap, dt, sa, sh, y, beta, decay, rs);
@@ -360,31 +396,51 @@ __global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const
                                                     const float *__restrict__ y, const float *__restrict__ beta,
                                                     const float *__restrict__ decay, DeltaShape sh, float *__restrict__ o,
                                                     const RowSet *__restrict__ rs) {
-  __shared__ float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128], vs[SPEC_MAXT][32];
-  __shared__ float red[32];
-  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs->n;
+  __shared__ float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128], vs[SPEC_MAXT][32], db[SPEC_MAXT][2];
+  __shared__ float red[2 * SPEC_MAXT][4];
+  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs->n, lane = tid & 31, wp = tid >> 5;
   const int g = hh % sh.GK;   // value head hh reads q/k group hh % GK (tile, tools/qwen35_engine.c:621-626)
-  for (int t = 0; t < n; t++) {
-    const float qv = y[(size_t)t * sh.convd + g * 128 + tid], kv = y[(size_t)t * sh.convd + sh.kdc + g * 128 + tid];
-    const float sq = block_sum(qv * qv, red), sk = block_sum(kv * kv, red);
-    const float nq = sqrtf(sq), nk = sqrtf(sk);
-    const float iq = (1.0f / (nq > sh.eps ? nq : sh.eps)) / sqrtf(128.0f), ik = 1.0f / (nk > sh.eps ? nk : sh.eps);
-    qs[t][tid] = qv * iq;
-    ks[t][tid] = kv * ik;
-    if (tid < 32) vs[t][tid] = y[(size_t)t * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + tid];
-  }
-  __syncthreads();
   const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
   const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
   const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 32 * cq;
+  // the state rows first: their latency hides behind the q/k preparation
   float st[32];
   {
     const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
 #pragma unroll
     for (int i = 0; i < 8; i++) { float4 v = src[i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
   }
+  float qv[SPEC_MAXT], kv[SPEC_MAXT];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    qv[t] = t < n ? y[(size_t)t * sh.convd + g * 128 + tid] : 0.0f;
+    kv[t] = t < n ? y[(size_t)t * sh.convd + sh.kdc + g * 128 + tid] : 0.0f;
+  }
+  if (tid < 32) {
+#pragma unroll
+    for (int t = 0; t < SPEC_MAXT; t++) if (t < n) vs[t][tid] = y[(size_t)t * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + tid];
+  }
+  if (tid < 2 * SPEC_MAXT && (tid >> 1) < n) db[tid >> 1][tid & 1] = (tid & 1) ? beta[(tid >> 1) * sh.TR + hh] : decay[(tid >> 1) * sh.TR + hh];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    const float a = warp_sum(qv[t] * qv[t]), b = warp_sum(kv[t] * kv[t]);
+    if (lane == 0) { red[2 * t][wp] = a; red[2 * t + 1][wp] = b; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    if (t < n) {
+      const float sq = red[2 * t][0] + red[2 * t][1] + red[2 * t][2] + red[2 * t][3];
+      const float sk = red[2 * t + 1][0] + red[2 * t + 1][1] + red[2 * t + 1][2] + red[2 * t + 1][3];
+      const float nq = sqrtf(sq), nk = sqrtf(sk);
+      const float iq = (1.0f / (nq > sh.eps ? nq : sh.eps)) / sqrtf(128.0f), ik = 1.0f / (nk > sh.eps ? nk : sh.eps);
+      qs[t][tid] = qv[t] * iq;
+      ks[t][tid] = kv[t] * ik;
+    }
+  }
+  __syncthreads();
   for (int t = 0; t < n; t++) {
-    const float dec = decay[t * sh.TR + hh], bt = beta[t * sh.TR + hh];
+    const float dec = db[t][0], bt = db[t][1];
     float kvacc = 0.0f;
 #pragma unroll
     for (int i = 0; i < 32; i++) { st[i] *= dec; kvacc += st[i] * ks[t][32 * cq + i]; }
@@ -449,15 +505,15 @@ __device__ __forceinline__ Top2 t2_warp(Top2 a) {
   }
   return a;
 }
-__global__ void __launch_bounds__(256) k_top2_part(const float *__restrict__ logits, int V, long long row_stride,
+__global__ void __launch_bounds__(256) k_top2_part(PartIn logits, int V, long long row_stride,
                                                    float *__restrict__ part, const RowSet *__restrict__ rs) {
   __shared__ Top2 sh[8];
   const int t = blockIdx.y;
   if (t >= rs->n) return;
-  const float *z = logits + (size_t)t * row_stride;
+  const size_t z0 = (size_t)t * row_stride;
   const int per = (V + gridDim.x - 1) / gridDim.x, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
   Top2 a = {0.f, -1, 0.f, -1};
-  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) t2_push(a, z[i], i);
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) t2_push(a, part_get(logits, z0 + i), i);
   a = t2_warp(a);
   if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = a;
   __syncthreads();
@@ -470,7 +526,7 @@ __global__ void __launch_bounds__(256) k_top2_part(const float *__restrict__ log
     }
   }
 }
-int op_top2_part(cudaStream_t s, const float *logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax) {
+int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax) {
   k_top2_part<<<dim3(TOP2_NB, Tmax), 256, 0, s>>>(logits, V, row_stride, part, rs);
   CU_OK(cudaGetLastError());
   return 0;
