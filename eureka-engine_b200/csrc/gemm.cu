@@ -2,8 +2,11 @@
 #include "gemm2.cuh"
 #include "host.cuh"
 
-static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K; }
-static int g2_max_sb(int fmt, int NC) { return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : g2_max_slice_sb<LLB_FM_Q5_K>(NC); }
+static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K; }
+static int g2_max_sb(int fmt, int NC) {
+  return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC) : g2_max_slice_sb<LLB_FM_Q6_K>(NC);
+}
+static int g2_warps(int fmt) { return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS; }
 
 template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs &a, int grid) {
   k_gemm<FMT, NT><<<grid, GEMM_WARPS * 32, gemm_smem_bytes<FMT>(), s>>>(a);
@@ -16,9 +19,10 @@ template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs 
   int cps = g_llb.sms / a.ksplit;
   if (cps < 1) cps = 1;
   // no more CTAs per slice than there are 16-tile groups to hand out
+  constexpr int G2_WARPS = G2Traits<FMT>::WARPS;
   const int need = (a.tile0[a.nmat] + G2_WARPS - 1) / G2_WARPS;
   if (cps > need) cps = need;
-  const size_t smem = (size_t)g2_xp_bytes(nsl, NC) + g2_ring_bytes<FMT>();
+  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
   if (smem > G2_SMEM_MAX) return llb_fail("k_gemm2: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
   k_gemm2<FMT, NT><<<cps * a.ksplit, G2_WARPS * 32, smem, s>>>(a, cps);
   cudaError_t e = cudaGetLastError();
@@ -39,7 +43,7 @@ template <int FMT> static int setup_fmt2() {
 
 int gemm_setup(void) {
   if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
-  if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>()) return -1;
+  if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>()) return -1;
   return 0;
 }
 
@@ -65,7 +69,7 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
     long long rounds;
     if (is_g2(fmt)) {
       const int cps = sms / ks > 0 ? sms / ks : 1;
-      rounds = (ntiles + (long long)cps * G2_WARPS - 1) / ((long long)cps * G2_WARPS);
+      rounds = (ntiles + (long long)cps * g2_warps(fmt) - 1) / ((long long)cps * g2_warps(fmt));
     } else {
       const long long nw = (long long)sms * GEMM_WARPS;
       rounds = ((long long)ntiles * ks + nw - 1) / nw;
@@ -91,6 +95,7 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   const int NT = a.xp.NC / 8;
   if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : launch_two<LLB_FM_Q4_K, 2>(s, a);
   if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : launch_two<LLB_FM_Q5_K, 2>(s, a);
+  if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_two<LLB_FM_Q6_K, 1>(s, a) : launch_two<LLB_FM_Q6_K, 2>(s, a);
   const int nunits = a.tile0[a.nmat] * a.ksplit;
   int grid = (nunits + GEMM_WARPS - 1) / GEMM_WARPS;
   if (grid > g_llb.sms) grid = g_llb.sms;

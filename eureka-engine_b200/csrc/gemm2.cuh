@@ -16,20 +16,26 @@
 #pragma once
 #include "gemm.cuh"
 
-#define G2_WARPS 16
 #define G2_STAGES 3
 #define G2_SMEM_MAX 232448   // 227 KB per CTA on sm_100
 
+// SB bytes per super-block, RS ring row stride, P 16-byte pieces per row-super-block, WARPS per CTA,
+// XPAD: padding of a plane column in shared memory (column stride = 64 mod 128 bytes for the 16-byte
+// B reads of Q4_K/Q5_K, 32 mod 128 for the 8-byte ones of Q6_K), AUX: bytes per (super-block, column)
+// of the side array (Q4_K/Q5_K: 16 fp16 sub-block means; Q6_K: 16 f32 sums of 16 columns)
 template <int FMT> struct G2Traits;
-template <> struct G2Traits<LLB_FM_Q4_K> { enum { SB = 144, RS = 160, P = 9, QOFF = 16 }; };
-template <> struct G2Traits<LLB_FM_Q5_K> { enum { SB = 176, RS = 224, P = 11, QOFF = 48 }; };
+template <> struct G2Traits<LLB_FM_Q4_K> { enum { SB = 144, RS = 160, P = 9, QOFF = 16, WARPS = 16, XPAD = 64, AUX = 32 }; };
+template <> struct G2Traits<LLB_FM_Q5_K> { enum { SB = 176, RS = 224, P = 11, QOFF = 48, WARPS = 16, XPAD = 64, AUX = 32 }; };
+template <> struct G2Traits<LLB_FM_Q6_K> { enum { SB = 224, RS = 240, P = 14, QOFF = 0, WARPS = 12, XPAD = 32, AUX = 64 }; };
 
-template <int FMT> constexpr int g2_ring_bytes() { return G2_WARPS * G2_STAGES * 16 * G2Traits<FMT>::RS; }
+template <int FMT> constexpr int g2_ring_bytes() { return G2Traits<FMT>::WARPS * G2_STAGES * 16 * G2Traits<FMT>::RS; }
 // bytes of shared memory a K-slice of nsl super-blocks needs for NC activation columns
-__host__ __device__ inline int g2_xp_bytes(int nsl, int NC) { return NC * (nsl * 512 + 64) + nsl * NC * 32; }
+template <int FMT> __host__ __device__ inline int g2_xp_bytes(int nsl, int NC) {
+  return NC * (nsl * 512 + G2Traits<FMT>::XPAD) + nsl * NC * G2Traits<FMT>::AUX;
+}
 template <int FMT> inline int g2_max_slice_sb(int NC) {
-  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>() - NC * 64;
-  return left / (NC * 512 + NC * 32);
+  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>() - NC * G2Traits<FMT>::XPAD;
+  return left / (NC * 512 + NC * G2Traits<FMT>::AUX);
 }
 
 // D = A*B with a zero C operand
@@ -40,15 +46,15 @@ __device__ __forceinline__ void mma16816_z(float d[4], uint32_t a0, uint32_t a1,
 }
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(G2_WARPS * 32, 1) k_gemm2(const GemmArgs a, const int cps) {
+__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, 1) k_gemm2(const GemmArgs a, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   using TR = G2Traits<FMT>;
-  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32;
+  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = TR::WARPS;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
   const int ks = blockIdx.x % a.ksplit, ci = blockIdx.x / a.ksplit;
   const int sb0 = (int)(((long long)ks * a.nsb) / a.ksplit), nsl = (int)(((long long)(ks + 1) * a.nsb) / a.ksplit) - sb0;
-  const int CS = nsl * 512 + 64;
-  uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * 32 + (size_t)warp * G2_STAGES * 16 * RS;
+  const int CS = nsl * 512 + TR::XPAD;
+  uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * TR::AUX + (size_t)warp * G2_STAGES * 16 * RS;
   const uint32_t ring_s = smem_u32(ring);
   const int ntiles = a.tile0[a.nmat], nws = cps * G2_WARPS;
   const size_t rb = dev_row_bytes(FMT, a.K);
@@ -94,8 +100,9 @@ __global__ void __launch_bounds__(G2_WARPS * 32, 1) k_gemm2(const GemmArgs a, co
       const int c = i / per_col, p = i - c * per_col;
       cp_async16(smem_u32(xh_s + c * CS + p * 16), (const uint8_t *)(a.xp.xh + (size_t)c * a.K + (size_t)sb0 * 256) + p * 16);
     }
-    const uint8_t *xf = (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
-    for (int i = threadIdx.x; i < nsl * NC * 2; i += blockDim.x) cp_async16(smem_u32(xsf_s + i * 16), xf + i * 16);
+    // the side array of the slice: contiguous in global memory for both kinds
+    const uint8_t *xf = FMT == LLB_FM_Q6_K ? (const uint8_t *)(a.xp.xs16 + (size_t)sb0 * 16 * NC) : (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
+    for (int i = threadIdx.x; i < nsl * NC * (TR::AUX / 16); i += blockDim.x) cp_async16(smem_u32(xsf_s + i * 16), xf + i * 16);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
@@ -118,7 +125,53 @@ __global__ void __launch_bounds__(G2_WARPS * 32, 1) k_gemm2(const GemmArgs a, co
     pstage = pstage + 1 == G2_STAGES ? 0 : pstage + 1;
     cp_async_wait<G2_STAGES - 1>();      // all but the newest G2_STAGES-1 groups: the stage to consume is in
     __syncwarp();
-    {
+    if constexpr (FMT == LLB_FM_Q6_K) {
+      // 16 scale groups of 16 columns per super-block, one MMA each; code 0..63 as fp16 subnormals
+      // (quarters 2, 3 carry the code shifted left by 4), offset -32 through the 16-column sums
+      const uint8_t *b0 = ring + cstage * 16 * RS + gid * RS, *b1 = b0 + 8 * RS;
+      const float d0 = h2f_bits(*(const unsigned short *)(b0 + 208)), d1 = h2f_bits(*(const unsigned short *)(b1 + 208));
+      const uint4 sw0 = *(const uint4 *)(b0 + 192), sw1 = *(const uint4 *)(b1 + 192);
+      const uint32_t sc0w[4] = {sw0.x ^ 0x80808080u, sw0.y ^ 0x80808080u, sw0.z ^ 0x80808080u, sw0.w ^ 0x80808080u};
+      const uint32_t sc1w[4] = {sw1.x ^ 0x80808080u, sw1.y ^ 0x80808080u, sw1.z ^ 0x80808080u, sw1.w ^ 0x80808080u};
+      const uint8_t *xb6 = xh_s + gid * CS + 8 * j + (size_t)c_c * 512;
+      const float *xs6 = (const float *)xsf_s + (size_t)c_c * 16 * NC + 2 * j;
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) {
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int o = 16 * u + 4 * j;
+          const uint32_t la0 = *(const uint32_t *)(b0 + 64 * hf + o), lb0 = *(const uint32_t *)(b0 + 64 * hf + 32 + o);
+          const uint32_t la1 = *(const uint32_t *)(b1 + 64 * hf + o), lb1 = *(const uint32_t *)(b1 + 64 * hf + 32 + o);
+          const uint32_t hq0 = *(const uint32_t *)(b0 + 128 + 32 * hf + o), hq1 = *(const uint32_t *)(b1 + 128 + 32 * hf + o);
+          const uint32_t h0s4 = hq0 << 4, h0s2 = hq0 << 2, h1s4 = hq1 << 4, h1s2 = hq1 << 2;
+          const uint32_t h0o4 = (hq0 >> 8) << 4, h0o2 = (hq0 >> 8) << 2, h1o4 = (hq1 >> 8) << 4, h1o2 = (hq1 >> 8) << 2;
+#pragma unroll
+          for (int qd = 0; qd < 4; qd++) {
+            const uint32_t l0 = (qd & 1) ? lb0 : la0, l1 = (qd & 1) ? lb1 : la1;
+            const uint32_t nm = qd < 2 ? 0x000f000fu : 0x00f000f0u, hm = qd < 2 ? 0x00300030u : 0x03000300u;
+            const uint32_t e0 = (l0 & nm) | (((qd & 1) ? h0s2 : h0s4) & hm), e1 = (l1 & nm) | (((qd & 1) ? h1s2 : h1s4) & hm);
+            const uint32_t o0 = ((l0 >> 8) & nm) | (((qd & 1) ? h0o2 : h0o4) & hm), o1 = ((l1 >> 8) & nm) | (((qd & 1) ? h1o2 : h1o4) & hm);
+            const float w = qd < 2 ? TWO24 : TWO24 * 0.0625f;
+            const int gi = 8 * hf + 2 * qd + u;
+            // signed scale: (sc ^ 0x80) is sc + 128 as an unsigned byte
+            const float s0 = d0 * (__uint_as_float(__byte_perm(sc0w[gi >> 2], 0x4B000000u, 0x7650u | (gi & 3))) - 8388736.0f);
+            const float s1 = d1 * (__uint_as_float(__byte_perm(sc1w[gi >> 2], 0x4B000000u, 0x7650u | (gi & 3))) - 8388736.0f);
+            const int kl = 128 * hf + 32 * qd + 16 * u;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              const uint2 bx = *(const uint2 *)(xb6 + (size_t)nt * 8 * CS + kl * 2);
+              float p[4];
+              mma16816_z(p, e0, e1, o0, o1, bx.x, bx.y);
+              const float2 xs = *(const float2 *)(xs6 + (size_t)(kl >> 4) * NC + nt * 8);
+              acc[nt][0] += s0 * (p[0] * w - 32.0f * xs.x);
+              acc[nt][1] += s0 * (p[1] * w - 32.0f * xs.y);
+              acc[nt][2] += s1 * (p[2] * w - 32.0f * xs.x);
+              acc[nt][3] += s1 * (p[3] * w - 32.0f * xs.y);
+            }
+          }
+        }
+      }
+    } else {
       const uint8_t *b0 = ring + cstage * 16 * RS + gid * RS, *b1 = b0 + 8 * RS;
       const uint4 h0 = *(const uint4 *)b0, h1 = *(const uint4 *)b1;
       uint32_t scA0, scB0, mnA0, mnB0, scA1, scB1, mnA1, mnB1;
