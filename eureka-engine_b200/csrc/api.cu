@@ -1,5 +1,7 @@
 // api.cu -- the C ABI of include/llb_b200.h: backend primitives and operator entry points.
 #include "../../include/llb_b200.h"
+#include <stdlib.h>
+
 #include "host.cuh"
 
 LlbCtx g_llb;
@@ -27,6 +29,7 @@ int llb_b200_init(int device) {
   CU_OK(cudaGetDeviceProperties(&pr, device));
   if (pr.major < 10) return llb_fail("device %d is sm_%d%d; this library is built for sm_100a only", device, pr.major, pr.minor);
   g_llb.device = device;
+  { const char *e = getenv("LLB_PDL"); g_llb.pdl = !(e && e[0] == '0'); }
   g_llb.sms = pr.multiProcessorCount;
   // a blocking stream: ordered after work a caller queued on the legacy default stream (torch's), so
   // device buffers produced there can be handed in without an explicit synchronisation

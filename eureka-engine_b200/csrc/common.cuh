@@ -111,6 +111,15 @@ __device__ __forceinline__ void xp_store32(const XPlanes &xp, int t, int planes,
   }
 }
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// Every kernel of a pass is launched with the programmatic-serialization attribute: the next kernel's
+// CTAs may become resident while this one still runs, do whatever does not depend on it (a GEMM
+// prefetches its first weight chunks), and park in pdl_wait() until this grid has completed and its
+// writes are visible.  Each kernel calls pdl_trigger() first and pdl_wait() before its first
+// dependent read or any global write, so completion order stays the launch order.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- small PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {

@@ -80,6 +80,19 @@ struct llb_spec {
 };
 
 #define CK(call) do { if ((call)) return -1; } while (0)
+
+// Optional per-op timing of an eager (not captured) pass: an event after every op.
+struct ProfRec { const char *name; cudaEvent_t ev; };
+static std::vector<ProfRec> g_prof;
+static bool g_prof_on = false;
+static void prof_mark(const char *name) {
+  if (!g_prof_on) return;
+  cudaEvent_t e;
+  cudaEventCreate(&e);
+  cudaEventRecord(e, g_llb.stream);
+  g_prof.push_back({name, e});
+}
+#define PK(name, call) do { if ((call)) return -1; prof_mark(name); } while (0)
 #define RING_SPLITS 4   // K-slices the conv ring can hold per row
 static float bits_float(unsigned int u) { float f; memcpy(&f, &u, 4); return f; }
 
@@ -225,20 +238,20 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
 static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
   AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps};
-  CK(site_gemm(m, {{&w.q, &m->b_q, nullptr, nullptr, 0}, {&w.k, &m->b_k, nullptr, nullptr, 0}, {&w.v, &m->b_v, nullptr, nullptr, 0}}, m->xp_d, 0));
-  CK(op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
-  CK(op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
-  CK(site_gemm(m, {{&w.o, &m->b_a, nullptr, nullptr, 0}}, m->xp_qa, 0));
+  PK("gemm qkv", site_gemm(m, {{&w.q, &m->b_q, nullptr, nullptr, 0}, {&w.k, &m->b_k, nullptr, nullptr, 0}, {&w.v, &m->b_v, nullptr, nullptr, 0}}, m->xp_d, 0));
+  PK("qkrope", op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
+  PK("attention", op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
+  PK("gemm attn_out", site_gemm(m, {{&w.o, &m->b_a, nullptr, nullptr, 0}}, m->xp_qa, 0));
   return 0;
 }
 
 // x1 = xin + sum(b_a); h = rms(x1) * post -> planes; x1 + down(silu(gate h) * up h) stays split in b_dn
 static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
-  CK(op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
-  CK(site_gemm(m, {{&w.gate, &m->b_g, nullptr, nullptr, 0}, {&w.up, &m->b_u, nullptr, nullptr, 0}}, m->xp_d, 0));
-  CK(op_silu_xp(s, as_in(m->b_g), as_in(m->b_u), m->f, m->xp_f, rs, m->Tmax));
-  CK(site_gemm(m, {{&w.down, &m->b_dn, nullptr, nullptr, 0}}, m->xp_f, 0));
+  PK("norm post", op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
+  PK("gemm gate|up", site_gemm(m, {{&w.gate, &m->b_g, nullptr, nullptr, 0}, {&w.up, &m->b_u, nullptr, nullptr, 0}}, m->xp_d, 0));
+  PK("silu", op_silu_xp(s, as_in(m->b_g), as_in(m->b_u), m->f, m->xp_f, rs, m->Tmax));
+  PK("gemm down", site_gemm(m, {{&w.down, &m->b_dn, nullptr, nullptr, 0}}, m->xp_f, 0));
   return 0;
 }
 
@@ -247,13 +260,13 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const 
   DeltaShape sh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
   // raw qkv rows go straight into the conv ring slot of their position (host/llb_host.c:1747-1749)
   // (the ring keeps the K-slice partial sums of each row; the conv kernel adds them as it reads)
-  CK(site_gemm(m, {{&w.qkv, &m->b_ring, &m->ctl->verify.slot[0], ring, m->convd, (long long)CONV_RING * m->convd, RING_SPLITS},
+  PK("gemm qkv|z|b|a", site_gemm(m, {{&w.qkv, &m->b_ring, &m->ctl->verify.slot[0], ring, m->convd, (long long)CONV_RING * m->convd, RING_SPLITS},
                    {&w.z, &m->b_z, nullptr, nullptr, 0}, {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}},
                m->xp_d, 0));
-  CK(op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
-  CK(op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
-  CK(op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
-  CK(site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
+  PK("delta conv", op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
+  PK("delta scan", op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
+  PK("delta gnorm", op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
+  PK("gemm ssm_out", site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
   return 0;
 }
 
@@ -261,20 +274,20 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const 
 static int enq_verify(llb_spec *m) {
   cudaStream_t s = g_llb.stream;
   const RowSet *rs = &m->ctl->verify;
-  CK(op_embed(s, m->embd.fmt, m->embd.w, m->d, rs, m->Tmax, m->x));
+  PK("embed", op_embed(s, m->embd.fmt, m->embd.w, m->d, rs, m->Tmax, m->x));
   PartIn none{nullptr, 0, 0};
   for (int il = 0; il < m->L; il++) {
     const LayerW &l = m->layer[il];
     // x += previous layer's FFN output (kept as partial sums), h = rms(x) * attn_norm
-    CK(op_norm_xp(s, il ? m->x1 : m->x, il ? as_in(m->b_dn) : none, l.attn_norm, m->eps, m->d, m->x, m->xp_d, 0, nullptr, rs,
+    PK("norm attn", op_norm_xp(s, il ? m->x1 : m->x, il ? as_in(m->b_dn) : none, l.attn_norm, m->eps, m->d, m->x, m->xp_d, 0, nullptr, rs,
                   m->Tmax, 0));
     if (l.full) CK(enq_attn(m, l.at, m->Kc[il], m->Vc[il], rs));
     else CK(enq_delta(m, l.dn, m->ring[il], m->S[il], rs));
     CK(enq_ffn(m, l.ffn, m->x, m->x1, rs));
   }
-  CK(op_norm_xp(s, m->x1, as_in(m->b_dn), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
-  CK(site_gemm(m, {{&m->head, &m->b_lg, nullptr, nullptr, 0}}, m->xp_d, 0));
-  CK(op_top2_part(s, as_in(m->b_lg), m->V, m->V, m->t2part, rs, m->Tmax));
+  PK("norm out", op_norm_xp(s, m->x1, as_in(m->b_dn), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
+  PK("gemm head", site_gemm(m, {{&m->head, &m->b_lg, nullptr, nullptr, 0}}, m->xp_d, 0));
+  PK("top2", op_top2_part(s, as_in(m->b_lg), m->V, m->V, m->t2part, rs, m->Tmax));
   return 0;
 }
 
@@ -723,6 +736,35 @@ LLB_API int llb_spec_time_gemm(llb_spec *m, int iters, float *us_per_launch, dou
                       (double)m->NC * m->d * 2 + 2.0 * m->Tmax * m->f * 4;
   cudaEventDestroy(a); cudaEventDestroy(b);
   return 0;
+}
+
+// One eager verify pass with an event after every op; writes "name count total_us" lines into buf.
+LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap) {
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  for (int rep = 0; rep < 2; rep++) {      // the second pass is the one reported (warm)
+    for (auto &r : g_prof) cudaEventDestroy(r.ev);
+    g_prof.clear();
+    g_prof_on = true;
+    prof_mark("start");
+    int rc = enq_verify(m);
+    g_prof_on = false;
+    if (rc) return -1;
+    CU_OK(cudaStreamSynchronize(g_llb.stream));
+  }
+  std::vector<std::string> names;
+  std::vector<double> tot;
+  std::vector<int> cnt;
+  for (size_t i = 1; i < g_prof.size(); i++) {
+    float ms = 0;
+    cudaEventElapsedTime(&ms, g_prof[i - 1].ev, g_prof[i].ev);
+    size_t k = 0;
+    for (; k < names.size(); k++) if (names[k] == g_prof[i].name) break;
+    if (k == names.size()) { names.push_back(g_prof[i].name); tot.push_back(0); cnt.push_back(0); }
+    tot[k] += ms * 1000.0; cnt[k] += 1;
+  }
+  int off = 0;
+  for (size_t k = 0; k < names.size() && off < cap - 80; k++) off += snprintf(buf + off, cap - off, "%s\t%d\t%.1f\n", names[k].c_str(), cnt[k], tot[k]);
+  return off;
 }
 
 // kernels per replay of the cycle graph (which = 0) or of the verify pass (which = 2)

@@ -9,8 +9,7 @@ static int g2_max_sb(int fmt, int NC) {
 static int g2_warps(int fmt) { return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS; }
 
 template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs &a, int grid) {
-  k_gemm<FMT, NT><<<grid, GEMM_WARPS * 32, gemm_smem_bytes<FMT>(), s>>>(a);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = llb_launch(k_gemm<FMT, NT>, dim3(grid), dim3(GEMM_WARPS * 32), (size_t)gemm_smem_bytes<FMT>(), s, a);
   if (e != cudaSuccess) return llb_fail("k_gemm launch: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -24,8 +23,7 @@ template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs 
   if (cps > need) cps = need;
   const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
   if (smem > G2_SMEM_MAX) return llb_fail("k_gemm2: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
-  k_gemm2<FMT, NT><<<cps * a.ksplit, G2_WARPS * 32, smem, s>>>(a, cps);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = llb_launch(k_gemm2<FMT, NT>, dim3(cps * a.ksplit), dim3(G2_WARPS * 32), smem, s, a, cps);
   if (e != cudaSuccess) return llb_fail("k_gemm2 launch: %s", cudaGetErrorString(e));
   return 0;
 }

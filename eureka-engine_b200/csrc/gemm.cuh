@@ -290,6 +290,7 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32, 1) k_gemm(const GemmArgs a) {
   uint8_t *ring = smem + (size_t)warp * STAGES * 16 * RS;
   const uint32_t ring_s = smem_u32(ring);
 
+  pdl_trigger();
   TileCursor prod, cons;
   prod.u = gw; cursor_load<FMT>(prod, a, ntiles, nunits);
   cons = prod;
@@ -304,6 +305,7 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32, 1) k_gemm(const GemmArgs a) {
     cp_async_commit();
     pstage = (pstage + 1) % STAGES;
   }
+  pdl_wait();   // the activation planes come from the previous kernel; the weights above do not
   int cstage = 0;
   float acc[NT][4];
 #pragma unroll 1

@@ -90,10 +90,13 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, 1) k_gemm2(const Ge
     }
     cp_async_commit();
   };
+  pdl_trigger();
   plan_tile(p_tile);
-  // weights first: the ring's prologue is in flight while the activation slice is staged
+  // weights first: the ring's prologue is in flight while the producer of the activations still
+  // runs (weights depend on no kernel), and while the activation slice is staged
 #pragma unroll 1
   for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
+  pdl_wait();
   {
     const int per_col = nsl * 32;   // 16-byte pieces of one column's slice
     for (int i = threadIdx.x; i < NC * per_col; i += blockDim.x) {

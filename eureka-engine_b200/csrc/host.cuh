@@ -11,6 +11,7 @@
 struct LlbCtx {
   int device = -1;
   int sms = 0;
+  int pdl = 1;     // programmatic dependent launch on every kernel of a pass (LLB_PDL=0 turns it off)
   cudaStream_t stream = nullptr;
   char err[512] = {0};
 };
@@ -28,6 +29,19 @@ inline int llb_fail(const char *fmt, ...) {
     cudaError_t e_ = (call);                                                                     \
     if (e_ != cudaSuccess) return llb_fail("%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
   } while (0)
+
+// Launch with (optionally) the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t llb_launch(void (*k)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = g_llb.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, k, KArgs(args)...);
+}
 
 // gemm.cu
 int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms);

@@ -3,12 +3,16 @@
 
 // ---- activations -> fp16 planes ----------------------------------------------------------------
 __global__ void k_xp_from_f32(const float *__restrict__ x, int K, int planes, XPlanes xp) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y, lane = threadIdx.x & 31;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31;
   if (c0 >= K) return;
   xp_store32(xp, t, planes, c0, x[(size_t)t * K + c0 + lane], lane);
 }
 __global__ void k_xp_from_bf16(const unsigned short *__restrict__ x, int K, XPlanes xp) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y, lane = threadIdx.x & 31;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31;
   if (c0 >= K) return;
@@ -18,14 +22,14 @@ __global__ void k_xp_from_bf16(const unsigned short *__restrict__ x, int K, XPla
 int ops_xp_from_f32(cudaStream_t s, const float *x, int T, int planes, XPlanes xp) {
   if (xp.K % 32) return llb_fail("xp: K %d", xp.K);
   if (T * planes > xp.NC) return llb_fail("xp: %d rows x %d planes do not fit %d columns", T, planes, xp.NC);
-  k_xp_from_f32<<<dim3((xp.K + 255) / 256, T), 256, 0, s>>>(x, xp.K, planes, xp);
+  CU_OK(llb_launch(k_xp_from_f32, dim3((xp.K + 255) / 256, T), dim3(256), (size_t)(0), s, x, xp.K, planes, xp));
   CU_OK(cudaGetLastError());
   return 0;
 }
 int ops_xp_from_bf16(cudaStream_t s, const void *x, int T, XPlanes xp) {
   if (xp.K % 32) return llb_fail("xp: K %d", xp.K);
   if (T > xp.NC) return llb_fail("xp: %d rows do not fit %d columns", T, xp.NC);
-  k_xp_from_bf16<<<dim3((xp.K + 255) / 256, T), 256, 0, s>>>((const unsigned short *)x, xp.K, xp);
+  CU_OK(llb_launch(k_xp_from_bf16, dim3((xp.K + 255) / 256, T), dim3(256), (size_t)(0), s, (const unsigned short *)x, xp.K, xp));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -33,6 +37,8 @@ int ops_xp_from_bf16(cudaStream_t s, const void *x, int T, XPlanes xp) {
 // ---- bit-exact row dequantisation (embedding rows; the dequant parity check) -------------------
 __global__ void k_dequant_rows(int fmt, const uint8_t *__restrict__ W, int cols, const int *__restrict__ row_ids,
                                float *__restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.y;
   const int row = row_ids ? row_ids[r] : r;
   const uint8_t *src = W + (size_t)row * dev_row_bytes(fmt, cols);
@@ -48,8 +54,8 @@ int ops_dequant_rows(cudaStream_t s, int fmt, const uint8_t *W, int rows, int co
   // gridDim.y is limited to 65535 rows per launch
   for (int r0 = 0; r0 < nrows; r0 += 65535) {
     int n = nrows - r0 < 65535 ? nrows - r0 : 65535;
-    k_dequant_rows<<<dim3(gx, n), 256, 0, s>>>(fmt, row_ids ? W : W + (size_t)r0 * dev_row_bytes(fmt, cols), cols,
-                                              row_ids ? row_ids + r0 : nullptr, out + (size_t)r0 * cols);
+    CU_OK(llb_launch(k_dequant_rows, dim3(gx, n), dim3(256), (size_t)(0), s, fmt, row_ids ? W : W + (size_t)r0 * dev_row_bytes(fmt, cols), cols,
+                                              row_ids ? row_ids + r0 : nullptr, out + (size_t)r0 * cols));
     CU_OK(cudaGetLastError());
   }
   return 0;
@@ -57,6 +63,8 @@ int ops_dequant_rows(cudaStream_t s, int fmt, const uint8_t *W, int rows, int co
 
 // ---- Q6_K: 210-byte stored super-blocks -> 224-byte device super-blocks ------------------------
 __global__ void k_repack_q6k(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t nblocks) {
+  pdl_trigger();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t n = nblocks * 224;
   for (; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -69,13 +77,15 @@ int ops_repack_q6k(cudaStream_t s, const uint8_t *src210, uint8_t *dst224, size_
   if (!nblocks) return 0;
   size_t n = nblocks * 224;
   int grid = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  k_repack_q6k<<<grid, 256, 0, s>>>(src210, dst224, nblocks);
+  CU_OK(llb_launch(k_repack_q6k, dim3(grid), dim3(256), (size_t)(0), s, src210, dst224, nblocks));
   CU_OK(cudaGetLastError());
   return 0;
 }
 
 // ---- fixed-order sum of K-slice partials --------------------------------------------------------
 __global__ void k_sum_parts(const float *__restrict__ parts, int nsplit, long long stride, int n, float *__restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float v = parts[i];
@@ -83,7 +93,7 @@ __global__ void k_sum_parts(const float *__restrict__ parts, int nsplit, long lo
   out[i] = v;
 }
 int ops_sum_parts(cudaStream_t s, const float *parts, int nsplit, long long split_stride, int n, float *out) {
-  k_sum_parts<<<(n + 255) / 256, 256, 0, s>>>(parts, nsplit, split_stride, n, out);
+  CU_OK(llb_launch(k_sum_parts, dim3((n + 255) / 256), dim3(256), (size_t)(0), s, parts, nsplit, split_stride, n, out));
   CU_OK(cudaGetLastError());
   return 0;
 }

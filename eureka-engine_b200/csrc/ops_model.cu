@@ -30,13 +30,15 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 
 // ---- embedding rows (llb_embedk, tools/payload-kpair.patch:526) ---------------------------------
 __global__ void k_embed(int fmt, const uint8_t *__restrict__ W, int d, const RowSet *__restrict__ rs, float *__restrict__ x) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y;
   if (t >= rs->n) return;
   const uint8_t *row = W + (size_t)rs->tok[t] * dev_row_bytes(fmt, d);
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < d; c += gridDim.x * blockDim.x) x[(size_t)t * d + c] = deq_elem(fmt, row, d, c);
 }
 int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs, int Tmax, float *x) {
-  k_embed<<<dim3((d + 255) / 256, Tmax), 256, 0, s>>>(fmt, W, d, rs, x);
+  CU_OK(llb_launch(k_embed, dim3((d + 255) / 256, Tmax), dim3(256), (size_t)(0), s, fmt, W, d, rs, x));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -50,6 +52,8 @@ int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs,
 __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
                                                           float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
                                                           const RowSet *__restrict__ rs, int zero_if_pos0) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int t = blockIdx.x;
   if (t >= rs->n) return;
@@ -63,13 +67,19 @@ __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restric
     v[i] = (c < d && xin && !zero) ? xin[row + c] : 0.0f;
   }
   if (add.p && !zero) {
-    for (int k = 0; k < add.ns; k++) {
+    // two slices per trip: 2 x NORM_MAXI independent loads in flight
+    for (int k = 0; k < add.ns; k += 2) {
       const float *pk = add.p + (size_t)k * add.stride + row;
+      const bool two = k + 1 < add.ns;
+      float l0[NORM_MAXI], l1[NORM_MAXI];
 #pragma unroll
       for (int i = 0; i < NORM_MAXI; i++) {
         const int c = threadIdx.x + i * NORM_THREADS;
-        if (c < d) v[i] += pk[c];
+        l0[i] = c < d ? pk[c] : 0.0f;
+        l1[i] = (c < d && two) ? pk[add.stride + c] : 0.0f;
       }
+#pragma unroll
+      for (int i = 0; i < NORM_MAXI; i++) { v[i] += l0[i]; v[i] += l1[i]; }
     }
   }
   float ss = 0.0f;
@@ -97,13 +107,15 @@ __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restric
 int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
                int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0) {
   if (d % 32 || d > NORM_THREADS * NORM_MAXI) return llb_fail("norm: d %d", d);
-  k_norm_xp<<<Tmax, NORM_THREADS, 0, s>>>(xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0);
+  CU_OK(llb_launch(k_norm_xp, dim3(Tmax), dim3(NORM_THREADS), (size_t)(0), s, xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0));
   CU_OK(cudaGetLastError());
   return 0;
 }
 
 // ---- silu(gate) * up -> planes (llb_t_siluq, tools/payload-spec2.patch:114-124) -----------------
 __global__ void k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y, lane = threadIdx.x & 31;
   if (t >= rs->n) return;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31;
@@ -113,7 +125,7 @@ __global__ void k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *_
 }
 int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax) {
   if (f % 32) return llb_fail("silu: f %d", f);
-  k_silu_xp<<<dim3((f + 255) / 256, Tmax), 256, 0, s>>>(g, u, f, xp, rs);
+  CU_OK(llb_launch(k_silu_xp, dim3((f + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -124,6 +136,8 @@ int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowS
 __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__ qn_w, const float *__restrict__ kn_w,
                          const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, float *__restrict__ Kc,
                          float *__restrict__ Vc, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float hv[];
   __shared__ float red[32];
   const int t = blockIdx.y, b = blockIdx.x, i = threadIdx.x, hd = sh.hd;
@@ -165,7 +179,7 @@ __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__
 }
 int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
               AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax) {
-  k_qkrope<<<dim3(sh.H + 2 * sh.KV, Tmax), sh.hd, (size_t)sh.hd * 4, s>>>(q, k, v, qn_w, kn_w, invfreq, sh, qout, Kc, Vc, rs);
+  CU_OK(llb_launch(k_qkrope, dim3(sh.H + 2 * sh.KV, Tmax), dim3(sh.hd), (size_t)((size_t)sh.hd * 4), s, q, k, v, qn_w, kn_w, invfreq, sh, qout, Kc, Vc, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -181,6 +195,8 @@ template <int HD, int QW>
 __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, const float *__restrict__ Kc,
                                                    const float *__restrict__ Vc, AttnShape sh, int Tmax, float *__restrict__ pm,
                                                    float *__restrict__ pl, float *__restrict__ po, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) float sm[];
   constexpr int KS = HD + 4, DPL = HD / 32;
   const int G = sh.H / sh.KV, NQ = G * Tmax, nsplit = gridDim.y;
@@ -281,6 +297,8 @@ __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, 
 // (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
 __global__ void k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
                             AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float wsm[128];
   __shared__ float red[32];
   const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = sh.hd, lane = threadIdx.x & 31;
@@ -312,7 +330,7 @@ __global__ void k_attn_comb(const float *__restrict__ pm, const float *__restric
 
 template <int HD> static int attn_launch(cudaStream_t s, int QW, dim3 grid, size_t smem, const float *q, const float *Kc,
                                          const float *Vc, AttnShape sh, int Tmax, float *pm, float *pl, float *po, const RowSet *rs) {
-#define ATT(Q) case Q: k_attn_part<HD, Q><<<grid, 256, smem, s>>>(q, Kc, Vc, sh, Tmax, pm, pl, po, rs); break;
+#define ATT(Q) case Q: CU_OK(llb_launch(k_attn_part<HD, Q>, dim3(grid), dim3(256), (size_t)(smem), s, q, Kc, Vc, sh, Tmax, pm, pl, po, rs)); break;
   switch (QW) { ATT(1) ATT(2) ATT(3) ATT(4) ATT(6) default: return llb_fail("attention: %d queries per warp", QW); }
 #undef ATT
   CU_OK(cudaGetLastError());
@@ -332,7 +350,7 @@ int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *V
   else if (sh.hd == 256) rc = attn_launch<256>(s, QW, grid, smem, q, Kc, Vc, sh, Tmax, pm, pl, po, rs);
   else return llb_fail("attention: head_dim %d", sh.hd);
   if (rc) return rc;
-  k_attn_comb<<<dim3(sh.H, Tmax), sh.hd, 0, s>>>(pm, pl, po, qg, sh, nsplit, Tmax, xp, rs);
+  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(sh.hd), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -356,6 +374,8 @@ int ops_model_setup(void) {
 __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn bp, PartIn ap,
                              const float *__restrict__ dt, const float *__restrict__ sa, DeltaShape sh, float *__restrict__ y,
                              float *__restrict__ beta, float *__restrict__ decay, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y;
   if (t >= rs->n) return;
   if (blockIdx.x == gridDim.x - 1) {
@@ -381,7 +401,7 @@ __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn b
 int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax) {
   if (sh.KC > CONV_RING / 2) return llb_fail("conv kernel %d", sh.KC);
-  k_delta_conv<<<dim3((sh.convd + 255) / 256 + 1, Tmax), 256, 0, s>>>(ring, cw, bp, ap, dt, sa, sh, y, beta, decay, rs);
+  CU_OK(llb_launch(k_delta_conv, dim3((sh.convd + 255) / 256 + 1, Tmax), dim3(256), (size_t)(0), s, ring, cw, bp, ap, dt, sa, sh, y, beta, decay, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -396,6 +416,8 @@ __global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const
                                                     const float *__restrict__ y, const float *__restrict__ beta,
                                                     const float *__restrict__ decay, DeltaShape sh, float *__restrict__ o,
                                                     const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128], vs[SPEC_MAXT][32], db[SPEC_MAXT][2];
   __shared__ float red[2 * SPEC_MAXT][4];
   const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs->n, lane = tid & 31, wp = tid >> 5;
@@ -462,7 +484,7 @@ int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, 
                   DeltaShape sh, float *o, const RowSet *rs, int Tmax) {
   (void)Tmax;
   if (sh.SZ != 128) return llb_fail("DeltaNet state size %d (only 128, as host/llb_host.c:1608)", sh.SZ);
-  k_delta_scan<<<dim3(sh.TR, 4), 128, 0, s>>>(S, ctl, y, beta, decay, sh, o, rs);
+  CU_OK(llb_launch(k_delta_scan, dim3(sh.TR, 4), dim3(128), (size_t)(0), s, S, ctl, y, beta, decay, sh, o, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -471,6 +493,8 @@ int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, 
 // (llb_t_grn, tools/payload-spec2.patch:413-447; tools/qwen35_engine.c:648-654)
 __global__ void __launch_bounds__(128) k_gnorm_xp(const float *__restrict__ o, PartIn z, const float *__restrict__ nw,
                                                   DeltaShape sh, XPlanes xp, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int hh = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
   if (t >= rs->n) return;
@@ -481,7 +505,7 @@ __global__ void __launch_bounds__(128) k_gnorm_xp(const float *__restrict__ o, P
   xp_store32(xp, t, 2, hh * 128 + (i & ~31), v * r * nw[i] * silu_f(part_get(z, idx)), i & 31);
 }
 int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs, int Tmax) {
-  k_gnorm_xp<<<dim3(sh.TR, Tmax), 128, 0, s>>>(o, z, nw, sh, xp, rs);
+  CU_OK(llb_launch(k_gnorm_xp, dim3(sh.TR, Tmax), dim3(128), (size_t)(0), s, o, z, nw, sh, xp, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -507,6 +531,8 @@ __device__ __forceinline__ Top2 t2_warp(Top2 a) {
 }
 __global__ void __launch_bounds__(256) k_top2_part(PartIn logits, int V, long long row_stride,
                                                    float *__restrict__ part, const RowSet *__restrict__ rs) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ Top2 sh[8];
   const int t = blockIdx.y;
   if (t >= rs->n) return;
@@ -527,7 +553,7 @@ __global__ void __launch_bounds__(256) k_top2_part(PartIn logits, int V, long lo
   }
 }
 int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax) {
-  k_top2_part<<<dim3(TOP2_NB, Tmax), 256, 0, s>>>(logits, V, row_stride, part, rs);
+  CU_OK(llb_launch(k_top2_part, dim3(TOP2_NB, Tmax), dim3(256), (size_t)(0), s, logits, V, row_stride, part, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -548,6 +574,8 @@ __device__ __forceinline__ Top2 t2_final(const float *part, int t, int lane) {
 // Here the whole decision runs on the device and also prepares the next cycle: new p0, ring slot,
 // committed token, and the drafter's catch-up rows (host/llb_host.c:1815).
 __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ ctl, SpecResult *__restrict__ ring, int ring_n) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ Top2 rows[SPEC_MAXT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = ctl->verify.n;
@@ -595,7 +623,7 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
   ctl->seq += 1;
 }
 int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax) {
-  k_accept<<<1, 32 * Tmax, 0, s>>>(part, ctl, ring, ring_n);
+  CU_OK(llb_launch(k_accept, dim3(1), dim3(32 * Tmax), (size_t)(0), s, part, ctl, ring, ring_n));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -605,6 +633,8 @@ int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring,
 // is the drafter's own normed hidden of that last row (host/llb_host.c:1824-1827).
 __global__ void k_draft_pick(const float *__restrict__ part, const int *__restrict__ ids, SpecCtl *__restrict__ ctl,
                              int from_chain, int j, const float *__restrict__ mt_hn, float *__restrict__ chain_h, int d) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int s_tok;
   const RowSet *rs = from_chain ? &ctl->chain : &ctl->catchup;
   const int last = rs->n - 1;
@@ -626,7 +656,7 @@ __global__ void k_draft_pick(const float *__restrict__ part, const int *__restri
 }
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
                   float *chain_h, int d) {
-  k_draft_pick<<<1, 256, 0, s>>>(part, ids, ctl, from_chain, j, mt_hn, chain_h, d);
+  CU_OK(llb_launch(k_draft_pick, dim3(1), dim3(256), (size_t)(0), s, part, ids, ctl, from_chain, j, mt_hn, chain_h, d));
   CU_OK(cudaGetLastError());
   return 0;
 }

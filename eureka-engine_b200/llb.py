@@ -61,6 +61,7 @@ def lib() -> C.CDLL:
             "llb_spec_read_state": (i32, [vp, i32, i32, i32, vp, sz]), "llb_spec_read_logits": (i32, [vp, i32, vp]),
             "llb_spec_run_cycles": (i32, [vp, i32, vp, i32]), "llb_spec_time_verify": (i32, [vp, i32, vp]),
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
+            "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
         }
         for name, (res, args) in sig.items():
             f = getattr(L, name)
@@ -197,6 +198,16 @@ class SpecEngine:
         us, nb = C.c_float(0), C.c_double(0)
         check(self.L.llb_spec_time_gemm(self.h, iters, C.addressof(us), C.addressof(nb)), "llb_spec_time_gemm")
         return us.value, nb.value
+
+    def profile_verify(self):
+        """Per-op device time of one eager verify pass: {name: (count, total_us)}."""
+        buf = C.create_string_buffer(1 << 16)
+        check(self.L.llb_spec_profile_verify(self.h, buf, len(buf)), "llb_spec_profile_verify")
+        out = {}
+        for line in buf.value.decode().splitlines():
+            n, c, t = line.split("\t")
+            out[n] = (int(c), float(t))
+        return out
 
     def graph_nodes(self, which: int = 0) -> int:
         return self.L.llb_spec_graph_nodes(self.h, which)

@@ -102,6 +102,8 @@ LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap);
 LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass);
 LLB_API int llb_spec_time_gemm(llb_spec *m, int iters, float *us_per_launch, double *bytes_per_launch);
 LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which);
+/* one eager verify pass with an event after every op: "name\tcount\ttotal_us" lines */
+LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap);
 /* out[19] = cycles, rows, served, drafted[8], accepted[8] by draft position (host/llb_host.c:1513-1523) */
 LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out);
 LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n);
