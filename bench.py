@@ -236,11 +236,7 @@ def main():
     stats = eng.stats()
     launches = eng.graph_nodes(0)
 
-    if world > 1:
-        t = torch.tensor([ms, float(toks), e2e_s, float(n_e2e)], device=f"cuda:{local}", dtype=torch.float64)
-        tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        ms, toks, e2e_s, n_e2e = tmax[0].item(), tsum[1].item(), tmax[2].item(), tsum[3].item()
+    (ms, e2e_s), (toks, n_e2e) = pkg.dp.aggregate([ms, e2e_s], [float(toks), float(n_e2e)], device=f"cuda:{local}")
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

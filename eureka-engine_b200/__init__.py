@@ -6,4 +6,4 @@
 
 The directory name is not a Python identifier; load it with `__graft_entry__.load_package()`.
 """
-from . import llb, packs  # noqa: F401
+from . import dp, llb, packs  # noqa: F401

@@ -1,0 +1,131 @@
+"""CPU tests of the host-side logic: the C ABI's symbol table, pack and container writers, stream
+sharding (2 gloo ranks).  No compute call is made: there is no GPU here."""
+import ctypes
+import os
+import re
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    """Every LLB_API function of include/llb_b200.h is exported by the built library."""
+    hdr = open(os.path.join(ROOT, "include", "llb_b200.h")).read()
+    names = re.findall(r"LLB_API\s+[A-Za-z_ \*]+?\b(llb_[a-z0-9_]+)\s*\(", hdr)
+    assert len(names) >= 30
+    if not os.path.exists(pkg.llb.SO_PATH):
+        pkg.llb.build()
+    lib = ctypes.CDLL(pkg.llb.SO_PATH)
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_calls_fail_loudly_without_a_device(pkg):
+    """No CPU fallback: initialisation reports the missing device, and calls before it say so."""
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    L = pkg.llb.lib()
+    assert L.llb_alloc_zero(16) == 0
+    assert b"llb_b200_init" in L.llb_b200_last_error()
+    with pytest.raises(pkg.llb.LlbError):
+        pkg.llb.init(0)
+
+
+def test_index_text_round_trip(packs, tmp_path):
+    cfg = packs.cfg_tiny(quant="q4_k_m", n_layers=8, tied_head=False)
+    pack = packs.build_pack(cfg)
+    pack.write(str(tmp_path))
+    back = packs.Pack.read(str(tmp_path), cfg)
+    assert [(e.name, e.off, e.nbytes, e.rows, e.cols, e.ty) for e in back.entries] == \
+           [(e.name, e.off, e.nbytes, e.rows, e.cols, e.ty) for e in pack.entries]
+    assert torch.equal(back.data, pack.data)
+    for e in pack.entries:
+        assert e.off % 64 == 0                                   # tools/q8_pack.py:32
+        want = e.rows * (e.cols * 4 if e.ty == "F32" else packs.row_bytes(e.ty, e.cols))
+        assert e.nbytes == want
+    types = {e.name.split(".")[-2]: e.ty for e in pack.entries if e.name.startswith("blk.0.") and e.rows > 1}
+    assert types["ffn_down"] == "Q6_K" and types["ffn_gate"] == "Q4_K"     # layer 0 is in the "more bits" eighth
+
+
+def test_tied_head_aliases_the_embedding(packs):
+    pack = packs.build_pack(packs.cfg_tiny())
+    a, b = pack.by_name["token_embd.weight"], pack.by_name["output.weight"]
+    assert (a.off, a.nbytes, a.ty) == (b.off, b.nbytes, b.ty)
+
+
+def test_truncated_pack_keeps_the_draws(packs):
+    """--layers L must see the same bytes for the layers it keeps (the generator is advanced in full pack order)."""
+    cfg = packs.cfg_tiny(n_layers=8)
+    full, cut = packs.build_pack(cfg), packs.build_pack(cfg, layers=4)
+    for e in cut.entries:
+        assert torch.equal(cut.raw(e.name), full.raw(e.name)), e.name
+
+
+def test_aux1_layout(packs):
+    """AUX1: 16-byte header, 72-byte named entries, 256-aligned payloads (tools/auxpack/auxpack.py:10-22)."""
+    pack = packs.build_pack(packs.cfg_tiny())
+    ent = packs.build_mtp(pack)
+    img = packs.aux1_bytes(ent)
+    assert img[:4] == b"AUX1" and struct.unpack_from("<III", img, 4) == (1, 17, 0)
+    for i, (name, ty, shape, raw) in enumerate(ent):
+        rec = struct.unpack_from("<32sII4IQQ", img, 16 + 72 * i)
+        assert rec[0].rstrip(b"\0").decode() == name and rec[1] == packs.AUX_DT[ty]
+        off, nb = rec[-2], rec[-1]
+        assert off % 256 == 0 and nb == raw.numel()
+        assert img[off:off + nb] == raw.numpy().tobytes()
+    assert [e[0] for e in ent] == packs.MTP_ORDER
+    d = pack.cfg.d_model
+    eh = packs.dequant(ent[2][1], ent[2][3], d, 2 * d)
+    assert float(eh[:, :d].abs().max()) == 0.0                    # eh_proj = [0 | I] up to quantisation
+    assert float((eh[:, d:] - torch.eye(d)).abs().max()) < 0.02
+
+
+def test_plane_permutation_is_an_involution():
+    perm = lambda c: (c & ~7) | ((c & 4) | ((c & 1) << 1) | ((c & 2) >> 1))
+    assert [perm(c) for c in range(8)] == [0, 2, 1, 3, 4, 6, 5, 7]
+    assert all(perm(perm(c)) == c for c in range(64))
+
+
+def test_stream_sharding(pkg):
+    dp = pkg.dp
+    for n, w in ((8, 1), (8, 2), (32, 8), (5, 4)):
+        got = sorted(s for r in range(w) for s in dp.shard_streams(n, r, w))
+        assert got == list(range(n))
+        sizes = [len(dp.shard_streams(n, r, w)) for r in range(w)]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        dp.shard_streams(4, 2, 2)
+    assert dp.aggregate([1.0], [2.0]) == ([1.0], [2.0])           # no process group: one rank
+
+
+def _gloo_rank(rank, world, port, q):
+    import sys
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    import __graft_entry__ as graft
+    dp = graft.load_package().dp
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    t, c = dp.aggregate([10.0 + rank, 5.0 - rank], [100.0 * (rank + 1), float(len(dp.shard_streams(7, rank, world)))])
+    q.put((rank, t, c))
+    dist.destroy_process_group()
+
+
+def test_aggregate_two_gloo_ranks():
+    """The N > 1 bench path: MAX of the ranks' times, SUM of what they emitted."""
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_gloo_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    out = sorted(q.get(timeout=120) for _ in ps)
+    for p in ps:
+        p.join(60)
+    for rank, t, c in out:
+        assert t == [11.0, 5.0] and c == [300.0, 7.0]

@@ -1,0 +1,118 @@
+"""CPU tests: the oracle (oracle/q35_oracle.c) against the golden vectors produced from the reference
+itself (tests/golden/make_golden.py), and its own invariants.  No GPU."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = os.path.join(HERE, "golden")
+
+
+@pytest.fixture(scope="module")
+def greedy_gold():
+    return json.load(open(os.path.join(GOLD, "reference_greedy.json")))
+
+
+@pytest.mark.parametrize("ty", ["Q8_0", "Q4_K", "Q5_K", "Q6_K"])
+def test_dequant_matches_reference_vectors(packs, oracle, ty):
+    """Bit-exact against the reference's numpy decoders (tools/q4k.py, q5k.py, q6k.py) on random blocks."""
+    z = np.load(os.path.join(GOLD, "dequant_vectors.npz"))
+    raw, want = z[f"{ty}_raw"], z[f"{ty}_deq"]
+    rows, cols = want.shape
+    got = oracle.Oracle.deq_rows(packs.FMT[ty], raw, rows, cols)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # the torch decoder used to check GPU-written packs agrees too
+    t = packs.dequant(ty, torch.from_numpy(raw.copy()), rows, cols).numpy()
+    assert np.array_equal(t.view(np.uint32), want.view(np.uint32))
+    # the dot is the serial sum of dequantised weight times x (tools/qwen35_engine.c:74-216)
+    x = np.random.default_rng(0).standard_normal(cols).astype(np.float32)
+    y = oracle.Oracle.gemv(packs.FMT[ty], raw, rows, cols, x)
+    for r in range(rows):
+        acc = np.float32(0)
+        for c in range(cols):
+            acc = np.float32(acc + np.float32(want[r, c] * x[c]))
+        assert y[r] == acc
+
+
+def _case(packs, gold, name):
+    g = gold[name]
+    cfg = packs.ModelCfg(**{k: g["cfg"][k] for k in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "d_ff", "vocab_size",
+                                                     "ssm_heads", "ssm_groups", "tied_head", "quant", "seed")})
+    pack = packs.build_pack(cfg)
+    assert hashlib.sha256(pack.data.numpy().tobytes()).hexdigest() == g["pack_sha256"], "the pack writer no longer reproduces the golden pack"
+    return cfg, pack, np.array(g["prompt"], np.int32), np.array(g["ids"], np.int32), np.array(g["top2"], np.uint32)
+
+
+@pytest.mark.parametrize("name", ["tiny_q8_0", "tiny_q4_k_m", "tiny_q4_k_s"])
+def test_greedy_matches_reference_engine(packs, oracle, greedy_gold, name):
+    """Token ids and top-2 logit bits equal those of the reference CPU engine built from its own sources."""
+    cfg, pack, prompt, ids, top2 = _case(packs, greedy_gold, name)
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=len(prompt) + len(ids) + 8)
+    got_ids, got_top2 = orc.greedy(prompt, len(ids))
+    assert np.array_equal(got_ids, ids)
+    assert np.array_equal(got_top2, top2)
+
+
+def test_c0_shape_matches_reference_engine(packs, oracle, greedy_gold):
+    """The 0.8B-shape Q8_0 configuration: first generated tokens against the reference engine's run."""
+    cfg, pack, prompt, ids, top2 = _case(packs, greedy_gold, "c0_0.8b_q8_0")
+    n = 6
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=len(prompt) + n + 8)
+    got_ids, got_top2 = orc.greedy(prompt, n)
+    assert np.array_equal(got_ids, ids[:n])
+    assert np.array_equal(got_top2, top2[:n])
+
+
+@pytest.mark.parametrize("k", [1, 3, 7])
+def test_spec_cycle_is_lossless(packs, oracle, greedy_gold, k):
+    """Greedy speculative decoding emits exactly the plain greedy stream (host/llb_sampler.h:20-26), for
+    both drafter containers, and its statistics add up."""
+    cfg, pack, prompt, ids, top2 = _case(packs, greedy_gold, "tiny_q8_0")
+    mtp = packs.build_mtp(pack)
+    for img in (packs.aux1_bytes(mtp),):
+        orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=128)
+        orc.mtp_load(img)
+        sids, stop2, st = orc.spec_greedy(prompt, len(ids), k)
+        assert np.array_equal(sids, ids) and np.array_equal(stop2, top2)
+        assert st.served >= len(ids) and st.rows == st.cycles * (k + 1)
+        acc = list(st.accepted)[1:k + 1]
+        assert all(a >= b for a, b in zip(acc, acc[1:]))          # position j+1 is accepted only if j was
+        assert st.served == st.cycles + sum(acc)
+
+
+def test_mtp1_container_rejects_wrong_formats(packs, oracle, greedy_gold):
+    """The positional container fixes Q4_K / Q6_K formats (host/llb_host.c:1574-1577): a Q8_0 drafter in it
+    fails the size check instead of being misread."""
+    cfg, pack, prompt, ids, top2 = _case(packs, greedy_gold, "tiny_q8_0")
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=64)
+    with pytest.raises(RuntimeError):
+        orc.mtp_load(packs.mtp1_bytes(packs.build_mtp(pack)))
+    cfg2, pack2, *_ = _case(packs, greedy_gold, "tiny_q4_k_m")
+    # Q4_K_M: attention matrices are Q4_K in this synthetic map, the container wants Q6_K: still refused
+    orc2 = oracle.Oracle(pack2.index_text(), pack2.data.numpy(), cap=64)
+    with pytest.raises(RuntimeError):
+        orc2.mtp_load(packs.mtp1_bytes(packs.build_mtp(pack2)))
+
+
+def test_oracle_equals_reference_build_when_present(packs, oracle, greedy_gold, tmp_path):
+    """Where the reference build exists (this container), step both and compare logits and state bits."""
+    if not os.path.exists(oracle.REF_SO):
+        pytest.skip("oracle/_ref is not built here")
+    import subprocess
+    import sys
+    cfg, pack, prompt, ids, top2 = _case(packs, greedy_gold, "tiny_q4_k_m")
+    pack.write(str(tmp_path))
+    code = ("import sys, json; sys.path.insert(0, %r); from oracle.bindings import RefTwin, Oracle; import numpy as np;"
+            "r = RefTwin(%r, cap=64); idx = open(%r).read(); pk = np.fromfile(%r, dtype=np.uint8); o = Oracle(idx, pk, cap=64); ok = True\n"
+            "for t, tok in enumerate(%r):\n"
+            "    r.forward(tok, t); o.forward(tok, t)\n"
+            "    ok &= bool((r.logits().view(np.uint32) == o.logits().view(np.uint32)).all())\n"
+            "    ok &= bool((r.state_S(0).view(np.uint32) == o.state_S(0).view(np.uint32)).all())\n"
+            "print(json.dumps(ok))"
+            % (os.path.dirname(HERE), str(tmp_path), str(tmp_path / "index.tsv"), str(tmp_path / "pack.bin"), [int(v) for v in prompt]))
+    out = subprocess.run([sys.executable, "-c", code], check=True, capture_output=True, text=True).stdout
+    assert json.loads(out.strip().splitlines()[-1]) is True
