@@ -5,7 +5,7 @@
  * host/llb_backend.h:7-9) and host pointers.  Every call returns 0 / a handle on success and
  * -1 / 0 on failure with llb_b200_last_error() holding the reason; nothing falls back to the CPU.
  * All work is queued on one in-order stream per process (the reference's null-stream contract,
- * host/llb_backend.h:15-18): each call sees the effects of every earlier one.
+ * host/llb_backend.h:14-18): each call sees the effects of every earlier one.
  *
  * Three layers, bottom up:
  *   1. backend primitives      -- what host/llb_backend.h:7-34 asks of a backend
@@ -37,12 +37,12 @@ enum { LLB_F32 = 0, LLB_Q8_0 = 1, LLB_Q4_K = 3, LLB_Q6_K = 4, LLB_Q5_K = 9 };
 LLB_API int llb_b200_init(int device);              /* binds the process to a GPU; creates the stream     */
 LLB_API const char *llb_b200_last_error(void);
 LLB_API int llb_b200_sm_count(void);
-LLB_API llb_dptr llb_alloc_zero(size_t bytes);      /* host/llb_backend.h:27   (0 on failure)            */
+LLB_API llb_dptr llb_alloc_zero(size_t bytes);      /* host/llb_backend.h:25-26, host/llb_backend_cuda.h:186-191 (0 on failure) */
 LLB_API int llb_free(llb_dptr p);
-LLB_API int llb_zero(llb_dptr p, size_t bytes);     /* host/llb_backend.h:29                              */
-LLB_API int llb_copy(llb_dptr d, llb_dptr s, size_t bytes);        /* host/llb_backend.h:30 (device to device, in order) */
-LLB_API int llb_write(llb_dptr d, const void *h, size_t bytes);    /* host/llb_backend.h:31 */
-LLB_API int llb_read(void *h, llb_dptr p, size_t bytes);           /* host/llb_backend.h:32 (synchronises) */
+LLB_API int llb_zero(llb_dptr p, size_t bytes);     /* host/llb_backend.h:27, host/llb_backend_cuda.h:193-196 */
+LLB_API int llb_copy(llb_dptr d, llb_dptr s, size_t bytes);        /* host/llb_backend.h:28, host/llb_backend_cuda.h:204-207 (device to device, in order) */
+LLB_API int llb_write(llb_dptr d, const void *h, size_t bytes);    /* host/llb_backend.h:29, host/llb_backend_cuda.h:210-213 */
+LLB_API int llb_read(void *h, llb_dptr p, size_t bytes);           /* host/llb_backend.h:30-31, host/llb_backend_cuda.h:198-201 (synchronises) */
 LLB_API int llb_sync(void);                                        /* host/llb_backend_cuda.h:216-219 */
 LLB_API llb_dptr llb_stream(void);                  /* the cudaStream_t all calls queue on, for event timing */
 
@@ -59,7 +59,7 @@ LLB_API int llb_b200_dequant(int fmt, int rows, int cols, llb_dptr w, llb_dptr r
 
 /* Activation planes of a T-row GEMM input (replaces the two-plane int8 quantiser llb_t_q8x2,
  * tools/payload-spec2.patch:126-145).  `planes` = 2 keeps about 22 bits of each f32 value in two
- * fp16 columns (T <= 8); `planes` = 1 takes bf16 rows as they are (T <= 16 rows... T <= 8 used). */
+ * fp16 columns (T <= 8); `planes` = 1 takes up to 16 bf16 rows as they are. */
 typedef struct llb_xp llb_xp;
 LLB_API llb_xp *llb_b200_xp_new(int K, int T, int planes);
 LLB_API void llb_b200_xp_free(llb_xp *xp);
