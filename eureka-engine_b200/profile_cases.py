@@ -1,0 +1,74 @@
+#!/usr/bin/env python
+"""Small, self-ending cases to run under ncu (one GPU).
+
+    python eureka-engine_b200/profile_cases.py gemm FMT ROWS[,ROWS..] K     three launches of one GEMM site
+    python eureka-engine_b200/profile_cases.py verify LAYERS [PROMPT]       two replays of the verify pass of the
+                                                                            27B-shape model truncated to LAYERS,
+                                                                            bracketed by cudaProfilerStart/Stop
+"""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import torch  # noqa: E402
+
+import __graft_entry__ as graft  # noqa: E402
+
+
+def case_gemm(fmt_name, rows_list, K, T=4):
+    pkg = graft.load_package()
+    llb, packs = pkg.llb, pkg.packs
+    llb.init(0)
+    L = llb.lib()
+    dev = torch.device("cuda:0")
+    fmt = packs.FMT[fmt_name]
+    raws = [packs.q4k_random_blocks(r, K, seed=2, device=dev) if fmt_name == "Q4_K"
+            else packs.QUANT[fmt_name](torch.randn(r, K, device=dev) * 0.02) for r in rows_list]
+    sets = []
+    for _ in range(3):
+        ws = []
+        for r, raw in zip(rows_list, raws):
+            p = llb.alloc(L.llb_b200_weight_bytes(fmt, r, K))
+            llb.check(L.llb_b200_weight_upload(fmt, r, K, raw.data_ptr(), 1, p), "weight_upload")
+            ws.append(p)
+        sets.append(ws)
+    x = torch.randn(T, K, device=dev)
+    xp = llb.handle(L.llb_b200_xp_new(K, T, 2), "xp_new")
+    llb.check(L.llb_b200_xp_set_f32(xp, x.data_ptr()), "xp_set")
+    ys = [torch.zeros(T, r, device=dev) for r in rows_list]
+    for ws in sets:
+        llb.gemm(fmt, ws, rows_list, [y.data_ptr() for y in ys], K, xp, 0)
+    L.llb_sync()
+    print("ok", float(ys[0].abs().max()))
+
+
+def case_verify(layers, nprompt=3011):
+    import bench
+    pkg = graft.load_package()
+    llb = pkg.llb
+    llb.init(0)
+    packs, pack, mtp, prompt = bench.build_model("cuda:0", layers=layers if layers < 64 else None)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    eng = llb.SpecEngine(pack, mtp, k=3, max_ctx=4300)
+    eng.prefill(prompt[:nprompt])
+    eng.run_cycles(2)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    ms = eng.time_verify(1)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print("verify ms", ms, "kernels", eng.graph_nodes(2))
+    for n, (c, t) in sorted(eng.profile_verify().items(), key=lambda kv: -kv[1][1]):
+        print(f"{n:18s} n={c:4d} total_us={t:9.1f}")
+    eng.close()
+
+
+if __name__ == "__main__":
+    if sys.argv[1] == "gemm":
+        case_gemm(sys.argv[2], [int(v) for v in sys.argv[3].split(",")], int(sys.argv[4]))
+    elif sys.argv[1] == "verify":
+        case_verify(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3011)
+    else:
+        raise SystemExit(__doc__)
