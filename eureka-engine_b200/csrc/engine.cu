@@ -63,6 +63,10 @@ struct llb_spec {
   XPlanes xp_d, xp_f, xp_qa, xp_v, xp_2d;
   OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg, b_ring;
   int att_split = 1;
+  // Measured on the 27B shape: letting the last writer of a tile add the K-slices costs the GEMM's tail more
+  // (fence, atomic, a dependent round of loads) than it saves the consumers, so it is off by default.
+  bool reduce_in_gemm = false;
+  unsigned int *tile_ctr = nullptr;   // last-writer reduction counters of the GEMMs (one word per row tile)
   // graphs
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
   size_t n_spec_nodes = 0, n_verify_nodes = 0;
@@ -202,7 +206,7 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
     if (done[i]) continue;
     GemmArgs a;
     memset(&a, 0, sizeof a);
-    a.K = mats[i].w->cols; a.xp = xp; a.planes = 2; a.T = m->Tmax;
+    a.K = mats[i].w->cols; a.xp = xp; a.planes = 2; a.T = m->Tmax; a.tile_ctr = m->reduce_in_gemm ? m->tile_ctr : nullptr;
     int ntiles = 0;
     std::vector<size_t> grp;
     for (size_t j = i; j < mats.size() && grp.size() < GEMM_MAXMAT; j++)
@@ -220,11 +224,12 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
       if (sm.direct) {
         if (ks > sm.direct_splits) return llb_fail("gemm site: %d K-slices, the direct output holds %d", ks, sm.direct_splits);
         a.m[g].out = sm.direct; a.m[g].ostride = sm.direct_stride; a.m[g].split_stride = sm.direct_split_stride;
-        if (sm.out) { sm.out->p = sm.direct; sm.out->ns = ks; sm.out->stride = sm.direct_split_stride; }
+        if (sm.out) { sm.out->p = sm.direct; sm.out->ns = m->reduce_in_gemm ? 1 : ks; sm.out->stride = sm.direct_split_stride; }
       }
       else {
         CK(out_prepare(m, *sm.out, sm.w->rows, ks));
         a.m[g].out = sm.out->p; a.m[g].ostride = sm.w->rows; a.m[g].split_stride = sm.out->stride;
+        if (m->reduce_in_gemm) sm.out->ns = 1;   // the launch reduces its own K-slices into slice 0
       }
       done[grp[g]] = true;
     }
@@ -358,6 +363,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (m->hd != 128 && m->hd != 256) return llb_fail("head_dim %d unsupported", m->hd);
   if (m->d % 256 || m->f % 256 || m->vdc % 256 || (m->H * m->hd) % 256) return llb_fail("model widths must be multiples of 256");
   if (m->TR % m->GK || m->H % m->KV) return llb_fail("head counts do not divide");
+  { const char *e = getenv("LLB_GEMM_REDUCE"); m->reduce_in_gemm = e && e[0] == '1'; }
   m->k = k; m->Tmax = k + 1; m->R = k + 2; m->max_ctx = max_ctx;
   m->NC = m->Tmax <= 4 ? 8 : 16;
   const int d = m->d, qa = m->H * m->hd, kvd = m->KV * m->hd, T = m->Tmax;
@@ -496,6 +502,13 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   CU_OK(cudaHostAlloc((void **)&m->res_host, sizeof(SpecResult) * m->res_n, cudaHostAllocMapped));
   memset(m->res_host, 0, sizeof(SpecResult) * m->res_n);
   CU_OK(cudaHostGetDevicePointer((void **)&m->res_dev, m->res_host, 0));
+  {
+    int mt = (m->V + 15) / 16 + 64;
+    if ((2 * m->f + 15) / 16 + 64 > mt) mt = (2 * m->f + 15) / 16 + 64;
+    if ((m->convd + m->vdc + 2 * m->TR + 63) / 16 + 64 > mt) mt = (m->convd + m->vdc + 2 * m->TR + 63) / 16 + 64;
+    m->tile_ctr = (unsigned int *)dalloc(m, (size_t)mt * 4);
+    if (!m->tile_ctr) return -1;
+  }
   CK(ops_model_setup());
   return 0;
 }

@@ -39,6 +39,8 @@ struct GemmArgs {
   XPlanes xp;
   int planes;                  // 2: hi/lo columns are folded into T = NC/2 tokens; 1: NC independent tokens
   int T;                       // tokens actually written
+  unsigned int *tile_ctr;      // optional, zeroed, one word per row tile: with ksplit > 1 the warp that
+                               // writes a tile's last K-slice adds the slices in index order into slice 0
 };
 
 template <int FMT> struct FmtTraits;
@@ -229,6 +231,72 @@ __device__ __forceinline__ void consume_chunk(const uint8_t *st, int csb, int kc
   }
 }
 
+// ---- epilogue of one (row tile, K-slice) unit ---------------------------------------------------
+// Folds the planes, writes the unit's partial sums and, when a.tile_ctr is given and K is split, lets
+// the last writer of the tile reduce: it adds the ksplit slices in index order (so the sum does not
+// depend on who came last) and stores the total over slice 0.  Consumers then read one array.
+template <int NT>
+__device__ __forceinline__ void gemm_epilogue(const GemmArgs &a, const GemmMat &M, int ks, int tile, int row0, float (&acc)[NT][4], int lane) {
+  const int gid = lane >> 2, j = lane & 3;
+  float val[NT][4];
+  size_t idx[NT][4];
+  bool on[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) { val[nt][i] = 0.0f; idx[nt][i] = 0; on[nt][i] = false; }
+  if (a.planes == 2) {
+    float lo[4];
+    if constexpr (NT == 1) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) lo[i] = __shfl_xor_sync(0xffffffffu, acc[0][i], 2);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) lo[i] = acc[NT - 1][i];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int t = 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
+      on[0][i] = (NT == 2 || j < 2) && t < a.T && r < M.rows;
+      if (on[0][i]) { idx[0][i] = (size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r; val[0][i] = acc[0][i] + lo[i] * XP_LO_INV; }
+    }
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int t = nt * 8 + 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
+        on[nt][i] = t < a.T && r < M.rows;
+        if (on[nt][i]) { idx[nt][i] = (size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r; val[nt][i] = acc[nt][i]; }
+      }
+  }
+  float *out = M.out + (size_t)ks * M.split_stride;
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) if (on[nt][i]) out[idx[nt][i]] = val[nt][i];
+  if (a.ksplit > 1 && a.tile_ctr) {
+    __threadfence();
+    __syncwarp();
+    unsigned int old = 0;
+    if (lane == 0) old = atomicAdd(&a.tile_ctr[tile], 1u);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old == (unsigned int)a.ksplit - 1) {
+      __threadfence();
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          if (!on[nt][i]) continue;
+          float v = __ldcg(M.out + idx[nt][i]);
+          for (int k = 1; k < a.ksplit; k++) v += __ldcg(M.out + (size_t)k * M.split_stride + idx[nt][i]);
+          M.out[idx[nt][i]] = v;
+        }
+      if (lane == 0) a.tile_ctr[tile] = 0;
+    }
+  }
+}
+
 // ---- the kernel --------------------------------------------------------------------------------
 struct TileCursor {
   int u;          // unit index (ks * ntiles + tile); >= nunits when exhausted
@@ -328,49 +396,7 @@ __global__ void __launch_bounds__(GEMM_WARPS * 32, 1) k_gemm(const GemmArgs a) {
     pstage = (pstage + 1) % STAGES;
     cstage = (cstage + 1) % STAGES;
     if (++cons.c == cons.nch) {
-      // epilogue: fold planes, write this unit's partial sums
-      const GemmMat &M = a.m[cons.mat];
-      const int gid = lane >> 2, j = lane & 3;
-      const int ks = cons.u / ntiles;
-      float *out = M.out + (size_t)ks * M.split_stride;
-      if (a.planes == 2) {
-        if constexpr (NT == 1) {
-          // columns 0..3 hi, 4..7 lo: lane j holds columns 2j, 2j+1; partner j^2 holds the other plane
-          float o[4];
-#pragma unroll
-          for (int i = 0; i < 4; i++) o[i] = __shfl_xor_sync(0xffffffffu, acc[0][i], 2);
-          if (j < 2) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-              int t = 2 * j + (i & 1), r = cons.row0 + gid + ((i >> 1) << 3);
-              if (t < a.T && r < M.rows) {
-                int slot = M.tok_slot ? M.tok_slot[t] : t;
-                out[(size_t)slot * M.ostride + r] = acc[0][i] + o[i] * XP_LO_INV;
-              }
-            }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            int t = 2 * j + (i & 1), r = cons.row0 + gid + ((i >> 1) << 3);
-            if (t < a.T && r < M.rows) {
-              int slot = M.tok_slot ? M.tok_slot[t] : t;
-              out[(size_t)slot * M.ostride + r] = acc[0][i] + acc[NT - 1][i] * XP_LO_INV;
-            }
-          }
-        }
-      } else {
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            int t = nt * 8 + 2 * j + (i & 1), r = cons.row0 + gid + ((i >> 1) << 3);
-            if (t < a.T && r < M.rows) {
-              int slot = M.tok_slot ? M.tok_slot[t] : t;
-              out[(size_t)slot * M.ostride + r] = acc[nt][i];
-            }
-          }
-      }
+      gemm_epilogue<NT>(a, a.m[cons.mat], cons.u / ntiles, cons.u % ntiles, cons.row0, acc, lane);
       cons.u += nw;
       cursor_load<FMT>(cons, a, ntiles, nunits);
     }

@@ -241,34 +241,7 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, 1) k_gemm2(const Ge
     if (++c_c == nsl) {
       int m = 0;
       while (m + 1 < a.nmat && c_tile >= a.tile0[m + 1]) m++;
-      const GemmMat &M = a.m[m];
-      const int row0 = (c_tile - a.tile0[m]) * 16;
-      float *out = M.out + (size_t)ks * M.split_stride;
-      if (a.planes == 2) {
-        float lo[4];
-        if constexpr (NT == 1) {
-#pragma unroll
-          for (int i = 0; i < 4; i++) lo[i] = __shfl_xor_sync(0xffffffffu, acc[0][i], 2);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 4; i++) lo[i] = acc[NT - 1][i];
-        }
-        if (NT == 2 || j < 2) {
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const int t = 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
-            if (t < a.T && r < M.rows) out[(size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r] = acc[0][i] + lo[i] * XP_LO_INV;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const int t = nt * 8 + 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
-            if (t < a.T && r < M.rows) out[(size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r] = acc[nt][i];
-          }
-      }
+      gemm_epilogue<NT>(a, a.m[m], ks, c_tile, (c_tile - a.tile0[m]) * 16, acc, lane);
       c_c = 0;
       c_tile += nws;
     }

@@ -67,19 +67,22 @@ __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restric
     v[i] = (c < d && xin && !zero) ? xin[row + c] : 0.0f;
   }
   if (add.p && !zero) {
-    // two slices per trip: 2 x NORM_MAXI independent loads in flight
-    for (int k = 0; k < add.ns; k += 2) {
+    // four slices per trip: 4 x NORM_MAXI independent loads in flight, added in slice order
+    for (int k = 0; k < add.ns; k += 4) {
       const float *pk = add.p + (size_t)k * add.stride + row;
-      const bool two = k + 1 < add.ns;
-      float l0[NORM_MAXI], l1[NORM_MAXI];
+      const int nk = add.ns - k;
+      float l[4][NORM_MAXI];
 #pragma unroll
-      for (int i = 0; i < NORM_MAXI; i++) {
-        const int c = threadIdx.x + i * NORM_THREADS;
-        l0[i] = c < d ? pk[c] : 0.0f;
-        l1[i] = (c < d && two) ? pk[add.stride + c] : 0.0f;
-      }
+      for (int q = 0; q < 4; q++)
 #pragma unroll
-      for (int i = 0; i < NORM_MAXI; i++) { v[i] += l0[i]; v[i] += l1[i]; }
+        for (int i = 0; i < NORM_MAXI; i++) {
+          const int c = threadIdx.x + i * NORM_THREADS;
+          l[q][i] = (c < d && q < nk) ? pk[(size_t)q * add.stride + c] : 0.0f;
+        }
+#pragma unroll
+      for (int q = 0; q < 4; q++)
+#pragma unroll
+        for (int i = 0; i < NORM_MAXI; i++) v[i] += l[q][i];
     }
   }
   float ss = 0.0f;
@@ -418,19 +421,23 @@ __global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const
                                                     const RowSet *__restrict__ rs) {
   pdl_trigger();
   pdl_wait();
-  __shared__ float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128], vs[SPEC_MAXT][32], db[SPEC_MAXT][2];
+  __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
+  __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2];
   __shared__ float red[2 * SPEC_MAXT][4];
   const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs->n, lane = tid & 31, wp = tid >> 5;
   const int g = hh % sh.GK;   // value head hh reads q/k group hh % GK (tile, tools/qwen35_engine.c:621-626)
   const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
   const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
-  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 32 * cq;
+  // thread (jr, cq) holds columns 16*i + 4*cq + e (i < 8, e < 4) of state row 32*jq + jr: the four
+  // threads of a row read 64 contiguous bytes per i, and their k / q reads from shared memory are four
+  // consecutive float4 (no bank conflict; a 32-column-per-thread split would put all four on one bank)
+  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 4 * cq;
   // the state rows first: their latency hides behind the q/k preparation
   float st[32];
   {
     const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
 #pragma unroll
-    for (int i = 0; i < 8; i++) { float4 v = src[i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
+    for (int i = 0; i < 8; i++) { float4 v = src[4 * i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
   }
   float qv[SPEC_MAXT], kv[SPEC_MAXT];
 #pragma unroll
@@ -463,21 +470,30 @@ __global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const
   __syncthreads();
   for (int t = 0; t < n; t++) {
     const float dec = db[t][0], bt = db[t][1];
-    float kvacc = 0.0f;
+    float kq[32];
 #pragma unroll
-    for (int i = 0; i < 32; i++) { st[i] *= dec; kvacc += st[i] * ks[t][32 * cq + i]; }
+    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&ks[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
+    float ka[4] = {0.f, 0.f, 0.f, 0.f};   // four independent chains instead of one of 32
+#pragma unroll
+    for (int i = 0; i < 32; i++) { st[i] *= dec; ka[i & 3] += st[i] * kq[i]; }
+    float kvacc = (ka[0] + ka[1]) + (ka[2] + ka[3]);
     kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 1);
     kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 2);
     const float delta = (vs[t][jr] - kvacc) * bt;
-    float oacc = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 32; i++) { st[i] += ks[t][32 * cq + i] * delta; oacc += st[i] * qs[t][32 * cq + i]; }
+    for (int i = 0; i < 32; i++) st[i] += kq[i] * delta;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&qs[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
+    float oa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i++) oa[i & 3] += st[i] * kq[i];
+    float oacc = (oa[0] + oa[1]) + (oa[2] + oa[3]);
     oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
     oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
     if (cq == 0) o[(size_t)t * sh.vdc + hh * 128 + 32 * jq + jr] = oacc;
     float4 *dst = (float4 *)(S + (size_t)((sc + t + 1) % R) * slot_sz + off);
 #pragma unroll
-    for (int i = 0; i < 8; i++) dst[i] = make_float4(st[4 * i], st[4 * i + 1], st[4 * i + 2], st[4 * i + 3]);
+    for (int i = 0; i < 8; i++) dst[4 * i] = make_float4(st[4 * i], st[4 * i + 1], st[4 * i + 2], st[4 * i + 3]);
   }
 }
 int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,
