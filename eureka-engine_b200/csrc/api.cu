@@ -188,4 +188,58 @@ int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16,
   return 0;
 }
 
+// ---- the GEMM for hosts that may not allocate -------------------------------------------------
+// Some hosts give a library its memory once, at start-up, and refuse driver allocations afterwards:
+// a serving process whose other streams must never stall on cudaMalloc's device-wide synchronisation,
+// or a plugin sandbox that simply denies the call.  For them the scratch this GEMM needs -- the fp16
+// activation planes and the K-slice partial sums -- lives in a fixed array inside the library image.
+// Every GPU that loads the library carries these 8.5 MB until the process exits.
+#define NOALLOC_MAX_K 8192
+#define NOALLOC_MAX_T 4
+#define NOALLOC_PART_FLOATS (2u << 20)                                   /* [K-slices][T][rows] f32 */
+#define NOALLOC_XP_BYTES 172032                                          /* xp_bytes(8192, 8), rounded up to 256 */
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_XP_BYTES + NOALLOC_PART_FLOATS * 4];
+// In host code the array's name is only a handle for the runtime; the device address is looked up
+// once per device, with that device current, and kept here.
+static unsigned char *g_noalloc_ptr[64];
+
+int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr x_f32, int T, llb_dptr out_f32) {
+  NEED_INIT(-1)
+  if (K < 256 || K % 256 || K > NOALLOC_MAX_K) return llb_fail("gemm_noalloc: K = %d; this entry point takes multiples of 256 up to %d", K, NOALLOC_MAX_K);
+  if (T < 1 || T > NOALLOC_MAX_T) return llb_fail("gemm_noalloc: T = %d; this entry point takes 1..%d rows", T, NOALLOC_MAX_T);
+  if (rows < 1) return llb_fail("gemm_noalloc: rows = %d", rows);
+  if (!dev_row_bytes(fmt, K) || fmt == LLB_FM_F32) return llb_fail("gemm_noalloc: format %d has no kernel", fmt);
+  const int NC = 8;
+  const int ks = gemm_pick_ksplit(fmt, NC, (rows + 15) / 16, K / 256, g_llb.sms);
+  if ((size_t)ks * T * rows > NOALLOC_PART_FLOATS)
+    return llb_fail("gemm_noalloc: %d K-slices x %d rows x %d output rows need %zu floats of scratch, the built-in array holds %u",
+                    ks, T, rows, (size_t)ks * T * rows, (unsigned)NOALLOC_PART_FLOATS);
+  if (xp_bytes(K, NC) > NOALLOC_XP_BYTES) return llb_fail("gemm_noalloc: planes of %d columns do not fit", K);
+  int dev = 0;
+  CU_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return llb_fail("gemm_noalloc: device ordinal %d", dev);
+  if (!g_noalloc_ptr[dev]) {
+    void *p = nullptr;
+    CU_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = (unsigned char *)p;
+  }
+  unsigned char *scratch = g_noalloc_ptr[dev];
+  // the array keeps the previous call's contents: the planes start from zero every time (unused
+  // columns would otherwise carry stale values into the tensor-core tiles); the partial sums are
+  // fully rewritten before they are read
+  CU_OK(cudaMemsetAsync(scratch, 0, xp_bytes(K, NC), g_llb.stream));
+  XPlanes xp = xp_carve(scratch, K, NC);
+  if (ops_xp_from_f32(g_llb.stream, (const float *)(uintptr_t)x_f32, T, 2, xp)) return -1;
+  float *parts = (float *)(scratch + NOALLOC_XP_BYTES);
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.nmat = 1; a.K = K; a.xp = xp; a.planes = 2; a.T = T; a.ksplit = ks;
+  a.m[0].W = (const uint8_t *)(uintptr_t)w; a.m[0].rows = rows; a.m[0].ostride = rows;
+  a.m[0].out = ks == 1 ? (float *)(uintptr_t)out_f32 : parts;
+  a.m[0].split_stride = ks == 1 ? 0 : (long long)T * rows;
+  if (gemm_launch(g_llb.stream, fmt, a)) return -1;
+  if (ks > 1 && ops_sum_parts(g_llb.stream, parts, ks, (long long)T * rows, T * rows, (float *)(uintptr_t)out_f32)) return -1;
+  return 0;
+}
+
 }  // extern "C"

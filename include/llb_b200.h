@@ -75,6 +75,18 @@ LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows,
 LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
                        llb_dptr x_dev, llb_dptr y_dev);
 
+/* Y[t][r] = sum_c W[r][c] x[t][c] for callers that are not allowed to allocate.  No counterpart in the
+ * reference.  Meant for hosts that fix a library's memory at start-up and forbid driver allocations
+ * afterwards (a serving process that cannot afford cudaMalloc's device-wide synchronisation, a plugin
+ * sandbox that denies it).  x: f32 [T][K], out: f32 [T][rows], w: device layout, all caller-owned.
+ * Planes and K-slice partial sums live in a fixed 8.5 MB array inside the library (held on every GPU that
+ * loads it until exit); the call itself makes no cudaMalloc / cudaFree / allocating library call.
+ * Limits: K a multiple of 256 up to 8192, T <= 4, (K-slices x T x rows) <= 2 Mi floats; anything larger
+ * returns -1 with the reason.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress): make that call before any stream capture begins.  All calls share the one array,
+ * so two calls whose GPU work overlaps (different streams, different threads) race. */
+LLB_API int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr x_f32, int T, llb_dptr out_f32);
+
 /* ---- 3. the speculative cycle ----------------------------------------------------------------- */
 /* Replaces host/llb_host.c:1474-1950 for greedy decoding with the MTP drafter.
  * index_text: the pack's index.tsv (tools/qwen35_engine.c:379-433); pack: pack.bin bytes (host, or a
