@@ -30,6 +30,7 @@ int llb_b200_init(int device) {
   if (pr.major < 10) return llb_fail("device %d is sm_%d%d; this library is built for sm_100a only", device, pr.major, pr.minor);
   g_llb.device = device;
   { const char *e = getenv("LLB_PDL"); g_llb.pdl = !(e && e[0] == '0'); }
+  { const char *e = getenv("LLB_GEMM3"); g_llb.gemm3 = e && e[0] == '1'; }
   g_llb.sms = pr.multiProcessorCount;
   // a blocking stream: ordered after work a caller queued on the legacy default stream (torch's), so
   // device buffers produced there can be handed in without an explicit synchronisation
@@ -175,6 +176,17 @@ int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const l
     for (int i = 0; i < nmat; i++)
       if (ops_sum_parts(g_llb.stream, a.m[i].out, a.ksplit, a.m[i].split_stride, xp->T * rows[i], (float *)(uintptr_t)out[i])) return -1;
   return 0;
+}
+
+int llb_b200_use_tcgen05(int on) {
+  NEED_INIT(-1)
+  const int was = g_llb.gemm3;
+  g_llb.gemm3 = on != 0;
+  return was;
+}
+int llb_b200_wait_errors(void) {
+  NEED_INIT(-1)
+  return gemm_wait_errors();
 }
 
 int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp, llb_dptr x_dev,

@@ -1,11 +1,15 @@
 // gemm.cu -- host side of the dequant-fused skinny GEMMs (kernels in gemm.cuh and gemm2.cuh).
 #include "gemm2.cuh"
+#include "gemm3.cuh"
 #include "host.cuh"
 
 static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K; }
 static int g2_max_sb(int fmt, int NC) {
   return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC) : g2_max_slice_sb<LLB_FM_Q6_K>(NC);
 }
+// the tcgen05 kernel takes Q4_K with T <= 4 (8 plane columns)
+static bool is_g3(int fmt, int NC) { return g_llb.gemm3 && fmt == LLB_FM_Q4_K && NC == 8; }
+static unsigned int *g_g3_err = nullptr;   // device word: set when a bounded wait of k_gemm3 ran out
 static int g2_warps(int fmt) { return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS; }
 
 template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs &a, int grid) {
@@ -15,7 +19,7 @@ template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs 
 }
 template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs &a) {
   const int NC = 8 * NT, nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
-  int cps = g_llb.sms / a.ksplit;
+  int cps = g_llb.sms * G2_CPSM / a.ksplit;
   if (cps < 1) cps = 1;
   // no more CTAs per slice than there are 16-tile groups to hand out
   constexpr int G2_WARPS = G2Traits<FMT>::WARPS;
@@ -26,6 +30,26 @@ template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs 
   cudaError_t e = llb_launch(k_gemm2<FMT, NT>, dim3(cps * a.ksplit), dim3(G2_WARPS * 32), smem, s, a, cps);
   if (e != cudaSuccess) return llb_fail("k_gemm2 launch: %s", cudaGetErrorString(e));
   return 0;
+}
+
+static int launch_three(cudaStream_t s, const GemmArgs &a) {
+  const int nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
+  int ntiles = 0;
+  for (int i = 0; i < a.nmat; i++) ntiles += (a.m[i].rows + 127) / 128;
+  int cps = g_llb.sms / a.ksplit;
+  if (cps < 1) cps = 1;
+  if (cps > ntiles) cps = ntiles;
+  const size_t smem = (size_t)g3_smem_bytes(nsl);
+  if (smem > G3_SMEM_MAX) return llb_fail("k_gemm3: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
+  cudaError_t e = llb_launch(k_gemm3, dim3(cps * a.ksplit), dim3(G3_BLOCK), smem, s, a, cps, g_g3_err);
+  if (e != cudaSuccess) return llb_fail("k_gemm3 launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+// 1 when a bounded wait of the tcgen05 kernel has run out since the library was initialised
+int gemm_wait_errors(void) {
+  unsigned int v = 0;
+  if (g_g3_err && cudaMemcpy(&v, g_g3_err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return (int)v;
 }
 
 template <int FMT> static int setup_fmt() {
@@ -42,12 +66,21 @@ template <int FMT> static int setup_fmt2() {
 int gemm_setup(void) {
   if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
   if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>()) return -1;
+  CU_OK(cudaFuncSetAttribute(k_gemm3, cudaFuncAttributeMaxDynamicSharedMemorySize, G3_SMEM_MAX));
+  if (!g_g3_err) {
+    CU_OK(cudaMalloc(&g_g3_err, 4));
+    CU_OK(cudaMemset(g_g3_err, 0, 4));
+  }
   return 0;
 }
 
 int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks) {
   if (ks < 1) ks = 1;
-  if (is_g2(fmt)) {
+  if (is_g3(fmt, NC)) {
+    const int mx = g3_max_slice_sb();
+    const int lo = (nsb + mx - 1) / mx;
+    if (ks < lo) ks = lo;
+  } else if (is_g2(fmt)) {
     const int mx = g2_max_sb(fmt, NC);
     const int lo = (nsb + mx - 1) / mx;       // the activation slice of a CTA has to fit in shared memory
     if (ks < lo) ks = lo;
@@ -65,8 +98,16 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
   for (int ks = 1; ks <= GEMM_MAXSPLIT && ks <= nsb; ks++) {
     if (gemm_fix_ksplit(fmt, NC, nsb, ks) != ks) continue;
     long long rounds;
-    if (is_g2(fmt)) {
-      const int cps = sms / ks > 0 ? sms / ks : 1;
+    if (is_g3(fmt, NC)) {
+      // 128-row tiles, one CTA per (tile, slice) at a time; 1.5 super-blocks of pipeline fill per tile
+      const int cps = sms / ks > 0 ? sms / ks : 1, nt128 = (ntiles + 7) / 8;
+      rounds = (nt128 + cps - 1) / cps;
+      const int slice = (nsb + ks - 1) / ks;
+      const double cost = (double)rounds * (slice + 1.5) * (1.0 + 0.02 * (ks - 1));
+      if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
+      continue;
+    } else if (is_g2(fmt)) {
+      const int cps = sms * G2_CPSM / ks > 0 ? sms * G2_CPSM / ks : 1;
       rounds = (ntiles + (long long)cps * g2_warps(fmt) - 1) / ((long long)cps * g2_warps(fmt));
     } else {
       const long long nw = (long long)sms * GEMM_WARPS;
@@ -91,6 +132,7 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   if (a.ksplit != gemm_fix_ksplit(fmt, a.xp.NC, a.nsb, a.ksplit)) return llb_fail("gemm: ksplit %d is not valid for this shape", a.ksplit);
   if (a.tile0[a.nmat] < 1) return 0;
   const int NT = a.xp.NC / 8;
+  if (is_g3(fmt, a.xp.NC)) return launch_three(s, a);
   if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : launch_two<LLB_FM_Q4_K, 2>(s, a);
   if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : launch_two<LLB_FM_Q5_K, 2>(s, a);
   if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_two<LLB_FM_Q6_K, 1>(s, a) : launch_two<LLB_FM_Q6_K, 2>(s, a);

@@ -11,6 +11,7 @@
 struct LlbCtx {
   int device = -1;
   int sms = 0;
+  int gemm3 = 0;   // Q4_K, T <= 4 on the tcgen05 kernel (LLB_GEMM3=1)
   int pdl = 1;     // programmatic dependent launch on every kernel of a pass (LLB_PDL=0 turns it off)
   cudaStream_t stream = nullptr;
   char err[512] = {0};
@@ -48,6 +49,7 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms);
 int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks);   // clamps a requested K-split to what the format's kernel can take
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
 int gemm_setup(void);
+int gemm_wait_errors(void);
 
 // ops.cu
 int ops_xp_from_f32(cudaStream_t s, const float *x, int T, int planes, XPlanes xp);

@@ -11,7 +11,7 @@ import os
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(HERE, "libllb_b200.so")
+SO_PATH = os.environ.get("LLB_SO") or os.path.join(HERE, "libllb_b200.so")   # LLB_SO: another build of the library
 
 F32, Q8_0, Q4_K, Q6_K, Q5_K = 0, 1, 3, 4, 9
 FMT_ID = {"F32": F32, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K, "Q5_K": Q5_K}
@@ -52,6 +52,7 @@ def lib() -> C.CDLL:
             "llb_b200_xp_new": (vp, [i32, i32, i32]), "llb_b200_xp_free": (None, [vp]),
             "llb_b200_xp_set_f32": (i32, [vp, u64]), "llb_b200_xp_set_bf16": (i32, [vp, u64]),
             "llb_b200_gemm": (i32, [i32, i32, C.POINTER(u64), C.POINTER(i32), C.POINTER(u64), i32, vp, i32]),
+            "llb_b200_wait_errors": (i32, []), "llb_b200_use_tcgen05": (i32, [i32]),
             "llb_b200_gemm_host": (i32, [i32, u64, i32, i32, vp, i32, vp, vp, u64, u64]),
             "llb_b200_gemm_noalloc": (i32, [i32, u64, i32, i32, u64, i32, u64]),
             "llb_spec_open": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32]),

@@ -71,6 +71,14 @@ LLB_API int llb_b200_xp_set_bf16(llb_xp *xp, llb_dptr x_bf16 /* [T][K] */);
  * out_i: f32 [T][rows_i].  ksplit = 0 picks the K-split; scratch for the partial sums is internal. */
 LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const llb_dptr *out, int K, const llb_xp *xp,
                   int ksplit);
+/* Q4_K GEMMs with T <= 4 on the tcgen05 kernel (weights unpacked into tensor memory, tcgen05.mma) instead
+ * of the mma.sync one; returns the previous setting.  Also set by LLB_GEMM3=1 at llb_b200_init.  Off by
+ * default: at the 27B shapes the mma.sync kernel is the faster of the two.  A speculative engine keeps the
+ * kernels it was opened with. */
+LLB_API int llb_b200_use_tcgen05(int on);
+/* 1 when a bounded wait inside a kernel (an mbarrier of the tensor-core GEMM) has run out since
+ * llb_b200_init: the results of that launch are not valid.  0 otherwise; -1 on a CUDA error. */
+LLB_API int llb_b200_wait_errors(void);
 /* The same through HOST buffers: bf16 x [T][K] in, f32 y [T][rows] out, copies included. */
 LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
                        llb_dptr x_dev, llb_dptr y_dev);

@@ -128,3 +128,32 @@ def test_column_independence(llb, packs, dev):
         ys.append(o.read((T, rows), np.float32))
         L.llb_b200_xp_free(xp)
     assert np.array_equal(ys[0][2].view(np.uint32), ys[1][0].view(np.uint32))
+
+
+@pytest.fixture
+def tcgen05(llb):
+    """Q4_K, T <= 4 GEMMs of this test run on the tcgen05 kernel (weights in tensor memory)."""
+    L = llb.lib()
+    was = L.llb_b200_use_tcgen05(1)
+    yield
+    L.llb_b200_use_tcgen05(was)
+    assert L.llb_b200_wait_errors() == 0      # no bounded wait on an mbarrier ran out
+
+
+@pytest.mark.parametrize("K,ksplit", [(256, 1), (768, 1), (1280, 0), (2560, 3), (5120, 0)])
+def test_tcgen05_gemm_vs_oracle(llb, packs, oracle, dev, tcgen05, K, ksplit):
+    _gemm_case(llb, packs, oracle, dev, "Q4_K", [80], K, 4, 2, ksplit, seed=K)
+    _gemm_case(llb, packs, oracle, dev, "Q4_K", [300], K, 3, 2, ksplit, seed=K + 1)
+
+
+def test_tcgen05_gemm_ragged_cat_and_planes(llb, packs, oracle, dev, tcgen05):
+    _gemm_case(llb, packs, oracle, dev, "Q4_K", [40, 8, 16, 3], 1024, 4, 2, 0, seed=5)
+    _gemm_case(llb, packs, oracle, dev, "Q4_K", [200, 130, 128], 1024, 4, 2, 2, seed=6)
+    for T, planes in ((1, 2), (2, 2), (1, 1), (8, 1)):
+        _gemm_case(llb, packs, oracle, dev, "Q4_K", [64], 1536, T, planes, 0, seed=T + planes)
+
+
+def test_tcgen05_gemm_many_tiles(llb, packs, oracle, dev, tcgen05):
+    # more 128-row tiles than CTAs: a CTA walks several tiles and prefetches across them
+    _gemm_case(llb, packs, oracle, dev, "Q4_K", [40000], 512, 4, 2, 0, seed=9)
+    _gemm_case(llb, packs, oracle, dev, "Q4_K", [20000], 1024, 4, 2, 2, seed=10)
