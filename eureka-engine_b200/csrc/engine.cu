@@ -66,6 +66,8 @@ struct llb_spec {
   // Measured on the 27B shape: letting the last writer of a tile add the K-slices costs the GEMM's tail more
   // (fence, atomic, a dependent round of loads) than it saves the consumers, so it is off by default.
   bool reduce_in_gemm = false;
+  bool rs_early = true;               // LLB_RS_EARLY=0: every kernel reads its row set after the wait
+  bool delta_fused = true;            // LLB_DELTA_FUSED=0: DeltaNet scan and gated norm as two kernels
   unsigned int *tile_ctr = nullptr;   // last-writer reduction counters of the GEMMs (one word per row tile)
   // graphs
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
@@ -96,7 +98,25 @@ static void prof_mark(const char *name) {
   cudaEventRecord(e, g_llb.stream);
   g_prof.push_back({name, e});
 }
+#ifdef LLB_DBG_SKIP
+// timing experiments only (never built into the shipped library): LLB_SKIP=small leaves out every kernel but the
+// GEMMs, LLB_SKIP=prefix[,prefix...] the ops whose names start with one of the prefixes
+static bool dbg_skip(const char *name) {
+  const char *e = getenv("LLB_SKIP");
+  if (!e) return false;
+  if (!strcmp(e, "small")) return strncmp(name, "gemm", 4) != 0;
+  while (*e) {
+    const char *c = strchr(e, ',');
+    const size_t n = c ? (size_t)(c - e) : strlen(e);
+    if (n && !strncmp(name, e, n)) return true;
+    e += n + (c ? 1 : 0);
+  }
+  return false;
+}
+#define PK(name, call) do { if (!dbg_skip(name)) { if ((call)) return -1; } prof_mark(name); } while (0)
+#else
 #define PK(name, call) do { if ((call)) return -1; prof_mark(name); } while (0)
+#endif
 #define RING_SPLITS 4   // K-slices the conv ring can hold per row
 static float bits_float(unsigned int u) { float f; memcpy(&f, &u, 4); return f; }
 
@@ -269,8 +289,12 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const 
                    {&w.z, &m->b_z, nullptr, nullptr, 0}, {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}},
                m->xp_d, 0));
   PK("delta conv", op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
-  PK("delta scan", op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
-  PK("delta gnorm", op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
+  if (m->delta_fused) {
+    PK("delta scan+gnorm", op_delta_fused(s, S, m->ctl, m->y, m->beta, m->decay, as_in(m->b_z), w.norm, sh, m->xp_v, rs));
+  } else {
+    PK("delta scan", op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
+    PK("delta gnorm", op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
+  }
   PK("gemm ssm_out", site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
   return 0;
 }
@@ -278,7 +302,9 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const 
 // the (k+1)-row verify pass (spec_rows, host/llb_host.c:1714-1769)
 static int enq_verify(llb_spec *m) {
   cudaStream_t s = g_llb.stream;
-  const RowSet *rs = &m->ctl->verify;
+  // the verify rows were set before this pass began (k_accept of the previous cycle, or the host for a
+  // prompt chunk): kernels may read them ahead of their wait
+  const RowSet *rs = m->rs_early ? rs_stable(&m->ctl->verify) : &m->ctl->verify;
   PK("embed", op_embed(s, m->embd.fmt, m->embd.w, m->d, rs, m->Tmax, m->x));
   PartIn none{nullptr, 0, 0};
   for (int il = 0; il < m->L; il++) {
@@ -363,6 +389,8 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (m->hd != 128 && m->hd != 256) return llb_fail("head_dim %d unsupported", m->hd);
   if (m->d % 256 || m->f % 256 || m->vdc % 256 || (m->H * m->hd) % 256) return llb_fail("model widths must be multiples of 256");
   if (m->TR % m->GK || m->H % m->KV) return llb_fail("head counts do not divide");
+  { const char *e = getenv("LLB_RS_EARLY"); m->rs_early = !(e && e[0] == '0'); }
+  { const char *e = getenv("LLB_DELTA_FUSED"); m->delta_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM_REDUCE"); m->reduce_in_gemm = e && e[0] == '1'; }
   m->k = k; m->Tmax = k + 1; m->R = k + 2; m->max_ctx = max_ctx;
   m->NC = m->Tmax <= 4 ? 8 : 16;

@@ -1,5 +1,6 @@
 // model.cuh -- device-side control block and kernel launchers of the verify / draft passes.
 #pragma once
+#include <stdint.h>
 #include "host.cuh"
 
 #define SPEC_MAXT 8      // rows per pass (k + 1 <= 8, host/llb_host.c:1608 limits k to 0..7)
@@ -79,6 +80,24 @@ int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, 
                   DeltaShape sh, float *o, const RowSet *rs, int Tmax);
 int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs,
                 int Tmax);
+int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,
+                   const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs);
+// A row set that no kernel of the pass in flight writes (the verify rows: k_accept sets them at the end
+// of the previous cycle) may be read before the wait on the preceding kernel, which takes one trip to L2
+// off every small kernel's critical path.  The host says so by setting bit 0 of the pointer it passes.
+static inline const RowSet *rs_stable(const RowSet *rs) { return (const RowSet *)((uintptr_t)rs | 1u); }
+#ifdef __CUDACC__
+// Opens every row-set kernel: trigger the dependents, read n and pos0 (early if tagged), wait.
+__device__ __forceinline__ const RowSet *rs_begin(const RowSet *rs, int &n, int &pos0) {
+  pdl_trigger();
+  const bool early = ((uintptr_t)rs & 1u) != 0;
+  rs = (const RowSet *)((uintptr_t)rs & ~(uintptr_t)1);
+  if (early) { n = *(const volatile int *)&rs->n; pos0 = *(const volatile int *)&rs->pos0; }
+  pdl_wait();
+  if (!early) { n = rs->n; pos0 = rs->pos0; }
+  return rs;
+}
+#endif
 int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
 int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax);
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,

@@ -2,7 +2,10 @@
 // Each kernel restates one or more of the reference's llb_t_* row kernels
 // (tools/payload-spec2.patch:35-483); the arithmetic follows the CPU engine
 // (tools/qwen35_engine.c:510-778), which is what parity is judged against.
+#include <cooperative_groups.h>
+
 #include "model.cuh"
+namespace cg = cooperative_groups;
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -29,11 +32,11 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // ---- embedding rows (llb_embedk, tools/payload-kpair.patch:526) ---------------------------------
-__global__ void k_embed(int fmt, const uint8_t *__restrict__ W, int d, const RowSet *__restrict__ rs, float *__restrict__ x) {
-  pdl_trigger();
-  pdl_wait();
+__global__ void k_embed(int fmt, const uint8_t *__restrict__ W, int d, const RowSet *rs, float *__restrict__ x) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   const int t = blockIdx.y;
-  if (t >= rs->n) return;
+  if (t >= rs_n) return;
   const uint8_t *row = W + (size_t)rs->tok[t] * dev_row_bytes(fmt, d);
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < d; c += gridDim.x * blockDim.x) x[(size_t)t * d + c] = deq_elem(fmt, row, d, c);
 }
@@ -51,13 +54,20 @@ int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs,
 #define NORM_MAXI 8   // columns per thread: d <= 8192
 __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
                                                           float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
-                                                          const RowSet *__restrict__ rs, int zero_if_pos0) {
-  pdl_trigger();
-  pdl_wait();
+                                                          const RowSet *rs, int zero_if_pos0) {
+  // the norm weights depend on no kernel: their trip to DRAM overlaps the wait on the producer
+  float wv[NORM_MAXI];
+#pragma unroll
+  for (int i = 0; i < NORM_MAXI; i++) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    wv[i] = c < d ? w[c] : 0.0f;
+  }
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float red[32];
   const int t = blockIdx.x;
-  if (t >= rs->n) return;
-  const bool zero = zero_if_pos0 && (rs->pos0 + t == 0);
+  if (t >= rs_n) return;
+  const bool zero = zero_if_pos0 && (rs_p0 + t == 0);
   const size_t row = (size_t)t * d;
   // every load of the row is issued before the first use: one round trip to L2, not one per element
   float v[NORM_MAXI];
@@ -101,7 +111,7 @@ __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restric
   for (int i = 0; i < NORM_MAXI; i++) {
     const int c = threadIdx.x + i * NORM_THREADS;   // a warp's 32 lanes hold 32 consecutive columns
     if (c < d) {
-      const float h = v[i] * sc * w[c];
+      const float h = v[i] * sc * wv[i];
       if (hn_out) hn_out[row + c] = h;
       xp_store32(xp, t, 2, xp_col0 + (c & ~31), h, lane);
     }
@@ -116,11 +126,11 @@ int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, flo
 }
 
 // ---- silu(gate) * up -> planes (llb_t_siluq, tools/payload-spec2.patch:114-124) -----------------
-__global__ void k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+__global__ void k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   const int t = blockIdx.y, lane = threadIdx.x & 31;
-  if (t >= rs->n) return;
+  if (t >= rs_n) return;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31;
   if (c0 >= f) return;
   const size_t i = (size_t)t * f + c0 + lane;
@@ -138,14 +148,14 @@ int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowS
 // grid (H + 2 KV, Tmax), block hd.  q input rows are [H][q(hd) | gate(hd)].
 __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__ qn_w, const float *__restrict__ kn_w,
                          const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, float *__restrict__ Kc,
-                         float *__restrict__ Vc, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                         float *__restrict__ Vc, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   extern __shared__ float hv[];
   __shared__ float red[32];
   const int t = blockIdx.y, b = blockIdx.x, i = threadIdx.x, hd = sh.hd;
-  if (t >= rs->n) return;
-  const int pos = rs->pos0 + t, kvd = sh.KV * hd;
+  if (t >= rs_n) return;
+  const int pos = rs_p0 + t, kvd = sh.KV * hd;
   if (b >= sh.H + sh.KV) {  // V row: copied
     const int g = b - sh.H - sh.KV;
     Vc[(size_t)pos * kvd + g * hd + i] = part_get(v, (size_t)t * kvd + g * hd + i);
@@ -197,9 +207,9 @@ int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, c
 template <int HD, int QW>
 __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, const float *__restrict__ Kc,
                                                    const float *__restrict__ Vc, AttnShape sh, int Tmax, float *__restrict__ pm,
-                                                   float *__restrict__ pl, float *__restrict__ po, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                                                   float *__restrict__ pl, float *__restrict__ po, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   extern __shared__ __align__(16) float sm[];
   constexpr int KS = HD + 4, DPL = HD / 32;
   const int G = sh.H / sh.KV, NQ = G * Tmax, nsplit = gridDim.y;
@@ -207,7 +217,7 @@ __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, 
   float *Ks = qs + (size_t)NQ * HD;       // [PT][HD + 4]
   float *Vs = Ks + ATT_PT * KS;           // [PT][HD]
   const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n = rs->n, pos0 = rs->pos0, total = pos0 + n, kvd = sh.KV * HD;
+  const int n = rs_n, pos0 = rs_p0, total = pos0 + n, kvd = sh.KV * HD;
   // slices of at least 64 positions: short contexts use the first few blocks only
   const int per = max(64, (total + nsplit - 1) / nsplit), s0 = split * per, s1 = min(total, s0 + per);
   // query (g, r) -> local index g * Tmax + r; global head h = kvh * G + g
@@ -299,16 +309,16 @@ __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, 
 // merge the splits, normalise, apply the sigmoid output gate, write the planes of attn_output's input
 // (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
 __global__ void k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
-                            AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                            AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float wsm[128];
   __shared__ float red[32];
   const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = sh.hd, lane = threadIdx.x & 31;
-  if (t >= rs->n) return;
+  if (t >= rs_n) return;
   const size_t qb = ((size_t)h * Tmax + t) * nsplit;
   // slices in use at this context length (the partial kernel's split rule)
-  const int total = rs->pos0 + rs->n;
+  const int total = rs_p0 + rs_n;
   const int per = max(64, (total + nsplit - 1) / nsplit), nact = min(nsplit, (total + per - 1) / per);
   float m = -INFINITY, l = 0.0f;
   if (i < nact) { m = pm[qb + i]; l = pl[qb + i]; }
@@ -376,11 +386,11 @@ int ops_model_setup(void) {
 // grid (ceil(convd/256) + 1, Tmax): the last block computes beta = sigmoid(b), decay = exp(softplus(a + dt) * ssm_a).
 __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn bp, PartIn ap,
                              const float *__restrict__ dt, const float *__restrict__ sa, DeltaShape sh, float *__restrict__ y,
-                             float *__restrict__ beta, float *__restrict__ decay, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                             float *__restrict__ beta, float *__restrict__ decay, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   const int t = blockIdx.y;
-  if (t >= rs->n) return;
+  if (t >= rs_n) return;
   if (blockIdx.x == gridDim.x - 1) {
     for (int h = threadIdx.x; h < sh.TR; h += blockDim.x) {
       const float b = part_get(bp, (size_t)t * sh.TR + h), a = part_get(ap, (size_t)t * sh.TR + h);
@@ -393,7 +403,7 @@ __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn b
   }
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= sh.convd) return;
-  const int pos = rs->pos0 + t;
+  const int pos = rs_p0 + t;
   float acc = 0.0f;
   for (int k = 0; k < sh.KC; k++) {  // tap KC-1 is the current token (tools/qwen35_engine.c:599-600)
     const int slot = (pos - (sh.KC - 1) + k) & (CONV_RING - 1);
@@ -418,13 +428,13 @@ int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartI
 __global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const SpecCtl *__restrict__ ctl,
                                                     const float *__restrict__ y, const float *__restrict__ beta,
                                                     const float *__restrict__ decay, DeltaShape sh, float *__restrict__ o,
-                                                    const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                                                    const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
   __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2];
   __shared__ float red[2 * SPEC_MAXT][4];
-  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs->n, lane = tid & 31, wp = tid >> 5;
+  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs_n, lane = tid & 31, wp = tid >> 5;
   const int g = hh % sh.GK;   // value head hh reads q/k group hh % GK (tile, tools/qwen35_engine.c:621-626)
   const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
   const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
@@ -508,12 +518,12 @@ int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, 
 // gated RMSNorm of each head's output -> planes of ssm_out's input
 // (llb_t_grn, tools/payload-spec2.patch:413-447; tools/qwen35_engine.c:648-654)
 __global__ void __launch_bounds__(128) k_gnorm_xp(const float *__restrict__ o, PartIn z, const float *__restrict__ nw,
-                                                  DeltaShape sh, XPlanes xp, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                                                  DeltaShape sh, XPlanes xp, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float red[32];
   const int hh = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
-  if (t >= rs->n) return;
+  if (t >= rs_n) return;
   const size_t idx = (size_t)t * sh.vdc + hh * 128 + i;
   const float v = o[idx];
   const float ss = block_sum(v * v, red);
@@ -523,6 +533,119 @@ __global__ void __launch_bounds__(128) k_gnorm_xp(const float *__restrict__ o, P
 int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs, int Tmax) {
   CU_OK(llb_launch(k_gnorm_xp, dim3(sh.TR, Tmax), dim3(128), (size_t)(0), s, o, z, nw, sh, xp, rs));
   CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- DeltaNet scan + gated RMSNorm as one kernel ------------------------------------------------
+// The scan of k_delta_scan, then the gated RMSNorm into the planes of ssm_out's input.  grid (TR, 4) in
+// clusters of four blocks = one value head: each block owns 32 state rows, and the RMSNorm's sum of
+// squares over the head's 128 outputs is exchanged through distributed shared memory.  Replaces
+// llb_t_gdl + llb_t_grn (tools/payload-spec2.patch:319-447) and one launch per DeltaNet layer.
+// (Folding the conv in as well was measured and dropped: every block has to redo the conv of its whole
+// q/k group from the four partial-sum slices of the ring, 12x the loads, 65 us against 29 us for three kernels.)
+__global__ void __cluster_dims__(1, 4, 1) __launch_bounds__(128)
+k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const float *__restrict__ y, const float *__restrict__ beta,
+              const float *__restrict__ decay, PartIn z, const float *__restrict__ nw, DeltaShape sh, XPlanes xp,
+              const RowSet *rs) {
+  __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
+  __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2], os[SPEC_MAXT][32], ssq[SPEC_MAXT], tot[SPEC_MAXT];
+  __shared__ float red[2 * SPEC_MAXT][4];
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
+  cg::cluster_group cl = cg::this_cluster();
+  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs_n, lane = tid & 31, wp = tid >> 5;
+  if (n < 1) return;   // every block of every cluster takes the same exit
+  const int g = hh % sh.GK;
+  const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
+  const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
+  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 4 * cq;
+  float st[32];
+  {
+    const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { float4 v = src[4 * i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
+  }
+  float qv[SPEC_MAXT], kv[SPEC_MAXT];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    qv[t] = t < n ? y[(size_t)t * sh.convd + g * 128 + tid] : 0.0f;
+    kv[t] = t < n ? y[(size_t)t * sh.convd + sh.kdc + g * 128 + tid] : 0.0f;
+  }
+  if (tid < 32) {
+#pragma unroll
+    for (int t = 0; t < SPEC_MAXT; t++) if (t < n) vs[t][tid] = y[(size_t)t * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + tid];
+  }
+  if (tid < 2 * SPEC_MAXT && (tid >> 1) < n) db[tid >> 1][tid & 1] = (tid & 1) ? beta[(tid >> 1) * sh.TR + hh] : decay[(tid >> 1) * sh.TR + hh];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    const float a = warp_sum(qv[t] * qv[t]), b = warp_sum(kv[t] * kv[t]);
+    if (lane == 0) { red[2 * t][wp] = a; red[2 * t + 1][wp] = b; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    if (t < n) {
+      const float sq = red[2 * t][0] + red[2 * t][1] + red[2 * t][2] + red[2 * t][3];
+      const float sk = red[2 * t + 1][0] + red[2 * t + 1][1] + red[2 * t + 1][2] + red[2 * t + 1][3];
+      const float nq = sqrtf(sq), nk = sqrtf(sk);
+      const float iq = (1.0f / (nq > sh.eps ? nq : sh.eps)) / sqrtf(128.0f), ik = 1.0f / (nk > sh.eps ? nk : sh.eps);
+      qs[t][tid] = qv[t] * iq;
+      ks[t][tid] = kv[t] * ik;
+    }
+  }
+  __syncthreads();
+  for (int t = 0; t < n; t++) {
+    const float dec = db[t][0], bt = db[t][1];
+    float kq[32];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&ks[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
+    float ka[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i++) { st[i] *= dec; ka[i & 3] += st[i] * kq[i]; }
+    float kvacc = (ka[0] + ka[1]) + (ka[2] + ka[3]);
+    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 1);
+    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 2);
+    const float delta = (vs[t][jr] - kvacc) * bt;
+#pragma unroll
+    for (int i = 0; i < 32; i++) st[i] += kq[i] * delta;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&qs[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
+    float oa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i++) oa[i & 3] += st[i] * kq[i];
+    float oacc = (oa[0] + oa[1]) + (oa[2] + oa[3]);
+    oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
+    oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
+    if (cq == 0) os[t][jr] = oacc;
+    float4 *dst = (float4 *)(S + (size_t)((sc + t + 1) % R) * slot_sz + off);
+#pragma unroll
+    for (int i = 0; i < 8; i++) dst[4 * i] = make_float4(st[4 * i], st[4 * i + 1], st[4 * i + 2], st[4 * i + 3]);
+  }
+  __syncthreads();
+  if (wp == 0) {
+    for (int t = 0; t < n; t++) {
+      const float v = os[t][lane], s2 = warp_sum(v * v);
+      if (lane == 0) ssq[t] = s2;
+    }
+  }
+  cl.sync();                                   // every block's partial sums of squares are in place
+  if (tid < n) {
+    float s2 = 0.0f;
+    for (unsigned r = 0; r < 4; r++) s2 += *cl.map_shared_rank(&ssq[tid], r);   // rank order: the same sum in all four blocks
+    tot[tid] = s2;
+  }
+  cl.sync();                                   // nobody leaves while a peer still reads its shared memory
+  for (int t = wp; t < n; t += 4) {
+    const float r = 1.0f / sqrtf(tot[t] / 128.0f + sh.eps);
+    const int col = hh * 128 + 32 * jq;
+    const float zz = part_get(z, (size_t)t * sh.vdc + col + lane);
+    xp_store32(xp, t, 2, col, os[t][lane] * r * nw[32 * jq + lane] * silu_f(zz), lane);
+  }
+}
+int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,
+                   const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs) {
+  if (sh.SZ != 128) return llb_fail("DeltaNet state size %d (only 128, as host/llb_host.c:1608)", sh.SZ);
+  CU_OK(llb_launch(k_delta_fused, dim3(sh.TR, 4), dim3(128), (size_t)0, s, S, ctl, y, beta, decay, z, nw, sh, xp, rs));
   return 0;
 }
 
@@ -546,12 +669,12 @@ __device__ __forceinline__ Top2 t2_warp(Top2 a) {
   return a;
 }
 __global__ void __launch_bounds__(256) k_top2_part(PartIn logits, int V, long long row_stride,
-                                                   float *__restrict__ part, const RowSet *__restrict__ rs) {
-  pdl_trigger();
-  pdl_wait();
+                                                   float *__restrict__ part, const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ Top2 sh[8];
   const int t = blockIdx.y;
-  if (t >= rs->n) return;
+  if (t >= rs_n) return;
   const size_t z0 = (size_t)t * row_stride;
   const int per = (V + gridDim.x - 1) / gridDim.x, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
   Top2 a = {0.f, -1, 0.f, -1};
