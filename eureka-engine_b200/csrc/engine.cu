@@ -44,6 +44,8 @@ struct llb_spec {
   double *invfreq = nullptr;
   // drafter
   bool has_mtp = false;
+  bool lookup = false;                // no drafter image and k > 0: the prompt-lookup drafter (host/llb_host.c:1936)
+  int *hist = nullptr;                // its token history on the device
   float *mt_enorm = nullptr, *mt_hnorm = nullptr, *mt_attn_norm = nullptr, *mt_shn = nullptr;
   DevMat mt_eh, mt_head;
   AttnW mt_at;
@@ -63,6 +65,7 @@ struct llb_spec {
   XPlanes xp_d, xp_f, xp_qa, xp_v, xp_2d;
   OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg, b_ring;
   int att_split = 1;
+  int att_min = 64;                   // fewest positions per attention block
   // Measured on the 27B shape: letting the last writer of a tile add the K-slices costs the GEMM's tail more
   // (fence, atomic, a dependent round of loads) than it saves the consumers, so it is off by default.
   bool reduce_in_gemm = false;
@@ -262,7 +265,7 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
 // full attention block on rows `rs`: planes xp_d hold the normed input; result partial sums in b_a
 static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
-  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps};
+  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min};
   PK("gemm qkv", site_gemm(m, {{&w.q, &m->b_q, nullptr, nullptr, 0}, {&w.k, &m->b_k, nullptr, nullptr, 0}, {&w.v, &m->b_v, nullptr, nullptr, 0}}, m->xp_d, 0));
   PK("qkrope", op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
   PK("attention", op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
@@ -357,6 +360,7 @@ static int enq_cycle(llb_spec *m, bool spec) {
   }
   CK(enq_verify(m));
   CK(op_accept(s, m->t2part, m->ctl, m->res_dev, m->res_n, m->Tmax));
+  if (m->lookup) CK(op_lookup_draft(s, m->ctl));   // the next cycle's drafts, from the history the accept kernel extended
   return 0;
 }
 
@@ -510,7 +514,12 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     m->mt_Kc = falloc(m, (size_t)max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)max_ctx * kvd);
     if (!m->mt_Kc || !m->mt_Vc) return -1;
     m->has_mtp = true;
-  } else if (k > 0) return llb_fail("k = %d drafts need a drafter image", k);
+  } else if (k > 0) {
+    // no MTP image: the reference's other drafter, prompt lookup over the token history
+    m->lookup = true;
+    m->hist = (int *)dalloc(m, ((size_t)max_ctx + 16) * 4);
+    if (!m->hist) return -1;
+  }
 
   // activations
   int big = m->f > m->convd ? m->f : m->convd;
@@ -519,6 +528,8 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   m->o = falloc(m, (size_t)T * m->vdc); m->t2part = falloc(m, (size_t)2 * SPEC_MAXT * TOP2_NB * 4);
   m->mt_x = falloc(m, (size_t)T * d); m->mt_hn = falloc(m, (size_t)T * d); m->chain_h = falloc(m, d);
   m->att_split = (2 * g_llb.sms) / m->KV;
+  { const char *e = getenv("LLB_ATT_SPLIT"); if (e && atoi(e) > 0) m->att_split = atoi(e); }
+  { const char *e = getenv("LLB_ATT_MIN"); if (e && atoi(e) >= 32) m->att_min = atoi(e) & ~31; }
   if (m->att_split < 1) m->att_split = 1;
   if (m->att_split > 128) m->att_split = 128;
   m->pm = falloc(m, (size_t)m->H * T * m->att_split); m->pl = falloc(m, (size_t)m->H * T * m->att_split);
@@ -599,7 +610,7 @@ LLB_API int llb_spec_reset(llb_spec *m) {
   CU_OK(cudaMemsetAsync(m->hn, 0, (size_t)SPEC_MAXT * m->d * 4, g_llb.stream));
   SpecCtl c;
   memset(&c, 0, sizeof c);
-  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq;
+  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq; c.hist = m->hist;
   CK(ctl_write(m, c));
   m->pos = 0; m->primed = false; m->have_last = false;
   m->cycles = m->rows = m->served = 0;
@@ -617,10 +628,12 @@ LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
   CK(llb_spec_reset(m));
   SpecCtl c;
   memset(&c, 0, sizeof c);
-  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq;
+  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq; c.hist = m->hist;
+  if (m->lookup) CU_OK(cudaMemcpyAsync(m->hist, ids, (size_t)n * 4, cudaMemcpyHostToDevice, g_llb.stream));
   // the drafter's row for position 0 pairs token 0 with a zero hidden (host/llb_host.c:1815-1817)
   c.catchup.n = 1; c.catchup.pos0 = 0; c.catchup.tok[0] = ids[0];
-  c.verify.n = m->Tmax; c.verify.pos0 = 0; c.verify.tok[0] = ids[0];
+  c.verify.n = m->lookup ? 1 : m->Tmax;   // nothing to look up at position 0
+  c.verify.pos0 = 0; c.verify.tok[0] = ids[0];
   for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
   CK(ctl_write(m, c));
   int p = 0;

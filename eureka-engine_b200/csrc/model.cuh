@@ -29,6 +29,7 @@ struct SpecCtl {
   int max_pos;           // exclusive bound on positions (context capacity)
   int chk_on, chk_pos, chk_tok;   // the caller's (pos, tok) for this cycle, checked against the committed state
   int err;               // sticky device-side error word (0 = none)
+  int *hist;             // prompt-lookup drafter only: the token at every position up to the committed one, else null
   unsigned long long seq;
 };
 
@@ -62,7 +63,8 @@ __device__ __forceinline__ float part_get(const PartIn &a, size_t i) {
   return v;
 }
 
-struct AttnShape { int H, KV, hd, rope_dim; float eps; };
+// min_per: fewest cache positions a split-K attention block takes (a multiple of 32)
+struct AttnShape { int H, KV, hd, rope_dim; float eps; int min_per; };
 struct DeltaShape { int TR, GK, SZ, KC, convd, kdc, vdc; float eps; };
 
 // launchers (ops_model.cu); every kernel covers SPEC_MAXT rows at most and ignores rows >= rs->n
@@ -98,6 +100,7 @@ __device__ __forceinline__ const RowSet *rs_begin(const RowSet *rs, int &n, int 
   return rs;
 }
 #endif
+int op_lookup_draft(cudaStream_t s, SpecCtl *ctl);
 int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
 int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax);
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,

@@ -218,8 +218,8 @@ __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, 
   float *Vs = Ks + ATT_PT * KS;           // [PT][HD]
   const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = rs_n, pos0 = rs_p0, total = pos0 + n, kvd = sh.KV * HD;
-  // slices of at least 64 positions: short contexts use the first few blocks only
-  const int per = max(64, (total + nsplit - 1) / nsplit), s0 = split * per, s1 = min(total, s0 + per);
+  // slices of whole 32-position tiles, at least min_per positions: short contexts use the first few blocks only
+  const int per = max(sh.min_per, ((total + nsplit - 1) / nsplit + 31) & ~31), s0 = split * per, s1 = min(total, s0 + per);
   // query (g, r) -> local index g * Tmax + r; global head h = kvh * G + g
   for (int i = threadIdx.x; i < NQ * HD; i += blockDim.x) {
     int ql = i / HD, dd = i - ql * HD, g = ql / Tmax, r = ql - g * Tmax;
@@ -319,7 +319,7 @@ __global__ void k_attn_comb(const float *__restrict__ pm, const float *__restric
   const size_t qb = ((size_t)h * Tmax + t) * nsplit;
   // slices in use at this context length (the partial kernel's split rule)
   const int total = rs_p0 + rs_n;
-  const int per = max(64, (total + nsplit - 1) / nsplit), nact = min(nsplit, (total + per - 1) / per);
+  const int per = max(sh.min_per, ((total + nsplit - 1) / nsplit + 31) & ~31), nact = min(nsplit, (total + per - 1) / per);
   float m = -INFINITY, l = 0.0f;
   if (i < nact) { m = pm[qb + i]; l = pl[qb + i]; }
   float M = warp_max(m);
@@ -750,6 +750,8 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
   ctl->catchup.pos0 = p0 + 1;
   for (int r = 0; r < served; r++) ctl->catchup.tok[r] = ctl->forced > 0 ? ctl->next_tok[r] : rows[r].i1;
   const int tok0 = ctl->catchup.tok[served - 1];
+  if (ctl->hist)   // the prompt-lookup drafter searches the whole token history
+    for (int r = 0; r < served; r++) ctl->hist[p0 + 1 + r] = ctl->catchup.tok[r];
   int Tn = ctl->k + 1;
   if (np0 + Tn > ctl->max_pos) Tn = ctl->max_pos - np0 > 0 ? ctl->max_pos - np0 : 1;
   ctl->verify.n = Tn;
@@ -763,6 +765,50 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
 }
 int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax) {
   CU_OK(llb_launch(k_accept, dim3(1), dim3(32 * Tmax), (size_t)(0), s, part, ctl, ring, ring_n));
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- prompt-lookup drafter (spec_draft, host/llb_host.c:1655-1676) --------------------------------
+// The reference scans the token history on the host every cycle: the LATEST earlier position j whose last
+// L = 3, 2, 1 tokens equal the history's last L, longest L first; the up-to-k tokens after j are the drafts.
+// Here one block scans the device copy of the history right after the accept kernel, so the next cycle's
+// rows are complete before its graph is launched.  Each thread keeps the latest match per L of its stride.
+__global__ void __launch_bounds__(256) k_lookup_draft(SpecCtl *__restrict__ ctl) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int best[3];
+  const int *hist = ctl->hist;
+  const int pos = ctl->verify.pos0;
+  if (!hist || ctl->verify.n < 1) return;
+  if (threadIdx.x < 3) best[threadIdx.x] = -1;
+  __syncthreads();
+  const int t0 = hist[pos], t1 = pos >= 1 ? hist[pos - 1] : -1, t2 = pos >= 2 ? hist[pos - 2] : -1;
+  int b1 = -1, b2 = -1, b3 = -1;
+  for (int j = pos - 1 - (int)threadIdx.x; j >= 0; j -= blockDim.x) {
+    if (hist[j] != t0) continue;
+    if (b1 < 0) b1 = j;
+    if (j >= 1 && pos >= 2 && hist[j - 1] == t1) {
+      if (b2 < 0) b2 = j;
+      if (j >= 2 && pos >= 3 && hist[j - 2] == t2) { if (b3 < 0) b3 = j; }
+    }
+    if (b3 >= 0) break;   // later iterations only see smaller j
+  }
+  if (b1 >= 0) atomicMax(&best[0], b1);
+  if (b2 >= 0) atomicMax(&best[1], b2);
+  if (b3 >= 0) atomicMax(&best[2], b3);
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  const int j = best[2] >= 0 ? best[2] : best[1] >= 0 ? best[1] : best[0];
+  int n = 0;
+  if (j >= 0) {
+    const int room = ctl->verify.n - 1;   // the accept kernel already clipped the rows to the context
+    while (n < ctl->k && n < room && j + 1 + n <= pos) { ctl->verify.tok[1 + n] = hist[j + 1 + n]; n++; }
+  }
+  ctl->verify.n = 1 + n;
+}
+int op_lookup_draft(cudaStream_t s, SpecCtl *ctl) {
+  CU_OK(llb_launch(k_lookup_draft, dim3(1), dim3(256), (size_t)(0), s, ctl));
   CU_OK(cudaGetLastError());
   return 0;
 }

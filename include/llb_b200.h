@@ -96,10 +96,11 @@ LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void 
 LLB_API int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr x_f32, int T, llb_dptr out_f32);
 
 /* ---- 3. the speculative cycle ----------------------------------------------------------------- */
-/* Replaces host/llb_host.c:1474-1950 for greedy decoding with the MTP drafter.
+/* Replaces host/llb_host.c:1474-1950 for greedy decoding with either of the reference's drafters.
  * index_text: the pack's index.tsv (tools/qwen35_engine.c:379-433); pack: pack.bin bytes (host, or a
- * device address when pack_on_device); mtp: the drafter as an AUX1 or MTP1 image
- * (host/llb_host.c:1525-1603), required when k > 0; k: drafts per cycle (0..7, LLB_SPEC);
+ * device address when pack_on_device); mtp: the MTP drafter as an AUX1 or MTP1 image
+ * (host/llb_host.c:1525-1603), or NULL: with k > 0 the cycle then drafts by prompt lookup over the token
+ * history (spec_draft, host/llb_host.c:1655-1676; 1 + found rows per cycle); k: drafts per cycle (0..7, LLB_SPEC);
  * max_ctx: positions of KV kept per full-attention layer; layers: > 0 truncates the model like the
  * reference engine's --layers. */
 typedef struct llb_spec llb_spec;

@@ -89,6 +89,10 @@ class Oracle:
             L.q35_mtp_load.argtypes = [_vp, C.c_char_p, C.c_size_t]
             L.q35_spec_greedy.restype = _i
             L.q35_spec_greedy.argtypes = [_vp, _vp, _i, _i, _i, _vp, _vp, C.POINTER(SpecStats)]
+            L.q35_spec_lookup.restype = _i
+            L.q35_spec_lookup.argtypes = [_vp, _vp, _i, _i, _i, _vp, _vp, C.POINTER(SpecStats)]
+            L.q35_lookup_draft.restype = _i
+            L.q35_lookup_draft.argtypes = [_vp, _i, _i, _vp]
             L.q35_mtp_rows.restype = _i
             L.q35_mtp_rows.argtypes = [_vp, _i, _i, _vp, _vp, _vp]
             L.q35_threads.argtypes = [_i]
@@ -194,6 +198,25 @@ class Oracle:
         if n != steps:
             raise RuntimeError(f"q35_spec_greedy returned {n}")
         return ids, top2, st
+
+    def spec_lookup(self, prompt, steps: int, k: int):
+        """Greedy generation with the prompt-lookup drafter (no MTP head)."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        ids = np.zeros(steps, np.int32)
+        top2 = np.zeros((steps, 4), np.uint32)
+        st = SpecStats()
+        n = self.L.q35_spec_lookup(self.h, _p(prompt), len(prompt), steps, k, _p(ids), _p(top2), C.byref(st))
+        if n != steps:
+            raise RuntimeError(f"q35_spec_lookup returned {n}")
+        return ids, top2, st
+
+
+def lookup_draft(hist, pos: int, k: int):
+    """Drafts of the prompt-lookup drafter for the history hist[0..pos]."""
+    hist = np.ascontiguousarray(hist, dtype=np.int32)
+    out = np.zeros(8, np.int32)
+    n = Oracle.lib().q35_lookup_draft(_p(hist), pos, k, _p(out))
+    return out[:n].copy()
 
 
 class RefTwin:

@@ -735,3 +735,66 @@ API int q35_spec_greedy(Q35 *m, const int *prompt, int np, int steps, int k, int
   free(hist); free(hn); free(mhn); free(keep);
   return out;
 }
+
+/* Prompt-lookup drafter (host/llb_host.c:1655-1676): the LATEST earlier match of the history's last
+ * L = 3, 2, 1 tokens (positions j-L+1..j == pos-L+1..pos, j < pos); the up-to-k tokens that followed
+ * it become the drafts.  Returns the count; hist[0..pos] must be valid. */
+API int q35_lookup_draft(const int *hist, int pos, int k, int *out) {
+  for (int L = 3; L >= 1; L--) {
+    for (int j = pos - 1; j >= L - 1; j--) {
+      int m = 0;
+      while (m < L && hist[j - m] == hist[pos - m]) m++;
+      if (m == L) {
+        int n = 0;
+        while (n < k && j + 1 + n <= pos) { out[n] = hist[j + 1 + n]; n++; }
+        return n;
+      }
+    }
+  }
+  return 0;
+}
+
+/* Greedy generation with the prompt-lookup drafter in place of the MTP head (the reference's path
+ * when LLB_SPEC is set without LLB_MTP, host/llb_host.c:1936): T = 1 + drafts rows per cycle, same
+ * accept rule.  The prompt positions before the last are plain single rows. */
+API int q35_spec_lookup(Q35 *m, const int *prompt, int np, int steps, int k, int *ids, uint32_t *top2, Q35SpecStats *st) {
+  const Q35Cfg *c = &m->c;
+  if (np < 1 || k < 0 || k > 7 || np + steps + k + 2 > m->cap) return -1;
+  int *hist = (int *)calloc((size_t)m->cap + 16, 4);
+  Q35SpecStats z;
+  memset(&z, 0, sizeof z);
+  q35_reset(m);
+  for (int t = 0; t + 1 < np; t++) {
+    hist[t] = prompt[t];
+    q35_forward(m, prompt[t], t);
+  }
+  int pos = np - 1, tok = prompt[np - 1], out = 0;
+  while (out < steps) {
+    int tin[9], nv = 0;
+    hist[pos] = tok;
+    tin[0] = tok;
+    const int T = 1 + q35_lookup_draft(hist, pos, k, tin + 1);
+    z.cycles++; z.rows += (uint64_t)T;
+    for (int r = 0; r < T; r++) {
+      q35_forward(m, tin[r], pos + r);
+      const float *lg = q35_logits(m);
+      uint32_t w[4];
+      put_top2(w, lg, c->vocab);
+      nv = r + 1;
+      hist[pos + r + 1] = (int)w[0];
+      if (out < steps) {
+        ids[out] = (int)w[0];
+        if (top2) memcpy(top2 + 4 * out, w, 16);
+        out++;
+      }
+      if (r + 1 < T && (int)w[0] != tin[r + 1]) break;
+    }
+    for (int j = 1; j < T; j++) { z.drafted[j]++; z.accepted[j] += nv > j; }
+    z.served += (uint64_t)nv;
+    tok = hist[pos + nv];
+    pos += nv;
+  }
+  if (st) *st = z;
+  free(hist);
+  return out;
+}

@@ -76,6 +76,9 @@ int q35_greedy(Q35 *m, const int *prompt, int np, int steps, int *ids, uint32_t 
 int q35_mtp_load(Q35 *m, const uint8_t *img, size_t bytes);
 int q35_spec_greedy(Q35 *m, const int *prompt, int np, int steps, int k, int *ids, uint32_t *top2,
                     Q35SpecStats *st);
+/* prompt-lookup drafter (host/llb_host.c:1655-1676) and the greedy loop that uses it in place of the MTP head */
+int q35_lookup_draft(const int *hist, int pos, int k, int *out);
+int q35_spec_lookup(Q35 *m, const int *prompt, int np, int steps, int k, int *ids, uint32_t *top2, Q35SpecStats *st);
 /* one drafter call for tests: n rows at positions pa.., tokens tk, hidden rows hs[n][d];
  * returns the draft id; hn_out[n][d] gets the drafter's own normed hidden */
 int q35_mtp_rows(Q35 *m, int n, int pa, const int *tk, const float *hs, float *hn_out);

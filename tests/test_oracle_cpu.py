@@ -116,3 +116,30 @@ def test_oracle_equals_reference_build_when_present(packs, oracle, greedy_gold, 
             % (os.path.dirname(HERE), str(tmp_path), str(tmp_path / "index.tsv"), str(tmp_path / "pack.bin"), [int(v) for v in prompt]))
     out = subprocess.run([sys.executable, "-c", code], check=True, capture_output=True, text=True).stdout
     assert json.loads(out.strip().splitlines()[-1]) is True
+
+
+def _lookup_py(hist, pos, k):
+    """host/llb_host.c:1658-1676 once more, in Python."""
+    for L in (3, 2, 1):
+        for j in range(pos - 1, L - 2, -1):
+            if all(hist[j - m] == hist[pos - m] for m in range(L)):
+                return [hist[j + 1 + n] for n in range(k) if j + 1 + n <= pos]
+    return []
+
+
+def test_prompt_lookup_drafter(packs, oracle, greedy_gold):
+    rng = np.random.default_rng(11)
+    for vocab in (3, 7, 40):
+        hist = rng.integers(0, vocab, 200).astype(np.int32)
+        for pos in (0, 1, 2, 3, 17, 199):
+            for k in (1, 3, 7):
+                assert list(oracle.lookup_draft(hist, pos, k)) == _lookup_py(list(hist), pos, k)
+    # the loop built on it emits the plain greedy stream
+    cfg, pack, prompt, ids, top2 = _case(packs, greedy_gold, "tiny_q8_0")
+    rep = np.concatenate([prompt, prompt]).astype(np.int32)
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=len(rep) + 40)
+    g_ids, g_top2 = orc.greedy(rep, 24)
+    l_ids, l_top2, st = orc.spec_lookup(rep, 24, 3)
+    assert np.array_equal(l_ids, g_ids) and np.array_equal(l_top2, g_top2)
+    assert st.served >= 24 and st.rows >= st.cycles
+    assert st.served == st.cycles + sum(list(st.accepted)[1:4])

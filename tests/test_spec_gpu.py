@@ -150,3 +150,31 @@ def test_reference_shaped_pass(pkg, packs, llb):
     assert eng.L.llb_spec_pass(eng.h, p0 + 7, tok, y.ctypes.data) == -1
     assert b"out of order" in eng.L.llb_b200_last_error()
     eng.close()
+
+
+@pytest.mark.parametrize("k", [1, 3, 5])
+def test_prompt_lookup_drafter(pkg, packs, oracle, llb, k):
+    """Without a drafter image the engine drafts by prompt lookup (host/llb_host.c:1655-1676, :1936): ids equal the
+    oracle's greedy ids, and cycles, rows and acceptance counts equal those of the oracle's lookup loop."""
+    cfg = packs.cfg_tiny(n_layers=8, seed=7)
+    pack = packs.build_pack(cfg)
+    # a prompt that repeats itself, so that lookups hit from the first cycle on
+    base = packs.synth_prompt(4, 12, cfg.vocab_size)
+    prompt = np.concatenate([base, base, base[:5]]).astype(np.int32)
+    steps = 48
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=len(prompt) + steps + 16)
+    ref_ids, ref_top2 = orc.greedy(prompt, steps)
+    lids, ltop2, st = orc.spec_lookup(prompt, steps, k)
+    assert np.array_equal(lids, ref_ids) and np.array_equal(ltop2, ref_top2)     # lossless in the oracle
+    eng = pkg.llb.SpecEngine(pack, None, k=k, max_ctx=len(prompt) + steps + 16)
+    try:
+        eng.prefill(prompt)
+        ids, top2 = eng.generate(steps)
+        assert _compare_ids(ids, ref_ids, ref_top2) == steps
+        stats = eng.stats()
+        assert stats["cycles"] == st.cycles and stats["rows"] == st.rows
+        assert stats["drafted"][1:k + 1] == [int(v) for v in list(st.drafted)[1:k + 1]]
+        assert stats["accepted"][1:k + 1] == [int(v) for v in list(st.accepted)[1:k + 1]]
+        assert stats["rows"] < stats["cycles"] * (k + 1) or k == 1   # some cycles found fewer than k drafts
+    finally:
+        eng.close()
