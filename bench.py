@@ -34,6 +34,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes one gate|up launch moved under ncu (102.1 MB read + 4.3 MB written; algorithmic 100.9 MB)
+GEMM_DRAM_TRAFFIC = 106.4e6
 METRIC = "spec-decode tok/s per B200, 27B-shape Q4_K_M MTP k=3; verify-step HBM GB/s"
 WORKLOAD = "config 2: 27B-shape hybrid (d 5120, 64 layers, f 17408, V 151936), Q4_K_M, batch 1, MTP k=3 greedy, prompt 3011"
 PROMPT, GEN_CAP, K_DRAFT = 3011, 1200, 3
@@ -271,8 +273,10 @@ def main():
             "e2e": {"value": n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 216,
                     "api": "llb_spec_pass(pos, tok) -> y[4], one call per token"},
             "gpu_launches": launches * steps,
-            "roofline": {"bound": "hbm", "kernel": "k_gemm<Q4_K> ffn_gate|ffn_up [2 x 17408 x 5120], T=4", "achieved": gemm_bytes / gemm_us / 1e3,
-                         "peak": peak, "unit": "GB/s", "frac": gemm_bytes / gemm_us / 1e3 / peak, "traffic": None, "peak_source": peak_src,
+            "roofline": {"bound": "hbm", "kernel": "k_gemm2<Q4_K> ffn_gate|ffn_up [2 x 17408 x 5120], T=4", "achieved": gemm_bytes / gemm_us / 1e3,
+                         "peak": peak, "unit": "GB/s", "frac": gemm_bytes / gemm_us / 1e3 / peak, "traffic": GEMM_DRAM_TRAFFIC,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape (profiles/k_gemm2_q4k_gate_up_2x17408x5120_T4.md)",
+                         "peak_source": peak_src,
                          "us_per_launch": gemm_us, "bytes_per_launch": gemm_bytes},
             "verify_step": {"bytes": vbytes, "ms": ver_ms, "GBs": vbytes / ver_ms / 1e6, "frac": vbytes / ver_ms / 1e6 / peak,
                             "kernels": eng.graph_nodes(2)},

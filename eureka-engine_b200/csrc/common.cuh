@@ -111,6 +111,53 @@ __device__ __forceinline__ void xp_store32(const XPlanes &xp, int t, int planes,
   }
 }
 
+// The same for a thread that holds FOUR consecutive columns c .. c+3 (c a multiple of 4) of row t; the eight
+// lanes 8j .. 8j+7 of a warp must hold one aligned group of 32 columns.  `on` is false for a thread past
+// the row's end (it still takes part in the shuffles).  Stored order inside the four: 0 2 1 3.
+__device__ __forceinline__ void xp_store4(const XPlanes &xp, int t, int planes, int c, const float (&v)[4], int lane, bool on) {
+  const int NH = xp.NC >> 1;
+  __half hi[4];
+  float hs = 0.0f, ls = 0.0f, hif[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) { hi[i] = __float2half_rn(on ? v[i] : 0.0f); hif[i] = __half2float(hi[i]); hs += hif[i]; }
+  if (on) {
+    const __half2 a = __halves2half2(hi[0], hi[2]), b = __halves2half2(hi[1], hi[3]);
+    *(uint2 *)(xp.xh + (size_t)t * xp.K + c) = make_uint2(*(const uint32_t *)&a, *(const uint32_t *)&b);
+  }
+  if (planes == 2) {
+    __half lo[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { lo[i] = __float2half_rn(on ? (v[i] - hif[i]) * XP_LO_SCALE : 0.0f); ls += __half2float(lo[i]); }
+    if (on) {
+      const __half2 a = __halves2half2(lo[0], lo[2]), b = __halves2half2(lo[1], lo[3]);
+      *(uint2 *)(xp.xh + (size_t)(NH + t) * xp.K + c) = make_uint2(*(const uint32_t *)&a, *(const uint32_t *)&b);
+    }
+  }
+  hs += __shfl_xor_sync(0xffffffffu, hs, 1); ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+  hs += __shfl_xor_sync(0xffffffffu, hs, 2); ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+  const float h32 = hs + __shfl_xor_sync(0xffffffffu, hs, 4), l32 = ls + __shfl_xor_sync(0xffffffffu, ls, 4);
+  if (!on) return;
+  if ((lane & 3) == 0) {
+    xp.xs16[(size_t)(c >> 4) * xp.NC + t] = hs;
+    if (planes == 2) xp.xs16[(size_t)(c >> 4) * xp.NC + NH + t] = ls;
+  }
+  if ((lane & 7) == 0) {
+    xp.xs32[(size_t)(c >> 5) * xp.NC + t] = h32;
+    if (planes == 2) xp.xs32[(size_t)(c >> 5) * xp.NC + NH + t] = l32;
+    const int b = (c >> 5) & 7;
+    __half *f = xp.xsf + ((size_t)(c >> 8) * xp.NC + t) * 16 + 4 * (b >> 1) + (b & 1);
+    float m = h32 * 0.03125f;
+    __half h1 = __float2half_rn(m);
+    f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
+    if (planes == 2) {
+      f += (size_t)NH * 16;
+      m = l32 * 0.03125f;
+      h1 = __float2half_rn(m);
+      f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
+    }
+  }
+}
+
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Every kernel of a pass is launched with the programmatic-serialization attribute: the next kernel's
 // CTAs may become resident while this one still runs, do whatever does not depend on it (a GEMM

@@ -50,17 +50,19 @@ int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs,
 // tools/payload-spec2.patch:35-112; rms_norm tools/qwen35_engine.c:510-515) ----------------------
 // v = xin + sum(partials); xout = v (optional); h = (v * s) * w, s = 1/sqrt(mean(v^2) + eps);
 // h goes to the planes at column offset xp_col0 and, optionally, to hn_out as f32.
-#define NORM_THREADS 1024
-#define NORM_MAXI 8   // columns per thread: d <= 8192
-__global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
-                                                          float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
-                                                          const RowSet *rs, int zero_if_pos0) {
+// One block per row; a thread holds NI groups of four consecutive columns (float4 loads and stores), so a
+// row of 5120 columns costs each of 640 threads a handful of instructions instead of one SM 13k.
+#define NORM_MAXT 1024
+template <int NI>
+__global__ void __launch_bounds__(NORM_MAXT) k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
+                                                       float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
+                                                       const RowSet *rs, int zero_if_pos0) {
   // the norm weights depend on no kernel: their trip to DRAM overlaps the wait on the producer
-  float wv[NORM_MAXI];
+  float4 wv[NI];
 #pragma unroll
-  for (int i = 0; i < NORM_MAXI; i++) {
-    const int c = threadIdx.x + i * NORM_THREADS;
-    wv[i] = c < d ? w[c] : 0.0f;
+  for (int i = 0; i < NI; i++) {
+    const int c = 4 * (threadIdx.x + i * blockDim.x);
+    wv[i] = c < d ? *(const float4 *)(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
@@ -69,58 +71,64 @@ __global__ void __launch_bounds__(NORM_THREADS) k_norm_xp(const float *__restric
   if (t >= rs_n) return;
   const bool zero = zero_if_pos0 && (rs_p0 + t == 0);
   const size_t row = (size_t)t * d;
-  // every load of the row is issued before the first use: one round trip to L2, not one per element
-  float v[NORM_MAXI];
+  // every load of a trip is issued before the first use: one round trip to L2 per four slices
+  float4 v[NI];
 #pragma unroll
-  for (int i = 0; i < NORM_MAXI; i++) {
-    const int c = threadIdx.x + i * NORM_THREADS;
-    v[i] = (c < d && xin && !zero) ? xin[row + c] : 0.0f;
+  for (int i = 0; i < NI; i++) {
+    const int c = 4 * (threadIdx.x + i * blockDim.x);
+    v[i] = (c < d && xin && !zero) ? *(const float4 *)(xin + row + c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   if (add.p && !zero) {
-    // four slices per trip: 4 x NORM_MAXI independent loads in flight, added in slice order
     for (int k = 0; k < add.ns; k += 4) {
       const float *pk = add.p + (size_t)k * add.stride + row;
       const int nk = add.ns - k;
-      float l[4][NORM_MAXI];
+      float4 l[4][NI];
 #pragma unroll
       for (int q = 0; q < 4; q++)
 #pragma unroll
-        for (int i = 0; i < NORM_MAXI; i++) {
-          const int c = threadIdx.x + i * NORM_THREADS;
-          l[q][i] = (c < d && q < nk) ? pk[(size_t)q * add.stride + c] : 0.0f;
+        for (int i = 0; i < NI; i++) {
+          const int c = 4 * (threadIdx.x + i * blockDim.x);
+          l[q][i] = (c < d && q < nk) ? *(const float4 *)(pk + (size_t)q * add.stride + c) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-      for (int q = 0; q < 4; q++)
+      for (int q = 0; q < 4; q++)   // added in slice order
 #pragma unroll
-        for (int i = 0; i < NORM_MAXI; i++) v[i] += l[q][i];
+        for (int i = 0; i < NI; i++) { v[i].x += l[q][i].x; v[i].y += l[q][i].y; v[i].z += l[q][i].z; v[i].w += l[q][i].w; }
     }
   }
   float ss = 0.0f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAXI; i++) {
-    const int c = threadIdx.x + i * NORM_THREADS;
+  for (int i = 0; i < NI; i++) {
+    const int c = 4 * (threadIdx.x + i * blockDim.x);
     if (c < d) {
-      if (xout) xout[row + c] = v[i];
-      ss += v[i] * v[i];
+      if (xout) *(float4 *)(xout + row + c) = v[i];
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     }
   }
   ss = block_sum(ss, red);
   const float sc = 1.0f / sqrtf(ss / (float)d + eps);
   const int lane = threadIdx.x & 31;
 #pragma unroll
-  for (int i = 0; i < NORM_MAXI; i++) {
-    const int c = threadIdx.x + i * NORM_THREADS;   // a warp's 32 lanes hold 32 consecutive columns
-    if (c < d) {
-      const float h = v[i] * sc * wv[i];
-      if (hn_out) hn_out[row + c] = h;
-      xp_store32(xp, t, 2, xp_col0 + (c & ~31), h, lane);
-    }
+  for (int i = 0; i < NI; i++) {
+    const int c = 4 * (threadIdx.x + i * blockDim.x);   // eight lanes hold 32 consecutive columns
+    const float h[4] = {v[i].x * sc * wv[i].x, v[i].y * sc * wv[i].y, v[i].z * sc * wv[i].z, v[i].w * sc * wv[i].w};
+    if (c < d && hn_out) *(float4 *)(hn_out + row + c) = make_float4(h[0], h[1], h[2], h[3]);
+    xp_store4(xp, t, 2, xp_col0 + c, h, lane, c < d);
   }
 }
 int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
                int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0) {
-  if (d % 32 || d > NORM_THREADS * NORM_MAXI) return llb_fail("norm: d %d", d);
-  CU_OK(llb_launch(k_norm_xp, dim3(Tmax), dim3(NORM_THREADS), (size_t)(0), s, xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0));
+  if (d % 32 || xp_col0 % 32 || d > 4 * 4 * NORM_MAXT) return llb_fail("norm: d %d at column %d", d, xp_col0);
+  const int d4 = d / 4, ni = (d4 + NORM_MAXT - 1) / NORM_MAXT;
+  const int threads = (((d4 + ni - 1) / ni) + 31) & ~31;
+#define NORM_GO(NI) CU_OK(llb_launch(k_norm_xp<NI>, dim3(Tmax), dim3(threads), (size_t)(0), s, xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0))
+  switch (ni) {
+    case 1: NORM_GO(1); break;
+    case 2: NORM_GO(2); break;
+    case 3: NORM_GO(3); break;
+    default: NORM_GO(4); break;
+  }
+#undef NORM_GO
   CU_OK(cudaGetLastError());
   return 0;
 }
