@@ -50,6 +50,23 @@ struct PartIn {
 };
 // (the slices are added in index order; four loads are in flight at a time so that a value split
 // seven ways costs two round trips to L2, not seven)
+// four consecutive values (i a multiple of 4, strides multiples of 4): all slices of a trip in flight at once
+__device__ __forceinline__ float4 part_get4(const PartIn &a, size_t i) {
+  float4 v = *(const float4 *)(a.p + i);
+  for (int k = 1; k < a.ns; k += 4) {
+    const float *p = a.p + (size_t)k * a.stride + i;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 l0 = *(const float4 *)p;
+    const float4 l1 = k + 1 < a.ns ? *(const float4 *)(p + a.stride) : z;
+    const float4 l2 = k + 2 < a.ns ? *(const float4 *)(p + 2 * a.stride) : z;
+    const float4 l3 = k + 3 < a.ns ? *(const float4 *)(p + 3 * a.stride) : z;
+    v.x += l0.x; v.y += l0.y; v.z += l0.z; v.w += l0.w;
+    v.x += l1.x; v.y += l1.y; v.z += l1.z; v.w += l1.w;
+    v.x += l2.x; v.y += l2.y; v.z += l2.z; v.w += l2.w;
+    v.x += l3.x; v.y += l3.y; v.z += l3.z; v.w += l3.w;
+  }
+  return v;
+}
 __device__ __forceinline__ float part_get(const PartIn &a, size_t i) {
   float v = a.p[i];
   for (int k = 1; k < a.ns; k += 4) {

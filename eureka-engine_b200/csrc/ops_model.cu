@@ -134,19 +134,24 @@ int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, flo
 }
 
 // ---- silu(gate) * up -> planes (llb_t_siluq, tools/payload-spec2.patch:114-124) -----------------
-__global__ void k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs) {
+__global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs) {
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   const int t = blockIdx.y, lane = threadIdx.x & 31;
   if (t >= rs_n) return;
-  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31;
-  if (c0 >= f) return;
-  const size_t i = (size_t)t * f + c0 + lane;
-  xp_store32(xp, t, 2, c0, silu_f(part_get(g, i)) * part_get(u, i), lane);
+  const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);   // four columns per thread, eight lanes per 32-column group
+  const bool on = c < f;
+  float h[4] = {0.f, 0.f, 0.f, 0.f};
+  if (on) {
+    const size_t i = (size_t)t * f + c;
+    const float4 gv = part_get4(g, i), uv = part_get4(u, i);
+    h[0] = silu_f(gv.x) * uv.x; h[1] = silu_f(gv.y) * uv.y; h[2] = silu_f(gv.z) * uv.z; h[3] = silu_f(gv.w) * uv.w;
+  }
+  xp_store4(xp, t, 2, c, h, lane, on);
 }
 int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax) {
   if (f % 32) return llb_fail("silu: f %d", f);
-  CU_OK(llb_launch(k_silu_xp, dim3((f + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs));
+  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -316,12 +321,14 @@ __global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, 
 
 // merge the splits, normalise, apply the sigmoid output gate, write the planes of attn_output's input
 // (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
-__global__ void k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
-                            AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs) {
+// block = (head, row); thread (sg, i4): split group sg of 4, dims 4*i4 .. 4*i4+3
+__global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
+                                                   AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs) {
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float wsm[128];
   __shared__ float red[32];
+  __shared__ __align__(16) float osm[1024];   // [split group][hd]
   const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = sh.hd, lane = threadIdx.x & 31;
   if (t >= rs_n) return;
   const size_t qb = ((size_t)h * Tmax + t) * nsplit;
@@ -339,14 +346,32 @@ __global__ void k_attn_comb(const float *__restrict__ pm, const float *__restric
   const float wgt = (i < nact && m != -INFINITY) ? expf(m - M) : 0.0f;
   if (i < 128) wsm[i] = wgt;
   const float L = block_sum(l * wgt, red);   // (block_sum synchronises: wsm is visible after it)
-  float o = 0.0f;
-#pragma unroll 4
-  for (int s = 0; s < nact; s++) {
-    const float ws = wsm[s];
-    if (ws != 0.0f) o += po[(qb + s) * hd + i] * ws;
+  const int hd4 = hd >> 2, ng = blockDim.x / hd4, sg = i / hd4, i4 = i - sg * hd4;   // ng split groups of hd/4 threads
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (sg < ng) {
+    // split s = sg + ng*j: four loads in flight per trip, added in split order within the group
+    for (int s0 = sg; s0 < nact; s0 += 4 * ng) {
+      float4 v[4];
+      float ws[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int s = s0 + j * ng;
+        ws[j] = s < nact ? wsm[s] : 0.0f;
+        v[j] = ws[j] != 0.0f ? *(const float4 *)(po + (qb + s) * hd + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) { o.x += v[j].x * ws[j]; o.y += v[j].y * ws[j]; o.z += v[j].z * ws[j]; o.w += v[j].w * ws[j]; }
+    }
+    *(float4 *)&osm[sg * hd + 4 * i4] = o;
   }
-  const float gate = part_get(qg, (size_t)t * 2 * sh.H * hd + (size_t)h * 2 * hd + hd + i);
-  xp_store32(xp, t, 2, h * hd + (i & ~31), (o / L) * sigmoid_f(gate), lane);
+  __syncthreads();
+  if (i < hd4) {   // a multiple of 8 threads: eight lanes per 32 dims
+    float4 a = *(const float4 *)&osm[4 * i];
+    for (int g = 1; g < ng; g++) { const float4 b = *(const float4 *)&osm[g * hd + 4 * i]; a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+    const float4 gate = part_get4(qg, (size_t)t * 2 * sh.H * hd + (size_t)h * 2 * hd + hd + 4 * i);
+    const float hv[4] = {(a.x / L) * sigmoid_f(gate.x), (a.y / L) * sigmoid_f(gate.y), (a.z / L) * sigmoid_f(gate.z), (a.w / L) * sigmoid_f(gate.w)};
+    xp_store4(xp, t, 2, h * hd + 4 * i, hv, lane, true);
+  }
 }
 
 template <int HD> static int attn_launch(cudaStream_t s, int QW, dim3 grid, size_t smem, const float *q, const float *Kc,
@@ -371,7 +396,7 @@ int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *V
   else if (sh.hd == 256) rc = attn_launch<256>(s, QW, grid, smem, q, Kc, Vc, sh, Tmax, pm, pl, po, rs);
   else return llb_fail("attention: head_dim %d", sh.hd);
   if (rc) return rc;
-  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(sh.hd), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs));
+  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(256), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }
