@@ -265,7 +265,7 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
 // full attention block on rows `rs`: planes xp_d hold the normed input; result partial sums in b_a
 static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
-  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min};
+  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd};
   PK("gemm qkv", site_gemm(m, {{&w.q, &m->b_q, nullptr, nullptr, 0}, {&w.k, &m->b_k, nullptr, nullptr, 0}, {&w.v, &m->b_v, nullptr, nullptr, 0}}, m->xp_d, 0));
   PK("qkrope", op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
   PK("attention", op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
@@ -844,8 +844,17 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
     SpecCtl c;
     CU_OK(cudaMemcpy(&c, m->ctl, sizeof c, cudaMemcpyDeviceToHost));
     have = (size_t)m->TR * m->SZ * m->SZ; src = m->S[il] + (size_t)c.sc * have;
-  } else if (what == 1 && il < m->L && m->Kc[il]) { have = kvd; src = m->Kc[il] + (size_t)pos * kvd; }
-  else if (what == 2 && il < m->L && m->Vc[il]) { have = kvd; src = m->Vc[il] + (size_t)pos * kvd; }
+  } else if ((what == 1 || what == 2 || what == 5) && (what == 5 ? m->mt_Kc != nullptr : (il < m->L && m->Kc[il]))) {
+    // a cache row is kept as two fp16 planes, hi and lo * 2048
+    const __half *c = (const __half *)(what == 5 ? m->mt_Kc : what == 1 ? m->Kc[il] : m->Vc[il]);
+    have = kvd;
+    if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
+    std::vector<__half> hi(have), lo(have);
+    CU_OK(cudaMemcpy(hi.data(), c + (size_t)pos * kvd, have * 2, cudaMemcpyDeviceToHost));
+    CU_OK(cudaMemcpy(lo.data(), c + (size_t)m->max_ctx * kvd + (size_t)pos * kvd, have * 2, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < have; i++) out[i] = __half2float(hi[i]) + __half2float(lo[i]) * XP_LO_INV;
+    return (int)have;
+  }
   else if (what == 3 && il < m->L && m->ring[il]) {
     have = m->convd;
     if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
@@ -859,7 +868,6 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
     return (int)have;
   }
   else if (what == 4) { have = m->d; src = m->hn + (size_t)pos * m->d; }
-  else if (what == 5 && m->mt_Kc) { have = kvd; src = m->mt_Kc + (size_t)pos * kvd; }
   else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
   if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
   CU_OK(cudaMemcpy(out, src, have * 4, cudaMemcpyDeviceToHost));

@@ -81,7 +81,8 @@ __device__ __forceinline__ float part_get(const PartIn &a, size_t i) {
 }
 
 // min_per: fewest cache positions a split-K attention block takes (a multiple of 32)
-struct AttnShape { int H, KV, hd, rope_dim; float eps; int min_per; };
+// kv_plane: halves between the hi and the lo plane of a K or V cache (max_ctx * KV * hd)
+struct AttnShape { int H, KV, hd, rope_dim; float eps; int min_per; long long kv_plane; };
 struct DeltaShape { int TR, GK, SZ, KC, convd, kdc, vdc; float eps; };
 
 // launchers (ops_model.cu); every kernel covers SPEC_MAXT rows at most and ignores rows >= rs->n

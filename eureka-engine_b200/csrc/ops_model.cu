@@ -158,10 +158,17 @@ int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowS
 
 // ---- per-head QK RMSNorm + partial NEOX RoPE; K and V rows straight into their cache slots
 // (llb_t_qkr, tools/payload-spec2.patch:159-204; tools/qwen35_engine.c:523-533, 667-690) ----------
-// grid (H + 2 KV, Tmax), block hd.  q input rows are [H][q(hd) | gate(hd)].
+// grid (H + 2 KV, Tmax), block hd.  q input rows are [H][q(hd) | gate(hd)].  The cache keeps a value as two
+// fp16 numbers in two planes kv_plane halves apart, hi = fp16(x) and lo = fp16((x - hi) * 2048): the bytes
+// of the f32, in the form the attention kernel's tensor-core operands take.
+__device__ __forceinline__ void kv_put(__half *c, long long plane, size_t i, float x) {
+  const __half h = __float2half_rn(x);
+  c[i] = h;
+  c[plane + i] = __float2half_rn((x - __half2float(h)) * XP_LO_SCALE);
+}
 __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__ qn_w, const float *__restrict__ kn_w,
-                         const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, float *__restrict__ Kc,
-                         float *__restrict__ Vc, const RowSet *rs) {
+                         const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, __half *__restrict__ Kc,
+                         __half *__restrict__ Vc, const RowSet *rs) {
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   extern __shared__ float hv[];
@@ -171,12 +178,13 @@ __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__
   const int pos = rs_p0 + t, kvd = sh.KV * hd;
   if (b >= sh.H + sh.KV) {  // V row: copied
     const int g = b - sh.H - sh.KV;
-    Vc[(size_t)pos * kvd + g * hd + i] = part_get(v, (size_t)t * kvd + g * hd + i);
+    kv_put(Vc, sh.kv_plane, (size_t)pos * kvd + g * hd + i, part_get(v, (size_t)t * kvd + g * hd + i));
     return;
   }
   float x;
   const float *nw;
-  float *dst;
+  float *dst = nullptr;
+  size_t kdst = 0;
   if (b < sh.H) {
     x = part_get(q, (size_t)t * 2 * sh.H * hd + (size_t)b * 2 * hd + i);
     nw = qn_w;
@@ -185,7 +193,7 @@ __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__
     const int g = b - sh.H;
     x = part_get(k, (size_t)t * kvd + g * hd + i);
     nw = kn_w;
-    dst = Kc + (size_t)pos * kvd + g * hd;
+    kdst = (size_t)pos * kvd + g * hd;
   }
   const float ss = block_sum(x * x, red);
   const float sc = 1.0f / sqrtf(ss / (float)hd + sh.eps);
@@ -201,215 +209,14 @@ __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__
     const float a = hv[pi], bb = hv[pi + half];
     out = i < half ? __fsub_rn(__fmul_rn(a, c), __fmul_rn(bb, sn)) : __fadd_rn(__fmul_rn(a, sn), __fmul_rn(bb, c));
   }
-  dst[i] = out;
+  if (dst) dst[i] = out;
+  else kv_put(Kc, sh.kv_plane, kdst + i, out);
 }
 int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
               AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax) {
-  CU_OK(llb_launch(k_qkrope, dim3(sh.H + 2 * sh.KV, Tmax), dim3(sh.hd), (size_t)((size_t)sh.hd * 4), s, q, k, v, qn_w, kn_w, invfreq, sh, qout, Kc, Vc, rs));
+  CU_OK(llb_launch(k_qkrope, dim3(sh.H + 2 * sh.KV, Tmax), dim3(sh.hd), (size_t)((size_t)sh.hd * 4), s, q, k, v, qn_w, kn_w, invfreq, sh, qout,
+                   (__half *)Kc, (__half *)Vc, rs));
   CU_OK(cudaGetLastError());
-  return 0;
-}
-
-// ---- split-K GQA attention of the T query rows over the KV cache --------------------------------
-// (llb_t_attn4 computes one block per (head, row) with no split, tools/payload-spec2.patch:208-315;
-// the reference's own split-K form is llb_attn4_sk8, tools/payload-sk8add.patch:16-93.)
-// grid (KV, nsplit), 8 warps.  One block streams a slice of one kv head's K and V rows ONCE through
-// shared memory for all G = H/KV query heads x T rows; warp w owns queries w*QW .. w*QW+QW-1.
-// Output: per (query, split) a running max m, a sum l and an unnormalised accumulator o[hd].
-#define ATT_PT 32
-template <int HD, int QW>
-__global__ void __launch_bounds__(256) k_attn_part(const float *__restrict__ q, const float *__restrict__ Kc,
-                                                   const float *__restrict__ Vc, AttnShape sh, int Tmax, float *__restrict__ pm,
-                                                   float *__restrict__ pl, float *__restrict__ po, const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  extern __shared__ __align__(16) float sm[];
-  constexpr int KS = HD + 4, DPL = HD / 32;
-  const int G = sh.H / sh.KV, NQ = G * Tmax, nsplit = gridDim.y;
-  float *qs = sm;                         // [NQ][HD]
-  float *Ks = qs + (size_t)NQ * HD;       // [PT][HD + 4]
-  float *Vs = Ks + ATT_PT * KS;           // [PT][HD]
-  const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n = rs_n, pos0 = rs_p0, total = pos0 + n, kvd = sh.KV * HD;
-  // slices of whole 32-position tiles, at least min_per positions: short contexts use the first few blocks only
-  const int per = max(sh.min_per, ((total + nsplit - 1) / nsplit + 31) & ~31), s0 = split * per, s1 = min(total, s0 + per);
-  // query (g, r) -> local index g * Tmax + r; global head h = kvh * G + g
-  for (int i = threadIdx.x; i < NQ * HD; i += blockDim.x) {
-    int ql = i / HD, dd = i - ql * HD, g = ql / Tmax, r = ql - g * Tmax;
-    qs[i] = r < n ? q[((size_t)r * sh.H + kvh * G + g) * HD + dd] : 0.0f;
-  }
-  float m[QW], l[QW], acc[QW][DPL];
-#pragma unroll
-  for (int a = 0; a < QW; a++) {
-    m[a] = -INFINITY; l[a] = 0.0f;
-#pragma unroll
-    for (int i = 0; i < DPL; i++) acc[a][i] = 0.0f;
-  }
-  const float scale = 1.0f / sqrtf((float)HD);
-  for (int p0 = s0; p0 < s1; p0 += ATT_PT) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < ATT_PT * (HD / 4); i += blockDim.x) {
-      int pp = i / (HD / 4), c4 = i - pp * (HD / 4), p = p0 + pp;
-      float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
-      if (p < s1) {
-        kk = *(const float4 *)(Kc + (size_t)p * kvd + kvh * HD + 4 * c4);
-        vv = *(const float4 *)(Vc + (size_t)p * kvd + kvh * HD + 4 * c4);
-      }
-      *(float4 *)(Ks + pp * KS + 4 * c4) = kk;
-      *(float4 *)(Vs + pp * HD + 4 * c4) = vv;
-    }
-    __syncthreads();
-    float pr[QW];
-    bool any = false;
-#pragma unroll
-    for (int a = 0; a < QW; a++) {
-      const int ql = warp * QW + a;
-      pr[a] = 0.0f;
-      if (ql >= NQ) continue;
-      const int r = ql % Tmax;
-      if (r >= n) continue;
-      // lane <-> position p0 + lane
-      const float4 *kr = (const float4 *)(Ks + lane * KS);
-      const float4 *qr = (const float4 *)(qs + (size_t)ql * HD);
-      float sdot = 0.0f;
-#pragma unroll 8
-      for (int i = 0; i < HD / 4; i++) {
-        float4 kk = kr[i], qq = qr[i];
-        sdot += kk.x * qq.x + kk.y * qq.y + kk.z * qq.z + kk.w * qq.w;
-      }
-      const int p = p0 + lane;
-      float sc = (p < s1 && p <= pos0 + r) ? sdot * scale : -INFINITY;
-      const float mt = warp_max(sc);
-      if (mt == -INFINITY) continue;      // the whole tile is masked for this query
-      const float mn = fmaxf(m[a], mt);
-      const float corr = expf(m[a] - mn);  // exp(-inf) = 0 on the first tile
-      const float e = expf(sc - mn);
-      l[a] = l[a] * corr + warp_sum(e);
-      m[a] = mn;
-#pragma unroll
-      for (int i = 0; i < DPL; i++) acc[a][i] *= corr;
-      pr[a] = e;
-      any = true;
-    }
-    if (any) {
-      for (int pp = 0; pp < ATT_PT; pp++) {
-        float vv[DPL];
-#pragma unroll
-        for (int i = 0; i < DPL; i++) vv[i] = Vs[pp * HD + lane + 32 * i];
-#pragma unroll
-        for (int a = 0; a < QW; a++) {
-          const float e = __shfl_sync(0xffffffffu, pr[a], pp);
-#pragma unroll
-          for (int i = 0; i < DPL; i++) acc[a][i] += e * vv[i];
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int a = 0; a < QW; a++) {
-    const int ql = warp * QW + a;
-    if (ql >= NQ) continue;
-    const int g = ql / Tmax, r = ql - g * Tmax;
-    if (r >= n) continue;
-    const size_t qi = ((size_t)(kvh * G + g) * Tmax + r) * nsplit + split;
-    if (lane == 0) { pm[qi] = m[a]; pl[qi] = l[a]; }
-    if (m[a] == -INFINITY) continue;   // an empty slice: the merge skips it on m alone
-#pragma unroll
-    for (int i = 0; i < DPL; i++) po[qi * HD + lane + 32 * i] = acc[a][i];
-  }
-}
-
-// merge the splits, normalise, apply the sigmoid output gate, write the planes of attn_output's input
-// (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
-// block = (head, row); thread (sg, i4): split group sg of 4, dims 4*i4 .. 4*i4+3
-__global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
-                                                   AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  __shared__ float wsm[128];
-  __shared__ float red[32];
-  __shared__ __align__(16) float osm[1024];   // [split group][hd]
-  const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = sh.hd, lane = threadIdx.x & 31;
-  if (t >= rs_n) return;
-  const size_t qb = ((size_t)h * Tmax + t) * nsplit;
-  // slices in use at this context length (the partial kernel's split rule)
-  const int total = rs_p0 + rs_n;
-  const int per = max(sh.min_per, ((total + nsplit - 1) / nsplit + 31) & ~31), nact = min(nsplit, (total + per - 1) / per);
-  float m = -INFINITY, l = 0.0f;
-  if (i < nact) { m = pm[qb + i]; l = pl[qb + i]; }
-  float M = warp_max(m);
-  __syncthreads();
-  if (lane == 0) red[i >> 5] = M;
-  __syncthreads();
-  M = red[0];
-  for (int k = 1; k < (blockDim.x >> 5); k++) M = fmaxf(M, red[k]);
-  const float wgt = (i < nact && m != -INFINITY) ? expf(m - M) : 0.0f;
-  if (i < 128) wsm[i] = wgt;
-  const float L = block_sum(l * wgt, red);   // (block_sum synchronises: wsm is visible after it)
-  const int hd4 = hd >> 2, ng = blockDim.x / hd4, sg = i / hd4, i4 = i - sg * hd4;   // ng split groups of hd/4 threads
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (sg < ng) {
-    // split s = sg + ng*j: four loads in flight per trip, added in split order within the group
-    for (int s0 = sg; s0 < nact; s0 += 4 * ng) {
-      float4 v[4];
-      float ws[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int s = s0 + j * ng;
-        ws[j] = s < nact ? wsm[s] : 0.0f;
-        v[j] = ws[j] != 0.0f ? *(const float4 *)(po + (qb + s) * hd + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; j++) { o.x += v[j].x * ws[j]; o.y += v[j].y * ws[j]; o.z += v[j].z * ws[j]; o.w += v[j].w * ws[j]; }
-    }
-    *(float4 *)&osm[sg * hd + 4 * i4] = o;
-  }
-  __syncthreads();
-  if (i < hd4) {   // a multiple of 8 threads: eight lanes per 32 dims
-    float4 a = *(const float4 *)&osm[4 * i];
-    for (int g = 1; g < ng; g++) { const float4 b = *(const float4 *)&osm[g * hd + 4 * i]; a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
-    const float4 gate = part_get4(qg, (size_t)t * 2 * sh.H * hd + (size_t)h * 2 * hd + hd + 4 * i);
-    const float hv[4] = {(a.x / L) * sigmoid_f(gate.x), (a.y / L) * sigmoid_f(gate.y), (a.z / L) * sigmoid_f(gate.z), (a.w / L) * sigmoid_f(gate.w)};
-    xp_store4(xp, t, 2, h * hd + 4 * i, hv, lane, true);
-  }
-}
-
-template <int HD> static int attn_launch(cudaStream_t s, int QW, dim3 grid, size_t smem, const float *q, const float *Kc,
-                                         const float *Vc, AttnShape sh, int Tmax, float *pm, float *pl, float *po, const RowSet *rs) {
-#define ATT(Q) case Q: CU_OK(llb_launch(k_attn_part<HD, Q>, dim3(grid), dim3(256), (size_t)(smem), s, q, Kc, Vc, sh, Tmax, pm, pl, po, rs)); break;
-  switch (QW) { ATT(1) ATT(2) ATT(3) ATT(4) ATT(6) default: return llb_fail("attention: %d queries per warp", QW); }
-#undef ATT
-  CU_OK(cudaGetLastError());
-  return 0;
-}
-static size_t attn_smem(int hd, int NQ) { return ((size_t)NQ * hd + ATT_PT * (hd + 4) + ATT_PT * hd) * 4; }
-static int attn_qw(int NQ) { int q = (NQ + 7) / 8; return q == 5 ? 6 : q; }
-
-int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
-                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax) {
-  const int G = sh.H / sh.KV, NQ = G * Tmax, QW = attn_qw(NQ);
-  if (QW > 6) return llb_fail("attention: %d queries per kv head", NQ);
-  const size_t smem = attn_smem(sh.hd, NQ);
-  dim3 grid(sh.KV, nsplit);
-  int rc;
-  if (sh.hd == 128) rc = attn_launch<128>(s, QW, grid, smem, q, Kc, Vc, sh, Tmax, pm, pl, po, rs);
-  else if (sh.hd == 256) rc = attn_launch<256>(s, QW, grid, smem, q, Kc, Vc, sh, Tmax, pm, pl, po, rs);
-  else return llb_fail("attention: head_dim %d", sh.hd);
-  if (rc) return rc;
-  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(256), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs));
-  CU_OK(cudaGetLastError());
-  return 0;
-}
-
-template <int HD> static int attn_setup_hd() {
-  const int mx = (int)attn_smem(HD, 48);
-#define ATT(Q) CU_OK(cudaFuncSetAttribute(k_attn_part<HD, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, mx));
-  ATT(1) ATT(2) ATT(3) ATT(4) ATT(6)
-#undef ATT
-  return 0;
-}
-int ops_model_setup(void) {
-  if (attn_setup_hd<128>() || attn_setup_hd<256>()) return -1;
   return 0;
 }
 
