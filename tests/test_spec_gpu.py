@@ -178,3 +178,12 @@ def test_prompt_lookup_drafter(pkg, packs, oracle, llb, k):
         assert stats["rows"] < stats["cycles"] * (k + 1) or k == 1   # some cycles found fewer than k drafts
     finally:
         eng.close()
+
+
+def test_long_context_attention(pkg, packs, oracle, llb):
+    """A context of several hundred positions: many 32-position tiles and several context slices per kv head in the
+    attention kernel, prefill chunks on a warm cache, and the drafter's own KV at the same length."""
+    cfg = packs.cfg_tiny(n_layers=4, seed=33)
+    same, stats, st, eng, orc, ids = _run_case(pkg, packs, oracle, cfg, 3, 700, 16, seed=8)
+    eng.close()
+    assert same == 16
