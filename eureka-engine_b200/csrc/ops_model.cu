@@ -383,103 +383,90 @@ int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, Delta
 // llb_t_gdl + llb_t_grn (tools/payload-spec2.patch:319-447) and one launch per DeltaNet layer.
 // (Folding the conv in as well was measured and dropped: every block has to redo the conv of its whole
 // q/k group from the four partial-sum slices of the ring, 12x the loads, 65 us against 29 us for three kernels.)
-// 512 threads: sixteen per state row (eight columns each), so a row step is a chain of about 45 instructions per
-// thread with sixteen warps to hide it behind, instead of 170 in four warps.
-__global__ void __cluster_dims__(1, 4, 1) __launch_bounds__(512)
+__global__ void __cluster_dims__(1, 4, 1) __launch_bounds__(128)
 k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const float *__restrict__ y, const float *__restrict__ beta,
               const float *__restrict__ decay, PartIn z, const float *__restrict__ nw, DeltaShape sh, XPlanes xp,
               const RowSet *rs) {
   __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
   __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2], os[SPEC_MAXT][32], ssq[SPEC_MAXT], tot[SPEC_MAXT];
   __shared__ float red[2 * SPEC_MAXT][4];
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
   cg::cluster_group cl = cg::this_cluster();
-  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
-  const int jr = tid >> 4, cq = tid & 15;
-  const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
-  // thread (jr, cq) holds columns 4 cq .. 4 cq + 3 and 64 + 4 cq .. of state row 32 jq + jr: the sixteen threads of
-  // a row read 256 contiguous bytes twice, and their k / q reads from shared memory are consecutive float4
-  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 4 * cq;
-  // The committed state was written by the previous cycle and the ring index by its accept kernel: when the row
-  // set is marked stable both may be read ahead of the wait, so the state's trip to DRAM overlaps the producer.
-  pdl_trigger();
-  const bool early = ((uintptr_t)rs & 1u) != 0;
-  rs = (const RowSet *)((uintptr_t)rs & ~(uintptr_t)1);
-  int n = 0, sc = 0, R = 1;
-  float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-  if (early) {
-    n = *(const volatile int *)&rs->n; sc = *(const volatile int *)&ctl->sc; R = *(const volatile int *)&ctl->R;
-    const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
-    v0 = __ldcg(src); v1 = __ldcg(src + 16);
-  }
-  pdl_wait();
-  if (!early) {
-    n = rs->n; sc = ctl->sc; R = ctl->R;
-    const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
-    v0 = src[0]; v1 = src[16];
-  }
+  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs_n, lane = tid & 31, wp = tid >> 5;
   if (n < 1) return;   // every block of every cluster takes the same exit
-  const int g = hh % sh.GK;   // value head hh reads q/k group hh % GK (tile, tools/qwen35_engine.c:621-626)
-  float st[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-  // q / k of the head's group: thread (tg, ch) takes channel ch of rows tg and tg + 4
-  const int tg = tid >> 7, ch = tid & 127;
-  float qv[2], kv[2];
+  const int g = hh % sh.GK;
+  const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
+  const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
+  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 4 * cq;
+  float st[32];
+  {
+    const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
 #pragma unroll
-  for (int i = 0; i < 2; i++) {
-    const int t = tg + 4 * i;
-    qv[i] = t < n ? y[(size_t)t * sh.convd + g * 128 + ch] : 0.0f;
-    kv[i] = t < n ? y[(size_t)t * sh.convd + sh.kdc + g * 128 + ch] : 0.0f;
+    for (int i = 0; i < 8; i++) { float4 v = src[4 * i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
   }
-  if (tid < 32 * SPEC_MAXT && (tid >> 5) < n) vs[tid >> 5][lane] = y[(size_t)(tid >> 5) * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + lane];
-  if (tid < 2 * SPEC_MAXT && (tid >> 1) < n) db[tid >> 1][tid & 1] = (tid & 1) ? beta[(tid >> 1) * sh.TR + hh] : decay[(tid >> 1) * sh.TR + hh];
-  // what the gated norm at the end needs from memory, fetched now
-  const float zpre = wp < n ? part_get(z, (size_t)wp * sh.vdc + hh * 128 + 32 * jq + lane) : 0.0f;
-  const float nwv = nw[32 * jq + lane];
+  float qv[SPEC_MAXT], kv[SPEC_MAXT];
 #pragma unroll
-  for (int i = 0; i < 2; i++) {
-    const int t = tg + 4 * i;
-    const float a = warp_sum(qv[i] * qv[i]), b = warp_sum(kv[i] * kv[i]);
-    if (lane == 0) { red[2 * t][wp & 3] = a; red[2 * t + 1][wp & 3] = b; }
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    qv[t] = t < n ? y[(size_t)t * sh.convd + g * 128 + tid] : 0.0f;
+    kv[t] = t < n ? y[(size_t)t * sh.convd + sh.kdc + g * 128 + tid] : 0.0f;
+  }
+  if (tid < 32) {
+#pragma unroll
+    for (int t = 0; t < SPEC_MAXT; t++) if (t < n) vs[t][tid] = y[(size_t)t * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + tid];
+  }
+  if (tid < 2 * SPEC_MAXT && (tid >> 1) < n) db[tid >> 1][tid & 1] = (tid & 1) ? beta[(tid >> 1) * sh.TR + hh] : decay[(tid >> 1) * sh.TR + hh];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    const float a = warp_sum(qv[t] * qv[t]), b = warp_sum(kv[t] * kv[t]);
+    if (lane == 0) { red[2 * t][wp] = a; red[2 * t + 1][wp] = b; }
   }
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < 2; i++) {
-    const int t = tg + 4 * i;
+  for (int t = 0; t < SPEC_MAXT; t++) {
     if (t < n) {
       const float sq = red[2 * t][0] + red[2 * t][1] + red[2 * t][2] + red[2 * t][3];
       const float sk = red[2 * t + 1][0] + red[2 * t + 1][1] + red[2 * t + 1][2] + red[2 * t + 1][3];
       const float nq = sqrtf(sq), nk = sqrtf(sk);
       const float iq = (1.0f / (nq > sh.eps ? nq : sh.eps)) / sqrtf(128.0f), ik = 1.0f / (nk > sh.eps ? nk : sh.eps);
-      qs[t][ch] = qv[i] * iq;
-      ks[t][ch] = kv[i] * ik;
+      qs[t][tid] = qv[t] * iq;
+      ks[t][tid] = kv[t] * ik;
     }
   }
   __syncthreads();
   for (int t = 0; t < n; t++) {
     const float dec = db[t][0], bt = db[t][1];
-    const float4 k0 = *(const float4 *)&ks[t][4 * cq], k1 = *(const float4 *)&ks[t][64 + 4 * cq];
-    const float kq[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-    float ka0 = 0.0f, ka1 = 0.0f;
+    float kq[32];
 #pragma unroll
-    for (int i = 0; i < 4; i++) { st[i] *= dec; ka0 += st[i] * kq[i]; st[4 + i] *= dec; ka1 += st[4 + i] * kq[4 + i]; }
-    float kvacc = ka0 + ka1;
+    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&ks[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
+    float ka[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int m = 1; m < 16; m <<= 1) kvacc += __shfl_xor_sync(0xffffffffu, kvacc, m);
+    for (int i = 0; i < 32; i++) { st[i] *= dec; ka[i & 3] += st[i] * kq[i]; }
+    float kvacc = (ka[0] + ka[1]) + (ka[2] + ka[3]);
+    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 1);
+    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 2);
     const float delta = (vs[t][jr] - kvacc) * bt;
 #pragma unroll
-    for (int i = 0; i < 8; i++) st[i] += kq[i] * delta;
-    const float4 q0 = *(const float4 *)&qs[t][4 * cq], q1 = *(const float4 *)&qs[t][64 + 4 * cq];
-    float oacc = (st[0] * q0.x + st[1] * q0.y) + (st[2] * q0.z + st[3] * q0.w) + ((st[4] * q1.x + st[5] * q1.y) + (st[6] * q1.z + st[7] * q1.w));
+    for (int i = 0; i < 32; i++) st[i] += kq[i] * delta;
 #pragma unroll
-    for (int m = 1; m < 16; m <<= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, m);
+    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&qs[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
+    float oa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i++) oa[i & 3] += st[i] * kq[i];
+    float oacc = (oa[0] + oa[1]) + (oa[2] + oa[3]);
+    oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
+    oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
     if (cq == 0) os[t][jr] = oacc;
     float4 *dst = (float4 *)(S + (size_t)((sc + t + 1) % R) * slot_sz + off);
-    dst[0] = make_float4(st[0], st[1], st[2], st[3]);
-    dst[16] = make_float4(st[4], st[5], st[6], st[7]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) dst[4 * i] = make_float4(st[4 * i], st[4 * i + 1], st[4 * i + 2], st[4 * i + 3]);
   }
   __syncthreads();
-  if (wp < n) {   // warp t: the block's part of row t's sum of squares
-    const float v = os[wp][lane], s2 = warp_sum(v * v);
-    if (lane == 0) ssq[wp] = s2;
+  if (wp == 0) {
+    for (int t = 0; t < n; t++) {
+      const float v = os[t][lane], s2 = warp_sum(v * v);
+      if (lane == 0) ssq[t] = s2;
+    }
   }
   cl.sync();                                   // every block's partial sums of squares are in place
   if (tid < n) {
@@ -488,15 +475,17 @@ k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const floa
     tot[tid] = s2;
   }
   cl.sync();                                   // nobody leaves while a peer still reads its shared memory
-  if (wp < n) {
-    const float r = 1.0f / sqrtf(tot[wp] / 128.0f + sh.eps);
-    xp_store32(xp, wp, 2, hh * 128 + 32 * jq, os[wp][lane] * r * nwv * silu_f(zpre), lane);
+  for (int t = wp; t < n; t += 4) {
+    const float r = 1.0f / sqrtf(tot[t] / 128.0f + sh.eps);
+    const int col = hh * 128 + 32 * jq;
+    const float zz = part_get(z, (size_t)t * sh.vdc + col + lane);
+    xp_store32(xp, t, 2, col, os[t][lane] * r * nw[32 * jq + lane] * silu_f(zz), lane);
   }
 }
 int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,
                    const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs) {
   if (sh.SZ != 128) return llb_fail("DeltaNet state size %d (only 128, as host/llb_host.c:1608)", sh.SZ);
-  CU_OK(llb_launch(k_delta_fused, dim3(sh.TR, 4), dim3(512), (size_t)0, s, S, ctl, y, beta, decay, z, nw, sh, xp, rs));
+  CU_OK(llb_launch(k_delta_fused, dim3(sh.TR, 4), dim3(128), (size_t)0, s, S, ctl, y, beta, decay, z, nw, sh, xp, rs));
   return 0;
 }
 
