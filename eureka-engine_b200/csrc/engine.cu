@@ -65,7 +65,7 @@ struct llb_spec {
   XPlanes xp_d, xp_f, xp_qa, xp_v, xp_2d;
   OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg, b_ring;
   int att_split = 1;
-  int att_min = 64;                   // fewest positions per attention block
+  int att_min = 96;                   // fewest positions per attention block (three 32-position tiles)
   // Measured on the 27B shape: letting the last writer of a tile add the K-slices costs the GEMM's tail more
   // (fence, atomic, a dependent round of loads) than it saves the consumers, so it is off by default.
   bool reduce_in_gemm = false;
@@ -527,7 +527,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   m->qn = falloc(m, (size_t)T * qa); m->y = falloc(m, (size_t)T * big); m->beta = falloc(m, (size_t)T * m->TR); m->decay = falloc(m, (size_t)T * m->TR);
   m->o = falloc(m, (size_t)T * m->vdc); m->t2part = falloc(m, (size_t)2 * SPEC_MAXT * TOP2_NB * 4);
   m->mt_x = falloc(m, (size_t)T * d); m->mt_hn = falloc(m, (size_t)T * d); m->chain_h = falloc(m, d);
-  m->att_split = (2 * g_llb.sms) / m->KV;
+  m->att_split = g_llb.sms / m->KV;   // one wave of blocks: the kernel takes a whole SM's shared memory
   { const char *e = getenv("LLB_ATT_SPLIT"); if (e && atoi(e) > 0) m->att_split = atoi(e); }
   { const char *e = getenv("LLB_ATT_MIN"); if (e && atoi(e) >= 32) m->att_min = atoi(e) & ~31; }
   if (m->att_split < 1) m->att_split = 1;
