@@ -95,8 +95,10 @@ __device__ __forceinline__ void quarter_sync(int q) { asm volatile("bar.sync %0,
 __device__ __forceinline__ bool mbar_wait(uint32_t bar_s, uint32_t parity) {
   for (uint32_t it = 0; it < G3_WAIT_LIMIT; it++) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(ok) : "r"(bar_s), "r"(parity) : "memory");
+    // the hint lets the hardware park the thread until the phase completes (or about a microsecond passes)
+    // instead of polling: sixteen worker warps and four issuing warps otherwise spend most issue slots on polls
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(bar_s), "r"(parity), "r"(1000u) : "memory");
     if (ok) return true;
   }
   return false;

@@ -2,6 +2,7 @@
 """Small, self-ending cases to run under ncu (one GPU).
 
     python eureka-engine_b200/profile_cases.py gemm FMT ROWS[,ROWS..] K     three launches of one GEMM site
+    python eureka-engine_b200/profile_cases.py gemm3 ROWS[,ROWS..] K        the same for Q4_K on the tcgen05 kernel
     python eureka-engine_b200/profile_cases.py verify LAYERS [PROMPT]       two replays of the verify pass of the
                                                                             27B-shape model truncated to LAYERS,
                                                                             bracketed by cudaProfilerStart/Stop
@@ -16,11 +17,12 @@ import torch  # noqa: E402
 import __graft_entry__ as graft  # noqa: E402
 
 
-def case_gemm(fmt_name, rows_list, K, T=4):
+def case_gemm(fmt_name, rows_list, K, T=4, tcgen05=False):
     pkg = graft.load_package()
     llb, packs = pkg.llb, pkg.packs
     llb.init(0)
     L = llb.lib()
+    L.llb_b200_use_tcgen05(1 if tcgen05 else 0)
     dev = torch.device("cuda:0")
     fmt = packs.FMT[fmt_name]
     raws = [packs.q4k_random_blocks(r, K, seed=2, device=dev) if fmt_name == "Q4_K"
@@ -40,7 +42,7 @@ def case_gemm(fmt_name, rows_list, K, T=4):
     for ws in sets:
         llb.gemm(fmt, ws, rows_list, [y.data_ptr() for y in ys], K, xp, 0)
     L.llb_sync()
-    print("ok", float(ys[0].abs().max()))
+    print("ok", float(ys[0].abs().max()), "wait errors", L.llb_b200_wait_errors())
 
 
 def case_verify(layers, nprompt=3011):
@@ -68,6 +70,8 @@ def case_verify(layers, nprompt=3011):
 if __name__ == "__main__":
     if sys.argv[1] == "gemm":
         case_gemm(sys.argv[2], [int(v) for v in sys.argv[3].split(",")], int(sys.argv[4]))
+    elif sys.argv[1] == "gemm3":
+        case_gemm("Q4_K", [int(v) for v in sys.argv[2].split(",")], int(sys.argv[3]), tcgen05=True)
     elif sys.argv[1] == "verify":
         case_verify(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3011)
     else:
