@@ -21,10 +21,9 @@ template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs 
   const int NC = 8 * NT, nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
   int cps = g_llb.sms * G2_CPSM / a.ksplit;
   if (cps < 1) cps = 1;
-  // no more CTAs per slice than there are 16-tile groups to hand out
+  // every SM takes part as long as there is a tile for it: the tiles are dealt out one per CTA in turn
   constexpr int G2_WARPS = G2Traits<FMT>::WARPS;
-  const int need = (a.tile0[a.nmat] + G2_WARPS - 1) / G2_WARPS;
-  if (cps > need) cps = need;
+  if (cps > a.tile0[a.nmat]) cps = a.tile0[a.nmat];
   const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
   if (smem > G2_SMEM_MAX) return llb_fail("k_gemm2: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
   cudaError_t e = llb_launch(k_gemm2<FMT, NT>, dim3(cps * a.ksplit), dim3(G2_WARPS * 32), smem, s, a, cps);

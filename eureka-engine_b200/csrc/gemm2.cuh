@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
     row_of[it] = r; pc_of[it] = p * 16; dst_rel[it] = i < 16 * P ? r * RS + p * 16 : 0xffffffffu;
   }
   // producer cursor
-  int p_tile = ci * G2_WARPS + warp, p_c = 0;
+  // tile of (CTA ci, warp w, round n) = (n * WARPS + w) * cps + ci: consecutive tiles go to different SMs, so the
+  // SMs' tile counts differ by one at most (the kernel is issue-bound per SM: time follows the fullest SM)
+  int p_tile = warp * cps + ci, p_c = 0;
   const uint8_t *p_W = nullptr;
   uint32_t p_off[NIT];
   auto plan_tile = [&](int tile) {
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
   // the XP group sits between prologue groups and later ones; from here on group accounting is per
   // warp again: G2_STAGES-1 chunks are complete, none pending
   int pstage = G2_STAGES - 1, cstage = 0;
-  int c_tile = ci * G2_WARPS + warp, c_c = 0;
+  int c_tile = warp * cps + ci, c_c = 0;
   float acc[NT][4];
   const uint8_t *xb = xh_s + gid * CS + 16 * j;          // B fragments of column gid (n-tile 0)
   const uint8_t *xfb = xsf_s + gid * 32 + 8 * j;
