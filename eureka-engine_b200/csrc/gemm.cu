@@ -3,14 +3,17 @@
 #include "gemm3.cuh"
 #include "host.cuh"
 
-static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K; }
+static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K || (fmt == LLB_FM_Q8_0 && !g_llb.q8_v1); }
 static int g2_max_sb(int fmt, int NC) {
-  return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC) : g2_max_slice_sb<LLB_FM_Q6_K>(NC);
+  return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC)
+       : fmt == LLB_FM_Q8_0 ? g2_max_slice_sb<LLB_FM_Q8_0>(NC) : g2_max_slice_sb<LLB_FM_Q6_K>(NC);
 }
 // the tcgen05 kernel takes Q4_K with T <= 4 (8 plane columns)
 static bool is_g3(int fmt, int NC) { return g_llb.gemm3 && fmt == LLB_FM_Q4_K && NC == 8; }
 static unsigned int *g_g3_err = nullptr;   // device word: set when a bounded wait of k_gemm3 ran out
-static int g2_warps(int fmt) { return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS; }
+static int g2_warps(int fmt) {
+  return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : fmt == LLB_FM_Q8_0 ? (int)G2Traits<LLB_FM_Q8_0>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS;
+}
 
 template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs &a, int grid) {
   cudaError_t e = llb_launch(k_gemm<FMT, NT>, dim3(grid), dim3(GEMM_WARPS * 32), (size_t)gemm_smem_bytes<FMT>(), s, a);
@@ -64,7 +67,7 @@ template <int FMT> static int setup_fmt2() {
 
 int gemm_setup(void) {
   if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
-  if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>()) return -1;
+  if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>() || setup_fmt2<LLB_FM_Q8_0>()) return -1;
   CU_OK(cudaFuncSetAttribute(k_gemm3, cudaFuncAttributeMaxDynamicSharedMemorySize, G3_SMEM_MAX));
   if (!g_g3_err) {
     CU_OK(cudaMalloc(&g_g3_err, 4));
@@ -135,6 +138,7 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : launch_two<LLB_FM_Q4_K, 2>(s, a);
   if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : launch_two<LLB_FM_Q5_K, 2>(s, a);
   if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_two<LLB_FM_Q6_K, 1>(s, a) : launch_two<LLB_FM_Q6_K, 2>(s, a);
+  if (fmt == LLB_FM_Q8_0 && !g_llb.q8_v1) return NT == 1 ? launch_two<LLB_FM_Q8_0, 1>(s, a) : launch_two<LLB_FM_Q8_0, 2>(s, a);
   const int nunits = a.tile0[a.nmat] * a.ksplit;
   int grid = (nunits + GEMM_WARPS - 1) / GEMM_WARPS;
   if (grid > g_llb.sms) grid = g_llb.sms;

@@ -36,6 +36,9 @@ template <int FMT> struct G2Traits;
 template <> struct G2Traits<LLB_FM_Q4_K> { enum { SB = 144, RS = 160, P = 9, QOFF = 16, WARPS = 16 / G2_CPSM, XPAD = 64, AUX = 32 }; };
 template <> struct G2Traits<LLB_FM_Q5_K> { enum { SB = 176, RS = 224, P = 11, QOFF = 48, WARPS = 16 / G2_CPSM, XPAD = 64, AUX = 32 }; };
 template <> struct G2Traits<LLB_FM_Q6_K> { enum { SB = 224, RS = 240, P = 14, QOFF = 0, WARPS = 12 / G2_CPSM, XPAD = 32, AUX = 64 }; };
+// Q8_0 rows are [K x int8][K/32 x f16]: a "super-block" here is 256 codes plus their 8 scales, which sit K - 256 sb + 16 sb
+// bytes further on in the row; piece 16 of a row-super-block is that scale piece (copy plan below).  AUX: 8 f32 sums of 32 columns.
+template <> struct G2Traits<LLB_FM_Q8_0> { enum { SB = 256, RS = 304, P = 17, QOFF = 0, WARPS = 8 / G2_CPSM, XPAD = 32, AUX = 32 }; };
 
 template <int FMT> constexpr int g2_ring_bytes() { return G2Traits<FMT>::WARPS * G2_STAGES * 16 * G2Traits<FMT>::RS; }
 // bytes of shared memory a K-slice of nsl super-blocks needs for NC activation columns
@@ -70,23 +73,29 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
 
   // per-lane copy plan: piece i = lane + 32*it of the 16 x P sixteen-byte pieces of a stage
   uint32_t dst_rel[NIT], row_of[NIT], pc_of[NIT];
+  bool is_sc[NIT];
 #pragma unroll
   for (int it = 0; it < NIT; it++) {
+    is_sc[it] = false;
     const int i = lane + 32 * it, r = i / P, p = i - r * P;
     row_of[it] = r; pc_of[it] = p * 16; dst_rel[it] = i < 16 * P ? r * RS + p * 16 : 0xffffffffu;
+    // Q8_0: the scale piece comes from the row's scale area (K bytes into the row) and advances 16 bytes per
+    // super-block, not 256; its source is taken from the row start, not from the slice's first code
+    if (FMT == LLB_FM_Q8_0 && p == P - 1) { pc_of[it] = (uint32_t)a.K + (uint32_t)sb0 * 16; is_sc[it] = true; }
   }
   // producer cursor
   // tile of (CTA ci, warp w, round n) = (n * WARPS + w) * cps + ci: consecutive tiles go to different SMs, so the
   // SMs' tile counts differ by one at most (the kernel is issue-bound per SM: time follows the fullest SM)
   int p_tile = warp * cps + ci, p_c = 0;
-  const uint8_t *p_W = nullptr;
+  const uint8_t *p_W = nullptr, *p_W0 = nullptr;   // first code of the slice in row 0 of the matrix; the matrix itself
   uint32_t p_off[NIT];
   auto plan_tile = [&](int tile) {
     if (tile >= ntiles) return;
     int m = 0;
     while (m + 1 < a.nmat && tile >= a.tile0[m + 1]) m++;
     const int row0 = (tile - a.tile0[m]) * 16, rows = a.m[m].rows;
-    p_W = a.m[m].W + (size_t)sb0 * SB;
+    p_W0 = a.m[m].W;
+    p_W = p_W0 + (size_t)sb0 * SB;
 #pragma unroll
     for (int it = 0; it < NIT; it++) p_off[it] = (uint32_t)min(row0 + (int)row_of[it], rows - 1) * (uint32_t)rb + pc_of[it];
   };
@@ -96,7 +105,10 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
       const uint32_t dst = ring_s + stage * 16 * RS;
 #pragma unroll
       for (int it = 0; it < NIT; it++)
-        if (dst_rel[it] != 0xffffffffu) cp_async16(dst + dst_rel[it], src + p_off[it]);
+        if (dst_rel[it] != 0xffffffffu) {
+          if (FMT == LLB_FM_Q8_0 && is_sc[it]) cp_async16(dst + dst_rel[it], p_W0 + (size_t)p_c * 16 + p_off[it]);
+          else cp_async16(dst + dst_rel[it], src + p_off[it]);
+        }
       if (++p_c == nsl) { p_c = 0; p_tile += nws; plan_tile(p_tile); }
     }
     cp_async_commit();
@@ -115,7 +127,9 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
       cp_async16(smem_u32(xh_s + c * CS + p * 16), (const uint8_t *)(a.xp.xh + (size_t)c * a.K + (size_t)sb0 * 256) + p * 16);
     }
     // the side array of the slice: contiguous in global memory for both kinds
-    const uint8_t *xf = FMT == LLB_FM_Q6_K ? (const uint8_t *)(a.xp.xs16 + (size_t)sb0 * 16 * NC) : (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
+    const uint8_t *xf = FMT == LLB_FM_Q6_K   ? (const uint8_t *)(a.xp.xs16 + (size_t)sb0 * 16 * NC)
+                        : FMT == LLB_FM_Q8_0 ? (const uint8_t *)(a.xp.xs32 + (size_t)sb0 * 8 * NC)
+                                             : (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
     for (int i = threadIdx.x; i < nsl * NC * (TR::AUX / 16); i += blockDim.x) cp_async16(smem_u32(xsf_s + i * 16), xf + i * 16);
     cp_async_commit();
     cp_async_wait<0>();
@@ -139,7 +153,41 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
     pstage = pstage + 1 == G2_STAGES ? 0 : pstage + 1;
     cp_async_wait<G2_STAGES - 1>();      // all but the newest G2_STAGES-1 groups: the stage to consume is in
     __syncwarp();
-    if constexpr (FMT == LLB_FM_Q6_K) {
+    if constexpr (FMT == LLB_FM_Q8_0) {
+      // eight blocks of 32 codes per super-block, two MMAs each; code (q ^ 0x80) = q + 128 as an fp16 subnormal,
+      // the offset taken back through the 32-column sums: d * (2^24 P - 128 sum x)
+      const uint8_t *b0 = ring + cstage * 16 * RS + gid * RS, *b1 = b0 + 8 * RS;
+      const uint4 sw0 = *(const uint4 *)(b0 + 256), sw1 = *(const uint4 *)(b1 + 256);
+      const uint32_t d0w[4] = {sw0.x, sw0.y, sw0.z, sw0.w}, d1w[4] = {sw1.x, sw1.y, sw1.z, sw1.w};
+      const uint8_t *xb8 = xh_s + gid * CS + 8 * j + (size_t)c_c * 512;
+      const float *xs8 = (const float *)xsf_s + (size_t)c_c * 8 * NC + 2 * j;
+#pragma unroll
+      for (int blk = 0; blk < 8; blk++) {
+        float p[NT][4];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int m = 2 * blk + u;
+          const uint32_t w0 = *(const uint32_t *)(b0 + 16 * m + 4 * j) ^ 0x80808080u, w1 = *(const uint32_t *)(b1 + 16 * m + 4 * j) ^ 0x80808080u;
+          const uint32_t a0 = __byte_perm(w0, 0, 0x4240), a2 = __byte_perm(w0, 0, 0x4341);
+          const uint32_t a1 = __byte_perm(w1, 0, 0x4240), a3 = __byte_perm(w1, 0, 0x4341);
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            const uint2 bx = *(const uint2 *)(xb8 + (size_t)nt * 8 * CS + 32 * m);
+            if (u == 0) mma16816_z(p[nt], a0, a1, a2, a3, bx.x, bx.y);
+            else mma16816(p[nt], a0, a1, a2, a3, bx.x, bx.y);
+          }
+        }
+        const float d0 = h2f_bits((d0w[blk >> 1] >> (16 * (blk & 1))) & 0xffffu), d1 = h2f_bits((d1w[blk >> 1] >> (16 * (blk & 1))) & 0xffffu);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const float2 xs = *(const float2 *)(xs8 + (size_t)blk * NC + nt * 8);
+          acc[nt][0] += d0 * (p[nt][0] * TWO24 - 128.0f * xs.x);
+          acc[nt][1] += d0 * (p[nt][1] * TWO24 - 128.0f * xs.y);
+          acc[nt][2] += d1 * (p[nt][2] * TWO24 - 128.0f * xs.x);
+          acc[nt][3] += d1 * (p[nt][3] * TWO24 - 128.0f * xs.y);
+        }
+      }
+    } else if constexpr (FMT == LLB_FM_Q6_K) {
       // 16 scale groups of 16 columns per super-block, one MMA each; code 0..63 as fp16 subnormals
       // (quarters 2, 3 carry the code shifted left by 4), offset -32 through the 16-column sums
       const uint8_t *b0 = ring + cstage * 16 * RS + gid * RS, *b1 = b0 + 8 * RS;

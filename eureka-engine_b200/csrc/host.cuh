@@ -11,6 +11,7 @@
 struct LlbCtx {
   int device = -1;
   int sms = 0;
+  int q8_v1 = 0;   // Q8_0 on the first-generation kernel (LLB_Q8_V1=1)
   int gemm3 = 0;   // Q4_K, T <= 4 on the tcgen05 kernel (LLB_GEMM3=1)
   int pdl = 1;     // programmatic dependent launch on every kernel of a pass (LLB_PDL=0 turns it off)
   cudaStream_t stream = nullptr;
