@@ -35,7 +35,7 @@
 template <int FMT> struct G2Traits;
 template <> struct G2Traits<LLB_FM_Q4_K> { enum { SB = 144, RS = 160, P = 9, QOFF = 16, WARPS = 16 / G2_CPSM, XPAD = 64, AUX = 32 }; };
 template <> struct G2Traits<LLB_FM_Q5_K> { enum { SB = 176, RS = 224, P = 11, QOFF = 48, WARPS = 16 / G2_CPSM, XPAD = 64, AUX = 32 }; };
-template <> struct G2Traits<LLB_FM_Q6_K> { enum { SB = 224, RS = 240, P = 14, QOFF = 0, WARPS = 12 / G2_CPSM, XPAD = 32, AUX = 64 }; };
+template <> struct G2Traits<LLB_FM_Q6_K> { enum { SB = 224, RS = 240, P = 14, QOFF = 0, WARPS = 16 / G2_CPSM, XPAD = 32, AUX = 64 }; };
 // Q8_0 rows are [K x int8][K/32 x f16]: a "super-block" here is 256 codes plus their 8 scales, which sit K - 256 sb + 16 sb
 // bytes further on in the row; piece 16 of a row-super-block is that scale piece (copy plan below).  AUX: 8 f32 sums of 32 columns.
 template <> struct G2Traits<LLB_FM_Q8_0> { enum { SB = 256, RS = 304, P = 17, QOFF = 0, WARPS = 8 / G2_CPSM, XPAD = 32, AUX = 32 }; };
