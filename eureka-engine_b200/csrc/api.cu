@@ -32,6 +32,7 @@ int llb_b200_init(int device) {
   { const char *e = getenv("LLB_PDL"); g_llb.pdl = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM3"); g_llb.gemm3 = e && e[0] == '1'; }
   { const char *e = getenv("LLB_Q8_V1"); g_llb.q8_v1 = e && e[0] == '1'; }
+  { const char *e = getenv("LLB_FFN_FUSED"); g_llb.ffn_fused = e && e[0] == '1'; }
   g_llb.sms = pr.multiProcessorCount;
   // a blocking stream: ordered after work a caller queued on the legacy default stream (torch's), so
   // device buffers produced there can be handed in without an explicit synchronisation

@@ -277,6 +277,21 @@ static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const Row
 static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
   PK("norm post", op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
+  if (w.gate.fmt == w.up.fmt && gemm_ffn_fusable(w.gate.fmt, w.down.fmt, m->NC, m->d) && !m->reduce_in_gemm) {
+    // one launch: gate|up in one K-slice, a grid barrier, silu(gate) * up built in shared memory, down
+    GemmArgs a1, a2;
+    memset(&a1, 0, sizeof a1); memset(&a2, 0, sizeof a2);
+    a1.K = m->d; a1.xp = m->xp_d; a1.planes = 2; a1.T = m->Tmax; a1.nmat = 2; a1.ksplit = 1;
+    CK(out_prepare(m, m->b_g, w.gate.rows, 1)); CK(out_prepare(m, m->b_u, w.up.rows, 1));
+    a1.m[0].W = w.gate.w; a1.m[0].rows = w.gate.rows; a1.m[0].out = m->b_g.p; a1.m[0].ostride = w.gate.rows; a1.m[0].split_stride = m->b_g.stride;
+    a1.m[1].W = w.up.w; a1.m[1].rows = w.up.rows; a1.m[1].out = m->b_u.p; a1.m[1].ostride = w.up.rows; a1.m[1].split_stride = m->b_u.stride;
+    const int ks2 = gemm_fix_ksplit(w.down.fmt, m->NC, m->f / 256, gemm_pick_ksplit(w.down.fmt, m->NC, (w.down.rows + 15) / 16, m->f / 256, g_llb.sms));
+    a2.K = m->f; a2.xp = m->xp_f; a2.planes = 2; a2.T = m->Tmax; a2.nmat = 1; a2.ksplit = ks2;
+    CK(out_prepare(m, m->b_dn, w.down.rows, ks2));
+    a2.m[0].W = w.down.w; a2.m[0].rows = w.down.rows; a2.m[0].out = m->b_dn.p; a2.m[0].ostride = w.down.rows; a2.m[0].split_stride = m->b_dn.stride;
+    PK("ffn fused", gemm_launch_ffn(s, a1, w.down.fmt, a2));
+    return 0;
+  }
   PK("gemm gate|up", site_gemm(m, {{&w.gate, &m->b_g, nullptr, nullptr, 0}, {&w.up, &m->b_u, nullptr, nullptr, 0}}, m->xp_d, 0));
   PK("silu", op_silu_xp(s, as_in(m->b_g), as_in(m->b_u), m->f, m->xp_f, rs, m->Tmax));
   PK("gemm down", site_gemm(m, {{&w.down, &m->b_dn, nullptr, nullptr, 0}}, m->xp_f, 0));

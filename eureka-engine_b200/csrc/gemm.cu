@@ -1,6 +1,7 @@
 // gemm.cu -- host side of the dequant-fused skinny GEMMs (kernels in gemm.cuh and gemm2.cuh).
 #include "gemm2.cuh"
 #include "gemm3.cuh"
+#include "ffn_fused.cuh"
 #include "host.cuh"
 
 static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K || (fmt == LLB_FM_Q8_0 && !g_llb.q8_v1); }
@@ -10,6 +11,7 @@ static int g2_max_sb(int fmt, int NC) {
 }
 // the tcgen05 kernel takes Q4_K with T <= 4 (8 plane columns)
 static bool is_g3(int fmt, int NC) { return g_llb.gemm3 && fmt == LLB_FM_Q4_K && NC == 8; }
+static unsigned int *g_ffn_sync = nullptr;   // the fused FFN's grid barrier: two counters
 static unsigned int *g_g3_err = nullptr;   // device word: set when a bounded wait of k_gemm3 ran out
 static int g2_warps(int fmt) {
   return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : fmt == LLB_FM_Q8_0 ? (int)G2Traits<LLB_FM_Q8_0>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS;
@@ -69,6 +71,13 @@ int gemm_setup(void) {
   if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
   if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>() || setup_fmt2<LLB_FM_Q8_0>()) return -1;
   CU_OK(cudaFuncSetAttribute(k_gemm3, cudaFuncAttributeMaxDynamicSharedMemorySize, G3_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_ffn<LLB_FM_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_ffn<LLB_FM_Q5_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_ffn<LLB_FM_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  if (!g_ffn_sync) {
+    CU_OK(cudaMalloc(&g_ffn_sync, 8));
+    CU_OK(cudaMemset(g_ffn_sync, 0, 8));
+  }
   if (!g_g3_err) {
     CU_OK(cudaMalloc(&g_g3_err, 4));
     CU_OK(cudaMemset(g_g3_err, 0, 4));
@@ -122,7 +131,8 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
   return gemm_fix_ksplit(fmt, NC, nsb, best);
 }
 
-int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
+// fills nsb and the tile table of a launch and checks its shape
+static int gemm_prepare(int fmt, GemmArgs &a) {
   if (a.nmat < 1 || a.nmat > GEMM_MAXMAT) return llb_fail("gemm: nmat %d", a.nmat);
   if (a.K % 256) return llb_fail("gemm: K %d is not a multiple of 256", a.K);
   if (a.xp.NC != 8 && a.xp.NC != 16) return llb_fail("gemm: NC %d", a.xp.NC);
@@ -132,6 +142,45 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   for (int i = 0; i < a.nmat; i++) a.tile0[i + 1] = a.tile0[i] + (a.m[i].rows + 15) / 16;
   for (int i = a.nmat; i < GEMM_MAXMAT; i++) a.tile0[i + 1] = a.tile0[a.nmat];
   if (a.ksplit != gemm_fix_ksplit(fmt, a.xp.NC, a.nsb, a.ksplit)) return llb_fail("gemm: ksplit %d is not valid for this shape", a.ksplit);
+  return 0;
+}
+
+// ---- the fused FFN launch (ffn_fused.cuh) ------------------------------------------------------
+template <int FMT2> static int launch_ffn(cudaStream_t s, const GemmArgs &a1, const GemmArgs &a2) {
+  int cps1 = g_llb.sms, cps2 = g_llb.sms / a2.ksplit;
+  if (cps1 > a1.tile0[a1.nmat]) cps1 = a1.tile0[a1.nmat];
+  if (cps2 < 1) cps2 = 1;
+  if (cps2 > a2.tile0[a2.nmat]) cps2 = a2.tile0[a2.nmat];
+  const int grid = cps1 > cps2 * a2.ksplit ? cps1 : cps2 * a2.ksplit;
+  if (grid > g_llb.sms) return llb_fail("k_ffn: %d CTAs do not fit %d SMs", grid, g_llb.sms);   // the barrier needs them all resident
+  const size_t s1 = (size_t)g2_xp_bytes<LLB_FM_Q4_K>(a1.nsb, 8) + 16 * G2_STAGES * 16 * G2Traits<LLB_FM_Q4_K>::RS;
+  const int nsl2 = (a2.nsb + a2.ksplit - 1) / a2.ksplit;
+  const size_t s2 = (size_t)g2_xp_bytes<FMT2>(nsl2, 8) + 16 * G2_STAGES * 16 * G2Traits<FMT2>::RS;
+  const size_t smem = s1 > s2 ? s1 : s2;
+  if (smem > G2_SMEM_MAX) return llb_fail("k_ffn: %zu bytes of shared memory", smem);
+  cudaError_t e = llb_launch(k_ffn<FMT2>, dim3(grid), dim3(512), smem, s, a1, a2, cps1, cps2, g_ffn_sync, g_g3_err);
+  if (e != cudaSuccess) return llb_fail("k_ffn launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+// can the FFN of these formats and widths run as one launch?  (gate|up in one K-slice, T <= 4)
+bool gemm_ffn_fusable(int fmt_gu, int fmt_dn, int NC, int d) {
+  return g_llb.ffn_fused && g_ffn_sync && NC == 8 && fmt_gu == LLB_FM_Q4_K &&
+         (fmt_dn == LLB_FM_Q4_K || fmt_dn == LLB_FM_Q5_K || fmt_dn == LLB_FM_Q6_K) && d % 256 == 0 &&
+         d / 256 <= g2_max_slice_sb<LLB_FM_Q4_K>(8);
+}
+// a1: gate and up (two matrices, Q4_K, ksplit 1, outputs complete); a2: down in format fmt2 with its own K-split
+int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2) {
+  if (a1.nmat != 2 || a1.ksplit != 1 || a2.nmat != 1 || a1.xp.NC != 8 || a2.xp.NC != 8) return llb_fail("k_ffn: unsupported launch shape");
+  if (gemm_prepare(LLB_FM_Q4_K, a1) || gemm_prepare(fmt2, a2)) return -1;
+  if (a2.K != a1.m[0].rows || a1.m[1].rows != a1.m[0].rows) return llb_fail("k_ffn: down takes %d columns, gate/up have %d/%d rows", a2.K, a1.m[0].rows, a1.m[1].rows);
+  if (fmt2 == LLB_FM_Q4_K) return launch_ffn<LLB_FM_Q4_K>(s, a1, a2);
+  if (fmt2 == LLB_FM_Q5_K) return launch_ffn<LLB_FM_Q5_K>(s, a1, a2);
+  if (fmt2 == LLB_FM_Q6_K) return launch_ffn<LLB_FM_Q6_K>(s, a1, a2);
+  return llb_fail("k_ffn: down format %d", fmt2);
+}
+
+int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
+  if (gemm_prepare(fmt, a)) return -1;
   if (a.tile0[a.nmat] < 1) return 0;
   const int NT = a.xp.NC / 8;
   if (is_g3(fmt, a.xp.NC)) return launch_three(s, a);

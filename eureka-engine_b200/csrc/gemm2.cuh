@@ -57,18 +57,22 @@ __device__ __forceinline__ void mma16816_z(float d[4], uint32_t a0, uint32_t a1,
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
-template <int FMT, int NT>
-__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(const GemmArgs a, const int cps) {
-  extern __shared__ __align__(128) uint8_t smem[];
+// One GEMM launch's work of a CTA (bid of cps * ksplit): fill the ring, call stage(xh_s, xsf_s, CS, sb0, nsl) --
+// which waits for whatever produces the activations, puts the CTA's slice of the planes and its side array into
+// shared memory and ends with a block-wide barrier --, then stream the CTA's tiles.  Warps beyond the format's
+// count and CTAs beyond the launch's only take part in the staging step's barriers.
+template <int FMT, int NT, class Stage>
+__device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage) {
   using TR = G2Traits<FMT>;
   constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = TR::WARPS;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
-  const int ks = blockIdx.x % a.ksplit, ci = blockIdx.x / a.ksplit;
+  const bool live = bid < cps * a.ksplit && warp < G2_WARPS;
+  const int ks = bid % a.ksplit, ci = bid / a.ksplit;
   const int sb0 = (int)(((long long)ks * a.nsb) / a.ksplit), nsl = (int)(((long long)(ks + 1) * a.nsb) / a.ksplit) - sb0;
   const int CS = nsl * 512 + TR::XPAD;
   uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * TR::AUX + (size_t)warp * G2_STAGES * 16 * RS;
   const uint32_t ring_s = smem_u32(ring);
-  const int ntiles = a.tile0[a.nmat], nws = cps * G2_WARPS;
+  const int ntiles = live ? a.tile0[a.nmat] : 0, nws = cps * G2_WARPS;   // a warp that is not live sees no tiles
   const size_t rb = dev_row_bytes(FMT, a.K);
 
   // per-lane copy plan: piece i = lane + 32*it of the 16 x P sixteen-byte pieces of a stage
@@ -113,28 +117,12 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
     }
     cp_async_commit();
   };
-  pdl_trigger();
   plan_tile(p_tile);
   // weights first: the ring's prologue is in flight while the producer of the activations still
   // runs (weights depend on no kernel), and while the activation slice is staged
 #pragma unroll 1
   for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
-  pdl_wait();
-  {
-    const int per_col = nsl * 32;   // 16-byte pieces of one column's slice
-    for (int i = threadIdx.x; i < NC * per_col; i += blockDim.x) {
-      const int c = i / per_col, p = i - c * per_col;
-      cp_async16(smem_u32(xh_s + c * CS + p * 16), (const uint8_t *)(a.xp.xh + (size_t)c * a.K + (size_t)sb0 * 256) + p * 16);
-    }
-    // the side array of the slice: contiguous in global memory for both kinds
-    const uint8_t *xf = FMT == LLB_FM_Q6_K   ? (const uint8_t *)(a.xp.xs16 + (size_t)sb0 * 16 * NC)
-                        : FMT == LLB_FM_Q8_0 ? (const uint8_t *)(a.xp.xs32 + (size_t)sb0 * 8 * NC)
-                                             : (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
-    for (int i = threadIdx.x; i < nsl * NC * (TR::AUX / 16); i += blockDim.x) cp_async16(smem_u32(xsf_s + i * 16), xf + i * 16);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-  }
+  stage(xh_s, xsf_s, CS, sb0, nsl);
   // the XP group sits between prologue groups and later ones; from here on group accounting is per
   // warp again: G2_STAGES-1 chunks are complete, none pending
   int pstage = G2_STAGES - 1, cstage = 0;
@@ -306,4 +294,34 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(co
     }
   }
   cp_async_wait<0>();
+}
+
+// the activation slice from the planes in global memory: cp.async, one wait, one barrier
+template <int FMT, int NT> struct G2StagePlanes {
+  const GemmArgs &a;
+  __device__ __forceinline__ void operator()(uint8_t *xh_s, uint8_t *xsf_s, int CS, int sb0, int nsl) const {
+    using TR = G2Traits<FMT>;
+    constexpr int NC = 8 * NT;
+    pdl_wait();
+    const int per_col = nsl * 32;   // 16-byte pieces of one column's slice
+    for (int i = threadIdx.x; i < NC * per_col; i += blockDim.x) {
+      const int c = i / per_col, p = i - c * per_col;
+      cp_async16(smem_u32(xh_s + c * CS + p * 16), (const uint8_t *)(a.xp.xh + (size_t)c * a.K + (size_t)sb0 * 256) + p * 16);
+    }
+    // the side array of the slice: contiguous in global memory for all kinds
+    const uint8_t *xf = FMT == LLB_FM_Q6_K   ? (const uint8_t *)(a.xp.xs16 + (size_t)sb0 * 16 * NC)
+                        : FMT == LLB_FM_Q8_0 ? (const uint8_t *)(a.xp.xs32 + (size_t)sb0 * 8 * NC)
+                                             : (const uint8_t *)(a.xp.xsf + (size_t)sb0 * NC * 16);
+    for (int i = threadIdx.x; i < nsl * NC * (TR::AUX / 16); i += blockDim.x) cp_async16(smem_u32(xsf_s + i * 16), xf + i * 16);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+};
+
+template <int FMT, int NT>
+__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(const GemmArgs a, const int cps) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_trigger();
+  g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a});
 }

@@ -11,6 +11,7 @@
 struct LlbCtx {
   int device = -1;
   int sms = 0;
+  int ffn_fused = 0;   // the FFN as one launch with a grid barrier (LLB_FFN_FUSED=1)
   int q8_v1 = 0;   // Q8_0 on the first-generation kernel (LLB_Q8_V1=1)
   int gemm3 = 0;   // Q4_K, T <= 4 on the tcgen05 kernel (LLB_GEMM3=1)
   int pdl = 1;     // programmatic dependent launch on every kernel of a pass (LLB_PDL=0 turns it off)
@@ -51,6 +52,8 @@ int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks);   // clamps a requested K
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
 int gemm_setup(void);
 int gemm_wait_errors(void);
+bool gemm_ffn_fusable(int fmt_gu, int fmt_dn, int NC, int d);
+int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2);   // gate|up (Q4_K, one K-slice), silu, down in one launch
 
 // ops.cu
 int ops_xp_from_f32(cudaStream_t s, const float *x, int T, int planes, XPlanes xp);
