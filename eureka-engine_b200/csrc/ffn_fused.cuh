@@ -32,37 +32,43 @@ __device__ __forceinline__ void ffn_grid_sync(unsigned int *sync, unsigned int n
   __syncthreads();
 }
 
-// silu(g) * u of 32 consecutive slice columns (lane = column) of token t into the planes and the side array in
-// shared memory, laid out exactly as G2StagePlanes would have copied them from global memory
-template <int FMT> __device__ __forceinline__ void ffn_store32(uint8_t *xh_s, uint8_t *xsf_s, int CS, int t, int blk32, float v, int lane) {
+// silu(g) * u of FOUR consecutive slice columns c .. c+3 (c a multiple of 4; the eight lanes 8j .. 8j+7 of a warp hold
+// one aligned group of 32 columns) of token t into the planes and the side array in shared memory, laid out exactly as
+// G2StagePlanes would have copied them from global memory.  Stored order inside the four: 0 2 1 3.
+template <int FMT> __device__ __forceinline__ void ffn_store4(uint8_t *xh_s, uint8_t *xsf_s, int CS, int t, int c, const float (&v)[4], int lane) {
   constexpr int NC = 8, NH = 4;
-  const int c = blk32 * 32 + lane, pc = (c & ~7) | ((c & 4) | ((c & 1) << 1) | ((c & 2) >> 1));
-  const __half hi = __float2half_rn(v);
-  float hif = __half2float(hi);
-  const __half lo = __float2half_rn((v - hif) * XP_LO_SCALE);
-  float lof = __half2float(lo);
-  ((__half *)(xh_s + (size_t)t * CS))[pc] = hi;
-  ((__half *)(xh_s + (size_t)(NH + t) * CS))[pc] = lo;
+  __half hi[4], lo[4];
+  float hs = 0.0f, ls = 0.0f;
 #pragma unroll
-  for (int m = 1; m < 16; m <<= 1) {
-    hif += __shfl_xor_sync(0xffffffffu, hif, m);
-    lof += __shfl_xor_sync(0xffffffffu, lof, m);
+  for (int i = 0; i < 4; i++) {
+    hi[i] = __float2half_rn(v[i]);
+    const float hf = __half2float(hi[i]);
+    lo[i] = __float2half_rn((v[i] - hf) * XP_LO_SCALE);
+    hs += hf; ls += __half2float(lo[i]);
   }
-  const float hi32 = hif + __shfl_xor_sync(0xffffffffu, hif, 16), lo32 = lof + __shfl_xor_sync(0xffffffffu, lof, 16);
+  {
+    const __half2 a = __halves2half2(hi[0], hi[2]), b = __halves2half2(hi[1], hi[3]);
+    *(uint2 *)(xh_s + (size_t)t * CS + (size_t)c * 2) = make_uint2(*(const uint32_t *)&a, *(const uint32_t *)&b);
+    const __half2 e = __halves2half2(lo[0], lo[2]), f = __halves2half2(lo[1], lo[3]);
+    *(uint2 *)(xh_s + (size_t)(NH + t) * CS + (size_t)c * 2) = make_uint2(*(const uint32_t *)&e, *(const uint32_t *)&f);
+  }
+  hs += __shfl_xor_sync(0xffffffffu, hs, 1); ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+  hs += __shfl_xor_sync(0xffffffffu, hs, 2); ls += __shfl_xor_sync(0xffffffffu, ls, 2);   // 16 columns
   if constexpr (FMT == LLB_FM_Q6_K) {
-    if ((lane & 15) == 0) {   // f32 sums of 16 columns: [16-column group][NC]
-      float *x16 = (float *)xsf_s + (size_t)(blk32 * 2 + (lane >> 4)) * NC;
-      x16[t] = hif; x16[NH + t] = lof;
+    if ((lane & 3) == 0) {   // f32 sums of 16 columns: [16-column group][NC]
+      float *x16 = (float *)xsf_s + (size_t)(c >> 4) * NC;
+      x16[t] = hs; x16[NH + t] = ls;
     }
   } else {
-    if (lane == 0) {          // 32-column means as fp16 hi / rest, in the order the min-term MMA's B fragment reads them
-      const int sb = blk32 >> 3, b = blk32 & 7;
+    const float h32 = hs + __shfl_xor_sync(0xffffffffu, hs, 4), l32 = ls + __shfl_xor_sync(0xffffffffu, ls, 4);
+    if ((lane & 7) == 0) {   // 32-column means as fp16 hi / rest, in the order the min-term MMA's B fragment reads them
+      const int sb = c >> 8, b = (c >> 5) & 7;
       __half *f = (__half *)xsf_s + ((size_t)sb * NC + t) * 16 + 4 * (b >> 1) + (b & 1);
-      float m = hi32 * 0.03125f;
+      float m = h32 * 0.03125f;
       __half h1 = __float2half_rn(m);
       f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
       f += (size_t)NH * 16;
-      m = lo32 * 0.03125f;
+      m = l32 * 0.03125f;
       h1 = __float2half_rn(m);
       f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
     }
@@ -75,25 +81,29 @@ template <int FMT> struct FfnStageSilu {
   unsigned int *sync, *err;
   __device__ __forceinline__ void operator()(uint8_t *xh_s, uint8_t *xsf_s, int CS, int sb0, int nsl) const {
     ffn_grid_sync(sync, gridDim.x, err);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    // tasks: (token t of 4 plane pairs, 32-column block); rows t >= T are zero planes.  Eight tasks at a time: their
-    // sixteen loads are in flight together (one trip to L2 per batch, not per task)
-    const int ntask = 4 * nsl * 8;
-    for (int t0 = warp; t0 < ntask; t0 += 8 * nwarp) {
-      float gv[8], uv[8];
+    const int lane = threadIdx.x & 31;
+    // thread task = (token t of the 4 plane pairs, group of four columns); rows t >= T are zero planes.  The slice
+    // has nsl * 64 groups per token; up to six tasks of a thread are loaded together (one trip to L2)
+    const int ngrp = nsl * 64, ntask = 4 * ngrp;
+    for (int t0 = threadIdx.x; t0 < ntask; t0 += 6 * blockDim.x) {
+      float4 gv[6], uv[6];
 #pragma unroll
-      for (int q = 0; q < 8; q++) {
-        const int task = t0 + q * nwarp, t = task & 3, blk32 = task >> 2;
-        gv[q] = 0.0f; uv[q] = 0.0f;
+      for (int q = 0; q < 6; q++) {
+        const int task = t0 + q * blockDim.x, t = task / ngrp, c = 4 * (task - t * ngrp);
+        gv[q] = make_float4(0.f, 0.f, 0.f, 0.f); uv[q] = gv[q];
         if (task < ntask && t < T) {
-          const size_t i = (size_t)t * f + (size_t)sb0 * 256 + blk32 * 32 + lane;
-          gv[q] = __ldcg(g + i); uv[q] = __ldcg(u + i);
+          const size_t i = (size_t)t * f + (size_t)sb0 * 256 + c;
+          gv[q] = __ldcg((const float4 *)(g + i)); uv[q] = __ldcg((const float4 *)(u + i));
         }
       }
 #pragma unroll
-      for (int q = 0; q < 8; q++) {
-        const int task = t0 + q * nwarp;
-        if (task < ntask) ffn_store32<FMT>(xh_s, xsf_s, CS, task & 3, task >> 2, (gv[q] / (1.0f + expf(-gv[q]))) * uv[q], lane);
+      for (int q = 0; q < 6; q++) {
+        const int task = t0 + q * blockDim.x, t = task / ngrp, c = 4 * (task - t * ngrp);
+        if (task < ntask) {   // whole warps: ngrp and blockDim are multiples of 32
+          const float h[4] = {(gv[q].x / (1.0f + expf(-gv[q].x))) * uv[q].x, (gv[q].y / (1.0f + expf(-gv[q].y))) * uv[q].y,
+                              (gv[q].z / (1.0f + expf(-gv[q].z))) * uv[q].z, (gv[q].w / (1.0f + expf(-gv[q].w))) * uv[q].w};
+          ffn_store4<FMT>(xh_s, xsf_s, CS, t, c, h, lane);
+        }
       }
     }
     __syncthreads();
