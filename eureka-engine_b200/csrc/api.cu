@@ -186,6 +186,12 @@ int llb_b200_use_tcgen05(int on) {
   g_llb.gemm3 = on != 0;
   return was;
 }
+int llb_b200_use_fused_ffn(int on) {
+  NEED_INIT(-1)
+  const int was = g_llb.ffn_fused;
+  g_llb.ffn_fused = on != 0;
+  return was;
+}
 int llb_b200_wait_errors(void) {
   NEED_INIT(-1)
   return gemm_wait_errors();

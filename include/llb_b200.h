@@ -76,7 +76,11 @@ LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows,
  * default: at the 27B shapes the mma.sync kernel is the faster of the two.  A speculative engine keeps the
  * kernels it was opened with. */
 LLB_API int llb_b200_use_tcgen05(int on);
-/* 1 when a bounded wait inside a kernel (an mbarrier of the tensor-core GEMM) has run out since
+/* The SwiGLU FFN of engines opened from now on as ONE launch (gate|up GEMM, grid-wide barrier, silu(gate) * up built in
+ * shared memory, down GEMM) instead of three; returns the previous setting.  Also LLB_FFN_FUSED=1 at llb_b200_init.  Off by
+ * default: measured no faster at the 27B shape.  Applies where gate and up are Q4_K and T <= 4. */
+LLB_API int llb_b200_use_fused_ffn(int on);
+/* 1 when a bounded wait inside a kernel (an mbarrier of the tcgen05 GEMM, the fused FFN's grid barrier) has run out since
  * llb_b200_init: the results of that launch are not valid.  0 otherwise; -1 on a CUDA error. */
 LLB_API int llb_b200_wait_errors(void);
 /* The same through HOST buffers: bf16 x [T][K] in, f32 y [T][rows] out, copies included. */

@@ -187,3 +187,22 @@ def test_long_context_attention(pkg, packs, oracle, llb):
     same, stats, st, eng, orc, ids = _run_case(pkg, packs, oracle, cfg, 3, 700, 16, seed=8)
     eng.close()
     assert same == 16
+
+
+def test_fused_ffn_launch(pkg, packs, oracle, llb):
+    """The FFN as one launch with a grid-wide barrier (off by default): same ids as the oracle, no barrier wait ran out,
+    fewer kernels in the cycle's graph."""
+    L = llb.lib()
+    cfg = packs.cfg_tiny(quant="q4_k_m", n_layers=8, tied_head=False, seed=12)
+    nodes = {}
+    for on in (0, 1):
+        was = L.llb_b200_use_fused_ffn(on)
+        try:
+            same, stats, st, eng, orc, ids = _run_case(pkg, packs, oracle, cfg, 3, 6, 20)
+            nodes[on] = eng.graph_nodes(2)
+            eng.close()
+        finally:
+            L.llb_b200_use_fused_ffn(was)
+        assert same == 20
+    assert L.llb_b200_wait_errors() == 0
+    assert nodes[1] < nodes[0]
