@@ -29,7 +29,7 @@ static_assert(GEMM_MAXMAT == 4, "k_gemm3 finds a tile's matrix with three compar
 #define G3_BLOCK (G3_THREADS + 128)
 #define G3_STAGES 6
 #define G3_STAGE_BYTES (128 * 144)
-#define G3_RED_BYTES (4 * 128 * 8 * 4)
+#define G3_RED_BYTES (5 * 128 * 8 * 4)   // four partial sums per row and column, and the row's min terms
 #define G3_HDR_BYTES 128
 #define G3_SMEM_MAX 232448
 #define G3_TMEM_COLS 512
@@ -301,12 +301,12 @@ __global__ void __launch_bounds__(G3_BLOCK, 1) k_gemm3(const GemmArgs a, const i
         accm[1] += dm_p * vm[1];
         if (++e_c == nsl) {
           // tile done: the four threads of a row add up through shared memory
-#pragma unroll
-          for (int j = 0; j < 8; j++)
-            if ((j >> 1) == c) acc[j] -= accm[j & 1];
+          // (the min term of a column is subtracted after the four partial sums are added, so that a
+          // column's result does not depend on which column of the launch it is)
           float4 *rp = (float4 *)(red + ((size_t)c * 128 + r) * 8);
           rp[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
           rp[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+          *(float2 *)(red + (size_t)(4 * 128 + r) * 8 + 2 * c) = make_float2(accm[0], accm[1]);
           quarter_sync(q);
           if (c == 0) {
             float sum[8];
@@ -316,6 +316,10 @@ __global__ void __launch_bounds__(G3_BLOCK, 1) k_gemm3(const GemmArgs a, const i
             for (int cc = 0; cc < 4; cc++) {
               const float4 x0 = *(const float4 *)(red + ((size_t)cc * 128 + r) * 8), x1 = *(const float4 *)(red + ((size_t)cc * 128 + r) * 8 + 4);
               sum[0] += x0.x; sum[1] += x0.y; sum[2] += x0.z; sum[3] += x0.w; sum[4] += x1.x; sum[5] += x1.y; sum[6] += x1.z; sum[7] += x1.w;
+            }
+            {
+              const float4 m0 = *(const float4 *)(red + (size_t)(4 * 128 + r) * 8), m1 = *(const float4 *)(red + (size_t)(4 * 128 + r) * 8 + 4);
+              sum[0] -= m0.x; sum[1] -= m0.y; sum[2] -= m0.z; sum[3] -= m0.w; sum[4] -= m1.x; sum[5] -= m1.y; sum[6] -= m1.z; sum[7] -= m1.w;
             }
             const int m = (e_tile >= t128[1]) + (e_tile >= t128[2]) + (e_tile >= t128[3]);
             const GemmMat &M = a.m[m];

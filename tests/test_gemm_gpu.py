@@ -112,6 +112,10 @@ def test_column_independence(llb, packs, dev):
     """Row t of a T-row launch equals the T = 1 launch bit for bit (the property that makes greedy
     speculative decoding lossless; the reference checks the same for its T-row leaves,
     tools/payload-spec.patch:41-44)."""
+    _column_independence(llb, packs, dev)
+
+
+def _column_independence(llb, packs, dev):
     L = llb.lib()
     rows, K = 256, 2048
     rng = np.random.default_rng(1)
@@ -144,6 +148,10 @@ def tcgen05(llb):
 def test_tcgen05_gemm_vs_oracle(llb, packs, oracle, dev, tcgen05, K, ksplit):
     _gemm_case(llb, packs, oracle, dev, "Q4_K", [80], K, 4, 2, ksplit, seed=K)
     _gemm_case(llb, packs, oracle, dev, "Q4_K", [300], K, 3, 2, ksplit, seed=K + 1)
+
+
+def test_tcgen05_column_independence(llb, packs, dev, tcgen05):
+    _column_independence(llb, packs, dev)
 
 
 def test_tcgen05_gemm_ragged_cat_and_planes(llb, packs, oracle, dev, tcgen05):
