@@ -233,6 +233,11 @@ class ModelCfg:
     quant: str = "q8_0"       # q8_0 | q4_k_m | q4_k_s
     seed: int = 0
     name: str = "synthetic"
+    # routed-expert FFN (qwen35moe; host/llb_host.c:622-724): 0 experts = the dense FFN of d_ff columns
+    n_experts: int = 0
+    n_experts_used: int = 0
+    d_expert: int = 0         # expert_feed_forward_length
+    d_shared: int = 0         # expert_shared_feed_forward_length
 
     @property
     def kdc(self): return self.ssm_groups * self.ssm_state
@@ -272,6 +277,23 @@ def cfg_c4(**kw) -> ModelCfg:
     return ModelCfg(**a)
 
 
+def cfg_c3(**kw) -> ModelCfg:
+    """MoE hybrid (35B-A3B shape): 256 experts, top 8 plus a shared expert, Q4_K_S."""
+    a = dict(n_layers=40, d_model=2048, n_heads=16, n_kv_heads=2, head_dim=256, d_ff=512,
+             vocab_size=151936, ssm_heads=32, ssm_groups=16, tied_head=False, quant="q4_k_s", seed=4,
+             name="c3-moe-q4_k_s", n_experts=256, n_experts_used=8, d_expert=512, d_shared=512)
+    a.update(kw)
+    return ModelCfg(**a)
+
+
+def cfg_tiny_moe(**kw) -> ModelCfg:
+    """cfg_tiny with a routed-expert FFN: 8 experts, top 2, plus the shared expert."""
+    a = dict(quant="q4_k_s", seed=13, name="tiny-moe", d_ff=256, n_experts=8, n_experts_used=2, d_expert=256,
+             d_shared=256)
+    a.update(kw)
+    return cfg_tiny(**a)
+
+
 def cfg_tiny(**kw) -> ModelCfg:
     """A few-MB model with every structural feature (GQA, head tiling hh % GK with rep 2,
     partial rope, both layer kinds); used by the fast parity tests."""
@@ -293,12 +315,14 @@ def tensor_type(cfg: ModelCfg, name: str) -> str:
     q4_k_s : Q4_K, except Q6_K for output.weight and Q5_K for attn_v / ffn_down in the first
              eighth of the layers."""
     if name.endswith("norm.weight") or name.endswith("ssm_a") or name.endswith("ssm_dt.bias") \
-            or name.endswith("ssm_conv1d.weight"):
+            or name.endswith("ssm_conv1d.weight") or "ffn_gate_inp" in name:
         return "F32"
     if cfg.quant == "q8_0":
         return "Q8_0"
     il = int(name.split(".")[1]) if name.startswith("blk.") else -1
     leaf = name.split(".")[-2] if name.endswith(".weight") else name
+    if leaf.endswith("_exps") or leaf.endswith("_shexp"):   # ffn_down_exps / ffn_down_shexp follow ffn_down's rule
+        leaf = leaf.rsplit("_", 1)[0]
     if name == "output.weight":
         return "Q6_K"
     if cfg.quant == "q4_k_m":
@@ -331,8 +355,18 @@ def tensor_plan(cfg: ModelCfg) -> List[Tuple[str, int, int]]:
                      (p + "ssm_dt.bias", 1, cfg.ssm_heads), (p + "ssm_a", 1, cfg.ssm_heads),
                      (p + "ssm_conv1d.weight", cfg.convd, cfg.conv_kernel), (p + "ssm_norm.weight", 1, cfg.ssm_state),
                      (p + "ssm_out.weight", d, cfg.vdc)]
-        plan += [(p + "post_attention_norm.weight", 1, d), (p + "ffn_gate.weight", cfg.d_ff, d),
-                 (p + "ffn_up.weight", cfg.d_ff, d), (p + "ffn_down.weight", d, cfg.d_ff)]
+        plan.append((p + "post_attention_norm.weight", 1, d))
+        if cfg.n_experts:
+            # the expert stacks are [expert][row] flattened over their first two dimensions (GGUF names,
+            # reports/cuda-moe/scripts/gen_moe.py:104-113)
+            ne, ef, sf = cfg.n_experts, cfg.d_expert, cfg.d_shared
+            plan += [(p + "ffn_gate_inp.weight", ne, d), (p + "ffn_gate_inp_shexp.weight", 1, d),
+                     (p + "ffn_gate_exps.weight", ne * ef, d), (p + "ffn_up_exps.weight", ne * ef, d),
+                     (p + "ffn_down_exps.weight", ne * d, ef), (p + "ffn_gate_shexp.weight", sf, d),
+                     (p + "ffn_up_shexp.weight", sf, d), (p + "ffn_down_shexp.weight", d, sf)]
+        else:
+            plan += [(p + "ffn_gate.weight", cfg.d_ff, d), (p + "ffn_up.weight", cfg.d_ff, d),
+                     (p + "ffn_down.weight", d, cfg.d_ff)]
     plan.append(("output_norm.weight", 1, d))
     if not cfg.tied_head:
         plan.append(("output.weight", cfg.vocab_size, d))
@@ -407,6 +441,9 @@ class Pack:
               ("ssm_inner_size", c.vdc), ("linear_key_dim", c.kdc), ("linear_value_head_dim", c.ssm_state),
               ("linear_conv_dim", c.convd), ("rope_dim", c.rope_dim), ("rope_freq_base", repr(float(c.rope_base))),
               ("rms_norm_eps", repr(float(c.eps)))]
+        if c.n_experts:
+            kv += [("expert_count", c.n_experts), ("expert_used_count", c.n_experts_used),
+                   ("expert_feed_forward_length", c.d_expert), ("expert_shared_feed_forward_length", c.d_shared)]
         lines = [f"#cfg\t{k}\t{v}" for k, v in kv]
         lines.append(f"# pack_bytes\t{self.data.numel()}")
         lines.append("# name\toffset\tbytes\trows\tcols\tsrc_type\trow_bytes\tfmt")

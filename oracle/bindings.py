@@ -37,7 +37,8 @@ def _p(a: np.ndarray):
 class Cfg(C.Structure):
     _fields_ = [(n, _i) for n in ("n_layers d_model n_heads n_kv_heads head_dim d_ff vocab interval conv_kernel "
                                   "ssm_state ssm_groups ssm_heads vhd kdc vdc convd rope_dim").split()] + \
-               [("rope_base", _f), ("eps", _f)]
+               [("rope_base", _f), ("eps", _f)] + \
+               [(n, _i) for n in "n_experts n_used d_expert d_shared".split()]
 
 
 class SpecStats(C.Structure):
@@ -93,6 +94,8 @@ class Oracle:
             L.q35_spec_lookup.argtypes = [_vp, _vp, _i, _i, _i, _vp, _vp, C.POINTER(SpecStats)]
             L.q35_lookup_draft.restype = _i
             L.q35_lookup_draft.argtypes = [_vp, _i, _i, _vp]
+            L.q35_moe_ffn.restype = _i
+            L.q35_moe_ffn.argtypes = [_vp, _i, _vp, _vp, _vp, _vp]
             L.q35_mtp_rows.restype = _i
             L.q35_mtp_rows.argtypes = [_vp, _i, _i, _vp, _vp, _vp]
             L.q35_threads.argtypes = [_i]
@@ -140,6 +143,17 @@ class Oracle:
 
     def reset(self):
         self.L.q35_reset(self.h)
+
+    def moe_ffn(self, il: int, h2: np.ndarray):
+        """The routed-expert FFN of layer il on one normed row: (out[d], ids[k], wts[k + 1])."""
+        c = self.cfg
+        h2 = np.ascontiguousarray(h2, np.float32)
+        out = np.zeros(c.d_model, np.float32)
+        ids = np.zeros(c.n_used, np.int32)
+        wts = np.zeros(c.n_used + 1, np.float32)
+        if self.L.q35_moe_ffn(self.h, int(il), _p(h2), _p(out), _p(ids), _p(wts)):
+            raise RuntimeError("q35_moe_ffn: layer %d has no routed experts" % il)
+        return out, ids, wts
 
     def forward(self, tok: int, pos: int):
         self.L.q35_forward(self.h, int(tok), int(pos))

@@ -149,7 +149,9 @@ typedef struct { /* one full-attention block's weights (trunk layer or the draft
   Mat q, k, v, o;
   const float *qn, *kn;
 } AttnW;
-typedef struct { Mat gate, up, down; const float *post; } FfnW;
+/* moe != 0: router [ne x d] and sh_inp [d] F32; gate/up/down are the shared expert; eg/eu [ne*ef x d] and
+ * ed [ne*d x ef] the expert stacks (GGUF tensors ffn_gate_exps, ffn_up_exps, ffn_down_exps) */
+typedef struct { Mat gate, up, down; const float *post; int moe; Mat router, eg, eu, ed; const float *sh_inp; } FfnW;
 typedef struct {
   Mat qkv, z, beta, alpha, out;
   const float *dt, *a, *conv, *norm;
@@ -167,7 +169,7 @@ struct Q35 {
   /* state */
   float *S, *conv, *K, *V;
   /* scratch */
-  float *x, *h, *a, *qkv, *z, *y, *qg, *qn, *kb, *vb, *att, *prob, *qt, *kt, *f1, *f2, *o128, *logits, *hn;
+  float *x, *h, *a, *qkv, *z, *y, *qg, *qn, *kb, *vb, *att, *prob, *qt, *kt, *f1, *f2, *o128, *logits, *hn, *moe_p, *moe_o;
   /* drafter */
   int has_mtp, mt_nv;
   uint8_t *mt_img;
@@ -226,7 +228,9 @@ static int parse_index(Q35 *m, const char *text) {
         {"full_attention_interval", &c->interval}, {"ssm_conv_kernel", &c->conv_kernel},
         {"ssm_state_size", &c->ssm_state}, {"ssm_group_count", &c->ssm_groups},
         {"ssm_time_step_rank", &c->ssm_heads}, {"ssm_inner_size", &c->vdc}, {"linear_key_dim", &c->kdc},
-        {"linear_value_head_dim", &c->vhd}, {"linear_conv_dim", &c->convd}, {"rope_dim", &c->rope_dim}};
+        {"linear_value_head_dim", &c->vhd}, {"linear_conv_dim", &c->convd}, {"rope_dim", &c->rope_dim},
+        {"expert_count", &c->n_experts}, {"expert_used_count", &c->n_used}, {"expert_feed_forward_length", &c->d_expert},
+        {"expert_shared_feed_forward_length", &c->d_shared}};
       for (size_t i = 0; i < sizeof im / sizeof *im; i++) if (!strcmp(key, im[i].k)) *im[i].v = atoi(val);
       if (!strcmp(key, "rope_freq_base")) c->rope_base = strtof(val, NULL);
       if (!strcmp(key, "rms_norm_eps")) c->eps = strtof(val, NULL);
@@ -280,6 +284,18 @@ static Q35 *finish_open(Q35 *m, int layers, int cap) {
       l->dn.norm = vec_of(m, il, "ssm_norm.weight");
     }
     l->ffn.post = vec_of(m, il, "post_attention_norm.weight");
+    if (c->n_experts > 0) {
+      l->ffn.moe = 1;
+      l->ffn.router = mat_of(m, "blk.%d.%s", il, "ffn_gate_inp.weight");
+      l->ffn.sh_inp = vec_of(m, il, "ffn_gate_inp_shexp.weight");
+      l->ffn.eg = mat_of(m, "blk.%d.%s", il, "ffn_gate_exps.weight");
+      l->ffn.eu = mat_of(m, "blk.%d.%s", il, "ffn_up_exps.weight");
+      l->ffn.ed = mat_of(m, "blk.%d.%s", il, "ffn_down_exps.weight");
+      l->ffn.gate = mat_of(m, "blk.%d.%s", il, "ffn_gate_shexp.weight");
+      l->ffn.up = mat_of(m, "blk.%d.%s", il, "ffn_up_shexp.weight");
+      l->ffn.down = mat_of(m, "blk.%d.%s", il, "ffn_down_shexp.weight");
+      continue;
+    }
     l->ffn.gate = mat_of(m, "blk.%d.%s", il, "ffn_gate.weight");
     l->ffn.up = mat_of(m, "blk.%d.%s", il, "ffn_up.weight");
     l->ffn.down = mat_of(m, "blk.%d.%s", il, "ffn_down.weight");
@@ -294,6 +310,9 @@ static Q35 *finish_open(Q35 *m, int layers, int cap) {
   m->V = fz((size_t)L * cap * kvd);
   int big = c->d_ff > c->convd ? c->d_ff : c->convd;
   if (d > big) big = d;
+  if (c->d_expert > big) big = c->d_expert;
+  if (c->d_shared > big) big = c->d_shared;
+  if (c->n_experts > 0) { m->moe_p = fz(c->n_experts); m->moe_o = fz(d); }
   if (c->vdc > big) big = c->vdc;
   m->x = fz(d); m->h = fz(d); m->a = fz(big); m->qkv = fz(c->convd); m->z = fz(c->vdc); m->y = fz(big);
   m->qg = fz(2 * qa); m->qn = fz(qa); m->kb = fz(kvd); m->vb = fz(kvd); m->att = fz(qa); m->prob = fz(cap);
@@ -342,7 +361,7 @@ API void q35_close(Q35 *m) {
   if (!m) return;
   float *bufs[] = {m->S, m->conv, m->K, m->V, m->x, m->h, m->a, m->qkv, m->z, m->y, m->qg, m->qn, m->kb, m->vb,
                    m->att, m->prob, m->qt, m->kt, m->f1, m->f2, m->o128, m->logits, m->hn, m->mt_K, m->mt_V,
-                   m->mt_cat, m->mt_logits};
+                   m->mt_cat, m->mt_logits, m->moe_p, m->moe_o};
   for (size_t i = 0; i < sizeof bufs / sizeof *bufs; i++) free(bufs[i]);
   if (m->owns_pack) free((void *)m->pack);
   free(m->mt_img); free(m->layer); free(m->t); free(m);
@@ -474,10 +493,70 @@ static void delta_block(Q35 *m, const DeltaW *w, float *S, float *cs, const floa
   gemv(&w->out, m->a, out);
 }
 
+/* The routed-expert FFN on one normed row h2[d]: out[d] = sum_j wt_j * down_{e_j}(silu(gate_{e_j} h2) * up_{e_j} h2)
+ * in rank order, plus sigmoid(sh_inp . h2) * shared(h2); no residual.  Routing as host/llb_host.c:622-724 with
+ * tools/payload-moeany.patch (llb_moe_topk, llb_moe_gu, llb_moe_dn): softmax over every expert's logit (exp
+ * through double), the k largest probabilities with ties to the lower index, their weights divided by their sum
+ * clamped at 6.103515625e-5.  ids[k], wts[k + 1] (the last is the shared gate) may be NULL. */
+static void moe_rows(Q35 *m, const FfnW *w, const float *h2, float *out, int *ids, float *wts) {
+  const Q35Cfg *c = &m->c;
+  int d = c->d_model, ne = c->n_experts, nk = c->n_used, ef = c->d_expert, sf = c->d_shared;
+  float *p = m->moe_p, mx = -INFINITY, sum = 0.0f;
+  gemv(&w->router, h2, p);
+  for (int e = 0; e < ne; e++) if (p[e] > mx) mx = p[e];
+  for (int e = 0; e < ne; e++) { p[e] = f_exp(p[e] - mx); sum += p[e]; }
+  float inv = 1.0f / sum;
+  for (int e = 0; e < ne; e++) p[e] *= inv;
+  int id[64];
+  float wt[65], s = 0.0f;
+  if (nk > 64) nk = 64;
+  for (int j = 0; j < nk; j++) {
+    int b = -1;
+    float bv = -1.0f;
+    for (int e = 0; e < ne; e++) if (p[e] > bv) { bv = p[e]; b = e; }   /* strict: the lower index wins a tie */
+    id[j] = b; wt[j] = bv; p[b] = -2.0f;
+    s += bv;
+  }
+  if (s < 6.103515625e-5f) s = 6.103515625e-5f;
+  for (int j = 0; j < nk; j++) wt[j] = wt[j] / s;
+  float sg = 0.0f;
+  for (int i = 0; i < d; i++) sg += w->sh_inp[i] * h2[i];
+  wt[nk] = 1.0f / (1.0f + f_exp(-sg));
+  for (int i = 0; i < d; i++) out[i] = 0.0f;
+  for (int j = 0; j < nk; j++) {
+    Mat g = w->eg, u = w->eu, dn = w->ed;
+    g.w += (size_t)id[j] * ef * g.rb; g.rows = ef;
+    u.w += (size_t)id[j] * ef * u.rb; u.rows = ef;
+    dn.w += (size_t)id[j] * d * dn.rb; dn.rows = d;
+    gemv(&g, h2, m->f1);
+    gemv(&u, h2, m->f2);
+    for (int i = 0; i < ef; i++) m->f1[i] = q35_silu(m->f1[i]) * m->f2[i];
+    gemv(&dn, m->f1, m->f2);
+    for (int i = 0; i < d; i++) out[i] = j == 0 ? m->f2[i] * wt[0] : out[i] + m->f2[i] * wt[j];
+  }
+  gemv(&w->gate, h2, m->f1);
+  gemv(&w->up, h2, m->f2);
+  for (int i = 0; i < sf; i++) m->f1[i] = q35_silu(m->f1[i]) * m->f2[i];
+  gemv(&w->down, m->f1, m->f2);
+  for (int i = 0; i < d; i++) out[i] = out[i] + m->f2[i] * wt[nk];
+  if (ids) memcpy(ids, id, (size_t)nk * sizeof(int));
+  if (wts) memcpy(wts, wt, (size_t)(nk + 1) * sizeof(float));
+}
+API int q35_moe_ffn(Q35 *m, int il, const float *h2, float *out, int *ids, float *wts) {
+  if (il < 0 || il >= m->c.n_layers || !m->layer[il].ffn.moe) return 1;
+  moe_rows(m, &m->layer[il].ffn, h2, out, ids, wts);
+  return 0;
+}
+
 /* x += down(silu(gate h2) * (up h2)), h2 = rms(x) * post   (tools/qwen35_engine.c:741-746) */
 static void ffn_block(Q35 *m, const FfnW *w, float *x) {
   const Q35Cfg *c = &m->c;
   rms_norm(m->h, x, w->post, c->d_model, c->eps);
+  if (w->moe) {   /* (moe_out + shared) + residual, llb_moe_dn's last line */
+    moe_rows(m, w, m->h, m->moe_o, NULL, NULL);
+    for (int i = 0; i < c->d_model; i++) x[i] = m->moe_o[i] + x[i];
+    return;
+  }
   gemv(&w->gate, m->h, m->f1);
   gemv(&w->up, m->h, m->f2);
   for (int i = 0; i < c->d_ff; i++) m->f1[i] = q35_silu(m->f1[i]) * m->f2[i];

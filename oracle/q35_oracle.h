@@ -9,12 +9,15 @@
  *   MTP drafter (NextN block)      host/llb_host.c:1771-1829, tools/mtp27/mtp_pack.py:14-30
  *   cycle / accept / rollback      host/llb_host.c:1902-1950, tools/payload-spec2.patch:375-410
  *   greedy accept rule             host/llb_sampler_impl.h:400-405
+ *   routed-expert FFN              host/llb_host.c:622-724, tools/payload-moeany.patch
  *
  * Parity pin: the trunk forward, logits and top-2 of this restatement are bit-identical to the
  * reference engine compiled from its own sources (oracle/_ref, see oracle/Makefile) on the same
  * packs; tests/golden holds vectors produced by that reference build.  The MTP drafter and the
  * cycle have no CPU code in the reference ("parity unpinned" for draft ids): they are pinned only
- * through the lossless property (spec ids == plain greedy ids).
+ * through the lossless property (spec ids == plain greedy ids).  The routed-expert FFN has no CPU code in
+ * the reference either; it is pinned against the reference's float64 checker
+ * (reports/metal-catchup/tools/mx_ref.py) run on this restatement's outputs (tests/golden/moe_ffn.npz).
  */
 #ifndef Q35_ORACLE_H
 #define Q35_ORACLE_H
@@ -31,6 +34,7 @@ typedef struct {
   int n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab, interval, conv_kernel, ssm_state,
       ssm_groups, ssm_heads, vhd, kdc, vdc, convd, rope_dim;
   float rope_base, eps;
+  int n_experts, n_used, d_expert, d_shared; /* routed-expert FFN (0 experts: dense) */
 } Q35Cfg;
 
 typedef struct {
@@ -68,6 +72,10 @@ const float *q35_state_S(const Q35 *m, int il);
 const float *q35_state_conv(const Q35 *m, int il);
 const float *q35_state_k(const Q35 *m, int il, int pos);
 const float *q35_state_v(const Q35 *m, int il, int pos);
+
+/* the routed-expert FFN of layer il on one normed row h2[d] (no residual): out[d], ids[k], wts[k + 1]
+ * (host/llb_host.c:622-724, tools/payload-moeany.patch) */
+int q35_moe_ffn(Q35 *m, int il, const float *h2, float *out, int *ids, float *wts);
 
 /* plain greedy: ids[steps]; top2[steps][4] = id1, bits1, id2, bits2 (may be NULL) */
 int q35_greedy(Q35 *m, const int *prompt, int np, int steps, int *ids, uint32_t *top2);

@@ -143,3 +143,40 @@ def test_prompt_lookup_drafter(packs, oracle, greedy_gold):
     assert np.array_equal(l_ids, g_ids) and np.array_equal(l_top2, g_top2)
     assert st.served >= 24 and st.rows >= st.cycles
     assert st.served == st.cycles + sum(list(st.accepted)[1:4])
+
+
+def _moe_gold_model(packs, oracle):
+    """The tiny MoE pack the fixture was made from (tests/golden/make_golden_moe.py) and its known answers."""
+    z = np.load(os.path.join(GOLD, "moe_ffn.npz"))
+    cfg = packs.cfg_tiny_moe(n_layers=8, d_expert=512, d_shared=512)
+    pack = packs.build_pack(cfg)
+    assert hashlib.sha256(pack.data.numpy().tobytes()).hexdigest() == str(z["pack_sha256"])
+    return z, cfg, pack
+
+
+def test_moe_ffn_matches_reference_checker(packs, oracle):
+    """The routed-expert FFN of the restatement against the float64 answers of the reference's own checker
+    (reports/metal-catchup/tools/mx_ref.py): same experts in the same ranks, weights and shared gate to
+    1e-6, output to 5e-6 relative (f32 sums of 256..512 terms against float64)."""
+    z, cfg, pack = _moe_gold_model(packs, oracle)
+    o = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=8)
+    assert bool(np.all(z["oracle_ids_equal"])) and float(z["oracle_rel"].max()) < 5e-6
+    for i in range(len(z["layer"])):
+        out, ids, wts = o.moe_ffn(int(z["layer"][i]), z["h2"][i])
+        assert list(ids) == list(z["rid"][i])
+        assert np.abs(wts[:-1] - z["rw"][i]).max() < 1e-6 and abs(wts[-1] - z["gs"][i]) < 1e-6
+        ref = z["ref"][i]
+        assert np.linalg.norm(out - ref) / np.linalg.norm(ref) < 5e-6
+    o.close()
+
+
+def test_moe_greedy_runs_and_is_deterministic(packs, oracle):
+    cfg = packs.cfg_tiny_moe()
+    pack = packs.build_pack(cfg)
+    prompt = packs.synth_prompt(1, 6, cfg.vocab_size)
+    a = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=32)
+    ids1, _ = a.greedy(prompt, 8)
+    a.reset()
+    ids2, _ = a.greedy(prompt, 8)
+    assert list(ids1) == list(ids2) and len(ids1) == 8
+    a.close()
