@@ -24,7 +24,11 @@ struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; size_t cap
 static PartIn as_in(const OutBuf &o) { return PartIn{o.p, o.ns, o.stride}; }
 
 struct AttnW { DevMat q, k, v, o; float *qn = nullptr, *kn = nullptr; };
-struct FfnW { DevMat gate, up, down; float *post = nullptr; };
+// moe: the layer's FFN is the routed-expert one (host/llb_host.c:622-724).  router: [ne + 1][d] F32, the ne
+// router rows and then the shared expert's gate row; gu / dn: the expert stacks in the layout of moe.cuh, the
+// shared expert being block ne; gate / up / down are unused then.
+struct FfnW { DevMat gate, up, down; float *post = nullptr; bool moe = false; float *router = nullptr; uint8_t *gu = nullptr, *dn = nullptr;
+              long long es_gu = 0, es_dn = 0; int fmt_gu = -1, fmt_dn = -1; };
 struct DeltaW { DevMat qkv, z, beta, alpha, out; float *dt = nullptr, *a = nullptr, *conv = nullptr, *norm = nullptr; };
 struct LayerW { bool full = false; float *attn_norm = nullptr; AttnW at; DeltaW dn; FfnW ffn; };
 
@@ -35,6 +39,10 @@ struct llb_spec {
   int L = 0, d = 0, H = 0, KV = 0, hd = 0, f = 0, V = 0, interval = 4, KC = 4, SZ = 128, GK = 0, TR = 0, vdc = 0, kdc = 0,
       convd = 0, rope_dim = 64;
   float rope_base = 1e7f, eps = 1e-6f;
+  int ne = 0, nk = 0, ef = 0, sf = 0;   // routed experts, experts per token, expert width, shared expert width (ne = 0: dense FFN)
+  float *moe_lg = nullptr, *moe_wt = nullptr, *moe_g = nullptr, *moe_u = nullptr, *hn2 = nullptr;
+  int *moe_ids = nullptr;
+  XPlanes xp_e;
   int k = 0, Tmax = 1, R = 2, max_ctx = 0, NC = 8;
   // weights
   std::vector<void *> allocs;
@@ -164,7 +172,8 @@ static int parse_index(llb_spec *m, const char *text, std::unordered_map<std::st
         {"n_layers", &m->L}, {"n_heads", &m->H}, {"n_kv_heads", &m->KV}, {"d_model", &m->d}, {"head_dim", &m->hd},
         {"d_ff", &m->f}, {"vocab_size", &m->V}, {"full_attention_interval", &m->interval}, {"ssm_conv_kernel", &m->KC},
         {"ssm_state_size", &m->SZ}, {"ssm_group_count", &m->GK}, {"ssm_time_step_rank", &m->TR}, {"ssm_inner_size", &m->vdc},
-        {"linear_key_dim", &m->kdc}, {"linear_conv_dim", &m->convd}, {"rope_dim", &m->rope_dim}};
+        {"linear_key_dim", &m->kdc}, {"linear_conv_dim", &m->convd}, {"rope_dim", &m->rope_dim}, {"expert_count", &m->ne},
+        {"expert_used_count", &m->nk}, {"expert_feed_forward_length", &m->ef}, {"expert_shared_feed_forward_length", &m->sf}};
       for (auto &kv : im) if (key == kv.k) *kv.v = atoi(val.c_str());
       if (key == "rope_freq_base") m->rope_base = strtof(val.c_str(), nullptr);
       if (key == "rms_norm_eps") m->eps = strtof(val.c_str(), nullptr);
@@ -195,6 +204,53 @@ static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, int
   CK(llb_b200_weight_upload(t.fmt, t.rows, t.cols, pack + t.off, on_device, (llb_dptr)(uintptr_t)dst));
   dedupe[t.off] = dst;
   *out = dst;
+  return 0;
+}
+
+// The routed experts of one layer: the router and the shared gate row into one F32 matrix, the expert
+// stacks (GGUF tensors ffn_gate_exps / ffn_up_exps [ne * ef][d], ffn_down_exps [ne * d][ef]) and the shared
+// expert re-laid as blocks [gate rows | up rows] and [down rows], the shared expert last.
+static int load_moe(llb_spec *m, FfnW &w, const std::string &p, const std::unordered_map<std::string, TensorRec> &tab, const uint8_t *pack,
+                    int on_device) {
+  const int d = m->d, ne = m->ne, ef = m->ef;
+  auto rec = [&](const char *leaf, int rows, int cols, TensorRec &out) -> int {
+    auto it = tab.find(p + leaf);
+    if (it == tab.end()) return llb_fail("pack has no tensor %s%s", p.c_str(), leaf);
+    out = it->second;
+    if (out.rows != rows || out.cols != cols) return llb_fail("%s%s is [%d x %d], the configuration needs [%d x %d]", p.c_str(), leaf, out.rows, out.cols, rows, cols);
+    if ((size_t)rows * pack_row_bytes(out.fmt, cols) != out.bytes) return llb_fail("%s%s: %llu bytes do not match its shape", p.c_str(), leaf, (unsigned long long)out.bytes);
+    return 0;
+  };
+  TensorRec r_in, r_sh, eg, eu, ed, sg, su, sd;
+  CK(rec("ffn_gate_inp.weight", ne, d, r_in)); CK(rec("ffn_gate_inp_shexp.weight", 1, d, r_sh));
+  CK(rec("ffn_gate_exps.weight", ne * ef, d, eg)); CK(rec("ffn_up_exps.weight", ne * ef, d, eu)); CK(rec("ffn_down_exps.weight", ne * d, ef, ed));
+  CK(rec("ffn_gate_shexp.weight", ef, d, sg)); CK(rec("ffn_up_shexp.weight", ef, d, su)); CK(rec("ffn_down_shexp.weight", d, ef, sd));
+  if (r_in.fmt != LLB_FM_F32 || r_sh.fmt != LLB_FM_F32) return llb_fail("%sffn_gate_inp must be F32", p.c_str());
+  if (eg.fmt != eu.fmt || sg.fmt != eg.fmt || su.fmt != eg.fmt || sd.fmt != ed.fmt)
+    return llb_fail("%s: the shared expert and the expert stacks must share their formats (gate/up %d %d %d %d, down %d %d)", p.c_str(), eg.fmt, eu.fmt, sg.fmt,
+                    su.fmt, ed.fmt, sd.fmt);
+  for (int fm : {eg.fmt, ed.fmt})
+    if (fm != LLB_FM_Q4_K && fm != LLB_FM_Q5_K && fm != LLB_FM_Q6_K) return llb_fail("%s: expert stacks of format %d have no kernel (Q4_K, Q5_K, Q6_K do)", p.c_str(), fm);
+  w.moe = true; w.fmt_gu = eg.fmt; w.fmt_dn = ed.fmt;
+  w.router = falloc(m, (size_t)(ne + 1) * d);
+  if (!w.router) return -1;
+  const cudaMemcpyKind kind = on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+  CU_OK(cudaMemcpyAsync(w.router, pack + r_in.off, (size_t)ne * d * 4, kind, g_llb.stream));
+  CU_OK(cudaMemcpyAsync(w.router + (size_t)ne * d, pack + r_sh.off, (size_t)d * 4, kind, g_llb.stream));
+  const size_t rb_gu = dev_row_bytes(eg.fmt, d), rb_dn = dev_row_bytes(ed.fmt, ef);
+  const size_t pb_gu = pack_row_bytes(eg.fmt, d), pb_dn = pack_row_bytes(ed.fmt, ef);
+  w.es_gu = (long long)(2 * ef * rb_gu); w.es_dn = (long long)(d * rb_dn);
+  w.gu = (uint8_t *)dalloc(m, (size_t)(ne + 1) * w.es_gu);
+  w.dn = (uint8_t *)dalloc(m, (size_t)(ne + 1) * w.es_dn);
+  if (!w.gu || !w.dn) return -1;
+  for (int e = 0; e <= ne; e++) {
+    const uint8_t *g = e < ne ? pack + eg.off + (size_t)e * ef * pb_gu : pack + sg.off;
+    const uint8_t *u = e < ne ? pack + eu.off + (size_t)e * ef * pb_gu : pack + su.off;
+    const uint8_t *dn = e < ne ? pack + ed.off + (size_t)e * d * pb_dn : pack + sd.off;
+    CK(llb_b200_weight_upload(eg.fmt, ef, d, g, on_device, (llb_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu)));
+    CK(llb_b200_weight_upload(eg.fmt, ef, d, u, on_device, (llb_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu + (size_t)ef * rb_gu)));
+    CK(llb_b200_weight_upload(ed.fmt, d, ef, dn, on_device, (llb_dptr)(uintptr_t)(w.dn + (size_t)e * w.es_dn)));
+  }
   return 0;
 }
 
@@ -274,8 +330,38 @@ static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const Row
 }
 
 // x1 = xin + sum(b_a); h = rms(x1) * post -> planes; x1 + down(silu(gate h) * up h) stays split in b_dn
+// The routed-expert FFN: router logits and top k on the normed rows, gate|up of every (row, slot), the slots'
+// weights folded into silu(gate) * up, and one down launch per pass whose accumulation order is the rank order;
+// like the dense FFN it leaves x1 + (its output) as x1 and K-slice partial sums in b_dn.
+static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs);
+static int enq_moe_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
+  cudaStream_t s = g_llb.stream;
+  PK("norm post", op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, m->hn2, rs, m->Tmax, 0));
+  return enq_moe_core(m, w, rs);
+}
+// ... from the normed rows on: planes in xp_d, the same rows as F32 in hn2
+static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs) {
+  cudaStream_t s = g_llb.stream;
+  const int ns = m->nk + 1, fe = ns * m->ef;
+  const int *n_rows = &((const RowSet *)((uintptr_t)rs & ~(uintptr_t)1))->n;
+  PK("moe route", op_moe_route(s, w.router, m->hn2, m->d, m->ne, m->nk, m->moe_lg, m->moe_ids, m->moe_wt, rs, m->Tmax));
+  MoeArgs a;
+  memset(&a, 0, sizeof a);
+  a.ids = m->moe_ids; a.nslot = ns; a.ne = m->ne; a.ef = m->ef; a.d = m->d; a.T = m->Tmax; a.n_rows = n_rows;
+  a.W = w.gu; a.es = w.es_gu; a.g = m->moe_g; a.u = m->moe_u;
+  int one = 1;
+  PK("moe gate|up", gemm_launch_moe(s, w.fmt_gu, false, m->xp_d, a, &one));
+  PK("moe silu", op_silu_scaled_xp(s, PartIn{m->moe_g, 1, 0}, PartIn{m->moe_u, 1, 0}, fe, m->xp_e, rs, m->Tmax, m->moe_wt, m->ef));
+  int ks = gemm_fix_ksplit(w.fmt_dn, m->NC, fe / 256, gemm_pick_ksplit(w.fmt_dn, m->NC, m->Tmax * (m->d / 16), fe / 256, g_llb.sms));
+  CK(out_prepare(m, m->b_dn, m->d, ks));
+  a.W = w.dn; a.es = w.es_dn; a.out = m->b_dn.p; a.split_stride = m->b_dn.stride;
+  PK("moe down", gemm_launch_moe(s, w.fmt_dn, true, m->xp_e, a, &ks));
+  return 0;
+}
+
 static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
+  if (w.moe) return enq_moe_ffn(m, w, xin, x1, rs);
   PK("norm post", op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
   if (w.gate.fmt == w.up.fmt && gemm_ffn_fusable(w.gate.fmt, w.down.fmt, m->NC, m->d) && !m->reduce_in_gemm) {
     // one launch: gate|up in one K-slice, a grid barrier, silu(gate) * up built in shared memory, down
@@ -406,6 +492,9 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (k < 0 || k > 7) return llb_fail("k = %d: the path takes 0..7 drafts (host/llb_host.c:1608)", k);
   if (m->SZ != 128 || m->KC < 2) return llb_fail("ssm_state_size %d / conv kernel %d unsupported", m->SZ, m->KC);
   if (m->hd != 128 && m->hd != 256) return llb_fail("head_dim %d unsupported", m->hd);
+  if (m->ne > 0 && (m->sf != m->ef || m->ef % 256 || m->nk < 1 || m->nk > 32 || m->nk > m->ne || m->ne > 1024))
+    return llb_fail("routed experts: %d experts, top %d, widths %d / %d (the shared expert must be as wide as the others, a multiple of 256; at most 1024 experts, top 32)",
+                    m->ne, m->nk, m->ef, m->sf);
   if (m->d % 256 || m->f % 256 || m->vdc % 256 || (m->H * m->hd) % 256) return llb_fail("model widths must be multiples of 256");
   if (m->TR % m->GK || m->H % m->KV) return llb_fail("head counts do not divide");
   { const char *e = getenv("LLB_RS_EARLY"); m->rs_early = !(e && e[0] == '0'); }
@@ -466,6 +555,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
       if (!m->ring[il] || !m->S[il]) return -1;
     }
     CK(vec(p + "post_attention_norm.weight", &l.ffn.post, d));
+    if (m->ne > 0) { CK(load_moe(m, l.ffn, p, tab, pack, on_device)); continue; }
     CK(mat(p + "ffn_gate.weight", l.ffn.gate)); CK(check_k(l.ffn.gate, m->f, d, "ffn_gate"));
     CK(mat(p + "ffn_up.weight", l.ffn.up)); CK(check_k(l.ffn.up, m->f, d, "ffn_up"));
     CK(mat(p + "ffn_down.weight", l.ffn.down)); CK(check_k(l.ffn.down, d, m->f, "ffn_down"));
@@ -551,6 +641,13 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   m->po = falloc(m, (size_t)m->H * T * m->att_split * m->hd);
   CK(xp_alloc(m, m->xp_d, d)); CK(xp_alloc(m, m->xp_f, m->f)); CK(xp_alloc(m, m->xp_qa, qa)); CK(xp_alloc(m, m->xp_v, m->vdc));
   CK(xp_alloc(m, m->xp_2d, 2 * d));
+  if (m->ne > 0) {
+    const int ns = m->nk + 1;
+    m->moe_lg = falloc(m, (size_t)T * (m->ne + 1)); m->moe_wt = falloc(m, (size_t)T * ns); m->moe_ids = (int *)dalloc(m, (size_t)T * ns * 4);
+    m->moe_g = falloc(m, (size_t)T * ns * m->ef); m->moe_u = falloc(m, (size_t)T * ns * m->ef); m->hn2 = falloc(m, (size_t)T * d);
+    CK(xp_alloc(m, m->xp_e, ns * m->ef));
+    if (!m->moe_lg || !m->moe_wt || !m->moe_ids || !m->moe_g || !m->moe_u || !m->hn2) return -1;
+  }
   m->ctl = (SpecCtl *)dalloc(m, sizeof(SpecCtl));
   if (!m->x || !m->po || !m->ctl) return -1;
   CU_OK(cudaHostAlloc((void **)&m->res_host, sizeof(SpecResult) * m->res_n, cudaHostAllocMapped));
@@ -890,6 +987,34 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
 }
 
 // The logits of verify row r of the last pass (f32 [V]), for the logit-tolerance parity check.
+// Test entry: the routed-expert FFN of layer il alone on T given normed rows (host memory, [T][d]); out[T][d]
+// is its output without the residual, ids / wt [T][k + 1] the chosen experts and weights (slot k: the shared
+// expert and its gate).  Resets the sequence state: call it before llb_spec_prefill, not between cycles.
+LLB_API int llb_spec_moe_ffn(llb_spec *m, int il, int T, const float *h2, float *out, int *ids, float *wt) {
+  if (il < 0 || il >= m->L || !m->layer[il].ffn.moe) return llb_fail("moe_ffn: layer %d has no routed experts", il);
+  if (T < 1 || T > m->Tmax) return llb_fail("moe_ffn: %d rows, the engine was opened for %d", T, m->Tmax);
+  CK(llb_spec_reset(m));
+  SpecCtl c;
+  memset(&c, 0, sizeof c);
+  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq; c.hist = m->hist; c.verify.n = T;
+  CK(ctl_write(m, c));
+  cudaStream_t s = g_llb.stream;
+  CU_OK(cudaMemcpyAsync(m->hn2, h2, (size_t)T * m->d * 4, cudaMemcpyHostToDevice, s));
+  CK(ops_xp_from_f32(s, m->hn2, T, 2, m->xp_d));
+  CK(enq_moe_core(m, m->layer[il].ffn, &m->ctl->verify));
+  CU_OK(cudaStreamSynchronize(s));
+  const int ns = m->nk + 1;
+  std::vector<float> tmp((size_t)T * m->d);
+  for (size_t i = 0; i < tmp.size(); i++) out[i] = 0.0f;
+  for (int k = 0; k < m->b_dn.ns; k++) {
+    CU_OK(cudaMemcpy(tmp.data(), m->b_dn.p + (size_t)k * m->b_dn.stride, tmp.size() * 4, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < tmp.size(); i++) out[i] += tmp[i];
+  }
+  if (ids) CU_OK(cudaMemcpy(ids, m->moe_ids, (size_t)T * ns * 4, cudaMemcpyDeviceToHost));
+  if (wt) CU_OK(cudaMemcpy(wt, m->moe_wt, (size_t)T * ns * 4, cudaMemcpyDeviceToHost));
+  return llb_spec_reset(m);
+}
+
 LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out) {
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   std::vector<float> tmp(m->V);

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(512, 1) k_ffn(const GemmArgs a1, const GemmArg
                                                 unsigned int *err) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
-  g2_phase<LLB_FM_Q4_K, 1>(a1, cps1, (int)blockIdx.x, smem, G2StagePlanes<LLB_FM_Q4_K, 1>{a1});
+  g2_phase<LLB_FM_Q4_K, 1>(a1, cps1, (int)blockIdx.x, smem, G2StagePlanes<LLB_FM_Q4_K, 1>{a1}, G2MatsPlain<LLB_FM_Q4_K>{a1});
   __syncthreads();   // the CTA is done with the first launch's shared memory
-  g2_phase<FMT2, 1>(a2, cps2, (int)blockIdx.x, smem, FfnStageSilu<FMT2>{a1.m[0].out, a1.m[1].out, a1.m[0].rows, a1.T, sync, err});
+  g2_phase<FMT2, 1>(a2, cps2, (int)blockIdx.x, smem, FfnStageSilu<FMT2>{a1.m[0].out, a1.m[1].out, a1.m[0].rows, a1.T, sync, err}, G2MatsPlain<FMT2>{a2});
 }

@@ -2,6 +2,7 @@
 #include "gemm2.cuh"
 #include "gemm3.cuh"
 #include "ffn_fused.cuh"
+#include "moe.cuh"
 #include "host.cuh"
 
 static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K || (fmt == LLB_FM_Q8_0 && !g_llb.q8_v1); }
@@ -67,10 +68,19 @@ template <int FMT> static int setup_fmt2() {
   return 0;
 }
 
+template <int FMT> static int setup_moe() {
+  CU_OK(cudaFuncSetAttribute(k_moe_gu<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_moe_gu<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  return 0;
+}
+
 int gemm_setup(void) {
   if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
   if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>() || setup_fmt2<LLB_FM_Q8_0>()) return -1;
   CU_OK(cudaFuncSetAttribute(k_gemm3, cudaFuncAttributeMaxDynamicSharedMemorySize, G3_SMEM_MAX));
+  if (setup_moe<LLB_FM_Q4_K>() || setup_moe<LLB_FM_Q5_K>() || setup_moe<LLB_FM_Q6_K>()) return -1;
   CU_OK(cudaFuncSetAttribute(k_ffn<LLB_FM_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_ffn<LLB_FM_Q5_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_ffn<LLB_FM_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
@@ -177,6 +187,44 @@ int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2) {
   if (fmt2 == LLB_FM_Q5_K) return launch_ffn<LLB_FM_Q5_K>(s, a1, a2);
   if (fmt2 == LLB_FM_Q6_K) return launch_ffn<LLB_FM_Q6_K>(s, a1, a2);
   return llb_fail("k_ffn: down format %d", fmt2);
+}
+
+// ---- the routed experts' GEMMs (moe.cuh) ---------------------------------------------------------
+template <int FMT, int NT> static int launch_moe(cudaStream_t s, bool down, const GemmArgs &a, const MoeArgs &m, int ntiles) {
+  const int NC = 8 * NT, nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
+  int cps = g_llb.sms * G2_CPSM / a.ksplit;
+  if (cps < 1) cps = 1;
+  if (cps > ntiles) cps = ntiles;
+  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
+  if (smem > G2_SMEM_MAX) return llb_fail("moe gemm: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
+  cudaError_t e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps)
+                       : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps);
+  if (e != cudaSuccess) return llb_fail("moe gemm launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+// down == false: gate|up of every (token, slot) on planes of K = d columns, one K-slice (the epilogue needs whole sums);
+// down == true: the per-token virtual matrices of K = nslot * ef columns, *ksplit slices (0: chosen here) into m.out
+int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit) {
+  if (fmt != LLB_FM_Q4_K && fmt != LLB_FM_Q5_K && fmt != LLB_FM_Q6_K) return llb_fail("moe gemm: expert stacks of format %d have no kernel", fmt);
+  if (m.ef % 256 || m.d % 256) return llb_fail("moe gemm: widths %d, %d are not multiples of 256", m.ef, m.d);
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.K = down ? m.nslot * m.ef : m.d;
+  if (xp.K != a.K || (xp.NC != 8 && xp.NC != 16)) return llb_fail("moe gemm: planes of %d x %d columns, K is %d", xp.K, xp.NC, a.K);
+  a.nsb = a.K / 256; a.xp = xp; a.planes = 2; a.T = m.T; a.nmat = 0;
+  const int ntiles = down ? m.T * (m.d / 16) : m.T * m.nslot * (m.ef / 8);
+  int ks = 1;
+  if (down) ks = *ksplit > 0 ? *ksplit : gemm_pick_ksplit(fmt, xp.NC, ntiles, a.nsb, g_llb.sms);
+  ks = gemm_fix_ksplit(fmt, xp.NC, a.nsb, ks);
+  if (!down && ks != 1) return llb_fail("moe gemm: %d columns do not fit one K-slice", a.K);
+  a.ksplit = ks;
+  if (ksplit) *ksplit = ks;
+  const int NT = xp.NC / 8;
+#define MOE_GO(F) return NT == 1 ? launch_moe<F, 1>(s, down, a, m, ntiles) : launch_moe<F, 2>(s, down, a, m, ntiles)
+  if (fmt == LLB_FM_Q4_K) MOE_GO(LLB_FM_Q4_K);
+  if (fmt == LLB_FM_Q5_K) MOE_GO(LLB_FM_Q5_K);
+  MOE_GO(LLB_FM_Q6_K);
+#undef MOE_GO
 }
 
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {

@@ -43,6 +43,20 @@ struct GemmArgs {
                                // writes a tile's last K-slice adds the slices in index order into slice 0
 };
 
+// a routed-expert launch (moe.cuh)
+struct MoeArgs {
+  const uint8_t *W;     // GU or D stack
+  long long es;         // bytes per expert block
+  const int *ids;       // [T][nslot]
+  int nslot;            // k + 1
+  int ne;               // block ne is the shared expert; ids are clamped to 0..ne
+  int ef, d, T;
+  const int *n_rows;    // rows of the pass in flight (<= T); tiles of later rows are not computed
+  float *g, *u;         // k_moe_gu: [T][nslot * ef]
+  float *out;           // k_moe_dn: [ksplit][T][d]
+  long long split_stride;
+};
+
 template <int FMT> struct FmtTraits;
 template <> struct FmtTraits<LLB_FM_Q4_K> { enum { SB = 144, RS = 288, STAGES = 4 }; };
 template <> struct FmtTraits<LLB_FM_Q5_K> { enum { SB = 176, RS = 352, STAGES = 4 }; };

@@ -61,8 +61,36 @@ __device__ __forceinline__ void mma16816_z(float d[4], uint32_t a0, uint32_t a1,
 // which waits for whatever produces the activations, puts the CTA's slice of the planes and its side array into
 // shared memory and ends with a block-wide barrier --, then stream the CTA's tiles.  Warps beyond the format's
 // count and CTAs beyond the launch's only take part in the staging step's barriers.
-template <int FMT, int NT, class Stage>
-__device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage) {
+// Where a launch's row tiles live.  A policy says how many 16-row tiles there are, where tile i's rows and
+// the super-blocks of the CTA's K-slice start, and what to do with a finished tile.  G2MatsPlain is the
+// launch of up to four matrices that GemmArgs describes; the routed-expert launches (moe.cuh) find their
+// matrices through the expert ids an earlier kernel chose.
+//   EARLY   the weight addresses depend on no earlier kernel: the ring's prologue is issued before the wait
+//   Cur     per-thread cursor of the tile being copied
+//   locate  tile -> first row, row count, cursor;  src: row 0 of super-block (sb0 + c) of the slice
+template <int FMT> struct G2MatsPlain {
+  static constexpr bool EARLY = true;
+  const GemmArgs &a;
+  struct Cur { const uint8_t *W, *W0; };   // first code of the slice in row 0 of the matrix; the matrix itself
+  __device__ __forceinline__ int ntiles() const { return a.tile0[a.nmat]; }
+  __device__ __forceinline__ size_t row_bytes() const { return dev_row_bytes(FMT, a.K); }
+  __device__ __forceinline__ void locate(int tile, int sb0, Cur &c, int &row0, int &rows) const {
+    int m = 0;
+    while (m + 1 < a.nmat && tile >= a.tile0[m + 1]) m++;
+    row0 = (tile - a.tile0[m]) * 16; rows = a.m[m].rows;
+    c.W0 = a.m[m].W;
+    c.W = c.W0 + (size_t)sb0 * G2Traits<FMT>::SB;
+  }
+  __device__ __forceinline__ const uint8_t *src(const Cur &c, int sb0, int pc) const { return c.W + (size_t)pc * G2Traits<FMT>::SB; }
+  template <int NT> __device__ __forceinline__ void epilogue(int ks, int tile, float (&acc)[NT][4], int lane) const {
+    int m = 0;
+    while (m + 1 < a.nmat && tile >= a.tile0[m + 1]) m++;
+    gemm_epilogue<NT>(a, a.m[m], ks, tile, (tile - a.tile0[m]) * 16, acc, lane);
+  }
+};
+
+template <int FMT, int NT, class Stage, class Mats>
+__device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage, const Mats mats) {
   using TR = G2Traits<FMT>;
   constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = TR::WARPS;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
@@ -72,8 +100,9 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
   const int CS = nsl * 512 + TR::XPAD;
   uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * TR::AUX + (size_t)warp * G2_STAGES * 16 * RS;
   const uint32_t ring_s = smem_u32(ring);
-  const int ntiles = live ? a.tile0[a.nmat] : 0, nws = cps * G2_WARPS;   // a warp that is not live sees no tiles
-  const size_t rb = dev_row_bytes(FMT, a.K);
+  int ntiles = live && Mats::EARLY ? mats.ntiles() : 0;   // a warp that is not live sees no tiles
+  const int nws = cps * G2_WARPS;
+  const size_t rb = mats.row_bytes();
 
   // per-lane copy plan: piece i = lane + 32*it of the 16 x P sixteen-byte pieces of a stage
   uint32_t dst_rel[NIT], row_of[NIT], pc_of[NIT];
@@ -91,38 +120,46 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
   // tile of (CTA ci, warp w, round n) = (n * WARPS + w) * cps + ci: consecutive tiles go to different SMs, so the
   // SMs' tile counts differ by one at most (the kernel is issue-bound per SM: time follows the fullest SM)
   int p_tile = warp * cps + ci, p_c = 0;
-  const uint8_t *p_W = nullptr, *p_W0 = nullptr;   // first code of the slice in row 0 of the matrix; the matrix itself
+  typename Mats::Cur p_cur;
   uint32_t p_off[NIT];
   auto plan_tile = [&](int tile) {
     if (tile >= ntiles) return;
-    int m = 0;
-    while (m + 1 < a.nmat && tile >= a.tile0[m + 1]) m++;
-    const int row0 = (tile - a.tile0[m]) * 16, rows = a.m[m].rows;
-    p_W0 = a.m[m].W;
-    p_W = p_W0 + (size_t)sb0 * SB;
+    int row0, rows;
+    mats.locate(tile, sb0, p_cur, row0, rows);
 #pragma unroll
     for (int it = 0; it < NIT; it++) p_off[it] = (uint32_t)min(row0 + (int)row_of[it], rows - 1) * (uint32_t)rb + pc_of[it];
   };
   auto issue = [&](int stage) {
     if (p_tile < ntiles) {
-      const uint8_t *src = p_W + (size_t)p_c * SB;
+      const uint8_t *src = mats.src(p_cur, sb0, p_c);
       const uint32_t dst = ring_s + stage * 16 * RS;
 #pragma unroll
       for (int it = 0; it < NIT; it++)
         if (dst_rel[it] != 0xffffffffu) {
-          if (FMT == LLB_FM_Q8_0 && is_sc[it]) cp_async16(dst + dst_rel[it], p_W0 + (size_t)p_c * 16 + p_off[it]);
-          else cp_async16(dst + dst_rel[it], src + p_off[it]);
+          if constexpr (FMT == LLB_FM_Q8_0) {
+            if (is_sc[it]) { cp_async16(dst + dst_rel[it], p_cur.W0 + (size_t)p_c * 16 + p_off[it]); continue; }
+          }
+          cp_async16(dst + dst_rel[it], src + p_off[it]);
         }
       if (++p_c == nsl) { p_c = 0; p_tile += nws; plan_tile(p_tile); }
     }
     cp_async_commit();
   };
-  plan_tile(p_tile);
-  // weights first: the ring's prologue is in flight while the producer of the activations still
-  // runs (weights depend on no kernel), and while the activation slice is staged
+  if constexpr (Mats::EARLY) {
+    plan_tile(p_tile);
+    // weights first: the ring's prologue is in flight while the producer of the activations still
+    // runs (weights depend on no kernel), and while the activation slice is staged
 #pragma unroll 1
-  for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
-  stage(xh_s, xsf_s, CS, sb0, nsl);
+    for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
+    stage(xh_s, xsf_s, CS, sb0, nsl);
+  } else {
+    // the weight addresses come from an earlier kernel's choice: the wait (inside stage) comes first
+    stage(xh_s, xsf_s, CS, sb0, nsl);
+    ntiles = live ? mats.ntiles() : 0;
+    plan_tile(p_tile);
+#pragma unroll 1
+    for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
+  }
   // the XP group sits between prologue groups and later ones; from here on group accounting is per
   // warp again: G2_STAGES-1 chunks are complete, none pending
   int pstage = G2_STAGES - 1, cstage = 0;
@@ -286,9 +323,7 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
     __syncwarp();
     cstage = cstage + 1 == G2_STAGES ? 0 : cstage + 1;
     if (++c_c == nsl) {
-      int m = 0;
-      while (m + 1 < a.nmat && c_tile >= a.tile0[m + 1]) m++;
-      gemm_epilogue<NT>(a, a.m[m], ks, c_tile, (c_tile - a.tile0[m]) * 16, acc, lane);
+      mats.template epilogue<NT>(ks, c_tile, acc, lane);
       c_c = 0;
       c_tile += nws;
     }
@@ -323,5 +358,5 @@ template <int FMT, int NT>
 __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(const GemmArgs a, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
-  g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a});
+  g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, G2MatsPlain<FMT>{a});
 }

@@ -90,6 +90,9 @@ int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs,
 int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
                int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0);
 int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax);
+int op_silu_scaled_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax, const float *scale, int seg);
+// router logits (ne rows + the shared gate row of Wr, F32) on the normed rows h[T][d], then ids / wt [T][nk + 1]
+int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne, int nk, float *lg, int *ids, float *wt, const RowSet *rs, int Tmax);
 int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
               AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax);
 int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,

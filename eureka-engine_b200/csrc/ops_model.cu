@@ -134,7 +134,9 @@ int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, flo
 }
 
 // ---- silu(gate) * up -> planes (llb_t_siluq, tools/payload-spec2.patch:114-124) -----------------
-__global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs) {
+// scale (optional): the product of row t, columns [j seg, (j+1) seg) is multiplied by scale[t * (f / seg) + j]
+// (the routed experts' weights, folded into the activations the down matrices see)
+__global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, const float *__restrict__ scale, int seg) {
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   const int t = blockIdx.y, lane = threadIdx.x & 31;
@@ -146,12 +148,119 @@ __global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPla
     const size_t i = (size_t)t * f + c;
     const float4 gv = part_get4(g, i), uv = part_get4(u, i);
     h[0] = silu_f(gv.x) * uv.x; h[1] = silu_f(gv.y) * uv.y; h[2] = silu_f(gv.z) * uv.z; h[3] = silu_f(gv.w) * uv.w;
+    if (scale) {
+      const float w = scale[(size_t)t * (f / seg) + c / seg];
+      h[0] *= w; h[1] *= w; h[2] *= w; h[3] *= w;
+    }
   }
   xp_store4(xp, t, 2, c, h, lane, on);
 }
 int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax) {
   if (f % 32) return llb_fail("silu: f %d", f);
-  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs));
+  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs, (const float *)nullptr, f));
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+int op_silu_scaled_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax, const float *scale, int seg) {
+  if (f % 32 || seg % 4 || f % seg) return llb_fail("silu: f %d, segments of %d", f, seg);
+  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs, scale, seg));
+  CU_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---- the router of a routed-expert layer (host/llb_host.c:622-724; llb_moe_topk of tools/payload-moeany.patch) ----
+// logits: lg[t][r] = W[r] . h[t] for the ne router rows and the shared expert's gate row (row ne), F32
+// weights, a warp per row, all rows of the pass at once.
+__global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int nrows, float *__restrict__ lg,
+                                                    const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
+  const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= nrows) return;
+  float acc[SPEC_MAXT];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) acc[t] = 0.0f;
+  const float4 *wr = (const float4 *)(W + (size_t)r * d);
+  for (int c = lane; c < d / 4; c += 32) {
+    const float4 w = __ldg(wr + c);
+#pragma unroll
+    for (int t = 0; t < SPEC_MAXT; t++)
+      if (t < rs_n) {
+        const float4 x = *(const float4 *)(h + (size_t)t * d + 4 * c);
+        acc[t] += (w.x * x.x + w.y * x.y) + (w.z * x.z + w.w * x.w);
+      }
+  }
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++)
+    if (t < rs_n) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) lg[(size_t)t * nrows + r] = v;
+    }
+}
+// One warp per row of the pass: softmax over the ne logits (exp through double, as the reference's attn_exp),
+// the k largest probabilities in descending order with ties to the lower index, their weights divided by
+// their sum clamped at 6.103515625e-5; slot k is the shared expert (id ne) with weight sigmoid(its gate logit).
+__global__ void __launch_bounds__(32) k_moe_route(const float *__restrict__ lg, int ne, int nk, int *__restrict__ ids, float *__restrict__ wt,
+                                                  const RowSet *rs) {
+  int rs_n, rs_p0;
+  rs = rs_begin(rs, rs_n, rs_p0);
+  const int t = blockIdx.x, lane = threadIdx.x;
+  if (t >= rs_n) return;
+  const float *l = lg + (size_t)t * (ne + 1);
+  float p[32];   // experts lane, lane + 32, ...: ne <= 1024
+  float mx = -INFINITY;
+#pragma unroll
+  for (int q = 0; q < 32; q++) {
+    const int e = lane + 32 * q;
+    p[q] = e < ne ? l[e] : -INFINITY;
+    mx = fmaxf(mx, p[q]);
+  }
+  mx = warp_max(mx);
+  float sm = 0.0f;
+#pragma unroll
+  for (int q = 0; q < 32; q++) {
+    const int e = lane + 32 * q;
+    if (e < ne) { p[q] = (float)exp((double)(p[q] - mx)); sm += p[q]; }
+    else p[q] = -1.0f;
+  }
+  sm = warp_sum(sm);
+  const float inv = 1.0f / sm;
+#pragma unroll
+  for (int q = 0; q < 32; q++)
+    if (p[q] >= 0.0f) p[q] *= inv;
+  float s = 0.0f, mine_w = 0.0f;   // lane j keeps the weight of rank j
+  int mine_id = 0;
+  for (int j = 0; j < nk; j++) {
+    float bv = -1.0f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int q = 0; q < 32; q++)
+      if (p[q] > bv) { bv = p[q]; bi = lane + 32 * q; }   // ascending q: the lane's lowest index among equals
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int q = 0; q < 32; q++)
+        if (q == (bi >> 5)) p[q] = -2.0f;
+    }
+    s += bv;
+    if ((j & 31) == lane) { mine_w = bv; mine_id = bi; }
+  }
+  s = s < 6.103515625e-5f ? 6.103515625e-5f : s;
+  if (lane < nk) { ids[(size_t)t * (nk + 1) + lane] = mine_id; wt[(size_t)t * (nk + 1) + lane] = mine_w / s; }
+  if (lane == 0) {
+    ids[(size_t)t * (nk + 1) + nk] = ne;
+    wt[(size_t)t * (nk + 1) + nk] = 1.0f / (1.0f + (float)exp((double)-l[ne]));
+  }
+}
+int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne, int nk, float *lg, int *ids, float *wt, const RowSet *rs, int Tmax) {
+  if (ne < 1 || ne > 1024 || nk < 1 || nk > 32 || nk > ne || d % 4) return llb_fail("moe route: %d experts, top %d, d %d", ne, nk, d);
+  CU_OK(llb_launch(k_moe_router, dim3((ne + 1 + 7) / 8), dim3(256), (size_t)(0), s, Wr, h, d, ne + 1, lg, rs));
+  CU_OK(llb_launch(k_moe_route, dim3(Tmax), dim3(32), (size_t)(0), s, (const float *)lg, ne, nk, ids, wt, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }

@@ -61,6 +61,7 @@ def lib() -> C.CDLL:
             "llb_spec_generate": (i32, [vp, i32, vp, vp]), "llb_spec_pass": (i32, [vp, i32, i32, vp]),
             "llb_spec_position": (i32, [vp]), "llb_spec_stats": (i32, [vp, vp]),
             "llb_spec_read_state": (i32, [vp, i32, i32, i32, vp, sz]), "llb_spec_read_logits": (i32, [vp, i32, vp]),
+            "llb_spec_moe_ffn": (i32, [vp, i32, i32, vp, vp, vp, vp]),
             "llb_spec_run_cycles": (i32, [vp, i32, vp, i32]), "llb_spec_time_verify": (i32, [vp, i32, vp]),
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
             "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
@@ -227,3 +228,15 @@ class SpecEngine:
         out = np.zeros(self.vocab, np.float32)
         check(self.L.llb_spec_read_logits(self.h, r, out.ctypes.data), "llb_spec_read_logits")
         return out
+
+    def moe_ffn(self, il: int, h2):
+        """Layer il's routed-expert FFN alone on normed rows h2[T][d]: (out[T][d], ids[T][k+1], wt[T][k+1])."""
+        import numpy as np
+        h2 = np.ascontiguousarray(h2, np.float32)
+        T, d = h2.shape
+        ns = self.cfg.n_experts_used + 1
+        out = np.zeros((T, d), np.float32)
+        ids = np.zeros((T, ns), np.int32)
+        wt = np.zeros((T, ns), np.float32)
+        check(self.L.llb_spec_moe_ffn(self.h, il, T, h2.ctypes.data, out.ctypes.data, ids.ctypes.data, wt.ctypes.data), "llb_spec_moe_ffn")
+        return out, ids, wt

@@ -133,6 +133,12 @@ LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap);
 LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out);
 LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n);
 LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out);
+/* Test entry for models with a routed-expert FFN (host/llb_host.c:622-724 llb_moe_run; kernels llb_moe_topk,
+ * llb_moe_gu, llb_moe_dn of tools/payload-moeany.patch): layer il's expert FFN alone on T normed rows h2[T][d] in
+ * host memory.  out[T][d]: sum_j wt_j down_j(silu(gate_j h2) * up_j h2) + sigmoid(shared gate) * shared(h2), no
+ * residual; ids, wt [T][k + 1]: the chosen experts in rank order and their weights, slot k = the shared expert (id =
+ * expert count) and its gate.  Resets the sequence state. */
+LLB_API int llb_spec_moe_ffn(llb_spec *m, int il, int T, const float *h2, float *out, int *ids, float *wt);
 
 #ifdef __cplusplus
 }
