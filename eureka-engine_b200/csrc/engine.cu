@@ -18,6 +18,7 @@
 
 #include "../../include/llb_b200.h"
 #include "model.cuh"
+#include "gguf.cuh"
 
 struct DevMat { uint8_t *w = nullptr; int rows = 0, cols = 0, fmt = -1; };
 struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; size_t cap = 0; };   // K-slice partial sums of one matrix (cap: floats allocated)
@@ -32,7 +33,8 @@ struct FfnW { DevMat gate, up, down; float *post = nullptr; bool moe = false; fl
 struct DeltaW { DevMat qkv, z, beta, alpha, out; float *dt = nullptr, *a = nullptr, *conv = nullptr, *norm = nullptr; };
 struct LayerW { bool full = false; float *attn_norm = nullptr; AttnW at; DeltaW dn; FfnW ffn; };
 
-struct TensorRec { uint64_t off, bytes; int rows, cols, fmt; };
+// blocked: Q8_0 in GGUF's [f16 d][32 x int8] blocks (host memory only), re-sliced to the row-split layout at upload
+struct TensorRec { uint64_t off, bytes; int rows, cols, fmt; bool blocked = false; };
 
 struct llb_spec {
   // configuration (index.tsv #cfg keys, tools/qwen35_engine.c:386-409)
@@ -184,9 +186,12 @@ static int parse_index(llb_spec *m, const char *text, std::unordered_map<std::st
     unsigned long long off, nb;
     int rows, cols;
     if (sscanf(line.c_str(), "%127[^\t]\t%llu\t%llu\t%d\t%d\t%31[^\t\n]", name, &off, &nb, &rows, &cols, ty) != 6) continue;
-    int fm = fmt_of(ty);
+    const bool blocked = !strcmp(ty, "Q8_0G");
+    int fm = blocked ? LLB_FM_Q8_0 : fmt_of(ty);
     if (fm < 0) return llb_fail("index: tensor %s has unsupported type %s", name, ty);
-    tab[name] = TensorRec{off, nb, rows, cols, fm};
+    TensorRec tr{off, nb, rows, cols, fm};
+    tr.blocked = blocked;
+    tab[name] = tr;
   }
   return 0;
 }
@@ -201,6 +206,25 @@ static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, int
                                        (unsigned long long)t.bytes, want);
   void *dst = dalloc(m, (size_t)t.rows * dev_row_bytes(t.fmt, t.cols));
   if (!dst) return -1;
+  if (t.blocked) {
+    // [f16 d][32 q] x cols/32 per row -> [cols q][cols/32 f16 d] per row (tools/gguf2pack.c:25-27), 4096 rows at a time
+    if (on_device) return llb_fail("index: blocked Q8_0 tensors are read from host memory only");
+    const size_t rb = (size_t)t.cols + (size_t)t.cols / 16, nb = (size_t)t.cols / 32;
+    std::vector<uint8_t> tmp;
+    for (int r0 = 0; r0 < t.rows; r0 += 4096) {
+      const int nr = t.rows - r0 < 4096 ? t.rows - r0 : 4096;
+      tmp.resize((size_t)nr * rb);
+      for (int r = 0; r < nr; r++) {
+        const uint8_t *src = pack + t.off + (size_t)(r0 + r) * rb;
+        uint8_t *q = tmp.data() + (size_t)r * rb, *sc = q + t.cols;
+        for (size_t b = 0; b < nb; b++) { memcpy(sc + 2 * b, src + 34 * b, 2); memcpy(q + 32 * b, src + 34 * b + 2, 32); }
+      }
+      CK(llb_b200_weight_upload(t.fmt, nr, t.cols, tmp.data(), 0, (llb_dptr)(uintptr_t)((uint8_t *)dst + (size_t)r0 * dev_row_bytes(t.fmt, t.cols))));
+    }
+    dedupe[t.off] = dst;
+    *out = dst;
+    return 0;
+  }
   CK(llb_b200_weight_upload(t.fmt, t.rows, t.cols, pack + t.off, on_device, (llb_dptr)(uintptr_t)dst));
   dedupe[t.off] = dst;
   *out = dst;
@@ -223,8 +247,20 @@ static int load_moe(llb_spec *m, FfnW &w, const std::string &p, const std::unord
   };
   TensorRec r_in, r_sh, eg, eu, ed, sg, su, sd;
   CK(rec("ffn_gate_inp.weight", ne, d, r_in)); CK(rec("ffn_gate_inp_shexp.weight", 1, d, r_sh));
-  CK(rec("ffn_gate_exps.weight", ne * ef, d, eg)); CK(rec("ffn_up_exps.weight", ne * ef, d, eu)); CK(rec("ffn_down_exps.weight", ne * d, ef, ed));
+  // the experts' gate and up either as two stacks or as one of [gate rows | up rows] per expert (ffn_gate_up_exps,
+  // host/llb_host.c:629 "fz")
+  const bool fused = tab.count(p + "ffn_gate_up_exps.weight") != 0;
+  size_t gu_stride = (size_t)ef;   // rows between consecutive experts in the gate (and up) source
+  if (fused) {
+    CK(rec("ffn_gate_up_exps.weight", ne * 2 * ef, d, eg));
+    eu = eg; eu.off += (uint64_t)ef * pack_row_bytes(eg.fmt, d);
+    gu_stride = 2 * (size_t)ef;
+  } else {
+    CK(rec("ffn_gate_exps.weight", ne * ef, d, eg)); CK(rec("ffn_up_exps.weight", ne * ef, d, eu));
+  }
+  CK(rec("ffn_down_exps.weight", ne * d, ef, ed));
   CK(rec("ffn_gate_shexp.weight", ef, d, sg)); CK(rec("ffn_up_shexp.weight", ef, d, su)); CK(rec("ffn_down_shexp.weight", d, ef, sd));
+  for (const TensorRec *t : {&eg, &eu, &ed, &sg, &su, &sd}) if (t->blocked) return llb_fail("%s: blocked Q8_0 expert stacks have no kernel", p.c_str());
   if (r_in.fmt != LLB_FM_F32 || r_sh.fmt != LLB_FM_F32) return llb_fail("%sffn_gate_inp must be F32", p.c_str());
   if (eg.fmt != eu.fmt || sg.fmt != eg.fmt || su.fmt != eg.fmt || sd.fmt != ed.fmt)
     return llb_fail("%s: the shared expert and the expert stacks must share their formats (gate/up %d %d %d %d, down %d %d)", p.c_str(), eg.fmt, eu.fmt, sg.fmt,
@@ -244,8 +280,8 @@ static int load_moe(llb_spec *m, FfnW &w, const std::string &p, const std::unord
   w.dn = (uint8_t *)dalloc(m, (size_t)(ne + 1) * w.es_dn);
   if (!w.gu || !w.dn) return -1;
   for (int e = 0; e <= ne; e++) {
-    const uint8_t *g = e < ne ? pack + eg.off + (size_t)e * ef * pb_gu : pack + sg.off;
-    const uint8_t *u = e < ne ? pack + eu.off + (size_t)e * ef * pb_gu : pack + su.off;
+    const uint8_t *g = e < ne ? pack + eg.off + (size_t)e * gu_stride * pb_gu : pack + sg.off;
+    const uint8_t *u = e < ne ? pack + eu.off + (size_t)e * gu_stride * pb_gu : pack + su.off;
     const uint8_t *dn = e < ne ? pack + ed.off + (size_t)e * d * pb_dn : pack + sd.off;
     CK(llb_b200_weight_upload(eg.fmt, ef, d, g, on_device, (llb_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu)));
     CK(llb_b200_weight_upload(eg.fmt, ef, d, u, on_device, (llb_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu + (size_t)ef * rb_gu)));
@@ -699,6 +735,24 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
     return nullptr;
   }
   return m;
+}
+
+// The same engine from a GGUF file (qwen35 / qwen35moe): the header gives the index, the mapped file is the pack.
+LLB_API llb_spec *llb_spec_open_gguf(const char *path, const void *mtp, size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers) {
+  GgufFile g;
+  if (gguf_map(path, g)) return nullptr;
+  llb_spec *m = llb_spec_open(g.index.c_str(), g.map, g.size, 0, mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers);
+  gguf_unmap(g);   // every tensor now lives on the device
+  return m;
+}
+// The index text llb_spec_open_gguf derives from a file's header (no GPU needed): returns its length, or -1.
+LLB_API int llb_b200_gguf_index(const char *path, char *buf, int cap) {
+  GgufFile g;
+  if (gguf_map(path, g)) return -1;
+  const int n = (int)g.index.size();
+  if (buf && cap > 0) { const int c = n < cap - 1 ? n : cap - 1; memcpy(buf, g.index.data(), (size_t)c); buf[c] = 0; }
+  gguf_unmap(g);
+  return n;
 }
 
 LLB_API void llb_spec_close(llb_spec *m) {

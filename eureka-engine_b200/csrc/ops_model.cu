@@ -169,64 +169,30 @@ int op_silu_scaled_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, con
 }
 
 // ---- the router of a routed-expert layer (host/llb_host.c:622-724; llb_moe_topk of tools/payload-moeany.patch) ----
-// logits: lg[t][r] = W[r] . h[t] for the ne router rows and the shared expert's gate row (row ne), F32
-// weights, a warp per row, all rows of the pass at once.
-__global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int nrows, float *__restrict__ lg,
-                                                    const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= nrows) return;
-  float acc[SPEC_MAXT];
-#pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++) acc[t] = 0.0f;
-  const float4 *wr = (const float4 *)(W + (size_t)r * d);
-  for (int c = lane; c < d / 4; c += 32) {
-    const float4 w = __ldg(wr + c);
-#pragma unroll
-    for (int t = 0; t < SPEC_MAXT; t++)
-      if (t < rs_n) {
-        const float4 x = *(const float4 *)(h + (size_t)t * d + 4 * c);
-        acc[t] += (w.x * x.x + w.y * x.y) + (w.z * x.z + w.w * x.w);
-      }
-  }
-#pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++)
-    if (t < rs_n) {
-      const float v = warp_sum(acc[t]);
-      if (lane == 0) lg[(size_t)t * nrows + r] = v;
-    }
-}
-// One warp per row of the pass: softmax over the ne logits (exp through double, as the reference's attn_exp),
-// the k largest probabilities in descending order with ties to the lower index, their weights divided by
-// their sum clamped at 6.103515625e-5; slot k is the shared expert (id ne) with weight sigmoid(its gate logit).
-__global__ void __launch_bounds__(32) k_moe_route(const float *__restrict__ lg, int ne, int nk, int *__restrict__ ids, float *__restrict__ wt,
-                                                  const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  const int t = blockIdx.x, lane = threadIdx.x;
-  if (t >= rs_n) return;
-  const float *l = lg + (size_t)t * (ne + 1);
-  float p[32];   // experts lane, lane + 32, ...: ne <= 1024
+// One warp per row of the pass: softmax over the ne logits, the k largest probabilities in descending order with
+// ties to the lower index, their weights divided by their sum clamped at 6.103515625e-5; slot k is the shared
+// expert (id ne) with weight sigmoid(its gate logit).
+template <int NQ> __device__ __forceinline__ void moe_route_row(const float *l, int ne, int nk, int *ids, float *wt, int lane) {
+  float p[NQ];   // experts lane, lane + 32, ...: ne <= 32 NQ
   float mx = -INFINITY;
 #pragma unroll
-  for (int q = 0; q < 32; q++) {
+  for (int q = 0; q < NQ; q++) {
     const int e = lane + 32 * q;
-    p[q] = e < ne ? l[e] : -INFINITY;
+    p[q] = e < ne ? __ldcg(l + e) : -INFINITY;
     mx = fmaxf(mx, p[q]);
   }
   mx = warp_max(mx);
   float sm = 0.0f;
 #pragma unroll
-  for (int q = 0; q < 32; q++) {
+  for (int q = 0; q < NQ; q++) {
     const int e = lane + 32 * q;
-    if (e < ne) { p[q] = (float)exp((double)(p[q] - mx)); sm += p[q]; }
+    if (e < ne) { p[q] = expf(p[q] - mx); sm += p[q]; }
     else p[q] = -1.0f;
   }
   sm = warp_sum(sm);
   const float inv = 1.0f / sm;
 #pragma unroll
-  for (int q = 0; q < 32; q++)
+  for (int q = 0; q < NQ; q++)
     if (p[q] >= 0.0f) p[q] *= inv;
   float s = 0.0f, mine_w = 0.0f;   // lane j keeps the weight of rank j
   int mine_id = 0;
@@ -234,7 +200,7 @@ __global__ void __launch_bounds__(32) k_moe_route(const float *__restrict__ lg, 
     float bv = -1.0f;
     int bi = 0x7fffffff;
 #pragma unroll
-    for (int q = 0; q < 32; q++)
+    for (int q = 0; q < NQ; q++)
       if (p[q] > bv) { bv = p[q]; bi = lane + 32 * q; }   // ascending q: the lane's lowest index among equals
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) {
@@ -244,23 +210,79 @@ __global__ void __launch_bounds__(32) k_moe_route(const float *__restrict__ lg, 
     }
     if ((bi & 31) == lane) {
 #pragma unroll
-      for (int q = 0; q < 32; q++)
+      for (int q = 0; q < NQ; q++)
         if (q == (bi >> 5)) p[q] = -2.0f;
     }
     s += bv;
-    if ((j & 31) == lane) { mine_w = bv; mine_id = bi; }
+    if (j == lane) { mine_w = bv; mine_id = bi; }
   }
   s = s < 6.103515625e-5f ? 6.103515625e-5f : s;
-  if (lane < nk) { ids[(size_t)t * (nk + 1) + lane] = mine_id; wt[(size_t)t * (nk + 1) + lane] = mine_w / s; }
+  if (lane < nk) { ids[lane] = mine_id; wt[lane] = mine_w / s; }
   if (lane == 0) {
-    ids[(size_t)t * (nk + 1) + nk] = ne;
-    wt[(size_t)t * (nk + 1) + nk] = 1.0f / (1.0f + (float)exp((double)-l[ne]));
+    ids[nk] = ne;
+    wt[nk] = 1.0f / (1.0f + expf(-__ldcg(l + ne)));
   }
 }
+// Router logits lg[t][r] = W[r] . h[t] for the ne router rows and the shared expert's gate row (row ne): F32
+// weights, a block per row (every load of the row in flight at once), all rows of the pass.  The block that
+// finishes last (a counter, no waiting) then routes: its warp t takes row t of the pass.
+template <int NQ>
+__global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int ne, int nk, float *__restrict__ lg,
+                                                    int *__restrict__ ids, float *__restrict__ wt, unsigned int *__restrict__ ctr, const RowSet *rs) {
+  int rs_n, rs_p0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.x, nrows = ne + 1;
+  __shared__ float red[8][SPEC_MAXT];
+  __shared__ unsigned int last;
+  // the row's weights depend on no kernel: fetched before the wait (two float4 per thread cover d <= 2048)
+  const float4 *wr = (const float4 *)(W + (size_t)r * d);
+  const int c0 = threadIdx.x, c1 = threadIdx.x + 256, nc = d / 4;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 w0 = c0 < nc ? __ldg(wr + c0) : z4, w1 = c1 < nc ? __ldg(wr + c1) : z4;
+  rs = rs_begin(rs, rs_n, rs_p0);
+  float acc[SPEC_MAXT];
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    acc[t] = 0.0f;
+    if (t < rs_n) {
+      const float4 *x = (const float4 *)(h + (size_t)t * d);
+      if (c0 < nc) { const float4 v = x[c0]; acc[t] += (w0.x * v.x + w0.y * v.y) + (w0.z * v.z + w0.w * v.w); }
+      if (c1 < nc) { const float4 v = x[c1]; acc[t] += (w1.x * v.x + w1.y * v.y) + (w1.z * v.z + w1.w * v.w); }
+      for (int c = threadIdx.x + 512; c < nc; c += 256) {
+        const float4 w = __ldg(wr + c), v = x[c];
+        acc[t] += (w.x * v.x + w.y * v.y) + (w.z * v.z + w.w * v.w);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < SPEC_MAXT; t++) {
+    const float v = warp_sum(acc[t]);
+    if (lane == 0) red[warp][t] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < rs_n) {
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) v += red[w][threadIdx.x];
+    lg[(size_t)threadIdx.x * nrows + r] = v;
+    __threadfence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(ctr, 1u);
+  __syncthreads();
+  if (last != gridDim.x - 1) return;
+  __threadfence();
+  if (threadIdx.x == 0) *ctr = 0;   // ready for the next launch (launches of one stream do not overlap here)
+  for (int t = warp; t < rs_n; t += 8) moe_route_row<NQ>(lg + (size_t)t * nrows, ne, nk, ids + (size_t)t * (nk + 1), wt + (size_t)t * (nk + 1), lane);
+}
+static unsigned int *g_moe_ctr = nullptr;
 int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne, int nk, float *lg, int *ids, float *wt, const RowSet *rs, int Tmax) {
   if (ne < 1 || ne > 1024 || nk < 1 || nk > 32 || nk > ne || d % 4) return llb_fail("moe route: %d experts, top %d, d %d", ne, nk, d);
-  CU_OK(llb_launch(k_moe_router, dim3((ne + 1 + 7) / 8), dim3(256), (size_t)(0), s, Wr, h, d, ne + 1, lg, rs));
-  CU_OK(llb_launch(k_moe_route, dim3(Tmax), dim3(32), (size_t)(0), s, (const float *)lg, ne, nk, ids, wt, rs));
+  if (!g_moe_ctr) {
+    CU_OK(cudaMalloc(&g_moe_ctr, 4));
+    CU_OK(cudaMemset(g_moe_ctr, 0, 4));
+  }
+  if (ne <= 256) CU_OK(llb_launch(k_moe_router<8>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs));
+  else CU_OK(llb_launch(k_moe_router<32>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs));
   CU_OK(cudaGetLastError());
   return 0;
 }

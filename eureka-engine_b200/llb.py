@@ -62,6 +62,7 @@ def lib() -> C.CDLL:
             "llb_spec_position": (i32, [vp]), "llb_spec_stats": (i32, [vp, vp]),
             "llb_spec_read_state": (i32, [vp, i32, i32, i32, vp, sz]), "llb_spec_read_logits": (i32, [vp, i32, vp]),
             "llb_spec_moe_ffn": (i32, [vp, i32, i32, vp, vp, vp, vp]),
+            "llb_spec_open_gguf": (vp, [C.c_char_p, vp, sz, i32, i32, i32, i32]), "llb_b200_gguf_index": (i32, [C.c_char_p, vp, i32]),
             "llb_spec_run_cycles": (i32, [vp, i32, vp, i32]), "llb_spec_time_verify": (i32, [vp, i32, vp]),
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
             "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
@@ -136,6 +137,22 @@ class SpecEngine:
                                         layers), "llb_spec_open")
         self.k, self.vocab, self.d = k, pack.cfg.vocab_size, pack.cfg.d_model
         self.cfg = pack.cfg
+
+    @classmethod
+    def from_gguf(cls, path: str, cfg, mtp=None, k: int = 3, max_ctx: int = 4096, layers: int = 0):
+        """The engine opened straight from a GGUF file (llb_spec_open_gguf); cfg only names vocabulary and widths
+        for the Python-side helpers."""
+        import numpy as np
+        self = cls.__new__(cls)
+        self.L = lib()
+        if mtp is None:
+            mptr, mbytes = None, 0
+        else:
+            self._mtp_keep = np.frombuffer(mtp, dtype=np.uint8)
+            mptr, mbytes = self._mtp_keep.ctypes.data, len(mtp)
+        self.h = handle(self.L.llb_spec_open_gguf(path.encode(), mptr, mbytes, 0, k, max_ctx, layers), "llb_spec_open_gguf")
+        self.k, self.vocab, self.d, self.cfg = k, cfg.vocab_size, cfg.d_model, cfg
+        return self
 
     def close(self):
         if getattr(self, "h", None):
@@ -240,3 +257,14 @@ class SpecEngine:
         wt = np.zeros((T, ns), np.float32)
         check(self.L.llb_spec_moe_ffn(self.h, il, T, h2.ctypes.data, out.ctypes.data, ids.ctypes.data, wt.ctypes.data), "llb_spec_moe_ffn")
         return out, ids, wt
+
+
+def gguf_index(path: str) -> str:
+    """The index text the library derives from a GGUF header (no GPU needed)."""
+    L = lib()
+    n = L.llb_b200_gguf_index(path.encode(), None, 0)
+    if n < 0:
+        raise LlbError("llb_b200_gguf_index failed: " + L.llb_b200_last_error().decode())
+    buf = C.create_string_buffer(n + 1)
+    L.llb_b200_gguf_index(path.encode(), buf, n + 1)
+    return buf.value.decode()

@@ -609,3 +609,94 @@ def q4k_random_blocks(rows: int, cols: int, seed: int = 2, device="cpu") -> torc
         dd = torch.from_numpy(np.abs(g.standard_normal((rows, nsb, 2), dtype=np.float32) * np.float32(0.01)))
     blk = torch.cat([_bytes_of(_f16(dd)).reshape(rows, nsb, 4), _pack_scale_min(sc, mn), qs], dim=-1)
     return blk.reshape(rows, nsb * 144)
+
+
+# --------------------------------------------------------------------------------------------
+# a pack written as a GGUF file (what llb_spec_open_gguf reads)
+# --------------------------------------------------------------------------------------------
+
+def write_gguf(pack: Pack, path: str, fused_gate_up: bool = False, nextn: int = 0) -> str:
+    """Write `pack` as a GGUF file of architecture qwen35 / qwen35moe with the metadata keys the reference reads
+    (tools/gguf2pack.c:541-600) and the pack's quantised bytes: K-quants and F32 verbatim, Q8_0 re-sliced from the
+    pack's row-split rows to GGUF's [f16 d][32 x int8] blocks, expert stacks as 3-D tensors (optionally gate and
+    up fused into ffn_gate_up_exps, [expert][gate rows | up rows]).  A tied head is written as no output.weight.
+    `nextn` only adds the key nextn_predict_layers and that many to block_count (no tensors), to exercise the
+    reader's trunk-length rule.  Needs the gguf Python package."""
+    from gguf import GGUFWriter, GGMLQuantizationType as Q
+    c = pack.cfg
+    arch = "qwen35moe" if c.n_experts else "qwen35"
+    w = GGUFWriter(path, arch)
+    w.add_uint32(f"{arch}.block_count", c.n_layers + nextn)
+    if nextn:
+        w.add_uint32(f"{arch}.nextn_predict_layers", nextn)
+    w.add_uint32(f"{arch}.embedding_length", c.d_model)
+    w.add_uint32(f"{arch}.feed_forward_length", c.d_ff)
+    w.add_uint32(f"{arch}.attention.head_count", c.n_heads)
+    w.add_uint32(f"{arch}.attention.head_count_kv", c.n_kv_heads)
+    w.add_uint32(f"{arch}.attention.key_length", c.head_dim)
+    w.add_uint32(f"{arch}.attention.value_length", c.head_dim)
+    w.add_float32(f"{arch}.attention.layer_norm_rms_epsilon", c.eps)
+    w.add_uint32(f"{arch}.rope.dimension_count", c.rope_dim)
+    w.add_float32(f"{arch}.rope.freq_base", c.rope_base)
+    w.add_uint32(f"{arch}.ssm.conv_kernel", c.conv_kernel)
+    w.add_uint32(f"{arch}.ssm.state_size", c.ssm_state)
+    w.add_uint32(f"{arch}.ssm.group_count", c.ssm_groups)
+    w.add_uint32(f"{arch}.ssm.time_step_rank", c.ssm_heads)
+    w.add_uint32(f"{arch}.ssm.inner_size", c.vdc)
+    w.add_uint32(f"{arch}.full_attention_interval", c.interval)
+    w.add_uint32(f"{arch}.vocab_size", c.vocab_size)
+    if c.n_experts:
+        w.add_uint32(f"{arch}.expert_count", c.n_experts)
+        w.add_uint32(f"{arch}.expert_used_count", c.n_experts_used)
+        w.add_uint32(f"{arch}.expert_feed_forward_length", c.d_expert)
+        w.add_uint32(f"{arch}.expert_shared_feed_forward_length", c.d_shared)
+    qt = {"Q4_K": Q.Q4_K, "Q5_K": Q.Q5_K, "Q6_K": Q.Q6_K, "Q8_0": Q.Q8_0}
+    tied = c.tied_head
+    todo = []
+
+    def blocked_q8(raw: np.ndarray, rows: int, cols: int) -> np.ndarray:
+        nb = cols // 32
+        a = raw.reshape(rows, cols + 2 * nb)
+        out = np.empty((rows, nb, 34), np.uint8)
+        out[:, :, 0:2] = a[:, cols:].reshape(rows, nb, 2)
+        out[:, :, 2:] = a[:, :cols].reshape(rows, nb, 32)
+        return out.reshape(rows, nb * 34)
+
+    def add(name, e, raw, lead=None):
+        """lead: leading dimensions replacing e.rows (expert stacks)."""
+        shape_rows = lead if lead is not None else (e.rows,)
+        if e.ty == "F32":
+            arr = raw.view(np.float32).reshape(*(shape_rows if e.rows > 1 else ()), e.cols)
+            w.add_tensor_info(name, arr.shape, np.dtype(np.float32), arr.nbytes)
+        else:
+            rows = int(np.prod(shape_rows))
+            if e.ty == "Q8_0":
+                raw = blocked_q8(raw, rows, e.cols)
+            arr = raw.reshape(*shape_rows, -1)
+            w.add_tensor_info(name, arr.shape, np.dtype(np.uint8), arr.nbytes, raw_dtype=qt[e.ty])
+        todo.append(np.ascontiguousarray(arr))
+
+    skip = set()
+    for e in pack.entries:
+        if e.name in skip or (e.name == "output.weight" and tied):
+            continue
+        raw = pack.raw(e.name).cpu().numpy()
+        if e.name.endswith("ffn_gate_exps.weight") and fused_gate_up:
+            up = pack.by_name[e.name.replace("ffn_gate_exps", "ffn_up_exps")]
+            ne, ef = c.n_experts, c.d_expert
+            g3 = raw.reshape(ne, ef, -1)
+            u3 = pack.raw(up.name).cpu().numpy().reshape(ne, ef, -1)
+            both = np.concatenate([g3, u3], axis=1).reshape(-1)
+            add(e.name.replace("ffn_gate_exps", "ffn_gate_up_exps"), e, both, lead=(ne, 2 * ef))
+            skip.add(up.name)
+            continue
+        if e.name.endswith("_exps.weight"):
+            ne = c.n_experts
+            add(e.name, e, raw, lead=(ne, e.rows // ne))
+            continue
+        add(e.name, e, raw)
+    w.write_header_to_file(); w.write_kv_data_to_file(); w.write_ti_data_to_file()
+    for arr in todo:
+        w.write_tensor_data(arr)
+    w.close()
+    return path

@@ -6,6 +6,9 @@
     python eureka-engine_b200/profile_cases.py verify LAYERS [PROMPT]       two replays of the verify pass of the
                                                                             27B-shape model truncated to LAYERS,
                                                                             bracketed by cudaProfilerStart/Stop
+    python eureka-engine_b200/profile_cases.py moe LAYERS [K] [PROMPT]      the MoE configuration (256 experts, top 8 +
+                                                                            shared, Q4_K_S) truncated to LAYERS: verify-pass
+                                                                            time, bytes and per-op times, prompt-lookup drafter
 """
 import os
 import sys
@@ -67,6 +70,42 @@ def case_verify(layers, nprompt=3011):
     eng.close()
 
 
+def moe_verify_bytes(pack, packs, T):
+    """Algorithmic bytes of one verify pass of an MoE model at context 0: every dense matrix, the routers, the head
+    and the shared experts once; each of the T x k (row, rank) slots reads its expert's three matrices once."""
+    c = pack.cfg
+    dense = sum(e.nbytes for e in pack.entries
+                if e.name == "output.weight" or "ffn_gate_inp" in e.name
+                or (e.name.startswith("blk.") and e.rows > 1 and e.ty != "F32" and "_exps" not in e.name))
+    routed = T * c.n_experts_used * sum(e.nbytes / c.n_experts for e in pack.entries if "_exps" in e.name)
+    return dense, routed
+
+
+def case_moe(layers, k=3, nprompt=512):
+    pkg = graft.load_package()
+    llb, packs = pkg.llb, pkg.packs
+    llb.init(0)
+    cfg = packs.cfg_c3()
+    pack = packs.build_pack(cfg, device="cuda:0", layers=layers if layers < cfg.n_layers else None)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    eng = llb.SpecEngine(pack, None, k=k, max_ctx=nprompt + 512)
+    eng.prefill(packs.synth_prompt(4, nprompt, cfg.vocab_size))
+    ids, got = eng.run_cycles(8)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    ms1 = eng.time_verify(1)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ms = eng.time_verify(20)
+    dense, routed = moe_verify_bytes(pack, packs, k + 1)
+    print(f"moe verify: layers {pack.cfg.n_layers} T {k + 1} {ms:.3f} ms/pass (first {ms1:.3f}); dense+shared {dense / 1e9:.3f} GB, "
+          f"routed slots {routed / 1e9:.3f} GB -> {(dense + routed) / ms / 1e6:.1f} GB/s; kernels {eng.graph_nodes(2)}")
+    for n, (c, t) in sorted(eng.profile_verify().items(), key=lambda kv: -kv[1][1]):
+        print(f"{n:18s} n={c:4d} total_us={t:9.1f}")
+    eng.close()
+
+
 if __name__ == "__main__":
     if sys.argv[1] == "gemm":
         case_gemm(sys.argv[2], [int(v) for v in sys.argv[3].split(",")], int(sys.argv[4]))
@@ -74,5 +113,7 @@ if __name__ == "__main__":
         case_gemm("Q4_K", [int(v) for v in sys.argv[2].split(",")], int(sys.argv[3]), tcgen05=True)
     elif sys.argv[1] == "verify":
         case_verify(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3011)
+    elif sys.argv[1] == "moe":
+        case_moe(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3, int(sys.argv[4]) if len(sys.argv) > 4 else 512)
     else:
         raise SystemExit(__doc__)

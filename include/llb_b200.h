@@ -132,6 +132,16 @@ LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap);
 /* out[19] = cycles, rows, served, drafted[8], accepted[8] by draft position (host/llb_host.c:1513-1523) */
 LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out);
 LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n);
+/* The engine straight from a GGUF file of architecture qwen35 or qwen35moe (replaces the reference's GGUF ->
+ * pack step, tools/gguf2pack.c, and its in-place reader host/llb_gguf.c:854-865): configuration from the
+ * metadata keys of tools/gguf2pack.c:541-600, tensors uploaded from the mapped file (F32, Q4_K, Q5_K, Q6_K
+ * verbatim; Q8_0 re-sliced from GGUF blocks to the pack's row-split layout), tied head when the file has no
+ * output.weight, nextn blocks left out of the trunk.  mtp: an optional AUX1 / MTP1 drafter image as for
+ * llb_spec_open.  NULL on failure (llb_last_error). */
+LLB_API llb_spec *llb_spec_open_gguf(const char *path, const void *mtp, size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers);
+/* the index text derived from a GGUF header ("#cfg" lines, then name, file offset, bytes, rows, cols, type per
+ * tensor); returns its length or -1; needs no GPU */
+LLB_API int llb_b200_gguf_index(const char *path, char *buf, int cap);
 LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out);
 /* Test entry for models with a routed-expert FFN (host/llb_host.c:622-724 llb_moe_run; kernels llb_moe_topk,
  * llb_moe_gu, llb_moe_dn of tools/payload-moeany.patch): layer il's expert FFN alone on T normed rows h2[T][d] in

@@ -129,3 +129,64 @@ def test_aggregate_two_gloo_ranks():
         p.join(60)
     for rank, t, c in out:
         assert t == [11.0, 5.0] and c == [300.0, 7.0]
+
+
+# ---- GGUF reader (no GPU: the header only) -------------------------------------------------------
+def _index_fields(text):
+    cfg, tens = {}, {}
+    for line in text.splitlines():
+        if line.startswith("#cfg\t"):
+            _, k, v = line.split("\t")
+            cfg[k] = v
+        elif line and not line.startswith("#"):
+            n, off, nb, rows, cols, ty = line.split("\t")[:6]
+            tens[n] = (int(off), int(nb), int(rows), int(cols), ty)
+    return cfg, tens
+
+
+@pytest.mark.parametrize("case", ["q8_tied", "q4_k_m_nextn", "moe_fused", "moe_split"])
+def test_gguf_header_gives_the_packs_index(pkg, packs, tmp_path, case):
+    """A pack written as GGUF and read back by the library: same configuration keys, same tensors with the same
+    shapes and types (Q8_0 marked as GGUF-blocked), bytes at the recorded file offsets equal the pack's
+    (tools/gguf2pack.c:541-600 for the keys; block_count counts nextn blocks, which are left out)."""
+    kw = {}
+    if case == "q8_tied":
+        cfg = packs.cfg_tiny()
+    elif case == "q4_k_m_nextn":
+        cfg, kw = packs.cfg_tiny(quant="q4_k_m", n_layers=8, tied_head=False, seed=12), {"nextn": 1}
+    else:
+        cfg, kw = packs.cfg_tiny_moe(n_layers=8, d_expert=512, d_shared=512), {"fused_gate_up": case == "moe_fused"}
+    pack = packs.build_pack(cfg)
+    path = packs.write_gguf(pack, str(tmp_path / "m.gguf"), **kw)
+    gcfg, gt = _index_fields(pkg.llb.gguf_index(path))
+    pcfg, pt = _index_fields(pack.index_text())
+    for k, v in pcfg.items():
+        if k in ("rope_freq_base", "rms_norm_eps"):
+            assert float(gcfg[k]) == pytest.approx(float(v), rel=1e-6)
+        else:
+            assert gcfg[k] == v, k
+    blob = open(path, "rb").read()
+    for name, (off, nb, rows, cols, ty) in pt.items():
+        if case == "moe_fused" and ("ffn_gate_exps" in name or "ffn_up_exps" in name):
+            fused = gt[name.replace("ffn_gate_exps", "ffn_gate_up_exps").replace("ffn_up_exps", "ffn_gate_up_exps")]
+            assert fused[2] == 2 * rows and fused[3] == cols and fused[4] == ty
+            continue
+        goff, gnb, grows, gcols, gty = gt[name]
+        assert (grows, gcols, gnb) == (rows, cols, nb), name
+        assert gty == ("Q8_0G" if ty == "Q8_0" else ty)
+        if ty != "Q8_0":
+            assert blob[goff:goff + gnb] == pack.raw(name).numpy().tobytes(), name
+    if cfg.tied_head:
+        assert gt["output.weight"] == gt["token_embd.weight"]
+
+
+def test_gguf_reader_refuses_bad_files(pkg, tmp_path):
+    p = tmp_path / "bad.gguf"
+    p.write_bytes(b"GGUF" + b"\x03\x00\x00\x00" + b"\xff" * 40)
+    with pytest.raises(pkg.llb.LlbError):
+        pkg.llb.gguf_index(str(p))
+    p.write_bytes(b"not a gguf file at all, just some text that is long enough")
+    with pytest.raises(pkg.llb.LlbError):
+        pkg.llb.gguf_index(str(p))
+    with pytest.raises(pkg.llb.LlbError):
+        pkg.llb.gguf_index(str(tmp_path / "missing.gguf"))
