@@ -163,6 +163,8 @@ def test_gguf_header_gives_the_packs_index(pkg, packs, tmp_path, case):
     for k, v in pcfg.items():
         if k in ("rope_freq_base", "rms_norm_eps"):
             assert float(gcfg[k]) == pytest.approx(float(v), rel=1e-6)
+        elif k == "d_ff" and cfg.n_experts:
+            assert int(gcfg[k]) == max(cfg.d_expert, cfg.d_shared)    # the reference's rule for qwen35moe
         else:
             assert gcfg[k] == v, k
     blob = open(path, "rb").read()
