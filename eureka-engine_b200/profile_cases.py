@@ -9,6 +9,9 @@
     python eureka-engine_b200/profile_cases.py moe LAYERS [K] [PROMPT]      the MoE configuration (256 experts, top 8 +
                                                                             shared, Q4_K_S) truncated to LAYERS: verify-pass
                                                                             time, bytes and per-op times, prompt-lookup drafter
+    python eureka-engine_b200/profile_cases.py c4 CTX [K] [LAYERS]          the 9B-shape Q8_0 configuration at a context of
+                                                                            CTX positions (prompt fed through the T-row pass):
+                                                                            prefill time, verify-pass time and bytes, per-op times
 """
 import os
 import sys
@@ -106,6 +109,33 @@ def case_moe(layers, k=3, nprompt=512):
     eng.close()
 
 
+def case_c4(ctx, k=3, layers=0):
+    import time
+    import bench
+    pkg = graft.load_package()
+    llb, packs = pkg.llb, pkg.packs
+    llb.init(0)
+    cfg = packs.cfg_c4()
+    pack = packs.build_pack(cfg, device="cuda:0", layers=layers if 0 < layers < cfg.n_layers else None)
+    mtp = packs.aux1_bytes(packs.build_mtp(pack))
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    eng = llb.SpecEngine(pack, mtp, k=k, max_ctx=ctx + 640)
+    prompt = packs.synth_prompt(5, ctx, cfg.vocab_size)
+    t0 = time.time()
+    eng.prefill(prompt)
+    torch.cuda.synchronize()
+    t_pf = time.time() - t0
+    ids, got = eng.run_cycles(8)
+    ms = eng.time_verify(10)
+    nb = bench.verify_bytes(pack, ctx, k + 1)
+    print(f"c4: layers {pack.cfg.n_layers} ctx {ctx} T {k + 1}: prefill {t_pf:.1f} s ({ctx / t_pf:.0f} tok/s), verify {ms:.3f} ms/pass, "
+          f"{nb / 1e9:.3f} GB -> {nb / ms / 1e6:.1f} GB/s; kernels {eng.graph_nodes(2)}")
+    for n, (c, t) in sorted(eng.profile_verify().items(), key=lambda kv: -kv[1][1]):
+        print(f"{n:18s} n={c:4d} total_us={t:9.1f}")
+    eng.close()
+
+
 if __name__ == "__main__":
     if sys.argv[1] == "gemm":
         case_gemm(sys.argv[2], [int(v) for v in sys.argv[3].split(",")], int(sys.argv[4]))
@@ -113,6 +143,8 @@ if __name__ == "__main__":
         case_gemm("Q4_K", [int(v) for v in sys.argv[2].split(",")], int(sys.argv[3]), tcgen05=True)
     elif sys.argv[1] == "verify":
         case_verify(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3011)
+    elif sys.argv[1] == "c4":
+        case_c4(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3, int(sys.argv[4]) if len(sys.argv) > 4 else 0)
     elif sys.argv[1] == "moe":
         case_moe(int(sys.argv[2]), int(sys.argv[3]) if len(sys.argv) > 3 else 3, int(sys.argv[4]) if len(sys.argv) > 4 else 512)
     else:
