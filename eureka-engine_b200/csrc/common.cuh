@@ -43,8 +43,9 @@ __host__ __device__ inline size_t pack_row_bytes(int fmt, int cols) {
 //                   0 2 1 3 4 6 5 7, which is the order the tensor-core B fragments consume
 //   xs16 [K/16][NC] f32 sums of the fp16 values over 16 consecutive columns
 //   xs32 [K/32][NC] f32 sums over 32 consecutive columns
-//   xsf  [K/256][NC][16] fp16: the eight 32-column MEANS of a super-block as hi/lo pairs, in the order
-//                   the min-term MMA's B fragment reads them: for j = 0..3: hi(2j) hi(2j+1) lo(2j) lo(2j+1)
+//   xsf  [K/256][NC][16] fp16: the eight 32-column MEANS of a super-block as hi/lo pairs (hi = fp16(m),
+//                   lo = fp16((m - hi) * 2048), like the planes), in the order the min-term MMA's B fragment
+//                   reads them: for j = 0..3: hi(2j) hi(2j+1) lo(2j) lo(2j+1)
 struct XPlanes {
   __half *xh;
   float *xs16;
@@ -101,12 +102,12 @@ __device__ __forceinline__ void xp_store32(const XPlanes &xp, int t, int planes,
     __half *f = xp.xsf + ((size_t)(c >> 8) * xp.NC + t) * 16 + 4 * (b >> 1) + (b & 1);
     float v = hi32 * 0.03125f;
     __half h1 = __float2half_rn(v);
-    f[0] = h1; f[2] = __float2half_rn(v - __half2float(h1));
+    f[0] = h1; f[2] = __float2half_rn((v - __half2float(h1)) * XP_LO_SCALE);
     if (planes == 2) {
       f += (size_t)NH * 16;
       v = lo32 * 0.03125f;
       h1 = __float2half_rn(v);
-      f[0] = h1; f[2] = __float2half_rn(v - __half2float(h1));
+      f[0] = h1; f[2] = __float2half_rn((v - __half2float(h1)) * XP_LO_SCALE);
     }
   }
 }
@@ -148,12 +149,12 @@ __device__ __forceinline__ void xp_store4(const XPlanes &xp, int t, int planes, 
     __half *f = xp.xsf + ((size_t)(c >> 8) * xp.NC + t) * 16 + 4 * (b >> 1) + (b & 1);
     float m = h32 * 0.03125f;
     __half h1 = __float2half_rn(m);
-    f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
+    f[0] = h1; f[2] = __float2half_rn((m - __half2float(h1)) * XP_LO_SCALE);
     if (planes == 2) {
       f += (size_t)NH * 16;
       m = l32 * 0.03125f;
       h1 = __float2half_rn(m);
-      f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
+      f[0] = h1; f[2] = __float2half_rn((m - __half2float(h1)) * XP_LO_SCALE);
     }
   }
 }

@@ -935,6 +935,25 @@ LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass) {
   return 0;
 }
 
+// The same with the pass forced to `rows` rows (1 .. k + 1): a drafter that found fewer drafts leaves a shorter
+// pass in the control block; for timing, the missing rows repeat the pass's first token at the following
+// positions.  The control block is restored afterwards, but the rows' KV / conv / state-ring slots have been
+// overwritten with the forced rows' values: call it after the tokens that matter have been generated.
+LLB_API int llb_spec_time_verify_rows(llb_spec *m, int iters, int rows, float *ms_per_pass) {
+  if (rows < 1 || rows > m->Tmax) return llb_fail("time_verify_rows: %d rows, the engine was opened for %d", rows, m->Tmax);
+  SpecCtl c, keep;
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  CU_OK(cudaMemcpy(&c, m->ctl, sizeof c, cudaMemcpyDeviceToHost));
+  keep = c;
+  if (c.verify.pos0 + rows + 1 > m->max_ctx) return llb_fail("time_verify_rows: the context is full");
+  for (int t = c.verify.n > 0 ? c.verify.n : 1; t < rows; t++) { c.verify.tok[t] = c.verify.tok[0]; c.verify.slot[t] = (c.verify.pos0 + t) & (CONV_RING - 1); }
+  c.verify.n = rows;
+  CU_OK(cudaMemcpy(m->ctl, &c, sizeof c, cudaMemcpyHostToDevice));
+  const int rc = llb_spec_time_verify(m, iters, ms_per_pass);
+  CU_OK(cudaMemcpy(m->ctl, &keep, sizeof keep, cudaMemcpyHostToDevice));
+  return rc;
+}
+
 // Device time per launch of the FFN gate|up GEMM (the largest launch of the pass), cycling over the
 // layers so that every launch streams weights that are not in L2.  bytes_per_launch = the two
 // matrices' stored bytes plus the activation planes and the outputs.

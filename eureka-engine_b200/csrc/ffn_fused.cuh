@@ -66,11 +66,11 @@ template <int FMT> __device__ __forceinline__ void ffn_store4(uint8_t *xh_s, uin
       __half *f = (__half *)xsf_s + ((size_t)sb * NC + t) * 16 + 4 * (b >> 1) + (b & 1);
       float m = h32 * 0.03125f;
       __half h1 = __float2half_rn(m);
-      f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
+      f[0] = h1; f[2] = __float2half_rn((m - __half2float(h1)) * XP_LO_SCALE);
       f += (size_t)NH * 16;
       m = l32 * 0.03125f;
       h1 = __float2half_rn(m);
-      f[0] = h1; f[2] = __float2half_rn(m - __half2float(h1));
+      f[0] = h1; f[2] = __float2half_rn((m - __half2float(h1)) * XP_LO_SCALE);
     }
   }
 }

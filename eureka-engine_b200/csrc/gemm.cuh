@@ -88,6 +88,13 @@ __device__ __forceinline__ float byte_f_scaled(uint32_t w, int i, float s) {
 
 #define TWO24 16777216.0f
 
+// a * b + c on two fp16 lanes
+__device__ __forceinline__ uint32_t g2_hfma2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // ---- one chunk (<= 2 super-blocks = 512 columns) of a 16-row tile ------------------------------
 // st: this warp's stage, rows at stride RS; kc0: first column of the chunk; acc[nt][4]: the C
 // fragment (rows gid, gid+8; columns 2j, 2j+1 of n-tile nt).

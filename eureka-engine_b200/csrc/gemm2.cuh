@@ -10,8 +10,9 @@
 //    (row stride 160 / 224 bytes = 32 / 96 mod 128: conflict-free 8-byte A-fragment reads);
 //  * the copy issue loop has no division and no per-piece address arithmetic beyond one add;
 //  * the Q4_K "min" term  dmin * sum_b m_b * sum(x in sub-block b)  is ONE extra MMA per
-//    tile-super-block: A = the eight 6-bit mins (fp16 subnormal integers, twice), B = the
-//    sub-block activation means as fp16 hi/lo pairs prepared with the planes;
+//    tile-super-block: A = the eight 6-bit mins as fp16 numbers (m against the means' hi halves,
+//    m / 2048 against their lo halves), B = the sub-block activation means as fp16 hi/lo pairs
+//    prepared with the planes;
 //  * first MMAs of a sub-block take a zero C operand instead of zeroing registers.
 #pragma once
 #include "gemm.cuh"
@@ -264,7 +265,11 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
       uint32_t scA0, scB0, mnA0, mnB0, scA1, scB1, mnA1, mnB1;
       k4_scales(h0.y, h0.z, h0.w, scA0, scB0, mnA0, mnB0);
       k4_scales(h1.y, h1.z, h1.w, scA1, scB1, mnA1, mnB1);
-      const uint32_t am0 = __byte_perm(j < 2 ? mnA0 : mnB0, 0, mn_sel), am1 = __byte_perm(j < 2 ? mnA1 : mnB1, 0, mn_sel);
+      // the two mins of this thread's k-pair as fp16 numbers: 0x6400 | m is 1024 + m exactly; one FMA each gives m for
+      // the means' hi halves and m / 2048 for their lo halves (which are stored times 2048), both exact
+      const uint32_t at0 = __byte_perm(j < 2 ? mnA0 : mnB0, 0, mn_sel) | 0x64006400u, at1 = __byte_perm(j < 2 ? mnA1 : mnB1, 0, mn_sel) | 0x64006400u;
+      const uint32_t am0 = g2_hfma2(at0, 0x3c003c00u, 0xe400e400u), am1 = g2_hfma2(at1, 0x3c003c00u, 0xe400e400u);       // * 1 - 1024
+      const uint32_t al0 = g2_hfma2(at0, 0x10001000u, 0xb800b800u), al1 = g2_hfma2(at1, 0x10001000u, 0xb800b800u);       // * 2^-11 - 0.5
       uint32_t qh0 = 0, qh0b = 0, qh1 = 0, qh1b = 0;
       if constexpr (FMT == LLB_FM_Q5_K) {
         const uint2 t0 = *(const uint2 *)(b0 + 16 + 8 * j), t1 = *(const uint2 *)(b1 + 16 + 8 * j);
@@ -274,7 +279,7 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
         const uint2 xf = *(const uint2 *)(xfb + (size_t)c_c * NC * 32 + nt * 8 * 32);
-        mma16816_z(pm[nt], am0, am1, am0, am1, xf.x, xf.y);
+        mma16816_z(pm[nt], am0, am1, al0, al1, xf.x, xf.y);
         sS[nt][0] = sS[nt][1] = sS[nt][2] = sS[nt][3] = 0.0f;
       }
 #pragma unroll
@@ -310,8 +315,8 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
           sS[nt][3] += sc1l * pl[3] + sc1h * ph[3];
         }
       }
-      const float d0 = h2f_bits(h0.x & 0xffffu) * TWO24, dm0 = h2f_bits(h0.x >> 16) * (TWO24 * 32.0f);
-      const float d1 = h2f_bits(h1.x & 0xffffu) * TWO24, dm1 = h2f_bits(h1.x >> 16) * (TWO24 * 32.0f);
+      const float d0 = h2f_bits(h0.x & 0xffffu) * TWO24, dm0 = h2f_bits(h0.x >> 16) * 32.0f;
+      const float d1 = h2f_bits(h1.x & 0xffffu) * TWO24, dm1 = h2f_bits(h1.x >> 16) * 32.0f;
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
         acc[nt][0] += d0 * sS[nt][0] - dm0 * pm[nt][0];

@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(G3_BLOCK, 1) k_gemm3(const GemmArgs a, const i
           mn0 = ((hv >> 4) & 15) | ((mi >> 2) & 0x30); mn1 = ((hv >> 12) & 15) | ((mi >> 10) & 0x30);
         }
         const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
-        s0 = d * (float)sc0 * TWO24; s1 = d * (float)sc1 * (TWO24 * 0.0625f); dm = dmin * (TWO24 * 32.0f);
+        s0 = d * (float)sc0 * TWO24; s1 = d * (float)sc1 * (TWO24 * 0.0625f); dm = dmin * 32.0f;
         const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
         uint32_t v[32];
 #pragma unroll
@@ -272,8 +272,10 @@ __global__ void __launch_bounds__(G3_BLOCK, 1) k_gemm3(const GemmArgs a, const i
         // A[buf] is free: this thread waited for the MMAs of item s - 2 when it read their accumulators
         const uint32_t abuf = tmem_base + lane_off + (uint32_t)(buf * G3_A_COLS);
         t5_st32(abuf + 32 * c, v);
-        const uint32_t mcol = mn0 | (mn1 << 16);
-        t5_st2(abuf + 128 + 2 * c, mcol, mcol);
+        // the pair's mins as fp16 numbers (0x6400 | m is 1024 + m): m against the means' hi halves, m / 2048 against
+        // their lo halves, which are stored times 2048
+        const uint32_t mt = mn0 | (mn1 << 16) | 0x64006400u;
+        t5_st2(abuf + 128 + 2 * c, g2_hfma2(mt, 0x3c003c00u, 0xe400e400u), g2_hfma2(mt, 0x10001000u, 0xb800b800u));
         t5_wait_st();
         t5_fence_before();
         __syncwarp();

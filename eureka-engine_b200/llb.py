@@ -64,6 +64,7 @@ def lib() -> C.CDLL:
             "llb_spec_moe_ffn": (i32, [vp, i32, i32, vp, vp, vp, vp]),
             "llb_spec_open_gguf": (vp, [C.c_char_p, vp, sz, i32, i32, i32, i32]), "llb_b200_gguf_index": (i32, [C.c_char_p, vp, i32]),
             "llb_spec_run_cycles": (i32, [vp, i32, vp, i32]), "llb_spec_time_verify": (i32, [vp, i32, vp]),
+            "llb_spec_time_verify_rows": (i32, [vp, i32, i32, vp]),
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
             "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
         }
@@ -212,6 +213,11 @@ class SpecEngine:
     def time_verify(self, iters: int) -> float:
         ms = C.c_float(0)
         check(self.L.llb_spec_time_verify(self.h, iters, C.addressof(ms)), "llb_spec_time_verify")
+        return ms.value
+
+    def time_verify_rows(self, iters: int, rows: int) -> float:
+        ms = C.c_float(0)
+        check(self.L.llb_spec_time_verify_rows(self.h, iters, rows, C.addressof(ms)), "llb_spec_time_verify_rows")
         return ms.value
 
     def time_gemm(self, iters: int):

@@ -125,6 +125,9 @@ LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap);
 /* measurement helpers: device time (CUDA events on the library's stream) of the verify pass alone and
  * of the largest GEMM launch; kernels per graph replay (which: 0 cycle, 2 verify pass) */
 LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass);
+/* the verify pass timed with `rows` rows whatever the drafter found (missing rows repeat the first token); overwrites
+ * those rows' cache slots: a measurement entry, to be called after the generation that matters */
+LLB_API int llb_spec_time_verify_rows(llb_spec *m, int iters, int rows, float *ms_per_pass);
 LLB_API int llb_spec_time_gemm(llb_spec *m, int iters, float *us_per_launch, double *bytes_per_launch);
 LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which);
 /* one eager verify pass with an event after every op: "name\tcount\ttotal_us" lines */
