@@ -524,6 +524,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
                      int mtp_on_device, int k, int max_ctx, int layers) {
   std::unordered_map<std::string, TensorRec> tab;
   CK(parse_index(m, index_text, tab));
+  const int L_index = m->L;   // the trunk's length in the index: a nextn (MTP) block, if the index has one, is block L_index
   if (layers > 0 && layers < m->L) m->L = layers;
   if (k < 0 || k > 7) return llb_fail("k = %d: the path takes 0..7 drafts (host/llb_host.c:1608)", k);
   if (m->SZ != 128 || m->KC < 2) return llb_fail("ssm_state_size %d / conv kernel %d unsupported", m->SZ, m->KC);
@@ -652,6 +653,28 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     m->mt_at.o = MM(9); m->mt_ffn.post = (float *)ptr[10]; m->mt_ffn.gate = MM(11); m->mt_ffn.up = MM(12); m->mt_ffn.down = MM(13);
     m->mt_shn = (float *)ptr[14]; m->mt_head = MM(15); m->mt_ids = (int *)ptr[16]; m->mt_nv = nv;
     CK(check_k(m->mt_eh, d, 2 * d, "nextn.eh_proj")); CK(check_k(m->mt_head, nv, d, "mtp.head_slice"));
+    m->mt_Kc = falloc(m, (size_t)max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)max_ctx * kvd);
+    if (!m->mt_Kc || !m->mt_Vc) return -1;
+    m->has_mtp = true;
+  } else if (k > 0 && m->ne == 0 && tab.count("blk." + std::to_string(L_index) + ".nextn.eh_proj.weight")) {
+    // no image, but the index holds the model's own nextn block after the trunk (a GGUF with nextn_predict_layers,
+    // reports/cuda-moe/scripts/gen_moe.py:116-118): the same 15 tensors by their GGUF names, the trunk's head and the
+    // whole vocabulary (no draft-vocabulary slice, ids = identity)
+    const std::string p = "blk." + std::to_string(L_index) + ".";
+    CK(vec(p + "nextn.enorm.weight", &m->mt_enorm, d)); CK(vec(p + "nextn.hnorm.weight", &m->mt_hnorm, d));
+    CK(mat(p + "nextn.eh_proj.weight", m->mt_eh)); CK(check_k(m->mt_eh, d, 2 * d, "nextn.eh_proj"));
+    CK(vec(p + "attn_norm.weight", &m->mt_attn_norm, d));
+    CK(mat(p + "attn_q.weight", m->mt_at.q)); CK(check_k(m->mt_at.q, 2 * qa, d, "nextn attn_q"));
+    CK(mat(p + "attn_k.weight", m->mt_at.k)); CK(check_k(m->mt_at.k, kvd, d, "nextn attn_k"));
+    CK(mat(p + "attn_v.weight", m->mt_at.v)); CK(check_k(m->mt_at.v, kvd, d, "nextn attn_v"));
+    CK(mat(p + "attn_output.weight", m->mt_at.o)); CK(check_k(m->mt_at.o, d, qa, "nextn attn_output"));
+    CK(vec(p + "attn_q_norm.weight", &m->mt_at.qn, m->hd)); CK(vec(p + "attn_k_norm.weight", &m->mt_at.kn, m->hd));
+    CK(vec(p + "post_attention_norm.weight", &m->mt_ffn.post, d));
+    CK(mat(p + "ffn_gate.weight", m->mt_ffn.gate)); CK(check_k(m->mt_ffn.gate, m->f, d, "nextn ffn_gate"));
+    CK(mat(p + "ffn_up.weight", m->mt_ffn.up)); CK(check_k(m->mt_ffn.up, m->f, d, "nextn ffn_up"));
+    CK(mat(p + "ffn_down.weight", m->mt_ffn.down)); CK(check_k(m->mt_ffn.down, d, m->f, "nextn ffn_down"));
+    CK(vec(p + "nextn.shared_head_norm.weight", &m->mt_shn, d));
+    m->mt_head = m->head; m->mt_ids = nullptr; m->mt_nv = m->V;
     m->mt_Kc = falloc(m, (size_t)max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)max_ctx * kvd);
     if (!m->mt_Kc || !m->mt_Vc) return -1;
     m->has_mtp = true;

@@ -5,8 +5,8 @@
 // What it follows in the reference: the key mapping and defaults of tools/gguf2pack.c:541-600 (build_config),
 // the tensor naming of its packs (GGUF names kept, tied head = alias of token_embd.weight), Q8_0 re-sliced from
 // GGUF's [f16 d][32 x int8] blocks to the pack's row-split [cols x int8][cols/32 x f16] (tools/gguf2pack.c:25-27;
-// done at upload, engine.cu: load_tensor), nextn (MTP) blocks counted in block_count and left out of the trunk
-// (reports/cuda-moe/scripts/gen_moe.py:56,70).  The GGUF container itself (v2 / v3: magic, counts, typed
+// done at upload, engine.cu: load_tensor), nextn (MTP) blocks counted in block_count, listed after the trunk's and
+// not part of it (reports/cuda-moe/scripts/gen_moe.py:56,70).  The GGUF container itself (v2 / v3: magic, counts, typed
 // key-values, tensor infos, aligned data section) is read as its public specification describes it.
 #include <fcntl.h>
 #include <sys/mman.h>
@@ -195,11 +195,11 @@ int gguf_map(const char *path, GgufFile &g) {
     return 0;
   };
   for (const auto &t : tis) {
-    // only what the path reads: the trunk's blocks, the embedding, the head and its norm (tokenizer-side and
-    // vision tensors, and the nextn blocks, stay in the file)
+    // only what the path reads: the blocks (the trunk's, and a nextn block after them, which the engine takes as
+    // its drafter), the embedding, the head and its norm (tokenizer-side and vision tensors stay in the file)
     long long il = -1;
     if (t.name.rfind("blk.", 0) == 0) il = atoll(t.name.c_str() + 4);
-    const bool want = (il >= 0 && il < L) || t.name == "token_embd.weight" || t.name == "output.weight" || t.name == "output_norm.weight";
+    const bool want = (il >= 0 && il < blocks) || t.name == "token_embd.weight" || t.name == "output.weight" || t.name == "output_norm.weight";
     if (!want) continue;
     if (line(t.name, t)) { gguf_unmap(g); return -1; }
   }

@@ -10,7 +10,7 @@ struct GgufFile {
   const uint8_t *map = nullptr;   // the whole file; tensor offsets in `index` are relative to it
   size_t size = 0;
   std::string index;              // "#cfg" lines and one line per tensor the path reads
-  int nextn = 0;                  // MTP blocks the file holds after the trunk (not loaded)
+  int nextn = 0;                  // MTP blocks the file holds after the trunk
 };
 int gguf_map(const char *path, GgufFile &g);   // 0, or -1 with llb_fail's message
 void gguf_unmap(GgufFile &g);

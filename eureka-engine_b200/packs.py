@@ -615,15 +615,19 @@ def q4k_random_blocks(rows: int, cols: int, seed: int = 2, device="cpu") -> torc
 # a pack written as a GGUF file (what llb_spec_open_gguf reads)
 # --------------------------------------------------------------------------------------------
 
-def write_gguf(pack: Pack, path: str, fused_gate_up: bool = False, nextn: int = 0) -> str:
+def write_gguf(pack: Pack, path: str, fused_gate_up: bool = False, nextn: int = 0, mtp_entries=None) -> str:
     """Write `pack` as a GGUF file of architecture qwen35 / qwen35moe with the metadata keys the reference reads
     (tools/gguf2pack.c:541-600) and the pack's quantised bytes: K-quants and F32 verbatim, Q8_0 re-sliced from the
     pack's row-split rows to GGUF's [f16 d][32 x int8] blocks, expert stacks as 3-D tensors (optionally gate and
     up fused into ffn_gate_up_exps, [expert][gate rows | up rows]).  A tied head is written as no output.weight.
     `nextn` only adds the key nextn_predict_layers and that many to block_count (no tensors), to exercise the
-    reader's trunk-length rule.  Needs the gguf Python package."""
+    reader's trunk-length rule; `mtp_entries` (build_mtp's list) writes the drafter as the file's nextn block
+    blk.<n_layers>.* (its 15 block tensors; the head is the file's own output.weight) and sets nextn = 1.
+    Needs the gguf Python package."""
     from gguf import GGUFWriter, GGMLQuantizationType as Q
     c = pack.cfg
+    if mtp_entries is not None:
+        nextn = 1
     arch = "qwen35moe" if c.n_experts else "qwen35"
     w = GGUFWriter(path, arch)
     w.add_uint32(f"{arch}.block_count", c.n_layers + nextn)
@@ -695,6 +699,8 @@ def write_gguf(pack: Pack, path: str, fused_gate_up: bool = False, nextn: int = 
             add(e.name, e, raw, lead=(ne, e.rows // ne))
             continue
         add(e.name, e, raw)
+    for name, ty, (rows, cols), raw in (mtp_entries or [])[:15]:
+        add(f"blk.{c.n_layers}.{name}.weight", TensorEntry(name, 0, raw.numel(), rows, cols, ty), raw.cpu().numpy())
     w.write_header_to_file(); w.write_kv_data_to_file(); w.write_ti_data_to_file()
     for arr in todo:
         w.write_tensor_data(arr)

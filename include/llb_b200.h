@@ -140,7 +140,9 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
  * metadata keys of tools/gguf2pack.c:541-600, tensors uploaded from the mapped file (F32, Q4_K, Q5_K, Q6_K
  * verbatim; Q8_0 re-sliced from GGUF blocks to the pack's row-split layout), tied head when the file has no
  * output.weight, nextn blocks left out of the trunk.  mtp: an optional AUX1 / MTP1 drafter image as for
- * llb_spec_open.  NULL on failure (llb_last_error). */
+ * llb_spec_open; without one, a dense model's own nextn block (blk.<trunk length>.nextn.* and its attention / FFN
+ * tensors) is the drafter, with the file's head over the whole vocabulary; without either, prompt lookup.
+ * NULL on failure (llb_last_error). */
 LLB_API llb_spec *llb_spec_open_gguf(const char *path, const void *mtp, size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers);
 /* the index text derived from a GGUF header ("#cfg" lines, then name, file offset, bytes, rows, cols, type per
  * tensor); returns its length or -1; needs no GPU */
