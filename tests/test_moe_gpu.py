@@ -127,3 +127,30 @@ def test_moe_config3_shape_layers(pkg, packs, oracle, llb):
     finally:
         eng.close()
         orc.close()
+
+
+def test_moe_router_ties_and_all_experts(pkg, packs, oracle, llb):
+    """Edge cases of the routing rule (llb_moe_topk): two experts with bit-identical router rows tie in
+    probability and the LOWER id takes the earlier rank; with k = expert count every expert is chosen, in
+    descending order of probability, and the weights sum to one."""
+    cfg = packs.cfg_tiny_moe(n_layers=4, d_expert=256, d_shared=256, n_experts_used=8)
+    pack = packs.build_pack(cfg)
+    e = pack.by_name["blk.1.ffn_gate_inp.weight"]
+    r = pack.raw(e.name).view(-1, cfg.d_model * 4)
+    r[2] = r[5]                                  # experts 2 and 5 of layer 1 get the same router row
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=8)
+    eng = pkg.llb.SpecEngine(pack, None, k=3, max_ctx=64)
+    try:
+        h2 = np.random.default_rng(9).standard_normal((4, cfg.d_model)).astype(np.float32)
+        out, ids, wt = eng.moe_ffn(1, h2)
+        for t in range(4):
+            ro, rid, rw = orc.moe_ffn(1, h2[t])
+            assert list(ids[t, :-1]) == list(rid) and sorted(rid) == list(range(8))
+            pos = list(rid)
+            assert pos.index(2) + 1 == pos.index(5) and wt[t, pos.index(2)] == wt[t, pos.index(5)]
+            assert np.all(np.diff(wt[t, :-1]) <= 0) and abs(float(wt[t, :-1].sum()) - 1.0) < 1e-5
+            assert np.abs(wt[t] - rw).max() < 1e-6
+            assert np.linalg.norm(out[t] - ro) / np.linalg.norm(ro) < 3e-4
+    finally:
+        eng.close()
+        orc.close()
