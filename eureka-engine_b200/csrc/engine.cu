@@ -81,6 +81,7 @@ struct llb_spec {
   bool reduce_in_gemm = false;
   bool rs_early = true;               // LLB_RS_EARLY=0: every kernel reads its row set after the wait
   bool delta_fused = true;            // LLB_DELTA_FUSED=0: DeltaNet scan and gated norm as two kernels
+  bool moe_silu_fused = true;         // LLB_MOE_SILU_FUSED=0: the experts' silu as its own kernel also for T <= 4
   unsigned int *tile_ctr = nullptr;   // last-writer reduction counters of the GEMMs (one word per row tile)
   // graphs
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
@@ -386,12 +387,13 @@ static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs) {
   a.ids = m->moe_ids; a.nslot = ns; a.ne = m->ne; a.ef = m->ef; a.d = m->d; a.T = m->Tmax; a.n_rows = n_rows;
   a.W = w.gu; a.es = w.es_gu; a.g = m->moe_g; a.u = m->moe_u;
   int one = 1;
-  PK("moe gate|up", gemm_launch_moe(s, w.fmt_gu, false, m->xp_d, a, &one));
-  PK("moe silu", op_silu_scaled_xp(s, PartIn{m->moe_g, 1, 0}, PartIn{m->moe_u, 1, 0}, fe, m->xp_e, rs, m->Tmax, m->moe_wt, m->ef));
+  PK("moe gate|up", gemm_launch_moe(s, w.fmt_gu, false, m->xp_d, a, &one, nullptr));
+  const bool silu_in_down = m->NC == 8 && m->moe_silu_fused;
+  if (!silu_in_down) PK("moe silu", op_silu_scaled_xp(s, PartIn{m->moe_g, 1, 0}, PartIn{m->moe_u, 1, 0}, fe, m->xp_e, rs, m->Tmax, m->moe_wt, m->ef));
   int ks = gemm_fix_ksplit(w.fmt_dn, m->NC, fe / 256, gemm_pick_ksplit(w.fmt_dn, m->NC, m->Tmax * (m->d / 16), fe / 256, g_llb.sms));
   CK(out_prepare(m, m->b_dn, m->d, ks));
   a.W = w.dn; a.es = w.es_dn; a.out = m->b_dn.p; a.split_stride = m->b_dn.stride;
-  PK("moe down", gemm_launch_moe(s, w.fmt_dn, true, m->xp_e, a, &ks));
+  PK("moe down", gemm_launch_moe(s, w.fmt_dn, true, m->xp_e, a, &ks, silu_in_down ? m->moe_wt : nullptr));
   return 0;
 }
 
@@ -536,6 +538,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (m->TR % m->GK || m->H % m->KV) return llb_fail("head counts do not divide");
   { const char *e = getenv("LLB_RS_EARLY"); m->rs_early = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_DELTA_FUSED"); m->delta_fused = !(e && e[0] == '0'); }
+  { const char *e = getenv("LLB_MOE_SILU_FUSED"); m->moe_silu_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM_REDUCE"); m->reduce_in_gemm = e && e[0] == '1'; }
   m->k = k; m->Tmax = k + 1; m->R = k + 2; m->max_ctx = max_ctx;
   m->NC = m->Tmax <= 4 ? 8 : 16;

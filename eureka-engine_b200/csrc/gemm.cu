@@ -73,6 +73,7 @@ template <int FMT> static int setup_moe() {
   CU_OK(cudaFuncSetAttribute(k_moe_gu<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_moe_dn_silu<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   return 0;
 }
 
@@ -190,21 +191,28 @@ int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2) {
 }
 
 // ---- the routed experts' GEMMs (moe.cuh) ---------------------------------------------------------
-template <int FMT, int NT> static int launch_moe(cudaStream_t s, bool down, const GemmArgs &a, const MoeArgs &m, int ntiles) {
+template <int FMT, int NT> static int launch_moe(cudaStream_t s, bool down, const GemmArgs &a, const MoeArgs &m, int ntiles, const float *wt_silu) {
   const int NC = 8 * NT, nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
   int cps = g_llb.sms * G2_CPSM / a.ksplit;
   if (cps < 1) cps = 1;
   if (cps > ntiles) cps = ntiles;
   const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
   if (smem > G2_SMEM_MAX) return llb_fail("moe gemm: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
-  cudaError_t e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps)
-                       : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps);
+  cudaError_t e;
+  if (down && wt_silu) {
+    if constexpr (NT == 1) e = llb_launch(k_moe_dn_silu<FMT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, wt_silu, cps);
+    else return llb_fail("moe gemm: the down launch builds its own activations for T <= 4 only");
+  } else {
+    e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps)
+             : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps);
+  }
   if (e != cudaSuccess) return llb_fail("moe gemm launch: %s", cudaGetErrorString(e));
   return 0;
 }
 // down == false: gate|up of every (token, slot) on planes of K = d columns, one K-slice (the epilogue needs whole sums);
 // down == true: the per-token virtual matrices of K = nslot * ef columns, *ksplit slices (0: chosen here) into m.out
-int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit) {
+// wt_silu (down only, T <= 4): the launch builds wt * silu(m.g) * m.u in shared memory itself; xp then only gives K and NC
+int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit, const float *wt_silu) {
   if (fmt != LLB_FM_Q4_K && fmt != LLB_FM_Q5_K && fmt != LLB_FM_Q6_K) return llb_fail("moe gemm: expert stacks of format %d have no kernel", fmt);
   if (m.ef % 256 || m.d % 256) return llb_fail("moe gemm: widths %d, %d are not multiples of 256", m.ef, m.d);
   GemmArgs a;
@@ -220,7 +228,7 @@ int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeAr
   a.ksplit = ks;
   if (ksplit) *ksplit = ks;
   const int NT = xp.NC / 8;
-#define MOE_GO(F) return NT == 1 ? launch_moe<F, 1>(s, down, a, m, ntiles) : launch_moe<F, 2>(s, down, a, m, ntiles)
+#define MOE_GO(F) return NT == 1 ? launch_moe<F, 1>(s, down, a, m, ntiles, wt_silu) : launch_moe<F, 2>(s, down, a, m, ntiles, wt_silu)
   if (fmt == LLB_FM_Q4_K) MOE_GO(LLB_FM_Q4_K);
   if (fmt == LLB_FM_Q5_K) MOE_GO(LLB_FM_Q5_K);
   MOE_GO(LLB_FM_Q6_K);

@@ -54,7 +54,7 @@ int gemm_setup(void);
 int gemm_wait_errors(void);
 bool gemm_ffn_fusable(int fmt_gu, int fmt_dn, int NC, int d);
 int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2);   // gate|up (Q4_K, one K-slice), silu, down in one launch
-int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit);   // moe.cuh
+int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit, const float *wt_silu);   // moe.cuh
 
 // ops.cu
 int ops_xp_from_f32(cudaStream_t s, const float *x, int T, int planes, XPlanes xp);

@@ -11,7 +11,8 @@
 //   k_moe_gu   one virtual matrix per (token, slot): the 2 ef rows of the slot's expert against the
 //              activation planes of ALL rows (an MMA has 8 columns whether one is wanted or four); the
 //              epilogue keeps the slot's own token: g, u [T][(k+1) ef]
-//   (k_silu_xp then builds planes of wt * silu(g) * u, (k+1) ef columns per token)
+//   (k_silu_xp then builds planes of wt * silu(g) * u, (k+1) ef columns per token; with T <= 4 the down launch
+//   builds its slice of them in shared memory itself, k_moe_dn_silu)
 //   k_moe_dn   one virtual matrix per token: d rows of (k+1) ef columns whose super-blocks come from
 //              the token's experts in rank order, so that the MMA accumulation IS the rank-order
 //              weighted sum plus the gated shared expert; the epilogue keeps the token's own column.
@@ -20,6 +21,7 @@
 // result does not depend on which rows share its pass.
 #pragma once
 #include "gemm2.cuh"
+#include "ffn_fused.cuh"
 
 
 // column t of a finished tile: hi + lo / 2048, rows gid and gid + 8 (every lane takes part in the shuffles)
@@ -97,6 +99,51 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_gu(c
   pdl_trigger();
   g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeGuMats<FMT>{m});
 }
+// The down launch's activation slice built in shared memory from the gate|up outputs (T <= 4 rows): wt * silu(g) * u
+// of the CTA's K-slice, planes and side array exactly as k_silu_xp + G2StagePlanes would have left them, without the
+// launch in between.  Every CTA of a K-slice computes the same few thousand values.
+template <int FMT> struct MoeStageSilu {
+  const MoeArgs &m;
+  const float *wt;   // [T][nslot]
+  __device__ __forceinline__ void operator()(uint8_t *xh_s, uint8_t *xsf_s, int CS, int sb0, int nsl) const {
+    pdl_wait();
+    const int lane = threadIdx.x & 31, T = min(*m.n_rows, m.T), f = m.nslot * m.ef;
+    const int ngrp = nsl * 64, ntask = 4 * ngrp;   // (row of the 4 plane pairs, group of four columns); rows >= T are zero planes
+    for (int t0 = threadIdx.x; t0 < ntask; t0 += 4 * blockDim.x) {
+      float4 gv[4], uv[4];
+      float w[4];
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const int task = t0 + q * blockDim.x, t = task / ngrp, c = 4 * (task - t * ngrp);
+        gv[q] = make_float4(0.f, 0.f, 0.f, 0.f); uv[q] = gv[q]; w[q] = 0.0f;
+        if (task < ntask && t < T) {
+          const int cg = sb0 * 256 + c;
+          const size_t i = (size_t)t * f + cg;
+          gv[q] = __ldcg((const float4 *)(m.g + i)); uv[q] = __ldcg((const float4 *)(m.u + i));
+          w[q] = __ldcg(wt + (size_t)t * m.nslot + cg / m.ef);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const int task = t0 + q * blockDim.x, t = task / ngrp, c = 4 * (task - t * ngrp);
+        if (task < ntask) {   // whole warps: ngrp and blockDim are multiples of 32
+          const float h[4] = {(gv[q].x / (1.0f + expf(-gv[q].x))) * uv[q].x * w[q], (gv[q].y / (1.0f + expf(-gv[q].y))) * uv[q].y * w[q],
+                              (gv[q].z / (1.0f + expf(-gv[q].z))) * uv[q].z * w[q], (gv[q].w / (1.0f + expf(-gv[q].w))) * uv[q].w * w[q]};
+          ffn_store4<FMT>(xh_s, xsf_s, CS, t, c, h, lane);
+        }
+      }
+    }
+    __syncthreads();
+  }
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_dn_silu(const GemmArgs a, const MoeArgs m, const float *wt, const int cps) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_trigger();
+  g2_phase<FMT, 1>(a, cps, (int)blockIdx.x, smem, MoeStageSilu<FMT>{m, wt}, MoeDnMats<FMT>{m});
+}
+
 template <int FMT, int NT>
 __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_dn(const GemmArgs a, const MoeArgs m, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
