@@ -45,7 +45,12 @@ struct llb_spec {
   float *moe_lg = nullptr, *moe_wt = nullptr, *moe_g = nullptr, *moe_u = nullptr, *hn2 = nullptr;
   int *moe_ids = nullptr;
   XPlanes xp_e;
-  int k = 0, Tmax = 1, R = 2, max_ctx = 0, NC = 8;
+  int k = 0, Tmax = 1, R = 2, max_ctx = 0, NC = 8;   // Tmax / NC: rows and plane columns of the pass being enqueued
+  // A speculative pass has k + 1 rows; a prompt chunk has Tpf rows (8 where the attention kernel's query budget allows:
+  // the weights stream once per pass whatever its rows, so a wider chunk halves the prompt's time).  The two widths
+  // share every buffer; the planes have one view per column count.
+  int Tspec = 1, Tpf = 1;
+  XPlanes xpv[2][6];   // [NC == 16][xp_d, xp_f, xp_qa, xp_v, xp_2d, xp_e]
   // weights
   std::vector<void *> allocs;
   std::vector<LayerW> layer;
@@ -143,11 +148,19 @@ static void *dalloc(llb_spec *m, size_t bytes) {
   return p;
 }
 static float *falloc(llb_spec *m, size_t n) { return (float *)dalloc(m, n * 4); }
-static int xp_alloc(llb_spec *m, XPlanes &xp, int K) {
-  void *b = dalloc(m, xp_bytes(K, m->NC));
+static int xp_alloc(llb_spec *m, int which, int K) {
+  const int ncmax = (m->Tspec > 4 || m->Tpf > 4) ? 16 : 8;
+  void *b = dalloc(m, xp_bytes(K, ncmax));
   if (!b) return -1;
-  xp = xp_carve(b, K, m->NC);
+  m->xpv[0][which] = xp_carve(b, K, 8);
+  m->xpv[1][which] = xp_carve(b, K, ncmax);
   return 0;
+}
+// the width of the passes enqueued from here on
+static void set_width(llb_spec *m, int T) {
+  m->Tmax = T; m->NC = T <= 4 ? 8 : 16;
+  const XPlanes *v = m->xpv[m->NC == 16];
+  m->xp_d = v[0]; m->xp_f = v[1]; m->xp_qa = v[2]; m->xp_v = v[3]; m->xp_2d = v[4]; m->xp_e = v[5];
 }
 
 static int fmt_of(const std::string &ty) {
@@ -540,7 +553,17 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   { const char *e = getenv("LLB_DELTA_FUSED"); m->delta_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_MOE_SILU_FUSED"); m->moe_silu_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM_REDUCE"); m->reduce_in_gemm = e && e[0] == '1'; }
-  m->k = k; m->Tmax = k + 1; m->R = k + 2; m->max_ctx = max_ctx;
+  m->k = k; m->Tspec = k + 1; m->max_ctx = max_ctx;
+  {
+    // rows of a prompt chunk: 8, fewer where (H / KV) x rows would pass the attention kernel's 48 queries per kv head
+    int pf = 8;
+    const char *e = getenv("LLB_PREFILL_ROWS");
+    if (e && atoi(e) >= 1 && atoi(e) <= SPEC_MAXT) pf = atoi(e);
+    if (pf > 48 / (m->H / m->KV)) pf = 48 / (m->H / m->KV);
+    m->Tpf = pf > m->Tspec ? pf : m->Tspec;
+  }
+  m->Tmax = m->Tpf;                      // buffers are sized for the wider pass
+  m->R = m->Tmax + 1;                    // state-ring slots: rows + 1 (k + 2 in the reference, host/llb_host.c:1621)
   m->NC = m->Tmax <= 4 ? 8 : 16;
   const int d = m->d, qa = m->H * m->hd, kvd = m->KV * m->hd, T = m->Tmax;
   std::unordered_map<uint64_t, void *> dedupe;
@@ -701,13 +724,14 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (m->att_split > 128) m->att_split = 128;
   m->pm = falloc(m, (size_t)m->H * T * m->att_split); m->pl = falloc(m, (size_t)m->H * T * m->att_split);
   m->po = falloc(m, (size_t)m->H * T * m->att_split * m->hd);
-  CK(xp_alloc(m, m->xp_d, d)); CK(xp_alloc(m, m->xp_f, m->f)); CK(xp_alloc(m, m->xp_qa, qa)); CK(xp_alloc(m, m->xp_v, m->vdc));
-  CK(xp_alloc(m, m->xp_2d, 2 * d));
+  CK(xp_alloc(m, 0, d)); CK(xp_alloc(m, 1, m->f)); CK(xp_alloc(m, 2, qa)); CK(xp_alloc(m, 3, m->vdc));
+  CK(xp_alloc(m, 4, 2 * d));
+  m->xpv[0][5] = m->xpv[0][0]; m->xpv[1][5] = m->xpv[1][0];   // placeholder where there are no routed experts
   if (m->ne > 0) {
     const int ns = m->nk + 1;
     m->moe_lg = falloc(m, (size_t)T * (m->ne + 1)); m->moe_wt = falloc(m, (size_t)T * ns); m->moe_ids = (int *)dalloc(m, (size_t)T * ns * 4);
     m->moe_g = falloc(m, (size_t)T * ns * m->ef); m->moe_u = falloc(m, (size_t)T * ns * m->ef); m->hn2 = falloc(m, (size_t)T * d);
-    CK(xp_alloc(m, m->xp_e, ns * m->ef));
+    CK(xp_alloc(m, 5, ns * m->ef));
     if (!m->moe_lg || !m->moe_wt || !m->moe_ids || !m->moe_g || !m->moe_u || !m->hn2) return -1;
   }
   m->ctl = (SpecCtl *)dalloc(m, sizeof(SpecCtl));
@@ -723,6 +747,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     if (!m->tile_ctr) return -1;
   }
   CK(ops_model_setup());
+  set_width(m, m->Tspec);
   return 0;
 }
 
@@ -755,8 +780,17 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
   // One eager pass with empty row sets sizes and allocates every partial-sum buffer, so that the
   // captures below allocate nothing.  Then the graphs are captured once; everything that changes
   // between cycles lives in device memory.
-  if (llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m) || capture(m, 0, &m->g_spec, &m->n_spec_nodes) ||
-      capture(m, 1, &m->g_prefill, nullptr) || capture(m, 2, &m->g_verify, &m->n_verify_nodes) || llb_spec_reset(m)) {
+  // (an eager pass at either width first: a K-split, and so a buffer's size, may differ between them)
+  bool bad = false;
+  set_width(m, m->Tpf);
+  bad = bad || llb_spec_reset(m) || enq_cycle(m, false);
+  set_width(m, m->Tspec);
+  bad = bad || llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m) || capture(m, 0, &m->g_spec, &m->n_spec_nodes);
+  set_width(m, m->Tpf);
+  bad = bad || capture(m, 1, &m->g_prefill, nullptr);
+  set_width(m, m->Tspec);
+  bad = bad || capture(m, 2, &m->g_verify, &m->n_verify_nodes) || llb_spec_reset(m);
+  if (bad) {
     llb_spec_close(m);
     return nullptr;
   }
@@ -815,7 +849,7 @@ LLB_API int llb_spec_reset(llb_spec *m) {
 // reference's first cycle after a prompt starts (host/llb_host.c:1911, pos = n-1).
 LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
   if (n < 1) return llb_fail("prefill: empty prompt");
-  if (n + m->Tmax + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
+  if (n + m->Tpf + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
   for (int i = 0; i < n; i++) if (ids[i] < 0 || ids[i] >= m->V) return llb_fail("prefill: token %d out of range", ids[i]);
   CK(llb_spec_reset(m));
   SpecCtl c;
@@ -830,7 +864,10 @@ LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
   CK(ctl_write(m, c));
   int p = 0;
   while (p < n - 1) {
-    const int rows = (n - 1 - p) < m->Tmax ? (n - 1 - p) : m->Tmax;
+    // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
+    // over the rows of the last chunk, and that cycle's kernels cover k + 1 rows
+    const int rem = n - 1 - p;
+    const int rows = rem <= m->Tspec ? rem : (rem - m->Tspec < m->Tpf ? rem - m->Tspec : m->Tpf);
     // rows and their successors are given; only these fields of the control block change
     struct { int n, pos0, tok[SPEC_MAXT], slot[SPEC_MAXT]; } v;
     v.n = rows; v.pos0 = p;
