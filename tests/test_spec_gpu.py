@@ -206,3 +206,30 @@ def test_fused_ffn_launch(pkg, packs, oracle, llb):
         assert same == 20
     assert L.llb_b200_wait_errors() == 0
     assert nodes[1] < nodes[0]
+
+
+def test_prompt_chunk_width_does_not_change_the_result(pkg, packs, oracle, llb, monkeypatch):
+    """The prompt is fed in chunks of 8 rows by default (LLB_PREFILL_ROWS), whatever k is; chunks of 1, 3 or k + 1 rows
+    leave the same emitted ids (the oracle's), the same cycle and acceptance counts, and a DeltaNet state within the
+    path's tolerance.  (37 prompt tokens: wide chunks, a ragged one, and the last one held to k + 1 rows.)"""
+    cfg = packs.cfg_tiny(n_layers=8, seed=21)
+    pack = packs.build_pack(cfg)
+    mtp = packs.aux1_bytes(packs.build_mtp(pack))
+    prompt = packs.synth_prompt(6, 37, cfg.vocab_size)
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=96)
+    ref_ids, ref_top2 = orc.greedy(prompt, 20)
+    runs = []
+    for rows in ("1", "3", "4", "8"):
+        monkeypatch.setenv("LLB_PREFILL_ROWS", rows)
+        eng = pkg.llb.SpecEngine(pack, mtp, k=3, max_ctx=96)
+        try:
+            eng.prefill(prompt)
+            state = eng.read_state(0, 0)
+            ids, top2 = eng.generate(20)
+            runs.append((ids, eng.stats(), state))
+        finally:
+            eng.close()
+    for ids, st, state in runs:
+        assert _compare_ids(ids, ref_ids, ref_top2) == 20
+        assert st == runs[0][1]
+        assert np.allclose(state, runs[0][2], rtol=1e-2, atol=2e-2)
