@@ -1,10 +1,10 @@
 #!/usr/bin/env python
 """Writes the golden fixtures of tests/golden/ from the REFERENCE itself.
 
-Run in a checkout that has the reference tree (default /root/reference) and after
+Run in a checkout that has the reference tree (--ref REFERENCE_DIR) and after
 `make -C oracle ref REF=<reference>`:
 
-    python tests/golden/make_golden.py [--ref /root/reference] [--skip-c0]
+    python tests/golden/make_golden.py [--ref REFERENCE_DIR] [--skip-c0]
 
 Sources of truth used here (nothing from this repository's CUDA path or C restatement):
   * the reference's numpy dequantisers tools/q4k.py, tools/q5k.py, tools/q6k.py (dequant_rows) and the

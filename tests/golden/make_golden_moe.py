@@ -3,7 +3,7 @@
 float64 checker reports/metal-catchup/tools/mx_ref.py (run unmodified, through runpy) on a synthetic
 tiny MoE model.
 
-    python tests/golden/make_golden_moe.py [--ref /root/reference]
+    python tests/golden/make_golden_moe.py [--ref REFERENCE_DIR]
 
 What happens: the tiny MoE pack of eureka-engine_b200/packs.py (seeded) is written as a GGUF holding the
 MoE tensors under their GGUF names with the pack's quantised bytes; for a few seeded FFN inputs h2 the C
