@@ -192,7 +192,7 @@ def main():
     steps, warm = args.steps, max(args.warmup, 3)
     if (steps + warm) * 2 * (K_DRAFT + 1) + 16 > GEN_CAP:
         raise SystemExit("--steps too large for the context this benchmark allocates")
-    st = torch.cuda.ExternalStream(llb.lib().llb_stream())
+    st = torch.cuda.ExternalStream(llb.lib().llb_b200_stream())
     sampler = ClockSampler(local)
 
     def barrier():

@@ -19,7 +19,12 @@ static size_t g_parts_floats = 0;
 extern "C" {
 
 int llb_b200_init(int device) {
-  if (g_llb.device == device && g_llb.stream) return 0;
+  if (g_llb.stream) {
+    // one device and one stream per process: the stream, the kernels' attributes and the library's own device words
+    // belong to the first device; a second binding would leave them pointing into another GPU's memory
+    if (g_llb.device == device) return 0;
+    return llb_fail("llb_b200_init(%d): this process is already bound to device %d", device, g_llb.device);
+  }
   int n = 0;
   cudaError_t e = cudaGetDeviceCount(&n);
   if (e != cudaSuccess || n < 1) return llb_fail("no CUDA device: %s", cudaGetErrorString(e));
@@ -28,7 +33,6 @@ int llb_b200_init(int device) {
   cudaDeviceProp pr;
   CU_OK(cudaGetDeviceProperties(&pr, device));
   if (pr.major < 10) return llb_fail("device %d is sm_%d%d; this library is built for sm_100a only", device, pr.major, pr.minor);
-  g_llb.device = device;
   { const char *e = getenv("LLB_PDL"); g_llb.pdl = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM3"); g_llb.gemm3 = e && e[0] == '1'; }
   { const char *e = getenv("LLB_Q8_V1"); g_llb.q8_v1 = e && e[0] == '1'; }
@@ -36,8 +40,10 @@ int llb_b200_init(int device) {
   g_llb.sms = pr.multiProcessorCount;
   // a blocking stream: ordered after work a caller queued on the legacy default stream (torch's), so
   // device buffers produced there can be handed in without an explicit synchronisation
-  CU_OK(cudaStreamCreate(&g_llb.stream));
-  if (gemm_setup()) return -1;
+  cudaStream_t st = nullptr;
+  CU_OK(cudaStreamCreate(&st));
+  g_llb.device = device; g_llb.stream = st;
+  if (gemm_setup()) { cudaStreamDestroy(st); g_llb.stream = nullptr; g_llb.device = -1; return -1; }
   return 0;
 }
 const char *llb_b200_last_error(void) { return g_llb.err; }
@@ -46,52 +52,59 @@ int llb_b200_sm_count(void) { return g_llb.sms; }
 #define NEED_INIT(ret) \
   if (!g_llb.stream) { llb_fail("llb_b200_init has not been called"); return ret; }
 
-llb_dptr llb_alloc_zero(size_t bytes) {
+llb_b200_dptr llb_b200_alloc_zero(size_t bytes) {
   NEED_INIT(0)
+  if (backend_graph_bail()) return 0;
   void *p = nullptr;
   if (cudaMalloc(&p, bytes ? bytes : 4) != cudaSuccess) { llb_fail("cudaMalloc(%zu) failed", bytes); cudaGetLastError(); return 0; }
   if (cudaMemsetAsync(p, 0, bytes, g_llb.stream) != cudaSuccess) { cudaFree(p); llb_fail("memset failed"); return 0; }
-  return (llb_dptr)(uintptr_t)p;
+  return (llb_b200_dptr)(uintptr_t)p;
 }
-int llb_free(llb_dptr p) {
+int llb_b200_free(llb_b200_dptr p) {
   NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   CU_OK(cudaFree((void *)(uintptr_t)p));
   return 0;
 }
-int llb_zero(llb_dptr p, size_t bytes) {
+int llb_b200_zero(llb_b200_dptr p, size_t bytes) {
   NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
   CU_OK(cudaMemsetAsync((void *)(uintptr_t)p, 0, bytes, g_llb.stream));
   return 0;
 }
-int llb_copy(llb_dptr d, llb_dptr s, size_t bytes) {
+int llb_b200_copy(llb_b200_dptr d, llb_b200_dptr s, size_t bytes) {
   NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
   CU_OK(cudaMemcpyAsync((void *)(uintptr_t)d, (const void *)(uintptr_t)s, bytes, cudaMemcpyDeviceToDevice, g_llb.stream));
   return 0;
 }
-int llb_write(llb_dptr d, const void *h, size_t bytes) {
+int llb_b200_write(llb_b200_dptr d, const void *h, size_t bytes) {
   NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
   CU_OK(cudaMemcpyAsync((void *)(uintptr_t)d, h, bytes, cudaMemcpyHostToDevice, g_llb.stream));
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   return 0;
 }
-int llb_read(void *h, llb_dptr p, size_t bytes) {
+int llb_b200_read(void *h, llb_b200_dptr p, size_t bytes) {
   NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
   CU_OK(cudaMemcpyAsync(h, (const void *)(uintptr_t)p, bytes, cudaMemcpyDeviceToHost, g_llb.stream));
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   return 0;
 }
-int llb_sync(void) {
+int llb_b200_sync(void) {
   NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   CU_OK(cudaGetLastError());
   return 0;
 }
-llb_dptr llb_stream(void) { return (llb_dptr)(uintptr_t)g_llb.stream; }
+llb_b200_dptr llb_b200_stream(void) { return (llb_b200_dptr)(uintptr_t)g_llb.stream; }
 
 size_t llb_b200_weight_bytes(int fmt, int rows, int cols) { return (size_t)rows * dev_row_bytes(fmt, cols); }
 
-int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src_on_device, llb_dptr dst) {
+int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src_on_device, llb_b200_dptr dst) {
   NEED_INIT(-1)
   const size_t pb = (size_t)rows * pack_row_bytes(fmt, cols);
   if (!pack_row_bytes(fmt, cols)) return llb_fail("weight_upload: format %d / cols %d", fmt, cols);
@@ -105,7 +118,8 @@ int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src
   void *tmp = nullptr;
   if (!src_on_device) {
     CU_OK(cudaMalloc(&tmp, pb));
-    CU_OK(cudaMemcpyAsync(tmp, src, pb, cudaMemcpyHostToDevice, g_llb.stream));
+    const cudaError_t ce = cudaMemcpyAsync(tmp, src, pb, cudaMemcpyHostToDevice, g_llb.stream);
+    if (ce != cudaSuccess) { cudaFree(tmp); return llb_fail("weight_upload: copy of %zu bytes: %s", pb, cudaGetErrorString(ce)); }
     s = (const uint8_t *)tmp;
   }
   int rc = ops_repack_q6k(g_llb.stream, s, (uint8_t *)(uintptr_t)dst, (size_t)rows * (cols / 256));
@@ -116,7 +130,7 @@ int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src
   return rc;
 }
 
-int llb_b200_dequant(int fmt, int rows, int cols, llb_dptr w, llb_dptr row_ids, int nrows, llb_dptr out) {
+int llb_b200_dequant(int fmt, int rows, int cols, llb_b200_dptr w, llb_b200_dptr row_ids, int nrows, llb_b200_dptr out) {
   NEED_INIT(-1)
   return ops_dequant_rows(g_llb.stream, fmt, (const uint8_t *)(uintptr_t)w, rows, cols, (const int *)(uintptr_t)row_ids, nrows,
                           (float *)(uintptr_t)out);
@@ -139,17 +153,17 @@ void llb_b200_xp_free(llb_xp *xp) {
   cudaFree(xp->base);
   delete xp;
 }
-int llb_b200_xp_set_f32(llb_xp *xp, llb_dptr x) {
+int llb_b200_xp_set_f32(llb_xp *xp, llb_b200_dptr x) {
   NEED_INIT(-1)
   return ops_xp_from_f32(g_llb.stream, (const float *)(uintptr_t)x, xp->T, xp->planes, xp->p);
 }
-int llb_b200_xp_set_bf16(llb_xp *xp, llb_dptr x) {
+int llb_b200_xp_set_bf16(llb_xp *xp, llb_b200_dptr x) {
   NEED_INIT(-1)
   if (xp->planes != 1) return llb_fail("xp_set_bf16 needs planes == 1");
   return ops_xp_from_bf16(g_llb.stream, (const void *)(uintptr_t)x, xp->T, xp->p);
 }
 
-int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const llb_dptr *out, int K, const llb_xp *xp, int ksplit) {
+int llb_b200_gemm(int fmt, int nmat, const llb_b200_dptr *w, const int *rows, const llb_b200_dptr *out, int K, const llb_xp *xp, int ksplit) {
   NEED_INIT(-1)
   if (nmat < 1 || nmat > GEMM_MAXMAT) return llb_fail("gemm: nmat %d", nmat);
   GemmArgs a;
@@ -160,9 +174,14 @@ int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const l
   a.ksplit = gemm_fix_ksplit(fmt, xp->p.NC, K / 256, ksplit > 0 ? ksplit : gemm_pick_ksplit(fmt, xp->p.NC, ntiles, K / 256, g_llb.sms));
   const size_t per_split = (size_t)xp->T * total_rows;
   if (a.ksplit > 1 && per_split * a.ksplit > g_parts_floats) {
-    if (g_parts) { CU_OK(cudaStreamSynchronize(g_llb.stream)); CU_OK(cudaFree(g_parts)); }
-    g_parts_floats = per_split * GEMM_MAXSPLIT;
-    CU_OK(cudaMalloc(&g_parts, g_parts_floats * 4));
+    if (g_parts) {
+      float *old = g_parts;
+      g_parts = nullptr; g_parts_floats = 0;   // nothing dangles if the calls below fail
+      CU_OK(cudaStreamSynchronize(g_llb.stream)); CU_OK(cudaFree(old));
+    }
+    float *fresh = nullptr;
+    CU_OK(cudaMalloc(&fresh, per_split * GEMM_MAXSPLIT * 4));
+    g_parts = fresh; g_parts_floats = per_split * GEMM_MAXSPLIT;
   }
   size_t off = 0;
   for (int i = 0; i < nmat; i++) {
@@ -178,6 +197,11 @@ int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const l
     for (int i = 0; i < nmat; i++)
       if (ops_sum_parts(g_llb.stream, a.m[i].out, a.ksplit, a.m[i].split_stride, xp->T * rows[i], (float *)(uintptr_t)out[i])) return -1;
   return 0;
+}
+
+int llb_b200_gemm_ksplit(int fmt, int nc, int ntiles, int nsb, int sms) { return gemm_pick_ksplit(fmt, nc, ntiles, nsb, sms); }
+int llb_b200_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_prefill, int sms) {
+  return gemm_ring_ksplit(fmt, nsb, ntiles, nc_spec, nc_prefill, sms, 8);
 }
 
 int llb_b200_use_tcgen05(int on) {
@@ -197,8 +221,8 @@ int llb_b200_wait_errors(void) {
   return gemm_wait_errors();
 }
 
-int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp, llb_dptr x_dev,
-                       llb_dptr y_dev) {
+int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp, llb_b200_dptr x_dev,
+                       llb_b200_dptr y_dev) {
   NEED_INIT(-1)
   CU_OK(cudaMemcpyAsync((void *)(uintptr_t)x_dev, x_bf16, (size_t)T * K * 2, cudaMemcpyHostToDevice, g_llb.stream));
   if (llb_b200_xp_set_bf16(xp, x_dev)) return -1;
@@ -217,13 +241,13 @@ int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16,
 #define NOALLOC_MAX_K 8192
 #define NOALLOC_MAX_T 4
 #define NOALLOC_PART_FLOATS (2u << 20)                                   /* [K-slices][T][rows] f32 */
-#define NOALLOC_XP_BYTES 172032                                          /* xp_bytes(8192, 8), rounded up to 256 */
+#define NOALLOC_XP_BYTES 172032                                          /* xp_bytes(8192, 8) = 163840, plus 8 KB of slack */
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_XP_BYTES + NOALLOC_PART_FLOATS * 4];
 // In host code the array's name is only a handle for the runtime; the device address is looked up
 // once per device, with that device current, and kept here.
 static unsigned char *g_noalloc_ptr[64];
 
-int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr x_f32, int T, llb_dptr out_f32) {
+int llb_b200_gemm_noalloc(int fmt, llb_b200_dptr w, int rows, int K, llb_b200_dptr x_f32, int T, llb_b200_dptr out_f32) {
   NEED_INIT(-1)
   if (K < 256 || K % 256 || K > NOALLOC_MAX_K) return llb_fail("gemm_noalloc: K = %d; this entry point takes multiples of 256 up to %d", K, NOALLOC_MAX_K);
   if (T < 1 || T > NOALLOC_MAX_T) return llb_fail("gemm_noalloc: T = %d; this entry point takes 1..%d rows", T, NOALLOC_MAX_T);
@@ -235,12 +259,18 @@ int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr x_f32, 
     return llb_fail("gemm_noalloc: %d K-slices x %d rows x %d output rows need %zu floats of scratch, the built-in array holds %u",
                     ks, T, rows, (size_t)ks * T * rows, (unsigned)NOALLOC_PART_FLOATS);
   if (xp_bytes(K, NC) > NOALLOC_XP_BYTES) return llb_fail("gemm_noalloc: planes of %d columns do not fit", K);
-  int dev = 0;
-  CU_OK(cudaGetDevice(&dev));
+  // the work is queued on the library's stream, so the array of the library's device is the one to use, whatever
+  // device the calling thread has current
+  const int dev = g_llb.device;
   if (dev < 0 || dev >= 64) return llb_fail("gemm_noalloc: device ordinal %d", dev);
   if (!g_noalloc_ptr[dev]) {
+    int cur = -1;
+    CU_OK(cudaGetDevice(&cur));
+    if (cur != dev) CU_OK(cudaSetDevice(dev));
     void *p = nullptr;
-    CU_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    const cudaError_t ce = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (cur != dev && cur >= 0) cudaSetDevice(cur);
+    if (ce != cudaSuccess) return llb_fail("gemm_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
     g_noalloc_ptr[dev] = (unsigned char *)p;
   }
   unsigned char *scratch = g_noalloc_ptr[dev];

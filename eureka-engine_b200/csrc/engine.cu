@@ -45,6 +45,7 @@ struct llb_spec {
   float *moe_lg = nullptr, *moe_wt = nullptr, *moe_g = nullptr, *moe_u = nullptr, *hn2 = nullptr;
   int *moe_ids = nullptr;
   XPlanes xp_e;
+  size_t pack_bytes = 0;   // size of the pack the index describes: every tensor range is checked against it
   int k = 0, Tmax = 1, R = 2, max_ctx = 0, NC = 8;   // Tmax / NC: rows and plane columns of the pass being enqueued
   // A speculative pass has k + 1 rows; a prompt chunk has Tpf rows (8 where the attention kernel's query budget allows:
   // the weights stream once per pass whatever its rows, so a wider chunk halves the prompt's time).  The two widths
@@ -69,6 +70,9 @@ struct llb_spec {
   int mt_nv = 0;
   // per-sequence state
   std::vector<float *> Kc, Vc, ring, S;   // per layer (null where not applicable)
+  // K-slices of the attn_qkv launch of each DeltaNet layer.  The conv ring keeps a row as that many partial sums and
+  // every later pass adds them up again, so the split is fixed at open and is the same at both pass widths.
+  std::vector<int> ring_ks;
   float *mt_Kc = nullptr, *mt_Vc = nullptr;
   SpecCtl *ctl = nullptr;
   SpecResult *res_host = nullptr, *res_dev = nullptr;
@@ -117,26 +121,8 @@ static void prof_mark(const char *name) {
   cudaEventRecord(e, g_llb.stream);
   g_prof.push_back({name, e});
 }
-#ifdef LLB_DBG_SKIP
-// timing experiments only (never built into the shipped library): LLB_SKIP=small leaves out every kernel but the
-// GEMMs, LLB_SKIP=prefix[,prefix...] the ops whose names start with one of the prefixes
-static bool dbg_skip(const char *name) {
-  const char *e = getenv("LLB_SKIP");
-  if (!e) return false;
-  if (!strcmp(e, "small")) return strncmp(name, "gemm", 4) != 0;
-  while (*e) {
-    const char *c = strchr(e, ',');
-    const size_t n = c ? (size_t)(c - e) : strlen(e);
-    if (n && !strncmp(name, e, n)) return true;
-    e += n + (c ? 1 : 0);
-  }
-  return false;
-}
-#define PK(name, call) do { if (!dbg_skip(name)) { if ((call)) return -1; } prof_mark(name); } while (0)
-#else
 #define PK(name, call) do { if ((call)) return -1; prof_mark(name); } while (0)
-#endif
-#define RING_SPLITS 4   // K-slices the conv ring can hold per row
+#define RING_MAXSPLIT 8   // most K-slices a conv ring keeps per row
 static float bits_float(unsigned int u) { float f; memcpy(&f, &u, 4); return f; }
 
 static void *dalloc(llb_spec *m, size_t bytes) {
@@ -210,14 +196,50 @@ static int parse_index(llb_spec *m, const char *text, std::unordered_map<std::st
   return 0;
 }
 
+static bool in_range(uint64_t off, uint64_t bytes, size_t src_bytes);
+static size_t rec_bytes(const TensorRec &t);
+// The configuration values every later division, modulo and allocation relies on (a stale or zeroed index must be an
+// error message, not a SIGFPE or a wild allocation), then every tensor record against the pack's size.
+static int validate_index(const llb_spec *m, const std::unordered_map<std::string, TensorRec> &tab, size_t pack_bytes) {
+  struct { const char *k; int v; } pos[] = {{"n_layers", m->L}, {"n_heads", m->H}, {"n_kv_heads", m->KV}, {"d_model", m->d}, {"head_dim", m->hd},
+    {"vocab_size", m->V}, {"full_attention_interval", m->interval}, {"ssm_conv_kernel", m->KC}, {"ssm_state_size", m->SZ},
+    {"ssm_group_count", m->GK}, {"ssm_time_step_rank", m->TR}, {"ssm_inner_size", m->vdc}, {"linear_key_dim", m->kdc},
+    {"linear_conv_dim", m->convd}, {"rope_dim", m->rope_dim}};
+  for (auto &p : pos) if (p.v < 1) return llb_fail("index: #cfg %s is %d (missing or not positive)", p.k, p.v);
+  if (m->ne == 0 && m->f < 1) return llb_fail("index: #cfg d_ff is %d (missing or not positive)", m->f);
+  if (m->ne < 0 || m->nk < 0 || m->ef < 0 || m->sf < 0) return llb_fail("index: negative expert configuration");
+  if (m->L > 4096 || m->V > (1 << 24) || m->d > (1 << 16)) return llb_fail("index: n_layers %d / vocab_size %d / d_model %d out of range", m->L, m->V, m->d);
+  if (m->rope_dim > m->hd || (m->rope_dim & 1)) return llb_fail("index: rope_dim %d with head_dim %d", m->rope_dim, m->hd);
+  if (m->convd != 2 * m->kdc + m->vdc) return llb_fail("index: linear_conv_dim %d is not 2 x %d + %d", m->convd, m->kdc, m->vdc);
+  if (m->kdc != m->GK * m->SZ || m->vdc != m->TR * m->SZ) return llb_fail("index: DeltaNet widths %d / %d do not match %d groups, %d heads of %d", m->kdc, m->vdc, m->GK, m->TR, m->SZ);
+  if (!(m->eps > 0.0f) || !(m->rope_base > 0.0f)) return llb_fail("index: rms_norm_eps / rope_freq_base must be positive");
+  for (const auto &kv : tab) {
+    const TensorRec &t = kv.second;
+    if (t.rows < 1 || t.cols < 1) return llb_fail("index: tensor %s is [%d x %d]", kv.first.c_str(), t.rows, t.cols);
+    if (t.fmt != LLB_FM_F32 && t.cols % (t.fmt == LLB_FM_Q8_0 ? 32 : 256)) return llb_fail("index: tensor %s has %d columns, not whole blocks of its format", kv.first.c_str(), t.cols);
+    if (rec_bytes(t) != t.bytes) return llb_fail("index: tensor %s has %llu bytes, its shape needs %zu", kv.first.c_str(), (unsigned long long)t.bytes, rec_bytes(t));
+    if (!in_range(t.off, t.bytes, pack_bytes))
+      return llb_fail("index: tensor %s (offset %llu, %llu bytes) reaches past the end of the pack (%zu bytes): truncated pack or stale index",
+                      kv.first.c_str(), (unsigned long long)t.off, (unsigned long long)t.bytes, pack_bytes);
+  }
+  return 0;
+}
+
 // one tensor from pack bytes into its device layout; `dedupe` shares the copy of aliased tensors
-static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, int on_device, void **out,
+// does [off, off + bytes) lie inside a source of src_bytes bytes?  (no overflow: the two sides are compared separately)
+static bool in_range(uint64_t off, uint64_t bytes, size_t src_bytes) { return off <= src_bytes && bytes <= src_bytes - off; }
+// bytes a tensor record occupies in its source (GGUF-blocked Q8_0 has the same size as the row-split layout)
+static size_t rec_bytes(const TensorRec &t) { return (size_t)t.rows * pack_row_bytes(t.fmt, t.cols); }
+
+static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, size_t src_bytes, int on_device, void **out,
                        std::unordered_map<uint64_t, void *> &dedupe) {
   auto it = dedupe.find(t.off);
   if (it != dedupe.end()) { *out = it->second; return 0; }
-  const size_t want = (size_t)t.rows * pack_row_bytes(t.fmt, t.cols);
+  const size_t want = rec_bytes(t);
   if (want != t.bytes) return llb_fail("index: tensor at %llu has %llu bytes, its shape needs %zu", (unsigned long long)t.off,
                                        (unsigned long long)t.bytes, want);
+  if (!in_range(t.off, t.bytes, src_bytes)) return llb_fail("index: tensor at %llu (%llu bytes) reaches past the end of its source (%zu bytes)",
+                                                             (unsigned long long)t.off, (unsigned long long)t.bytes, src_bytes);
   void *dst = dalloc(m, (size_t)t.rows * dev_row_bytes(t.fmt, t.cols));
   if (!dst) return -1;
   if (t.blocked) {
@@ -233,13 +255,13 @@ static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, int
         uint8_t *q = tmp.data() + (size_t)r * rb, *sc = q + t.cols;
         for (size_t b = 0; b < nb; b++) { memcpy(sc + 2 * b, src + 34 * b, 2); memcpy(q + 32 * b, src + 34 * b + 2, 32); }
       }
-      CK(llb_b200_weight_upload(t.fmt, nr, t.cols, tmp.data(), 0, (llb_dptr)(uintptr_t)((uint8_t *)dst + (size_t)r0 * dev_row_bytes(t.fmt, t.cols))));
+      CK(llb_b200_weight_upload(t.fmt, nr, t.cols, tmp.data(), 0, (llb_b200_dptr)(uintptr_t)((uint8_t *)dst + (size_t)r0 * dev_row_bytes(t.fmt, t.cols))));
     }
     dedupe[t.off] = dst;
     *out = dst;
     return 0;
   }
-  CK(llb_b200_weight_upload(t.fmt, t.rows, t.cols, pack + t.off, on_device, (llb_dptr)(uintptr_t)dst));
+  CK(llb_b200_weight_upload(t.fmt, t.rows, t.cols, pack + t.off, on_device, (llb_b200_dptr)(uintptr_t)dst));
   dedupe[t.off] = dst;
   *out = dst;
   return 0;
@@ -257,6 +279,7 @@ static int load_moe(llb_spec *m, FfnW &w, const std::string &p, const std::unord
     out = it->second;
     if (out.rows != rows || out.cols != cols) return llb_fail("%s%s is [%d x %d], the configuration needs [%d x %d]", p.c_str(), leaf, out.rows, out.cols, rows, cols);
     if ((size_t)rows * pack_row_bytes(out.fmt, cols) != out.bytes) return llb_fail("%s%s: %llu bytes do not match its shape", p.c_str(), leaf, (unsigned long long)out.bytes);
+    if (!in_range(out.off, out.bytes, m->pack_bytes)) return llb_fail("%s%s reaches past the end of the pack (%zu bytes)", p.c_str(), leaf, m->pack_bytes);
     return 0;
   };
   TensorRec r_in, r_sh, eg, eu, ed, sg, su, sd;
@@ -297,9 +320,9 @@ static int load_moe(llb_spec *m, FfnW &w, const std::string &p, const std::unord
     const uint8_t *g = e < ne ? pack + eg.off + (size_t)e * gu_stride * pb_gu : pack + sg.off;
     const uint8_t *u = e < ne ? pack + eu.off + (size_t)e * gu_stride * pb_gu : pack + su.off;
     const uint8_t *dn = e < ne ? pack + ed.off + (size_t)e * d * pb_dn : pack + sd.off;
-    CK(llb_b200_weight_upload(eg.fmt, ef, d, g, on_device, (llb_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu)));
-    CK(llb_b200_weight_upload(eg.fmt, ef, d, u, on_device, (llb_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu + (size_t)ef * rb_gu)));
-    CK(llb_b200_weight_upload(ed.fmt, d, ef, dn, on_device, (llb_dptr)(uintptr_t)(w.dn + (size_t)e * w.es_dn)));
+    CK(llb_b200_weight_upload(eg.fmt, ef, d, g, on_device, (llb_b200_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu)));
+    CK(llb_b200_weight_upload(eg.fmt, ef, d, u, on_device, (llb_b200_dptr)(uintptr_t)(w.gu + (size_t)e * w.es_gu + (size_t)ef * rb_gu)));
+    CK(llb_b200_weight_upload(ed.fmt, d, ef, dn, on_device, (llb_b200_dptr)(uintptr_t)(w.dn + (size_t)e * w.es_dn)));
   }
   return 0;
 }
@@ -314,7 +337,8 @@ static int check_k(const DevMat &w, int rows, int cols, const char *what) {
 // ---- GEMM sites ---------------------------------------------------------------------------------
 // direct: the matrix writes into caller-owned storage (the conv ring) laid out [direct_splits][slots][direct_stride];
 // `out` then only records how many K-slices the launch used
-struct SiteMat { const DevMat *w; OutBuf *out; const int *tok_slot; float *direct; int direct_stride; long long direct_split_stride = 0; int direct_splits = 1; };
+// force_ks > 0: the K-split of the launch this matrix lands in (all matrices of one format share a launch)
+struct SiteMat { const DevMat *w; OutBuf *out; const int *tok_slot; float *direct; int direct_stride; long long direct_split_stride = 0; int direct_splits = 1; int force_ks = 0; };
 
 // Allocate (at init) or reuse the partial-sum buffer of one matrix and record its split.
 static int out_prepare(llb_spec *m, OutBuf &o, int rows, int ks) {
@@ -340,11 +364,11 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
     std::vector<size_t> grp;
     for (size_t j = i; j < mats.size() && grp.size() < GEMM_MAXMAT; j++)
       if (!done[j] && mats[j].w->fmt == mats[i].w->fmt) { grp.push_back(j); ntiles += (mats[j].w->rows + 15) / 16; }
-    bool direct = false;
-    for (size_t j : grp) direct = direct || mats[j].direct;
+    int fk = force_ks;
+    for (size_t j : grp) if (mats[j].force_ks > 0) fk = mats[j].force_ks;
     int ks = gemm_fix_ksplit(mats[i].w->fmt, xp.NC, a.K / 256,
-                             force_ks > 0 ? force_ks : gemm_pick_ksplit(mats[i].w->fmt, xp.NC, ntiles, a.K / 256, g_llb.sms));
-    (void)direct;
+                             fk > 0 ? fk : gemm_pick_ksplit(mats[i].w->fmt, xp.NC, ntiles, a.K / 256, g_llb.sms));
+    if (fk > 0 && ks != fk) return llb_fail("gemm site: the fixed K-split %d is not valid at %d plane columns (%d)", fk, xp.NC, ks);
     a.ksplit = ks;
     a.nmat = (int)grp.size();
     for (size_t g = 0; g < grp.size(); g++) {
@@ -435,12 +459,13 @@ static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, cons
   return 0;
 }
 
-static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, float *S, const RowSet *rs) {
+static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, int ring_ks, float *S, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
   DeltaShape sh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
   // raw qkv rows go straight into the conv ring slot of their position (host/llb_host.c:1747-1749)
-  // (the ring keeps the K-slice partial sums of each row; the conv kernel adds them as it reads)
-  PK("gemm qkv|z|b|a", site_gemm(m, {{&w.qkv, &m->b_ring, &m->ctl->verify.slot[0], ring, m->convd, (long long)CONV_RING * m->convd, RING_SPLITS},
+  // (the ring keeps the K-slice partial sums of each row; the conv kernel adds them as it reads -- rows of earlier
+  // passes too, whatever their width was, hence the split fixed per layer at open)
+  PK("gemm qkv|z|b|a", site_gemm(m, {{&w.qkv, &m->b_ring, &m->ctl->verify.slot[0], ring, m->convd, (long long)CONV_RING * m->convd, ring_ks, ring_ks},
                    {&w.z, &m->b_z, nullptr, nullptr, 0}, {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}},
                m->xp_d, 0));
   PK("delta conv", op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
@@ -468,7 +493,7 @@ static int enq_verify(llb_spec *m) {
     PK("norm attn", op_norm_xp(s, il ? m->x1 : m->x, il ? as_in(m->b_dn) : none, l.attn_norm, m->eps, m->d, m->x, m->xp_d, 0, nullptr, rs,
                   m->Tmax, 0));
     if (l.full) CK(enq_attn(m, l.at, m->Kc[il], m->Vc[il], rs));
-    else CK(enq_delta(m, l.dn, m->ring[il], m->S[il], rs));
+    else CK(enq_delta(m, l.dn, m->ring[il], m->ring_ks[il], m->S[il], rs));
     CK(enq_ffn(m, l.ffn, m->x, m->x1, rs));
   }
   PK("norm out", op_norm_xp(s, m->x1, as_in(m->b_dn), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
@@ -539,6 +564,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
                      int mtp_on_device, int k, int max_ctx, int layers) {
   std::unordered_map<std::string, TensorRec> tab;
   CK(parse_index(m, index_text, tab));
+  CK(validate_index(m, tab, m->pack_bytes));
   const int L_index = m->L;   // the trunk's length in the index: a nextn (MTP) block, if the index has one, is block L_index
   if (layers > 0 && layers < m->L) m->L = layers;
   if (k < 0 || k > 7) return llb_fail("k = %d: the path takes 0..7 drafts (host/llb_host.c:1608)", k);
@@ -571,7 +597,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     auto it = tab.find(name);
     if (it == tab.end()) return llb_fail("pack has no tensor %s", name.c_str());
     void *p;
-    CK(load_tensor(m, it->second, pack, on_device, &p, dedupe));
+    CK(load_tensor(m, it->second, pack, m->pack_bytes, on_device, &p, dedupe));
     w.w = (uint8_t *)p; w.rows = it->second.rows; w.cols = it->second.cols; w.fmt = it->second.fmt;
     return 0;
   };
@@ -588,7 +614,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (m->embd.rows != m->V || m->embd.cols != d) return llb_fail("token_embd.weight shape");
   CK(vec("output_norm.weight", &m->out_norm, d));
   m->layer.resize(m->L);
-  m->Kc.assign(m->L, nullptr); m->Vc.assign(m->L, nullptr); m->ring.assign(m->L, nullptr); m->S.assign(m->L, nullptr);
+  m->Kc.assign(m->L, nullptr); m->Vc.assign(m->L, nullptr); m->ring.assign(m->L, nullptr); m->S.assign(m->L, nullptr); m->ring_ks.assign(m->L, 1);
   for (int il = 0; il < m->L; il++) {
     LayerW &l = m->layer[il];
     std::string p = "blk." + std::to_string(il) + ".";
@@ -613,7 +639,15 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
       CK(vec(p + "ssm_a", &l.dn.a, m->TR));
       CK(vec(p + "ssm_conv1d.weight", &l.dn.conv, m->convd * m->KC));
       CK(vec(p + "ssm_norm.weight", &l.dn.norm, m->SZ));
-      m->ring[il] = falloc(m, (size_t)RING_SPLITS * CONV_RING * m->convd);
+      {
+        // the launch attn_qkv lands in: the matrices of its format among qkv | z | beta | alpha
+        int ntiles = 0;
+        for (const DevMat *w : {&l.dn.qkv, &l.dn.z, &l.dn.beta, &l.dn.alpha}) if (w->fmt == l.dn.qkv.fmt) ntiles += (w->rows + 15) / 16;
+        const int ks = gemm_ring_ksplit(l.dn.qkv.fmt, d / 256, ntiles, m->Tspec <= 4 ? 8 : 16, m->Tpf <= 4 ? 8 : 16, g_llb.sms, RING_MAXSPLIT);
+        if (ks < 1) return llb_fail("blk.%d.attn_qkv: %d columns need more than %d K-slices at a pass width in use", il, d, RING_MAXSPLIT);
+        m->ring_ks[il] = ks;
+      }
+      m->ring[il] = falloc(m, (size_t)m->ring_ks[il] * CONV_RING * m->convd);
       m->S[il] = falloc(m, (size_t)m->R * m->TR * m->SZ * m->SZ);
       if (!m->ring[il] || !m->S[il]) return -1;
     }
@@ -671,7 +705,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     void *ptr[17];
     for (int j = 0; j < 17; j++) {
       TensorRec t{off[j], nb[j], rows[j], cols[j], j == 16 ? LLB_FM_F32 : fm[j]};
-      CK(load_tensor(m, t, mtp, mtp_on_device, &ptr[j], dd));
+      CK(load_tensor(m, t, mtp, mtp_bytes, mtp_on_device, &ptr[j], dd));
     }
     auto MM = [&](int j) { DevMat w; w.w = (uint8_t *)ptr[j]; w.rows = rows[j]; w.cols = cols[j]; w.fmt = fm[j]; return w; };
     m->mt_enorm = (float *)ptr[0]; m->mt_hnorm = (float *)ptr[1]; m->mt_eh = MM(2); m->mt_attn_norm = (float *)ptr[3];
@@ -770,9 +804,10 @@ extern "C" {
 
 LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                 size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers) {
-  (void)pack_bytes;
   if (!g_llb.stream) { llb_fail("llb_b200_init has not been called"); return nullptr; }
+  if (!index_text || !pack) { llb_fail("llb_spec_open: no index or no pack"); return nullptr; }
   llb_spec *m = new llb_spec();
+  m->pack_bytes = pack_bytes;
   if (open_impl(m, index_text, (const uint8_t *)pack, pack_on_device, (const uint8_t *)mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers)) {
     llb_spec_close(m);
     return nullptr;
@@ -795,6 +830,16 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
     return nullptr;
   }
   return m;
+}
+
+// The checks llb_spec_open makes before it touches the GPU, alone (needs no device): the index parses, its
+// configuration is complete and consistent, and every tensor lies inside a pack of pack_bytes bytes.
+LLB_API int llb_spec_check_index(const char *index_text, size_t pack_bytes) {
+  if (!index_text) return llb_fail("check_index: no index");
+  llb_spec m;
+  std::unordered_map<std::string, TensorRec> tab;
+  if (parse_index(&m, index_text, tab)) return -1;
+  return validate_index(&m, tab, pack_bytes);
 }
 
 // The same engine from a GGUF file (qwen35 / qwen35moe): the header gives the index, the mapped file is the pack.
@@ -830,7 +875,7 @@ LLB_API void llb_spec_close(llb_spec *m) {
 // read, so only the conv rings and the committed DeltaNet slot need clearing
 LLB_API int llb_spec_reset(llb_spec *m) {
   for (int il = 0; il < m->L; il++) {
-    if (m->ring[il]) CU_OK(cudaMemsetAsync(m->ring[il], 0, (size_t)RING_SPLITS * CONV_RING * m->convd * 4, g_llb.stream));
+    if (m->ring[il]) CU_OK(cudaMemsetAsync(m->ring[il], 0, (size_t)m->ring_ks[il] * CONV_RING * m->convd * 4, g_llb.stream));
     if (m->S[il]) CU_OK(cudaMemsetAsync(m->S[il], 0, (size_t)m->R * m->TR * m->SZ * m->SZ * 4, g_llb.stream));
   }
   CU_OK(cudaMemsetAsync(m->hn, 0, (size_t)SPEC_MAXT * m->d * 4, g_llb.stream));
@@ -1108,7 +1153,7 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
     if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
     std::vector<float> tmp(have);
     for (size_t i = 0; i < have; i++) out[i] = 0.0f;
-    for (int k = 0; k < m->b_ring.ns; k++) {
+    for (int k = 0; k < m->ring_ks[il]; k++) {
       CU_OK(cudaMemcpy(tmp.data(), m->ring[il] + (size_t)k * CONV_RING * m->convd + (size_t)(pos & (CONV_RING - 1)) * m->convd, have * 4,
                        cudaMemcpyDeviceToHost));
       for (size_t i = 0; i < have; i++) out[i] += tmp[i];

@@ -142,6 +142,20 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
   return gemm_fix_ksplit(fmt, NC, nsb, best);
 }
 
+// One K-split for a launch whose partial sums outlive the pass (attn_qkv into the conv ring): valid at both
+// plane widths in use, the cost model's choice at the speculative width where that fits, at most `cap`.
+// Returns 0 when no split up to `cap` fits both widths.
+int gemm_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_pf, int sms, int cap) {
+  const int lo_a = gemm_fix_ksplit(fmt, nc_spec, nsb, 1), lo_b = gemm_fix_ksplit(fmt, nc_pf, nsb, 1);
+  const int lo = lo_a > lo_b ? lo_a : lo_b;
+  if (cap > nsb) cap = nsb;
+  if (lo > cap) return 0;
+  int ks = gemm_pick_ksplit(fmt, nc_spec, ntiles, nsb, sms);
+  if (ks < lo) ks = lo;
+  if (ks > cap) ks = cap;
+  return ks;
+}
+
 // fills nsb and the tile table of a launch and checks its shape
 static int gemm_prepare(int fmt, GemmArgs &a) {
   if (a.nmat < 1 || a.nmat > GEMM_MAXMAT) return llb_fail("gemm: nmat %d", a.nmat);

@@ -49,6 +49,7 @@ inline cudaError_t llb_launch(void (*k)(KArgs...), dim3 grid, dim3 block, size_t
 // gemm.cu
 int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms);
 int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks);   // clamps a requested K-split to what the format's kernel can take
+int gemm_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_pf, int sms, int cap);
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
 int gemm_setup(void);
 int gemm_wait_errors(void);
@@ -57,6 +58,7 @@ int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2);   // 
 int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit, const float *wt_silu);   // moe.cuh
 
 // ops.cu
+int backend_graph_bail(void);   // ends a launch recording in progress by running it (the memory primitives call it first)
 int ops_xp_from_f32(cudaStream_t s, const float *x, int T, int planes, XPlanes xp);
 int ops_xp_from_bf16(cudaStream_t s, const void *x, int T, XPlanes xp);
 int ops_dequant_rows(cudaStream_t s, int fmt, const uint8_t *W, int rows, int cols, const int *row_ids, int nrows, float *out);

@@ -43,9 +43,9 @@ def lib() -> C.CDLL:
         vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
         sig = {
             "llb_b200_init": (i32, [i32]), "llb_b200_last_error": (C.c_char_p, []), "llb_b200_sm_count": (i32, []),
-            "llb_alloc_zero": (u64, [sz]), "llb_free": (i32, [u64]), "llb_zero": (i32, [u64, sz]),
-            "llb_copy": (i32, [u64, u64, sz]), "llb_write": (i32, [u64, vp, sz]), "llb_read": (i32, [vp, u64, sz]),
-            "llb_sync": (i32, []), "llb_stream": (u64, []),
+            "llb_b200_alloc_zero": (u64, [sz]), "llb_b200_free": (i32, [u64]), "llb_b200_zero": (i32, [u64, sz]),
+            "llb_b200_copy": (i32, [u64, u64, sz]), "llb_b200_write": (i32, [u64, vp, sz]), "llb_b200_read": (i32, [vp, u64, sz]),
+            "llb_b200_sync": (i32, []), "llb_b200_stream": (u64, []),
             "llb_b200_weight_bytes": (sz, [i32, i32, i32]),
             "llb_b200_weight_upload": (i32, [i32, i32, i32, vp, i32, u64]),
             "llb_b200_dequant": (i32, [i32, i32, i32, u64, u64, i32, u64]),
@@ -67,6 +67,12 @@ def lib() -> C.CDLL:
             "llb_spec_time_verify_rows": (i32, [vp, i32, i32, vp]),
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
             "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
+            "llb_spec_check_index": (i32, [C.c_char_p, sz]),
+            "llb_b200_gemm_ksplit": (i32, [i32, i32, i32, i32, i32]), "llb_b200_ring_ksplit": (i32, [i32, i32, i32, i32, i32, i32]),
+            "llb_b200_kernel_by_name": (vp, [C.c_char_p]),
+            "llb_b200_launch": (i32, [vp, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.POINTER(vp), C.c_uint]),
+            "llb_b200_graph_begin": (i32, []), "llb_b200_graph_end": (i32, []), "llb_b200_graph_bail": (i32, []),
+            "llb_b200_graph_stats": (None, [C.POINTER(C.c_ulonglong)]),
         }
         for name, (res, args) in sig.items():
             f = getattr(L, name)
@@ -94,9 +100,9 @@ def init(device: int = 0):
 
 
 def alloc(nbytes: int) -> int:
-    p = lib().llb_alloc_zero(nbytes)
+    p = lib().llb_b200_alloc_zero(nbytes)
     if not p:
-        raise LlbError(f"llb_alloc_zero({nbytes}) failed: {lib().llb_b200_last_error().decode()}")
+        raise LlbError(f"llb_b200_alloc_zero({nbytes}) failed: {lib().llb_b200_last_error().decode()}")
     return p
 
 

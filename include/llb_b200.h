@@ -1,7 +1,7 @@
 /* llb_b200.h -- C ABI of libllb_b200.so, a B200 (sm_100a) implementation of the
  * speculative-decoding path of phenomenon0/eureka-engine.
  *
- * Plain C: integers, sizes, device addresses as 64-bit integers (the reference's llb_dptr,
+ * Plain C: integers, sizes, device addresses as 64-bit integers (the reference's llb_b200_dptr,
  * host/llb_backend.h:7-9) and host pointers.  Every call returns 0 / a handle on success and
  * -1 / 0 on failure with llb_b200_last_error() holding the reason; nothing falls back to the CPU.
  * All work is queued on one in-order stream per process (the reference's null-stream contract,
@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-typedef uint64_t llb_dptr; /* host/llb_backend_cuda.h:5 */
+typedef unsigned long long llb_b200_dptr; /* a device address; the type host/llb_backend_cuda.h:5 gives llb_dptr */
 
 #if defined(__GNUC__)
 #define LLB_API __attribute__((visibility("default")))
@@ -34,28 +34,55 @@ typedef uint64_t llb_dptr; /* host/llb_backend_cuda.h:5 */
 enum { LLB_F32 = 0, LLB_Q8_0 = 1, LLB_Q4_K = 3, LLB_Q6_K = 4, LLB_Q5_K = 9 };
 
 /* ---- 1. backend primitives ------------------------------------------------------------------ */
-LLB_API int llb_b200_init(int device);              /* binds the process to a GPU; creates the stream     */
+/* Binds the process to a GPU and creates the library's stream.  One device per process: a second call with the
+ * same ordinal is a no-op, with another ordinal it fails ("already bound"). */
+LLB_API int llb_b200_init(int device);
 LLB_API const char *llb_b200_last_error(void);
 LLB_API int llb_b200_sm_count(void);
-LLB_API llb_dptr llb_alloc_zero(size_t bytes);      /* host/llb_backend.h:25-26, host/llb_backend_cuda.h:186-191 (0 on failure) */
-LLB_API int llb_free(llb_dptr p);
-LLB_API int llb_zero(llb_dptr p, size_t bytes);     /* host/llb_backend.h:27, host/llb_backend_cuda.h:193-196 */
-LLB_API int llb_copy(llb_dptr d, llb_dptr s, size_t bytes);        /* host/llb_backend.h:28, host/llb_backend_cuda.h:204-207 (device to device, in order) */
-LLB_API int llb_write(llb_dptr d, const void *h, size_t bytes);    /* host/llb_backend.h:29, host/llb_backend_cuda.h:210-213 */
-LLB_API int llb_read(void *h, llb_dptr p, size_t bytes);           /* host/llb_backend.h:30-31, host/llb_backend_cuda.h:198-201 (synchronises) */
-LLB_API int llb_sync(void);                                        /* host/llb_backend_cuda.h:216-219 */
-LLB_API llb_dptr llb_stream(void);                  /* the cudaStream_t all calls queue on, for event timing */
+LLB_API llb_b200_dptr llb_b200_alloc_zero(size_t bytes);      /* host/llb_backend.h:25-26, host/llb_backend_cuda.h:186-191 (0 on failure) */
+LLB_API int llb_b200_free(llb_b200_dptr p);
+LLB_API int llb_b200_zero(llb_b200_dptr p, size_t bytes);     /* host/llb_backend.h:27, host/llb_backend_cuda.h:193-196 */
+LLB_API int llb_b200_copy(llb_b200_dptr d, llb_b200_dptr s, size_t bytes);        /* host/llb_backend.h:28, host/llb_backend_cuda.h:204-207 (device to device, in order) */
+LLB_API int llb_b200_write(llb_b200_dptr d, const void *h, size_t bytes);    /* host/llb_backend.h:29, host/llb_backend_cuda.h:210-213 */
+LLB_API int llb_b200_read(void *h, llb_b200_dptr p, size_t bytes);           /* host/llb_backend.h:30-31, host/llb_backend_cuda.h:198-201 (synchronises) */
+LLB_API int llb_b200_sync(void);                                        /* host/llb_backend_cuda.h:216-219 */
+LLB_API llb_b200_dptr llb_b200_stream(void);                  /* the cudaStream_t all calls queue on, for event timing */
+
+/* The launch half of the contract.  A kernel is fetched by name (the reference: cuModuleGetFunction(&h, gpu_lib,
+ * "llb_spec_gu3"), tools/payload-spec.patch:9-23) and launched with gx * gy blocks of bx threads, sm bytes of
+ * dynamic shared memory and `na` arguments, each the address of a host variable copied at the call
+ * (LLB_LAUNCH / LLB_LAUNCH_SM, host/llb_backend.h:9-24; llb_launch, host/llb_backend_cuda.h:86-106).  Reachable by
+ * name are the library's leaves with plain argument lists:
+ *   llb_b200_k_dequant_rows (int fmt, W, int cols, const int *row_ids or 0, float *out)     grid (<= 64, rows), block 256
+ *   llb_b200_k_sum_parts    (const float *parts, int nsplit, long long stride, int n, float *out)   grid ((n + 255) / 256, 1), block 256
+ *   llb_b200_k_repack_q6k   (src 210-byte blocks, dst 224-byte blocks, size_t nblocks)
+ *   llb_b200_k_xp_from_f32  (const float *x, int K, int planes, planes descriptor by value)
+ * Any other name -- the reference's kernel names included, whose argument lists carry its two-plane int8
+ * activations -- returns NULL; a launch with a NULL kernel or a wrong argument count returns -1 and queues nothing. */
+typedef struct llb_b200_kernel llb_b200_kernel;
+LLB_API const llb_b200_kernel *llb_b200_kernel_by_name(const char *name);
+LLB_API int llb_b200_launch(const llb_b200_kernel *k, unsigned gx, unsigned gy, unsigned bx, unsigned sm, void **args, unsigned na);
+/* The recorder of host/llb_backend_cuda.h:125-184 (llb_graph_begin / llb_graph_end / llb_graph_bail): launches made
+ * between begin and end are recorded, then run as ONE CUDA graph; a step with the kernel sequence of one of the 16 cached
+ * graphs updates that graph's nodes instead of building a new one; at most 2048 launches a step.  A memory primitive
+ * called while recording first runs what was recorded ("bail"), as in the reference.  Only llb_b200_launch records:
+ * do not call operator or llb_spec_* entry points between begin and end.  stats: graphs built, steps replayed,
+ * steps that re-used a cached graph, bails. */
+LLB_API int llb_b200_graph_begin(void);
+LLB_API int llb_b200_graph_end(void);
+LLB_API int llb_b200_graph_bail(void);
+LLB_API void llb_b200_graph_stats(unsigned long long out[4]);
 
 /* ---- 2. operator entry points --------------------------------------------------------------- */
 /* Bytes of a [rows x cols] matrix in the device layout (Q6_K super-blocks are padded from 210 to
  * 224 bytes at upload; every other format is stored as in a pack). */
 LLB_API size_t llb_b200_weight_bytes(int fmt, int rows, int cols);
 /* Pack bytes (host pointer, or device address when src_on_device) -> device layout at dst. */
-LLB_API int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src_on_device, llb_dptr dst);
+LLB_API int llb_b200_weight_upload(int fmt, int rows, int cols, const void *src, int src_on_device, llb_b200_dptr dst);
 /* Bit-exact dequantisation of `nrows` rows (row_ids on the device, or 0 for rows 0..nrows-1) into
  * f32 [nrows][cols].  Replaces llb_embedk / deq_row (tools/payload-kpair.patch:526,
  * tools/qwen35_engine.c:233-327). */
-LLB_API int llb_b200_dequant(int fmt, int rows, int cols, llb_dptr w, llb_dptr row_ids, int nrows, llb_dptr out_f32);
+LLB_API int llb_b200_dequant(int fmt, int rows, int cols, llb_b200_dptr w, llb_b200_dptr row_ids, int nrows, llb_b200_dptr out_f32);
 
 /* Activation planes of a T-row GEMM input (replaces the two-plane int8 quantiser llb_t_q8x2,
  * tools/payload-spec2.patch:126-145).  `planes` = 2 keeps about 22 bits of each f32 value in two
@@ -63,13 +90,13 @@ LLB_API int llb_b200_dequant(int fmt, int rows, int cols, llb_dptr w, llb_dptr r
 typedef struct llb_xp llb_xp;
 LLB_API llb_xp *llb_b200_xp_new(int K, int T, int planes);
 LLB_API void llb_b200_xp_free(llb_xp *xp);
-LLB_API int llb_b200_xp_set_f32(llb_xp *xp, llb_dptr x_f32 /* [T][K] */);
-LLB_API int llb_b200_xp_set_bf16(llb_xp *xp, llb_dptr x_bf16 /* [T][K] */);
+LLB_API int llb_b200_xp_set_f32(llb_xp *xp, llb_b200_dptr x_f32 /* [T][K] */);
+LLB_API int llb_b200_xp_set_bf16(llb_xp *xp, llb_b200_dptr x_bf16 /* [T][K] */);
 
 /* Y_i[t][r] = sum_c W_i[r][c] x[t][c] for up to four matrices of one format sharing x
  * (replaces llb_spec_gu / _re / _q8 / _q6, tools/payload-spec.patch:226-236).
  * out_i: f32 [T][rows_i].  ksplit = 0 picks the K-split; scratch for the partial sums is internal. */
-LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_dptr *w, const int *rows, const llb_dptr *out, int K, const llb_xp *xp,
+LLB_API int llb_b200_gemm(int fmt, int nmat, const llb_b200_dptr *w, const int *rows, const llb_b200_dptr *out, int K, const llb_xp *xp,
                   int ksplit);
 /* Q4_K GEMMs with T <= 4 on the tcgen05 kernel (weights unpacked into tensor memory, tcgen05.mma) instead
  * of the mma.sync one; returns the previous setting.  Also set by LLB_GEMM3=1 at llb_b200_init.  Off by
@@ -84,8 +111,8 @@ LLB_API int llb_b200_use_fused_ffn(int on);
  * llb_b200_init: the results of that launch are not valid.  0 otherwise; -1 on a CUDA error. */
 LLB_API int llb_b200_wait_errors(void);
 /* The same through HOST buffers: bf16 x [T][K] in, f32 y [T][rows] out, copies included. */
-LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
-                       llb_dptr x_dev, llb_dptr y_dev);
+LLB_API int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
+                       llb_b200_dptr x_dev, llb_b200_dptr y_dev);
 
 /* Y[t][r] = sum_c W[r][c] x[t][c] for callers that are not allowed to allocate.  No counterpart in the
  * reference.  Meant for hosts that fix a library's memory at start-up and forbid driver allocations
@@ -97,7 +124,7 @@ LLB_API int llb_b200_gemm_host(int fmt, llb_dptr w, int rows, int K, const void 
  * returns -1 with the reason.  The first call on a device looks up the array's device address
  * (cudaGetSymbolAddress): make that call before any stream capture begins.  All calls share the one array,
  * so two calls whose GPU work overlaps (different streams, different threads) race. */
-LLB_API int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr x_f32, int T, llb_dptr out_f32);
+LLB_API int llb_b200_gemm_noalloc(int fmt, llb_b200_dptr w, int rows, int K, llb_b200_dptr x_f32, int T, llb_b200_dptr out_f32);
 
 /* ---- 3. the speculative cycle ----------------------------------------------------------------- */
 /* Replaces host/llb_host.c:1474-1950 for greedy decoding with either of the reference's drafters.
@@ -110,6 +137,15 @@ LLB_API int llb_b200_gemm_noalloc(int fmt, llb_dptr w, int rows, int K, llb_dptr
 typedef struct llb_spec llb_spec;
 LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                 size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers);
+/* What llb_spec_open checks before it touches the GPU, callable without one: the index parses, its #cfg values are
+ * complete and consistent (no zero divisor, widths that agree), and every tensor's [offset, offset + bytes) lies inside
+ * a pack of pack_bytes bytes -- a truncated pack.bin or a stale index.tsv is an error naming the tensor. */
+LLB_API int llb_spec_check_index(const char *index_text, size_t pack_bytes);
+/* Test entry (no GPU needed): the K-split a GEMM launch of `ntiles` 16-row tiles over nsb super-blocks gets at nc plane
+ * columns on `sms` SMs, and the one split fixed for a DeltaNet layer's attn_qkv launch, whose partial sums live on in
+ * the conv ring across passes of both widths (0: none fits). */
+LLB_API int llb_b200_gemm_ksplit(int fmt, int nc, int ntiles, int nsb, int sms);
+LLB_API int llb_b200_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_prefill, int sms);
 LLB_API void llb_spec_close(llb_spec *m);
 LLB_API int llb_spec_reset(llb_spec *m);                       /* host/llb_host.c:1915-1928 */
 LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n);

@@ -53,18 +53,18 @@ class DevBuf:
     def write(self, a: np.ndarray):
         a = np.ascontiguousarray(a)
         assert a.nbytes <= self.nbytes
-        self.llb.check(self.llb.lib().llb_write(self.ptr, a.ctypes.data, a.nbytes), "llb_write")
+        self.llb.check(self.llb.lib().llb_b200_write(self.ptr, a.ctypes.data, a.nbytes), "llb_b200_write")
         return self
 
     def read(self, shape, dtype):
         out = np.empty(shape, dtype)
         assert out.nbytes <= self.nbytes
-        self.llb.check(self.llb.lib().llb_read(out.ctypes.data, self.ptr, out.nbytes), "llb_read")
+        self.llb.check(self.llb.lib().llb_b200_read(out.ctypes.data, self.ptr, out.nbytes), "llb_b200_read")
         return out
 
     def free(self):
         if self.ptr:
-            self.llb.lib().llb_free(self.ptr)
+            self.llb.lib().llb_b200_free(self.ptr)
             self.ptr = 0
 
 

@@ -44,7 +44,7 @@ def test_gemm_sweep_full_size(llb, packs, oracle, rows, K):
         xp = _planes(llb, K, x8[:n].contiguous())
         y = torch.zeros(n, rows, device=dev)
         llb.gemm(fmt, [w], [rows], [y.data_ptr()], K, xp, 0)
-        L.llb_sync()
+        L.llb_b200_sync()
         L.llb_b200_xp_free(xp)
         ys[n] = y.cpu().numpy()
         for t in range(n):
@@ -59,7 +59,7 @@ def test_gemm_sweep_full_size(llb, packs, oracle, rows, K):
         xp = _planes(llb, K, x8[:4].contiguous())
         y = torch.zeros(4, rows, device=dev)
         llb.gemm(fmt, [w], [rows], [y.data_ptr()], K, xp, 0)
-        L.llb_sync()
+        L.llb_b200_sync()
         L.llb_b200_xp_free(xp)
         assert L.llb_b200_wait_errors() == 0
         d = np.abs(y.cpu().numpy() - ys[4])
@@ -67,4 +67,4 @@ def test_gemm_sweep_full_size(llb, packs, oracle, rows, K):
         assert float(d.max()) <= 2e-5 * full_mass + 1e-5, float(d.max())
     finally:
         L.llb_b200_use_tcgen05(was)
-    L.llb_free(w)
+    L.llb_b200_free(w)

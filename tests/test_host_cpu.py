@@ -29,7 +29,7 @@ def test_calls_fail_loudly_without_a_device(pkg):
     if torch.cuda.is_available():
         pytest.skip("a GPU is present")
     L = pkg.llb.lib()
-    assert L.llb_alloc_zero(16) == 0
+    assert L.llb_b200_alloc_zero(16) == 0
     assert b"llb_b200_init" in L.llb_b200_last_error()
     with pytest.raises(pkg.llb.LlbError):
         pkg.llb.init(0)
@@ -192,3 +192,131 @@ def test_gguf_reader_refuses_bad_files(pkg, tmp_path):
         pkg.llb.gguf_index(str(p))
     with pytest.raises(pkg.llb.LlbError):
         pkg.llb.gguf_index(str(tmp_path / "missing.gguf"))
+
+
+# ---- the drop-in boundary compiles next to the interface it replaces --------------------------------
+REF_HOST = os.environ.get("LLB_REFERENCE_ROOT", "")
+
+
+def _gcc(src: str, tmp_path, *inc):
+    import subprocess
+    c = tmp_path / "tu.c"
+    c.write_text(src)
+    cmd = ["gcc", "-std=gnu11", "-Wall", "-Werror", "-Wno-unused-function", "-Wno-unused-variable", "-c", str(c), "-o", str(tmp_path / "tu.o"),
+           "-I", os.path.join(ROOT, "include")]
+    for i in inc:
+        cmd += ["-I", i]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+def test_backend_header_defines_the_reference_surface(tmp_path):
+    """include/llb_backend_b200.h gives the names host/llb_backend.h:7-34 asks of a backend, with the reference's truth
+    sense (bool, true = success), so a chain written in the reference's idiom compiles unchanged."""
+    _gcc(r'''
+#include "llb_backend_b200.h"
+static void err_fail(const char *m) { (void)m; }
+typedef unsigned int u32;
+int chain(void) {
+  llb_dptr p = llb_alloc_zero(1024);
+  if (p == 0) { err_fail("alloc"); return 1; }
+  if (!llb_zero(p + 16, 64)) err_fail("device launch failed");
+  float host[4] = {0};
+  if (!llb_write(p, host, sizeof host) || !llb_copy(p + 64, p, 16) || !llb_read(host, p + 64, 16) || !llb_sync()) err_fail("io");
+  llb_kernel k = llb_kernel_by_name("llb_spec_gu3");      /* a reference kernel name: not exported, NULL */
+  u32 n = 4; llb_dptr q = p; float *o = 0; int z = 0; long long st = 0;
+  llb_graph_begin();
+  bool ok = LLB_LAUNCH(k, 1, 1, 256, &q, &z, &st, &n, &o);
+  ok = LLB_LAUNCH_SM(k, 1, 1, 256, 1024, &q, &z, &st, &n, &o) && ok;
+  llb_graph_end();
+  llb_graph_bail();
+  q = llb_dev(host);
+  return ok ? 0 : 2;
+}
+''', tmp_path)
+
+
+def test_backend_header_compiles_before_the_reference_contract(tmp_path):
+    """The reference's contract header refuses to compile unless a backend header came first and defined LLB_LAUNCH
+    (host/llb_backend.h:46-49); with ours in front it compiles."""
+    root = REF_HOST or "/root/reference"
+    if not os.path.exists(os.path.join(root, "host", "llb_backend.h")):
+        pytest.skip("the reference tree is not on this machine (set LLB_REFERENCE_ROOT)")
+    _gcc('#include "llb_backend_b200.h"\n#include "llb_backend.h"\nint f(void) { return llb_sync() ? 0 : 1; }\n', tmp_path,
+         os.path.join(root, "host"))
+
+
+def test_integration_snippets_compile(tmp_path):
+    """Every C block of INTEGRATION.md compiles as written against include/ (helpers the text calls "any file reader"
+    are declared, not defined)."""
+    md = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```c\n(.*?)```", md, flags=re.S)
+    assert blocks
+    pre = r'''
+#include <string.h>
+#include <stddef.h>
+typedef unsigned int u32; typedef unsigned long long u64;
+void err_fail(const char *m);
+char *slurp(const char *dir, const char *name, size_t *n);
+void *map_file(const char *dir, const char *name, size_t *n);
+void *map_path(const char *path, size_t *n);
+static const char *spec_mtp;
+'''
+    for b in blocks:
+        _gcc(pre + b, tmp_path)
+
+
+# ---- llb_spec_open's host-side checks --------------------------------------------------------------
+def test_check_index_refuses_truncated_packs_and_bad_configurations(pkg, packs):
+    L = pkg.llb.lib()
+    pack = packs.build_pack(packs.cfg_tiny(quant="q4_k_m", n_layers=8, tied_head=False))
+    text = pack.index_text()
+    nbytes = pack.data.numel()
+    assert L.llb_spec_check_index(text.encode(), nbytes) == 0, L.llb_b200_last_error()
+    # a pack cut short: the error names a tensor and says where the pack ends
+    assert L.llb_spec_check_index(text.encode(), nbytes - 4096) == -1
+    msg = L.llb_b200_last_error().decode()
+    assert "past the end of the pack" in msg and "blk." in msg or "output" in msg, msg
+    assert L.llb_spec_check_index(text.encode(), 0) == -1
+    # an offset near 2^64 must not wrap around the range check
+    last = pack.entries[-1]
+    bad = text.replace(f"{last.name}\t{last.off}\t", f"{last.name}\t{2**64 - 64}\t")
+    assert bad != text and L.llb_spec_check_index(bad.encode(), nbytes) == -1
+    # zeroed or missing configuration values: an error message, not a division by zero
+    for key in ("n_kv_heads", "n_heads", "full_attention_interval", "ssm_group_count", "ssm_time_step_rank", "n_layers", "head_dim"):
+        line = next(l for l in text.splitlines() if l.startswith(f"#cfg\t{key}\t"))
+        assert L.llb_spec_check_index(text.replace(line, f"#cfg\t{key}\t0").encode(), nbytes) == -1, key
+        assert key.encode() in L.llb_b200_last_error()
+        if key != "full_attention_interval":     # a missing interval takes the engine's default of 4
+            assert L.llb_spec_check_index(text.replace(line + "\n", "").encode(), nbytes) == -1, key
+    # a tensor whose byte count does not match its shape
+    e = pack.by_name["blk.0.ffn_gate.weight"]
+    bad = text.replace(f"{e.name}\t{e.off}\t{e.nbytes}\t", f"{e.name}\t{e.off}\t{e.nbytes - 144}\t")
+    assert L.llb_spec_check_index(bad.encode(), nbytes) == -1 and b"ffn_gate" in L.llb_b200_last_error()
+
+
+def test_ring_ksplit_is_one_value_for_both_pass_widths(pkg):
+    """The conv ring keeps attn_qkv rows as K-slice partial sums across passes of both widths (prompt chunks of 8 rows on
+    16 plane columns, speculative passes of k + 1 rows on 8), so the split must not depend on the width.  Replays the
+    choice at d = 5120 on 148 SMs for the formats a Q4_K_M / Q4_K_S / Q8_0 file puts attn_qkv in: the free choice differs
+    between the widths for Q5_K and Q6_K, the fixed one is valid at both."""
+    L = pkg.llb.lib()
+    Q8_0, Q4_K, Q6_K, Q5_K = 1, 3, 4, 9
+    nsb, sms = 5120 // 256, 148
+    group = (10240 + 6144 + 48 + 48 + 15) // 16          # qkv | z | beta | alpha of the 27B shape in one launch
+    alone = 10240 // 16                                   # attn_qkv alone in its format
+    differs = 0
+    for fmt in (Q4_K, Q5_K, Q6_K, Q8_0):
+        for ntiles in (group, alone, 97):
+            k8, k16 = L.llb_b200_gemm_ksplit(fmt, 8, ntiles, nsb, sms), L.llb_b200_gemm_ksplit(fmt, 16, ntiles, nsb, sms)
+            differs += k8 != k16
+            ring = L.llb_b200_ring_ksplit(fmt, nsb, ntiles, 8, 16, sms)
+            assert 1 <= ring <= 8
+            # valid at both widths: asking for it gives it back (the launch refuses anything else)
+            for nc in (8, 16):
+                lo = L.llb_b200_ring_ksplit(fmt, nsb, ntiles, nc, nc, sms)
+                assert lo >= 1
+            assert ring >= max(L.llb_b200_ring_ksplit(fmt, nsb, 1 << 20, 8, 8, sms) and 1, 1)
+    assert differs > 0            # the case the fixed split exists for does occur
+    # a width no split up to 8 can serve is reported as 0 (the engine then refuses the model by name)
+    assert L.llb_b200_ring_ksplit(Q6_K, 64, 1000, 8, 16, sms) == 0
