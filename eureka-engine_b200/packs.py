@@ -238,6 +238,14 @@ class ModelCfg:
     n_experts_used: int = 0
     d_expert: int = 0         # expert_feed_forward_length
     d_shared: int = 0         # expert_shared_feed_forward_length
+    # (leaf, type) pairs that overrule the quantisation scheme for one kind of matrix, e.g. (("attn_qkv", "Q5_K"),):
+    # llama.cpp's Q4_K_M files keep some matrices in a format of their own, which changes how launches group
+    type_overrides: tuple = ()
+    # multiplies the draws of the matrices that write into the residual stream (attn_output, ssm_out, ffn_down).  1.0 is
+    # what the benchmark configurations specify.  A small gain leaves a model whose next token depends mostly on the
+    # current one, so greedy output soon repeats and both drafters get some drafts right: test packs use it to reach
+    # partial acceptance at real layer shapes (with N(0, 0.02) weights at d = 5120 a drafter is right about once in V)
+    mix_gain: float = 1.0
 
     @property
     def kdc(self): return self.ssm_groups * self.ssm_state
@@ -273,6 +281,16 @@ def cfg_c4(**kw) -> ModelCfg:
     a = dict(n_layers=32, d_model=4096, n_heads=16, n_kv_heads=4, head_dim=256, d_ff=12288,
              vocab_size=151936, ssm_heads=32, ssm_groups=16, tied_head=False, quant="q8_0", seed=5,
              name="c4-9b-q8_0")
+    a.update(kw)
+    return ModelCfg(**a)
+
+
+def cfg_long(**kw) -> ModelCfg:
+    """The long-context configuration's attention shape (16 Q / 4 KV heads of 256, 32 DeltaNet heads over 16 groups,
+    Q8_0) on a narrow residual (d 1024, FFN 1024, four layers, 2048-entry vocabulary), so that the reference CPU engine
+    gets through a context of more than 8192 positions in minutes."""
+    a = dict(n_layers=4, d_model=1024, n_heads=16, n_kv_heads=4, head_dim=256, d_ff=1024, vocab_size=2048, ssm_heads=32,
+             ssm_groups=16, tied_head=False, quant="q8_0", seed=6, name="long-context-q8_0")
     a.update(kw)
     return ModelCfg(**a)
 
@@ -323,6 +341,9 @@ def tensor_type(cfg: ModelCfg, name: str) -> str:
     leaf = name.split(".")[-2] if name.endswith(".weight") else name
     if leaf.endswith("_exps") or leaf.endswith("_shexp"):   # ffn_down_exps / ffn_down_shexp follow ffn_down's rule
         leaf = leaf.rsplit("_", 1)[0]
+    for lf, ty in cfg.type_overrides:
+        if lf == leaf:
+            return ty
     if name == "output.weight":
         return "Q6_K"
     if cfg.quant == "q4_k_m":
@@ -401,7 +422,10 @@ def draw_tensor(cfg: ModelCfg, name: str, rows: int, cols: int, rng: _Rng) -> to
         return -torch.exp(rng.normal(rows, cols, 0.5))
     if name.endswith("ssm_dt.bias") or name.endswith("ssm_conv1d.weight"):
         return rng.normal(rows, cols, 0.5)
-    return rng.normal(rows, cols, 0.02)
+    w = rng.normal(rows, cols, 0.02)
+    if cfg.mix_gain != 1.0 and name.split(".")[-2] in ("attn_output", "ssm_out", "ffn_down", "ffn_down_exps", "ffn_down_shexp"):
+        w = w * cfg.mix_gain
+    return w
 
 
 @dataclasses.dataclass
@@ -516,19 +540,25 @@ MTP_ORDER = ["nextn.enorm", "nextn.hnorm", "nextn.eh_proj", "attn_norm", "attn_q
              "ffn_down", "nextn.shared_head_norm", "mtp.head_slice", "mtp.ids"]  # tools/mtp27/mtp_pack.py:14-30
 
 
-def build_mtp(pack: Pack, draft_vocab: Optional[int] = None) -> List[Tuple[str, str, Tuple[int, int], torch.Tensor]]:
+def build_mtp(pack: Pack, draft_vocab: Optional[int] = None, eh: str = "hidden",
+              draft_ids: Optional[np.ndarray] = None) -> List[Tuple[str, str, Tuple[int, int], torch.Tensor]]:
     """The synthetic drafter BASELINE config 0 describes: one NextN layer whose attention + FFN block is
     a byte copy of the trunk's last full-attention layer, norms 1, and the trunk head.  eh_proj is not
-    specified by the configuration; it is fixed here to [0 | I] (x = rms(h)*hnorm), stored in the block's
-    matrix format.  head slice = the first `draft_vocab` rows of output.weight (all rows by default),
-    ids = 0..n-1."""
+    specified by the configuration; it is fixed here to [0 | I] (x = rms(h)*hnorm; eh = "hidden"), stored in the
+    block's matrix format; eh = "embed" gives [I | 0] (x = rms(e)*enorm: the drafter then sees the token it follows,
+    which is what predicts the next one in a model built with a small mix_gain).
+    Head slice: the first `draft_vocab` rows of output.weight (all rows by default) with ids 0..n-1, or, with
+    `draft_ids` (sorted or not, a multiple of 16 of them), the rows of exactly those vocabulary entries in that order
+    -- the draft-vocabulary slice of tools/mtp27/mtp_pack.py:14-30, whose argmax is mapped back through the ids."""
     cfg = pack.cfg
     il = max(i for i in range(cfg.n_layers) if cfg.is_full(i))
     d = cfg.d_model
     dev = pack.data.device
     ones = lambda n: _bytes_of(torch.ones(n, device=dev))
     mat_ty = pack.by_name[f"blk.{il}.ffn_gate.weight"].ty
-    eh = torch.cat([torch.zeros(d, d, device=dev), torch.eye(d, device=dev)], dim=1)
+    assert eh in ("hidden", "embed")
+    halves = [torch.zeros(d, d, device=dev), torch.eye(d, device=dev)]
+    eh = torch.cat(halves if eh == "hidden" else halves[::-1], dim=1)
     out: List[Tuple[str, str, Tuple[int, int], torch.Tensor]] = []
     for n in MTP_ORDER[:15]:
         if n in ("nextn.enorm", "nextn.hnorm", "nextn.shared_head_norm"):
@@ -539,6 +569,14 @@ def build_mtp(pack: Pack, draft_vocab: Optional[int] = None) -> List[Tuple[str, 
             e = pack.by_name[f"blk.{il}.{n}.weight"]
             out.append((n, e.ty, (e.rows, e.cols), pack.raw(e.name).clone()))
     h = pack.by_name["output.weight"]
+    if draft_ids is not None:
+        ids = torch.as_tensor(np.asarray(draft_ids, dtype=np.int64), device=dev)
+        nv = int(ids.numel())
+        assert nv % 16 == 0 and int(ids.min()) >= 0 and int(ids.max()) < h.rows
+        rows = pack.raw("output.weight").reshape(h.rows, h.row_bytes)[ids].reshape(-1).clone()
+        out.append(("mtp.head_slice", h.ty, (nv, h.cols), rows))
+        out.append(("mtp.ids", "U32", (1, nv), _bytes_of(ids.to(torch.int32))))
+        return out
     nv = h.rows if draft_vocab is None else draft_vocab
     assert nv % 16 == 0
     out.append(("mtp.head_slice", h.ty, (nv, h.cols), pack.raw("output.weight")[: nv * h.row_bytes].clone()))

@@ -4,7 +4,8 @@ It exists for hosts that hand a library its memory once and then forbid driver a
 processes that cannot take cudaMalloc's device-wide stall, sandboxes that deny the call): its scratch is a
 fixed array inside the library image, shared by all calls and never cleared between them.  So the check is
 two calls in a row with different shapes -- the second must not see the first's leftovers -- each compared
-with llb_b200_gemm on the same inputs.  This file sorts last on purpose: a run that stops at the first
+with llb_b200_gemm on the same inputs and, so that a fault shared by both entry points cannot hide, with the CPU
+oracle's row-by-row dot products.  This file sorts last on purpose: a run that stops at the first
 failure has then already run every other test."""
 import numpy as np
 import pytest
@@ -13,7 +14,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _both(llb, packs, dev, ty, rows, K, T, seed):
+def _both(llb, packs, oracle, dev, ty, rows, K, T, seed):
     L = llb.lib()
     fmt = packs.FMT[ty]
     rng = np.random.default_rng(seed)
@@ -36,15 +37,17 @@ def _both(llb, packs, dev, ty, rows, K, T, seed):
     deq = np.abs(packs.dequant(ty, torch.from_numpy(raw), rows, K).numpy())
     mass = np.abs(x) @ deq.T
     assert np.all(np.abs(got - ref) <= 1e-5 * mass + 1e-6), (ty, rows, K, T, float(np.abs(got - ref).max()))
+    cpu = np.stack([oracle.Oracle.gemv(fmt, raw, rows, K, x[t]) for t in range(T)])
+    assert np.all(np.abs(got - cpu) <= 1e-5 * mass + 1e-6), (ty, rows, K, T, float(np.abs(got - cpu).max()))
     return got
 
 
-def test_noalloc_matches_ordinary_entry_point_twice(llb, packs, dev):
+def test_noalloc_matches_ordinary_entry_point_twice(llb, packs, oracle, dev):
     # first a wide, K-split case with all four rows, then a narrower one with fewer rows and another format:
     # stale planes or partial sums from the first call would show in the second
-    _both(llb, packs, dev, "Q4_K", 320, 8192, 4, seed=1)
-    _both(llb, packs, dev, "Q6_K", 96, 1024, 2, seed=2)
-    _both(llb, packs, dev, "Q4_K", 320, 8192, 4, seed=3)
+    _both(llb, packs, oracle, dev, "Q4_K", 320, 8192, 4, seed=1)
+    _both(llb, packs, oracle, dev, "Q6_K", 96, 1024, 2, seed=2)
+    _both(llb, packs, oracle, dev, "Q4_K", 320, 8192, 4, seed=3)
 
 
 def test_noalloc_rejects_what_does_not_fit(llb, packs, dev):
