@@ -521,21 +521,27 @@ k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const floa
   __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
   __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2], os[SPEC_MAXT][32], ssq[SPEC_MAXT], tot[SPEC_MAXT];
   __shared__ float red[2 * SPEC_MAXT][4];
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
   cg::cluster_group cl = cg::this_cluster();
-  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs_n, lane = tid & 31, wp = tid >> 5;
-  if (n < 1) return;   // every block of every cluster takes the same exit
+  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
   const int g = hh % sh.GK;
-  const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
+  const int jr = tid >> 2, cq = tid & 3;
   const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
   const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 4 * cq;
+  // The committed state (ring slot sc) was written by an earlier pass and sc by that pass's accept kernel: neither
+  // depends on the kernel in front, so the 16 KB a block reads from HBM are requested before the dependency wait.
+  pdl_trigger();
+  const int R = *(const volatile int *)&ctl->R, sc = *(const volatile int *)&ctl->sc;
   float st[32];
   {
     const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
 #pragma unroll
-    for (int i = 0; i < 8; i++) { float4 v = src[4 * i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
+    for (int i = 0; i < 8; i++) { float4 v = __ldcg(src + 4 * i); st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
   }
+  const float nwv = nw[32 * jq + lane];
+  pdl_wait();
+  rs = (const RowSet *)((uintptr_t)rs & ~(uintptr_t)1);
+  const int n = rs->n;
+  if (n < 1) return;   // every block of every cluster takes the same exit
   float qv[SPEC_MAXT], kv[SPEC_MAXT];
 #pragma unroll
   for (int t = 0; t < SPEC_MAXT; t++) {
@@ -610,7 +616,7 @@ k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const floa
     const float r = 1.0f / sqrtf(tot[t] / 128.0f + sh.eps);
     const int col = hh * 128 + 32 * jq;
     const float zz = part_get(z, (size_t)t * sh.vdc + col + lane);
-    xp_store32(xp, t, 2, col, os[t][lane] * r * nw[32 * jq + lane] * silu_f(zz), lane);
+    xp_store32(xp, t, 2, col, os[t][lane] * r * nwv * silu_f(zz), lane);
   }
 }
 int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,

@@ -2,8 +2,8 @@
 heads of 256 dims: four queries per kv head, 37 context slices per kv head on 148 SMs, 224 positions a slice -- the
 slice length is not a divisor of the context), the fp16 hi/lo K/V cache at that depth, 1027 prompt chunks of eight rows,
 and k = 1 and k = 5 (two and six verify rows: both plane widths).  Checked against ids, top-2 logit bits, the whole logit
-row after the prompt and a K row, all written by the REFERENCE CPU engine (tests/golden/make_golden_long.py, about
-a quarter of an hour of host time, which is why the fixture is committed instead of recomputed)."""
+row after the prompt and a K row, all written by the REFERENCE CPU engine (tests/golden/make_golden_long.py: half an
+hour of host time on eight cores, which is why the fixture is committed instead of recomputed)."""
 import hashlib
 import os
 
