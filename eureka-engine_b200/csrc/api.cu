@@ -3,6 +3,7 @@
 #include <stdlib.h>
 
 #include "host.cuh"
+#include "pf.cuh"
 
 LlbCtx g_llb;
 
@@ -218,7 +219,8 @@ int llb_b200_use_fused_ffn(int on) {
 }
 int llb_b200_wait_errors(void) {
   NEED_INIT(-1)
-  return gemm_wait_errors();
+  const int a = gemm_wait_errors(), b = pf_wait_errors();
+  return a < 0 || b < 0 ? -1 : (a | b);
 }
 
 int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp, llb_b200_dptr x_dev,

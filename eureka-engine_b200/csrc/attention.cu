@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256) k_attn_mma(const float *__restrict__ q, c
   for (int i = tid; i < NQP * (HD / 2); i += 256) {
     const int qi = i / (HD / 2), dd = 2 * (i - qi * (HD / 2)), g = qi / Tmax, r = qi - g * Tmax;
     float2 v = make_float2(0.f, 0.f);
-    if (qi < NQ && r < n) v = *(const float2 *)(q + ((size_t)r * sh.H + kvh * G + g) * HD + dd);
+    if (qi < NQ && r < n) v = __ldcg((const float2 *)(q + ((size_t)r * sh.H + kvh * G + g) * HD + dd));
     const __half2 h = __floats2half2_rn(v.x, v.y);
     const float2 hf = __half22float2(h);
     *(__half2 *)(qh + qi * RSK + dd) = h;
@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(256) k_attn_mma(const float *__restrict__ q, c
 // (llb_attn4_combine + llb_t_ogq, tools/payload-sk8add.patch, tools/payload-spec2.patch:149-156)
 // block = (head, row); thread (sg, i4): split group sg, dims 4*i4 .. 4*i4+3
 __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
-                                                   AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs) {
+                                                   AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs, __half *__restrict__ kg, int kg_row0) {
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float wsm[128];
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm,
   const int total = rs_p0 + rs_n;
   const int per = max(sh.min_per, ((total + nsplit - 1) / nsplit + 31) & ~31), nact = min(nsplit, (total + per - 1) / per);
   float m = -INFINITY, l = 0.0f;
-  if (i < nact) { m = pm[qb + i]; l = pl[qb + i]; }
+  if (i < nact) { m = __ldcg(pm + qb + i); l = __ldcg(pl + qb + i); }
   float M = aw_max(m);
   __syncthreads();
   if (lane == 0) red[i >> 5] = M;
@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm,
       for (int jj = 0; jj < 4; jj++) {
         const int s = s0 + jj * ng;
         ws[jj] = s < nact ? wsm[s] : 0.0f;
-        v[jj] = ws[jj] != 0.0f ? *(const float4 *)(po + (qb + s) * hd + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[jj] = ws[jj] != 0.0f ? __ldcg((const float4 *)(po + (qb + s) * hd + 4 * i4)) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
       for (int jj = 0; jj < 4; jj++) { o.x += v[jj].x * ws[jj]; o.y += v[jj].y * ws[jj]; o.z += v[jj].z * ws[jj]; o.w += v[jj].w * ws[jj]; }
@@ -277,7 +277,9 @@ __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm,
     const float4 gate = part_get4(qg, (size_t)t * 2 * sh.H * hd + (size_t)h * 2 * hd + hd + 4 * i);
     const float hv[4] = {(a.x / L) / (1.0f + expf(-gate.x)), (a.y / L) / (1.0f + expf(-gate.y)), (a.z / L) / (1.0f + expf(-gate.z)),
                          (a.w / L) / (1.0f + expf(-gate.w))};
-    xp_store4(xp, t, 2, h * hd + 4 * i, hv, lane, true);
+    // the prompt path takes the rows as fp16 in the dense GEMM's k-group-major order instead of the T-row planes
+    if (kg) pf_kg_store4(kg, sh.H * hd, kg_row0 + t, h * hd + 4 * i, hv[0], hv[1], hv[2], hv[3]);
+    else xp_store4(xp, t, 2, h * hd + 4 * i, hv, lane, true);
   }
 }
 
@@ -300,7 +302,7 @@ template <int HD> static int att_hd(cudaStream_t s, int nqg, dim3 grid, const fl
 }
 
 int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
-                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax) {
+                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg, int kg_row0) {
   const int G = sh.H / sh.KV, NQ = G * Tmax, nqg = (NQ + 7) / 8;
   dim3 grid(sh.KV, nsplit);
   int rc;
@@ -309,7 +311,7 @@ int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *V
   else return llb_fail("attention: head_dim %d", sh.hd);
   if (rc) return rc;
   CU_OK(cudaGetLastError());
-  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(256), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs));
+  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(256), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs, kg, kg_row0));
   CU_OK(cudaGetLastError());
   return 0;
 }

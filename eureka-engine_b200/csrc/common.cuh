@@ -159,6 +159,23 @@ __device__ __forceinline__ void xp_store4(const XPlanes &xp, int t, int planes, 
   }
 }
 
+// ---- activations of a prompt chunk ----------------------------------------------------------------
+#define PF_R 128              // rows of a prompt chunk (= N of the dense GEMM's MMA, pfmm.cuh)
+// Activations of a chunk for the dense GEMM, "k-group major", as two fp16 planes like the T-row planes: hi = fp16(x),
+// lo = fp16((x - hi) * 2048), about 22 bits of x.  Element (row r, column k) of a [PF_R][K] matrix sits at half index
+// ((k >> 3) * PF_R + r) * 8 + (k & 7) of its plane; the lo plane follows the hi plane (K * PF_R halves further on).  Eight
+// consecutive columns of one row are one 16-byte core-matrix row, the PF_R rows of a k-group are contiguous (2 KB), and
+// a 64-column stage of one plane is one 16 KB run.
+__host__ __device__ inline size_t pf_kg_halves(int K) { return (size_t)2 * K * PF_R; }
+// four consecutive columns k .. k+3 (k a multiple of 4) of row r into both planes
+__device__ __forceinline__ void pf_kg_store4(__half *x, int K, int r, int k, float v0, float v1, float v2, float v3) {
+  const size_t i = ((size_t)(k >> 3) * PF_R + r) * 8 + (k & 4);
+  const __half2 a = __floats2half2_rn(v0, v1), b = __floats2half2_rn(v2, v3);
+  const float2 af = __half22float2(a), bf = __half22float2(b);
+  const __half2 c = __floats2half2_rn((v0 - af.x) * XP_LO_SCALE, (v1 - af.y) * XP_LO_SCALE), d = __floats2half2_rn((v2 - bf.x) * XP_LO_SCALE, (v3 - bf.y) * XP_LO_SCALE);
+  *(uint2 *)(x + i) = make_uint2(*(const uint32_t *)&a, *(const uint32_t *)&b);
+  *(uint2 *)(x + (size_t)K * PF_R + i) = make_uint2(*(const uint32_t *)&c, *(const uint32_t *)&d);
+}
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Every kernel of a pass is launched with the programmatic-serialization attribute: the next kernel's
 // CTAs may become resident while this one still runs, do whatever does not depend on it (a GEMM

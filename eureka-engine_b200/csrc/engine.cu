@@ -19,6 +19,7 @@
 #include "../../include/llb_b200.h"
 #include "model.cuh"
 #include "gguf.cuh"
+#include "pf.cuh"
 
 struct DevMat { uint8_t *w = nullptr; int rows = 0, cols = 0, fmt = -1; };
 struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; size_t cap = 0; };   // K-slice partial sums of one matrix (cap: floats allocated)
@@ -35,6 +36,17 @@ struct LayerW { bool full = false; float *attn_norm = nullptr; AttnW at; DeltaW 
 
 // blocked: Q8_0 in GGUF's [f16 d][32 x int8] blocks (host memory only), re-sliced to the row-split layout at upload
 struct TensorRec { uint64_t off, bytes; int rows, cols, fmt; bool blocked = false; };
+
+// Buffers of the prompt path (pf.cu), allocated at the first fast prefill: residual rows, fp16 activations in the
+// dense GEMM's k-group-major order, GEMM outputs as K-slice partial sums of PF_R rows, and the row sets of the chunk.
+struct PfState {
+  bool ready = false;
+  float *x = nullptr, *x1 = nullptr, *hn = nullptr, *e = nullptr, *qn = nullptr, *y = nullptr, *beta = nullptr, *decay = nullptr, *o = nullptr;
+  __half *kg_d = nullptr, *kg_f = nullptr, *kg_qa = nullptr, *kg_v = nullptr, *kg_2d = nullptr;
+  OutBuf q, k, v, qkv, z, bp, ap, a, g, u, dn, eh;
+  RowSet *rs = nullptr;    // [0] the whole chunk, [1 + i] its i-th group of attention rows
+  int *ids = nullptr;      // the chunk's tokens
+};
 
 struct llb_spec {
   // configuration (index.tsv #cfg keys, tools/qwen35_engine.c:386-409)
@@ -92,6 +104,9 @@ struct llb_spec {
   bool delta_fused = true;            // LLB_DELTA_FUSED=0: DeltaNet scan and gated norm as two kernels
   bool moe_silu_fused = true;         // LLB_MOE_SILU_FUSED=0: the experts' silu as its own kernel also for T <= 4
   unsigned int *tile_ctr = nullptr;   // last-writer reduction counters of the GEMMs (one word per row tile)
+  PfState pf;
+  int prefill_mode = 0;   // 0: every prompt row through the T-row pass; 1: chunks of PF_R rows through the dense path (LLB_PREFILL=fast)
+  double pf_rows = 0;     // prompt rows the dense path has processed since the engine was opened
   // graphs
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
   size_t n_spec_nodes = 0, n_verify_nodes = 0;
@@ -579,6 +594,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   { const char *e = getenv("LLB_DELTA_FUSED"); m->delta_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_MOE_SILU_FUSED"); m->moe_silu_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM_REDUCE"); m->reduce_in_gemm = e && e[0] == '1'; }
+  { const char *e = getenv("LLB_PREFILL"); m->prefill_mode = e && !strcmp(e, "fast"); }   // the reference's switch (host/llb_host.c:206)
   m->k = k; m->Tspec = k + 1; m->max_ctx = max_ctx;
   {
     // rows of a prompt chunk: 8, fewer where (H / KV) x rows would pass the attention kernel's 48 queries per kv head
@@ -785,6 +801,143 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   return 0;
 }
 
+// ---- the prompt path: chunks of up to PF_R rows through dense tcgen05 GEMMs (pf.cu) ----------------------------
+#define PF_GROUPS (PF_R + 1)
+static int pf_alloc(llb_spec *m) {
+  PfState &f = m->pf;
+  if (f.ready) return 0;
+  CK(pf_setup());
+  const int d = m->d, qa = m->H * m->hd;
+  auto kg = [&](int K) { return (__half *)dalloc(m, pf_kg_halves(K) * 2); };
+  f.x = falloc(m, (size_t)PF_R * d); f.x1 = falloc(m, (size_t)PF_R * d); f.hn = falloc(m, (size_t)(PF_R + 1) * d); f.e = falloc(m, (size_t)PF_R * d);
+  f.qn = falloc(m, (size_t)PF_R * qa); f.y = falloc(m, (size_t)PF_R * m->convd); f.beta = falloc(m, (size_t)PF_R * m->TR);
+  f.decay = falloc(m, (size_t)PF_R * m->TR); f.o = falloc(m, (size_t)PF_R * m->vdc);
+  f.kg_d = kg(d); f.kg_f = kg(m->f); f.kg_qa = kg(qa); f.kg_v = kg(m->vdc); f.kg_2d = kg(2 * d);
+  f.rs = (RowSet *)dalloc(m, sizeof(RowSet) * (1 + PF_GROUPS));
+  f.ids = (int *)dalloc(m, (size_t)(PF_R + 1) * 4);
+  if (!f.x || !f.x1 || !f.hn || !f.e || !f.qn || !f.y || !f.beta || !f.decay || !f.o || !f.kg_d || !f.kg_f || !f.kg_qa || !f.kg_v || !f.kg_2d ||
+      !f.rs || !f.ids) return -1;
+  f.ready = true;
+  return 0;
+}
+
+struct PfSiteMat { const DevMat *w; OutBuf *out; };
+// the dense GEMMs of one site: matrices sharing the activations `kg` of K columns, one launch per format
+static int pf_site(llb_spec *m, std::vector<PfSiteMat> mats, const __half *kg, int K, int R) {
+  std::vector<bool> done(mats.size(), false);
+  for (size_t i = 0; i < mats.size(); i++) {
+    if (done[i]) continue;
+    PfArgs a;
+    memset(&a, 0, sizeof a);
+    a.K = K; a.R = R; a.x = kg;
+    int ntiles = 0;
+    std::vector<size_t> grp;
+    for (size_t j = i; j < mats.size() && grp.size() < PF_MAXMAT; j++)
+      if (!done[j] && mats[j].w->fmt == mats[i].w->fmt) { grp.push_back(j); ntiles += (mats[j].w->rows + 127) / 128; }
+    a.ksplit = pf_pick_ksplit(ntiles, K / 256, g_llb.sms);
+    a.nmat = (int)grp.size();
+    for (size_t g = 0; g < grp.size(); g++) {
+      const PfSiteMat &sm = mats[grp[g]];
+      OutBuf &o = *sm.out;
+      const size_t need = (size_t)a.ksplit * PF_R * sm.w->rows;
+      if (!o.p || o.cap < need) {
+        o.p = falloc(m, need);
+        if (!o.p) return -1;
+        o.cap = need;
+      }
+      o.ns = a.ksplit; o.stride = (long long)PF_R * sm.w->rows;
+      a.m[g].W = sm.w->w; a.m[g].rows = sm.w->rows; a.m[g].ostride = sm.w->rows; a.m[g].out = o.p; a.m[g].split_stride = o.stride;
+      done[grp[g]] = true;
+    }
+    CK(pf_gemm(g_llb.stream, mats[i].w->fmt, a));
+  }
+  return 0;
+}
+
+// One chunk: rows of positions p0 .. p0 + R - 1 with the given tokens through every layer.  Leaves the trunk's K/V rows,
+// conv rings and DeltaNet states as the T-row pass would have (the state written back into the committed slot), the
+// drafter's K/V rows of the same positions, and in pf.hn row 0 the normed hidden of the chunk's last row.
+static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
+  PfState &f = m->pf;
+  cudaStream_t s = g_llb.stream;
+  const int d = m->d, qa = m->H * m->hd, gsz = m->Tpf, ngrp = (R + gsz - 1) / gsz;
+  std::vector<RowSet> rs(1 + ngrp);
+  memset(rs.data(), 0, rs.size() * sizeof(RowSet));
+  rs[0].n = R; rs[0].pos0 = p0;
+  for (int g = 0; g < ngrp; g++) { rs[1 + g].n = R - g * gsz < gsz ? R - g * gsz : gsz; rs[1 + g].pos0 = p0 + g * gsz; }
+  CU_OK(cudaMemcpyAsync(f.rs, rs.data(), rs.size() * sizeof(RowSet), cudaMemcpyHostToDevice, s));
+  CU_OK(cudaMemcpyAsync(f.ids, ids + p0, (size_t)R * 4, cudaMemcpyHostToDevice, s));
+  CU_OK(cudaStreamSynchronize(s));   // rs is a local: the copy must have read it before it goes
+  PartIn none{nullptr, 0, 0};
+  AttnShape ash{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd};
+  DeltaShape dsh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
+  CK(op_pf_embed(s, m->embd.fmt, m->embd.w, d, f.ids, R, f.x));
+  for (int il = 0; il < m->L; il++) {
+    const LayerW &l = m->layer[il];
+    CK(op_pf_norm(s, il ? f.x1 : f.x, il ? as_in(f.dn) : none, l.attn_norm, m->eps, d, f.x, f.kg_d, d, 0, nullptr, R));
+    if (l.full) {
+      CK(pf_site(m, {{&l.at.q, &f.q}, {&l.at.k, &f.k}, {&l.at.v, &f.v}}, f.kg_d, d, R));
+      CK(op_qkrope(s, as_in(f.q), as_in(f.k), as_in(f.v), l.at.qn, l.at.kn, m->invfreq, ash, f.qn, m->Kc[il], m->Vc[il], &f.rs[0], R));
+      for (int g = 0; g < ngrp; g++) {
+        PartIn qg{f.q.p + (size_t)g * gsz * 2 * qa, f.q.ns, f.q.stride};
+        CK(op_attention(s, f.qn + (size_t)g * gsz * qa, m->Kc[il], m->Vc[il], qg, ash, m->att_split, m->pm, m->pl, m->po, m->xp_qa, &f.rs[1 + g], gsz,
+                        f.kg_qa, g * gsz));
+      }
+      CK(pf_site(m, {{&l.at.o, &f.a}}, f.kg_qa, qa, R));
+    } else {
+      CK(pf_site(m, {{&l.dn.qkv, &f.qkv}, {&l.dn.z, &f.z}, {&l.dn.beta, &f.bp}, {&l.dn.alpha, &f.ap}}, f.kg_d, d, R));
+      CK(op_pf_delta(s, as_in(f.qkv), as_in(f.z), as_in(f.bp), as_in(f.ap), m->ring[il], m->ring_ks[il], l.dn.conv, l.dn.dt, l.dn.a, l.dn.norm, dsh,
+                     m->S[il], m->ctl, f.y, f.beta, f.decay, f.o, f.kg_v, p0, R));
+      CK(pf_site(m, {{&l.dn.out, &f.a}}, f.kg_v, m->vdc, R));
+    }
+    CK(op_pf_norm(s, f.x, as_in(f.a), l.ffn.post, m->eps, d, f.x1, f.kg_d, d, 0, nullptr, R));
+    CK(pf_site(m, {{&l.ffn.gate, &f.g}, {&l.ffn.up, &f.u}}, f.kg_d, d, R));
+    CK(op_pf_silu(s, as_in(f.g), as_in(f.u), m->f, f.kg_f, R));
+    CK(pf_site(m, {{&l.ffn.down, &f.dn}}, f.kg_f, m->f, R));
+  }
+  // the trunk's output-normed rows: row r of the chunk into pf.hn row r + 1 (row 0 holds the row before the chunk)
+  CK(op_pf_norm(s, f.x1, as_in(f.dn), m->out_norm, m->eps, d, nullptr, nullptr, 0, 0, f.hn + d, R));
+  if (m->has_mtp) {
+    // the drafter's row at position p pairs token p with the trunk's normed hidden of position p - 1
+    // (host/llb_host.c:1775-1808); a prompt chunk only needs its K and V rows (:1831-1876)
+    CK(op_pf_embed(s, m->embd.fmt, m->embd.w, d, f.ids, R, f.e));
+    CK(op_pf_norm(s, f.e, none, m->mt_enorm, m->eps, d, nullptr, f.kg_2d, 2 * d, 0, nullptr, R));
+    CK(op_pf_norm(s, f.hn, none, m->mt_hnorm, m->eps, d, nullptr, f.kg_2d, 2 * d, d, nullptr, R));
+    CK(pf_site(m, {{&m->mt_eh, &f.eh}}, f.kg_2d, 2 * d, R));
+    CK(op_pf_norm(s, nullptr, as_in(f.eh), m->mt_attn_norm, m->eps, d, nullptr, f.kg_d, d, 0, nullptr, R));
+    CK(pf_site(m, {{&m->mt_at.k, &f.k}, {&m->mt_at.v, &f.v}}, f.kg_d, d, R));
+    CK(op_qkrope(s, none, as_in(f.k), as_in(f.v), m->mt_at.qn, m->mt_at.kn, m->invfreq, ash, f.qn, m->mt_Kc, m->mt_Vc, &f.rs[0], R, true));
+  }
+  CU_OK(cudaMemcpyAsync(f.hn, f.hn + (size_t)R * d, (size_t)d * 4, cudaMemcpyDeviceToDevice, s));
+  m->pf_rows += R;
+  return 0;
+}
+
+// The fast part of a prompt: whole chunks from position 0 while more than `keep` rows remain for the T-row pass.
+// Returns the position the T-row pass continues from; the drafter's row there is left pending as a one-row catch-up
+// whose hidden (the normed row of the position before) is put where the catch-up reads it.
+static int pf_prefill(llb_spec *m, const int *ids, int n_rows, int keep, int *p_out) {
+  CK(pf_alloc(m));
+  PfState &f = m->pf;
+  CU_OK(cudaMemsetAsync(f.hn, 0, (size_t)m->d * 4, g_llb.stream));   // the hidden before position 0 is zero (host/llb_host.c:1816)
+  int p = 0;
+  while (n_rows - p > keep) {
+    const int R = n_rows - p - keep < PF_R ? n_rows - p - keep : PF_R;
+    CK(pf_chunk(m, ids, p, R));
+    p += R;
+  }
+  if (p > 0) {
+    CU_OK(cudaMemcpyAsync(m->hn, f.hn, (size_t)m->d * 4, cudaMemcpyDeviceToDevice, g_llb.stream));
+    struct { int n, pos0, tok[SPEC_MAXT], slot[SPEC_MAXT]; } c;
+    memset(&c, 0, sizeof c);
+    c.n = m->has_mtp ? 1 : 0; c.pos0 = p; c.tok[0] = ids[p];
+    CU_OK(cudaMemcpyAsync(&m->ctl->catchup, &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaStreamSynchronize(g_llb.stream));
+  }
+  *p_out = p;
+  return 0;
+}
+
 static int ctl_write(llb_spec *m, const SpecCtl &c) {
   CU_OK(cudaMemcpyAsync(m->ctl, &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
   CU_OK(cudaStreamSynchronize(g_llb.stream));
@@ -908,6 +1061,8 @@ LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
   for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
   CK(ctl_write(m, c));
   int p = 0;
+  // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_R rows through the dense path (dense FFN only)
+  if (m->prefill_mode == 1 && m->ne == 0 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, ids, n - 1, m->Tspec, &p));
   while (p < n - 1) {
     // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
     // over the rows of the last chunk, and that cycle's kernels cover k + 1 rows
@@ -1119,6 +1274,15 @@ LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which) { return (int)(wh
 
 LLB_API int llb_spec_position(const llb_spec *m) { return m->pos; }
 
+// mode 1: prompts go through the dense tcgen05 path in chunks of 128 rows (all but their last k + 1 rows); mode 0: every
+// row through the T-row pass.  Returns the previous mode.
+LLB_API int llb_spec_set_prefill(llb_spec *m, int mode) {
+  const int was = m->prefill_mode;
+  m->prefill_mode = mode == 1;
+  return was;
+}
+LLB_API double llb_spec_fast_rows(const llb_spec *m) { return m->pf_rows; }
+
 LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out /* cycles, rows, served, drafted[8], accepted[8] */) {
   out[0] = m->cycles; out[1] = m->rows; out[2] = m->served;
   for (int j = 0; j < 8; j++) { out[3 + j] = m->drafted[j]; out[11 + j] = m->accepted[j]; }
@@ -1127,7 +1291,8 @@ LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out /* cycles,
 
 // State read-back for parity checks: what = 0 committed DeltaNet state of layer il [TR][128][128],
 // 1 the K row and 2 the V row of position `pos` in layer il, 3 the conv ring row of position `pos`,
-// 4 the trunk's output-normed hidden row `pos` (0..k) of the last pass, 5 the drafter's K row.
+// 4 the trunk's output-normed hidden row `pos` (0..k) of the last pass, 5 the drafter's K row, 6 the output-normed
+// hidden of row `pos` of the last chunk the dense prompt path processed.
 LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n) {
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   const float *src = nullptr;
@@ -1161,6 +1326,7 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
     return (int)have;
   }
   else if (what == 4) { have = m->d; src = m->hn + (size_t)pos * m->d; }
+  else if (what == 6 && m->pf.ready && pos >= 0 && pos < PF_R) { have = m->d; src = m->pf.hn + (size_t)(pos + 1) * m->d; }   // dense path: normed hidden of row `pos` of its last chunk
   else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
   if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
   CU_OK(cudaMemcpy(out, src, have * 4, cudaMemcpyDeviceToHost));

@@ -23,6 +23,7 @@
 //   its tensor memory and returns.
 #pragma once
 #include "gemm.cuh"
+#include "tc5.cuh"
 static_assert(GEMM_MAXMAT == 4, "k_gemm3 finds a tile's matrix with three compares");
 
 #define G3_THREADS 512        // worker threads; four more warps issue the MMAs
@@ -37,77 +38,14 @@ static_assert(GEMM_MAXMAT == 4, "k_gemm3 finds a tile's matrix with three compar
 #define G3_D0 272
 #define G3_D_COLS 104
 #define G3_IDESC 0x08040010u   // kind::f16: D f32, A/B f16 K-major, N = 16, M = 128
-#define G3_WAIT_LIMIT (1u << 22)
 
 // bytes of shared memory for a K-slice of nsl super-blocks (NC = 8 activation columns)
 __host__ __device__ inline int g3_xp_bytes(int nsl) { return nsl * (32 * 8 * 16 + 2 * 8 * 16) + 256; }
 inline int g3_smem_bytes(int nsl) { return G3_HDR_BYTES + g3_xp_bytes(nsl) + G3_RED_BYTES + G3_STAGES * G3_STAGE_BYTES; }
 inline int g3_max_slice_sb() { return (G3_SMEM_MAX - G3_HDR_BYTES - 256 - G3_RED_BYTES - G3_STAGES * G3_STAGE_BYTES) / (32 * 8 * 16 + 2 * 8 * 16); }
 
-__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void t5_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void t5_commit(uint32_t bar_s) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_s) : "memory");
-}
-__device__ __forceinline__ void t5_st32(uint32_t taddr, const uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
-      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]),
-      "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
-      "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-      : "memory");
-}
-__device__ __forceinline__ void t5_st2(uint32_t taddr, uint32_t v0, uint32_t v1) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1,%2};" ::"r"(taddr), "r"(v0), "r"(v1) : "memory");
-}
-__device__ __forceinline__ void t5_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void t5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void t5_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-                 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr)
-               : "memory");
-#pragma unroll
-  for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void t5_ld2(uint32_t taddr, float (&v)[2]) {
-  uint32_t r0, r1;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr) : "memory");
-  v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar_s, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_s), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar_s) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_s) : "memory");
-}
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(G3_THREADS) : "memory"); }
 __device__ __forceinline__ void quarter_sync(int q) { asm volatile("bar.sync %0, 128;" ::"r"(2 + q) : "memory"); }
-// bounded wait for the phase with the given parity; false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(uint32_t bar_s, uint32_t parity) {
-  for (uint32_t it = 0; it < G3_WAIT_LIMIT; it++) {
-    uint32_t ok;
-    // the hint lets the hardware park the thread until the phase completes (or about a microsecond passes)
-    // instead of polling: sixteen worker warps and four issuing warps otherwise spend most issue slots on polls
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(ok) : "r"(bar_s), "r"(parity), "r"(1000u) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-// K-major, no swizzle: 8 rows x 16 bytes per core matrix; LBO = step between the two k-chunks of an
-// MMA, SBO = step between 8-row groups (bytes, both multiples of 16); descriptor version 1 (sm_100)
-__device__ __forceinline__ uint64_t g3_desc(uint32_t addr_s, uint32_t lbo, uint32_t sbo) {
-  return (uint64_t)((addr_s >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
-}
 
 __global__ void __launch_bounds__(G3_BLOCK, 1) k_gemm3(const GemmArgs a, const int cps, unsigned int *__restrict__ err) {
   extern __shared__ __align__(128) uint8_t smem[];

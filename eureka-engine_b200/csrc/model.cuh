@@ -51,15 +51,17 @@ struct PartIn {
 // (the slices are added in index order; four loads are in flight at a time so that a value split
 // seven ways costs two round trips to L2, not seven)
 // four consecutive values (i a multiple of 4, strides multiples of 4): all slices of a trip in flight at once
+// (loads of another kernel's output go to L2, ld.global.cg: under programmatic dependent launch a consumer kernel can be
+// resident on an SM long before its producer runs, and that SM's L1 may still hold the buffer's previous contents)
 __device__ __forceinline__ float4 part_get4(const PartIn &a, size_t i) {
-  float4 v = *(const float4 *)(a.p + i);
+  float4 v = __ldcg((const float4 *)(a.p + i));
   for (int k = 1; k < a.ns; k += 4) {
     const float *p = a.p + (size_t)k * a.stride + i;
     const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 l0 = *(const float4 *)p;
-    const float4 l1 = k + 1 < a.ns ? *(const float4 *)(p + a.stride) : z;
-    const float4 l2 = k + 2 < a.ns ? *(const float4 *)(p + 2 * a.stride) : z;
-    const float4 l3 = k + 3 < a.ns ? *(const float4 *)(p + 3 * a.stride) : z;
+    const float4 l0 = __ldcg((const float4 *)p);
+    const float4 l1 = k + 1 < a.ns ? __ldcg((const float4 *)(p + a.stride)) : z;
+    const float4 l2 = k + 2 < a.ns ? __ldcg((const float4 *)(p + 2 * a.stride)) : z;
+    const float4 l3 = k + 3 < a.ns ? __ldcg((const float4 *)(p + 3 * a.stride)) : z;
     v.x += l0.x; v.y += l0.y; v.z += l0.z; v.w += l0.w;
     v.x += l1.x; v.y += l1.y; v.z += l1.z; v.w += l1.w;
     v.x += l2.x; v.y += l2.y; v.z += l2.z; v.w += l2.w;
@@ -68,13 +70,13 @@ __device__ __forceinline__ float4 part_get4(const PartIn &a, size_t i) {
   return v;
 }
 __device__ __forceinline__ float part_get(const PartIn &a, size_t i) {
-  float v = a.p[i];
+  float v = __ldcg(a.p + i);
   for (int k = 1; k < a.ns; k += 4) {
     const float *p = a.p + (size_t)k * a.stride + i;
-    const float l0 = p[0];
-    const float l1 = k + 1 < a.ns ? p[a.stride] : 0.0f;
-    const float l2 = k + 2 < a.ns ? p[2 * a.stride] : 0.0f;
-    const float l3 = k + 3 < a.ns ? p[3 * a.stride] : 0.0f;
+    const float l0 = __ldcg(p);
+    const float l1 = k + 1 < a.ns ? __ldcg(p + a.stride) : 0.0f;
+    const float l2 = k + 2 < a.ns ? __ldcg(p + 2 * a.stride) : 0.0f;
+    const float l3 = k + 3 < a.ns ? __ldcg(p + 3 * a.stride) : 0.0f;
     v += l0; v += l1; v += l2; v += l3;
   }
   return v;
@@ -93,10 +95,12 @@ int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowS
 int op_silu_scaled_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax, const float *scale, int seg);
 // router logits (ne rows + the shared gate row of Wr, F32) on the normed rows h[T][d], then ids / wt [T][nk + 1]
 int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne, int nk, float *lg, int *ids, float *wt, const RowSet *rs, int Tmax);
+// kv_only: only the K and V rows (the drafter's cache fill of the prompt path: no query rows)
 int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
-              AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax);
+              AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax, bool kv_only = false);
+// kg != null: the gated rows go out as fp16 rows kg_row0 .. of a k-group-major chunk buffer (pf.cu) instead of the planes
 int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
-                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax);
+                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg = nullptr, int kg_row0 = 0);
 int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax);
 int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,

@@ -299,12 +299,12 @@ __device__ __forceinline__ void kv_put(__half *c, long long plane, size_t i, flo
 }
 __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__ qn_w, const float *__restrict__ kn_w,
                          const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, __half *__restrict__ Kc,
-                         __half *__restrict__ Vc, const RowSet *rs) {
+                         __half *__restrict__ Vc, const RowSet *rs, int blk0) {
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   extern __shared__ float hv[];
   __shared__ float red[32];
-  const int t = blockIdx.y, b = blockIdx.x, i = threadIdx.x, hd = sh.hd;
+  const int t = blockIdx.y, b = blockIdx.x + blk0, i = threadIdx.x, hd = sh.hd;
   if (t >= rs_n) return;
   const int pos = rs_p0 + t, kvd = sh.KV * hd;
   if (b >= sh.H + sh.KV) {  // V row: copied
@@ -344,9 +344,11 @@ __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__
   else kv_put(Kc, sh.kv_plane, kdst + i, out);
 }
 int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
-              AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax) {
-  CU_OK(llb_launch(k_qkrope, dim3(sh.H + 2 * sh.KV, Tmax), dim3(sh.hd), (size_t)((size_t)sh.hd * 4), s, q, k, v, qn_w, kn_w, invfreq, sh, qout,
-                   (__half *)Kc, (__half *)Vc, rs));
+              AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax, bool kv_only) {
+  // blocks 0 .. H-1 are the query heads, then KV key heads, then KV value heads
+  const int blk0 = kv_only ? sh.H : 0;
+  CU_OK(llb_launch(k_qkrope, dim3(sh.H + 2 * sh.KV - blk0, Tmax), dim3(sh.hd), (size_t)((size_t)sh.hd * 4), s, q, k, v, qn_w, kn_w, invfreq, sh, qout,
+                   (__half *)Kc, (__half *)Vc, rs, blk0));
   CU_OK(cudaGetLastError());
   return 0;
 }

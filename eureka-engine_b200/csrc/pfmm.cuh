@@ -1,70 +1,38 @@
 // pfmm.cuh -- the prompt path's dense GEMM on the fifth-generation tensor cores: Y[r][n] = sum_k W[n][k] X[r][k] for a
-// chunk of up to 256 prompt rows against Q4_K / Q5_K / Q6_K / Q8_0 weights.  It replaces, for this library, the
+// chunk of up to PF_R = 128 prompt rows against Q4_K / Q5_K / Q6_K / Q8_0 weights.  It replaces, for this library, the
 // reference's chunked tensor-core prefill GEMM (tools/pf27/pfmm.cuh:311-384: int8 mma.sync + cp.async on sm_86; its
 // caller host/llb_pf.h:551 pf_take) with a design for sm_100a:
 //
-//   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 256 prompt rows, K = 16 per instruction) issued
-//     by ONE thread, both operands in shared memory, the fp32 accumulator in TENSOR MEMORY (two accumulators of 256
-//     columns: the epilogue of one tile runs while the next tile multiplies);
-//   * the activation operand arrives by TMA: the chunk's activations are kept in global memory in the order the
-//     operand wants (k-group major, see PF_KG below), so a 64-column stage of all 256 rows is ONE contiguous 32 KB
-//     cp.async.bulk that completes on an mbarrier (plain bulk copy of this GPU's own memory, no multicast);
-//   * the weight operand is dequantised on the fly: eight warps read the packed super-blocks (each thread one row's 32
-//     weights of a stage), turn the integer codes into fp16 exactly (0x6400 | code is 1024 + code), apply the sub-block
-//     scale and min in one fp16 FMA and store 16-byte core-matrix rows; stores of a warp are conflict-free;
-//   * a four-stage ring of (16 KB weights, 32 KB activations) with full / empty mbarriers decouples the three roles;
-//     four more warps read finished accumulators with tcgen05.ld and write Y as f32, coalesced along the weight rows;
+//   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 128 prompt rows, K = 16 per instruction) issued
+//     by ONE thread, both operands in shared memory, fp32 accumulators in TENSOR MEMORY;
+//   * BOTH operands are two fp16 planes, hi = fp16(v) and lo = fp16((v - hi) * 2048) (about 22 bits of v, as the T-row
+//     path's activation planes): a 16-column step is three MMAs, hi.hi into one accumulator, hi.lo + lo.hi into a second
+//     one that the epilogue adds divided by 2048 (lo.lo is below fp32 resolution).  With one fp16 plane per operand every
+//     GEMM output carried a relative error of 4e-4, which a random 8-layer model amplified past the path's 2e-2 bar;
+//   * the activation planes arrive by TMA: the chunk's activations are kept in global memory in the order the operand
+//     wants (k-group major, common.cuh), so a 64-column stage of one plane is ONE contiguous 16 KB cp.async.bulk that
+//     completes on an mbarrier (plain bulk copies of this GPU's own memory, no multicast);
+//   * the weight planes are made on the fly: eight warps read the packed super-blocks (each thread one row's 32 weights
+//     of a stage), dequantise in fp32 with the reference's own operation order (tools/qwen35_engine.c:233-307), split
+//     each weight into its two planes and store 16-byte core-matrix rows; stores of a warp are conflict-free;
+//   * a three-stage ring of (32 KB weights, 32 KB activations) with full / empty mbarriers decouples the roles; two sets
+//     of accumulators let four more warps read a finished tile with tcgen05.ld while the next one multiplies;
 //   * every wait is bounded: a wait that runs out sets *err, and all roles then run through without waiting, so the
 //     kernel returns, frees its tensor memory and leaves the context usable (llb_b200_wait_errors() reports it).
-//
-// Numerics: weights and activations are rounded to fp16 (11 bits) before the multiply, sums are fp32.  That is the
-// prompt path's trade (the reference's fast prefill rounds to int8); the T-row verify path keeps about 22 bits.
 #pragma once
-#include "gemm3.cuh"
+#include "gemm.cuh"
+#include "tc5.cuh"
+#include "pf.cuh"
 
-#define PF_R 256              // rows of a prompt chunk = N of the MMA
 #define PF_KS 64              // columns per ring stage
-#define PF_STAGES 4
-#define PF_A_BYTES (128 * PF_KS * 2)
-#define PF_B_BYTES (PF_R * PF_KS * 2)
-#define PF_STAGE_BYTES (PF_A_BYTES + PF_B_BYTES)
+#define PF_STAGES 3
+#define PF_A_BYTES (128 * PF_KS * 2)     // one plane of 128 weight rows
+#define PF_B_BYTES (PF_R * PF_KS * 2)    // one plane of the chunk's rows
+#define PF_STAGE_BYTES (2 * PF_A_BYTES + 2 * PF_B_BYTES)   // [A hi | A lo | B hi | B lo]
 #define PF_SMEM (1024 + PF_STAGES * PF_STAGE_BYTES)
 #define PF_THREADS 512        // warps 0-7 dequantise, 8 loads activations, 9 issues MMAs, 12-15 write results
-#define PF_IDESC 0x08400010u  // kind::f16: D f32, A / B f16 K-major, N = 256, M = 128
-#define PF_MAXMAT 4
+#define PF_IDESC 0x08200010u  // kind::f16: D f32, A / B f16 K-major, N = 128, M = 128
 
-// Activations of a chunk for the dense GEMM, "k-group major": element (row r, column k) of a [PF_R][K] matrix sits at
-// half index ((k >> 3) * PF_R + r) * 8 + pf_perm(k & 7): eight consecutive columns of one row are one 16-byte
-// core-matrix row, the 256 rows of a k-group are contiguous (4 KB), and a 64-column stage is one 32 KB run.  Inside the
-// eight the stored order is 0 2 1 3 4 6 5 7, the order in which the weight unpack produces its codes (both operands
-// use it, so the contraction is unchanged).
-__host__ __device__ inline size_t pf_kg_halves(int K) { return (size_t)K * PF_R; }
-__device__ __forceinline__ size_t pf_kg_index4(int r, int k) { return ((size_t)(k >> 3) * PF_R + r) * 8 + (k & 4); }   // k a multiple of 4
-// four consecutive columns k .. k+3 of row r (stored 0 2 1 3)
-__device__ __forceinline__ void pf_kg_store4(__half *x, int r, int k, float v0, float v1, float v2, float v3) {
-  const __half2 a = __floats2half2_rn(v0, v2), b = __floats2half2_rn(v1, v3);
-  *(uint2 *)(x + pf_kg_index4(r, k)) = make_uint2(*(const uint32_t *)&a, *(const uint32_t *)&b);
-}
-
-struct PfMat {
-  const uint8_t *W;     // device layout, row stride dev_row_bytes(fmt, K)
-  float *out;           // [ksplit][PF rows][ostride]
-  int rows, ostride;
-  long long split_stride;
-};
-struct PfArgs {
-  PfMat m[PF_MAXMAT];
-  int nmat;
-  int t128[PF_MAXMAT + 1];   // prefix sums of 128-row tiles
-  int K, ksplit, R;          // columns, K-slices, rows of the chunk in use (<= PF_R)
-  const __half *x;           // activations, k-group major
-  unsigned int *err;
-};
-
-// half2 helpers on raw words
-__device__ __forceinline__ uint32_t pf_hsub2(uint32_t a, uint32_t b) { uint32_t d; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
-__device__ __forceinline__ uint32_t pf_hmul2(uint32_t a, uint32_t b) { uint32_t d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
-__device__ __forceinline__ uint32_t pf_h2(float v) { const __half2 h = __float2half2_rn(v); return *(const uint32_t *)&h; }
 
 __device__ __forceinline__ void pf_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -72,8 +40,280 @@ __device__ __forceinline__ void pf_mma_ss(uint32_t d_tmem, uint64_t adesc, uint6
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void pf_bulk_load(uint32_t dst_s, const void *src, uint32_t bytes, uint32_t bar_s) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_s), "r"(bytes) : "memory");
+__device__ __forceinline__ void pf_bulk_copy(uint32_t dst_s, const void *src, uint32_t bytes, uint32_t bar_s) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_s), "l"(src), "r"(bytes), "r"(bar_s)
                : "memory");
+}
+
+// ---- weights: packed super-blocks -> fp16 core-matrix rows ------------------------------------------
+// A thread takes the 32 weights of one row that start at column c0 (a multiple of 32): raw words with pf_load, fp32
+// values with pf_deq, then pf_split8 turns every eight of them into a 16-byte row of each plane (k-groups c0/8 .. + 3).
+struct PfRaw { uint32_t w[8], x[8], h[4]; };
+
+template <int FMT> __device__ __forceinline__ void pf_load(const uint8_t *row, int K, int c0, PfRaw &r) {
+  if constexpr (FMT == LLB_FM_Q8_0) {
+    const uint4 a = ldg128(row + c0), b = ldg128(row + c0 + 16);
+    r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+    r.h[0] = *(const unsigned short *)(row + K + 2 * (c0 >> 5));
+  } else if constexpr (FMT == LLB_FM_Q6_K) {
+    const uint8_t *blk = row + (size_t)(c0 >> 8) * 224;
+    const int j8 = (c0 >> 5) & 7, hf = j8 >> 2, qd = j8 & 3;
+    const uint4 a = ldg128(blk + 64 * hf + 32 * (qd & 1)), b = ldg128(blk + 64 * hf + 32 * (qd & 1) + 16);
+    const uint4 c = ldg128(blk + 128 + 32 * hf), d = ldg128(blk + 128 + 32 * hf + 16);
+    r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+    r.x[0] = c.x; r.x[1] = c.y; r.x[2] = c.z; r.x[3] = c.w; r.x[4] = d.x; r.x[5] = d.y; r.x[6] = d.z; r.x[7] = d.w;
+    r.h[0] = *(const unsigned short *)(blk + 192 + 8 * hf + 2 * qd);   // the two int8 scales of this quarter
+    r.h[1] = *(const unsigned short *)(blk + 208);
+  } else {
+    constexpr int SB = FMT == LLB_FM_Q4_K ? 144 : 176, QOFF = FMT == LLB_FM_Q4_K ? 16 : 48;
+    const uint8_t *blk = row + (size_t)(c0 >> 8) * SB;
+    const int g = (c0 >> 6) & 3;
+    const uint4 hd = ldg128(blk), a = ldg128(blk + QOFF + 32 * g), b = ldg128(blk + QOFF + 32 * g + 16);
+    r.h[0] = hd.x; r.h[1] = hd.y; r.h[2] = hd.z; r.h[3] = hd.w;
+    r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+    if constexpr (FMT == LLB_FM_Q5_K) {
+      const uint4 c = ldg128(blk + 16), d = ldg128(blk + 32);
+      r.x[0] = c.x; r.x[1] = c.y; r.x[2] = c.z; r.x[3] = c.w; r.x[4] = d.x; r.x[5] = d.y; r.x[6] = d.z; r.x[7] = d.w;
+    }
+  }
+}
+
+// byte b (0..255) as a float without the conversion pipe: 0x4B0000bb is 2^23 + b exactly
+__device__ __forceinline__ float pf_b2f(uint32_t b) { return __uint_as_float(0x4B000000u | b) - 8388608.0f; }
+
+// the 32 weights as fp32, dequantised with the reference's operation order (one rounding per operation, no FMA)
+template <int FMT> __device__ __forceinline__ void pf_deq(const PfRaw &r, int c0, float (&w)[32]) {
+  if constexpr (FMT == LLB_FM_Q8_0) {
+    const float d = h2f_bits(r.h[0]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t x = r.w[i] ^ 0x80808080u;   // q + 128 as an unsigned byte
+#pragma unroll
+      for (int j = 0; j < 4; j++) w[4 * i + j] = __fmul_rn(pf_b2f((x >> (8 * j)) & 0xffu) - 128.0f, d);
+    }
+  } else if constexpr (FMT == LLB_FM_Q6_K) {
+    const int qd = (c0 >> 5) & 3;
+    const float d = h2f_bits(r.h[1]);
+    const float s0 = __fmul_rn(d, (float)(int8_t)(r.h[0] & 0xff)), s1 = __fmul_rn(d, (float)(int8_t)(r.h[0] >> 8));
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t x = qd < 2 ? r.w[i] : r.w[i] >> 4, hb = r.x[i] >> (2 * qd);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const uint32_t code = ((x >> (8 * j)) & 15u) | (((hb >> (8 * j)) & 3u) << 4);
+        w[4 * i + j] = __fmul_rn(i < 4 ? s0 : s1, pf_b2f(code) - 32.0f);
+      }
+    }
+  } else {
+    const int j8 = (c0 >> 5) & 7, hi = j8 & 1;
+    uint32_t scA, scB, mnA, mnB;
+    k4_scales(r.h[1], r.h[2], r.h[3], scA, scB, mnA, mnB);
+    const float sc = (float)(((j8 < 4 ? scA : scB) >> (8 * (j8 & 3))) & 0xffu), mn = (float)(((j8 < 4 ? mnA : mnB) >> (8 * (j8 & 3))) & 0xffu);
+    const float ds = __fmul_rn(h2f_bits(r.h[0] & 0xffffu), sc), dm = __fmul_rn(h2f_bits(r.h[0] >> 16), mn);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t x = hi ? r.w[i] >> 4 : r.w[i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint32_t q = (x >> (8 * j)) & 15u;
+        if constexpr (FMT == LLB_FM_Q5_K) q |= ((r.x[i] >> (8 * j + j8)) & 1u) << 4;   // the fifth bit of column l is bit j8 of qh byte l
+        w[4 * i + j] = __fsub_rn(__fmul_rn(ds, pf_b2f(q)), dm);
+      }
+    }
+  }
+}
+// eight weights -> one 16-byte row of the hi plane and one of the lo plane.  hi is the weight with its low 13 mantissa
+// bits cleared (exactly an fp16 number for normal magnitudes), lo the exact remainder times 2048.
+__device__ __forceinline__ void pf_split8(const float *w, uint4 &hi, uint4 &lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const float a = w[2 * i], b = w[2 * i + 1];
+    const float ah = __uint_as_float(__float_as_uint(a) & 0xffffe000u), bh = __uint_as_float(__float_as_uint(b) & 0xffffe000u);
+    const __half2 hh = __floats2half2_rn(ah, bh), ll = __floats2half2_rn((a - ah) * XP_LO_SCALE, (b - bh) * XP_LO_SCALE);
+    h[i] = *(const uint32_t *)&hh; l[i] = *(const uint32_t *)&ll;
+  }
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------------------
+// Work unit = (128-row tile, K-slice); CTA b takes units b, b + grid, ...  Every role walks the same unit sequence.
+__device__ __forceinline__ void pf_locate(const PfArgs &a, int tile, int &m, int &row0) {
+  m = 0;
+  while (m + 1 < a.nmat && tile >= a.t128[m + 1]) m++;
+  row0 = (tile - a.t128[m]) * 128;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // header: full_a[4] +0, full_b[4] +32, empty[4] +64, acc_full[2] +96, acc_empty[2] +112, tensor-memory address +128, dead +132
+  const uint32_t bar_s = smem_u32(smem);
+  auto full_a = [&](int s) { return bar_s + 8u * (uint32_t)s; };
+  auto full_b = [&](int s) { return bar_s + 32u + 8u * (uint32_t)s; };
+  auto empty = [&](int s) { return bar_s + 64u + 8u * (uint32_t)s; };
+  auto acc_full = [&](int b) { return bar_s + 96u + 8u * (uint32_t)b; };
+  auto acc_empty = [&](int b) { return bar_s + 112u + 8u * (uint32_t)b; };
+  uint32_t *tmem_slot = (uint32_t *)(smem + 128);
+  volatile uint32_t *dead = (volatile uint32_t *)(smem + 132);
+  uint8_t *ring = smem + 1024;
+  const uint32_t ring_s = smem_u32(ring);
+  const int ntiles = a.t128[a.nmat], nunits = ntiles * a.ksplit, kslice = a.K / a.ksplit, nst = kslice / PF_KS;
+  const size_t rb = dev_row_bytes(FMT, a.K);
+
+  pdl_trigger();
+  if (tid == 0) {
+    for (int s = 0; s < PF_STAGES; s++) { mbar_init(full_a(s), 8); mbar_init(full_b(s), 1); mbar_init(empty(s), 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    *dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 10) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_wait();              // the activations come from the kernel in front
+  t5_fence_before();
+  __syncthreads();
+  t5_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // a bounded wait that gives up for the whole CTA
+  auto wait = [&](uint32_t bar, uint32_t parity) {
+    if (*dead) return;
+    if (!mbar_wait(bar, parity)) { *dead = 1; if (a.err) atomicExch(a.err, 1u); }
+  };
+
+  if (warp < 8) {
+    // ---- weights: thread = (row r of the tile, half h of the stage's 64 columns) ----
+    const int r = tid & 127, h = tid >> 7;
+    PfRaw raw0, raw1;                                  // two stages of raw words in flight (never indexed: they stay in registers)
+    int it = 0;                                        // stages produced so far by this CTA
+    // the loads run two stages ahead of the conversion: cursor (lu, ls) is the stage to load next
+    int lu = blockIdx.x, ls = 0, lm = 0, lrow0 = 0;
+    const uint8_t *lrow = nullptr;
+    auto lplan = [&]() {
+      if (lu < nunits) { pf_locate(a, lu % ntiles, lm, lrow0); lrow = a.m[lm].W + (size_t)min(lrow0 + r, a.m[lm].rows - 1) * rb; }
+    };
+    auto lnext = [&](PfRaw &dst) {
+      if (lu < nunits) {
+        pf_load<FMT>(lrow, a.K, (lu / ntiles) * kslice + ls * PF_KS + 32 * h, dst);
+        if (++ls == nst) { ls = 0; lu += gridDim.x; lplan(); }
+      }
+    };
+    // converts the stage held in rw (columns c0 ..), refills rw with the stage two ahead, publishes the stage
+    auto one = [&](PfRaw &rw, int c0) {
+      const int slot = it % PF_STAGES;
+      float w[32];
+      pf_deq<FMT>(rw, c0, w);
+      lnext(rw);
+      if (it >= PF_STAGES) wait(empty(slot), (uint32_t)((it / PF_STAGES) + 1) & 1u);
+      uint8_t *A = ring + (size_t)slot * PF_STAGE_BYTES;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint4 hi, lo;
+        pf_split8(w + 8 * j, hi, lo);
+        *(uint4 *)(A + ((size_t)(4 * h + j) * 128 + r) * 16) = hi;
+        *(uint4 *)(A + PF_A_BYTES + ((size_t)(4 * h + j) * 128 + r) * 16) = lo;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these bytes through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_a(slot));
+      it++;
+    };
+    lplan();
+    lnext(raw0);
+    lnext(raw1);
+    for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+      const int kbase = (u / ntiles) * kslice + 32 * h;
+      for (int s = 0; s < nst; s += 2) {               // nst is a multiple of four: a K-slice is whole super-blocks
+        one(raw0, kbase + s * PF_KS);
+        one(raw1, kbase + (s + 1) * PF_KS);
+      }
+    }
+  } else if (warp == 8) {
+    // ---- activations: one 16 KB bulk copy per plane and stage ----
+    if (lane == 0) {
+      int it = 0;
+      for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+        const int kbase = (u / ntiles) * kslice;
+        for (int s = 0; s < nst; s++, it++) {
+          const int slot = it % PF_STAGES;
+          if (it >= PF_STAGES) wait(empty(slot), (uint32_t)((it / PF_STAGES) + 1) & 1u);
+          if (*dead) continue;
+          const __half *src = a.x + (size_t)((kbase + s * PF_KS) >> 3) * PF_R * 8;
+          const uint32_t dst = ring_s + slot * PF_STAGE_BYTES + 2 * PF_A_BYTES;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_b(slot)), "r"((uint32_t)(2 * PF_B_BYTES)) : "memory");
+          pf_bulk_copy(dst, src, PF_B_BYTES, full_b(slot));
+          pf_bulk_copy(dst + PF_B_BYTES, src + (size_t)a.K * PF_R, PF_B_BYTES, full_b(slot));
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---- the tensor core: per stage four steps of K = 16, three MMAs each ----
+    if (lane == 0) {
+      int it = 0, i = 0;
+      for (int u = blockIdx.x; u < nunits; u += gridDim.x, i++) {
+        const int buf = i & 1;
+        if (i >= 2) wait(acc_empty(buf), (uint32_t)((i >> 1) + 1) & 1u);
+        t5_fence_after();
+        const uint32_t d1 = tmem_base + (uint32_t)(buf * 2 * PF_R), d2 = d1 + PF_R;   // hi.hi ; hi.lo + lo.hi
+        for (int s = 0; s < nst; s++, it++) {
+          const int slot = it % PF_STAGES;
+          wait(full_a(slot), (uint32_t)(it / PF_STAGES) & 1u);
+          wait(full_b(slot), (uint32_t)(it / PF_STAGES) & 1u);
+          t5_fence_after();
+          const uint32_t A_s = ring_s + slot * PF_STAGE_BYTES, B_s = A_s + 2 * PF_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < PF_KS / 16; k++) {
+            const uint64_t ah = g3_desc(A_s + k * 2 * 2048, 2048, 128), al = g3_desc(A_s + PF_A_BYTES + k * 2 * 2048, 2048, 128);
+            const uint64_t bh = g3_desc(B_s + k * 2 * (PF_R * 16), PF_R * 16, 128), bl = g3_desc(B_s + PF_B_BYTES + k * 2 * (PF_R * 16), PF_R * 16, 128);
+            pf_mma_ss(d1, ah, bh, PF_IDESC, (s | k) != 0);
+            pf_mma_ss(d2, ah, bl, PF_IDESC, (s | k) != 0);
+            pf_mma_ss(d2, al, bh, PF_IDESC, 1);
+          }
+          t5_commit(empty(slot));        // arrives when these MMAs have read the stage
+        }
+        t5_commit(acc_full(buf));        // ... and when the whole tile is in tensor memory
+      }
+      // nothing of this CTA may still run on the tensor core when its tensor memory is freed
+      if (i > 0) wait(acc_full((i - 1) & 1), (uint32_t)((i - 1) >> 1) & 1u);
+    }
+  } else if (warp >= 12) {
+    // ---- results: lane quarter q of the accumulator, one weight row per thread ----
+    const int q = warp - 12;
+    int i = 0;
+    for (int u = blockIdx.x; u < nunits; u += gridDim.x, i++) {
+      const int buf = i & 1;
+      int m, row0;
+      pf_locate(a, u % ntiles, m, row0);
+      const PfMat &M = a.m[m];
+      const int row = row0 + 32 * q + lane;
+      float *out = M.out + (size_t)(u / ntiles) * M.split_stride + row;
+      wait(acc_full(buf), (uint32_t)(i >> 1) & 1u);
+      t5_fence_after();
+      const uint32_t t0 = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * 2 * PF_R);
+      for (int c = 0; c < a.R; c += 16) {
+        float v[16], vl[16];
+        t5_ld16(t0 + c, v);
+        t5_ld16(t0 + PF_R + c, vl);
+        t5_wait_ld();
+        if (row < M.rows) {
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            if (c + j < a.R) out[(size_t)(c + j) * M.ostride] = v[j] + vl[j] * XP_LO_INV;
+        }
+      }
+      t5_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
+    }
+  }
+  t5_fence_before();
+  __syncthreads();
+  if (warp == 10) {
+    t5_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
 }

@@ -68,6 +68,8 @@ def lib() -> C.CDLL:
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
             "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
             "llb_spec_check_index": (i32, [C.c_char_p, sz]),
+            "llb_spec_set_prefill": (i32, [vp, i32]), "llb_spec_fast_rows": (C.c_double, [vp]),
+            "llb_b200_pf_gemm": (i32, [i32, u64, i32, i32, u64, i32, u64, i32]),
             "llb_b200_gemm_ksplit": (i32, [i32, i32, i32, i32, i32]), "llb_b200_ring_ksplit": (i32, [i32, i32, i32, i32, i32, i32]),
             "llb_b200_kernel_by_name": (vp, [C.c_char_p]),
             "llb_b200_launch": (i32, [vp, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.POINTER(vp), C.c_uint]),
@@ -199,6 +201,13 @@ class SpecEngine:
         check(self.L.llb_spec_stats(self.h, out.ctypes.data), "llb_spec_stats")
         return {"cycles": int(out[0]), "rows": int(out[1]), "served": int(out[2]),
                 "drafted": [int(v) for v in out[3:11]], "accepted": [int(v) for v in out[11:19]]}
+
+    def set_prefill(self, fast: bool) -> int:
+        """True: prompts go through the dense tcgen05 path in chunks of 128 rows; returns the previous mode."""
+        return self.L.llb_spec_set_prefill(self.h, 1 if fast else 0)
+
+    def fast_rows(self) -> float:
+        return self.L.llb_spec_fast_rows(self.h)
 
     def position(self) -> int:
         return self.L.llb_spec_position(self.h)

@@ -114,6 +114,12 @@ LLB_API int llb_b200_wait_errors(void);
 LLB_API int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
                        llb_b200_dptr x_dev, llb_b200_dptr y_dev);
 
+/* The prompt path's dense GEMM alone (replaces the reference's chunked tensor-core prefill GEMM, tools/pf27/pfmm.cuh:311-384):
+ * Y[r][n] = sum_c W[n][c] x[r][c] for R <= 128 rows of f32 activations x [R][K] against a weight matrix in the device
+ * layout, out f32 [R][rows]; tcgen05.mma with both operands as two fp16 planes (about 22 bits) and fp32 sums in tensor memory.  ksplit = 0
+ * picks the K-split (it must divide K / 256).  Synchronises; scratch is allocated and freed inside the call. */
+LLB_API int llb_b200_pf_gemm(int fmt, llb_b200_dptr w, int rows, int K, llb_b200_dptr x_f32, int R, llb_b200_dptr out_f32, int ksplit);
+
 /* Y[t][r] = sum_c W[r][c] x[t][c] for callers that are not allowed to allocate.  No counterpart in the
  * reference.  Meant for hosts that fix a library's memory at start-up and forbid driver allocations
  * afterwards (a serving process that cannot afford cudaMalloc's device-wide synchronisation, a plugin
@@ -156,6 +162,15 @@ LLB_API int llb_spec_generate(llb_spec *m, int steps, int *ids, uint32_t *top2);
 /* the reference's per-token operator (spec_pass, host/llb_host.c:1902-1950): y = [v1, id1, v2, id2] */
 LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y);
 LLB_API int llb_spec_position(const llb_spec *m);
+/* How llb_spec_prefill feeds a prompt.  mode 0 (default): every row through the T-row verify pass, eight rows a pass, at
+ * the verify path's precision.  mode 1 (also LLB_PREFILL=fast in the environment at open, the reference's switch,
+ * host/llb_host.c:206): all but the last k + 1 rows in chunks of 128 rows through dense tcgen05 GEMMs (operands as two fp16 planes)
+ * (replaces pf_take / spec_pf / spec_take, host/llb_pf.h:551, host/llb_host.c:1831-1899): trunk K/V, conv history and
+ * DeltaNet state, and the drafter's K/V rows, are left as the T-row pass would have left them, within the path's
+ * tolerance.  Models with routed experts always take mode 0.  Returns the previous mode.
+ * llb_spec_fast_rows: prompt rows that went through the dense path since the engine was opened. */
+LLB_API int llb_spec_set_prefill(llb_spec *m, int mode);
+LLB_API double llb_spec_fast_rows(const llb_spec *m);
 /* n cycles enqueued back to back, no host round trip between them; returns the tokens emitted */
 LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap);
 /* measurement helpers: device time (CUDA events on the library's stream) of the verify pass alone and

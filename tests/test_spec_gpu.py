@@ -233,3 +233,39 @@ def test_prompt_chunk_width_does_not_change_the_result(pkg, packs, oracle, llb, 
         assert _compare_ids(ids, ref_ids, ref_top2) == 20
         assert st == runs[0][1]
         assert np.allclose(state, runs[0][2], rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("order", ["sorted", "shuffled"])
+def test_draft_vocabulary_slice(pkg, packs, oracle, llb, order):
+    """The drafter's head is a slice of the vocabulary (tools/mtp27/mtp_pack.py:14-30 keeps 40960 of 151936 rows): its
+    argmax is an index into the slice and goes back to a token id through the ids table (host/llb_host.c:1800-1807).
+    Half of a 1024-entry vocabulary, in ascending and in shuffled order: emitted ids are still the plain greedy ids, and
+    cycles and acceptance counts equal the oracle's loop with the same slice -- a drafter that read the slice index as
+    a token id would accept almost nothing."""
+    cfg = packs.cfg_tiny(n_layers=8, seed=5)
+    pack = packs.build_pack(cfg)
+    rng = np.random.default_rng(17)
+    ids_tab = rng.permutation(cfg.vocab_size)[:512]
+    if order == "sorted":
+        ids_tab = np.sort(ids_tab)
+    assert not np.array_equal(ids_tab, np.arange(512))
+    mtp = packs.aux1_bytes(packs.build_mtp(pack, draft_ids=ids_tab))
+    prompt = packs.synth_prompt(2, 17, cfg.vocab_size)
+    steps = 48
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=len(prompt) + steps + 16)
+    ref_ids, ref_top2 = orc.greedy(prompt, steps)
+    orc.mtp_load(mtp)
+    sids, _, st = orc.spec_greedy(prompt, steps, 3)
+    assert np.array_equal(sids, ref_ids)
+    eng = pkg.llb.SpecEngine(pack, mtp, k=3, max_ctx=len(prompt) + steps + 16)
+    try:
+        eng.prefill(prompt)
+        ids, _ = eng.generate(steps)
+        stats = eng.stats()
+    finally:
+        eng.close()
+        orc.close()
+    assert _compare_ids(ids, ref_ids, ref_top2) == steps
+    assert stats["cycles"] == st.cycles
+    assert stats["accepted"][1:4] == [int(v) for v in list(st.accepted)[1:4]]
+    assert stats["accepted"][1] > 0            # tokens inside the slice do get drafted and accepted
