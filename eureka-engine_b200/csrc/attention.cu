@@ -48,6 +48,12 @@ template <int HD, int NQG>
 __global__ void __launch_bounds__(256) k_attn_mma(const float *__restrict__ q, const __half *__restrict__ Kc, const __half *__restrict__ Vc,
                                                   AttnShape sh, int Tmax, float *__restrict__ pm, float *__restrict__ pl,
                                                   float *__restrict__ po, const RowSet *rs) {
+  // blockIdx.z: one of several row groups of a prompt chunk, each with its own row set, Tmax query rows and partial results
+  {
+    const size_t z = blockIdx.z, per = (size_t)sh.H * Tmax * gridDim.y;
+    rs = (const RowSet *)((uintptr_t)rs + z * sizeof(RowSet));
+    q += z * Tmax * sh.H * HD; pm += z * per; pl += z * per; po += z * per * HD;
+  }
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   extern __shared__ __align__(128) uint8_t sm[];
@@ -225,6 +231,13 @@ __global__ void __launch_bounds__(256) k_attn_mma(const float *__restrict__ q, c
 // block = (head, row); thread (sg, i4): split group sg, dims 4*i4 .. 4*i4+3
 __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po, PartIn qg,
                                                    AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs, __half *__restrict__ kg, int kg_row0) {
+  {
+    const size_t z = blockIdx.z, per = (size_t)sh.H * Tmax * nsplit;
+    rs = (const RowSet *)((uintptr_t)rs + z * sizeof(RowSet));
+    pm += z * per; pl += z * per; po += z * per * sh.hd;
+    qg.p += z * Tmax * 2 * sh.H * sh.hd;
+    kg_row0 += (int)z * Tmax;
+  }
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float wsm[128];
@@ -302,16 +315,16 @@ template <int HD> static int att_hd(cudaStream_t s, int nqg, dim3 grid, const fl
 }
 
 int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
-                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg, int kg_row0) {
+                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg, int kg_row0, int nz) {
   const int G = sh.H / sh.KV, NQ = G * Tmax, nqg = (NQ + 7) / 8;
-  dim3 grid(sh.KV, nsplit);
+  dim3 grid(sh.KV, nsplit, nz);
   int rc;
   if (sh.hd == 128) rc = att_hd<128>(s, nqg, grid, q, (const __half *)Kc, (const __half *)Vc, sh, Tmax, pm, pl, po, rs);
   else if (sh.hd == 256) rc = att_hd<256>(s, nqg, grid, q, (const __half *)Kc, (const __half *)Vc, sh, Tmax, pm, pl, po, rs);
   else return llb_fail("attention: head_dim %d", sh.hd);
   if (rc) return rc;
   CU_OK(cudaGetLastError());
-  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax), dim3(256), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs, kg, kg_row0));
+  CU_OK(llb_launch(k_attn_comb, dim3(sh.H, Tmax, nz), dim3(256), (size_t)(0), s, pm, pl, po, qg, sh, nsplit, Tmax, xp, rs, kg, kg_row0));
   CU_OK(cudaGetLastError());
   return 0;
 }

@@ -44,6 +44,7 @@ struct PfState {
   float *x = nullptr, *x1 = nullptr, *hn = nullptr, *e = nullptr, *qn = nullptr, *y = nullptr, *beta = nullptr, *decay = nullptr, *o = nullptr;
   __half *kg_d = nullptr, *kg_f = nullptr, *kg_qa = nullptr, *kg_v = nullptr, *kg_2d = nullptr;
   OutBuf q, k, v, qkv, z, bp, ap, a, g, u, dn, eh;
+  float *pm = nullptr, *pl = nullptr, *po = nullptr;   // split-K attention partials of every row group of a chunk
   RowSet *rs = nullptr;    // [0] the whole chunk, [1 + i] its i-th group of attention rows
   int *ids = nullptr;      // the chunk's tokens
 };
@@ -813,6 +814,11 @@ static int pf_alloc(llb_spec *m) {
   f.qn = falloc(m, (size_t)PF_R * qa); f.y = falloc(m, (size_t)PF_R * m->convd); f.beta = falloc(m, (size_t)PF_R * m->TR);
   f.decay = falloc(m, (size_t)PF_R * m->TR); f.o = falloc(m, (size_t)PF_R * m->vdc);
   f.kg_d = kg(d); f.kg_f = kg(m->f); f.kg_qa = kg(qa); f.kg_v = kg(m->vdc); f.kg_2d = kg(2 * d);
+  {
+    const size_t ng = (PF_R + m->Tpf - 1) / m->Tpf, per = (size_t)m->H * m->Tpf * m->att_split;
+    f.pm = falloc(m, ng * per); f.pl = falloc(m, ng * per); f.po = falloc(m, ng * per * m->hd);
+    if (!f.pm || !f.pl || !f.po) return -1;
+  }
   f.rs = (RowSet *)dalloc(m, sizeof(RowSet) * (1 + PF_GROUPS));
   f.ids = (int *)dalloc(m, (size_t)(PF_R + 1) * 4);
   if (!f.x || !f.x1 || !f.hn || !f.e || !f.qn || !f.y || !f.beta || !f.decay || !f.o || !f.kg_d || !f.kg_f || !f.kg_qa || !f.kg_v || !f.kg_2d ||
@@ -820,6 +826,35 @@ static int pf_alloc(llb_spec *m) {
   f.ready = true;
   return 0;
 }
+
+// LLB_PF_MS=1 (the reference's switch for timing a fast-prefill chunk, host/llb_backend_cuda.h:215): device time of a
+// prompt's dense path by kind of op, printed to stderr when the prompt is done
+struct PfProf { const char *name; cudaEvent_t a, b; };
+static std::vector<PfProf> g_pfprof;
+static int pf_prof_on() { static int v = -1; if (v < 0) { const char *e = getenv("LLB_PF_MS"); v = e && e[0] == '1'; } return v; }
+struct PfTimer {
+  PfProf r; bool on;
+  PfTimer(const char *name) : on(pf_prof_on() != 0) { if (on) { r.name = name; cudaEventCreate(&r.a); cudaEventCreate(&r.b); cudaEventRecord(r.a, g_llb.stream); } }
+  ~PfTimer() { if (on) { cudaEventRecord(r.b, g_llb.stream); g_pfprof.push_back(r); } }
+};
+static void pf_prof_report(int rows, double wall_ms) {
+  if (!pf_prof_on()) return;
+  cudaStreamSynchronize(g_llb.stream);
+  std::vector<std::string> names; std::vector<double> tot; std::vector<int> cnt;
+  for (auto &r : g_pfprof) {
+    float ms = 0; cudaEventElapsedTime(&ms, r.a, r.b);
+    size_t k = 0;
+    for (; k < names.size(); k++) if (names[k] == r.name) break;
+    if (k == names.size()) { names.push_back(r.name); tot.push_back(0); cnt.push_back(0); }
+    tot[k] += ms; cnt[k]++;
+    cudaEventDestroy(r.a); cudaEventDestroy(r.b);
+  }
+  g_pfprof.clear();
+  fprintf(stderr, "pf: %d rows in %.1f ms:", rows, wall_ms);
+  for (size_t k = 0; k < names.size(); k++) fprintf(stderr, " %s %.2f ms / %d;", names[k].c_str(), tot[k], cnt[k]);
+  fprintf(stderr, "\n");
+}
+#define PFK(name, call) do { PfTimer t_(name); if ((call)) return -1; } while (0)
 
 struct PfSiteMat { const DevMat *w; OutBuf *out; };
 // the dense GEMMs of one site: matrices sharing the activations `kg` of K columns, one launch per format
@@ -871,29 +906,26 @@ static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
   PartIn none{nullptr, 0, 0};
   AttnShape ash{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd};
   DeltaShape dsh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
-  CK(op_pf_embed(s, m->embd.fmt, m->embd.w, d, f.ids, R, f.x));
+  PFK("embed", op_pf_embed(s, m->embd.fmt, m->embd.w, d, f.ids, R, f.x));
   for (int il = 0; il < m->L; il++) {
     const LayerW &l = m->layer[il];
-    CK(op_pf_norm(s, il ? f.x1 : f.x, il ? as_in(f.dn) : none, l.attn_norm, m->eps, d, f.x, f.kg_d, d, 0, nullptr, R));
+    PFK("norm", op_pf_norm(s, il ? f.x1 : f.x, il ? as_in(f.dn) : none, l.attn_norm, m->eps, d, f.x, f.kg_d, d, 0, nullptr, R));
     if (l.full) {
-      CK(pf_site(m, {{&l.at.q, &f.q}, {&l.at.k, &f.k}, {&l.at.v, &f.v}}, f.kg_d, d, R));
-      CK(op_qkrope(s, as_in(f.q), as_in(f.k), as_in(f.v), l.at.qn, l.at.kn, m->invfreq, ash, f.qn, m->Kc[il], m->Vc[il], &f.rs[0], R));
-      for (int g = 0; g < ngrp; g++) {
-        PartIn qg{f.q.p + (size_t)g * gsz * 2 * qa, f.q.ns, f.q.stride};
-        CK(op_attention(s, f.qn + (size_t)g * gsz * qa, m->Kc[il], m->Vc[il], qg, ash, m->att_split, m->pm, m->pl, m->po, m->xp_qa, &f.rs[1 + g], gsz,
-                        f.kg_qa, g * gsz));
-      }
-      CK(pf_site(m, {{&l.at.o, &f.a}}, f.kg_qa, qa, R));
+      PFK("gemm qkv", pf_site(m, {{&l.at.q, &f.q}, {&l.at.k, &f.k}, {&l.at.v, &f.v}}, f.kg_d, d, R));
+      PFK("qkrope", op_qkrope(s, as_in(f.q), as_in(f.k), as_in(f.v), l.at.qn, l.at.kn, m->invfreq, ash, f.qn, m->Kc[il], m->Vc[il], &f.rs[0], R));
+      // every group of gsz rows in one launch (grid z): each streams the K/V rows up to its own last position
+      PFK("attention", op_attention(s, f.qn, m->Kc[il], m->Vc[il], as_in(f.q), ash, m->att_split, f.pm, f.pl, f.po, m->xp_qa, &f.rs[1], gsz, f.kg_qa, 0, ngrp));
+      PFK("gemm attn_out", pf_site(m, {{&l.at.o, &f.a}}, f.kg_qa, qa, R));
     } else {
-      CK(pf_site(m, {{&l.dn.qkv, &f.qkv}, {&l.dn.z, &f.z}, {&l.dn.beta, &f.bp}, {&l.dn.alpha, &f.ap}}, f.kg_d, d, R));
-      CK(op_pf_delta(s, as_in(f.qkv), as_in(f.z), as_in(f.bp), as_in(f.ap), m->ring[il], m->ring_ks[il], l.dn.conv, l.dn.dt, l.dn.a, l.dn.norm, dsh,
+      PFK("gemm qkv|z|b|a", pf_site(m, {{&l.dn.qkv, &f.qkv}, {&l.dn.z, &f.z}, {&l.dn.beta, &f.bp}, {&l.dn.alpha, &f.ap}}, f.kg_d, d, R));
+      PFK("delta", op_pf_delta(s, as_in(f.qkv), as_in(f.z), as_in(f.bp), as_in(f.ap), m->ring[il], m->ring_ks[il], l.dn.conv, l.dn.dt, l.dn.a, l.dn.norm, dsh,
                      m->S[il], m->ctl, f.y, f.beta, f.decay, f.o, f.kg_v, p0, R));
-      CK(pf_site(m, {{&l.dn.out, &f.a}}, f.kg_v, m->vdc, R));
+      PFK("gemm ssm_out", pf_site(m, {{&l.dn.out, &f.a}}, f.kg_v, m->vdc, R));
     }
-    CK(op_pf_norm(s, f.x, as_in(f.a), l.ffn.post, m->eps, d, f.x1, f.kg_d, d, 0, nullptr, R));
-    CK(pf_site(m, {{&l.ffn.gate, &f.g}, {&l.ffn.up, &f.u}}, f.kg_d, d, R));
-    CK(op_pf_silu(s, as_in(f.g), as_in(f.u), m->f, f.kg_f, R));
-    CK(pf_site(m, {{&l.ffn.down, &f.dn}}, f.kg_f, m->f, R));
+    PFK("norm", op_pf_norm(s, f.x, as_in(f.a), l.ffn.post, m->eps, d, f.x1, f.kg_d, d, 0, nullptr, R));
+    PFK("gemm gate|up", pf_site(m, {{&l.ffn.gate, &f.g}, {&l.ffn.up, &f.u}}, f.kg_d, d, R));
+    PFK("silu", op_pf_silu(s, as_in(f.g), as_in(f.u), m->f, f.kg_f, R));
+    PFK("gemm down", pf_site(m, {{&l.ffn.down, &f.dn}}, f.kg_f, m->f, R));
   }
   // the trunk's output-normed rows: row r of the chunk into pf.hn row r + 1 (row 0 holds the row before the chunk)
   CK(op_pf_norm(s, f.x1, as_in(f.dn), m->out_norm, m->eps, d, nullptr, nullptr, 0, 0, f.hn + d, R));
@@ -921,10 +953,18 @@ static int pf_prefill(llb_spec *m, const int *ids, int n_rows, int keep, int *p_
   PfState &f = m->pf;
   CU_OK(cudaMemsetAsync(f.hn, 0, (size_t)m->d * 4, g_llb.stream));   // the hidden before position 0 is zero (host/llb_host.c:1816)
   int p = 0;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (pf_prof_on()) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, g_llb.stream); }
   while (n_rows - p > keep) {
     const int R = n_rows - p - keep < PF_R ? n_rows - p - keep : PF_R;
     CK(pf_chunk(m, ids, p, R));
     p += R;
+  }
+  if (e0) {
+    float ms = 0;
+    cudaEventRecord(e1, g_llb.stream); cudaEventSynchronize(e1); cudaEventElapsedTime(&ms, e0, e1);
+    pf_prof_report(p, ms);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
   }
   if (p > 0) {
     CU_OK(cudaMemcpyAsync(m->hn, f.hn, (size_t)m->d * 4, cudaMemcpyDeviceToDevice, g_llb.stream));

@@ -99,8 +99,10 @@ int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne,
 int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, const float *kn_w, const double *invfreq,
               AttnShape sh, float *qout, float *Kc, float *Vc, const RowSet *rs, int Tmax, bool kv_only = false);
 // kg != null: the gated rows go out as fp16 rows kg_row0 .. of a k-group-major chunk buffer (pf.cu) instead of the planes
+// nz > 1: that many consecutive groups of Tmax rows in one launch (rs, q, qg, pm / pl / po and the output rows advance
+// by one group per grid z)
 int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *Vc, PartIn qg, AttnShape sh, int nsplit,
-                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg = nullptr, int kg_row0 = 0);
+                 float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg = nullptr, int kg_row0 = 0, int nz = 1);
 int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax);
 int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,

@@ -36,18 +36,17 @@ int pf_pick_ksplit(int ntiles, int nsb, int sms) {
   int best = 1;
   double best_cost = 1e30;
   for (int ks = 1; ks <= 8 && ks <= nsb; ks++) {
-    if (nsb % ks) continue;                       // equal slices keep every unit the same length
     const long long units = (long long)ntiles * ks, waves = (units + sms - 1) / sms;
-    const double cost = (double)waves * (nsb / ks + 2.0) * (1.0 + 0.03 * (ks - 1));
+    const double cost = (double)waves * ((nsb + ks - 1) / ks + 2.0) * (1.0 + 0.03 * (ks - 1));   // the longest slice sets the pace
     if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
   }
   return best;
 }
 
-// fills the tile table; a.ksplit must divide K / 256
+// fills the tile table; K-slices are whole super-blocks, as equal as they come
 int pf_gemm(cudaStream_t s, int fmt, PfArgs &a) {
   if (a.nmat < 1 || a.nmat > PF_MAXMAT) return llb_fail("pf gemm: nmat %d", a.nmat);
-  if (a.K % 256 || a.ksplit < 1 || (a.K / 256) % a.ksplit) return llb_fail("pf gemm: K %d in %d slices", a.K, a.ksplit);
+  if (a.K % 256 || a.ksplit < 1 || a.ksplit > a.K / 256) return llb_fail("pf gemm: K %d in %d slices", a.K, a.ksplit);
   if (a.R < 1 || a.R > PF_R) return llb_fail("pf gemm: %d rows", a.R);
   a.t128[0] = 0;
   for (int i = 0; i < PF_MAXMAT; i++) a.t128[i + 1] = a.t128[i] + (i < a.nmat ? (a.m[i].rows + 127) / 128 : 0);
@@ -354,7 +353,7 @@ int llb_b200_pf_gemm(int fmt, unsigned long long w, int rows, int K, unsigned lo
   if (pf_setup()) return -1;
   const int nsb = K / 256;
   if (ksplit <= 0) ksplit = pf_pick_ksplit((rows + 127) / 128, nsb, g_llb.sms);
-  if (nsb % ksplit) return llb_fail("pf_gemm: %d K-slices do not divide %d super-blocks", ksplit, nsb);
+  if (ksplit > nsb) return llb_fail("pf_gemm: %d K-slices of %d super-blocks", ksplit, nsb);
   __half *kg = nullptr;
   float *parts = nullptr;
   CU_OK(cudaMalloc(&kg, pf_kg_halves(K) * 2));

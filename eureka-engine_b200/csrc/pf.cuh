@@ -22,7 +22,7 @@ struct PfArgs {
 int pf_setup(void);
 int pf_wait_errors(void);                         // 1 when a bounded wait of the dense GEMM ran out
 int pf_pick_ksplit(int ntiles, int nsb, int sms);
-int pf_gemm(cudaStream_t s, int fmt, PfArgs &a);  // fills the tile table; a.ksplit divides K / 256
+int pf_gemm(cudaStream_t s, int fmt, PfArgs &a);  // fills the tile table; a.ksplit <= K / 256
 int op_pf_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const int *ids, int R, float *x);
 int op_pf_norm(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, __half *kg, int kg_K, int kg_col0, float *hn_out, int R);
 int op_pf_silu(cudaStream_t s, PartIn g, PartIn u, int f, __half *kg, int R);

@@ -6,17 +6,18 @@
 //   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 128 prompt rows, K = 16 per instruction) issued
 //     by ONE thread, both operands in shared memory, fp32 accumulators in TENSOR MEMORY;
 //   * BOTH operands are two fp16 planes, hi = fp16(v) and lo = fp16((v - hi) * 2048) (about 22 bits of v, as the T-row
-//     path's activation planes): a 16-column step is three MMAs, hi.hi into one accumulator, hi.lo + lo.hi into a second
-//     one that the epilogue adds divided by 2048 (lo.lo is below fp32 resolution).  With one fp16 plane per operand every
+//     path's activation planes): a 16-column step is three MMAs, hi.hi, hi.lo and lo.hi, each into its own accumulator
+//     and each issued by its own thread; the epilogue adds the two cross terms divided by 2048 (lo.lo is below fp32
+//     resolution).  With one fp16 plane per operand every
 //     GEMM output carried a relative error of 4e-4, which a random 8-layer model amplified past the path's 2e-2 bar;
 //   * the activation planes arrive by TMA: the chunk's activations are kept in global memory in the order the operand
 //     wants (k-group major, common.cuh), so a 64-column stage of one plane is ONE contiguous 16 KB cp.async.bulk that
 //     completes on an mbarrier (plain bulk copies of this GPU's own memory, no multicast);
 //   * the weight planes are made on the fly: eight warps read the packed super-blocks (each thread one row's 32 weights
-//     of a stage), dequantise in fp32 with the reference's own operation order (tools/qwen35_engine.c:233-307), split
+//     of a stage), dequantise in fp32 (the formulas of tools/qwen35_engine.c:233-307, one FMA per weight), split
 //     each weight into its two planes and store 16-byte core-matrix rows; stores of a warp are conflict-free;
-//   * a three-stage ring of (32 KB weights, 32 KB activations) with full / empty mbarriers decouples the roles; two sets
-//     of accumulators let four more warps read a finished tile with tcgen05.ld while the next one multiplies;
+//   * a three-stage ring of (32 KB weights, 32 KB activations) with full / empty mbarriers decouples the roles, so
+//     loads and dequantisation run ahead while four more warps read a finished tile out with tcgen05.ld;
 //   * every wait is bounded: a wait that runs out sets *err, and all roles then run through without waiting, so the
 //     kernel returns, frees its tensor memory and leaves the context usable (llb_b200_wait_errors() reports it).
 #pragma once
@@ -78,31 +79,40 @@ template <int FMT> __device__ __forceinline__ void pf_load(const uint8_t *row, i
   }
 }
 
-// byte b (0..255) as a float without the conversion pipe: 0x4B0000bb is 2^23 + b exactly
-__device__ __forceinline__ float pf_b2f(uint32_t b) { return __uint_as_float(0x4B000000u | b) - 8388608.0f; }
+// An integer code c < 128 sitting in bits 16.. of a word becomes the float 128 + c by OR-ing 0x43000000 (no conversion
+// instruction); one FMA then gives scale * c - offset: fmaf(128 + c, scale, -(128 scale + offset)).  The constant is rounded
+// once per sub-block (about 1e-6 of a weight), instead of every weight being rounded twice as in the reference's
+// d * sc * q - dmin * m; both planes together still carry the result to about 22 bits.
+__device__ __forceinline__ float pf_code_f(uint32_t x, int j, uint32_t mask) {
+  // byte j of x, masked, moved to bits 16..: shifts by 16, 8, 0, -8
+  const uint32_t v = j == 0 ? x << 16 : j == 1 ? x << 8 : j == 2 ? x : x >> 8;
+  return __uint_as_float((v & (mask << 16)) | 0x43000000u);
+}
 
-// the 32 weights as fp32, dequantised with the reference's operation order (one rounding per operation, no FMA)
+// the 32 weights as fp32
 template <int FMT> __device__ __forceinline__ void pf_deq(const PfRaw &r, int c0, float (&w)[32]) {
   if constexpr (FMT == LLB_FM_Q8_0) {
-    const float d = h2f_bits(r.h[0]);
+    const float d = h2f_bits(r.h[0]), c = -384.0f * d;     // byte = q + 128, float = 256 + byte
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const uint32_t x = r.w[i] ^ 0x80808080u;   // q + 128 as an unsigned byte
+      const uint32_t x = r.w[i] ^ 0x80808080u;
 #pragma unroll
-      for (int j = 0; j < 4; j++) w[4 * i + j] = __fmul_rn(pf_b2f((x >> (8 * j)) & 0xffu) - 128.0f, d);
+      for (int j = 0; j < 4; j++) {
+        const uint32_t v = j == 0 ? x << 15 : j == 1 ? x << 7 : j == 2 ? x >> 1 : x >> 9;
+        w[4 * i + j] = fmaf(__uint_as_float((v & (0xffu << 15)) | 0x43800000u), d, c);
+      }
     }
   } else if constexpr (FMT == LLB_FM_Q6_K) {
     const int qd = (c0 >> 5) & 3;
     const float d = h2f_bits(r.h[1]);
     const float s0 = __fmul_rn(d, (float)(int8_t)(r.h[0] & 0xff)), s1 = __fmul_rn(d, (float)(int8_t)(r.h[0] >> 8));
+    const float k0 = -160.0f * s0, k1 = -160.0f * s1;      // (128 + code) - 160 = code - 32
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const uint32_t x = qd < 2 ? r.w[i] : r.w[i] >> 4, hb = r.x[i] >> (2 * qd);
+      const uint32_t x = qd < 2 ? r.w[i] : r.w[i] >> 4, hb = (r.x[i] >> (2 * qd)) & 0x03030303u;
+      const uint32_t c6 = (x & 0x0f0f0f0fu) | (hb << 4);   // four six-bit codes, one a byte
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const uint32_t code = ((x >> (8 * j)) & 15u) | (((hb >> (8 * j)) & 3u) << 4);
-        w[4 * i + j] = __fmul_rn(i < 4 ? s0 : s1, pf_b2f(code) - 32.0f);
-      }
+      for (int j = 0; j < 4; j++) w[4 * i + j] = fmaf(pf_code_f(c6, j, 0x3fu), i < 4 ? s0 : s1, i < 4 ? k0 : k1);
     }
   } else {
     const int j8 = (c0 >> 5) & 7, hi = j8 & 1;
@@ -110,15 +120,13 @@ template <int FMT> __device__ __forceinline__ void pf_deq(const PfRaw &r, int c0
     k4_scales(r.h[1], r.h[2], r.h[3], scA, scB, mnA, mnB);
     const float sc = (float)(((j8 < 4 ? scA : scB) >> (8 * (j8 & 3))) & 0xffu), mn = (float)(((j8 < 4 ? mnA : mnB) >> (8 * (j8 & 3))) & 0xffu);
     const float ds = __fmul_rn(h2f_bits(r.h[0] & 0xffffu), sc), dm = __fmul_rn(h2f_bits(r.h[0] >> 16), mn);
+    const float c = -fmaf(128.0f, ds, dm);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-      const uint32_t x = hi ? r.w[i] >> 4 : r.w[i];
+      uint32_t x = (hi ? r.w[i] >> 4 : r.w[i]) & 0x0f0f0f0fu;
+      if constexpr (FMT == LLB_FM_Q5_K) x |= ((r.x[i] >> j8) & 0x01010101u) << 4;   // the fifth bit of column l is bit j8 of qh byte l
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        uint32_t q = (x >> (8 * j)) & 15u;
-        if constexpr (FMT == LLB_FM_Q5_K) q |= ((r.x[i] >> (8 * j + j8)) & 1u) << 4;   // the fifth bit of column l is bit j8 of qh byte l
-        w[4 * i + j] = __fsub_rn(__fmul_rn(ds, pf_b2f(q)), dm);
-      }
+      for (int j = 0; j < 4; j++) w[4 * i + j] = fmaf(pf_code_f(x, j, 0x1fu), ds, c);
     }
   }
 }
@@ -144,6 +152,12 @@ __device__ __forceinline__ void pf_locate(const PfArgs &a, int tile, int &m, int
   while (m + 1 < a.nmat && tile >= a.t128[m + 1]) m++;
   row0 = (tile - a.t128[m]) * 128;
 }
+// K-slices are whole super-blocks, as equal as they come: first column and 64-column stages of unit u
+__device__ __forceinline__ void pf_slice(const PfArgs &a, int u, int ntiles, int &kbase, int &nst) {
+  const int ks = u / ntiles, nsb = a.K >> 8;
+  const int sb0 = (int)(((long long)ks * nsb) / a.ksplit), sb1 = (int)(((long long)(ks + 1) * nsb) / a.ksplit);
+  kbase = sb0 << 8; nst = (sb1 - sb0) << 2;
+}
 
 template <int FMT>
 __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
@@ -160,13 +174,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
   volatile uint32_t *dead = (volatile uint32_t *)(smem + 132);
   uint8_t *ring = smem + 1024;
   const uint32_t ring_s = smem_u32(ring);
-  const int ntiles = a.t128[a.nmat], nunits = ntiles * a.ksplit, kslice = a.K / a.ksplit, nst = kslice / PF_KS;
+  const int ntiles = a.t128[a.nmat], nunits = ntiles * a.ksplit;
   const size_t rb = dev_row_bytes(FMT, a.K);
 
   pdl_trigger();
   if (tid == 0) {
-    for (int s = 0; s < PF_STAGES; s++) { mbar_init(full_a(s), 8); mbar_init(full_b(s), 1); mbar_init(empty(s), 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    for (int s = 0; s < PF_STAGES; s++) { mbar_init(full_a(s), 8); mbar_init(full_b(s), 1); mbar_init(empty(s), 3); }
+    mbar_init(acc_full(0), 3); mbar_init(acc_empty(0), 4);
     *dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -191,15 +205,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
     PfRaw raw0, raw1;                                  // two stages of raw words in flight (never indexed: they stay in registers)
     int it = 0;                                        // stages produced so far by this CTA
     // the loads run two stages ahead of the conversion: cursor (lu, ls) is the stage to load next
-    int lu = blockIdx.x, ls = 0, lm = 0, lrow0 = 0;
+    int lu = blockIdx.x, ls = 0, lkbase = 0, lnst = 0, lm = 0, lrow0 = 0;
     const uint8_t *lrow = nullptr;
     auto lplan = [&]() {
-      if (lu < nunits) { pf_locate(a, lu % ntiles, lm, lrow0); lrow = a.m[lm].W + (size_t)min(lrow0 + r, a.m[lm].rows - 1) * rb; }
+      if (lu < nunits) {
+        pf_locate(a, lu % ntiles, lm, lrow0);
+        pf_slice(a, lu, ntiles, lkbase, lnst);
+        lrow = a.m[lm].W + (size_t)min(lrow0 + r, a.m[lm].rows - 1) * rb;
+      }
     };
     auto lnext = [&](PfRaw &dst) {
       if (lu < nunits) {
-        pf_load<FMT>(lrow, a.K, (lu / ntiles) * kslice + ls * PF_KS + 32 * h, dst);
-        if (++ls == nst) { ls = 0; lu += gridDim.x; lplan(); }
+        pf_load<FMT>(lrow, a.K, lkbase + ls * PF_KS + 32 * h, dst);
+        if (++ls == lnst) { ls = 0; lu += gridDim.x; lplan(); }
       }
     };
     // converts the stage held in rw (columns c0 ..), refills rw with the stage two ahead, publishes the stage
@@ -226,10 +244,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
     lnext(raw0);
     lnext(raw1);
     for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
-      const int kbase = (u / ntiles) * kslice + 32 * h;
+      int kbase, nst;
+      pf_slice(a, u, ntiles, kbase, nst);
       for (int s = 0; s < nst; s += 2) {               // nst is a multiple of four: a K-slice is whole super-blocks
-        one(raw0, kbase + s * PF_KS);
-        one(raw1, kbase + (s + 1) * PF_KS);
+        one(raw0, kbase + 32 * h + s * PF_KS);
+        one(raw1, kbase + 32 * h + (s + 1) * PF_KS);
       }
     }
   } else if (warp == 8) {
@@ -237,7 +256,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
     if (lane == 0) {
       int it = 0;
       for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
-        const int kbase = (u / ntiles) * kslice;
+        int kbase, nst;
+        pf_slice(a, u, ntiles, kbase, nst);
         for (int s = 0; s < nst; s++, it++) {
           const int slot = it % PF_STAGES;
           if (it >= PF_STAGES) wait(empty(slot), (uint32_t)((it / PF_STAGES) + 1) & 1u);
@@ -250,64 +270,65 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
         }
       }
     }
-  } else if (warp == 9) {
-    // ---- the tensor core: per stage four steps of K = 16, three MMAs each ----
+  } else if (warp >= 9 && warp < 12) {
+    // ---- the tensor core.  Issuing one tcgen05.mma costs a thread 100 to 200 cycles, more than a 128 x 128 x 16 MMA
+    // takes to execute, so the three products of a step have a thread each, and an accumulator each (a thread's MMAs
+    // execute in its issue order; MMAs of different threads into one accumulator would not be ordered):
+    //   warp 9: hi.hi -> D1     warp 10: hi.lo -> D2     warp 11: lo.hi -> D3     result = D1 + (D2 + D3) / 2048
     if (lane == 0) {
+      const int which = warp - 9;
+      const uint32_t d = tmem_base + (uint32_t)(which * PF_R);
+      const uint32_t a_off = which == 2 ? PF_A_BYTES : 0, b_off = 2 * PF_A_BYTES + (which == 1 ? PF_B_BYTES : 0);
       int it = 0, i = 0;
       for (int u = blockIdx.x; u < nunits; u += gridDim.x, i++) {
-        const int buf = i & 1;
-        if (i >= 2) wait(acc_empty(buf), (uint32_t)((i >> 1) + 1) & 1u);
+        int kbase, nst;
+        pf_slice(a, u, ntiles, kbase, nst);
+        if (i >= 1) wait(acc_empty(0), (uint32_t)(i - 1) & 1u);   // the previous tile has been read out of tensor memory
         t5_fence_after();
-        const uint32_t d1 = tmem_base + (uint32_t)(buf * 2 * PF_R), d2 = d1 + PF_R;   // hi.hi ; hi.lo + lo.hi
         for (int s = 0; s < nst; s++, it++) {
           const int slot = it % PF_STAGES;
           wait(full_a(slot), (uint32_t)(it / PF_STAGES) & 1u);
           wait(full_b(slot), (uint32_t)(it / PF_STAGES) & 1u);
           t5_fence_after();
-          const uint32_t A_s = ring_s + slot * PF_STAGE_BYTES, B_s = A_s + 2 * PF_A_BYTES;
+          const uint64_t ad = g3_desc(ring_s + slot * PF_STAGE_BYTES + a_off, 2048, 128), bd = g3_desc(ring_s + slot * PF_STAGE_BYTES + b_off, PF_R * 16, 128);
 #pragma unroll
-          for (int k = 0; k < PF_KS / 16; k++) {
-            const uint64_t ah = g3_desc(A_s + k * 2 * 2048, 2048, 128), al = g3_desc(A_s + PF_A_BYTES + k * 2 * 2048, 2048, 128);
-            const uint64_t bh = g3_desc(B_s + k * 2 * (PF_R * 16), PF_R * 16, 128), bl = g3_desc(B_s + PF_B_BYTES + k * 2 * (PF_R * 16), PF_R * 16, 128);
-            pf_mma_ss(d1, ah, bh, PF_IDESC, (s | k) != 0);
-            pf_mma_ss(d2, ah, bl, PF_IDESC, (s | k) != 0);
-            pf_mma_ss(d2, al, bh, PF_IDESC, 1);
-          }
+          for (int k = 0; k < PF_KS / 16; k++)   // a step is two k-groups further on: the address field counts 16-byte units
+            pf_mma_ss(d, ad + (uint64_t)(k * 2 * 2048 / 16), bd + (uint64_t)(k * 2 * PF_R * 16 / 16), PF_IDESC, (s | k) != 0);
           t5_commit(empty(slot));        // arrives when these MMAs have read the stage
         }
-        t5_commit(acc_full(buf));        // ... and when the whole tile is in tensor memory
+        t5_commit(acc_full(0));          // ... and when this thread's share of the tile is in tensor memory
       }
       // nothing of this CTA may still run on the tensor core when its tensor memory is freed
-      if (i > 0) wait(acc_full((i - 1) & 1), (uint32_t)((i - 1) >> 1) & 1u);
+      if (i > 0) wait(acc_full(0), (uint32_t)(i - 1) & 1u);
     }
   } else if (warp >= 12) {
-    // ---- results: lane quarter q of the accumulator, one weight row per thread ----
+    // ---- results: lane quarter q of the accumulators, one weight row per thread ----
     const int q = warp - 12;
     int i = 0;
     for (int u = blockIdx.x; u < nunits; u += gridDim.x, i++) {
-      const int buf = i & 1;
       int m, row0;
       pf_locate(a, u % ntiles, m, row0);
       const PfMat &M = a.m[m];
       const int row = row0 + 32 * q + lane;
       float *out = M.out + (size_t)(u / ntiles) * M.split_stride + row;
-      wait(acc_full(buf), (uint32_t)(i >> 1) & 1u);
+      wait(acc_full(0), (uint32_t)i & 1u);
       t5_fence_after();
-      const uint32_t t0 = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * 2 * PF_R);
+      const uint32_t t0 = tmem_base + ((uint32_t)(32 * q) << 16);
       for (int c = 0; c < a.R; c += 16) {
-        float v[16], vl[16];
+        float v[16], v2[16], v3[16];
         t5_ld16(t0 + c, v);
-        t5_ld16(t0 + PF_R + c, vl);
+        t5_ld16(t0 + PF_R + c, v2);
+        t5_ld16(t0 + 2 * PF_R + c, v3);
         t5_wait_ld();
         if (row < M.rows) {
 #pragma unroll
           for (int j = 0; j < 16; j++)
-            if (c + j < a.R) out[(size_t)(c + j) * M.ostride] = v[j] + vl[j] * XP_LO_INV;
+            if (c + j < a.R) out[(size_t)(c + j) * M.ostride] = v[j] + (v2[j] + v3[j]) * XP_LO_INV;
         }
       }
       t5_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty(buf));
+      if (lane == 0) mbar_arrive(acc_empty(0));
     }
   }
   t5_fence_before();
