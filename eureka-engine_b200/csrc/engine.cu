@@ -20,6 +20,7 @@
 #include "model.cuh"
 #include "gguf.cuh"
 #include "pf.cuh"
+#include "tp.cuh"
 
 struct DevMat { uint8_t *w = nullptr; int rows = 0, cols = 0, fmt = -1; };
 struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; size_t cap = 0; };   // K-slice partial sums of one matrix (cap: floats allocated)
@@ -105,6 +106,11 @@ struct llb_spec {
   bool delta_fused = true;            // LLB_DELTA_FUSED=0: DeltaNet scan and gated norm as two kernels
   bool moe_silu_fused = true;         // LLB_MOE_SILU_FUSED=0: the experts' silu as its own kernel also for T <= 4
   unsigned int *tile_ctr = nullptr;   // last-writer reduction counters of the GEMMs (one word per row tile)
+  // tensor parallel (tp.cu): the dimensions above are this rank's share once the model is open; the full ones are kept
+  // for slicing.  r_a / r_dn: the out-projections' [T, d] tiles summed over K-slices and ranks.
+  TpPlan tp = {0, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  int Hf = 0, KVf = 0, ff = 0, GKf = 0, TRf = 0, kdcf = 0, vdcf = 0, convdf = 0;
+  OutBuf r_a, r_dn;
   PfState pf;
   int prefill_mode = 0;   // 0: every prompt row through the T-row pass; 1: chunks of PF_R rows through the dense path (LLB_PREFILL=fast)
   double pf_rows = 0;     // prompt rows the dense path has processed since the engine was opened
@@ -283,6 +289,52 @@ static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, siz
   return 0;
 }
 
+// rows / cols (either may be null = all) of a tensor into a matrix of its own in the device layout: the whole tensor goes
+// to a temporary first, then strided device copies pick the ranges (columns of a quantised row are whole super-blocks)
+static int load_sliced(llb_spec *m, const TensorRec &t, const uint8_t *pack, size_t src_bytes, int on_device, const TpSel *rows, const TpSel *cols,
+                       DevMat &out) {
+  std::unordered_map<uint64_t, void *> none;
+  void *full = nullptr;
+  CK(load_tensor(m, t, pack, src_bytes, on_device, &full, none));
+  m->allocs.pop_back();                                    // the temporary is freed below, not at close
+  TpSel allr, allc;
+  allr.add(0, t.rows); allc.add(0, t.cols);
+  if (!rows) rows = &allr;
+  if (!cols) cols = &allc;
+  const int lr = rows->total(), lc = cols->total();
+  const size_t frb = dev_row_bytes(t.fmt, t.cols), lrb = dev_row_bytes(t.fmt, lc);
+  int rc = 0;
+  uint8_t *dst = (uint8_t *)dalloc(m, (size_t)lr * lrb);
+  if (!dst) rc = -1;
+  const int unit = t.fmt == LLB_FM_F32 ? 1 : t.fmt == LLB_FM_Q8_0 ? 32 : 256;
+  int drow = 0;
+  for (int i = 0; i < rows->n && !rc; i++) {
+    int dcol = 0;
+    for (int j = 0; j < cols->n && !rc; j++) {
+      const int c0 = cols->start[j], cn = cols->count[j];
+      if (c0 % unit || cn % unit) { rc = llb_fail("tensor slice: columns %d + %d are not whole blocks", c0, cn); break; }
+      const uint8_t *src = (const uint8_t *)full + (size_t)rows->start[i] * frb;
+      cudaError_t e;
+      if (t.fmt == LLB_FM_Q8_0) {   // [cols x int8][cols / 32 x f16]: the codes and the scales are two column ranges
+        e = cudaMemcpy2DAsync(dst + (size_t)drow * lrb + dcol, lrb, src + c0, frb, cn, rows->count[i], cudaMemcpyDeviceToDevice, g_llb.stream);
+        if (e == cudaSuccess)
+          e = cudaMemcpy2DAsync(dst + (size_t)drow * lrb + lc + dcol / 16, lrb, src + t.cols + c0 / 16, frb, cn / 16, rows->count[i], cudaMemcpyDeviceToDevice, g_llb.stream);
+      } else {
+        e = cudaMemcpy2DAsync(dst + (size_t)drow * lrb + dev_row_bytes(t.fmt, dcol), lrb, src + dev_row_bytes(t.fmt, c0), frb, dev_row_bytes(t.fmt, cn),
+                              rows->count[i], cudaMemcpyDeviceToDevice, g_llb.stream);
+      }
+      if (e != cudaSuccess) rc = llb_fail("tensor slice: %s", cudaGetErrorString(e));
+      dcol += cn;
+    }
+    drow += rows->count[i];
+  }
+  cudaStreamSynchronize(g_llb.stream);
+  cudaFree(full);
+  if (rc) return rc;
+  out.w = dst; out.rows = lr; out.cols = lc; out.fmt = t.fmt;
+  return 0;
+}
+
 // The routed experts of one layer: the router and the shared gate row into one F32 matrix, the expert
 // stacks (GGUF tensors ffn_gate_exps / ffn_up_exps [ne * ef][d], ffn_down_exps [ne * d][ef]) and the shared
 // expert re-laid as blocks [gate rows | up rows] and [down rows], the shared expert last.
@@ -407,6 +459,24 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
   return 0;
 }
 
+// Tensor parallel: a row-split projection leaves, on every rank, partial sums over its share of the columns (and over
+// its K-slices).  Add the K-slices, sum over the ranks (NCCL all-reduce on the library's stream, captured into the graph
+// like a kernel), and hand the consumer one complete [T, d] tile.  One rank: the consumer adds the K-slices itself.
+static int tp_reduce(llb_spec *m, const OutBuf &part, OutBuf &whole) {
+  if (m->tp.size <= 1) return 0;
+  const size_t n = (size_t)m->Tmax * m->d;
+  if (!whole.p || whole.cap < n) {
+    whole.p = falloc(m, n);
+    if (!whole.p) return -1;
+    whole.cap = n;
+  }
+  whole.ns = 1; whole.stride = 0;
+  CK(ops_sum_parts(g_llb.stream, part.p, part.ns, part.stride, (int)n, whole.p));
+  return tp_allreduce(whole.p, n);
+}
+static PartIn in_a(const llb_spec *m) { return m->tp.size > 1 ? as_in(m->r_a) : as_in(m->b_a); }
+static PartIn in_dn(const llb_spec *m) { return m->tp.size > 1 ? as_in(m->r_dn) : as_in(m->b_dn); }
+
 // ---- blocks -------------------------------------------------------------------------------------
 // full attention block on rows `rs`: planes xp_d hold the normed input; result partial sums in b_a
 static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const RowSet *rs) {
@@ -416,6 +486,7 @@ static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const Row
   PK("qkrope", op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
   PK("attention", op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
   PK("gemm attn_out", site_gemm(m, {{&w.o, &m->b_a, nullptr, nullptr, 0}}, m->xp_qa, 0));
+  PK("all-reduce", tp_reduce(m, m->b_a, m->r_a));
   return 0;
 }
 
@@ -426,7 +497,7 @@ static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const Row
 static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs);
 static int enq_moe_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
-  PK("norm post", op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, m->hn2, rs, m->Tmax, 0));
+  PK("norm post", op_norm_xp(s, xin, in_a(m), w.post, m->eps, m->d, x1, m->xp_d, 0, m->hn2, rs, m->Tmax, 0));
   return enq_moe_core(m, w, rs);
 }
 // ... from the normed rows on: planes in xp_d, the same rows as F32 in hn2
@@ -453,8 +524,8 @@ static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs) {
 static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
   if (w.moe) return enq_moe_ffn(m, w, xin, x1, rs);
-  PK("norm post", op_norm_xp(s, xin, as_in(m->b_a), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
-  if (w.gate.fmt == w.up.fmt && gemm_ffn_fusable(w.gate.fmt, w.down.fmt, m->NC, m->d) && !m->reduce_in_gemm) {
+  PK("norm post", op_norm_xp(s, xin, in_a(m), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
+  if (w.gate.fmt == w.up.fmt && gemm_ffn_fusable(w.gate.fmt, w.down.fmt, m->NC, m->d) && !m->reduce_in_gemm && m->tp.size <= 1) {
     // one launch: gate|up in one K-slice, a grid barrier, silu(gate) * up built in shared memory, down
     GemmArgs a1, a2;
     memset(&a1, 0, sizeof a1); memset(&a2, 0, sizeof a2);
@@ -472,6 +543,7 @@ static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, cons
   PK("gemm gate|up", site_gemm(m, {{&w.gate, &m->b_g, nullptr, nullptr, 0}, {&w.up, &m->b_u, nullptr, nullptr, 0}}, m->xp_d, 0));
   PK("silu", op_silu_xp(s, as_in(m->b_g), as_in(m->b_u), m->f, m->xp_f, rs, m->Tmax));
   PK("gemm down", site_gemm(m, {{&w.down, &m->b_dn, nullptr, nullptr, 0}}, m->xp_f, 0));
+  PK("all-reduce", tp_reduce(m, m->b_dn, m->r_dn));
   return 0;
 }
 
@@ -492,6 +564,7 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, int ring_ks, flo
     PK("delta gnorm", op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
   }
   PK("gemm ssm_out", site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
+  PK("all-reduce", tp_reduce(m, m->b_a, m->r_a));
   return 0;
 }
 
@@ -506,13 +579,13 @@ static int enq_verify(llb_spec *m) {
   for (int il = 0; il < m->L; il++) {
     const LayerW &l = m->layer[il];
     // x += previous layer's FFN output (kept as partial sums), h = rms(x) * attn_norm
-    PK("norm attn", op_norm_xp(s, il ? m->x1 : m->x, il ? as_in(m->b_dn) : none, l.attn_norm, m->eps, m->d, m->x, m->xp_d, 0, nullptr, rs,
+    PK("norm attn", op_norm_xp(s, il ? m->x1 : m->x, il ? in_dn(m) : none, l.attn_norm, m->eps, m->d, m->x, m->xp_d, 0, nullptr, rs,
                   m->Tmax, 0));
     if (l.full) CK(enq_attn(m, l.at, m->Kc[il], m->Vc[il], rs));
     else CK(enq_delta(m, l.dn, m->ring[il], m->ring_ks[il], m->S[il], rs));
     CK(enq_ffn(m, l.ffn, m->x, m->x1, rs));
   }
-  PK("norm out", op_norm_xp(s, m->x1, as_in(m->b_dn), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
+  PK("norm out", op_norm_xp(s, m->x1, in_dn(m), m->out_norm, m->eps, m->d, m->x, m->xp_d, 0, m->hn, rs, m->Tmax, 0));
   PK("gemm head", site_gemm(m, {{&m->head, &m->b_lg, nullptr, nullptr, 0}}, m->xp_d, 0));
   PK("top2", op_top2_part(s, as_in(m->b_lg), m->V, m->V, m->t2part, rs, m->Tmax));
   return 0;
@@ -530,7 +603,7 @@ static int enq_mtp(llb_spec *m, const RowSet *rs, const float *h, bool with_head
   CK(op_norm_xp(s, nullptr, as_in(m->b_eh), m->mt_attn_norm, m->eps, m->d, m->mt_x, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
   CK(enq_attn(m, m->mt_at, m->mt_Kc, m->mt_Vc, rs));
   CK(enq_ffn(m, m->mt_ffn, m->mt_x, m->x1, rs));
-  CK(op_norm_xp(s, m->x1, as_in(m->b_dn), m->mt_shn, m->eps, m->d, nullptr, m->xp_d, 0, m->mt_hn, rs, m->Tmax, 0));
+  CK(op_norm_xp(s, m->x1, in_dn(m), m->mt_shn, m->eps, m->d, nullptr, m->xp_d, 0, m->mt_hn, rs, m->Tmax, 0));
   if (with_head) {
     CK(site_gemm(m, {{&m->mt_head, &m->b_mlg, nullptr, nullptr, 0}}, m->xp_d, 0));
     CK(op_top2_part(s, as_in(m->b_mlg), m->mt_nv, m->mt_nv, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, rs, m->Tmax));
@@ -577,7 +650,7 @@ static int capture(llb_spec *m, int which, cudaGraphExec_t *out, size_t *nodes) 
 
 // ---- open ---------------------------------------------------------------------------------------
 static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, int on_device, const uint8_t *mtp, size_t mtp_bytes,
-                     int mtp_on_device, int k, int max_ctx, int layers) {
+                     int mtp_on_device, int k, int max_ctx, int layers, int tp_n) {
   std::unordered_map<std::string, TensorRec> tab;
   CK(parse_index(m, index_text, tab));
   CK(validate_index(m, tab, m->pack_bytes));
@@ -591,6 +664,57 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
                     m->ne, m->nk, m->ef, m->sf);
   if (m->d % 256 || m->f % 256 || m->vdc % 256 || (m->H * m->hd) % 256) return llb_fail("model widths must be multiples of 256");
   if (m->TR % m->GK || m->H % m->KV) return llb_fail("head counts do not divide");
+  // ---- tensor parallel: this rank's share of the projections (tp.cuh).  Column split (rows of the matrix): attn_q by
+  // query head, attn_k / attn_v by kv head, attn_qkv / attn_gate / ssm_beta / ssm_alpha by DeltaNet group and the value
+  // heads that read it, ffn_gate / ffn_up by FFN column; row split (columns of the matrix, summed over the ranks by an
+  // all-reduce): attn_output, ssm_out, ffn_down.  Embedding, head and norms are replicated: every rank computes the
+  // same logits and takes the same accept decision, so no token ever has to be exchanged.
+  m->Hf = m->H; m->KVf = m->KV; m->ff = m->f; m->GKf = m->GK; m->TRf = m->TR; m->kdcf = m->kdc; m->vdcf = m->vdc; m->convdf = m->convd;
+  TpSel s_q, s_kv, s_o, s_f, s_qkv, s_vrow, s_head;   // rows of attn_q; of attn_k / v; columns of attn_output; FFN; rows of attn_qkv; value rows x 128; value heads
+  const bool tp_on = tp_n > 1;
+  if (tp_on) {
+    if (tp_size() != tp_n) return llb_fail("llb_spec_open_tp: %d ranks asked for, llb_b200_tp_init joined %d", tp_n, tp_size());
+    if (m->ne > 0) return llb_fail("tensor parallel: models with routed experts are not split");
+    CK(tp_plan(tp_rank(), tp_n, m->H, m->KV, m->f, m->GK, m->TR, &m->tp));
+    const TpPlan &t = m->tp;
+    s_q.add(t.h0 * 2 * m->hd, t.H_l * 2 * m->hd);
+    s_kv.add(t.kv0 * m->hd, t.KV_l * m->hd);
+    s_o.add(t.h0 * m->hd, t.H_l * m->hd);
+    s_f.add(t.f0, t.f_l);
+    s_qkv.add(t.g0 * m->SZ, t.GK_l * m->SZ);
+    s_qkv.add(m->kdc + t.g0 * m->SZ, t.GK_l * m->SZ);
+    if (t.reps + 2 > 8) return llb_fail("tensor parallel: %d value heads per q/k group", t.reps);
+    for (int r = 0; r < t.reps; r++) {
+      s_qkv.add(2 * m->kdc + (r * m->GK + t.g0) * m->SZ, t.GK_l * m->SZ);
+      s_vrow.add((r * m->GK + t.g0) * m->SZ, t.GK_l * m->SZ);
+      s_head.add(r * m->GK + t.g0, t.GK_l);
+    }
+    m->H = t.H_l; m->KV = t.KV_l; m->f = t.f_l; m->GK = t.GK_l; m->TR = t.TR_l;
+    m->kdc = m->GK * m->SZ; m->vdc = m->TR * m->SZ; m->convd = 2 * m->kdc + m->vdc;
+    if (m->vdc % 256 || (m->H * m->hd) % 256) return llb_fail("tensor parallel: a rank's share (%d value columns, %d attention columns) is not whole super-blocks", m->vdc, m->H * m->hd);
+  }
+  // which rows / columns of a tensor this rank keeps, by the tensor's leaf name (trunk layers, a nextn block and the
+  // drafter image use the same names)
+  auto tp_sel = [&](const std::string &leaf, const TpSel *&rows, const TpSel *&cols) {
+    rows = cols = nullptr;
+    if (!tp_on) return;
+    if (leaf == "attn_q") rows = &s_q;
+    else if (leaf == "attn_k" || leaf == "attn_v") rows = &s_kv;
+    else if (leaf == "attn_output") cols = &s_o;
+    else if (leaf == "ffn_gate" || leaf == "ffn_up") rows = &s_f;
+    else if (leaf == "ffn_down") cols = &s_f;
+    else if (leaf == "attn_qkv" || leaf == "ssm_conv1d") rows = &s_qkv;
+    else if (leaf == "attn_gate") rows = &s_vrow;
+    else if (leaf == "ssm_beta" || leaf == "ssm_alpha") rows = &s_head;
+    else if (leaf == "ssm_out") cols = &s_vrow;
+    else if (leaf == "ssm_dt" || leaf == "ssm_a") cols = &s_head;
+  };
+  auto leaf_of = [](const std::string &name) {
+    std::string n = name;
+    for (const char *suf : {".weight", ".bias"}) { const size_t l = strlen(suf); if (n.size() > l && n.compare(n.size() - l, l, suf) == 0) n.resize(n.size() - l); }
+    const size_t dot = n.rfind('.');
+    return dot == std::string::npos ? n : n.substr(dot + 1);
+  };
   { const char *e = getenv("LLB_RS_EARLY"); m->rs_early = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_DELTA_FUSED"); m->delta_fused = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_MOE_SILU_FUSED"); m->moe_silu_fused = !(e && e[0] == '0'); }
@@ -613,6 +737,9 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   auto mat = [&](const std::string &name, DevMat &w) -> int {
     auto it = tab.find(name);
     if (it == tab.end()) return llb_fail("pack has no tensor %s", name.c_str());
+    const TpSel *rsel, *csel;
+    tp_sel(leaf_of(name), rsel, csel);
+    if (rsel || csel) return load_sliced(m, it->second, pack, m->pack_bytes, on_device, rsel, csel, w);
     void *p;
     CK(load_tensor(m, it->second, pack, m->pack_bytes, on_device, &p, dedupe));
     w.w = (uint8_t *)p; w.rows = it->second.rows; w.cols = it->second.cols; w.fmt = it->second.fmt;
@@ -716,13 +843,23 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     } else return llb_fail("drafter image is neither AUX1 nor MTP1");
     for (int j = 0; j < 17; j++) if (!got[j] || fm[j] < 0 || off[j] + nb[j] > mtp_bytes) return llb_fail("drafter image: entry %s missing or out of range", names[j]);
     const int nv = (int)(nb[16] / 4);
-    const int rows[17] = {1, 1, d, 1, 2 * qa, kvd, kvd, 1, 1, d, 1, m->f, m->f, d, 1, nv, 1};
-    const int cols[17] = {d, d, 2 * d, d, d, d, d, m->hd, m->hd, qa, d, d, d, m->f, d, d, nv};
+    // shapes in the image are the whole model's; a tensor-parallel rank keeps its share of the attention and FFN matrices
+    const int qaf = m->Hf * m->hd, kvdf = m->KVf * m->hd;
+    int rows[17] = {1, 1, d, 1, 2 * qaf, kvdf, kvdf, 1, 1, d, 1, m->ff, m->ff, d, 1, nv, 1};
+    int cols[17] = {d, d, 2 * d, d, d, d, d, m->hd, m->hd, qaf, d, d, d, m->ff, d, d, nv};
     std::unordered_map<uint64_t, void *> dd;
     void *ptr[17];
     for (int j = 0; j < 17; j++) {
       TensorRec t{off[j], nb[j], rows[j], cols[j], j == 16 ? LLB_FM_F32 : fm[j]};
-      CK(load_tensor(m, t, mtp, mtp_bytes, mtp_on_device, &ptr[j], dd));
+      const TpSel *rsel, *csel;
+      tp_sel(names[j], rsel, csel);
+      if (rsel || csel) {
+        DevMat w;
+        CK(load_sliced(m, t, mtp, mtp_bytes, mtp_on_device, rsel, csel, w));
+        ptr[j] = w.w; rows[j] = w.rows; cols[j] = w.cols;
+      } else {
+        CK(load_tensor(m, t, mtp, mtp_bytes, mtp_on_device, &ptr[j], dd));
+      }
     }
     auto MM = [&](int j) { DevMat w; w.w = (uint8_t *)ptr[j]; w.rows = rows[j]; w.cols = cols[j]; w.fmt = fm[j]; return w; };
     m->mt_enorm = (float *)ptr[0]; m->mt_hnorm = (float *)ptr[1]; m->mt_eh = MM(2); m->mt_attn_norm = (float *)ptr[3];
@@ -997,11 +1134,19 @@ extern "C" {
 
 LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                 size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers) {
+  return llb_spec_open_tp(index_text, pack, pack_bytes, pack_on_device, mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, 1);
+}
+
+// The engine as rank tp_rank of tp_size tensor-parallel ranks (llb_b200_tp_init first): this rank loads its share of every
+// projection and the passes exchange one all-reduce after each row-split projection.  Every rank must make the same calls
+// in the same order (the collectives inside a cycle pair up across the ranks); all of them return the same tokens.
+LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
+                                   size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_n) {
   if (!g_llb.stream) { llb_fail("llb_b200_init has not been called"); return nullptr; }
   if (!index_text || !pack) { llb_fail("llb_spec_open: no index or no pack"); return nullptr; }
   llb_spec *m = new llb_spec();
   m->pack_bytes = pack_bytes;
-  if (open_impl(m, index_text, (const uint8_t *)pack, pack_on_device, (const uint8_t *)mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers)) {
+  if (open_impl(m, index_text, (const uint8_t *)pack, pack_on_device, (const uint8_t *)mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, tp_n)) {
     llb_spec_close(m);
     return nullptr;
   }
@@ -1102,7 +1247,7 @@ LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
   CK(ctl_write(m, c));
   int p = 0;
   // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_R rows through the dense path (dense FFN only)
-  if (m->prefill_mode == 1 && m->ne == 0 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, ids, n - 1, m->Tspec, &p));
+  if (m->prefill_mode == 1 && m->ne == 0 && m->tp.size <= 1 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, ids, n - 1, m->Tspec, &p));
   while (p < n - 1) {
     // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
     // over the rows of the last chunk, and that cycle's kernels cover k + 1 rows

@@ -68,6 +68,9 @@ def lib() -> C.CDLL:
             "llb_spec_time_gemm": (i32, [vp, i32, vp, vp]), "llb_spec_graph_nodes": (i32, [vp, i32]),
             "llb_spec_profile_verify": (i32, [vp, C.c_char_p, i32]),
             "llb_spec_check_index": (i32, [C.c_char_p, sz]),
+            "llb_b200_tp_unique_id": (i32, [C.c_char_p, vp]), "llb_b200_tp_init": (i32, [C.c_char_p, i32, i32, vp]),
+            "llb_b200_tp_finalize": (None, []), "llb_b200_tp_plan": (i32, [i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32)]),
+            "llb_spec_open_tp": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
             "llb_spec_set_prefill": (i32, [vp, i32]), "llb_spec_fast_rows": (C.c_double, [vp]),
             "llb_b200_pf_gemm": (i32, [i32, u64, i32, i32, u64, i32, u64, i32]),
             "llb_b200_gemm_ksplit": (i32, [i32, i32, i32, i32, i32]), "llb_b200_ring_ksplit": (i32, [i32, i32, i32, i32, i32, i32]),
@@ -101,6 +104,42 @@ def init(device: int = 0):
     check(lib().llb_b200_init(device), "llb_b200_init")
 
 
+def tp_plan(rank: int, size: int, H: int, KV: int, f: int, GK: int, TR: int):
+    """Rank `rank` of `size`'s share of a model (no GPU needed): dict of H_l, h0, KV_l, kv0, f_l, f0, GK_l, g0, TR_l, reps."""
+    out = (C.c_int * 10)()
+    check(lib().llb_b200_tp_plan(rank, size, H, KV, f, GK, TR, out), "llb_b200_tp_plan")
+    return dict(zip(("H_l", "h0", "KV_l", "kv0", "f_l", "f0", "GK_l", "g0", "TR_l", "reps"), list(out)))
+
+
+def exchange_unique_id(make_id, rank: int, device=None):
+    """Rank 0's 128-byte communicator id on every rank of the initialised torch.distributed group (gloo or nccl)."""
+    import torch
+    import torch.distributed as dist
+    buf = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = torch.frombuffer(bytearray(make_id()), dtype=torch.uint8).clone()
+    t = buf.to(device) if device is not None else buf
+    dist.broadcast(t, 0)
+    return bytes(t.cpu().numpy().tobytes())
+
+
+def tp_init(device=None):
+    """Join the tensor-parallel communicator of the torch.distributed group this process belongs to (after init(device)):
+    rank 0 makes the NCCL id, torch.distributed carries it to the others.  Returns (rank, size)."""
+    import torch.distributed as dist
+    L = lib()
+    rank, size = dist.get_rank(), dist.get_world_size()
+
+    def make():
+        b = C.create_string_buffer(128)
+        check(L.llb_b200_tp_unique_id(None, b), "llb_b200_tp_unique_id")
+        return b.raw
+    uid = exchange_unique_id(make, rank, device)
+    keep = C.create_string_buffer(uid, 128)
+    check(L.llb_b200_tp_init(None, rank, size, keep), "llb_b200_tp_init")
+    return rank, size
+
+
 def alloc(nbytes: int) -> int:
     p = lib().llb_b200_alloc_zero(nbytes)
     if not p:
@@ -125,7 +164,7 @@ class SpecEngine:
     tensor); `mtp` the drafter image as bytes (host) or a CUDA uint8 tensor.
     """
 
-    def __init__(self, pack, mtp=None, k: int = 3, max_ctx: int = 4096, layers: int = 0):
+    def __init__(self, pack, mtp=None, k: int = 3, max_ctx: int = 4096, layers: int = 0, tp: int = 1):
         import numpy as np
         import torch
         L = lib()
@@ -142,8 +181,8 @@ class SpecEngine:
         else:
             self._mtp_keep = mtp
             mptr, mbytes, mdev = mtp.data_ptr(), mtp.numel(), int(mtp.is_cuda)
-        self.h = handle(L.llb_spec_open(pack.index_text().encode(), ptr, nbytes, int(on_dev), mptr, mbytes, mdev, k, max_ctx,
-                                        layers), "llb_spec_open")
+        self.h = handle(L.llb_spec_open_tp(pack.index_text().encode(), ptr, nbytes, int(on_dev), mptr, mbytes, mdev, k, max_ctx,
+                                           layers, tp), "llb_spec_open")
         self.k, self.vocab, self.d = k, pack.cfg.vocab_size, pack.cfg.d_model
         self.cfg = pack.cfg
 

@@ -143,6 +143,25 @@ LLB_API int llb_b200_gemm_noalloc(int fmt, llb_b200_dptr w, int rows, int K, llb
 typedef struct llb_spec llb_spec;
 LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                 size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers);
+/* Tensor parallelism over the GPUs of one box (the reference is single-GPU, docs/limits.md:96; this is the split its
+ * benchmark configuration asks for).  One process per GPU.  Rank 0 makes a 128-byte id with llb_b200_tp_unique_id and the
+ * host program hands it to the other ranks; every rank then calls llb_b200_tp_init (after llb_b200_init) and opens the
+ * engine with llb_spec_open_tp(..., tp_size).  nccl_path: the NCCL library to load at run time (NULL: libnccl.so.2 as the
+ * process finds it).  A rank keeps its share of the column-split projections (attn_q by query head, attn_k / attn_v by kv
+ * head, attn_qkv / attn_gate / ssm_beta / ssm_alpha by DeltaNet group, ffn_gate / ffn_up by FFN column) and of the
+ * row-split ones (attn_output, ssm_out, ffn_down), whose [T, d_model] results are summed by an NCCL all-reduce on the
+ * library's stream, two per layer, inside the cycle's CUDA graph.  Embedding, head and norms are replicated, so every rank
+ * emits the same tokens.  All ranks must make the same calls in the same order.  Heads, kv heads (or ranks per kv head),
+ * DeltaNet groups and FFN super-blocks must split tp_size ways; routed-expert models and the dense prompt path are not split. */
+LLB_API int llb_b200_tp_unique_id(const char *nccl_path, void *id128);
+LLB_API int llb_b200_tp_init(const char *nccl_path, int rank, int size, const void *id128);
+LLB_API void llb_b200_tp_finalize(void);
+LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
+                                   size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_size);
+/* Test entry (no GPU needed): rank `rank` of `size`'s share of a model with H query heads, KV kv heads, FFN width f, GK
+ * DeltaNet groups and TR value heads: out[10] = H_l, h0, KV_l, kv0, f_l, f0, GK_l, g0, TR_l, reps; -1 if it does not split. */
+LLB_API int llb_b200_tp_plan(int rank, int size, int H, int KV, int f, int GK, int TR, int *out10);
+
 /* What llb_spec_open checks before it touches the GPU, callable without one: the index parses, its #cfg values are
  * complete and consistent (no zero divisor, widths that agree), and every tensor's [offset, offset + bytes) lies inside
  * a pack of pack_bytes bytes -- a truncated pack.bin or a stale index.tsv is an error naming the tensor. */

@@ -320,3 +320,63 @@ def test_ring_ksplit_is_one_value_for_both_pass_widths(pkg):
     assert differs > 0            # the case the fixed split exists for does occur
     # a width no split up to 8 can serve is reported as 0 (the engine then refuses the model by name)
     assert L.llb_b200_ring_ksplit(Q6_K, 64, 1000, 8, 16, sms) == 0
+
+
+# ---- tensor-parallel partition (no GPU) ----------------------------------------------------------------
+def test_tp_plan_partitions_the_27b_shape(pkg):
+    """Every rank's share of the 27B shape at 2, 4 and 8 ranks: query heads, FFN super-blocks and DeltaNet groups are
+    disjoint and cover the model; FFN shares are whole super-blocks, uneven at 8 (68 = 4 x 9 + 4 x 8); kv heads are split
+    up to 4 ranks and replicated above (each rank holds the one head its queries read); a rank's value heads are exactly
+    the heads hh with hh % 16 in its groups (the tiling of tools/qwen35_engine.c:621-626)."""
+    llb = pkg.llb
+    H, KV, f, GK, TR = 24, 4, 17408, 16, 48
+    for n in (1, 2, 4, 8):
+        plans = [llb.tp_plan(r, n, H, KV, f, GK, TR) for r in range(n)]
+        heads = sorted(h for p in plans for h in range(p["h0"], p["h0"] + p["H_l"]))
+        assert heads == list(range(H))
+        cols = sorted(c for p in plans for c in range(p["f0"], p["f0"] + p["f_l"], 256))
+        assert cols == list(range(0, f, 256)) and all(p["f_l"] % 256 == 0 for p in plans)
+        assert max(p["f_l"] for p in plans) - min(p["f_l"] for p in plans) <= 256
+        groups = sorted(g for p in plans for g in range(p["g0"], p["g0"] + p["GK_l"]))
+        assert groups == list(range(GK))
+        for p in plans:
+            assert p["reps"] == TR // GK and p["TR_l"] == p["reps"] * p["GK_l"]
+            G = H // KV
+            used = {h // G for h in range(p["h0"], p["h0"] + p["H_l"])}
+            assert used <= set(range(p["kv0"], p["kv0"] + p["KV_l"]))        # every query head finds its kv head on its rank
+            if n <= KV:
+                assert p["KV_l"] == KV // n
+            else:
+                assert p["KV_l"] == 1
+    assert [llb.tp_plan(r, 8, H, KV, f, GK, TR)["f_l"] // 256 for r in range(8)] == [9, 9, 9, 9, 8, 8, 8, 8]
+    for bad in ((0, 5, H, KV, f, GK, TR), (0, 2, 3, 1, 512, 2, 4), (0, 4, 8, 2, 512, 2, 4), (3, 2, H, KV, f, GK, TR)):
+        with pytest.raises(llb.LlbError):
+            llb.tp_plan(*bad)
+
+
+def _gloo_id_rank(rank, world, port, q):
+    import sys
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    import __graft_entry__ as graft
+    llb = graft.load_package().llb
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    uid = llb.exchange_unique_id(lambda: bytes(range(128)), rank)
+    q.put((rank, uid))
+    dist.destroy_process_group()
+
+
+def test_unique_id_reaches_every_rank():
+    """The N > 1 tensor-parallel set-up on CPU: what rank 0 makes is what rank 1 passes to llb_b200_tp_init."""
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_gloo_id_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    out = dict(q.get(timeout=120) for _ in ps)
+    for p in ps:
+        p.join(60)
+    assert out[0] == out[1] == bytes(range(128))
