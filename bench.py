@@ -150,6 +150,62 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_tp(args, rank, world, local):
+    """One request stream over all N GPUs, tensor parallel (strong scaling): every rank holds its share of the
+    projections and the passes exchange two all-reduces a layer.  The line's value is that one stream's tok/s."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    llb = pkg.llb
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    llb.init(local)
+    llb.tp_init(device=f"cuda:{local}")
+    packs, pack, mtp, prompt = build_model(f"cuda:{local}", layers=args.layers or None)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    eng = llb.SpecEngine(pack, mtp, k=K_DRAFT, max_ctx=PROMPT + GEN_CAP + 64, tp=world)
+    del pack
+    torch.cuda.empty_cache()
+    t_pre = time.time()
+    eng.prefill(prompt)
+    torch.cuda.synchronize()
+    t_pre = time.time() - t_pre
+    steps, warm = args.steps, max(args.warmup, 3)
+    st = torch.cuda.ExternalStream(llb.lib().llb_b200_stream())
+    sampler = ClockSampler(local)
+    sampler.start()
+    eng.run_cycles(warm)
+    dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    _, toks = eng.run_cycles(steps)
+    e1.record(st)
+    dist.barrier(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    ver_ms = eng.time_verify(10)
+    prof = eng.profile_verify()
+    t = torch.tensor([ms, ver_ms], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ver_ms = t.tolist()
+    if rank == 0:
+        total = sum(v[1] for v in prof.values())
+        ar = prof.get("all-reduce", (0, 0.0))
+        line = {"metric": METRIC, "value": toks / (ms / 1000.0), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
+                "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "streams": 1, "parallelism": f"tp{world}", "layers": args.layers or 64,
+                           "l2": "inputs larger than L2", "tokens_per_cycle": toks / steps, "prefill_s": round(t_pre, 2)},
+                "clocks": clocks, "gpu_launches": eng.graph_nodes(0) * steps,
+                "verify_step": {"ms": ver_ms, "kernels": eng.graph_nodes(2)},
+                "all_reduce": {"per_pass": ar[0], "eager_us_per_pass": ar[1], "share_of_eager_pass": ar[1] / total if total else None,
+                               "what": "NCCL all-reduce of a [4, 5120] f32 tile after attn_output / ssm_out and after ffn_down; eager per-op event timing"}}
+        print(json.dumps(line), flush=True)
+    eng.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -158,6 +214,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (debugging only; the number is then not the headline)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tp", action="store_true", help="one stream over all GPUs, tensor parallel with an NCCL all-reduce per row-split projection (strong scaling)")
     ap.add_argument("--no-plain", action="store_true", help="skip the plain-decoding (k = 0) leg")
     ap.add_argument("--exact-prefill", action="store_true", help="feed the prompt through the 8-row verify pass instead of the dense tcgen05 path")
     args = ap.parse_args()
@@ -170,6 +227,9 @@ def main():
         run_reference(args, rank)
         return
 
+    if args.tp and world > 1:
+        run_tp(args, rank, world, local)
+        return
     import numpy as np
     import torch
     import __graft_entry__ as graft
