@@ -364,6 +364,7 @@ def main():
                        "prefill_s": round(t_pre, 3), "prefill_tok_s": round(PROMPT / t_pre, 1),
                        "prefill": "8-row verify passes" if args.exact_prefill else "dense tcgen05 path, chunks of 128 rows (all but the last k + 1 rows)", "build_s": round(t_build, 2)},
             "cycle_ms": ms / steps, "tokens_per_cycle": toks / (steps * world), "plain_decode": plain,
+            "wait_errors": llb.lib().llb_b200_wait_errors(),   # 1 if a bounded device-side wait ever ran out (results then invalid)
             "clocks": clocks,
             "e2e": {"value": n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 216,
                     "api": "llb_spec_pass(pos, tok) -> y[4], one call per token"},
