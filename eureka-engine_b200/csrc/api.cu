@@ -36,7 +36,6 @@ int llb_b200_init(int device) {
   if (pr.major < 10) return llb_fail("device %d is sm_%d%d; this library is built for sm_100a only", device, pr.major, pr.minor);
   { const char *e = getenv("LLB_PDL"); g_llb.pdl = !(e && e[0] == '0'); }
   { const char *e = getenv("LLB_GEMM3"); g_llb.gemm3 = e && e[0] == '1'; }
-  { const char *e = getenv("LLB_Q8_V1"); g_llb.q8_v1 = e && e[0] == '1'; }
   { const char *e = getenv("LLB_FFN_FUSED"); g_llb.ffn_fused = e && e[0] == '1'; }
   g_llb.sms = pr.multiProcessorCount;
   // a blocking stream: ordered after work a caller queued on the legacy default stream (torch's), so
@@ -221,6 +220,15 @@ int llb_b200_wait_errors(void) {
   NEED_INIT(-1)
   const int a = gemm_wait_errors(), b = pf_wait_errors();
   return a < 0 || b < 0 ? -1 : (a | b);
+}
+int llb_b200_wait_errors_clear(void) {
+  NEED_INIT(-1)
+  return gemm_wait_errors_clear() || pf_wait_errors_clear() ? -1 : 0;
+}
+int llb_b200_wait_selftest(int which, int limit) {
+  NEED_INIT(-1)
+  if (backend_graph_bail()) return -1;
+  return gemm_wait_selftest(g_llb.stream, which, limit);
 }
 
 int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp, llb_b200_dptr x_dev,

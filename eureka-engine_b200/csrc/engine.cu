@@ -93,19 +93,12 @@ struct llb_spec {
   int res_n = 256;
   // activations
   float *x = nullptr, *x1 = nullptr, *hn = nullptr, *e = nullptr, *qn = nullptr, *y = nullptr, *beta = nullptr, *decay = nullptr,
-        *o = nullptr, *logits = nullptr, *t2part = nullptr, *pm = nullptr, *pl = nullptr, *po = nullptr;
+        *logits = nullptr, *t2part = nullptr, *pm = nullptr, *pl = nullptr, *po = nullptr;
   float *mt_x = nullptr, *mt_hn = nullptr, *chain_h = nullptr, *mt_logits = nullptr;
   XPlanes xp_d, xp_f, xp_qa, xp_v, xp_2d;
   OutBuf b_q, b_k, b_v, b_z, b_bp, b_ap, b_a, b_g, b_u, b_dn, b_eh, b_lg, b_mlg, b_ring;
   int att_split = 1;
   int att_min = 96;                   // fewest positions per attention block (three 32-position tiles)
-  // Measured on the 27B shape: letting the last writer of a tile add the K-slices costs the GEMM's tail more
-  // (fence, atomic, a dependent round of loads) than it saves the consumers, so it is off by default.
-  bool reduce_in_gemm = false;
-  bool rs_early = true;               // LLB_RS_EARLY=0: every kernel reads its row set after the wait
-  bool delta_fused = true;            // LLB_DELTA_FUSED=0: DeltaNet scan and gated norm as two kernels
-  bool moe_silu_fused = true;         // LLB_MOE_SILU_FUSED=0: the experts' silu as its own kernel also for T <= 4
-  unsigned int *tile_ctr = nullptr;   // last-writer reduction counters of the GEMMs (one word per row tile)
   // tensor parallel (tp.cu): the dimensions above are this rank's share once the model is open; the full ones are kept
   // for slicing.  r_a / r_dn: the out-projections' [T, d] tiles summed over K-slices and ranks.
   TpPlan tp = {0, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
@@ -427,7 +420,7 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
     if (done[i]) continue;
     GemmArgs a;
     memset(&a, 0, sizeof a);
-    a.K = mats[i].w->cols; a.xp = xp; a.planes = 2; a.T = m->Tmax; a.tile_ctr = m->reduce_in_gemm ? m->tile_ctr : nullptr;
+    a.K = mats[i].w->cols; a.xp = xp; a.planes = 2; a.T = m->Tmax;
     int ntiles = 0;
     std::vector<size_t> grp;
     for (size_t j = i; j < mats.size() && grp.size() < GEMM_MAXMAT; j++)
@@ -445,12 +438,11 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
       if (sm.direct) {
         if (ks > sm.direct_splits) return llb_fail("gemm site: %d K-slices, the direct output holds %d", ks, sm.direct_splits);
         a.m[g].out = sm.direct; a.m[g].ostride = sm.direct_stride; a.m[g].split_stride = sm.direct_split_stride;
-        if (sm.out) { sm.out->p = sm.direct; sm.out->ns = m->reduce_in_gemm ? 1 : ks; sm.out->stride = sm.direct_split_stride; }
+        if (sm.out) { sm.out->p = sm.direct; sm.out->ns = ks; sm.out->stride = sm.direct_split_stride; }
       }
       else {
         CK(out_prepare(m, *sm.out, sm.w->rows, ks));
         a.m[g].out = sm.out->p; a.m[g].ostride = sm.w->rows; a.m[g].split_stride = sm.out->stride;
-        if (m->reduce_in_gemm) sm.out->ns = 1;   // the launch reduces its own K-slices into slice 0
       }
       done[grp[g]] = true;
     }
@@ -512,7 +504,7 @@ static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs) {
   a.W = w.gu; a.es = w.es_gu; a.g = m->moe_g; a.u = m->moe_u;
   int one = 1;
   PK("moe gate|up", gemm_launch_moe(s, w.fmt_gu, false, m->xp_d, a, &one, nullptr));
-  const bool silu_in_down = m->NC == 8 && m->moe_silu_fused;
+  const bool silu_in_down = m->NC == 8;
   if (!silu_in_down) PK("moe silu", op_silu_scaled_xp(s, PartIn{m->moe_g, 1, 0}, PartIn{m->moe_u, 1, 0}, fe, m->xp_e, rs, m->Tmax, m->moe_wt, m->ef));
   int ks = gemm_fix_ksplit(w.fmt_dn, m->NC, fe / 256, gemm_pick_ksplit(w.fmt_dn, m->NC, m->Tmax * (m->d / 16), fe / 256, g_llb.sms));
   CK(out_prepare(m, m->b_dn, m->d, ks));
@@ -525,7 +517,7 @@ static int enq_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, cons
   cudaStream_t s = g_llb.stream;
   if (w.moe) return enq_moe_ffn(m, w, xin, x1, rs);
   PK("norm post", op_norm_xp(s, xin, in_a(m), w.post, m->eps, m->d, x1, m->xp_d, 0, nullptr, rs, m->Tmax, 0));
-  if (w.gate.fmt == w.up.fmt && gemm_ffn_fusable(w.gate.fmt, w.down.fmt, m->NC, m->d) && !m->reduce_in_gemm && m->tp.size <= 1) {
+  if (w.gate.fmt == w.up.fmt && gemm_ffn_fusable(w.gate.fmt, w.down.fmt, m->NC, m->d) && m->tp.size <= 1) {
     // one launch: gate|up in one K-slice, a grid barrier, silu(gate) * up built in shared memory, down
     GemmArgs a1, a2;
     memset(&a1, 0, sizeof a1); memset(&a2, 0, sizeof a2);
@@ -557,12 +549,7 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, int ring_ks, flo
                    {&w.z, &m->b_z, nullptr, nullptr, 0}, {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}},
                m->xp_d, 0));
   PK("delta conv", op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
-  if (m->delta_fused) {
-    PK("delta scan+gnorm", op_delta_fused(s, S, m->ctl, m->y, m->beta, m->decay, as_in(m->b_z), w.norm, sh, m->xp_v, rs));
-  } else {
-    PK("delta scan", op_delta_scan(s, S, m->ctl, m->y, m->beta, m->decay, sh, m->o, rs, m->Tmax));
-    PK("delta gnorm", op_gnorm_xp(s, m->o, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->Tmax));
-  }
+  PK("delta scan+gnorm", op_delta_fused(s, S, m->ctl, m->y, m->beta, m->decay, as_in(m->b_z), w.norm, sh, m->xp_v, rs));
   PK("gemm ssm_out", site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
   PK("all-reduce", tp_reduce(m, m->b_a, m->r_a));
   return 0;
@@ -573,7 +560,7 @@ static int enq_verify(llb_spec *m) {
   cudaStream_t s = g_llb.stream;
   // the verify rows were set before this pass began (k_accept of the previous cycle, or the host for a
   // prompt chunk): kernels may read them ahead of their wait
-  const RowSet *rs = m->rs_early ? rs_stable(&m->ctl->verify) : &m->ctl->verify;
+  const RowSet *rs = rs_stable(&m->ctl->verify);
   PK("embed", op_embed(s, m->embd.fmt, m->embd.w, m->d, rs, m->Tmax, m->x));
   PartIn none{nullptr, 0, 0};
   for (int il = 0; il < m->L; il++) {
@@ -715,10 +702,6 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     const size_t dot = n.rfind('.');
     return dot == std::string::npos ? n : n.substr(dot + 1);
   };
-  { const char *e = getenv("LLB_RS_EARLY"); m->rs_early = !(e && e[0] == '0'); }
-  { const char *e = getenv("LLB_DELTA_FUSED"); m->delta_fused = !(e && e[0] == '0'); }
-  { const char *e = getenv("LLB_MOE_SILU_FUSED"); m->moe_silu_fused = !(e && e[0] == '0'); }
-  { const char *e = getenv("LLB_GEMM_REDUCE"); m->reduce_in_gemm = e && e[0] == '1'; }
   { const char *e = getenv("LLB_PREFILL"); m->prefill_mode = e && !strcmp(e, "fast"); }   // the reference's switch (host/llb_host.c:206)
   m->k = k; m->Tspec = k + 1; m->max_ctx = max_ctx;
   {
@@ -903,11 +886,9 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   int big = m->f > m->convd ? m->f : m->convd;
   m->x = falloc(m, (size_t)T * d); m->x1 = falloc(m, (size_t)T * d); m->hn = falloc(m, (size_t)SPEC_MAXT * d); m->e = falloc(m, (size_t)T * d);
   m->qn = falloc(m, (size_t)T * qa); m->y = falloc(m, (size_t)T * big); m->beta = falloc(m, (size_t)T * m->TR); m->decay = falloc(m, (size_t)T * m->TR);
-  m->o = falloc(m, (size_t)T * m->vdc); m->t2part = falloc(m, (size_t)2 * SPEC_MAXT * TOP2_NB * 4);
+  m->t2part = falloc(m, (size_t)2 * SPEC_MAXT * TOP2_NB * 4);
   m->mt_x = falloc(m, (size_t)T * d); m->mt_hn = falloc(m, (size_t)T * d); m->chain_h = falloc(m, d);
   m->att_split = g_llb.sms / m->KV;   // one wave of blocks: the kernel takes a whole SM's shared memory
-  { const char *e = getenv("LLB_ATT_SPLIT"); if (e && atoi(e) > 0) m->att_split = atoi(e); }
-  { const char *e = getenv("LLB_ATT_MIN"); if (e && atoi(e) >= 32) m->att_min = atoi(e) & ~31; }
   if (m->att_split < 1) m->att_split = 1;
   if (m->att_split > 128) m->att_split = 128;
   m->pm = falloc(m, (size_t)m->H * T * m->att_split); m->pl = falloc(m, (size_t)m->H * T * m->att_split);
@@ -927,13 +908,6 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   CU_OK(cudaHostAlloc((void **)&m->res_host, sizeof(SpecResult) * m->res_n, cudaHostAllocMapped));
   memset(m->res_host, 0, sizeof(SpecResult) * m->res_n);
   CU_OK(cudaHostGetDevicePointer((void **)&m->res_dev, m->res_host, 0));
-  {
-    int mt = (m->V + 15) / 16 + 64;
-    if ((2 * m->f + 15) / 16 + 64 > mt) mt = (2 * m->f + 15) / 16 + 64;
-    if ((m->convd + m->vdc + 2 * m->TR + 63) / 16 + 64 > mt) mt = (m->convd + m->vdc + 2 * m->TR + 63) / 16 + 64;
-    m->tile_ctr = (unsigned int *)dalloc(m, (size_t)mt * 4);
-    if (!m->tile_ctr) return -1;
-  }
   CK(ops_model_setup());
   set_width(m, m->Tspec);
   return 0;

@@ -16,7 +16,7 @@
 
 #define FFN_SYNC_LIMIT (1u << 22)
 
-__device__ __forceinline__ void ffn_grid_sync(unsigned int *sync, unsigned int nblocks, unsigned int *err) {
+__device__ __forceinline__ void ffn_grid_sync(unsigned int *sync, unsigned int nblocks, unsigned int *err, unsigned int limit = FFN_SYNC_LIMIT) {
   __threadfence();   // this thread's gate|up outputs, before the CTA says it is done
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -24,7 +24,7 @@ __device__ __forceinline__ void ffn_grid_sync(unsigned int *sync, unsigned int n
     unsigned int seen = 0, it = 0;
     do {
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sync) : "memory");
-    } while (seen < nblocks && ++it < FFN_SYNC_LIMIT);
+    } while (seen < nblocks && ++it < limit);
     if (seen < nblocks && err) atomicExch(err, 1u);
     // everybody who increments the second counter has left the loop above: the last one may reset both
     if (atomicAdd(sync + 1, 1u) == nblocks - 1) { sync[0] = 0; sync[1] = 0; __threadfence(); }

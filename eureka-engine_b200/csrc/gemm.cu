@@ -1,11 +1,10 @@
-// gemm.cu -- host side of the dequant-fused skinny GEMMs (kernels in gemm.cuh and gemm2.cuh).
+// gemm.cu -- host side of the dequant-fused skinny GEMMs (kernel in gemm2.cuh, its arithmetic in gemm.cuh).
 #include "gemm2.cuh"
 #include "gemm3.cuh"
 #include "ffn_fused.cuh"
 #include "moe.cuh"
 #include "host.cuh"
 
-static bool is_g2(int fmt) { return fmt == LLB_FM_Q4_K || fmt == LLB_FM_Q5_K || fmt == LLB_FM_Q6_K || (fmt == LLB_FM_Q8_0 && !g_llb.q8_v1); }
 static int g2_max_sb(int fmt, int NC) {
   return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC)
        : fmt == LLB_FM_Q8_0 ? g2_max_slice_sb<LLB_FM_Q8_0>(NC) : g2_max_slice_sb<LLB_FM_Q6_K>(NC);
@@ -18,11 +17,6 @@ static int g2_warps(int fmt) {
   return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : fmt == LLB_FM_Q8_0 ? (int)G2Traits<LLB_FM_Q8_0>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS;
 }
 
-template <int FMT, int NT> static int launch_one(cudaStream_t s, const GemmArgs &a, int grid) {
-  cudaError_t e = llb_launch(k_gemm<FMT, NT>, dim3(grid), dim3(GEMM_WARPS * 32), (size_t)gemm_smem_bytes<FMT>(), s, a);
-  if (e != cudaSuccess) return llb_fail("k_gemm launch: %s", cudaGetErrorString(e));
-  return 0;
-}
 template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs &a) {
   const int NC = 8 * NT, nsl = (a.nsb + a.ksplit - 1) / a.ksplit;
   int cps = g_llb.sms * G2_CPSM / a.ksplit;
@@ -50,18 +44,49 @@ static int launch_three(cudaStream_t s, const GemmArgs &a) {
   if (e != cudaSuccess) return llb_fail("k_gemm3 launch: %s", cudaGetErrorString(e));
   return 0;
 }
-// 1 when a bounded wait of the tcgen05 kernel has run out since the library was initialised
+// 1 when a bounded wait of the tcgen05 kernel or of the fused FFN's barrier has run out since the library was
+// initialised (or since the word was last cleared)
 int gemm_wait_errors(void) {
   unsigned int v = 0;
   if (g_g3_err && cudaMemcpy(&v, g_g3_err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   return (int)v;
 }
-
-template <int FMT> static int setup_fmt() {
-  CU_OK(cudaFuncSetAttribute(k_gemm<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem_bytes<FMT>()));
-  CU_OK(cudaFuncSetAttribute(k_gemm<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem_bytes<FMT>()));
+int gemm_wait_errors_clear(void) {
+  if (g_g3_err) CU_OK(cudaMemset(g_g3_err, 0, 4));
   return 0;
 }
+
+// The two device-side waits of this file, each made to run out on purpose with a small limit: an mbarrier nobody
+// arrives on (the wait of k_gemm3 and k_pfmm, tc5.cuh) and the fused FFN's grid barrier told to expect one block more
+// than the launch has.  One block, one waiting thread; the wait gives up after `limit` tries, sets the error word
+// exactly as in the real kernels and the kernel returns.
+__global__ void k_wait_selftest(int which, unsigned int limit, unsigned int *sync, unsigned int *err) {
+  __shared__ __align__(8) uint64_t bar;
+  if (which == 0) {
+    const uint32_t bar_s = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+      mbar_init(bar_s, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(bar_s, 0, limit)) atomicExch(err, 1u);
+  } else {
+    ffn_grid_sync(sync, 2u, err, limit);
+    if (threadIdx.x == 0) { sync[0] = 0; sync[1] = 0; }   // the block that never came would have reset them
+  }
+}
+int gemm_wait_selftest(cudaStream_t s, int which, int limit) {
+  if (which < 0 || which > 1 || limit < 1 || limit > 100000) return llb_fail("wait selftest: which 0..1, limit 1..100000");
+  unsigned int *sync = nullptr;
+  CU_OK(cudaMalloc(&sync, 8));           // a private pair of counters: the barrier of real launches is not touched
+  CU_OK(cudaMemsetAsync(sync, 0, 8, s));
+  k_wait_selftest<<<1, 32, 0, s>>>(which, (unsigned int)limit, sync, g_g3_err);
+  CU_OK(cudaGetLastError());
+  CU_OK(cudaStreamSynchronize(s));
+  CU_OK(cudaFree(sync));
+  return 0;
+}
+
 template <int FMT> static int setup_fmt2() {
   CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
@@ -78,7 +103,6 @@ template <int FMT> static int setup_moe() {
 }
 
 int gemm_setup(void) {
-  if (setup_fmt<LLB_FM_Q4_K>() || setup_fmt<LLB_FM_Q5_K>() || setup_fmt<LLB_FM_Q6_K>() || setup_fmt<LLB_FM_Q8_0>()) return -1;
   if (setup_fmt2<LLB_FM_Q4_K>() || setup_fmt2<LLB_FM_Q5_K>() || setup_fmt2<LLB_FM_Q6_K>() || setup_fmt2<LLB_FM_Q8_0>()) return -1;
   CU_OK(cudaFuncSetAttribute(k_gemm3, cudaFuncAttributeMaxDynamicSharedMemorySize, G3_SMEM_MAX));
   if (setup_moe<LLB_FM_Q4_K>() || setup_moe<LLB_FM_Q5_K>() || setup_moe<LLB_FM_Q6_K>()) return -1;
@@ -102,7 +126,7 @@ int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks) {
     const int mx = g3_max_slice_sb();
     const int lo = (nsb + mx - 1) / mx;
     if (ks < lo) ks = lo;
-  } else if (is_g2(fmt)) {
+  } else {
     const int mx = g2_max_sb(fmt, NC);
     const int lo = (nsb + mx - 1) / mx;       // the activation slice of a CTA has to fit in shared memory
     if (ks < lo) ks = lo;
@@ -128,12 +152,9 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
       const double cost = (double)rounds * (slice + 1.5) * (1.0 + 0.02 * (ks - 1));
       if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
       continue;
-    } else if (is_g2(fmt)) {
+    } else {
       const int cps = sms * G2_CPSM / ks > 0 ? sms * G2_CPSM / ks : 1;
       rounds = (ntiles + (long long)cps * g2_warps(fmt) - 1) / ((long long)cps * g2_warps(fmt));
-    } else {
-      const long long nw = (long long)sms * GEMM_WARPS;
-      rounds = ((long long)ntiles * ks + nw - 1) / nw;
     }
     const int slice = (nsb + ks - 1) / ks;
     const double cost = (double)rounds * slice * (1.0 + 0.02 * (ks - 1));
@@ -257,11 +278,6 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : launch_two<LLB_FM_Q4_K, 2>(s, a);
   if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : launch_two<LLB_FM_Q5_K, 2>(s, a);
   if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_two<LLB_FM_Q6_K, 1>(s, a) : launch_two<LLB_FM_Q6_K, 2>(s, a);
-  if (fmt == LLB_FM_Q8_0 && !g_llb.q8_v1) return NT == 1 ? launch_two<LLB_FM_Q8_0, 1>(s, a) : launch_two<LLB_FM_Q8_0, 2>(s, a);
-  const int nunits = a.tile0[a.nmat] * a.ksplit;
-  int grid = (nunits + GEMM_WARPS - 1) / GEMM_WARPS;
-  if (grid > g_llb.sms) grid = g_llb.sms;
-  if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_one<LLB_FM_Q6_K, 1>(s, a, grid) : launch_one<LLB_FM_Q6_K, 2>(s, a, grid);
-  if (fmt == LLB_FM_Q8_0) return NT == 1 ? launch_one<LLB_FM_Q8_0, 1>(s, a, grid) : launch_one<LLB_FM_Q8_0, 2>(s, a, grid);
+  if (fmt == LLB_FM_Q8_0) return NT == 1 ? launch_two<LLB_FM_Q8_0, 1>(s, a) : launch_two<LLB_FM_Q8_0, 2>(s, a);
   return llb_fail("gemm: format %d has no kernel", fmt);
 }

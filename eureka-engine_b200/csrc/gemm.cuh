@@ -10,14 +10,14 @@
 //  * activations are fp16 hi/lo planes (common.cuh), T <= 4 rows fill the n = 8 tile exactly;
 //  * every warp streams its own 16-row weight tiles through a private cp.async ring in shared
 //    memory (16-byte coalesced copies of the packed super-blocks, bank-conflict-free row stride),
-//    prefetching across tile boundaries so HBM requests never drain between tiles;
+//    prefetching across tile boundaries so HBM requests never drain between tiles (the kernel
+//    itself is k_gemm2 in gemm2.cuh; this file holds the arithmetic of a staged chunk and the epilogue);
 //  * up to four matrices that share the activations run in one launch (gate|up, q|k|v,
 //    qkv|z|beta|alpha), and K can be split into slices whose partial sums the consumer adds in a
 //    fixed order (deterministic, no atomics).
 #pragma once
 #include "common.cuh"
 
-#define GEMM_WARPS 8
 #define GEMM_MAXMAT 4
 #define GEMM_MAXSPLIT 16
 
@@ -39,8 +39,6 @@ struct GemmArgs {
   XPlanes xp;
   int planes;                  // 2: hi/lo columns are folded into T = NC/2 tokens; 1: NC independent tokens
   int T;                       // tokens actually written
-  unsigned int *tile_ctr;      // optional, zeroed, one word per row tile: with ksplit > 1 the warp that
-                               // writes a tile's last K-slice adds the slices in index order into slice 0
 };
 
 // a routed-expert launch (moe.cuh)
@@ -63,9 +61,6 @@ template <> struct FmtTraits<LLB_FM_Q5_K> { enum { SB = 176, RS = 352, STAGES = 
 template <> struct FmtTraits<LLB_FM_Q6_K> { enum { SB = 224, RS = 480, STAGES = 3 }; };
 template <> struct FmtTraits<LLB_FM_Q8_0> { enum { SB = 272, RS = 544, STAGES = 3 }; };  // 256 int8 + 16 B of scales
 
-template <int FMT> constexpr int gemm_smem_bytes() {
-  return GEMM_WARPS * FmtTraits<FMT>::STAGES * 16 * FmtTraits<FMT>::RS;
-}
 
 // the 8 six-bit scales and 8 six-bit mins of a Q4_K / Q5_K super-block as four byte-packed words
 // (tools/qwen35_engine.c:66-72, all eight pairs at once)
@@ -253,9 +248,7 @@ __device__ __forceinline__ void consume_chunk(const uint8_t *st, int csb, int kc
 }
 
 // ---- epilogue of one (row tile, K-slice) unit ---------------------------------------------------
-// Folds the planes, writes the unit's partial sums and, when a.tile_ctr is given and K is split, lets
-// the last writer of the tile reduce: it adds the ksplit slices in index order (so the sum does not
-// depend on who came last) and stores the total over slice 0.  Consumers then read one array.
+// Folds the planes and writes the unit's partial sums; the consumer adds the K-slices in index order.
 template <int NT>
 __device__ __forceinline__ void gemm_epilogue(const GemmArgs &a, const GemmMat &M, int ks, int tile, int row0, float (&acc)[NT][4], int lane) {
   const int gid = lane >> 2, j = lane & 3;
@@ -296,131 +289,4 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs &a, const GemmMat &
   for (int nt = 0; nt < NT; nt++)
 #pragma unroll
     for (int i = 0; i < 4; i++) if (on[nt][i]) out[idx[nt][i]] = val[nt][i];
-  if (a.ksplit > 1 && a.tile_ctr) {
-    __threadfence();
-    __syncwarp();
-    unsigned int old = 0;
-    if (lane == 0) old = atomicAdd(&a.tile_ctr[tile], 1u);
-    old = __shfl_sync(0xffffffffu, old, 0);
-    if (old == (unsigned int)a.ksplit - 1) {
-      __threadfence();
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          if (!on[nt][i]) continue;
-          float v = __ldcg(M.out + idx[nt][i]);
-          for (int k = 1; k < a.ksplit; k++) v += __ldcg(M.out + (size_t)k * M.split_stride + idx[nt][i]);
-          M.out[idx[nt][i]] = v;
-        }
-      if (lane == 0) a.tile_ctr[tile] = 0;
-    }
-  }
-}
-
-// ---- the kernel --------------------------------------------------------------------------------
-struct TileCursor {
-  int u;          // unit index (ks * ntiles + tile); >= nunits when exhausted
-  int c;          // chunk within the unit
-  int nch;        // chunks in this unit
-  int sb0, nsb;   // K-slice of this unit in super-blocks
-  int mat, row0;  // matrix and first row of the tile
-};
-
-template <int FMT>
-__device__ __forceinline__ void cursor_load(TileCursor &t, const GemmArgs &a, int ntiles, int nunits) {
-  if (t.u >= nunits) { t.nch = 0; return; }
-  int ks = t.u / ntiles, tile = t.u - ks * ntiles;
-  t.sb0 = (int)(((long long)ks * a.nsb) / a.ksplit);
-  t.nsb = (int)(((long long)(ks + 1) * a.nsb) / a.ksplit) - t.sb0;
-  t.nch = (t.nsb + 1) >> 1;
-  int m = 0;
-  while (m + 1 < a.nmat && tile >= a.tile0[m + 1]) m++;
-  t.mat = m;
-  t.row0 = (tile - a.tile0[m]) * 16;
-  t.c = 0;
-}
-
-// Issue the cp.async copies of chunk t.c of tile t into stage `st` (all 32 lanes cooperate).
-template <int FMT>
-__device__ __forceinline__ void issue_chunk(const TileCursor &t, const GemmArgs &a, uint32_t st, int lane) {
-  constexpr int RS = FmtTraits<FMT>::RS;
-  const GemmMat &M = a.m[t.mat];
-  const size_t rb = dev_row_bytes(FMT, a.K);
-  const int sb = t.sb0 + 2 * t.c, csb = min(2, t.nsb - 2 * t.c);
-  if constexpr (FMT == LLB_FM_Q8_0) {
-    // per row: csb*256 bytes of int8 then csb*16 bytes of scales (placed at stage offset 512)
-    const int per_row = csb * 16 + csb;  // 16-byte pieces
-    for (int i = lane; i < 16 * per_row; i += 32) {
-      int r = i / per_row, p = i - r * per_row;
-      int row = min(t.row0 + r, M.rows - 1);
-      const uint8_t *src = M.W + (size_t)row * rb;
-      if (p < csb * 16) cp_async16(st + r * RS + p * 16, src + (size_t)sb * 256 + p * 16);
-      else cp_async16(st + r * RS + 512 + (p - csb * 16) * 16, src + a.K + (size_t)sb * 16 + (p - csb * 16) * 16);
-    }
-  } else {
-    constexpr int SB = FmtTraits<FMT>::SB;
-    const int per_row = csb * (SB / 16);
-    for (int i = lane; i < 16 * per_row; i += 32) {
-      int r = i / per_row, p = i - r * per_row;
-      int row = min(t.row0 + r, M.rows - 1);
-      cp_async16(st + r * RS + p * 16, M.W + (size_t)row * rb + (size_t)sb * SB + p * 16);
-    }
-  }
-}
-
-template <int FMT, int NT>
-__global__ void __launch_bounds__(GEMM_WARPS * 32, 1) k_gemm(const GemmArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  constexpr int RS = FmtTraits<FMT>::RS, STAGES = FmtTraits<FMT>::STAGES;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nw = gridDim.x * GEMM_WARPS, gw = blockIdx.x * GEMM_WARPS + warp;
-  const int ntiles = a.tile0[a.nmat], nunits = ntiles * a.ksplit;
-  uint8_t *ring = smem + (size_t)warp * STAGES * 16 * RS;
-  const uint32_t ring_s = smem_u32(ring);
-
-  pdl_trigger();
-  TileCursor prod, cons;
-  prod.u = gw; cursor_load<FMT>(prod, a, ntiles, nunits);
-  cons = prod;
-  // prologue: STAGES-1 chunks in flight
-  int pstage = 0;
-#pragma unroll 1
-  for (int s = 0; s < STAGES - 1; s++) {
-    if (prod.nch) {
-      issue_chunk<FMT>(prod, a, ring_s + pstage * 16 * RS, lane);
-      if (++prod.c == prod.nch) { prod.u += nw; cursor_load<FMT>(prod, a, ntiles, nunits); }
-    }
-    cp_async_commit();
-    pstage = (pstage + 1) % STAGES;
-  }
-  pdl_wait();   // the activation planes come from the previous kernel; the weights above do not
-  int cstage = 0;
-  float acc[NT][4];
-#pragma unroll 1
-  while (cons.nch) {
-    if (cons.c == 0) {
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-    }
-    cp_async_wait<STAGES - 2>();
-    __syncwarp();
-    const int csb = min(2, cons.nsb - 2 * cons.c);
-    consume_chunk<FMT, NT>(ring + cstage * 16 * RS, csb, (cons.sb0 + 2 * cons.c) * 256, a, acc, lane);
-    __syncwarp();
-    // refill the stage just freed... the one consumed one iteration ago is `pstage`
-    if (prod.nch) {
-      issue_chunk<FMT>(prod, a, ring_s + pstage * 16 * RS, lane);
-      if (++prod.c == prod.nch) { prod.u += nw; cursor_load<FMT>(prod, a, ntiles, nunits); }
-    }
-    cp_async_commit();
-    pstage = (pstage + 1) % STAGES;
-    cstage = (cstage + 1) % STAGES;
-    if (++cons.c == cons.nch) {
-      gemm_epilogue<NT>(a, a.m[cons.mat], cons.u / ntiles, cons.u % ntiles, cons.row0, acc, lane);
-      cons.u += nw;
-      cursor_load<FMT>(cons, a, ntiles, nunits);
-    }
-  }
-  cp_async_wait<0>();
 }

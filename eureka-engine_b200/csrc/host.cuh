@@ -12,7 +12,6 @@ struct LlbCtx {
   int device = -1;
   int sms = 0;
   int ffn_fused = 0;   // the FFN as one launch with a grid barrier (LLB_FFN_FUSED=1)
-  int q8_v1 = 0;   // Q8_0 on the first-generation kernel (LLB_Q8_V1=1)
   int gemm3 = 0;   // Q4_K, T <= 4 on the tcgen05 kernel (LLB_GEMM3=1)
   int pdl = 1;     // programmatic dependent launch on every kernel of a pass (LLB_PDL=0 turns it off)
   cudaStream_t stream = nullptr;
@@ -53,6 +52,8 @@ int gemm_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_pf, int s
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
 int gemm_setup(void);
 int gemm_wait_errors(void);
+int gemm_wait_errors_clear(void);
+int gemm_wait_selftest(cudaStream_t s, int which, int limit);
 bool gemm_ffn_fusable(int fmt_gu, int fmt_dn, int NC, int d);
 int gemm_launch_ffn(cudaStream_t s, GemmArgs &a1, int fmt2, GemmArgs &a2);   // gate|up (Q4_K, one K-slice), silu, down in one launch
 int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeArgs &m, int *ksplit, const float *wt_silu);   // moe.cuh

@@ -105,10 +105,6 @@ int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *V
                  float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg = nullptr, int kg_row0 = 0, int nz = 1);
 int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax);
-int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,
-                  DeltaShape sh, float *o, const RowSet *rs, int Tmax);
-int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs,
-                int Tmax);
 int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,
                    const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs);
 // A row set that no kernel of the pass in flight writes (the verify rows: k_accept sets them at the end

@@ -392,128 +392,16 @@ int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartI
   return 0;
 }
 
-// The recurrent scan over the T rows with per-row state checkpoints
-// (llb_t_l2qk + llb_t_gdl, tools/payload-spec2.patch:353-410; tools/qwen35_engine.c:610-646).
-// grid (TR, 4), 128 threads: block (hh, jq) owns state rows j = 32 jq .. 32 jq + 31 of head hh, 32
-// registers of state per thread (thread = row jr, column quarter cq).  The state is read from ring
-// slot sc and the state after row r is written to slot (sc + r + 1) % R, so rejecting rows costs
-// nothing: the next cycle simply starts from the slot of the last served row.
-__global__ void __launch_bounds__(128) k_delta_scan(float *__restrict__ S, const SpecCtl *__restrict__ ctl,
-                                                    const float *__restrict__ y, const float *__restrict__ beta,
-                                                    const float *__restrict__ decay, DeltaShape sh, float *__restrict__ o,
-                                                    const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
-  __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2];
-  __shared__ float red[2 * SPEC_MAXT][4];
-  const int hh = blockIdx.x, jq = blockIdx.y, tid = threadIdx.x, n = rs_n, lane = tid & 31, wp = tid >> 5;
-  const int g = hh % sh.GK;   // value head hh reads q/k group hh % GK (tile, tools/qwen35_engine.c:621-626)
-  const int jr = tid >> 2, cq = tid & 3, R = ctl->R, sc = ctl->sc;
-  const size_t head_sz = 128 * 128, slot_sz = (size_t)sh.TR * head_sz;
-  // thread (jr, cq) holds columns 16*i + 4*cq + e (i < 8, e < 4) of state row 32*jq + jr: the four
-  // threads of a row read 64 contiguous bytes per i, and their k / q reads from shared memory are four
-  // consecutive float4 (no bank conflict; a 32-column-per-thread split would put all four on one bank)
-  const size_t off = (size_t)hh * head_sz + (size_t)(32 * jq + jr) * 128 + 4 * cq;
-  // the state rows first: their latency hides behind the q/k preparation
-  float st[32];
-  {
-    const float4 *src = (const float4 *)(S + (size_t)sc * slot_sz + off);
-#pragma unroll
-    for (int i = 0; i < 8; i++) { float4 v = src[4 * i]; st[4 * i] = v.x; st[4 * i + 1] = v.y; st[4 * i + 2] = v.z; st[4 * i + 3] = v.w; }
-  }
-  float qv[SPEC_MAXT], kv[SPEC_MAXT];
-#pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++) {
-    qv[t] = t < n ? y[(size_t)t * sh.convd + g * 128 + tid] : 0.0f;
-    kv[t] = t < n ? y[(size_t)t * sh.convd + sh.kdc + g * 128 + tid] : 0.0f;
-  }
-  if (tid < 32) {
-#pragma unroll
-    for (int t = 0; t < SPEC_MAXT; t++) if (t < n) vs[t][tid] = y[(size_t)t * sh.convd + 2 * sh.kdc + hh * 128 + 32 * jq + tid];
-  }
-  if (tid < 2 * SPEC_MAXT && (tid >> 1) < n) db[tid >> 1][tid & 1] = (tid & 1) ? beta[(tid >> 1) * sh.TR + hh] : decay[(tid >> 1) * sh.TR + hh];
-#pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++) {
-    const float a = warp_sum(qv[t] * qv[t]), b = warp_sum(kv[t] * kv[t]);
-    if (lane == 0) { red[2 * t][wp] = a; red[2 * t + 1][wp] = b; }
-  }
-  __syncthreads();
-#pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++) {
-    if (t < n) {
-      const float sq = red[2 * t][0] + red[2 * t][1] + red[2 * t][2] + red[2 * t][3];
-      const float sk = red[2 * t + 1][0] + red[2 * t + 1][1] + red[2 * t + 1][2] + red[2 * t + 1][3];
-      const float nq = sqrtf(sq), nk = sqrtf(sk);
-      const float iq = (1.0f / (nq > sh.eps ? nq : sh.eps)) / sqrtf(128.0f), ik = 1.0f / (nk > sh.eps ? nk : sh.eps);
-      qs[t][tid] = qv[t] * iq;
-      ks[t][tid] = kv[t] * ik;
-    }
-  }
-  __syncthreads();
-  for (int t = 0; t < n; t++) {
-    const float dec = db[t][0], bt = db[t][1];
-    float kq[32];
-#pragma unroll
-    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&ks[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
-    float ka[4] = {0.f, 0.f, 0.f, 0.f};   // four independent chains instead of one of 32
-#pragma unroll
-    for (int i = 0; i < 32; i++) { st[i] *= dec; ka[i & 3] += st[i] * kq[i]; }
-    float kvacc = (ka[0] + ka[1]) + (ka[2] + ka[3]);
-    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 1);
-    kvacc += __shfl_xor_sync(0xffffffffu, kvacc, 2);
-    const float delta = (vs[t][jr] - kvacc) * bt;
-#pragma unroll
-    for (int i = 0; i < 32; i++) st[i] += kq[i] * delta;
-#pragma unroll
-    for (int i = 0; i < 8; i++) { const float4 v = *(const float4 *)&qs[t][16 * i + 4 * cq]; kq[4 * i] = v.x; kq[4 * i + 1] = v.y; kq[4 * i + 2] = v.z; kq[4 * i + 3] = v.w; }
-    float oa[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 32; i++) oa[i & 3] += st[i] * kq[i];
-    float oacc = (oa[0] + oa[1]) + (oa[2] + oa[3]);
-    oacc += __shfl_xor_sync(0xffffffffu, oacc, 1);
-    oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
-    if (cq == 0) o[(size_t)t * sh.vdc + hh * 128 + 32 * jq + jr] = oacc;
-    float4 *dst = (float4 *)(S + (size_t)((sc + t + 1) % R) * slot_sz + off);
-#pragma unroll
-    for (int i = 0; i < 8; i++) dst[4 * i] = make_float4(st[4 * i], st[4 * i + 1], st[4 * i + 2], st[4 * i + 3]);
-  }
-}
-int op_delta_scan(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay,
-                  DeltaShape sh, float *o, const RowSet *rs, int Tmax) {
-  (void)Tmax;
-  if (sh.SZ != 128) return llb_fail("DeltaNet state size %d (only 128, as host/llb_host.c:1608)", sh.SZ);
-  CU_OK(llb_launch(k_delta_scan, dim3(sh.TR, 4), dim3(128), (size_t)(0), s, S, ctl, y, beta, decay, sh, o, rs));
-  CU_OK(cudaGetLastError());
-  return 0;
-}
-
-// gated RMSNorm of each head's output -> planes of ssm_out's input
-// (llb_t_grn, tools/payload-spec2.patch:413-447; tools/qwen35_engine.c:648-654)
-__global__ void __launch_bounds__(128) k_gnorm_xp(const float *__restrict__ o, PartIn z, const float *__restrict__ nw,
-                                                  DeltaShape sh, XPlanes xp, const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  __shared__ float red[32];
-  const int hh = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
-  if (t >= rs_n) return;
-  const size_t idx = (size_t)t * sh.vdc + hh * 128 + i;
-  const float v = o[idx];
-  const float ss = block_sum(v * v, red);
-  const float r = 1.0f / sqrtf(ss / 128.0f + sh.eps);
-  xp_store32(xp, t, 2, hh * 128 + (i & ~31), v * r * nw[i] * silu_f(part_get(z, idx)), i & 31);
-}
-int op_gnorm_xp(cudaStream_t s, const float *o, PartIn z, const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs, int Tmax) {
-  CU_OK(llb_launch(k_gnorm_xp, dim3(sh.TR, Tmax), dim3(128), (size_t)(0), s, o, z, nw, sh, xp, rs));
-  CU_OK(cudaGetLastError());
-  return 0;
-}
-
 // ---- DeltaNet scan + gated RMSNorm as one kernel ------------------------------------------------
-// The scan of k_delta_scan, then the gated RMSNorm into the planes of ssm_out's input.  grid (TR, 4) in
-// clusters of four blocks = one value head: each block owns 32 state rows, and the RMSNorm's sum of
-// squares over the head's 128 outputs is exchanged through distributed shared memory.  Replaces
-// llb_t_gdl + llb_t_grn (tools/payload-spec2.patch:319-447) and one launch per DeltaNet layer.
+// The recurrent scan over the T rows with per-row state checkpoints (llb_t_l2qk + llb_t_gdl,
+// tools/payload-spec2.patch:353-410; tools/qwen35_engine.c:610-646), then the gated RMSNorm of each head's
+// output into the planes of ssm_out's input (llb_t_grn, tools/payload-spec2.patch:413-447;
+// tools/qwen35_engine.c:648-654).  grid (TR, 4) in clusters of four blocks = one value head, 128 threads:
+// block (hh, jq) owns state rows j = 32 jq .. 32 jq + 31 of head hh, 32 registers of state per thread
+// (thread = row jr, column quarter cq); the RMSNorm's sum of squares over the head's 128 outputs is
+// exchanged through distributed shared memory.  The state is read from ring slot sc and the state after
+// row r is written to slot (sc + r + 1) % R, so rejecting rows costs nothing: the next cycle simply
+// starts from the slot of the last served row.
 // (Folding the conv in as well was measured and dropped: every block has to redo the conv of its whole
 // q/k group from the four partial-sum slices of the ring, 12x the loads, 65 us against 29 us for three kernels.)
 __global__ void __cluster_dims__(1, 4, 1) __launch_bounds__(128)

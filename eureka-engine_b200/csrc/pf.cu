@@ -29,6 +29,10 @@ int pf_wait_errors(void) {
   if (g_pf_err && cudaMemcpy(&v, g_pf_err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   return (int)v;
 }
+int pf_wait_errors_clear(void) {
+  if (g_pf_err) CU_OK(cudaMemset(g_pf_err, 0, 4));
+  return 0;
+}
 
 // K-slices of a dense launch: whole waves of (tile, slice) units over the SMs, each unit costing its slice's
 // super-blocks plus about two super-blocks' worth of pipeline fill and epilogue; slices are whole super-blocks.
@@ -230,7 +234,7 @@ __global__ void __launch_bounds__(128) k_pf_l2(float *__restrict__ y, int convd,
   *k = kv * (1.0f / (nk > eps ? nk : eps));
 }
 
-// The recurrence over the chunk's R rows.  grid (TR, 4), 128 threads, as k_delta_scan: block (hh, jq) keeps state rows
+// The recurrence over the chunk's R rows.  grid (TR, 4), 128 threads, as k_delta_fused: block (hh, jq) keeps state rows
 // 32 jq .. 32 jq + 31 of value head hh in registers (thread = row jr, column quarter cq) from the first row of the chunk
 // to the last and writes the state back once.  Rows come in batches of eight through double-buffered shared memory:
 // the next batch's q, k, v, beta and decay are requested before the current batch is computed.  Per row and state

@@ -20,6 +20,7 @@ struct PfArgs {
 
 
 int pf_setup(void);
+int pf_wait_errors_clear(void);
 int pf_wait_errors(void);                         // 1 when a bounded wait of the dense GEMM ran out
 int pf_pick_ksplit(int ntiles, int nsb, int sms);
 int pf_gemm(cudaStream_t s, int fmt, PfArgs &a);  // fills the tile table; a.ksplit <= K / 256

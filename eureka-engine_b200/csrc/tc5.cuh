@@ -51,8 +51,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar_s) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_s) : "memory");
 }
 // bounded wait for the phase with the given parity; false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(uint32_t bar_s, uint32_t parity) {
-  for (uint32_t it = 0; it < T5_WAIT_LIMIT; it++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar_s, uint32_t parity, uint32_t limit = T5_WAIT_LIMIT) {
+  for (uint32_t it = 0; it < limit; it++) {
     uint32_t ok;
     // the hint lets the hardware park the thread until the phase completes (or about a microsecond passes)
     // instead of polling: sixteen worker warps and four issuing warps otherwise spend most issue slots on polls

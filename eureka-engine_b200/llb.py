@@ -52,7 +52,7 @@ def lib() -> C.CDLL:
             "llb_b200_xp_new": (vp, [i32, i32, i32]), "llb_b200_xp_free": (None, [vp]),
             "llb_b200_xp_set_f32": (i32, [vp, u64]), "llb_b200_xp_set_bf16": (i32, [vp, u64]),
             "llb_b200_gemm": (i32, [i32, i32, C.POINTER(u64), C.POINTER(i32), C.POINTER(u64), i32, vp, i32]),
-            "llb_b200_wait_errors": (i32, []), "llb_b200_use_tcgen05": (i32, [i32]), "llb_b200_use_fused_ffn": (i32, [i32]),
+            "llb_b200_wait_errors": (i32, []), "llb_b200_wait_errors_clear": (i32, []), "llb_b200_wait_selftest": (i32, [i32, i32]), "llb_b200_use_tcgen05": (i32, [i32]), "llb_b200_use_fused_ffn": (i32, [i32]),
             "llb_b200_gemm_host": (i32, [i32, u64, i32, i32, vp, i32, vp, vp, u64, u64]),
             "llb_b200_gemm_noalloc": (i32, [i32, u64, i32, i32, u64, i32, u64]),
             "llb_spec_open": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32]),

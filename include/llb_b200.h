@@ -110,6 +110,14 @@ LLB_API int llb_b200_use_fused_ffn(int on);
 /* 1 when a bounded wait inside a kernel (an mbarrier of the tcgen05 GEMM, the fused FFN's grid barrier) has run out since
  * llb_b200_init: the results of that launch are not valid.  0 otherwise; -1 on a CUDA error. */
 LLB_API int llb_b200_wait_errors(void);
+/* Puts that status back to 0. */
+LLB_API int llb_b200_wait_errors_clear(void);
+/* Failure-detection check: one small launch whose only wait can never be satisfied -- which 0: an mbarrier nobody arrives
+ * on, waited for with the tcgen05 kernels' own bounded wait; which 1: the fused FFN's grid barrier told to expect a block
+ * that does not exist -- with a limit of `limit` tries (1..100000) instead of the kernels' 2^22.  The wait runs out, the
+ * kernel sets the status word and returns: afterwards llb_b200_wait_errors() is 1 and the device keeps working.  Returns 0
+ * when the launch completed. */
+LLB_API int llb_b200_wait_selftest(int which, int limit);
 /* The same through HOST buffers: bf16 x [T][K] in, f32 y [T][rows] out, copies included. */
 LLB_API int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const void *x_bf16, int T, float *y, llb_xp *xp,
                        llb_b200_dptr x_dev, llb_b200_dptr y_dev);

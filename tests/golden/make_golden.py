@@ -44,7 +44,8 @@ def random_blocks(fmt, rows, cols, seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("LLB_REFERENCE_ROOT"), required=not os.environ.get("LLB_REFERENCE_ROOT"),
+                    help="the reference tree (or LLB_REFERENCE_ROOT)")
     ap.add_argument("--skip-c0", action="store_true")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.ref, "tools"))

@@ -68,7 +68,8 @@ def write_gguf(path, pack, cfg):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("LLB_REFERENCE_ROOT"), required=not os.environ.get("LLB_REFERENCE_ROOT"),
+                    help="the reference tree (or LLB_REFERENCE_ROOT)")
     args = ap.parse_args()
     import __graft_entry__ as graft
     packs = graft.load_package().packs

@@ -74,3 +74,29 @@ def test_one_device_per_process(llb):
     assert L.llb_b200_init(0) == 0                          # the same device again: a no-op
     assert L.llb_b200_init(1) == -1
     assert b"already bound" in L.llb_b200_last_error()
+
+
+@pytest.mark.parametrize("which", [0, 1], ids=["mbarrier", "grid-barrier"])
+def test_a_bounded_wait_that_runs_out(llb, packs, oracle, dev, which):
+    """Failure detection without a fault: a launch whose only wait nothing can satisfy (an mbarrier nobody arrives on,
+    waited for with the tcgen05 kernels' bounded wait; the fused FFN's grid barrier told to expect a block that does
+    not exist) gives up after 2000 tries, sets the status word and returns.  The host reads 1, clears it, and the
+    device still computes: a dequantisation afterwards is bit-exact."""
+    L = llb.lib()
+    assert L.llb_b200_wait_errors() == 0
+    assert L.llb_b200_wait_selftest(which, 0) == -1 and b"limit" in L.llb_b200_last_error()
+    assert L.llb_b200_wait_selftest(which, 2000) == 0
+    assert L.llb_b200_wait_errors() == 1
+    assert L.llb_b200_wait_errors_clear() == 0
+    assert L.llb_b200_wait_errors() == 0
+    rows, cols, ty = 16, 512, "Q6_K"
+    fmt = packs.FMT[ty]
+    rng = np.random.default_rng(5)
+    raw = packs.QUANT[ty](torch.from_numpy(rng.standard_normal((rows, cols), dtype=np.float32) * 0.05)).numpy()
+    w = dev(L.llb_b200_weight_bytes(fmt, rows, cols))
+    llb.check(L.llb_b200_weight_upload(fmt, rows, cols, raw.ctypes.data, 0, w.ptr), "upload")
+    out = dev(rows * cols * 4)
+    llb.check(L.llb_b200_dequant(fmt, rows, cols, w.ptr, 0, rows, out.ptr), "dequant")
+    ref = oracle.Oracle.deq_rows(fmt, raw, rows, cols)
+    assert np.array_equal(out.read((rows, cols), np.float32).view(np.uint32), ref.view(np.uint32))
+    assert L.llb_b200_wait_errors() == 0
