@@ -138,10 +138,10 @@ int llb_b200_dequant(int fmt, int rows, int cols, llb_b200_dptr w, llb_b200_dptr
 
 llb_xp *llb_b200_xp_new(int K, int T, int planes) {
   NEED_INIT(nullptr)
-  if (K % 256 || T < 1 || (planes != 1 && planes != 2) || T * planes > 16) { llb_fail("xp_new: K %d T %d planes %d", K, T, planes); return nullptr; }
+  if (K % 256 || T < 1 || (planes != 1 && planes != 2) || T * planes > 32) { llb_fail("xp_new: K %d T %d planes %d", K, T, planes); return nullptr; }
   llb_xp *x = new llb_xp();
   x->T = T; x->planes = planes;
-  const int NC = T * planes <= 8 ? 8 : 16;
+  const int NC = T * planes <= 8 ? 8 : T * planes <= 16 ? 16 : 32;
   if (cudaMalloc(&x->base, xp_bytes(K, NC)) != cudaSuccess) { llb_fail("xp_new: out of memory"); delete x; return nullptr; }
   cudaMemsetAsync(x->base, 0, xp_bytes(K, NC), g_llb.stream);
   x->p = xp_carve(x->base, K, NC);

@@ -24,7 +24,7 @@ template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs 
   // every SM takes part as long as there is a tile for it: the tiles are dealt out one per CTA in turn
   constexpr int G2_WARPS = G2Traits<FMT>::WARPS;
   if (cps > a.tile0[a.nmat]) cps = a.tile0[a.nmat];
-  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
+  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>(NC);
   if (smem > G2_SMEM_MAX) return llb_fail("k_gemm2: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
   cudaError_t e = llb_launch(k_gemm2<FMT, NT>, dim3(cps * a.ksplit), dim3(G2_WARPS * 32), smem, s, a, cps);
   if (e != cudaSuccess) return llb_fail("k_gemm2 launch: %s", cudaGetErrorString(e));
@@ -90,6 +90,7 @@ int gemm_wait_selftest(cudaStream_t s, int which, int limit) {
 template <int FMT> static int setup_fmt2() {
   CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_gemm2<FMT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   return 0;
 }
 
@@ -181,7 +182,7 @@ int gemm_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_pf, int s
 static int gemm_prepare(int fmt, GemmArgs &a) {
   if (a.nmat < 1 || a.nmat > GEMM_MAXMAT) return llb_fail("gemm: nmat %d", a.nmat);
   if (a.K % 256) return llb_fail("gemm: K %d is not a multiple of 256", a.K);
-  if (a.xp.NC != 8 && a.xp.NC != 16) return llb_fail("gemm: NC %d", a.xp.NC);
+  if (a.xp.NC != 8 && a.xp.NC != 16 && a.xp.NC != 32) return llb_fail("gemm: NC %d", a.xp.NC);
   if (a.xp.K != a.K) return llb_fail("gemm: planes hold %d columns, K is %d", a.xp.K, a.K);
   a.nsb = a.K / 256;
   a.tile0[0] = 0;
@@ -231,7 +232,7 @@ template <int FMT, int NT> static int launch_moe(cudaStream_t s, bool down, cons
   int cps = g_llb.sms * G2_CPSM / a.ksplit;
   if (cps < 1) cps = 1;
   if (cps > ntiles) cps = ntiles;
-  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>();
+  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>(NC);
   if (smem > G2_SMEM_MAX) return llb_fail("moe gemm: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
   cudaError_t e;
   if (down && wt_silu) {
@@ -263,6 +264,7 @@ int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeAr
   a.ksplit = ks;
   if (ksplit) *ksplit = ks;
   const int NT = xp.NC / 8;
+  if (NT > 2) return llb_fail("moe gemm: at most 8 rows per pass (%d plane columns asked for)", xp.NC);
 #define MOE_GO(F) return NT == 1 ? launch_moe<F, 1>(s, down, a, m, ntiles, wt_silu) : launch_moe<F, 2>(s, down, a, m, ntiles, wt_silu)
   if (fmt == LLB_FM_Q4_K) MOE_GO(LLB_FM_Q4_K);
   if (fmt == LLB_FM_Q5_K) MOE_GO(LLB_FM_Q5_K);
@@ -275,9 +277,9 @@ int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a) {
   if (a.tile0[a.nmat] < 1) return 0;
   const int NT = a.xp.NC / 8;
   if (is_g3(fmt, a.xp.NC)) return launch_three(s, a);
-  if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : launch_two<LLB_FM_Q4_K, 2>(s, a);
-  if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : launch_two<LLB_FM_Q5_K, 2>(s, a);
-  if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_two<LLB_FM_Q6_K, 1>(s, a) : launch_two<LLB_FM_Q6_K, 2>(s, a);
-  if (fmt == LLB_FM_Q8_0) return NT == 1 ? launch_two<LLB_FM_Q8_0, 1>(s, a) : launch_two<LLB_FM_Q8_0, 2>(s, a);
+  if (fmt == LLB_FM_Q4_K) return NT == 1 ? launch_two<LLB_FM_Q4_K, 1>(s, a) : NT == 2 ? launch_two<LLB_FM_Q4_K, 2>(s, a) : launch_two<LLB_FM_Q4_K, 4>(s, a);
+  if (fmt == LLB_FM_Q5_K) return NT == 1 ? launch_two<LLB_FM_Q5_K, 1>(s, a) : NT == 2 ? launch_two<LLB_FM_Q5_K, 2>(s, a) : launch_two<LLB_FM_Q5_K, 4>(s, a);
+  if (fmt == LLB_FM_Q6_K) return NT == 1 ? launch_two<LLB_FM_Q6_K, 1>(s, a) : NT == 2 ? launch_two<LLB_FM_Q6_K, 2>(s, a) : launch_two<LLB_FM_Q6_K, 4>(s, a);
+  if (fmt == LLB_FM_Q8_0) return NT == 1 ? launch_two<LLB_FM_Q8_0, 1>(s, a) : NT == 2 ? launch_two<LLB_FM_Q8_0, 2>(s, a) : launch_two<LLB_FM_Q8_0, 4>(s, a);
   return llb_fail("gemm: format %d has no kernel", fmt);
 }

@@ -41,13 +41,16 @@ template <> struct G2Traits<LLB_FM_Q6_K> { enum { SB = 224, RS = 240, P = 14, QO
 // bytes further on in the row; piece 16 of a row-super-block is that scale piece (copy plan below).  AUX: 8 f32 sums of 32 columns.
 template <> struct G2Traits<LLB_FM_Q8_0> { enum { SB = 256, RS = 304, P = 17, QOFF = 0, WARPS = 8 / G2_CPSM, XPAD = 32, AUX = 32 }; };
 
-template <int FMT> constexpr int g2_ring_bytes() { return G2Traits<FMT>::WARPS * G2_STAGES * 16 * G2Traits<FMT>::RS; }
+// ring depth: three stages; two for Q5_K and Q6_K at 32 plane columns (16 rows), whose 224- and 240-byte rows would
+// otherwise leave the activation slice too little shared memory for a K of 17408 to split 16 ways
+template <int FMT> __host__ __device__ constexpr int g2_stages(int NC) { return ((FMT == LLB_FM_Q6_K || FMT == LLB_FM_Q5_K) && NC >= 32) ? 2 : G2_STAGES; }
+template <int FMT> __host__ __device__ constexpr int g2_ring_bytes(int NC) { return G2Traits<FMT>::WARPS * g2_stages<FMT>(NC) * 16 * G2Traits<FMT>::RS; }
 // bytes of shared memory a K-slice of nsl super-blocks needs for NC activation columns
 template <int FMT> __host__ __device__ inline int g2_xp_bytes(int nsl, int NC) {
   return NC * (nsl * 512 + G2Traits<FMT>::XPAD) + nsl * NC * G2Traits<FMT>::AUX;
 }
 template <int FMT> inline int g2_max_slice_sb(int NC) {
-  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>() - NC * G2Traits<FMT>::XPAD;
+  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>(NC) - NC * G2Traits<FMT>::XPAD;
   return left / (NC * 512 + NC * G2Traits<FMT>::AUX);
 }
 
@@ -93,13 +96,13 @@ template <int FMT> struct G2MatsPlain {
 template <int FMT, int NT, class Stage, class Mats>
 __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage, const Mats mats) {
   using TR = G2Traits<FMT>;
-  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = TR::WARPS;
+  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = TR::WARPS, ST = g2_stages<FMT>(8 * NT);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
   const bool live = bid < cps * a.ksplit && warp < G2_WARPS;
   const int ks = bid % a.ksplit, ci = bid / a.ksplit;
   const int sb0 = (int)(((long long)ks * a.nsb) / a.ksplit), nsl = (int)(((long long)(ks + 1) * a.nsb) / a.ksplit) - sb0;
   const int CS = nsl * 512 + TR::XPAD;
-  uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * TR::AUX + (size_t)warp * G2_STAGES * 16 * RS;
+  uint8_t *xh_s = smem, *xsf_s = smem + NC * CS, *ring = xsf_s + nsl * NC * TR::AUX + (size_t)warp * ST * 16 * RS;
   const uint32_t ring_s = smem_u32(ring);
   int ntiles = live && Mats::EARLY ? mats.ntiles() : 0;   // a warp that is not live sees no tiles
   const int nws = cps * G2_WARPS;
@@ -151,7 +154,7 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
     // weights first: the ring's prologue is in flight while the producer of the activations still
     // runs (weights depend on no kernel), and while the activation slice is staged
 #pragma unroll 1
-    for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
+    for (int s = 0; s < ST - 1; s++) issue(s);
     stage(xh_s, xsf_s, CS, sb0, nsl);
   } else {
     // the weight addresses come from an earlier kernel's choice: the wait (inside stage) comes first
@@ -159,11 +162,11 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
     ntiles = live ? mats.ntiles() : 0;
     plan_tile(p_tile);
 #pragma unroll 1
-    for (int s = 0; s < G2_STAGES - 1; s++) issue(s);
+    for (int s = 0; s < ST - 1; s++) issue(s);
   }
   // the XP group sits between prologue groups and later ones; from here on group accounting is per
-  // warp again: G2_STAGES-1 chunks are complete, none pending
-  int pstage = G2_STAGES - 1, cstage = 0;
+  // warp again: ST-1 chunks are complete, none pending
+  int pstage = ST - 1, cstage = 0;
   int c_tile = warp * cps + ci, c_c = 0;
   float acc[NT][4];
   const uint8_t *xb = xh_s + gid * CS + 16 * j;          // B fragments of column gid (n-tile 0)
@@ -176,8 +179,8 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
       for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
     }
     issue(pstage);                       // refill the stage consumed last iteration
-    pstage = pstage + 1 == G2_STAGES ? 0 : pstage + 1;
-    cp_async_wait<G2_STAGES - 1>();      // all but the newest G2_STAGES-1 groups: the stage to consume is in
+    pstage = pstage + 1 == ST ? 0 : pstage + 1;
+    cp_async_wait<ST - 1>();             // all but the newest ST-1 groups: the stage to consume is in
     __syncwarp();
     if constexpr (FMT == LLB_FM_Q8_0) {
       // eight blocks of 32 codes per super-block, two MMAs each; code (q ^ 0x80) = q + 128 as an fp16 subnormal,
@@ -326,7 +329,7 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
       }
     }
     __syncwarp();
-    cstage = cstage + 1 == G2_STAGES ? 0 : cstage + 1;
+    cstage = cstage + 1 == ST ? 0 : cstage + 1;
     if (++c_c == nsl) {
       mats.template epilogue<NT>(ks, c_tile, acc, lane);
       c_c = 0;

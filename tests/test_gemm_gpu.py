@@ -97,9 +97,17 @@ def test_gemm_ragged_rows_and_cat(llb, packs, oracle, dev, ty):
 
 
 @pytest.mark.parametrize("ty", FMTS)
-@pytest.mark.parametrize("T,planes", [(1, 2), (2, 2), (3, 2), (6, 2), (8, 2), (1, 1), (8, 1), (16, 1)])
+@pytest.mark.parametrize("T,planes", [(1, 2), (2, 2), (3, 2), (6, 2), (8, 2), (9, 2), (12, 2), (16, 2), (1, 1), (8, 1), (16, 1), (32, 1)])
 def test_gemm_row_counts(llb, packs, oracle, dev, ty, T, planes):
     _gemm_case(llb, packs, oracle, dev, ty, [64], 1536, T, planes, 0, seed=T + planes)
+
+
+@pytest.mark.parametrize("ty", FMTS)
+def test_gemm_sixteen_rows_long_k(llb, packs, oracle, dev, ty):
+    """Sixteen rows (the rows of several streams in one pass, 32 plane columns) at the 27B shape's widest K: the
+    activation slice a CTA can stage is small there, so K splits 12 to 16 ways (Q6_K on a two-stage ring)."""
+    _gemm_case(llb, packs, oracle, dev, ty, [48, 16], 17408, 16, 2, 0, seed=21)
+    _gemm_case(llb, packs, oracle, dev, ty, [33], 5120, 13, 2, 0, seed=22)
 
 
 def test_gemm_many_tiles(llb, packs, oracle, dev):
@@ -132,6 +140,29 @@ def _column_independence(llb, packs, dev):
         ys.append(o.read((T, rows), np.float32))
         L.llb_b200_xp_free(xp)
     assert np.array_equal(ys[0][2].view(np.uint32), ys[1][0].view(np.uint32))
+
+
+@pytest.mark.parametrize("ty", FMTS)
+def test_row_independence_at_sixteen_rows(llb, packs, dev, ty):
+    """A row's result does not depend on which other rows share the launch nor on its place among them: what lets
+    several streams be verified in one pass with each stream's tokens bit-identical to the stream run alone."""
+    L = llb.lib()
+    rows, K = 96, 2560
+    raw = _random_raw(packs, ty, rows, K, 31)
+    w = _upload(llb, packs, dev, ty, raw, rows, K)
+    rng = np.random.default_rng(2)
+    xa, xb = rng.standard_normal((16, K), dtype=np.float32), rng.standard_normal((16, K), dtype=np.float32)
+    xb[3] = xa[9]
+    ys = []
+    for xs in (xa, xb):
+        xd = dev(16 * K * 4).write(xs)
+        xp = llb.handle(L.llb_b200_xp_new(K, 16, 2), "xp_new")
+        llb.check(L.llb_b200_xp_set_f32(xp, xd.ptr), "xp_set")
+        o = dev(16 * rows * 4)
+        llb.gemm(packs.FMT[ty], [w.ptr], [rows], [o.ptr], K, xp, 0)
+        ys.append(o.read((16, rows), np.float32))
+        L.llb_b200_xp_free(xp)
+    assert np.array_equal(ys[0][9].view(np.uint32), ys[1][3].view(np.uint32))
 
 
 @pytest.fixture
