@@ -48,11 +48,13 @@ template <int HD, int NQG>
 __global__ void __launch_bounds__(256) k_attn_mma(const float *__restrict__ q, const __half *__restrict__ Kc, const __half *__restrict__ Vc,
                                                   AttnShape sh, int Tmax, float *__restrict__ pm, float *__restrict__ pl,
                                                   float *__restrict__ po, const RowSet *rs) {
-  // blockIdx.z: one of several row groups of a prompt chunk, each with its own row set, Tmax query rows and partial results
+  // blockIdx.z: one of several row groups -- the groups of a prompt chunk, which share a cache, or the streams of a pass,
+  // each with its own -- each with its own row set, Tmax query rows and partial results
   {
     const size_t z = blockIdx.z, per = (size_t)sh.H * Tmax * gridDim.y;
-    rs = (const RowSet *)((uintptr_t)rs + z * sizeof(RowSet));
+    rs = (const RowSet *)((uintptr_t)rs + z * sh.rs_stride);
     q += z * Tmax * sh.H * HD; pm += z * per; pl += z * per; po += z * per * HD;
+    Kc += z * sh.kv_group; Vc += z * sh.kv_group;
   }
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
@@ -233,11 +235,12 @@ __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm,
                                                    AttnShape sh, int nsplit, int Tmax, XPlanes xp, const RowSet *rs, __half *__restrict__ kg, int kg_row0) {
   {
     const size_t z = blockIdx.z, per = (size_t)sh.H * Tmax * nsplit;
-    rs = (const RowSet *)((uintptr_t)rs + z * sizeof(RowSet));
+    rs = (const RowSet *)((uintptr_t)rs + z * sh.rs_stride);
     pm += z * per; pl += z * per; po += z * per * sh.hd;
     qg.p += z * Tmax * 2 * sh.H * sh.hd;
     kg_row0 += (int)z * Tmax;
   }
+  const int xrow0 = blockIdx.z * Tmax;   // the group's rows in the planes
   int rs_n, rs_p0;
   rs = rs_begin(rs, rs_n, rs_p0);
   __shared__ float wsm[128];
@@ -292,7 +295,7 @@ __global__ void __launch_bounds__(256) k_attn_comb(const float *__restrict__ pm,
                          (a.w / L) / (1.0f + expf(-gate.w))};
     // the prompt path takes the rows as fp16 in the dense GEMM's k-group-major order instead of the T-row planes
     if (kg) pf_kg_store4(kg, sh.H * hd, kg_row0 + t, h * hd + 4 * i, hv[0], hv[1], hv[2], hv[3]);
-    else xp_store4(xp, t, 2, h * hd + 4 * i, hv, lane, true);
+    else xp_store4(xp, xrow0 + t, 2, h * hd + 4 * i, hv, lane, true);
   }
 }
 

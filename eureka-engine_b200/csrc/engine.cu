@@ -50,6 +50,20 @@ struct PfState {
   int *ids = nullptr;      // the chunk's tokens
 };
 
+// host mirror of one stream (sequence): where it is, what it reported last, and its statistics
+struct SeqHost {
+  unsigned long long seq = 0;
+  int pos = 0;            // position of the next cycle's row 0
+  int last_tok = -1;      // the committed token of the next cycle
+  bool primed = false;    // prefill done
+  // reference-shaped row serving (llb_spec_pass)
+  SpecResult last;
+  int last_served_idx = 0;
+  bool have_last = false;
+  // statistics, as the reference's "spec:" line (host/llb_host.c:1513-1523)
+  unsigned long long cycles = 0, rows = 0, served = 0, drafted[8] = {0}, accepted[8] = {0};
+};
+
 struct llb_spec {
   // configuration (index.tsv #cfg keys, tools/qwen35_engine.c:386-409)
   int L = 0, d = 0, H = 0, KV = 0, hd = 0, f = 0, V = 0, interval = 4, KC = 4, SZ = 128, GK = 0, TR = 0, vdc = 0, kdc = 0,
@@ -61,11 +75,17 @@ struct llb_spec {
   XPlanes xp_e;
   size_t pack_bytes = 0;   // size of the pack the index describes: every tensor range is checked against it
   int k = 0, Tmax = 1, R = 2, max_ctx = 0, NC = 8;   // Tmax / NC: rows and plane columns of the pass being enqueued
+  // Several streams (sequences) per engine share every weight read: a pass has B x per rows, row t belonging to stream
+  // t / per; every piece of per-sequence state below is B copies one after the other, and the control blocks, result
+  // rings and host mirrors are arrays of B.  B = 1: per = the pass's width, as before.
+  int B = 1, per = 1;
+  long long kv_group = 0, s_group = 0, ring_group_unit = 0;   // halves between the streams' K (V) caches; floats between their state rings
+  int *const_rows = nullptr;   // device word holding B x per (the routed-expert launches' row count in a multi-stream pass)
   // A speculative pass has k + 1 rows; a prompt chunk has Tpf rows (8 where the attention kernel's query budget allows:
   // the weights stream once per pass whatever its rows, so a wider chunk halves the prompt's time).  The two widths
   // share every buffer; the planes have one view per column count.
   int Tspec = 1, Tpf = 1;
-  XPlanes xpv[2][6];   // [NC == 16][xp_d, xp_f, xp_qa, xp_v, xp_2d, xp_e]
+  XPlanes xpv[3][6];   // [NC 8 / 16 / 32][xp_d, xp_f, xp_qa, xp_v, xp_2d, xp_e]
   // weights
   std::vector<void *> allocs;
   std::vector<LayerW> layer;
@@ -110,17 +130,21 @@ struct llb_spec {
   // graphs
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
   size_t n_spec_nodes = 0, n_verify_nodes = 0;
-  int last_tok = -1;      // the committed token of the next cycle (host mirror)
-  // host mirror
-  unsigned long long seq = 0;
-  int pos = 0;            // position of the next cycle's row 0
-  bool primed = false;    // prefill done
-  // reference-shaped row serving (llb_spec_pass)
-  SpecResult last;
-  int last_served_idx = 0;
-  bool have_last = false;
-  // statistics, as the reference's "spec:" line (host/llb_host.c:1513-1523)
-  unsigned long long cycles = 0, rows = 0, served = 0, drafted[8] = {0}, accepted[8] = {0};
+  std::vector<SeqHost> sq;   // one per stream
+};
+// the streams' copies of per-sequence device state
+static inline SpecCtl *ctl_of(const llb_spec *m, int b) { return m->ctl + b; }
+static inline float *kc_of(const llb_spec *m, float *base, int b) { return base ? (float *)((__half *)base + (size_t)b * m->kv_group) : nullptr; }
+static inline float *ring_of(const llb_spec *m, int il, int b) { return m->ring[il] + (size_t)b * m->ring_ks[il] * CONV_RING * m->convd; }
+static inline float *state_of(const llb_spec *m, int il, int b) { return m->S[il] + (size_t)b * m->s_group; }
+static inline int *hist_of(const llb_spec *m, int b) { return m->hist ? m->hist + (size_t)b * (m->max_ctx + 16) : nullptr; }
+// the launchers' stream geometry while this engine enqueues (engines of different shapes may coexist)
+struct StreamScope {
+  Streams was;
+  explicit StreamScope(const llb_spec *m, bool single = false) : was(ops_streams()) {
+    if (m->B > 1 && !single) ops_set_streams(m->Tspec, (int)sizeof(SpecCtl)); else ops_set_streams(0, 0);
+  }
+  ~StreamScope() { ops_set_streams(was.per, was.stride); }
 };
 
 #define CK(call) do { if ((call)) return -1; } while (0)
@@ -149,18 +173,23 @@ static void *dalloc(llb_spec *m, size_t bytes) {
   return p;
 }
 static float *falloc(llb_spec *m, size_t n) { return (float *)dalloc(m, n * 4); }
+// plane columns of a pass of T rows (hi and lo halves): 8, 16 or 32
+static int nc_of(int T) { return T <= 4 ? 8 : T <= 8 ? 16 : 32; }
+static int rows_cap(const llb_spec *m) { const int a = m->B * m->Tspec, b = m->Tpf; return a > b ? a : b; }
 static int xp_alloc(llb_spec *m, int which, int K) {
-  const int ncmax = (m->Tspec > 4 || m->Tpf > 4) ? 16 : 8;
+  const int ncmax = nc_of(rows_cap(m));
   void *b = dalloc(m, xp_bytes(K, ncmax));
   if (!b) return -1;
   m->xpv[0][which] = xp_carve(b, K, 8);
-  m->xpv[1][which] = xp_carve(b, K, ncmax);
+  m->xpv[1][which] = xp_carve(b, K, ncmax < 16 ? ncmax : 16);
+  m->xpv[2][which] = xp_carve(b, K, ncmax);
   return 0;
 }
-// the width of the passes enqueued from here on
+// the width of the passes enqueued from here on: T rows in all, `per` of them to a stream
 static void set_width(llb_spec *m, int T) {
-  m->Tmax = T; m->NC = T <= 4 ? 8 : 16;
-  const XPlanes *v = m->xpv[m->NC == 16];
+  m->Tmax = T; m->NC = nc_of(T);
+  m->per = m->B > 1 ? m->Tspec : T;
+  const XPlanes *v = m->xpv[m->NC == 8 ? 0 : m->NC == 16 ? 1 : 2];
   m->xp_d = v[0]; m->xp_f = v[1]; m->xp_qa = v[2]; m->xp_v = v[3]; m->xp_2d = v[4]; m->xp_e = v[5];
 }
 
@@ -435,6 +464,9 @@ static int site_gemm(llb_spec *m, std::vector<SiteMat> mats, const XPlanes &xp, 
     for (size_t g = 0; g < grp.size(); g++) {
       SiteMat &sm = mats[grp[g]];
       a.m[g].W = sm.w->w; a.m[g].rows = sm.w->rows; a.m[g].tok_slot = sm.tok_slot;
+      if (sm.tok_slot && m->B > 1) {   // every stream's rows go to that stream's ring, by that stream's slot numbers
+        a.m[g].tok_per = m->per; a.m[g].tok_stride = (int)(sizeof(SpecCtl) / 4); a.m[g].tok_add = sm.direct_splits * CONV_RING;
+      }
       if (sm.direct) {
         if (ks > sm.direct_splits) return llb_fail("gemm site: %d K-slices, the direct output holds %d", ks, sm.direct_splits);
         a.m[g].out = sm.direct; a.m[g].ostride = sm.direct_stride; a.m[g].split_stride = sm.direct_split_stride;
@@ -473,10 +505,11 @@ static PartIn in_dn(const llb_spec *m) { return m->tp.size > 1 ? as_in(m->r_dn) 
 // full attention block on rows `rs`: planes xp_d hold the normed input; result partial sums in b_a
 static int enq_attn(llb_spec *m, const AttnW &w, float *Kc, float *Vc, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
-  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd};
+  AttnShape sh{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd,
+               m->B > 1 ? (int)sizeof(SpecCtl) : 0, m->B > 1 ? m->kv_group : 0};
   PK("gemm qkv", site_gemm(m, {{&w.q, &m->b_q, nullptr, nullptr, 0}, {&w.k, &m->b_k, nullptr, nullptr, 0}, {&w.v, &m->b_v, nullptr, nullptr, 0}}, m->xp_d, 0));
   PK("qkrope", op_qkrope(s, as_in(m->b_q), as_in(m->b_k), as_in(m->b_v), w.qn, w.kn, m->invfreq, sh, m->qn, Kc, Vc, rs, m->Tmax));
-  PK("attention", op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->Tmax));
+  PK("attention", op_attention(s, m->qn, Kc, Vc, as_in(m->b_q), sh, m->att_split, m->pm, m->pl, m->po, m->xp_qa, rs, m->per, nullptr, 0, m->B));
   PK("gemm attn_out", site_gemm(m, {{&w.o, &m->b_a, nullptr, nullptr, 0}}, m->xp_qa, 0));
   PK("all-reduce", tp_reduce(m, m->b_a, m->r_a));
   return 0;
@@ -496,7 +529,7 @@ static int enq_moe_ffn(llb_spec *m, const FfnW &w, const float *xin, float *x1, 
 static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs) {
   cudaStream_t s = g_llb.stream;
   const int ns = m->nk + 1, fe = ns * m->ef;
-  const int *n_rows = &((const RowSet *)((uintptr_t)rs & ~(uintptr_t)1))->n;
+  const int *n_rows = m->B > 1 ? m->const_rows : &((const RowSet *)((uintptr_t)rs & ~(uintptr_t)1))->n;
   PK("moe route", op_moe_route(s, w.router, m->hn2, m->d, m->ne, m->nk, m->moe_lg, m->moe_ids, m->moe_wt, rs, m->Tmax));
   MoeArgs a;
   memset(&a, 0, sizeof a);
@@ -549,7 +582,7 @@ static int enq_delta(llb_spec *m, const DeltaW &w, float *ring, int ring_ks, flo
                    {&w.z, &m->b_z, nullptr, nullptr, 0}, {&w.beta, &m->b_bp, nullptr, nullptr, 0}, {&w.alpha, &m->b_ap, nullptr, nullptr, 0}},
                m->xp_d, 0));
   PK("delta conv", op_delta_conv(s, as_in(m->b_ring), w.conv, as_in(m->b_bp), as_in(m->b_ap), w.dt, w.a, sh, m->y, m->beta, m->decay, rs, m->Tmax));
-  PK("delta scan+gnorm", op_delta_fused(s, S, m->ctl, m->y, m->beta, m->decay, as_in(m->b_z), w.norm, sh, m->xp_v, rs));
+  PK("delta scan+gnorm", op_delta_fused(s, S, m->ctl, m->y, m->beta, m->decay, as_in(m->b_z), w.norm, sh, m->xp_v, rs, m->B, m->s_group));
   PK("gemm ssm_out", site_gemm(m, {{&w.out, &m->b_a, nullptr, nullptr, 0}}, m->xp_v, 0));
   PK("all-reduce", tp_reduce(m, m->b_a, m->r_a));
   return 0;
@@ -578,6 +611,8 @@ static int enq_verify(llb_spec *m) {
   return 0;
 }
 
+// where the drafter's top-2 partials start in t2part (the trunk's come first)
+static size_t t2_mtp(const llb_spec *m) { const int r = rows_cap(m); return (size_t)(r > SPEC_MAXT ? r : SPEC_MAXT) * TOP2_NB * 4; }
 // the drafter's NextN block over rows `rs` with hidden rows `h` (mtp_rows, host/llb_host.c:1775-1808)
 static int enq_mtp(llb_spec *m, const RowSet *rs, const float *h, bool with_head, int zero_h_at_pos0) {
   cudaStream_t s = g_llb.stream;
@@ -593,7 +628,7 @@ static int enq_mtp(llb_spec *m, const RowSet *rs, const float *h, bool with_head
   CK(op_norm_xp(s, m->x1, in_dn(m), m->mt_shn, m->eps, m->d, nullptr, m->xp_d, 0, m->mt_hn, rs, m->Tmax, 0));
   if (with_head) {
     CK(site_gemm(m, {{&m->mt_head, &m->b_mlg, nullptr, nullptr, 0}}, m->xp_d, 0));
-    CK(op_top2_part(s, as_in(m->b_mlg), m->mt_nv, m->mt_nv, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, rs, m->Tmax));
+    CK(op_top2_part(s, as_in(m->b_mlg), m->mt_nv, m->mt_nv, m->t2part + t2_mtp(m), rs, m->Tmax));
   }
   return 0;
 }
@@ -606,14 +641,14 @@ static int enq_cycle(llb_spec *m, bool spec) {
     CK(enq_mtp(m, &m->ctl->catchup, m->hn, spec && m->k > 0, 0));
     if (spec) {
       for (int j = 1; j <= m->k; j++) {
-        CK(op_draft_pick(s, m->t2part + (size_t)SPEC_MAXT * TOP2_NB * 4, m->mt_ids, m->ctl, j > 1, j, m->mt_hn, m->chain_h, m->d));
+        CK(op_draft_pick(s, m->t2part + t2_mtp(m), m->mt_ids, m->ctl, j > 1, j, m->mt_hn, m->chain_h, m->d, m->B, m->B > 1 ? m->per : 0));
         if (j < m->k) CK(enq_mtp(m, &m->ctl->chain, m->chain_h, true, 0));
       }
     }
   }
   CK(enq_verify(m));
-  CK(op_accept(s, m->t2part, m->ctl, m->res_dev, m->res_n, m->Tmax));
-  if (m->lookup) CK(op_lookup_draft(s, m->ctl));   // the next cycle's drafts, from the history the accept kernel extended
+  CK(op_accept(s, m->t2part, m->ctl, m->res_dev, m->res_n, m->Tmax, m->B, m->B > 1 ? m->per : 0));
+  if (m->lookup) CK(op_lookup_draft(s, m->ctl, m->B));   // the next cycle's drafts, from the history the accept kernel extended
   return 0;
 }
 
@@ -623,6 +658,7 @@ static int capture(llb_spec *m, int which, cudaGraphExec_t *out, size_t *nodes) 
   cudaStream_t s = g_llb.stream;
   cudaGraph_t g = nullptr;
   CU_OK(cudaStreamSynchronize(s));
+  StreamScope scope(m);
   CU_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
   int rc = which == 2 ? enq_verify(m) : enq_cycle(m, which == 0);
   cudaError_t e = cudaStreamEndCapture(s, &g);
@@ -637,7 +673,7 @@ static int capture(llb_spec *m, int which, cudaGraphExec_t *out, size_t *nodes) 
 
 // ---- open ---------------------------------------------------------------------------------------
 static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, int on_device, const uint8_t *mtp, size_t mtp_bytes,
-                     int mtp_on_device, int k, int max_ctx, int layers, int tp_n) {
+                     int mtp_on_device, int k, int max_ctx, int layers, int tp_n, int nstreams) {
   std::unordered_map<std::string, TensorRec> tab;
   CK(parse_index(m, index_text, tab));
   CK(validate_index(m, tab, m->pack_bytes));
@@ -704,6 +740,15 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   };
   { const char *e = getenv("LLB_PREFILL"); m->prefill_mode = e && !strcmp(e, "fast"); }   // the reference's switch (host/llb_host.c:206)
   m->k = k; m->Tspec = k + 1; m->max_ctx = max_ctx;
+  if (nstreams < 1 || nstreams > 16) return llb_fail("streams: %d (1..16 per engine)", nstreams);
+  m->B = nstreams;
+  if (m->B > 1) {
+    // the rows of all streams go through every GEMM together: 16 rows at most (32 plane columns), 8 with routed experts
+    const int cap = m->ne > 0 ? 8 : 16;
+    if (m->B * m->Tspec > cap) return llb_fail("streams: %d streams of k + 1 = %d rows are %d rows a pass, the limit is %d", m->B, m->Tspec, m->B * m->Tspec, cap);
+    if (tp_on) return llb_fail("streams: a tensor-parallel engine runs one stream");
+  }
+  m->sq.assign(m->B, SeqHost());
   {
     // rows of a prompt chunk: 8, fewer where (H / KV) x rows would pass the attention kernel's 48 queries per kv head
     int pf = 8;
@@ -711,11 +756,15 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     if (e && atoi(e) >= 1 && atoi(e) <= SPEC_MAXT) pf = atoi(e);
     if (pf > 48 / (m->H / m->KV)) pf = 48 / (m->H / m->KV);
     m->Tpf = pf > m->Tspec ? pf : m->Tspec;
+    if (m->B > 1) m->Tpf = m->Tspec;     // several streams: a stream's prompt chunk is as wide as its speculative pass
   }
-  m->Tmax = m->Tpf;                      // buffers are sized for the wider pass
-  m->R = m->Tmax + 1;                    // state-ring slots: rows + 1 (k + 2 in the reference, host/llb_host.c:1621)
-  m->NC = m->Tmax <= 4 ? 8 : 16;
-  const int d = m->d, qa = m->H * m->hd, kvd = m->KV * m->hd, T = m->Tmax;
+  m->per = m->Tpf;
+  m->Tmax = rows_cap(m);                 // buffers are sized for the widest pass
+  m->R = m->Tpf + 1;                     // state-ring slots: a stream's rows + 1 (k + 2 in the reference, host/llb_host.c:1621)
+  m->NC = nc_of(m->Tmax);
+  const int d = m->d, qa = m->H * m->hd, kvd = m->KV * m->hd, T = m->Tmax, B = m->B;
+  m->kv_group = 2LL * max_ctx * kvd;
+  m->s_group = (long long)m->R * m->TR * m->SZ * m->SZ;
   std::unordered_map<uint64_t, void *> dedupe;
   auto mat = [&](const std::string &name, DevMat &w) -> int {
     auto it = tab.find(name);
@@ -754,7 +803,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
       CK(mat(p + "attn_output.weight", l.at.o)); CK(check_k(l.at.o, d, qa, "attn_output"));
       CK(vec(p + "attn_q_norm.weight", &l.at.qn, m->hd));
       CK(vec(p + "attn_k_norm.weight", &l.at.kn, m->hd));
-      m->Kc[il] = falloc(m, (size_t)max_ctx * kvd); m->Vc[il] = falloc(m, (size_t)max_ctx * kvd);
+      m->Kc[il] = falloc(m, (size_t)B * max_ctx * kvd); m->Vc[il] = falloc(m, (size_t)B * max_ctx * kvd);
       if (!m->Kc[il] || !m->Vc[il]) return -1;
     } else {
       CK(mat(p + "attn_qkv.weight", l.dn.qkv)); CK(check_k(l.dn.qkv, m->convd, d, "attn_qkv"));
@@ -770,12 +819,12 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
         // the launch attn_qkv lands in: the matrices of its format among qkv | z | beta | alpha
         int ntiles = 0;
         for (const DevMat *w : {&l.dn.qkv, &l.dn.z, &l.dn.beta, &l.dn.alpha}) if (w->fmt == l.dn.qkv.fmt) ntiles += (w->rows + 15) / 16;
-        const int ks = gemm_ring_ksplit(l.dn.qkv.fmt, d / 256, ntiles, m->Tspec <= 4 ? 8 : 16, m->Tpf <= 4 ? 8 : 16, g_llb.sms, RING_MAXSPLIT);
+        const int ks = gemm_ring_ksplit(l.dn.qkv.fmt, d / 256, ntiles, nc_of(B * m->Tspec), nc_of(B > 1 ? B * m->Tspec : m->Tpf), g_llb.sms, RING_MAXSPLIT);
         if (ks < 1) return llb_fail("blk.%d.attn_qkv: %d columns need more than %d K-slices at a pass width in use", il, d, RING_MAXSPLIT);
         m->ring_ks[il] = ks;
       }
-      m->ring[il] = falloc(m, (size_t)m->ring_ks[il] * CONV_RING * m->convd);
-      m->S[il] = falloc(m, (size_t)m->R * m->TR * m->SZ * m->SZ);
+      m->ring[il] = falloc(m, (size_t)B * m->ring_ks[il] * CONV_RING * m->convd);
+      m->S[il] = falloc(m, (size_t)B * m->s_group);
       if (!m->ring[il] || !m->S[il]) return -1;
     }
     CK(vec(p + "post_attention_norm.weight", &l.ffn.post, d));
@@ -850,7 +899,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     m->mt_at.o = MM(9); m->mt_ffn.post = (float *)ptr[10]; m->mt_ffn.gate = MM(11); m->mt_ffn.up = MM(12); m->mt_ffn.down = MM(13);
     m->mt_shn = (float *)ptr[14]; m->mt_head = MM(15); m->mt_ids = (int *)ptr[16]; m->mt_nv = nv;
     CK(check_k(m->mt_eh, d, 2 * d, "nextn.eh_proj")); CK(check_k(m->mt_head, nv, d, "mtp.head_slice"));
-    m->mt_Kc = falloc(m, (size_t)max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)max_ctx * kvd);
+    m->mt_Kc = falloc(m, (size_t)B * max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)B * max_ctx * kvd);
     if (!m->mt_Kc || !m->mt_Vc) return -1;
     m->has_mtp = true;
   } else if (k > 0 && m->ne == 0 && tab.count("blk." + std::to_string(L_index) + ".nextn.eh_proj.weight")) {
@@ -872,30 +921,31 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     CK(mat(p + "ffn_down.weight", m->mt_ffn.down)); CK(check_k(m->mt_ffn.down, d, m->f, "nextn ffn_down"));
     CK(vec(p + "nextn.shared_head_norm.weight", &m->mt_shn, d));
     m->mt_head = m->head; m->mt_ids = nullptr; m->mt_nv = m->V;
-    m->mt_Kc = falloc(m, (size_t)max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)max_ctx * kvd);
+    m->mt_Kc = falloc(m, (size_t)B * max_ctx * kvd); m->mt_Vc = falloc(m, (size_t)B * max_ctx * kvd);
     if (!m->mt_Kc || !m->mt_Vc) return -1;
     m->has_mtp = true;
   } else if (k > 0) {
     // no MTP image: the reference's other drafter, prompt lookup over the token history
     m->lookup = true;
-    m->hist = (int *)dalloc(m, ((size_t)max_ctx + 16) * 4);
+    m->hist = (int *)dalloc(m, (size_t)B * ((size_t)max_ctx + 16) * 4);
     if (!m->hist) return -1;
   }
 
   // activations
   int big = m->f > m->convd ? m->f : m->convd;
-  m->x = falloc(m, (size_t)T * d); m->x1 = falloc(m, (size_t)T * d); m->hn = falloc(m, (size_t)SPEC_MAXT * d); m->e = falloc(m, (size_t)T * d);
+  const int Tc = T > SPEC_MAXT ? T : SPEC_MAXT;
+  m->x = falloc(m, (size_t)T * d); m->x1 = falloc(m, (size_t)T * d); m->hn = falloc(m, (size_t)Tc * d); m->e = falloc(m, (size_t)T * d);
   m->qn = falloc(m, (size_t)T * qa); m->y = falloc(m, (size_t)T * big); m->beta = falloc(m, (size_t)T * m->TR); m->decay = falloc(m, (size_t)T * m->TR);
-  m->t2part = falloc(m, (size_t)2 * SPEC_MAXT * TOP2_NB * 4);
-  m->mt_x = falloc(m, (size_t)T * d); m->mt_hn = falloc(m, (size_t)T * d); m->chain_h = falloc(m, d);
-  m->att_split = g_llb.sms / m->KV;   // one wave of blocks: the kernel takes a whole SM's shared memory
+  m->t2part = falloc(m, (size_t)2 * Tc * TOP2_NB * 4);
+  m->mt_x = falloc(m, (size_t)T * d); m->mt_hn = falloc(m, (size_t)T * d); m->chain_h = falloc(m, (size_t)T * d);
+  m->att_split = g_llb.sms / (m->KV * B);   // one wave of blocks: the kernel takes a whole SM's shared memory
   if (m->att_split < 1) m->att_split = 1;
   if (m->att_split > 128) m->att_split = 128;
   m->pm = falloc(m, (size_t)m->H * T * m->att_split); m->pl = falloc(m, (size_t)m->H * T * m->att_split);
   m->po = falloc(m, (size_t)m->H * T * m->att_split * m->hd);
   CK(xp_alloc(m, 0, d)); CK(xp_alloc(m, 1, m->f)); CK(xp_alloc(m, 2, qa)); CK(xp_alloc(m, 3, m->vdc));
   CK(xp_alloc(m, 4, 2 * d));
-  m->xpv[0][5] = m->xpv[0][0]; m->xpv[1][5] = m->xpv[1][0];   // placeholder where there are no routed experts
+  for (int v = 0; v < 3; v++) m->xpv[v][5] = m->xpv[v][0];   // placeholder where there are no routed experts
   if (m->ne > 0) {
     const int ns = m->nk + 1;
     m->moe_lg = falloc(m, (size_t)T * (m->ne + 1)); m->moe_wt = falloc(m, (size_t)T * ns); m->moe_ids = (int *)dalloc(m, (size_t)T * ns * 4);
@@ -903,13 +953,15 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     CK(xp_alloc(m, 5, ns * m->ef));
     if (!m->moe_lg || !m->moe_wt || !m->moe_ids || !m->moe_g || !m->moe_u || !m->hn2) return -1;
   }
-  m->ctl = (SpecCtl *)dalloc(m, sizeof(SpecCtl));
-  if (!m->x || !m->po || !m->ctl) return -1;
-  CU_OK(cudaHostAlloc((void **)&m->res_host, sizeof(SpecResult) * m->res_n, cudaHostAllocMapped));
-  memset(m->res_host, 0, sizeof(SpecResult) * m->res_n);
+  m->ctl = (SpecCtl *)dalloc(m, sizeof(SpecCtl) * B);
+  m->const_rows = (int *)dalloc(m, 4);
+  if (!m->x || !m->po || !m->ctl || !m->const_rows) return -1;
+  { const int rows = B * m->Tspec; CU_OK(cudaMemcpyAsync(m->const_rows, &rows, 4, cudaMemcpyHostToDevice, g_llb.stream)); CU_OK(cudaStreamSynchronize(g_llb.stream)); }
+  CU_OK(cudaHostAlloc((void **)&m->res_host, sizeof(SpecResult) * m->res_n * B, cudaHostAllocMapped));
+  memset(m->res_host, 0, sizeof(SpecResult) * m->res_n * B);
   CU_OK(cudaHostGetDevicePointer((void **)&m->res_dev, m->res_host, 0));
   CK(ops_model_setup());
-  set_width(m, m->Tspec);
+  set_width(m, B * m->Tspec);
   return 0;
 }
 
@@ -1003,9 +1055,10 @@ static int pf_site(llb_spec *m, std::vector<PfSiteMat> mats, const __half *kg, i
 // One chunk: rows of positions p0 .. p0 + R - 1 with the given tokens through every layer.  Leaves the trunk's K/V rows,
 // conv rings and DeltaNet states as the T-row pass would have (the state written back into the committed slot), the
 // drafter's K/V rows of the same positions, and in pf.hn row 0 the normed hidden of the chunk's last row.
-static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
+static int pf_chunk(llb_spec *m, int b, const int *ids, int p0, int R) {
   PfState &f = m->pf;
   cudaStream_t s = g_llb.stream;
+  StreamScope scope(m, true);   // the chunk's kernels see one stream: stream b's state is handed to them directly
   const int d = m->d, qa = m->H * m->hd, gsz = m->Tpf, ngrp = (R + gsz - 1) / gsz;
   std::vector<RowSet> rs(1 + ngrp);
   memset(rs.data(), 0, rs.size() * sizeof(RowSet));
@@ -1015,7 +1068,7 @@ static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
   CU_OK(cudaMemcpyAsync(f.ids, ids + p0, (size_t)R * 4, cudaMemcpyHostToDevice, s));
   CU_OK(cudaStreamSynchronize(s));   // rs is a local: the copy must have read it before it goes
   PartIn none{nullptr, 0, 0};
-  AttnShape ash{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd};
+  AttnShape ash{m->H, m->KV, m->hd, m->rope_dim, m->eps, m->att_min, (long long)m->max_ctx * m->KV * m->hd, (int)sizeof(RowSet), 0};
   DeltaShape dsh{m->TR, m->GK, m->SZ, m->KC, m->convd, m->kdc, m->vdc, m->eps};
   PFK("embed", op_pf_embed(s, m->embd.fmt, m->embd.w, d, f.ids, R, f.x));
   for (int il = 0; il < m->L; il++) {
@@ -1023,14 +1076,14 @@ static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
     PFK("norm", op_pf_norm(s, il ? f.x1 : f.x, il ? as_in(f.dn) : none, l.attn_norm, m->eps, d, f.x, f.kg_d, d, 0, nullptr, R));
     if (l.full) {
       PFK("gemm qkv", pf_site(m, {{&l.at.q, &f.q}, {&l.at.k, &f.k}, {&l.at.v, &f.v}}, f.kg_d, d, R));
-      PFK("qkrope", op_qkrope(s, as_in(f.q), as_in(f.k), as_in(f.v), l.at.qn, l.at.kn, m->invfreq, ash, f.qn, m->Kc[il], m->Vc[il], &f.rs[0], R));
+      PFK("qkrope", op_qkrope(s, as_in(f.q), as_in(f.k), as_in(f.v), l.at.qn, l.at.kn, m->invfreq, ash, f.qn, kc_of(m, m->Kc[il], b), kc_of(m, m->Vc[il], b), &f.rs[0], R));
       // every group of gsz rows in one launch (grid z): each streams the K/V rows up to its own last position
-      PFK("attention", op_attention(s, f.qn, m->Kc[il], m->Vc[il], as_in(f.q), ash, m->att_split, f.pm, f.pl, f.po, m->xp_qa, &f.rs[1], gsz, f.kg_qa, 0, ngrp));
+      PFK("attention", op_attention(s, f.qn, kc_of(m, m->Kc[il], b), kc_of(m, m->Vc[il], b), as_in(f.q), ash, m->att_split, f.pm, f.pl, f.po, m->xp_qa, &f.rs[1], gsz, f.kg_qa, 0, ngrp));
       PFK("gemm attn_out", pf_site(m, {{&l.at.o, &f.a}}, f.kg_qa, qa, R));
     } else {
       PFK("gemm qkv|z|b|a", pf_site(m, {{&l.dn.qkv, &f.qkv}, {&l.dn.z, &f.z}, {&l.dn.beta, &f.bp}, {&l.dn.alpha, &f.ap}}, f.kg_d, d, R));
-      PFK("delta", op_pf_delta(s, as_in(f.qkv), as_in(f.z), as_in(f.bp), as_in(f.ap), m->ring[il], m->ring_ks[il], l.dn.conv, l.dn.dt, l.dn.a, l.dn.norm, dsh,
-                     m->S[il], m->ctl, f.y, f.beta, f.decay, f.o, f.kg_v, p0, R));
+      PFK("delta", op_pf_delta(s, as_in(f.qkv), as_in(f.z), as_in(f.bp), as_in(f.ap), ring_of(m, il, b), m->ring_ks[il], l.dn.conv, l.dn.dt, l.dn.a, l.dn.norm, dsh,
+                     state_of(m, il, b), ctl_of(m, b), f.y, f.beta, f.decay, f.o, f.kg_v, p0, R));
       PFK("gemm ssm_out", pf_site(m, {{&l.dn.out, &f.a}}, f.kg_v, m->vdc, R));
     }
     PFK("norm", op_pf_norm(s, f.x, as_in(f.a), l.ffn.post, m->eps, d, f.x1, f.kg_d, d, 0, nullptr, R));
@@ -1049,7 +1102,7 @@ static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
     CK(pf_site(m, {{&m->mt_eh, &f.eh}}, f.kg_2d, 2 * d, R));
     CK(op_pf_norm(s, nullptr, as_in(f.eh), m->mt_attn_norm, m->eps, d, nullptr, f.kg_d, d, 0, nullptr, R));
     CK(pf_site(m, {{&m->mt_at.k, &f.k}, {&m->mt_at.v, &f.v}}, f.kg_d, d, R));
-    CK(op_qkrope(s, none, as_in(f.k), as_in(f.v), m->mt_at.qn, m->mt_at.kn, m->invfreq, ash, f.qn, m->mt_Kc, m->mt_Vc, &f.rs[0], R, true));
+    CK(op_qkrope(s, none, as_in(f.k), as_in(f.v), m->mt_at.qn, m->mt_at.kn, m->invfreq, ash, f.qn, kc_of(m, m->mt_Kc, b), kc_of(m, m->mt_Vc, b), &f.rs[0], R, true));
   }
   CU_OK(cudaMemcpyAsync(f.hn, f.hn + (size_t)R * d, (size_t)d * 4, cudaMemcpyDeviceToDevice, s));
   m->pf_rows += R;
@@ -1059,7 +1112,7 @@ static int pf_chunk(llb_spec *m, const int *ids, int p0, int R) {
 // The fast part of a prompt: whole chunks from position 0 while more than `keep` rows remain for the T-row pass.
 // Returns the position the T-row pass continues from; the drafter's row there is left pending as a one-row catch-up
 // whose hidden (the normed row of the position before) is put where the catch-up reads it.
-static int pf_prefill(llb_spec *m, const int *ids, int n_rows, int keep, int *p_out) {
+static int pf_prefill(llb_spec *m, int b, const int *ids, int n_rows, int keep, int *p_out) {
   CK(pf_alloc(m));
   PfState &f = m->pf;
   CU_OK(cudaMemsetAsync(f.hn, 0, (size_t)m->d * 4, g_llb.stream));   // the hidden before position 0 is zero (host/llb_host.c:1816)
@@ -1068,7 +1121,7 @@ static int pf_prefill(llb_spec *m, const int *ids, int n_rows, int keep, int *p_
   if (pf_prof_on()) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, g_llb.stream); }
   while (n_rows - p > keep) {
     const int R = n_rows - p - keep < PF_R ? n_rows - p - keep : PF_R;
-    CK(pf_chunk(m, ids, p, R));
+    CK(pf_chunk(m, b, ids, p, R));
     p += R;
   }
   if (e0) {
@@ -1078,30 +1131,48 @@ static int pf_prefill(llb_spec *m, const int *ids, int n_rows, int keep, int *p_
     cudaEventDestroy(e0); cudaEventDestroy(e1);
   }
   if (p > 0) {
-    CU_OK(cudaMemcpyAsync(m->hn, f.hn, (size_t)m->d * 4, cudaMemcpyDeviceToDevice, g_llb.stream));
+    // the stream's first row of the trunk's normed hidden rows: what the pending catch-up row pairs with
+    CU_OK(cudaMemcpyAsync(m->hn + (size_t)(m->B > 1 ? b * m->per : 0) * m->d, f.hn, (size_t)m->d * 4, cudaMemcpyDeviceToDevice, g_llb.stream));
     struct { int n, pos0, tok[SPEC_MAXT], slot[SPEC_MAXT]; } c;
     memset(&c, 0, sizeof c);
     c.n = m->has_mtp ? 1 : 0; c.pos0 = p; c.tok[0] = ids[p];
-    CU_OK(cudaMemcpyAsync(&m->ctl->catchup, &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->catchup, &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
     CU_OK(cudaStreamSynchronize(g_llb.stream));
   }
   *p_out = p;
   return 0;
 }
 
-static int ctl_write(llb_spec *m, const SpecCtl &c) {
-  CU_OK(cudaMemcpyAsync(m->ctl, &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
+static int ctl_write(llb_spec *m, int b, const SpecCtl &c) {
+  CU_OK(cudaMemcpyAsync(ctl_of(m, b), &c, sizeof c, cudaMemcpyHostToDevice, g_llb.stream));
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   return 0;
 }
+// a fresh control block of stream b
+static SpecCtl ctl_fresh(const llb_spec *m, int b) {
+  SpecCtl c;
+  memset(&c, 0, sizeof c);
+  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->sq[b].seq; c.hist = hist_of(m, b);
+  return c;
+}
 
-static int wait_result(llb_spec *m, SpecResult *out) {
+static int wait_result(llb_spec *m, int b, SpecResult *out) {
   CU_OK(cudaStreamSynchronize(g_llb.stream));
-  const SpecResult *r = &m->res_host[m->seq % (unsigned long long)m->res_n];
-  if (r->seq != m->seq + 1) return llb_fail("cycle %llu did not report (device error word set?)", m->seq);
+  SeqHost &q = m->sq[b];
+  const SpecResult *r = &m->res_host[(size_t)b * m->res_n + q.seq % (unsigned long long)m->res_n];
+  if (r->seq != q.seq + 1) return llb_fail("cycle %llu of stream %d did not report (device error word set?)", q.seq, b);
   *out = *r;
-  m->seq += 1;
+  q.seq += 1;
   return 0;
+}
+// the host mirror of stream b after a cycle that reported r
+static void note_cycle(llb_spec *m, int b, const SpecResult &r, int served_idx) {
+  SeqHost &q = m->sq[b];
+  q.pos += r.served;
+  q.last_tok = r.ids[r.served - 1];
+  q.cycles += 1; q.rows += (unsigned long long)r.T; q.served += (unsigned long long)r.served;
+  for (int j = 1; j < r.T; j++) { q.drafted[j] += 1; q.accepted[j] += r.served > j; }
+  q.last = r; q.have_last = true; q.last_served_idx = served_idx;
 }
 
 extern "C" {
@@ -1114,13 +1185,27 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
 // The engine as rank tp_rank of tp_size tensor-parallel ranks (llb_b200_tp_init first): this rank loads its share of every
 // projection and the passes exchange one all-reduce after each row-split projection.  Every rank must make the same calls
 // in the same order (the collectives inside a cycle pair up across the ranks); all of them return the same tokens.
+static llb_spec *open_any(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp, size_t mtp_bytes,
+                          int mtp_on_device, int k, int max_ctx, int layers, int tp_n, int nstreams);
 LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                    size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_n) {
+  return open_any(index_text, pack, pack_bytes, pack_on_device, mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, tp_n, 1);
+}
+// The engine with `streams` independent sequences that share every weight read: a pass carries the k + 1 rows of every
+// stream through each GEMM together (streams x (k + 1) <= 16 rows; <= 8 with routed experts), attention, the DeltaNet
+// scan, the drafter and the accept step run per stream in the same launches.  A stream's tokens are those of the
+// same stream alone in such an engine, bit for bit (a row's GEMM result does not depend on its neighbours).
+LLB_API llb_spec *llb_spec_open_streams(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
+                                        size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int streams) {
+  return open_any(index_text, pack, pack_bytes, pack_on_device, mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, 1, streams);
+}
+static llb_spec *open_any(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp, size_t mtp_bytes,
+                          int mtp_on_device, int k, int max_ctx, int layers, int tp_n, int nstreams) {
   if (!g_llb.stream) { llb_fail("llb_b200_init has not been called"); return nullptr; }
   if (!index_text || !pack) { llb_fail("llb_spec_open: no index or no pack"); return nullptr; }
   llb_spec *m = new llb_spec();
   m->pack_bytes = pack_bytes;
-  if (open_impl(m, index_text, (const uint8_t *)pack, pack_on_device, (const uint8_t *)mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, tp_n)) {
+  if (open_impl(m, index_text, (const uint8_t *)pack, pack_on_device, (const uint8_t *)mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, tp_n, nstreams)) {
     llb_spec_close(m);
     return nullptr;
   }
@@ -1129,13 +1214,18 @@ LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, siz
   // between cycles lives in device memory.
   // (an eager pass at either width first: a K-split, and so a buffer's size, may differ between them)
   bool bad = false;
-  set_width(m, m->Tpf);
-  bad = bad || llb_spec_reset(m) || enq_cycle(m, false);
-  set_width(m, m->Tspec);
-  bad = bad || llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m) || capture(m, 0, &m->g_spec, &m->n_spec_nodes);
-  set_width(m, m->Tpf);
+  const int w_spec = m->B * m->Tspec, w_pf = m->B > 1 ? w_spec : m->Tpf;
+  {
+    StreamScope scope(m);
+    set_width(m, w_pf);
+    bad = bad || llb_spec_reset(m) || enq_cycle(m, false);
+    set_width(m, w_spec);
+    bad = bad || llb_spec_reset(m) || enq_cycle(m, true) || llb_spec_reset(m);
+  }
+  bad = bad || capture(m, 0, &m->g_spec, &m->n_spec_nodes);
+  set_width(m, w_pf);
   bad = bad || capture(m, 1, &m->g_prefill, nullptr);
-  set_width(m, m->Tspec);
+  set_width(m, w_spec);
   bad = bad || capture(m, 2, &m->g_verify, &m->n_verify_nodes) || llb_spec_reset(m);
   if (bad) {
     llb_spec_close(m);
@@ -1183,45 +1273,59 @@ LLB_API void llb_spec_close(llb_spec *m) {
   delete m;
 }
 
-// zero the sequence state (host/llb_host.c:1915-1928): KV rows are overwritten before they are
+// zero the sequence state of stream b (host/llb_host.c:1915-1928): KV rows are overwritten before they are
 // read, so only the conv rings and the committed DeltaNet slot need clearing
-LLB_API int llb_spec_reset(llb_spec *m) {
+static int reset_stream(llb_spec *m, int b) {
   for (int il = 0; il < m->L; il++) {
-    if (m->ring[il]) CU_OK(cudaMemsetAsync(m->ring[il], 0, (size_t)m->ring_ks[il] * CONV_RING * m->convd * 4, g_llb.stream));
-    if (m->S[il]) CU_OK(cudaMemsetAsync(m->S[il], 0, (size_t)m->R * m->TR * m->SZ * m->SZ * 4, g_llb.stream));
+    if (m->ring[il]) CU_OK(cudaMemsetAsync(ring_of(m, il, b), 0, (size_t)m->ring_ks[il] * CONV_RING * m->convd * 4, g_llb.stream));
+    if (m->S[il]) CU_OK(cudaMemsetAsync(state_of(m, il, b), 0, (size_t)m->s_group * 4, g_llb.stream));
   }
-  CU_OK(cudaMemsetAsync(m->hn, 0, (size_t)SPEC_MAXT * m->d * 4, g_llb.stream));
-  SpecCtl c;
-  memset(&c, 0, sizeof c);
-  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq; c.hist = m->hist;
-  CK(ctl_write(m, c));
-  m->pos = 0; m->primed = false; m->have_last = false;
-  m->cycles = m->rows = m->served = 0;
-  memset(m->drafted, 0, sizeof m->drafted); memset(m->accepted, 0, sizeof m->accepted);
+  // the trunk's normed hidden rows the drafter pairs with (the stream's rows of the widest pass)
+  const int rows = m->B > 1 ? m->Tspec : (m->Tpf > SPEC_MAXT ? m->Tpf : SPEC_MAXT);
+  CU_OK(cudaMemsetAsync(m->hn + (size_t)b * rows * m->d, 0, (size_t)rows * m->d * 4, g_llb.stream));
+  CK(ctl_write(m, b, ctl_fresh(m, b)));
+  SeqHost &q = m->sq[b];
+  q.pos = 0; q.primed = false; q.have_last = false;
+  q.cycles = q.rows = q.served = 0;
+  memset(q.drafted, 0, sizeof q.drafted); memset(q.accepted, 0, sizeof q.accepted);
+  return 0;
+}
+LLB_API int llb_spec_reset(llb_spec *m) {
+  for (int b = 0; b < m->B; b++) CK(reset_stream(m, b));
   return 0;
 }
 
-// Feed the prompt.  Positions 0 .. n-2 run through the verify pass in chunks of k+1 given rows;
-// the last prompt token becomes the first speculative cycle's committed input, exactly where the
-// reference's first cycle after a prompt starts (host/llb_host.c:1911, pos = n-1).
-LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
+static int prefill_stream(llb_spec *m, int b, const int *ids, int n) {
+  if (b < 0 || b >= m->B) return llb_fail("prefill: stream %d of %d", b, m->B);
   if (n < 1) return llb_fail("prefill: empty prompt");
   if (n + m->Tpf + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
   for (int i = 0; i < n; i++) if (ids[i] < 0 || ids[i] >= m->V) return llb_fail("prefill: token %d out of range", ids[i]);
-  CK(llb_spec_reset(m));
-  SpecCtl c;
-  memset(&c, 0, sizeof c);
-  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq; c.hist = m->hist;
-  if (m->lookup) CU_OK(cudaMemcpyAsync(m->hist, ids, (size_t)n * 4, cudaMemcpyHostToDevice, g_llb.stream));
+  CK(reset_stream(m, b));
+  // the other streams sit this out: with no rows in their control blocks every kernel skips them, and the accept
+  // kernel neither decides nor reports for them; their blocks are put back afterwards
+  std::vector<SpecCtl> keep;
+  bool parked = false;
+  for (int o = 0; o < m->B; o++) parked = parked || (o != b && m->sq[o].primed);
+  if (parked) {
+    keep.resize(m->B);
+    CU_OK(cudaMemcpy(keep.data(), m->ctl, sizeof(SpecCtl) * m->B, cudaMemcpyDeviceToHost));
+    for (int o = 0; o < m->B; o++) if (o != b) {
+      SpecCtl c = keep[o];
+      c.verify.n = 0; c.catchup.n = 0; c.chain.n = 0;
+      CK(ctl_write(m, o, c));
+    }
+  }
+  SpecCtl c = ctl_fresh(m, b);
+  if (m->lookup) CU_OK(cudaMemcpyAsync(hist_of(m, b), ids, (size_t)n * 4, cudaMemcpyHostToDevice, g_llb.stream));
   // the drafter's row for position 0 pairs token 0 with a zero hidden (host/llb_host.c:1815-1817)
   c.catchup.n = 1; c.catchup.pos0 = 0; c.catchup.tok[0] = ids[0];
-  c.verify.n = m->lookup ? 1 : m->Tmax;   // nothing to look up at position 0
+  c.verify.n = m->lookup ? 1 : m->per;   // nothing to look up at position 0
   c.verify.pos0 = 0; c.verify.tok[0] = ids[0];
   for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
-  CK(ctl_write(m, c));
+  CK(ctl_write(m, b, c));
   int p = 0;
   // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_R rows through the dense path (dense FFN only)
-  if (m->prefill_mode == 1 && m->ne == 0 && m->tp.size <= 1 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, ids, n - 1, m->Tspec, &p));
+  if (m->prefill_mode == 1 && m->ne == 0 && m->tp.size <= 1 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, b, ids, n - 1, m->Tspec, &p));
   while (p < n - 1) {
     // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
     // over the rows of the last chunk, and that cycle's kernels cover k + 1 rows
@@ -1234,44 +1338,99 @@ LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) {
     int tail[1 + SPEC_MAXT];
     tail[0] = rows;  // forced
     for (int r = 0; r < SPEC_MAXT; r++) tail[1 + r] = r < rows ? ids[p + r + 1] : 0;
-    CU_OK(cudaMemcpyAsync(&m->ctl->verify, &v, sizeof v, cudaMemcpyHostToDevice, g_llb.stream));
-    CU_OK(cudaMemcpyAsync(&m->ctl->forced, tail, sizeof tail, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->verify, &v, sizeof v, cudaMemcpyHostToDevice, g_llb.stream));
+    CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->forced, tail, sizeof tail, cudaMemcpyHostToDevice, g_llb.stream));
     CU_OK(cudaGraphLaunch(m->g_prefill, g_llb.stream));
     SpecResult r;
-    CK(wait_result(m, &r));
+    CK(wait_result(m, b, &r));
     if (r.served != rows) return llb_fail("prefill: chunk at %d served %d of %d rows", p, r.served, rows);
     p += rows;
   }
-  if (n == 1) {
-    // nothing ran: the first cycle starts at position 0 with the single prompt token
-  }
-  m->pos = n - 1;
-  m->last_tok = ids[n - 1];
-  m->primed = true;
-  m->have_last = false;
+  if (parked) for (int o = 0; o < m->B; o++) if (o != b) CK(ctl_write(m, o, keep[o]));
+  SeqHost &q = m->sq[b];
+  q.pos = n - 1;        // n == 1: nothing ran, the first cycle starts at position 0 with the single prompt token
+  q.last_tok = ids[n - 1];
+  q.primed = true;
+  q.have_last = false;
   return 0;
 }
+// Feed the prompt.  Positions 0 .. n-2 run through the verify pass in chunks of given rows (or, for long prompts with
+// LLB_PREFILL=fast, through the dense path); the last prompt token becomes the first speculative cycle's committed
+// input, exactly where the reference's first cycle after a prompt starts (host/llb_host.c:1911, pos = n-1).
+LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) { return prefill_stream(m, 0, ids, n); }
+// The same for stream b of an engine opened with llb_spec_open_streams; the other streams keep their state.
+LLB_API int llb_spec_prefill_stream(llb_spec *m, int stream, const int *ids, int n) { return prefill_stream(m, stream, ids, n); }
 
 // One speculative cycle.  ids_out[0..*n_out-1] are the emitted tokens; top2_out (may be null) gets
 // [id1, bits1, id2, bits2] of each emitted row.
 LLB_API int llb_spec_cycle(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2_out) {
-  if (!m->primed) return llb_fail("llb_spec_cycle before llb_spec_prefill");
+  if (m->B > 1) return llb_fail("llb_spec_cycle: the engine has %d streams, use llb_spec_cycle_streams", m->B);
+  SeqHost &q = m->sq[0];
+  if (!q.primed) return llb_fail("llb_spec_cycle before llb_spec_prefill");
   // every row of the cycle, and the drafter's chained rows, must fit: no clipped cycles
-  if (m->pos + m->Tmax >= m->max_ctx) return llb_fail("context of %d positions is full", m->max_ctx);
+  if (q.pos + m->Tmax >= m->max_ctx) return llb_fail("context of %d positions is full", m->max_ctx);
   CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
   SpecResult r;
-  CK(wait_result(m, &r));
-  if (r.p0 != m->pos) return llb_fail("cycle ran at position %d, host expected %d", r.p0, m->pos);
+  CK(wait_result(m, 0, &r));
+  if (r.p0 != q.pos) return llb_fail("cycle ran at position %d, host expected %d", r.p0, q.pos);
   for (int i = 0; i < r.served; i++) {
     ids_out[i] = r.ids[i];
     if (top2_out) memcpy(top2_out + 4 * i, r.top2[i], 16);
   }
   *n_out = r.served;
-  m->pos += r.served;
-  m->last_tok = r.ids[r.served - 1];
-  m->cycles += 1; m->rows += (unsigned long long)r.T; m->served += (unsigned long long)r.served;
-  for (int j = 1; j < r.T; j++) { m->drafted[j] += 1; m->accepted[j] += r.served > j; }
-  m->last = r; m->have_last = true; m->last_served_idx = 0;
+  note_cycle(m, 0, r, 0);
+  return 0;
+}
+
+// One cycle of every stream that has a prompt, as ONE graph launch.  ids_out[b][0 .. n_out[b]-1] (rows of SPEC_MAXT
+// ints) are stream b's emitted tokens, n_out[b] = 0 for a stream without a prompt; top2_out (may be null) rows of
+// SPEC_MAXT x 4 words.
+LLB_API int llb_spec_cycle_streams(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2_out) {
+  int live = 0;
+  for (int b = 0; b < m->B; b++) {
+    const SeqHost &q = m->sq[b];
+    if (!q.primed) continue;
+    if (q.pos + m->per >= m->max_ctx) return llb_fail("stream %d: context of %d positions is full", b, m->max_ctx);
+    live++;
+  }
+  if (!live) return llb_fail("llb_spec_cycle_streams: no stream has a prompt");
+  CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
+  for (int b = 0; b < m->B; b++) {
+    n_out[b] = 0;
+    SeqHost &q = m->sq[b];
+    if (!q.primed) continue;
+    SpecResult r;
+    CK(wait_result(m, b, &r));
+    if (r.p0 != q.pos) return llb_fail("stream %d: cycle ran at position %d, host expected %d", b, r.p0, q.pos);
+    for (int i = 0; i < r.served; i++) {
+      ids_out[b * SPEC_MAXT + i] = r.ids[i];
+      if (top2_out) memcpy(top2_out + ((size_t)b * SPEC_MAXT + i) * 4, r.top2[i], 16);
+    }
+    n_out[b] = r.served;
+    note_cycle(m, b, r, r.served);
+  }
+  return 0;
+}
+
+// `n` cycles of every stream back to back with no host round trip between them; tokens[b] = tokens stream b emitted.
+LLB_API int llb_spec_run_cycles_streams(llb_spec *m, int n, int *tokens) {
+  if (n > m->res_n) return llb_fail("at most %d cycles per call", m->res_n);
+  for (int b = 0; b < m->B; b++) {
+    tokens[b] = 0;
+    const SeqHost &q = m->sq[b];
+    if (q.primed && q.pos + n * m->per >= m->max_ctx) return llb_fail("stream %d: context of %d positions cannot take %d more cycles", b, m->max_ctx, n);
+  }
+  for (int i = 0; i < n; i++) CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
+  for (int i = 0; i < n; i++)
+    for (int b = 0; b < m->B; b++) {
+      SeqHost &q = m->sq[b];
+      if (!q.primed) continue;
+      SpecResult r;
+      CK(wait_result(m, b, &r));
+      if (r.p0 != q.pos) return llb_fail("stream %d: cycle ran at position %d, host expected %d", b, r.p0, q.pos);
+      tokens[b] += r.served;
+      note_cycle(m, b, r, r.served);
+    }
   return 0;
 }
 
@@ -1297,21 +1456,22 @@ LLB_API int llb_spec_generate(llb_spec *m, int steps, int *ids, uint32_t *top2) 
 // greedy rule, a caller that leaves the greedy stream gets "a step out of order", the reference's
 // own error for that case (host/llb_host.c:1929-1930).
 LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y) {
-  if (m->have_last && m->last_served_idx < m->last.served && pos == m->last.p0 + m->last_served_idx &&
-      (m->last_served_idx == 0 || tok == m->last.ids[m->last_served_idx - 1])) {
-    const int r = m->last_served_idx++;
-    y[0] = bits_float(m->last.top2[r][1]); y[1] = (float)m->last.top2[r][0];
-    y[2] = bits_float(m->last.top2[r][3]); y[3] = (float)m->last.top2[r][2];
+  SeqHost &q = m->sq[0];
+  if (q.have_last && q.last_served_idx < q.last.served && pos == q.last.p0 + q.last_served_idx &&
+      (q.last_served_idx == 0 || tok == q.last.ids[q.last_served_idx - 1])) {
+    const int r = q.last_served_idx++;
+    y[0] = bits_float(q.last.top2[r][1]); y[1] = (float)q.last.top2[r][0];
+    y[2] = bits_float(q.last.top2[r][3]); y[3] = (float)q.last.top2[r][2];
     return 0;
   }
-  if (m->primed && pos == m->pos && tok == m->last_tok) {
+  if (q.primed && pos == q.pos && tok == q.last_tok) {
     // a new cycle at (pos, tok): the pair crosses to the device and the accept kernel checks it
     // against the state it committed itself
     int chk[3] = {1, pos, tok};
     CU_OK(cudaMemcpyAsync(&m->ctl->chk_on, chk, sizeof chk, cudaMemcpyHostToDevice, g_llb.stream));
     int ids[SPEC_MAXT], n = 0;
     CK(llb_spec_cycle(m, ids, &n, nullptr));
-    if (m->last.pad) return llb_fail("LLB_SPEC: the device's committed (pos, tok) differs from the caller's");
+    if (q.last.pad) return llb_fail("LLB_SPEC: the device's committed (pos, tok) differs from the caller's");
     return llb_spec_pass(m, pos, tok, y);
   }
   return llb_fail("LLB_SPEC: a step out of order");
@@ -1321,21 +1481,19 @@ LLB_API int llb_spec_pass(llb_spec *m, int pos, int tok, float *y) {
 // from the host), then collect what they emitted.  ids (may be null) receives the tokens in order,
 // at most cap of them; returns the number of tokens emitted by the n cycles.
 LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap) {
-  if (!m->primed) return llb_fail("llb_spec_run_cycles before llb_spec_prefill");
+  if (m->B > 1) return llb_fail("llb_spec_run_cycles: the engine has %d streams, use llb_spec_run_cycles_streams", m->B);
+  SeqHost &q = m->sq[0];
+  if (!q.primed) return llb_fail("llb_spec_run_cycles before llb_spec_prefill");
   if (n > m->res_n) return llb_fail("at most %d cycles per call", m->res_n);
-  if (m->pos + n * m->Tmax >= m->max_ctx) return llb_fail("context of %d positions cannot take %d more cycles", m->max_ctx, n);
+  if (q.pos + n * m->Tmax >= m->max_ctx) return llb_fail("context of %d positions cannot take %d more cycles", m->max_ctx, n);
   for (int i = 0; i < n; i++) CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
   int total = 0;
   for (int i = 0; i < n; i++) {
     SpecResult r;
-    CK(wait_result(m, &r));
-    if (r.p0 != m->pos) return llb_fail("cycle ran at position %d, host expected %d", r.p0, m->pos);
+    CK(wait_result(m, 0, &r));
+    if (r.p0 != q.pos) return llb_fail("cycle ran at position %d, host expected %d", r.p0, q.pos);
     for (int j = 0; j < r.served; j++, total++) if (ids && total < cap) ids[total] = r.ids[j];
-    m->pos += r.served;
-    m->last_tok = r.ids[r.served - 1];
-    m->cycles += 1; m->rows += (unsigned long long)r.T; m->served += (unsigned long long)r.served;
-    for (int j = 1; j < r.T; j++) { m->drafted[j] += 1; m->accepted[j] += r.served > j; }
-    m->last = r; m->have_last = true; m->last_served_idx = r.served;
+    note_cycle(m, 0, r, r.served);
   }
   return total;
 }
@@ -1362,6 +1520,7 @@ LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass) {
 // positions.  The control block is restored afterwards, but the rows' KV / conv / state-ring slots have been
 // overwritten with the forced rows' values: call it after the tokens that matter have been generated.
 LLB_API int llb_spec_time_verify_rows(llb_spec *m, int iters, int rows, float *ms_per_pass) {
+  if (m->B > 1) return llb_fail("time_verify_rows: a one-stream engine's entry");
   if (rows < 1 || rows > m->Tmax) return llb_fail("time_verify_rows: %d rows, the engine was opened for %d", rows, m->Tmax);
   SpecCtl c, keep;
   CU_OK(cudaStreamSynchronize(g_llb.stream));
@@ -1407,6 +1566,7 @@ LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap) {
     g_prof.clear();
     g_prof_on = true;
     prof_mark("start");
+    StreamScope scope(m);
     int rc = enq_verify(m);
     g_prof_on = false;
     if (rc) return -1;
@@ -1431,7 +1591,9 @@ LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap) {
 // kernels per replay of the cycle graph (which = 0) or of the verify pass (which = 2)
 LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which) { return (int)(which == 2 ? m->n_verify_nodes : m->n_spec_nodes); }
 
-LLB_API int llb_spec_position(const llb_spec *m) { return m->pos; }
+LLB_API int llb_spec_position(const llb_spec *m) { return m->sq[0].pos; }
+LLB_API int llb_spec_position_stream(const llb_spec *m, int stream) { return stream >= 0 && stream < m->B ? m->sq[stream].pos : -1; }
+LLB_API int llb_spec_streams(const llb_spec *m) { return m->B; }
 
 // mode 1: prompts go through the dense tcgen05 path in chunks of 128 rows (all but their last k + 1 rows); mode 0: every
 // row through the T-row pass.  Returns the previous mode.
@@ -1442,28 +1604,36 @@ LLB_API int llb_spec_set_prefill(llb_spec *m, int mode) {
 }
 LLB_API double llb_spec_fast_rows(const llb_spec *m) { return m->pf_rows; }
 
-LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out /* cycles, rows, served, drafted[8], accepted[8] */) {
-  out[0] = m->cycles; out[1] = m->rows; out[2] = m->served;
-  for (int j = 0; j < 8; j++) { out[3 + j] = m->drafted[j]; out[11 + j] = m->accepted[j]; }
+LLB_API int llb_spec_stats_stream(const llb_spec *m, int stream, unsigned long long *out /* cycles, rows, served, drafted[8], accepted[8] */) {
+  if (stream < 0 || stream >= m->B) return llb_fail("stats: stream %d of %d", stream, m->B);
+  const SeqHost &q = m->sq[stream];
+  out[0] = q.cycles; out[1] = q.rows; out[2] = q.served;
+  for (int j = 0; j < 8; j++) { out[3 + j] = q.drafted[j]; out[11 + j] = q.accepted[j]; }
   return 0;
 }
+LLB_API int llb_spec_stats(const llb_spec *m, unsigned long long *out) { return llb_spec_stats_stream(m, 0, out); }
 
 // State read-back for parity checks: what = 0 committed DeltaNet state of layer il [TR][128][128],
 // 1 the K row and 2 the V row of position `pos` in layer il, 3 the conv ring row of position `pos`,
 // 4 the trunk's output-normed hidden row `pos` (0..k) of the last pass, 5 the drafter's K row, 6 the output-normed
 // hidden of row `pos` of the last chunk the dense prompt path processed.
-LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n) {
+LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il, int pos, float *out, size_t n);
+LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *out, size_t n) { return llb_spec_read_state_stream(m, 0, what, il, pos, out, n); }
+// ... of stream `stream` (what = 4: `pos` is the row within the stream's rows of the pass)
+LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il, int pos, float *out, size_t n) {
+  if (stream < 0 || stream >= m->B) return llb_fail("read_state: stream %d of %d", stream, m->B);
+  const int b = stream;
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   const float *src = nullptr;
   size_t have = 0;
   const int kvd = m->KV * m->hd;
   if (what == 0 && il < m->L && m->S[il]) {
     SpecCtl c;
-    CU_OK(cudaMemcpy(&c, m->ctl, sizeof c, cudaMemcpyDeviceToHost));
-    have = (size_t)m->TR * m->SZ * m->SZ; src = m->S[il] + (size_t)c.sc * have;
+    CU_OK(cudaMemcpy(&c, ctl_of(m, b), sizeof c, cudaMemcpyDeviceToHost));
+    have = (size_t)m->TR * m->SZ * m->SZ; src = state_of(m, il, b) + (size_t)c.sc * have;
   } else if ((what == 1 || what == 2 || what == 5) && (what == 5 ? m->mt_Kc != nullptr : (il < m->L && m->Kc[il]))) {
     // a cache row is kept as two fp16 planes, hi and lo * 2048
-    const __half *c = (const __half *)(what == 5 ? m->mt_Kc : what == 1 ? m->Kc[il] : m->Vc[il]);
+    const __half *c = (const __half *)kc_of(m, what == 5 ? m->mt_Kc : what == 1 ? m->Kc[il] : m->Vc[il], b);
     have = kvd;
     if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
     std::vector<__half> hi(have), lo(have);
@@ -1478,13 +1648,13 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
     std::vector<float> tmp(have);
     for (size_t i = 0; i < have; i++) out[i] = 0.0f;
     for (int k = 0; k < m->ring_ks[il]; k++) {
-      CU_OK(cudaMemcpy(tmp.data(), m->ring[il] + (size_t)k * CONV_RING * m->convd + (size_t)(pos & (CONV_RING - 1)) * m->convd, have * 4,
+      CU_OK(cudaMemcpy(tmp.data(), ring_of(m, il, b) + (size_t)k * CONV_RING * m->convd + (size_t)(pos & (CONV_RING - 1)) * m->convd, have * 4,
                        cudaMemcpyDeviceToHost));
       for (size_t i = 0; i < have; i++) out[i] += tmp[i];
     }
     return (int)have;
   }
-  else if (what == 4) { have = m->d; src = m->hn + (size_t)pos * m->d; }
+  else if (what == 4) { have = m->d; src = m->hn + (size_t)((m->B > 1 ? b * m->Tspec : 0) + pos) * m->d; }
   else if (what == 6 && m->pf.ready && pos >= 0 && pos < PF_R) { have = m->d; src = m->pf.hn + (size_t)(pos + 1) * m->d; }   // dense path: normed hidden of row `pos` of its last chunk
   else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
   if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
@@ -1500,10 +1670,11 @@ LLB_API int llb_spec_moe_ffn(llb_spec *m, int il, int T, const float *h2, float 
   if (il < 0 || il >= m->L || !m->layer[il].ffn.moe) return llb_fail("moe_ffn: layer %d has no routed experts", il);
   if (T < 1 || T > m->Tmax) return llb_fail("moe_ffn: %d rows, the engine was opened for %d", T, m->Tmax);
   CK(llb_spec_reset(m));
-  SpecCtl c;
-  memset(&c, 0, sizeof c);
-  c.R = m->R; c.k = m->k; c.max_pos = m->max_ctx; c.seq = m->seq; c.hist = m->hist; c.verify.n = T;
-  CK(ctl_write(m, c));
+  if (m->B > 1) return llb_fail("moe_ffn: a test entry of one-stream engines");
+  SpecCtl c = ctl_fresh(m, 0);
+  c.verify.n = T;
+  CK(ctl_write(m, 0, c));
+  StreamScope scope(m);
   cudaStream_t s = g_llb.stream;
   CU_OK(cudaMemcpyAsync(m->hn2, h2, (size_t)T * m->d * 4, cudaMemcpyHostToDevice, s));
   CK(ops_xp_from_f32(s, m->hn2, T, 2, m->xp_d));

@@ -29,7 +29,17 @@ struct GemmMat {
   int ostride;        // floats between consecutive tokens of one partial
   long long split_stride;  // floats between consecutive K-slices
   const int *tok_slot;     // optional: token t is written to row-block tok_slot[t] instead of t
+  // several streams in one pass (tok_per > 0): token t is row t % tok_per of stream z = t / tok_per, whose slot array
+  // lies tok_stride ints after the previous stream's and whose row-blocks start at z * tok_add
+  int tok_per, tok_stride, tok_add;
 };
+
+__device__ __forceinline__ int gemm_out_block(const GemmMat &M, int t) {
+  if (!M.tok_slot) return t;
+  if (M.tok_per <= 0) return M.tok_slot[t];
+  const int z = t / M.tok_per;
+  return M.tok_slot[(size_t)z * M.tok_stride + (t - z * M.tok_per)] + z * M.tok_add;
+}
 
 struct GemmArgs {
   GemmMat m[GEMM_MAXMAT];
@@ -104,7 +114,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs &a, const GemmMat &
         const float lo = __shfl_xor_sync(0xffffffffu, acc[0][i], 2);
         const int t = 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
         on[0][i] = j < 2 && t < a.T && r < M.rows;
-        if (on[0][i]) { idx[0][i] = (size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r; val[0][i] = acc[0][i] + lo * XP_LO_INV; }
+        if (on[0][i]) { idx[0][i] = (size_t)gemm_out_block(M, t) * M.ostride + r; val[0][i] = acc[0][i] + lo * XP_LO_INV; }
       }
     } else {
       // n-tiles 0 .. NT/2-1 the hi halves of rows 8 nt .. 8 nt + 7, n-tiles NT/2 .. NT-1 their lo halves
@@ -114,7 +124,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs &a, const GemmMat &
         for (int i = 0; i < 4; i++) {
           const int t = nt * 8 + 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
           on[nt][i] = t < a.T && r < M.rows;
-          if (on[nt][i]) { idx[nt][i] = (size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r; val[nt][i] = acc[nt][i] + acc[nt + NT / 2][i] * XP_LO_INV; }
+          if (on[nt][i]) { idx[nt][i] = (size_t)gemm_out_block(M, t) * M.ostride + r; val[nt][i] = acc[nt][i] + acc[nt + NT / 2][i] * XP_LO_INV; }
         }
     }
   } else {
@@ -124,7 +134,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmArgs &a, const GemmMat &
       for (int i = 0; i < 4; i++) {
         const int t = nt * 8 + 2 * j + (i & 1), r = row0 + gid + ((i >> 1) << 3);
         on[nt][i] = t < a.T && r < M.rows;
-        if (on[nt][i]) { idx[nt][i] = (size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + r; val[nt][i] = acc[nt][i]; }
+        if (on[nt][i]) { idx[nt][i] = (size_t)gemm_out_block(M, t) * M.ostride + r; val[nt][i] = acc[nt][i]; }
       }
   }
   float *out = M.out + (size_t)ks * M.split_stride;

@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(G3_BLOCK, 1) k_gemm3(const GemmArgs a, const i
               for (int t = 0; t < 8; t++) {
                 if (t < a.T && (a.planes == 1 || t < 4)) {
                   const float val = a.planes == 2 ? sum[t & 3] + sum[4 + (t & 3)] * XP_LO_INV : sum[t];
-                  out[(size_t)(M.tok_slot ? M.tok_slot[t] : t) * M.ostride + row] = val;
+                  out[(size_t)gemm_out_block(M, t) * M.ostride + row] = val;
                 }
               }
             }

@@ -82,12 +82,21 @@ __device__ __forceinline__ float part_get(const PartIn &a, size_t i) {
   return v;
 }
 
+// Several streams in one pass: row t of the pass is row t % per of stream t / per, whose row sets (and the rest of its
+// control block) lie `stride` bytes after the previous stream's.  One stream: per is larger than any row index.
+struct Streams { int per; int stride; };
+// the geometry the launchers below hand to their kernels; the engine sets it before it enqueues a pass
+void ops_set_streams(int per, int stride);
+Streams ops_streams(void);
+
 // min_per: fewest cache positions a split-K attention block takes (a multiple of 32)
 // kv_plane: halves between the hi and the lo plane of a K or V cache (max_ctx * KV * hd)
-struct AttnShape { int H, KV, hd, rope_dim; float eps; int min_per; long long kv_plane; };
+// rs_stride: bytes between the row sets of consecutive row groups (grid z of the attention kernels)
+// kv_group: halves between the caches of consecutive row groups (0: all groups read one cache, as a prompt chunk's do)
+struct AttnShape { int H, KV, hd, rope_dim; float eps; int min_per; long long kv_plane; int rs_stride; long long kv_group; };
 struct DeltaShape { int TR, GK, SZ, KC, convd, kdc, vdc; float eps; };
 
-// launchers (ops_model.cu); every kernel covers SPEC_MAXT rows at most and ignores rows >= rs->n
+// launchers (ops_model.cu); a stream has SPEC_MAXT rows at most, a kernel ignores rows >= its stream's rs->n
 int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs, int Tmax, float *x);
 int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, float eps, int d, float *xout, XPlanes xp,
                int xp_col0, float *hn_out, const RowSet *rs, int Tmax, int zero_if_pos0);
@@ -105,8 +114,9 @@ int op_attention(cudaStream_t s, const float *q, const float *Kc, const float *V
                  float *pm, float *pl, float *po, XPlanes xp, const RowSet *rs, int Tmax, __half *kg = nullptr, int kg_row0 = 0, int nz = 1);
 int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax);
+// S: the streams' state rings one after the other (s_group floats apart); nz streams
 int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,
-                   const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs);
+                   const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs, int nz = 1, long long s_group = 0);
 // A row set that no kernel of the pass in flight writes (the verify rows: k_accept sets them at the end
 // of the previous cycle) may be read before the wait on the preceding kernel, which takes one trip to L2
 // off every small kernel's critical path.  The host says so by setting bit 0 of the pointer it passes.
@@ -122,10 +132,17 @@ __device__ __forceinline__ const RowSet *rs_begin(const RowSet *rs, int &n, int 
   if (!early) { n = rs->n; pos0 = rs->pos0; }
   return rs;
 }
+// The same for row t of a pass over several streams: the row set of the row's stream, and tl, the row's index in it.
+__device__ __forceinline__ const RowSet *rs_begin_row(const RowSet *rs, Streams sg, int t, int &n, int &pos0, int &tl) {
+  const int z = t / sg.per;
+  tl = t - z * sg.per;
+  return rs_begin((const RowSet *)((uintptr_t)rs + (size_t)z * (size_t)sg.stride), n, pos0);
+}
 #endif
-int op_lookup_draft(cudaStream_t s, SpecCtl *ctl);
+int op_lookup_draft(cudaStream_t s, SpecCtl *ctl, int nz = 1);
 int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
-int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax);
+// nz streams: control blocks consecutive, result rings ring_n records apart, rows of the pass `per` apart
+int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax, int nz = 1, int per = 0);
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
-                  float *chain_h, int d);
+                  float *chain_h, int d, int nz = 1, int per = 0);
 int ops_model_setup(void);

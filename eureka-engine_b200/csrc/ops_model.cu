@@ -28,20 +28,24 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
   for (int i = 0; i < nw; i++) t += red[i];
   return t;
 }
+static Streams g_streams = {1 << 30, 0};
+void ops_set_streams(int per, int stride) { g_streams.per = per > 0 ? per : 1 << 30; g_streams.stride = stride; }
+Streams ops_streams(void) { return g_streams; }
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // ---- embedding rows (llb_embedk, tools/payload-kpair.patch:526) ---------------------------------
-__global__ void k_embed(int fmt, const uint8_t *__restrict__ W, int d, const RowSet *rs, float *__restrict__ x) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
+__global__ void k_embed(int fmt, const uint8_t *__restrict__ W, int d, const RowSet *rs, Streams sg, float *__restrict__ x) {
+  int rs_n, rs_p0, tl;
   const int t = blockIdx.y;
-  if (t >= rs_n) return;
-  const uint8_t *row = W + (size_t)rs->tok[t] * dev_row_bytes(fmt, d);
+  rs = rs_begin_row(rs, sg, t, rs_n, rs_p0, tl);
+  if (tl >= rs_n) return;
+  const uint8_t *row = W + (size_t)rs->tok[tl] * dev_row_bytes(fmt, d);
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < d; c += gridDim.x * blockDim.x) x[(size_t)t * d + c] = deq_elem(fmt, row, d, c);
 }
 int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs, int Tmax, float *x) {
-  CU_OK(llb_launch(k_embed, dim3((d + 255) / 256, Tmax), dim3(256), (size_t)(0), s, fmt, W, d, rs, x));
+  CU_OK(llb_launch(k_embed, dim3((d + 255) / 256, Tmax), dim3(256), (size_t)(0), s, fmt, W, d, rs, g_streams, x));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -56,7 +60,7 @@ int op_embed(cudaStream_t s, int fmt, const uint8_t *W, int d, const RowSet *rs,
 template <int NI>
 __global__ void __launch_bounds__(NORM_MAXT) k_norm_xp(const float *__restrict__ xin, PartIn add, const float *__restrict__ w, float eps, int d,
                                                        float *__restrict__ xout, XPlanes xp, int xp_col0, float *__restrict__ hn_out,
-                                                       const RowSet *rs, int zero_if_pos0) {
+                                                       const RowSet *rs, Streams sg, int zero_if_pos0) {
   // the norm weights depend on no kernel: their trip to DRAM overlaps the wait on the producer
   float4 wv[NI];
 #pragma unroll
@@ -64,12 +68,12 @@ __global__ void __launch_bounds__(NORM_MAXT) k_norm_xp(const float *__restrict__
     const int c = 4 * (threadIdx.x + i * blockDim.x);
     wv[i] = c < d ? *(const float4 *)(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  __shared__ float red[32];
+  int rs_n, rs_p0, tl;
   const int t = blockIdx.x;
-  if (t >= rs_n) return;
-  const bool zero = zero_if_pos0 && (rs_p0 + t == 0);
+  rs = rs_begin_row(rs, sg, t, rs_n, rs_p0, tl);
+  __shared__ float red[32];
+  if (tl >= rs_n) return;
+  const bool zero = zero_if_pos0 && (rs_p0 + tl == 0);
   const size_t row = (size_t)t * d;
   // every load of a trip is issued before the first use: one round trip to L2 per four slices
   float4 v[NI];
@@ -121,7 +125,7 @@ int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, flo
   if (d % 32 || xp_col0 % 32 || d > 4 * 4 * NORM_MAXT) return llb_fail("norm: d %d at column %d", d, xp_col0);
   const int d4 = d / 4, ni = (d4 + NORM_MAXT - 1) / NORM_MAXT;
   const int threads = (((d4 + ni - 1) / ni) + 31) & ~31;
-#define NORM_GO(NI) CU_OK(llb_launch(k_norm_xp<NI>, dim3(Tmax), dim3(threads), (size_t)(0), s, xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, zero_if_pos0))
+#define NORM_GO(NI) CU_OK(llb_launch(k_norm_xp<NI>, dim3(Tmax), dim3(threads), (size_t)(0), s, xin, add, w, eps, d, xout, xp, xp_col0, hn_out, rs, g_streams, zero_if_pos0))
   switch (ni) {
     case 1: NORM_GO(1); break;
     case 2: NORM_GO(2); break;
@@ -136,11 +140,11 @@ int op_norm_xp(cudaStream_t s, const float *xin, PartIn add, const float *w, flo
 // ---- silu(gate) * up -> planes (llb_t_siluq, tools/payload-spec2.patch:114-124) -----------------
 // scale (optional): the product of row t, columns [j seg, (j+1) seg) is multiplied by scale[t * (f / seg) + j]
 // (the routed experts' weights, folded into the activations the down matrices see)
-__global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, const float *__restrict__ scale, int seg) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
+__global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, Streams sg, const float *__restrict__ scale, int seg) {
+  int rs_n, rs_p0, tl;
   const int t = blockIdx.y, lane = threadIdx.x & 31;
-  if (t >= rs_n) return;
+  rs = rs_begin_row(rs, sg, t, rs_n, rs_p0, tl);
+  if (tl >= rs_n) return;
   const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);   // four columns per thread, eight lanes per 32-column group
   const bool on = c < f;
   float h[4] = {0.f, 0.f, 0.f, 0.f};
@@ -157,13 +161,13 @@ __global__ void __launch_bounds__(256) k_silu_xp(PartIn g, PartIn u, int f, XPla
 }
 int op_silu_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax) {
   if (f % 32) return llb_fail("silu: f %d", f);
-  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs, (const float *)nullptr, f));
+  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs, g_streams, (const float *)nullptr, f));
   CU_OK(cudaGetLastError());
   return 0;
 }
 int op_silu_scaled_xp(cudaStream_t s, PartIn g, PartIn u, int f, XPlanes xp, const RowSet *rs, int Tmax, const float *scale, int seg) {
   if (f % 32 || seg % 4 || f % seg) return llb_fail("silu: f %d, segments of %d", f, seg);
-  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs, scale, seg));
+  CU_OK(llb_launch(k_silu_xp, dim3((f / 4 + 255) / 256, Tmax), dim3(256), (size_t)(0), s, g, u, f, xp, rs, g_streams, scale, seg));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -228,7 +232,7 @@ template <int NQ> __device__ __forceinline__ void moe_route_row(const float *l, 
 // finishes last (a counter, no waiting) then routes: its warp t takes row t of the pass.
 template <int NQ>
 __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int ne, int nk, float *__restrict__ lg,
-                                                    int *__restrict__ ids, float *__restrict__ wt, unsigned int *__restrict__ ctr, const RowSet *rs) {
+                                                    int *__restrict__ ids, float *__restrict__ wt, unsigned int *__restrict__ ctr, const RowSet *rs, int n_all) {
   int rs_n, rs_p0;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.x, nrows = ne + 1;
   __shared__ float red[8][SPEC_MAXT];
@@ -239,6 +243,7 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 w0 = c0 < nc ? __ldg(wr + c0) : z4, w1 = c1 < nc ? __ldg(wr + c1) : z4;
   rs = rs_begin(rs, rs_n, rs_p0);
+  if (n_all > 0) rs_n = n_all;   // a pass over several streams: every row of the pass (a stream's idle rows cost nothing that matters)
   float acc[SPEC_MAXT];
 #pragma unroll
   for (int t = 0; t < SPEC_MAXT; t++) {
@@ -276,13 +281,15 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
 }
 static unsigned int *g_moe_ctr = nullptr;
 int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne, int nk, float *lg, int *ids, float *wt, const RowSet *rs, int Tmax) {
+  const int n_all = g_streams.stride ? Tmax : 0;
+  if (Tmax > SPEC_MAXT) return llb_fail("moe route: %d rows in a pass (at most %d)", Tmax, SPEC_MAXT);
   if (ne < 1 || ne > 1024 || nk < 1 || nk > 32 || nk > ne || d % 4) return llb_fail("moe route: %d experts, top %d, d %d", ne, nk, d);
   if (!g_moe_ctr) {
     CU_OK(cudaMalloc(&g_moe_ctr, 4));
     CU_OK(cudaMemset(g_moe_ctr, 0, 4));
   }
-  if (ne <= 256) CU_OK(llb_launch(k_moe_router<8>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs));
-  else CU_OK(llb_launch(k_moe_router<32>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs));
+  if (ne <= 256) CU_OK(llb_launch(k_moe_router<8>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs, n_all));
+  else CU_OK(llb_launch(k_moe_router<32>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs, n_all));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -299,14 +306,15 @@ __device__ __forceinline__ void kv_put(__half *c, long long plane, size_t i, flo
 }
 __global__ void k_qkrope(PartIn q, PartIn k, PartIn v, const float *__restrict__ qn_w, const float *__restrict__ kn_w,
                          const double *__restrict__ invfreq, AttnShape sh, float *__restrict__ qout, __half *__restrict__ Kc,
-                         __half *__restrict__ Vc, const RowSet *rs, int blk0) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
+                         __half *__restrict__ Vc, const RowSet *rs, Streams sg, int blk0) {
+  int rs_n, rs_p0, tl;
+  const int t = blockIdx.y, b = blockIdx.x + blk0, i = threadIdx.x, hd = sh.hd;
+  rs = rs_begin_row(rs, sg, t, rs_n, rs_p0, tl);
   extern __shared__ float hv[];
   __shared__ float red[32];
-  const int t = blockIdx.y, b = blockIdx.x + blk0, i = threadIdx.x, hd = sh.hd;
-  if (t >= rs_n) return;
-  const int pos = rs_p0 + t, kvd = sh.KV * hd;
+  if (tl >= rs_n) return;
+  const int pos = rs_p0 + tl, kvd = sh.KV * hd;
+  Kc += (size_t)(t / sg.per) * sh.kv_group; Vc += (size_t)(t / sg.per) * sh.kv_group;   // the row's stream has its own cache
   if (b >= sh.H + sh.KV) {  // V row: copied
     const int g = b - sh.H - sh.KV;
     kv_put(Vc, sh.kv_plane, (size_t)pos * kvd + g * hd + i, part_get(v, (size_t)t * kvd + g * hd + i));
@@ -348,7 +356,7 @@ int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, c
   // blocks 0 .. H-1 are the query heads, then KV key heads, then KV value heads
   const int blk0 = kv_only ? sh.H : 0;
   CU_OK(llb_launch(k_qkrope, dim3(sh.H + 2 * sh.KV - blk0, Tmax), dim3(sh.hd), (size_t)((size_t)sh.hd * 4), s, q, k, v, qn_w, kn_w, invfreq, sh, qout,
-                   (__half *)Kc, (__half *)Vc, rs, blk0));
+                   (__half *)Kc, (__half *)Vc, rs, g_streams, blk0));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -359,11 +367,11 @@ int op_qkrope(cudaStream_t s, PartIn q, PartIn k, PartIn v, const float *qn_w, c
 // grid (ceil(convd/256) + 1, Tmax): the last block computes beta = sigmoid(b), decay = exp(softplus(a + dt) * ssm_a).
 __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn bp, PartIn ap,
                              const float *__restrict__ dt, const float *__restrict__ sa, DeltaShape sh, float *__restrict__ y,
-                             float *__restrict__ beta, float *__restrict__ decay, const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
+                             float *__restrict__ beta, float *__restrict__ decay, const RowSet *rs, Streams sg) {
+  int rs_n, rs_p0, tl;
   const int t = blockIdx.y;
-  if (t >= rs_n) return;
+  rs = rs_begin_row(rs, sg, t, rs_n, rs_p0, tl);
+  if (tl >= rs_n) return;
   if (blockIdx.x == gridDim.x - 1) {
     for (int h = threadIdx.x; h < sh.TR; h += blockDim.x) {
       const float b = part_get(bp, (size_t)t * sh.TR + h), a = part_get(ap, (size_t)t * sh.TR + h);
@@ -376,10 +384,10 @@ __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn b
   }
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= sh.convd) return;
-  const int pos = rs_p0 + t;
+  const int pos = rs_p0 + tl, slot0 = (t / sg.per) * ring.ns * CONV_RING;   // a stream's ring: [K-slice][CONV_RING slots], the streams' rings one after the other
   float acc = 0.0f;
   for (int k = 0; k < sh.KC; k++) {  // tap KC-1 is the current token (tools/qwen35_engine.c:599-600)
-    const int slot = (pos - (sh.KC - 1) + k) & (CONV_RING - 1);
+    const int slot = slot0 + ((pos - (sh.KC - 1) + k) & (CONV_RING - 1));
     acc = __fadd_rn(acc, __fmul_rn(part_get(ring, (size_t)slot * sh.convd + c), cw[c * sh.KC + k]));
   }
   y[(size_t)t * sh.convd + c] = silu_f(acc);
@@ -387,7 +395,7 @@ __global__ void k_delta_conv(PartIn ring, const float *__restrict__ cw, PartIn b
 int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartIn ap, const float *dt, const float *sa,
                   DeltaShape sh, float *y, float *beta, float *decay, const RowSet *rs, int Tmax) {
   if (sh.KC > CONV_RING / 2) return llb_fail("conv kernel %d", sh.KC);
-  CU_OK(llb_launch(k_delta_conv, dim3((sh.convd + 255) / 256 + 1, Tmax), dim3(256), (size_t)(0), s, ring, cw, bp, ap, dt, sa, sh, y, beta, decay, rs));
+  CU_OK(llb_launch(k_delta_conv, dim3((sh.convd + 255) / 256 + 1, Tmax), dim3(256), (size_t)(0), s, ring, cw, bp, ap, dt, sa, sh, y, beta, decay, rs, g_streams));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -407,7 +415,7 @@ int op_delta_conv(cudaStream_t s, PartIn ring, const float *cw, PartIn bp, PartI
 __global__ void __cluster_dims__(1, 4, 1) __launch_bounds__(128)
 k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const float *__restrict__ y, const float *__restrict__ beta,
               const float *__restrict__ decay, PartIn z, const float *__restrict__ nw, DeltaShape sh, XPlanes xp,
-              const RowSet *rs) {
+              const RowSet *rs, Streams sg, long long s_group) {
   __shared__ __align__(16) float qs[SPEC_MAXT][128], ks[SPEC_MAXT][128];
   __shared__ float vs[SPEC_MAXT][32], db[SPEC_MAXT][2], os[SPEC_MAXT][32], ssq[SPEC_MAXT], tot[SPEC_MAXT];
   __shared__ float red[2 * SPEC_MAXT][4];
@@ -420,6 +428,16 @@ k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const floa
   // The committed state (ring slot sc) was written by an earlier pass and sc by that pass's accept kernel: neither
   // depends on the kernel in front, so the 16 KB a block reads from HBM are requested before the dependency wait.
   pdl_trigger();
+  {
+    // blockIdx.z: the stream -- its control block, its state ring, its rows of the pass
+    const size_t zz = blockIdx.z;
+    ctl = (const SpecCtl *)((const char *)ctl + zz * sg.stride);
+    rs = (const RowSet *)((uintptr_t)rs + zz * sg.stride);
+    S += zz * s_group;
+    const size_t r0 = sg.stride ? zz * sg.per : 0;
+    y += r0 * sh.convd; beta += r0 * sh.TR; decay += r0 * sh.TR; z.p += r0 * sh.vdc;
+  }
+  const int row0 = sg.stride ? blockIdx.z * sg.per : 0;
   const int R = *(const volatile int *)&ctl->R, sc = *(const volatile int *)&ctl->sc;
   float st[32];
   {
@@ -506,13 +524,13 @@ k_delta_fused(float *__restrict__ S, const SpecCtl *__restrict__ ctl, const floa
     const float r = 1.0f / sqrtf(tot[t] / 128.0f + sh.eps);
     const int col = hh * 128 + 32 * jq;
     const float zz = part_get(z, (size_t)t * sh.vdc + col + lane);
-    xp_store32(xp, t, 2, col, os[t][lane] * r * nwv * silu_f(zz), lane);
+    xp_store32(xp, row0 + t, 2, col, os[t][lane] * r * nwv * silu_f(zz), lane);
   }
 }
 int op_delta_fused(cudaStream_t s, float *S, const SpecCtl *ctl, const float *y, const float *beta, const float *decay, PartIn z,
-                   const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs) {
+                   const float *nw, DeltaShape sh, XPlanes xp, const RowSet *rs, int nz, long long s_group) {
   if (sh.SZ != 128) return llb_fail("DeltaNet state size %d (only 128, as host/llb_host.c:1608)", sh.SZ);
-  CU_OK(llb_launch(k_delta_fused, dim3(sh.TR, 4), dim3(128), (size_t)0, s, S, ctl, y, beta, decay, z, nw, sh, xp, rs));
+  CU_OK(llb_launch(k_delta_fused, dim3(sh.TR, 4, nz), dim3(128), (size_t)0, s, S, ctl, y, beta, decay, z, nw, sh, xp, rs, g_streams, s_group));
   return 0;
 }
 
@@ -536,12 +554,12 @@ __device__ __forceinline__ Top2 t2_warp(Top2 a) {
   return a;
 }
 __global__ void __launch_bounds__(256) k_top2_part(PartIn logits, int V, long long row_stride,
-                                                   float *__restrict__ part, const RowSet *rs) {
-  int rs_n, rs_p0;
-  rs = rs_begin(rs, rs_n, rs_p0);
-  __shared__ Top2 sh[8];
+                                                   float *__restrict__ part, const RowSet *rs, Streams sg) {
+  int rs_n, rs_p0, tl;
   const int t = blockIdx.y;
-  if (t >= rs_n) return;
+  rs = rs_begin_row(rs, sg, t, rs_n, rs_p0, tl);
+  __shared__ Top2 sh[8];
+  if (tl >= rs_n) return;
   const size_t z0 = (size_t)t * row_stride;
   const int per = (V + gridDim.x - 1) / gridDim.x, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
   Top2 a = {0.f, -1, 0.f, -1};
@@ -559,7 +577,7 @@ __global__ void __launch_bounds__(256) k_top2_part(PartIn logits, int V, long lo
   }
 }
 int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax) {
-  CU_OK(llb_launch(k_top2_part, dim3(TOP2_NB, Tmax), dim3(256), (size_t)(0), s, logits, V, row_stride, part, rs));
+  CU_OK(llb_launch(k_top2_part, dim3(TOP2_NB, Tmax), dim3(256), (size_t)(0), s, logits, V, row_stride, part, rs, g_streams));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -579,15 +597,18 @@ __device__ __forceinline__ Top2 t2_final(const float *part, int t, int lane) {
 // sampling that is "accept while argmax(row j) == draft j+1" (host/llb_sampler_impl.h:400-405).
 // Here the whole decision runs on the device and also prepares the next cycle: new p0, ring slot,
 // committed token, and the drafter's catch-up rows (host/llb_host.c:1815).
-__global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ ctl, SpecResult *__restrict__ ring, int ring_n) {
+__global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ ctl, SpecResult *__restrict__ ring, int ring_n, int per) {
   pdl_trigger();
   pdl_wait();
   __shared__ Top2 rows[SPEC_MAXT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // one block per stream: its control block, its result ring, its rows of the pass
+  ctl += blockIdx.x; ring += (size_t)blockIdx.x * ring_n;
+  const int row0 = blockIdx.x * per;
   const int T = ctl->verify.n;
-  if (T < 1) return;   // an empty pass (the sizing run at open) decides nothing
+  if (T < 1) return;   // an empty pass (the sizing run at open, a stream that is not running) decides nothing
   if (warp < T) {
-    Top2 a = t2_final(part, warp, lane);
+    Top2 a = t2_final(part, row0 + warp, lane);
     if (lane == 0) rows[warp] = a;
   }
   __syncthreads();
@@ -630,8 +651,8 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
   res->seq = ctl->seq + 1;   // written last: the host polls it
   ctl->seq += 1;
 }
-int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax) {
-  CU_OK(llb_launch(k_accept, dim3(1), dim3(32 * Tmax), (size_t)(0), s, part, ctl, ring, ring_n));
+int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax, int nz, int per) {
+  CU_OK(llb_launch(k_accept, dim3(nz), dim3(32 * (nz > 1 ? per : Tmax)), (size_t)(0), s, part, ctl, ring, ring_n, per));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -645,6 +666,7 @@ __global__ void __launch_bounds__(256) k_lookup_draft(SpecCtl *__restrict__ ctl)
   pdl_trigger();
   pdl_wait();
   __shared__ int best[3];
+  ctl += blockIdx.x;   // one block per stream
   const int *hist = ctl->hist;
   const int pos = ctl->verify.pos0;
   if (!hist || ctl->verify.n < 1) return;
@@ -674,8 +696,8 @@ __global__ void __launch_bounds__(256) k_lookup_draft(SpecCtl *__restrict__ ctl)
   }
   ctl->verify.n = 1 + n;
 }
-int op_lookup_draft(cudaStream_t s, SpecCtl *ctl) {
-  CU_OK(llb_launch(k_lookup_draft, dim3(1), dim3(256), (size_t)(0), s, ctl));
+int op_lookup_draft(cudaStream_t s, SpecCtl *ctl, int nz) {
+  CU_OK(llb_launch(k_lookup_draft, dim3(nz), dim3(256), (size_t)(0), s, ctl));
   CU_OK(cudaGetLastError());
   return 0;
 }
@@ -684,10 +706,14 @@ int op_lookup_draft(cudaStream_t s, SpecCtl *ctl) {
 // host/llb_host.c:1800-1807); it becomes verify input j and the token of the next chained row, whose hidden
 // is the drafter's own normed hidden of that last row (host/llb_host.c:1824-1827).
 __global__ void k_draft_pick(const float *__restrict__ part, const int *__restrict__ ids, SpecCtl *__restrict__ ctl,
-                             int from_chain, int j, const float *__restrict__ mt_hn, float *__restrict__ chain_h, int d) {
+                             int from_chain, int j, const float *__restrict__ mt_hn, float *__restrict__ chain_h, int d, int per) {
   pdl_trigger();
   pdl_wait();
   __shared__ int s_tok;
+  // one block per stream: its control block and its rows of the drafter pass; the chained row is the stream's row 0
+  ctl += blockIdx.x;
+  const size_t row0 = (size_t)blockIdx.x * per;
+  part += row0 * TOP2_NB * 4; mt_hn += row0 * d; chain_h += row0 * d;
   const RowSet *rs = from_chain ? &ctl->chain : &ctl->catchup;
   const int last = rs->n - 1;
   if (last < 0) return;
@@ -707,8 +733,8 @@ __global__ void k_draft_pick(const float *__restrict__ part, const int *__restri
   }
 }
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
-                  float *chain_h, int d) {
-  CU_OK(llb_launch(k_draft_pick, dim3(1), dim3(256), (size_t)(0), s, part, ids, ctl, from_chain, j, mt_hn, chain_h, d));
+                  float *chain_h, int d, int nz, int per) {
+  CU_OK(llb_launch(k_draft_pick, dim3(nz), dim3(256), (size_t)(0), s, part, ids, ctl, from_chain, j, mt_hn, chain_h, d, per));
   CU_OK(cudaGetLastError());
   return 0;
 }

@@ -71,6 +71,11 @@ def lib() -> C.CDLL:
             "llb_b200_tp_unique_id": (i32, [C.c_char_p, vp]), "llb_b200_tp_init": (i32, [C.c_char_p, i32, i32, vp]),
             "llb_b200_tp_finalize": (None, []), "llb_b200_tp_plan": (i32, [i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32)]),
             "llb_spec_open_tp": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
+            "llb_spec_open_streams": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
+            "llb_spec_streams": (i32, [vp]), "llb_spec_prefill_stream": (i32, [vp, i32, vp, i32]),
+            "llb_spec_cycle_streams": (i32, [vp, vp, vp, vp]), "llb_spec_run_cycles_streams": (i32, [vp, i32, vp]),
+            "llb_spec_position_stream": (i32, [vp, i32]), "llb_spec_stats_stream": (i32, [vp, i32, vp]),
+            "llb_spec_read_state_stream": (i32, [vp, i32, i32, i32, i32, vp, sz]),
             "llb_spec_set_prefill": (i32, [vp, i32]), "llb_spec_fast_rows": (C.c_double, [vp]),
             "llb_b200_pf_gemm": (i32, [i32, u64, i32, i32, u64, i32, u64, i32]),
             "llb_b200_gemm_ksplit": (i32, [i32, i32, i32, i32, i32]), "llb_b200_ring_ksplit": (i32, [i32, i32, i32, i32, i32, i32]),
@@ -164,7 +169,7 @@ class SpecEngine:
     tensor); `mtp` the drafter image as bytes (host) or a CUDA uint8 tensor.
     """
 
-    def __init__(self, pack, mtp=None, k: int = 3, max_ctx: int = 4096, layers: int = 0, tp: int = 1):
+    def __init__(self, pack, mtp=None, k: int = 3, max_ctx: int = 4096, layers: int = 0, tp: int = 1, streams: int = 1):
         import numpy as np
         import torch
         L = lib()
@@ -181,8 +186,14 @@ class SpecEngine:
         else:
             self._mtp_keep = mtp
             mptr, mbytes, mdev = mtp.data_ptr(), mtp.numel(), int(mtp.is_cuda)
-        self.h = handle(L.llb_spec_open_tp(pack.index_text().encode(), ptr, nbytes, int(on_dev), mptr, mbytes, mdev, k, max_ctx,
-                                           layers, tp), "llb_spec_open")
+        if streams > 1:
+            assert tp == 1
+            self.h = handle(L.llb_spec_open_streams(pack.index_text().encode(), ptr, nbytes, int(on_dev), mptr, mbytes, mdev, k,
+                                                    max_ctx, layers, streams), "llb_spec_open_streams")
+        else:
+            self.h = handle(L.llb_spec_open_tp(pack.index_text().encode(), ptr, nbytes, int(on_dev), mptr, mbytes, mdev, k, max_ctx,
+                                               layers, tp), "llb_spec_open")
+        self.streams = streams
         self.k, self.vocab, self.d = k, pack.cfg.vocab_size, pack.cfg.d_model
         self.cfg = pack.cfg
 
@@ -217,6 +228,45 @@ class SpecEngine:
         import numpy as np
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         check(self.L.llb_spec_prefill(self.h, ids.ctypes.data, len(ids)), "llb_spec_prefill")
+
+    def prefill_stream(self, b: int, ids):
+        import numpy as np
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        check(self.L.llb_spec_prefill_stream(self.h, b, ids.ctypes.data, len(ids)), "llb_spec_prefill_stream")
+
+    def cycle_streams(self):
+        """One cycle of every stream with a prompt: [(ids, top2) per stream] (empty arrays for an idle stream)."""
+        import numpy as np
+        B = self.streams
+        ids = np.zeros((B, 8), np.int32)
+        n = np.zeros(B, np.int32)
+        t2 = np.zeros((B, 8, 4), np.uint32)
+        check(self.L.llb_spec_cycle_streams(self.h, ids.ctypes.data, n.ctypes.data, t2.ctypes.data), "llb_spec_cycle_streams")
+        return [(ids[b, : n[b]].copy(), t2[b, : n[b]].copy()) for b in range(B)]
+
+    def run_cycles_streams(self, n: int):
+        import numpy as np
+        tok = np.zeros(self.streams, np.int32)
+        check(self.L.llb_spec_run_cycles_streams(self.h, n, tok.ctypes.data), "llb_spec_run_cycles_streams")
+        return tok
+
+    def stats_stream(self, b: int):
+        import numpy as np
+        out = np.zeros(19, np.uint64)
+        check(self.L.llb_spec_stats_stream(self.h, b, out.ctypes.data), "llb_spec_stats_stream")
+        return {"cycles": int(out[0]), "rows": int(out[1]), "served": int(out[2]),
+                "drafted": [int(v) for v in out[3:11]], "accepted": [int(v) for v in out[11:19]]}
+
+    def position_stream(self, b: int) -> int:
+        return self.L.llb_spec_position_stream(self.h, b)
+
+    def read_state_stream(self, b: int, what: int, il: int = 0, pos: int = 0):
+        import numpy as np
+        c = self.cfg
+        n = max(c.ssm_heads * c.ssm_state * c.ssm_state, c.convd, c.d_model, c.n_kv_heads * c.head_dim)
+        out = np.zeros(n, np.float32)
+        got = check(self.L.llb_spec_read_state_stream(self.h, b, what, il, pos, out.ctypes.data, n), "llb_spec_read_state_stream")
+        return out[:got].copy()
 
     def cycle(self):
         import numpy as np

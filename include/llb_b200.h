@@ -166,6 +166,27 @@ LLB_API int llb_b200_tp_init(const char *nccl_path, int rank, int size, const vo
 LLB_API void llb_b200_tp_finalize(void);
 LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                    size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_size);
+/* Several streams per engine (multi-stream batching inside one GPU; the reference's analogue is its prefill-only
+ * LLB_BATCH, host/llb_host.c:2151-2793).  `streams` independent sequences share every weight read: a pass carries the k + 1
+ * rows of each stream through every GEMM together (streams x (k + 1) <= 16 rows; <= 8 with routed experts), while attention,
+ * the DeltaNet scan, the drafter and the accept step run per stream inside the same launches, each stream on its own KV
+ * cache, conv ring, state ring, control block and result ring.  A stream's tokens do not depend on what the other
+ * streams do (a row's GEMM result does not depend on its neighbours).  Prompts go in per stream, at any time; a cycle
+ * advances every stream that has a prompt.  The one-stream calls (llb_spec_cycle, _generate, _pass, _run_cycles) are
+ * refused by an engine of several streams; _prefill, _stats, _position and _read_state mean stream 0. */
+LLB_API llb_spec *llb_spec_open_streams(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
+                                        size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int streams);
+LLB_API int llb_spec_streams(const llb_spec *m);
+LLB_API int llb_spec_prefill_stream(llb_spec *m, int stream, const int *ids, int n);
+/* One cycle of every stream that has a prompt, as one graph launch: ids_out[stream * 8 + i], i < n_out[stream], are that
+ * stream's emitted tokens (n_out = 0 for a stream without a prompt); top2_out (may be NULL) [stream][8][4] words. */
+LLB_API int llb_spec_cycle_streams(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2_out);
+/* n cycles back to back without a host round trip; tokens[stream] = tokens that stream emitted. */
+LLB_API int llb_spec_run_cycles_streams(llb_spec *m, int n, int *tokens);
+LLB_API int llb_spec_position_stream(const llb_spec *m, int stream);
+LLB_API int llb_spec_stats_stream(const llb_spec *m, int stream, unsigned long long *out19);
+LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il, int pos, float *out, size_t n);
+
 /* Test entry (no GPU needed): rank `rank` of `size`'s share of a model with H query heads, KV kv heads, FFN width f, GK
  * DeltaNet groups and TR value heads: out[10] = H_l, h0, KV_l, kv0, f_l, f0, GK_l, g0, TR_l, reps; -1 if it does not split. */
 LLB_API int llb_b200_tp_plan(int rank, int size, int H, int KV, int f, int GK, int TR, int *out10);
