@@ -206,6 +206,124 @@ def run_tp(args, rank, world, local):
     dist.destroy_process_group()
 
 
+STREAM_CASES = {
+    # config: (builder, workload words, prompt, default k, default streams per GPU, metric)
+    2: ("cfg_c2", "config 2: 27B-shape hybrid (d 5120, 64 layers, f 17408, V 151936), Q4_K_M, MTP k=%d greedy, prompt %d, %d streams per GPU",
+        3011, 3, 4),
+    3: ("cfg_c3", "config 3: 35B-A3B-shape MoE hybrid (d 2048, 40 layers, 256 experts top 8 + shared, V 151936), Q4_K_S, prompt-lookup k=%d "
+        "greedy, prompt %d, %d streams per GPU", 512, 1, 4),
+    4: ("cfg_c4", "config 4: 9B-shape hybrid (d 4096, 32 layers, f 12288, V 151936), Q8_0, MTP k=%d greedy, prompt %d, %d streams per GPU",
+        32768, 3, 4),
+}
+
+
+def streams_bytes(packs, pack, positions, rows: int) -> float:
+    """Algorithmic bytes of one verify pass over several streams: every dense matrix and the head ONCE, one embedding row
+    per row of the pass, the K/V rows of every stream's context, and for routed experts one expert block per (row, slot)."""
+    c = pack.cfg
+    b = 0.0
+    ne = getattr(c, "n_experts", 0) or 0
+    for e in pack.entries:
+        if e.name == "token_embd.weight":
+            b += rows * packs.row_bytes(e.ty, e.cols)
+        elif "_exps." in e.name:
+            b += e.nbytes / ne * rows * c.n_experts_used
+        elif e.name == "output.weight" or (e.name.startswith("blk.") and e.rows > 1 and e.ty != "F32"):
+            b += e.nbytes
+    n_full = sum(1 for i in range(c.n_layers) if c.is_full(i))
+    for p in positions:
+        b += n_full * 2.0 * p * c.n_kv_heads * c.head_dim * 4
+    return b
+
+
+def run_streams(args, rank, world, local):
+    """Several streams per GPU sharing one weight read (llb_spec_open_streams), every GPU its own replica and streams
+    (weak scaling, no collective).  A step is one cycle of all the GPU's streams; value = tokens of all streams / s."""
+    import numpy as np
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    llb, packs = pkg.llb, pkg.packs
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    llb.init(local)
+    builder, words, prompt_len, k_def, b_def = STREAM_CASES[args.config]
+    k = args.k if args.k >= 0 else k_def
+    B = args.streams if args.streams > 0 else b_def
+    n_prompt = args.prompt if args.prompt > 0 else prompt_len
+    cfg = getattr(packs, builder)()
+    pack = packs.build_pack(cfg, device=f"cuda:{local}", layers=args.layers or None)
+    moe = bool(getattr(cfg, "n_experts", 0))
+    mtp = None if (moe or k == 0) else packs.aux1_bytes(packs.build_mtp(pack))
+    steps, warm = args.steps, max(args.warmup, 3)
+    max_ctx = n_prompt + (steps + warm + 8) * (k + 1) + 64
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    eng = llb.SpecEngine(pack, mtp, k=k, max_ctx=max_ctx, streams=B)
+    eng.set_prefill(True)
+    torch.cuda.synchronize()
+    t_pre = time.time()
+    for b in range(B):
+        eng.prefill_stream(b, packs.synth_prompt(100 * rank + b + 3, n_prompt, cfg.vocab_size))
+    torch.cuda.synchronize()
+    t_pre = time.time() - t_pre
+    st = torch.cuda.ExternalStream(llb.lib().llb_b200_stream())
+    sampler = ClockSampler(local)
+    sampler.start()
+    eng.run_cycles_streams(warm)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    toks = int(eng.run_cycles_streams(steps).sum())
+    e1.record(st)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    # end to end: one graph launch and B result records per cycle, the host reading every stream's tokens
+    t0 = time.perf_counter()
+    n_e2e = 0
+    for _ in range(steps):
+        n_e2e += sum(len(i) for i, _ in eng.cycle_streams())
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    ver_ms = eng.time_verify(10)
+    positions = [eng.position_stream(b) + k + 1 for b in range(B)]
+    vbytes = streams_bytes(packs, pack, positions, B * (k + 1))
+    peak, peak_src = peaks()
+    (ms, e2e_s), (toks, n_e2e) = pkg.dp.aggregate([ms, e2e_s], [float(toks), float(n_e2e)], device=f"cuda:{local}")
+    if rank == 0:
+        acc = [eng.stats_stream(b) for b in range(B)]
+        line = {
+            "metric": "spec-decode tok/s per B200 over all of its streams; verify-step HBM GB/s", "value": toks / (ms / 1000.0), "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": words % (k, n_prompt, B), "streams_per_gpu": B, "rows_per_pass": B * (k + 1), "parallelism": f"stream-dp{world}",
+                       "layers": args.layers or cfg.n_layers, "l2": "inputs larger than L2: a cycle streams the whole model",
+                       "drafter": "prompt lookup" if mtp is None and k > 0 else ("MTP" if k > 0 else "none"),
+                       "tokens_per_cycle_per_stream": toks / (steps * world * B),
+                       "accepted_by_position": [round(sum(a["accepted"][j] for a in acc) / max(1, sum(a["drafted"][j] for a in acc)), 4) for j in range(1, k + 1)],
+                       "prefill_s": round(t_pre, 3), "prefill_tok_s": round(B * n_prompt / t_pre, 1)},
+            "cycle_ms": ms / steps, "tok_s_per_stream": toks / (ms / 1000.0) / (B * world),
+            "wait_errors": llb.lib().llb_b200_wait_errors(), "clocks": clocks,
+            "e2e": {"value": n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 216 * B,
+                    "api": "llb_spec_cycle_streams: one graph launch, one result record per stream read back per cycle"},
+            "gpu_launches": eng.graph_nodes(0) * steps,
+            "verify_step": {"bytes": vbytes, "ms": ver_ms, "GBs": vbytes / ver_ms / 1e6, "frac": vbytes / ver_ms / 1e6 / peak, "peak": peak,
+                            "peak_source": peak_src, "kernels": eng.graph_nodes(2),
+                            "what": "dense weights and head once, KV of every stream, one expert block per (row, slot)"},
+        }
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -217,6 +335,10 @@ def main():
     ap.add_argument("--tp", action="store_true", help="one stream over all GPUs, tensor parallel with an NCCL all-reduce per row-split projection (strong scaling)")
     ap.add_argument("--no-plain", action="store_true", help="skip the plain-decoding (k = 0) leg")
     ap.add_argument("--exact-prefill", action="store_true", help="feed the prompt through the 8-row verify pass instead of the dense tcgen05 path")
+    ap.add_argument("--streams", type=int, default=0, help="several streams per GPU sharing one weight read (with --config; 0: the configuration's default)")
+    ap.add_argument("--config", type=int, default=0, choices=[0, 2, 3, 4], help="a multi-stream line for configuration 2, 3 or 4 (extra lines; the default run is the headline)")
+    ap.add_argument("--k", type=int, default=-1, help="drafts per cycle of a --config line")
+    ap.add_argument("--prompt", type=int, default=0, help="prompt length of a --config line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -229,6 +351,9 @@ def main():
 
     if args.tp and world > 1:
         run_tp(args, rank, world, local)
+        return
+    if args.config:
+        run_streams(args, rank, world, local)
         return
     import numpy as np
     import torch

@@ -136,6 +136,28 @@ def test_streams_with_the_prompt_lookup_drafter(pkg, packs, oracle, llb):
         eng.close()
 
 
+@pytest.mark.parametrize("k,B", [(3, 2), (1, 4), (0, 8)])
+def test_streams_of_a_routed_expert_model(pkg, packs, oracle, llb, k, B):
+    """Routed experts: the router runs over every row of the pass and the expert launches take each row's own experts;
+    at most eight rows a pass.  Plain decoding of eight streams, and the prompt-lookup drafter on two and four."""
+    cfg = packs.cfg_tiny_moe()
+    pack = packs.build_pack(cfg)
+    base = [packs.synth_prompt(50 + b, 6, cfg.vocab_size) for b in range(B)]
+    prompts = [np.concatenate([p, p, p[:2]]).astype(np.int32) for p in base]
+    steps = 16
+    refs = _oracle_runs(oracle, pack, None, prompts, steps, k, lookup=k > 0)
+    eng = pkg.llb.SpecEngine(pack, None, k=k, max_ctx=96, streams=B)
+    try:
+        for b, p in enumerate(prompts):
+            eng.prefill_stream(b, p)
+        ids, t2 = _drive(eng, steps, range(B))
+        for b in range(B):
+            ref_ids, ref_top2, st = refs[b]
+            assert _prefix(ids[b], ref_ids, ref_top2) == steps, b
+    finally:
+        eng.close()
+
+
 def test_streams_at_the_27b_layer_shapes(pkg, packs, oracle, llb):
     """Four streams of k + 1 = 4 rows (16 rows, 32 plane columns) on config 2's own layer shapes, truncated to four
     layers and a small vocabulary: Q4_K and Q6_K in one layer, K = 17408 split 12 to 14 ways, 48 value heads over 16
