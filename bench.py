@@ -161,7 +161,7 @@ def run_tp(args, rank, world, local):
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     llb.init(local)
-    llb.tp_init(device=f"cuda:{local}")
+    llb.tp_init(device=f"cuda:{local}", peer=not args.nccl_allreduce)
     packs, pack, mtp, prompt = build_model(f"cuda:{local}", layers=args.layers or None)
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
@@ -200,7 +200,9 @@ def run_tp(args, rank, world, local):
                 "clocks": clocks, "gpu_launches": eng.graph_nodes(0) * steps,
                 "verify_step": {"ms": ver_ms, "kernels": eng.graph_nodes(2)},
                 "all_reduce": {"per_pass": ar[0], "eager_us_per_pass": ar[1], "share_of_eager_pass": ar[1] / total if total else None,
-                               "what": "NCCL all-reduce of a [4, 5120] f32 tile after attn_output / ssm_out and after ffn_down; eager per-op event timing"}}
+                               "kind": "NCCL" if args.nccl_allreduce else "one-shot kernel over peer memory (K-slice sum, peer stores, flag wait, rank-order sum)",
+                               "what": "all-reduce of a [4, 5120] f32 tile after attn_output / ssm_out and after ffn_down; eager per-op event timing"},
+                "wait_errors": llb.lib().llb_b200_wait_errors()}
         print(json.dumps(line), flush=True)
     eng.close()
     dist.destroy_process_group()
@@ -333,6 +335,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (debugging only; the number is then not the headline)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--tp", action="store_true", help="one stream over all GPUs, tensor parallel with an NCCL all-reduce per row-split projection (strong scaling)")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="with --tp: NCCL all-reduces instead of the library's one-shot kernel over peer memory")
     ap.add_argument("--no-plain", action="store_true", help="skip the plain-decoding (k = 0) leg")
     ap.add_argument("--exact-prefill", action="store_true", help="feed the prompt through the 8-row verify pass instead of the dense tcgen05 path")
     ap.add_argument("--streams", type=int, default=0, help="several streams per GPU sharing one weight read (with --config; 0: the configuration's default)")

@@ -4,6 +4,7 @@
 
 #include "host.cuh"
 #include "pf.cuh"
+#include "tp.cuh"
 
 LlbCtx g_llb;
 
@@ -218,12 +219,12 @@ int llb_b200_use_fused_ffn(int on) {
 }
 int llb_b200_wait_errors(void) {
   NEED_INIT(-1)
-  const int a = gemm_wait_errors(), b = pf_wait_errors();
-  return a < 0 || b < 0 ? -1 : (a | b);
+  const int a = gemm_wait_errors(), b = pf_wait_errors(), c = tp_wait_errors();
+  return a < 0 || b < 0 || c < 0 ? -1 : (a | b | c);
 }
 int llb_b200_wait_errors_clear(void) {
   NEED_INIT(-1)
-  return gemm_wait_errors_clear() || pf_wait_errors_clear() ? -1 : 0;
+  return gemm_wait_errors_clear() || pf_wait_errors_clear() || tp_wait_errors_clear() ? -1 : 0;
 }
 int llb_b200_wait_selftest(int which, int limit) {
   NEED_INIT(-1)

@@ -495,6 +495,8 @@ static int tp_reduce(llb_spec *m, const OutBuf &part, OutBuf &whole) {
     whole.cap = n;
   }
   whole.ns = 1; whole.stride = 0;
+  // peer buffers open: one kernel adds the K-slices, stores the tile into every peer and adds what the peers stored here
+  if (tp_peer_ready()) return tp_allreduce_parts(part.p, part.ns, part.stride, n, whole.p);
   CK(ops_sum_parts(g_llb.stream, part.p, part.ns, part.stride, (int)n, whole.p));
   return tp_allreduce(whole.p, n);
 }
@@ -1215,6 +1217,7 @@ static llb_spec *open_any(const char *index_text, const void *pack, size_t pack_
   // (an eager pass at either width first: a K-split, and so a buffer's size, may differ between them)
   bool bad = false;
   const int w_spec = m->B * m->Tspec, w_pf = m->B > 1 ? w_spec : m->Tpf;
+  if (m->tp.size > 1 && tp_host_barrier()) { llb_spec_close(m); return nullptr; }   // the ranks finished loading at different times
   {
     StreamScope scope(m);
     set_width(m, w_pf);
@@ -1301,6 +1304,7 @@ static int prefill_stream(llb_spec *m, int b, const int *ids, int n) {
   if (n + m->Tpf + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
   for (int i = 0; i < n; i++) if (ids[i] < 0 || ids[i] >= m->V) return llb_fail("prefill: token %d out of range", ids[i]);
   CK(reset_stream(m, b));
+  if (m->tp.size > 1) CK(tp_host_barrier());
   // the other streams sit this out: with no rows in their control blocks every kernel skips them, and the accept
   // kernel neither decides nor reports for them; their blocks are put back afterwards
   std::vector<SpecCtl> keep;
@@ -1369,6 +1373,7 @@ LLB_API int llb_spec_cycle(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2
   if (!q.primed) return llb_fail("llb_spec_cycle before llb_spec_prefill");
   // every row of the cycle, and the drafter's chained rows, must fit: no clipped cycles
   if (q.pos + m->Tmax >= m->max_ctx) return llb_fail("context of %d positions is full", m->max_ctx);
+  if (m->tp.size > 1) CK(tp_host_barrier());
   CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
   SpecResult r;
   CK(wait_result(m, 0, &r));
@@ -1486,6 +1491,7 @@ LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap) {
   if (!q.primed) return llb_fail("llb_spec_run_cycles before llb_spec_prefill");
   if (n > m->res_n) return llb_fail("at most %d cycles per call", m->res_n);
   if (q.pos + n * m->Tmax >= m->max_ctx) return llb_fail("context of %d positions cannot take %d more cycles", m->max_ctx, n);
+  if (m->tp.size > 1) CK(tp_host_barrier());
   for (int i = 0; i < n; i++) CU_OK(cudaGraphLaunch(m->g_spec, g_llb.stream));
   int total = 0;
   for (int i = 0; i < n; i++) {
@@ -1501,6 +1507,7 @@ LLB_API int llb_spec_run_cycles(llb_spec *m, int n, int *ids, int cap) {
 // Device time of the verify pass alone at the current position: `iters` replays, CUDA events on the
 // library's stream.  Replaying commits nothing (no accept kernel), so the sequence is unchanged.
 LLB_API int llb_spec_time_verify(llb_spec *m, int iters, float *ms_per_pass) {
+  if (m->tp.size > 1) CK(tp_host_barrier());
   cudaEvent_t a, b;
   CU_OK(cudaEventCreate(&a)); CU_OK(cudaEventCreate(&b));
   CU_OK(cudaGraphLaunch(m->g_verify, g_llb.stream));
@@ -1560,6 +1567,7 @@ LLB_API int llb_spec_time_gemm(llb_spec *m, int iters, float *us_per_launch, dou
 
 // One eager verify pass with an event after every op; writes "name count total_us" lines into buf.
 LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap) {
+  if (m->tp.size > 1) CK(tp_host_barrier());
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   for (int rep = 0; rep < 2; rep++) {      // the second pass is the one reported (warm)
     for (auto &r : g_prof) cudaEventDestroy(r.ev);

@@ -4,7 +4,14 @@
 
 int tp_rank(void);
 int tp_size(void);
-int tp_allreduce(float *buf, size_t n);   // sum over the ranks, in place, on the library's stream
+int tp_allreduce(float *buf, size_t n);   // sum over the ranks, in place, on the library's stream (NCCL)
+// the one-shot all-reduce over peer memory (when the peer buffers are open): whole[n] = sum over ranks of the sum over the
+// ns K-slices of part, one kernel on the library's stream
+bool tp_peer_ready(void);
+int tp_allreduce_parts(const float *part, int ns, long long stride, size_t n, float *whole);
+int tp_host_barrier(void);   // all ranks meet on the host (no-op on one rank)
+int tp_wait_errors(void);
+int tp_wait_errors_clear(void);
 
 // A set of half-open ranges [start, start + count) of rows or columns, in order.
 struct TpSel {

@@ -71,6 +71,7 @@ def lib() -> C.CDLL:
             "llb_b200_tp_unique_id": (i32, [C.c_char_p, vp]), "llb_b200_tp_init": (i32, [C.c_char_p, i32, i32, vp]),
             "llb_b200_tp_finalize": (None, []), "llb_b200_tp_plan": (i32, [i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32)]),
             "llb_spec_open_tp": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
+            "llb_b200_tp_peer_alloc": (i32, [vp]), "llb_b200_tp_peer_open": (i32, [vp, i32]), "llb_b200_tp_peer_active": (i32, []),
             "llb_spec_open_streams": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
             "llb_spec_streams": (i32, [vp]), "llb_spec_prefill_stream": (i32, [vp, i32, vp, i32]),
             "llb_spec_cycle_streams": (i32, [vp, vp, vp, vp]), "llb_spec_run_cycles_streams": (i32, [vp, i32, vp]),
@@ -128,9 +129,11 @@ def exchange_unique_id(make_id, rank: int, device=None):
     return bytes(t.cpu().numpy().tobytes())
 
 
-def tp_init(device=None):
+def tp_init(device=None, peer: bool = True):
     """Join the tensor-parallel communicator of the torch.distributed group this process belongs to (after init(device)):
-    rank 0 makes the NCCL id, torch.distributed carries it to the others.  Returns (rank, size)."""
+    rank 0 makes the NCCL id, torch.distributed carries it to the others.  peer: also open the ranks' peer buffers, so
+    that the engines' all-reduces are the library's own one-shot kernel over peer memory instead of NCCL calls.
+    Returns (rank, size)."""
     import torch.distributed as dist
     L = lib()
     rank, size = dist.get_rank(), dist.get_world_size()
@@ -142,6 +145,17 @@ def tp_init(device=None):
     uid = exchange_unique_id(make, rank, device)
     keep = C.create_string_buffer(uid, 128)
     check(L.llb_b200_tp_init(None, rank, size, keep), "llb_b200_tp_init")
+    if peer and size > 1:
+        import torch
+        h = C.create_string_buffer(64)
+        check(L.llb_b200_tp_peer_alloc(h), "llb_b200_tp_peer_alloc")
+        mine = torch.frombuffer(bytearray(h.raw), dtype=torch.uint8).clone()
+        if device is not None:
+            mine = mine.to(device)
+        every = [torch.zeros_like(mine) for _ in range(size)]
+        dist.all_gather(every, mine)
+        blob = b"".join(bytes(t.cpu().numpy().tobytes()) for t in every)
+        check(L.llb_b200_tp_peer_open(C.create_string_buffer(blob, len(blob)), size), "llb_b200_tp_peer_open")
     return rank, size
 
 

@@ -164,6 +164,17 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
 LLB_API int llb_b200_tp_unique_id(const char *nccl_path, void *id128);
 LLB_API int llb_b200_tp_init(const char *nccl_path, int rank, int size, const void *id128);
 LLB_API void llb_b200_tp_finalize(void);
+/* The library's own all-reduce instead of NCCL's: ONE kernel per all-reduce that adds the projection's K-slices, stores the
+ * rank's [T, d_model] tile into a slot of every peer's buffer (plain stores through a peer mapping over NVLink; no multicast,
+ * no multimem), raises a flag beside it, waits -- bounded, llb_b200_wait_errors reports a wait that ran out -- for the peers'
+ * flags and adds the slots in rank order.  Every rank allocates its buffer and gets a 64-byte inter-process handle for it
+ * (llb_b200_tp_peer_alloc, after llb_b200_tp_init); the host program gathers the handles of all ranks in rank order and
+ * every rank opens them (llb_b200_tp_peer_open).  Engines opened afterwards use the peer buffers; the ranks meet on the host
+ * (a four-byte NCCL all-reduce) at the start of every call that enqueues passes, so the device-side waits only bridge the
+ * skew of ranks running in step. */
+LLB_API int llb_b200_tp_peer_alloc(void *handle64);
+LLB_API int llb_b200_tp_peer_open(const void *handles, int n);
+LLB_API int llb_b200_tp_peer_active(void);
 LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                    size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_size);
 /* Several streams per engine (multi-stream batching inside one GPU; the reference's analogue is its prefill-only

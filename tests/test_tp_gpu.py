@@ -21,7 +21,7 @@ def _cases(packs):
     yield "c2_4layers", packs.cfg_c2(n_layers=4, vocab_size=2048), "cuda", 45
 
 
-def _rank(rank, world, port, q):
+def _rank(rank, world, port, q, peer):
     import sys
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
@@ -32,7 +32,8 @@ def _rank(rank, world, port, q):
         torch.cuda.set_device(rank)
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
         llb.init(rank)
-        llb.tp_init()
+        llb.tp_init(peer=peer)
+        assert llb.lib().llb_b200_tp_peer_active() == int(peer)
         out = {}
         for name, cfg, where, n_prompt in _cases(packs):
             pack = packs.build_pack(cfg, device=f"cuda:{rank}" if where == "cuda" else "cpu")
@@ -47,6 +48,7 @@ def _rank(rank, world, port, q):
                 eng.close()
             out[name] = res
             dist.barrier()
+        assert llb.lib().llb_b200_wait_errors() == 0
         q.put((rank, out, None))
         dist.destroy_process_group()
     except Exception as ex:  # the parent must hear about it instead of waiting for the queue
@@ -54,14 +56,17 @@ def _rank(rank, world, port, q):
         q.put((rank, None, traceback.format_exc()))
 
 
-def test_two_ranks_equal_one_gpu():
+@pytest.mark.parametrize("peer", [False, True], ids=["nccl", "peer-stores"])
+def test_two_ranks_equal_one_gpu(peer):
+    """peer: the all-reduces are the library's one-shot kernel over peer memory (plain stores into the other rank's buffer,
+    bounded flag waits) instead of NCCL calls."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
+    ps = [ctx.Process(target=_rank, args=(r, 2, port, q, peer)) for r in range(2)]
     for p in ps:
         p.start()
     got = {}
