@@ -16,6 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(HERE, "_build", "libq35_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libq35ref.so")
 REF_CLI = os.path.join(HERE, "_ref", "qwen35_ref")
+REF_SMP_SO = os.path.join(HERE, "_ref", "libllbsmp.so")
 
 _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 
@@ -44,6 +45,71 @@ class Cfg(C.Structure):
 class SpecStats(C.Structure):
     _fields_ = [("cycles", C.c_uint64), ("rows", C.c_uint64), ("served", C.c_uint64),
                 ("drafted", C.c_uint64 * 8), ("accepted", C.c_uint64 * 8)]
+
+
+class SmpParams(C.Structure):
+    """Sampler parameters, in the oracle's layout (oracle/q35_sampler.c: Q35Smp)."""
+    _fields_ = [("temp", _f), ("top_p", _f), ("min_p", _f), ("top_k", _i), ("repeat_penalty", _f), ("repeat_last_n", _i),
+                ("presence", _f), ("frequency", _f), ("seed", C.c_uint64), ("min_keep", _i), ("n_bias", _i),
+                ("bias_ids", _i * 64), ("bias_vals", _f * 64)]
+
+    @classmethod
+    def make(cls, temp=0.0, top_p=1.0, min_p=0.0, top_k=0, repeat_penalty=1.0, repeat_last_n=64, presence=0.0, frequency=0.0,
+             seed=0, min_keep=0, bias=()):
+        p = cls()
+        p.temp, p.top_p, p.min_p, p.top_k = temp, top_p, min_p, top_k
+        p.repeat_penalty, p.repeat_last_n, p.presence, p.frequency = repeat_penalty, repeat_last_n, presence, frequency
+        p.seed, p.min_keep, p.n_bias = seed, min_keep, len(bias)
+        for j, (t, v) in enumerate(bias):
+            p.bias_ids[j], p.bias_vals[j] = t, v
+        return p
+
+
+class RefSmpParams(C.Structure):
+    """LlbSmpParams of the reference (host/llb_sampler.h:38-52), for oracle/_ref/libllbsmp.so."""
+    _fields_ = [("temp", _f), ("top_p", _f), ("min_p", _f), ("top_k", _i), ("repeat_penalty", _f), ("repeat_last_n", _i),
+                ("presence", _f), ("frequency", _f), ("seed", C.c_uint64), ("min_keep", _i), ("n_logprobs", _i), ("max_tokens", _i),
+                ("n_bias", _i), ("bias_ids", _i * 64), ("bias_vals", _f * 64)]
+
+
+def smp_row(params: SmpParams, logits: np.ndarray, hist, draft: int, pos: int):
+    """The oracle's sampler on one row: (token, accepted, margin)."""
+    L = Oracle.lib()
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    h = np.ascontiguousarray(hist if hist is not None else [], dtype=np.int32)
+    acc, mg = _i(0), C.c_double(0)
+    t = L.q35_smp_row(C.byref(params), _p(logits), len(logits), _p(h) if len(h) else None, len(h), draft, C.c_uint64(pos), C.byref(acc), C.byref(mg))
+    return t, acc.value, mg.value
+
+
+def ref_smp_row(params: SmpParams, logits: np.ndarray, hist, draft: int, pos: int):
+    """The reference's own sampler (oracle/_ref/libllbsmp.so: llb_smp_new / _history / _verify / _sample) on one row."""
+    L = C.CDLL(REF_SMP_SO)
+    L.llb_smp_new.restype = _vp
+    L.llb_smp_new.argtypes = [_vp, _i]
+    L.llb_smp_free.argtypes = [_vp]
+    L.llb_smp_history.argtypes = [_vp, _vp, _i]
+    L.llb_smp_sample.argtypes = [_vp, _vp, C.c_uint64]
+    L.llb_smp_verify.argtypes = [_vp, _vp, _i, _vp, C.c_uint64, _vp]
+    rp = RefSmpParams()
+    for n in ("temp", "top_p", "min_p", "top_k", "repeat_penalty", "repeat_last_n", "presence", "frequency", "seed", "min_keep", "n_bias"):
+        setattr(rp, n, getattr(params, n))
+    for j in range(params.n_bias):
+        rp.bias_ids[j], rp.bias_vals[j] = params.bias_ids[j], params.bias_vals[j]
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    s = L.llb_smp_new(C.byref(rp), len(logits))
+    try:
+        if hist is not None and len(hist):
+            h = np.ascontiguousarray(hist, dtype=np.int32)
+            L.llb_smp_history(s, _p(h), len(h))
+        acc = _i(0)
+        if draft >= 0:
+            t = L.llb_smp_verify(s, _p(logits), draft, None, C.c_uint64(pos), C.byref(acc))
+        else:
+            t = L.llb_smp_sample(s, _p(logits), C.c_uint64(pos))
+    finally:
+        L.llb_smp_free(s)
+    return t, acc.value
 
 
 class Oracle:
@@ -99,6 +165,8 @@ class Oracle:
             L.q35_mtp_rows.restype = _i
             L.q35_mtp_rows.argtypes = [_vp, _i, _i, _vp, _vp, _vp]
             L.q35_threads.argtypes = [_i]
+            L.q35_smp_row.restype = _i
+            L.q35_smp_row.argtypes = [_vp, _vp, _i, _vp, _i, _i, C.c_uint64, _vp, _vp]
             cls._lib = L
         return cls._lib
 

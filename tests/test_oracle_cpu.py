@@ -180,3 +180,51 @@ def test_moe_greedy_runs_and_is_deterministic(packs, oracle):
     ids2, _ = a.greedy(prompt, 8)
     assert list(ids1) == list(ids2) and len(ids1) == 8
     a.close()
+
+
+def _sampler_cases():
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "sampler_vectors.npz"))
+    from oracle import bindings
+    for name in z["names"]:
+        name = str(name)
+        p = bindings.SmpParams.from_buffer_copy(z[name + ".params"].tobytes())
+        hl = z[name + ".hist_len"]
+        off = np.concatenate([[0], np.cumsum(hl)])
+        for r in range(len(hl)):
+            yield name, r, p, z[name + ".logits"][r], z[name + ".hist"][off[r]:off[r + 1]], int(z[name + ".draft"][r]), int(z[name + ".pos"][r]), \
+                int(z[name + ".tok"][r]), int(z[name + ".acc"][r])
+
+
+def test_sampler_oracle_equals_the_reference_vectors():
+    """The oracle's restatement of the sampler chain and of the speculative verify step (oracle/q35_sampler.c) returns, on
+    every golden row, the token and the accept flag the reference's own sampler pack returned (host/llb_sampler.c, run by
+    tests/golden/make_golden_sampler.py): every stage of the chain, alone and combined."""
+    from oracle import bindings
+    n = acc = 0
+    for name, r, p, lg, hist, draft, pos, tok, a in _sampler_cases():
+        t, ac, _ = bindings.smp_row(p, lg, hist, draft, pos)
+        assert (t, ac) == (tok, a), (name, r, t, ac, tok, a)
+        n += 1
+        acc += a
+    assert n >= 200 and acc > 10
+
+
+def test_sampler_oracle_equals_the_reference_build_when_present():
+    """On fresh random rows, against the reference's sampler compiled from its own sources (when it is on this machine)."""
+    from oracle import bindings
+    if not os.path.exists(bindings.REF_SMP_SO):
+        pytest.skip("oracle/_ref/libllbsmp.so is not built")
+    rng = np.random.default_rng(77)
+    for it in range(150):
+        V = int(rng.integers(8, 700))
+        p = bindings.SmpParams.make(temp=float(rng.choice([0.0, 0.5, 1.0, 1.4])), top_k=int(rng.choice([0, 1, 5, 40, 300])),
+                                    top_p=float(rng.choice([1.0, 0.95, 0.5])), min_p=float(rng.choice([0.0, 0.05, 0.3])),
+                                    repeat_penalty=float(rng.choice([1.0, 1.2])), presence=float(rng.choice([0.0, 1.5])),
+                                    frequency=float(rng.choice([0.0, 0.1])), repeat_last_n=int(rng.choice([0, 4, 64])),
+                                    seed=int(rng.integers(0, 1 << 40)), min_keep=int(rng.choice([0, 1, 3])),
+                                    bias=((int(rng.integers(0, V)), float(rng.normal() * 5)),) if it % 3 == 0 else ())
+        lg = (rng.standard_normal(V) * float(rng.choice([0.3, 2.0, 8.0]))).astype(np.float32)
+        hist = rng.integers(0, V, int(rng.integers(0, 90))).astype(np.int32)
+        draft = int(np.argsort(-lg)[rng.integers(0, 3)]) if it % 4 else -1
+        pos = int(rng.integers(1, 1 << 20))
+        assert bindings.smp_row(p, lg, hist, draft, pos)[:2] == bindings.ref_smp_row(p, lg, hist, draft, pos), (it, V)
