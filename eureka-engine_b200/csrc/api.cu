@@ -5,6 +5,7 @@
 #include "host.cuh"
 #include "pf.cuh"
 #include "tp.cuh"
+#include "sampler.cuh"
 
 LlbCtx g_llb;
 
@@ -225,6 +226,50 @@ int llb_b200_wait_errors(void) {
 int llb_b200_wait_errors_clear(void) {
   NEED_INIT(-1)
   return gemm_wait_errors_clear() || pf_wait_errors_clear() || tp_wait_errors_clear() ? -1 : 0;
+}
+// the device sampler on T rows of given logits (test entry; the engine runs the same kernel from its control blocks)
+int llb_b200_smp_rows(const llb_smp_params *p, llb_b200_dptr logits, int T, int V, const int *drafts, const long long *pos, const int *win,
+                      const int *nwin, int *tok_out, int *acc_out, float *val_out) {
+  NEED_INIT(-1)
+  if (!p || T < 1 || T > 64 || V < 1) return llb_fail("smp_rows: T %d, V %d", T, V);
+  SmpDev d;
+  bool argmax_only = false;
+  if (smp_prepare(p, &d, &argmax_only)) return -1;
+  if (backend_graph_bail()) return -1;
+  void *buf = nullptr;
+  const size_t b_adj = (size_t)T * V * 4, b_win = (size_t)T * SMP_MAX_WIN * 4, b_i = (size_t)T * 4, b_l = (size_t)T * 8;
+  CU_OK(cudaMalloc(&buf, b_adj + b_win + 5 * b_i + b_l + 16));
+  char *c = (char *)buf;
+  float *adj = (float *)c; c += b_adj;
+  long long *d_pos = (long long *)c; c += b_l;
+  int *d_win = (int *)c; c += b_win;
+  int *d_draft = (int *)c; c += b_i;
+  int *d_nwin = (int *)c; c += b_i;
+  int *d_tok = (int *)c; c += b_i;
+  int *d_acc = (int *)c; c += b_i;
+  float *d_val = (float *)c; c += b_i;
+  unsigned int *d_err = (unsigned int *)c;
+  cudaStream_t s = g_llb.stream;
+  int rc = 0;
+  cudaError_t e = cudaMemsetAsync(buf, 0, b_adj + b_win + 5 * b_i + b_l + 16, s);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_pos, pos, b_l, cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_draft, drafts, b_i, cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess && win) e = cudaMemcpyAsync(d_win, win, b_win, cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess && nwin) e = cudaMemcpyAsync(d_nwin, nwin, b_i, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) rc = llb_fail("smp_rows: %s", cudaGetErrorString(e));
+  if (!rc) rc = op_smp_rows(s, d, PartIn{(const float *)(uintptr_t)logits, 1, 0}, V, adj, nullptr, T, d_draft, d_pos, d_win, d_nwin, d_tok, d_val, d_acc, d_err);
+  unsigned int err = 0;
+  if (!rc) {
+    e = cudaMemcpyAsync(tok_out, d_tok, b_i, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(acc_out, d_acc, b_i, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(val_out, d_val, b_i, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&err, d_err, 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) rc = llb_fail("smp_rows: %s", cudaGetErrorString(e));
+  }
+  cudaFree(buf);
+  if (!rc && err) rc = llb_fail("smp_rows: the device sampler reported %u", err);
+  return rc;
 }
 int llb_b200_wait_selftest(int which, int limit) {
   NEED_INIT(-1)

@@ -21,6 +21,7 @@
 #include "gguf.cuh"
 #include "pf.cuh"
 #include "tp.cuh"
+#include "sampler.cuh"
 
 struct DevMat { uint8_t *w = nullptr; int rows = 0, cols = 0, fmt = -1; };
 struct OutBuf { float *p = nullptr; int ns = 1; long long stride = 0; size_t cap = 0; };   // K-slice partial sums of one matrix (cap: floats allocated)
@@ -131,6 +132,12 @@ struct llb_spec {
   cudaGraphExec_t g_spec = nullptr, g_prefill = nullptr, g_verify = nullptr;
   size_t n_spec_nodes = 0, n_verify_nodes = 0;
   std::vector<SeqHost> sq;   // one per stream
+  // sampling-mode verify (sampler.cu): off while the parameters leave the argmax untouched
+  bool smp_on = false;
+  SmpDev smp;
+  float *smp_adj = nullptr, *smp_val = nullptr;   // biased / penalised logits of every row; the emitted tokens' raw logits
+  int *smp_tok = nullptr;
+  unsigned int *smp_err = nullptr;
 };
 // the streams' copies of per-sequence device state
 static inline SpecCtl *ctl_of(const llb_spec *m, int b) { return m->ctl + b; }
@@ -649,7 +656,11 @@ static int enq_cycle(llb_spec *m, bool spec) {
     }
   }
   CK(enq_verify(m));
-  CK(op_accept(s, m->t2part, m->ctl, m->res_dev, m->res_n, m->Tmax, m->B, m->B > 1 ? m->per : 0));
+  // sampling mode (speculative cycles only: a prompt chunk's rows are given): every row's emitted token from its logits
+  const bool smp = spec && m->smp_on;
+  if (smp) CK(op_smp_rows(s, m->smp, as_in(m->b_lg), m->V, m->smp_adj, m->ctl, m->Tmax, nullptr, nullptr, nullptr, nullptr, m->smp_tok, m->smp_val, nullptr,
+                          m->smp_err));
+  CK(op_accept(s, m->t2part, m->ctl, m->res_dev, m->res_n, m->Tmax, m->B, m->B > 1 ? m->per : 0, smp ? m->smp_tok : nullptr, smp ? m->smp_val : nullptr));
   if (m->lookup) CK(op_lookup_draft(s, m->ctl, m->B));   // the next cycle's drafts, from the history the accept kernel extended
   return 0;
 }
@@ -929,9 +940,10 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   } else if (k > 0) {
     // no MTP image: the reference's other drafter, prompt lookup over the token history
     m->lookup = true;
-    m->hist = (int *)dalloc(m, (size_t)B * ((size_t)max_ctx + 16) * 4);
-    if (!m->hist) return -1;
   }
+  // every stream's token history on the device: the lookup drafter searches it, the sampler's penalties read its tail
+  m->hist = (int *)dalloc(m, (size_t)B * ((size_t)max_ctx + 16) * 4);
+  if (!m->hist) return -1;
 
   // activations
   int big = m->f > m->convd ? m->f : m->convd;
@@ -1320,7 +1332,7 @@ static int prefill_stream(llb_spec *m, int b, const int *ids, int n) {
     }
   }
   SpecCtl c = ctl_fresh(m, b);
-  if (m->lookup) CU_OK(cudaMemcpyAsync(hist_of(m, b), ids, (size_t)n * 4, cudaMemcpyHostToDevice, g_llb.stream));
+  CU_OK(cudaMemcpyAsync(hist_of(m, b), ids, (size_t)n * 4, cudaMemcpyHostToDevice, g_llb.stream));
   // the drafter's row for position 0 pairs token 0 with a zero hidden (host/llb_host.c:1815-1817)
   c.catchup.n = 1; c.catchup.pos0 = 0; c.catchup.tok[0] = ids[0];
   c.verify.n = m->lookup ? 1 : m->per;   // nothing to look up at position 0
@@ -1599,6 +1611,47 @@ LLB_API int llb_spec_profile_verify(llb_spec *m, char *buf, int cap) {
 // kernels per replay of the cycle graph (which = 0) or of the verify pass (which = 2)
 LLB_API int llb_spec_graph_nodes(const llb_spec *m, int which) { return (int)(which == 2 ? m->n_verify_nodes : m->n_spec_nodes); }
 
+// Sampling parameters of the cycles from now on (set before llb_spec_prefill): the cycle graph is captured again with or
+// without the sampler's kernel in it.
+LLB_API int llb_spec_set_sampler(llb_spec *m, const llb_smp_params *p) {
+  if (!p) return llb_fail("set_sampler: no parameters");
+  for (int b = 0; b < m->B; b++) if (m->sq[b].primed) return llb_fail("set_sampler: set the sampler before the prompt goes in (stream %d has one)", b);
+  SmpDev d;
+  bool argmax_only = false;
+  CK(smp_prepare(p, &d, &argmax_only));
+  if (m->tp.size > 1 && !argmax_only) return llb_fail("set_sampler: a tensor-parallel engine decodes greedily");
+  const int rows = m->B * m->Tspec;
+  if (!argmax_only && !m->smp_adj) {
+    m->smp_adj = falloc(m, (size_t)rows * m->V); m->smp_val = falloc(m, rows); m->smp_tok = (int *)dalloc(m, (size_t)rows * 4);
+    m->smp_err = (unsigned int *)dalloc(m, 4);
+    if (!m->smp_adj || !m->smp_val || !m->smp_tok || !m->smp_err) return -1;
+  }
+  m->smp = d;
+  m->smp_on = !argmax_only;
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  if (m->g_spec) { cudaGraphExecDestroy(m->g_spec); m->g_spec = nullptr; }
+  set_width(m, rows);
+  CK(llb_spec_reset(m));
+  return capture(m, 0, &m->g_spec, &m->n_spec_nodes);
+}
+// 0, or the device sampler's error word: 2 min_keep above what min_p kept, 3 a token out of range
+LLB_API int llb_spec_sampler_errors(llb_spec *m) {
+  if (!m->smp_err) return 0;
+  unsigned int v = 0;
+  CU_OK(cudaStreamSynchronize(g_llb.stream));
+  CU_OK(cudaMemcpy(&v, m->smp_err, 4, cudaMemcpyDeviceToHost));
+  return (int)v;
+}
+
+// The result record of a stream's last cycle as 3 + 8 + 8 + 32 words: p0, T, served, the verify inputs tin[8] (the
+// committed token, then the drafts), the rows' emitted ids[8], and [id1, bits1, id2, bits2] of each row.
+LLB_API int llb_spec_last_record(const llb_spec *m, int stream, unsigned int *out51) {
+  if (stream < 0 || stream >= m->B || !m->sq[stream].have_last) return llb_fail("last_record: stream %d has not run a cycle", stream);
+  const SpecResult &r = m->sq[stream].last;
+  out51[0] = (unsigned)r.p0; out51[1] = (unsigned)r.T; out51[2] = (unsigned)r.served;
+  for (int i = 0; i < SPEC_MAXT; i++) { out51[3 + i] = (unsigned)r.tin[i]; out51[11 + i] = (unsigned)r.ids[i]; memcpy(out51 + 19 + 4 * i, r.top2[i], 16); }
+  return 0;
+}
 LLB_API int llb_spec_position(const llb_spec *m) { return m->sq[0].pos; }
 LLB_API int llb_spec_position_stream(const llb_spec *m, int stream) { return stream >= 0 && stream < m->B ? m->sq[stream].pos : -1; }
 LLB_API int llb_spec_streams(const llb_spec *m) { return m->B; }

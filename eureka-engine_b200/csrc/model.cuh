@@ -142,7 +142,9 @@ __device__ __forceinline__ const RowSet *rs_begin_row(const RowSet *rs, Streams 
 int op_lookup_draft(cudaStream_t s, SpecCtl *ctl, int nz = 1);
 int op_top2_part(cudaStream_t s, PartIn logits, int V, long long row_stride, float *part, const RowSet *rs, int Tmax);
 // nz streams: control blocks consecutive, result rings ring_n records apart, rows of the pass `per` apart
-int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax, int nz = 1, int per = 0);
+// smp_tok / smp_val (sampling mode): the emitted token of every row and its raw logit, in place of the argmax
+int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax, int nz = 1, int per = 0,
+              const int *smp_tok = nullptr, const float *smp_val = nullptr);
 int op_draft_pick(cudaStream_t s, const float *part, const int *ids, SpecCtl *ctl, int from_chain, int j, const float *mt_hn,
                   float *chain_h, int d, int nz = 1, int per = 0);
 int ops_model_setup(void);

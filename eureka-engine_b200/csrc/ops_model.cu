@@ -597,7 +597,8 @@ __device__ __forceinline__ Top2 t2_final(const float *part, int t, int lane) {
 // sampling that is "accept while argmax(row j) == draft j+1" (host/llb_sampler_impl.h:400-405).
 // Here the whole decision runs on the device and also prepares the next cycle: new p0, ring slot,
 // committed token, and the drafter's catch-up rows (host/llb_host.c:1815).
-__global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ ctl, SpecResult *__restrict__ ring, int ring_n, int per) {
+__global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ ctl, SpecResult *__restrict__ ring, int ring_n, int per,
+                         const int *__restrict__ smp_tok, const float *__restrict__ smp_val) {
   pdl_trigger();
   pdl_wait();
   __shared__ Top2 rows[SPEC_MAXT];
@@ -609,6 +610,9 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
   if (T < 1) return;   // an empty pass (the sizing run at open, a stream that is not running) decides nothing
   if (warp < T) {
     Top2 a = t2_final(part, row0 + warp, lane);
+    // sampling mode: the row's emitted token is the sampler's (llb_smp_verify / llb_smp_sample), not the argmax; the
+    // argmax's runner-up stays in the record's third and fourth words
+    if (smp_tok) { if (a.i1 != smp_tok[row0 + warp]) { a.i2 = a.i1; a.v2 = a.v1; } a.i1 = smp_tok[row0 + warp]; a.v1 = smp_val[row0 + warp]; }
     if (lane == 0) rows[warp] = a;
   }
   __syncthreads();
@@ -651,8 +655,9 @@ __global__ void k_accept(const float *__restrict__ part, SpecCtl *__restrict__ c
   res->seq = ctl->seq + 1;   // written last: the host polls it
   ctl->seq += 1;
 }
-int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax, int nz, int per) {
-  CU_OK(llb_launch(k_accept, dim3(nz), dim3(32 * (nz > 1 ? per : Tmax)), (size_t)(0), s, part, ctl, ring, ring_n, per));
+int op_accept(cudaStream_t s, const float *part, SpecCtl *ctl, SpecResult *ring, int ring_n, int Tmax, int nz, int per, const int *smp_tok,
+              const float *smp_val) {
+  CU_OK(llb_launch(k_accept, dim3(nz), dim3(32 * (nz > 1 ? per : Tmax)), (size_t)(0), s, part, ctl, ring, ring_n, per, smp_tok, smp_val));
   CU_OK(cudaGetLastError());
   return 0;
 }

@@ -72,6 +72,9 @@ def lib() -> C.CDLL:
             "llb_b200_tp_finalize": (None, []), "llb_b200_tp_plan": (i32, [i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32)]),
             "llb_spec_open_tp": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
             "llb_b200_tp_peer_alloc": (i32, [vp]), "llb_b200_tp_peer_open": (i32, [vp, i32]), "llb_b200_tp_peer_active": (i32, []),
+            "llb_spec_last_record": (i32, [vp, i32, vp]),
+            "llb_spec_set_sampler": (i32, [vp, vp]), "llb_spec_sampler_errors": (i32, [vp]),
+            "llb_b200_smp_rows": (i32, [vp, u64, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
             "llb_spec_open_streams": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
             "llb_spec_streams": (i32, [vp]), "llb_spec_prefill_stream": (i32, [vp, i32, vp, i32]),
             "llb_spec_cycle_streams": (i32, [vp, vp, vp, vp]), "llb_spec_run_cycles_streams": (i32, [vp, i32, vp]),
@@ -176,6 +179,41 @@ def gemm(fmt: int, ws, rows, outs, K: int, xp, ksplit: int = 0):
           "llb_b200_gemm")
 
 
+class SmpParams(C.Structure):
+    """llb_smp_params (include/llb_b200.h): the reference's LlbSmpParams without the two fields the path does not use."""
+    _fields_ = [("temp", C.c_float), ("top_p", C.c_float), ("min_p", C.c_float), ("top_k", C.c_int), ("repeat_penalty", C.c_float),
+                ("repeat_last_n", C.c_int), ("presence", C.c_float), ("frequency", C.c_float), ("seed", C.c_uint64), ("min_keep", C.c_int),
+                ("n_bias", C.c_int), ("bias_ids", C.c_int * 64), ("bias_vals", C.c_float * 64)]
+
+    @classmethod
+    def make(cls, temp=0.0, top_p=1.0, min_p=0.0, top_k=0, repeat_penalty=1.0, repeat_last_n=64, presence=0.0, frequency=0.0, seed=0,
+             min_keep=0, bias=()):
+        p = cls()
+        p.temp, p.top_p, p.min_p, p.top_k = temp, top_p, min_p, top_k
+        p.repeat_penalty, p.repeat_last_n, p.presence, p.frequency = repeat_penalty, repeat_last_n, presence, frequency
+        p.seed, p.min_keep, p.n_bias = seed, min_keep, len(bias)
+        for j, (t, v) in enumerate(bias):
+            p.bias_ids[j], p.bias_vals[j] = t, v
+        return p
+
+
+def smp_rows(params: "SmpParams", logits_ptr: int, T: int, V: int, drafts, pos, windows):
+    """The device sampler on T rows of logits on the device: (tokens, accepted, raw logit of each token)."""
+    import numpy as np
+    d = np.ascontiguousarray(drafts, dtype=np.int32)
+    ps = np.ascontiguousarray(pos, dtype=np.int64)
+    win = np.zeros((T, 256), np.int32)
+    nwin = np.zeros(T, np.int32)
+    for t, w in enumerate(windows):
+        w = np.asarray(w, dtype=np.int32)[-256:]
+        win[t, : len(w)] = w
+        nwin[t] = len(w)
+    tok, acc, val = np.zeros(T, np.int32), np.zeros(T, np.int32), np.zeros(T, np.float32)
+    check(lib().llb_b200_smp_rows(C.byref(params), logits_ptr, T, V, d.ctypes.data, ps.ctypes.data, win.ctypes.data, nwin.ctypes.data,
+                                  tok.ctypes.data, acc.ctypes.data, val.ctypes.data), "llb_b200_smp_rows")
+    return tok, acc, val
+
+
 class SpecEngine:
     """The speculative-decoding engine behind llb_spec_* (one sequence, greedy, MTP drafter).
 
@@ -242,6 +280,20 @@ class SpecEngine:
         import numpy as np
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         check(self.L.llb_spec_prefill(self.h, ids.ctypes.data, len(ids)), "llb_spec_prefill")
+
+    def last_record(self, b: int = 0):
+        import numpy as np
+        o = np.zeros(51, np.uint32)
+        check(self.L.llb_spec_last_record(self.h, b, o.ctypes.data), "llb_spec_last_record")
+        T = int(o[1])
+        return {"p0": int(o[0]), "T": T, "served": int(o[2]), "tin": [int(v) for v in o[3:3 + T].view(np.int32)],
+                "ids": [int(v) for v in o[11:11 + T].view(np.int32)], "top2": o[19:19 + 4 * T].reshape(T, 4).copy()}
+
+    def set_sampler(self, params: "SmpParams"):
+        check(self.L.llb_spec_set_sampler(self.h, C.byref(params)), "llb_spec_set_sampler")
+
+    def sampler_errors(self) -> int:
+        return self.L.llb_spec_sampler_errors(self.h)
 
     def prefill_stream(self, b: int, ids):
         import numpy as np

@@ -177,6 +177,37 @@ LLB_API int llb_b200_tp_peer_open(const void *handles, int n);
 LLB_API int llb_b200_tp_peer_active(void);
 LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                    size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_size);
+/* Sampling-mode verify (the llb_sampler contract beyond greedy, host/llb_sampler.h).  The fields are LlbSmpParams' (:38-52;
+ * n_logprobs and max_tokens, which the path does not use, left out): temp <= 0 greedy; top_p >= 1, top_k <= 0, min_p <= 0,
+ * repeat_last_n <= 0 switch their stage off.  With parameters that leave the argmax untouched (llb_smp_is_argmax) the cycle is
+ * the greedy one.  Otherwise every row of a verify pass gets, on the device and inside the cycle's graph, the token
+ * llb_smp_verify (a row with a draft; both drafters are deterministic, so q is one-hot) or llb_smp_sample (the row without)
+ * would return for its logits, with the reference's counter RNG (seed, position, draw), and the accept step takes those
+ * tokens in place of the argmax: the emitted stream is distributed as plain sampling's, whatever the drafter proposes.
+ * Limits, refused by name: top_k <= 256; top_p < 1 needs top_k; penalty window <= 256; min_keep above what min_p keeps.
+ * Must be set before llb_spec_prefill; the result record's top-2 words then carry (emitted id, its raw logit, argmax's
+ * runner-up id and value). */
+typedef struct {
+  float temp, top_p, min_p;
+  int top_k;
+  float repeat_penalty;
+  int repeat_last_n;
+  float presence, frequency;
+  unsigned long long seed;
+  int min_keep;
+  int n_bias;
+  int bias_ids[64];
+  float bias_vals[64];
+} llb_smp_params;
+LLB_API int llb_spec_set_sampler(llb_spec *m, const llb_smp_params *p);
+/* 0, or the device sampler's error word since the engine was opened (2: min_keep above what min_p kept; 3: a token out of range). */
+LLB_API int llb_spec_sampler_errors(llb_spec *m);
+/* Test entry: the device sampler on T rows of logits given on the device (f32 [T][V]): drafts[T] (-1: a plain draw),
+ * pos[T] (the position each token will occupy), the penalty windows win[T][256] with their lengths nwin[T] (host arrays);
+ * tok_out / acc_out / val_out[T] on the host. */
+LLB_API int llb_b200_smp_rows(const llb_smp_params *p, llb_b200_dptr logits, int T, int V, const int *drafts, const long long *pos,
+                              const int *win, const int *nwin, int *tok_out, int *acc_out, float *val_out);
+
 /* Several streams per engine (multi-stream batching inside one GPU; the reference's analogue is its prefill-only
  * LLB_BATCH, host/llb_host.c:2151-2793).  `streams` independent sequences share every weight read: a pass carries the k + 1
  * rows of each stream through every GEMM together (streams x (k + 1) <= 16 rows; <= 8 with routed experts), while attention,
@@ -195,6 +226,9 @@ LLB_API int llb_spec_cycle_streams(llb_spec *m, int *ids_out, int *n_out, uint32
 /* n cycles back to back without a host round trip; tokens[stream] = tokens that stream emitted. */
 LLB_API int llb_spec_run_cycles_streams(llb_spec *m, int n, int *tokens);
 LLB_API int llb_spec_position_stream(const llb_spec *m, int stream);
+/* The result record of a stream's last cycle: out[0..2] = p0, rows T, rows served; out[3..10] the verify inputs (the
+ * committed token, then the drafts); out[11..18] every row's emitted id; out[19 + 4 r ..] = [id1, bits1, id2, bits2] of row r. */
+LLB_API int llb_spec_last_record(const llb_spec *m, int stream, unsigned int *out51);
 LLB_API int llb_spec_stats_stream(const llb_spec *m, int stream, unsigned long long *out19);
 LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il, int pos, float *out, size_t n);
 
