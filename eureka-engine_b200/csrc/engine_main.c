@@ -10,6 +10,10 @@
  *                        LLB_MTP unset the cycle drafts by prompt lookup (host/llb_host.c:1936)
  *         LLB_GGUF=FILE  read the model from a GGUF instead of PACKDIR/pack.bin + index.tsv (host/llb_gguf.c:854-865)
  *         LLB_DEVICE=n   CUDA device ordinal (default 0)
+ *         LLB_SAMPLE=SPEC  sampler parameters "key=val,key=val" (llb_smp_parse, host/llb_sampler_impl.h:26-75): temp top_p
+ *                        top_k min_p repeat_penalty repeat_last_n presence frequency seed min_keep bias=ID:VAL;ID:VAL
+ *                        preset=greedy|qwen_thinking|qwen_non_thinking; the verify step then follows llb_smp_verify on
+ *                        the device (llb_spec_set_sampler).  --temp / --top-p / --seed set the same fields
  *   stdout  one generated id per line, then `wall_ms <ms>` and `tok_s <x>`
  *   stderr  `logits <pos> <id1> <bits1> <id2> <bits2>` for the row at <pos> (top-2 logits as raw f32 bits),
  *           `step <pos> <ms>` per generated token, and with LLB_SPEC the summary
@@ -18,8 +22,7 @@
  *
  * Every token goes through llb_spec_pass(pos, tok) -> [v1, id1, v2, id2], the reference's per-token operator
  * (spec_pass, host/llb_host.c:1902-1950): rows of a running cycle are served from its record, a new cycle starts where
- * the stream leaves the last one.  Sampling options of the reference CLI (--temp, --top-p) are refused: acceptance is
- * committed on the device under the greedy rule.
+ * the stream leaves the last one.  With sampling the row's id is the sampled token, which the caller feeds back.
  */
 #include <fcntl.h>
 #include <stdio.h>
@@ -54,26 +57,76 @@ static void *map_file(const char *path, size_t *size) {
 static void usage(const char *p) {
   fprintf(stderr,
           "usage: %s [--gpu SIZE] [--threads N] [--] PACKDIR id... [--steps N] [--layers L]\n"
-          "  env LLB_SPEC=k (0..7 drafts a cycle), LLB_MTP=FILE (AUX1 / MTP1 drafter image), LLB_GGUF=FILE, LLB_DEVICE=n\n"
+          "  env LLB_SPEC=k (0..7 drafts a cycle), LLB_MTP=FILE (AUX1 / MTP1 drafter image), LLB_GGUF=FILE, LLB_DEVICE=n,\n"
+          "      LLB_SAMPLE=\"temp=0.7,top_k=20,top_p=0.8,seed=1\" (also --temp --top-p --top-k --seed)\n"
           "  stdout: ids, wall_ms, tok_s;  stderr: logits / step lines and the spec: summary\n", p);
 }
 
 static unsigned bits_of(float f) { unsigned u; memcpy(&u, &f, 4); return u; }
 
+static void smp_defaults(llb_smp_params *p) {   /* llb_smp_defaults (host/llb_sampler_impl.h:15-18) */
+  memset(p, 0, sizeof *p);
+  p->top_p = 1.0f; p->repeat_penalty = 1.0f; p->repeat_last_n = 64;
+}
+/* "key=val,key=val" into p; 0, or -1 with a message on stderr */
+static int smp_parse(llb_smp_params *p, const char *spec) {
+  char buf[1024];
+  if (!spec) return 0;
+  if (strlen(spec) >= sizeof buf) { fprintf(stderr, "LLB_SAMPLE: too long\n"); return -1; }
+  strcpy(buf, spec);
+  for (char *tok = strtok(buf, ","); tok; tok = strtok(NULL, ",")) {
+    char *eq = strchr(tok, '=');
+    if (!eq) { fprintf(stderr, "LLB_SAMPLE: '%s' is not key=value\n", tok); return -1; }
+    *eq = 0;
+    const char *k = tok, *v = eq + 1;
+    if (!strcmp(k, "temp")) p->temp = strtof(v, NULL);
+    else if (!strcmp(k, "top_p")) p->top_p = strtof(v, NULL);
+    else if (!strcmp(k, "top_k")) p->top_k = atoi(v);
+    else if (!strcmp(k, "min_p")) p->min_p = strtof(v, NULL);
+    else if (!strcmp(k, "repeat_penalty")) p->repeat_penalty = strtof(v, NULL);
+    else if (!strcmp(k, "repeat_last_n")) p->repeat_last_n = atoi(v);
+    else if (!strcmp(k, "presence")) p->presence = strtof(v, NULL);
+    else if (!strcmp(k, "frequency")) p->frequency = strtof(v, NULL);
+    else if (!strcmp(k, "seed")) p->seed = strtoull(v, NULL, 10);
+    else if (!strcmp(k, "min_keep")) p->min_keep = atoi(v);
+    else if (!strcmp(k, "max_tokens")) continue;             /* a policy field of the caller */
+    else if (!strcmp(k, "preset")) {
+      if (!strcmp(v, "greedy")) smp_defaults(p);
+      else if (!strcmp(v, "qwen_thinking")) { p->temp = 1.0f; p->top_p = 0.95f; p->top_k = 20; p->presence = 1.5f; }
+      else if (!strcmp(v, "qwen_non_thinking")) { p->temp = 0.7f; p->top_p = 0.8f; p->top_k = 20; p->presence = 1.5f; }
+      else { fprintf(stderr, "LLB_SAMPLE: unknown preset '%s'\n", v); return -1; }
+    } else if (!strcmp(k, "bias")) {
+      for (const char *b = v; *b;) {
+        char *end;
+        const long id = strtol(b, &end, 10);
+        if (*end != ':' || p->n_bias >= 64) { fprintf(stderr, "LLB_SAMPLE: bias wants ID:VAL;ID:VAL, at most 64\n"); return -1; }
+        p->bias_ids[p->n_bias] = (int)id;
+        p->bias_vals[p->n_bias++] = strtof(end + 1, &end);
+        b = *end == ';' ? end + 1 : end;
+        if (*end && *end != ';') { fprintf(stderr, "LLB_SAMPLE: bias wants ID:VAL;ID:VAL\n"); return -1; }
+      }
+    } else { fprintf(stderr, "LLB_SAMPLE: no key '%s' on this path\n", k); return -1; }
+  }
+  return 0;
+}
+
 int main(int argc, char **argv) {
   const char *dir = NULL;
   static int ids[1 << 20];
   int nids = 0, steps = 8, layers = 0;
+  llb_smp_params smp;
+  smp_defaults(&smp);
+  if (smp_parse(&smp, getenv("LLB_SAMPLE"))) return 2;
   for (int a = 1; a < argc; a++) {
     if (!strcmp(argv[a], "--steps") && a + 1 < argc) steps = atoi(argv[++a]);
     else if (!strcmp(argv[a], "--layers") && a + 1 < argc) layers = atoi(argv[++a]);
     else if ((!strcmp(argv[a], "--gpu") || !strcmp(argv[a], "--threads")) && a + 1 < argc) a++;   /* the launcher's memory / thread hints */
     else if (!strcmp(argv[a], "--")) continue;
     else if (!strcmp(argv[a], "--ids") || !strcmp(argv[a], "--cpu") || !strcmp(argv[a], "--preload")) continue;
-    else if (!strcmp(argv[a], "--temp") || !strcmp(argv[a], "--top-p") || !strcmp(argv[a], "--seed")) {
-      fprintf(stderr, "%s: sampling is not available on this path (greedy acceptance is committed on the device)\n", argv[a]);
-      return 2;
-    }
+    else if (!strcmp(argv[a], "--temp") && a + 1 < argc) smp.temp = strtof(argv[++a], NULL);
+    else if (!strcmp(argv[a], "--top-p") && a + 1 < argc) smp.top_p = strtof(argv[++a], NULL);
+    else if (!strcmp(argv[a], "--top-k") && a + 1 < argc) smp.top_k = atoi(argv[++a]);
+    else if (!strcmp(argv[a], "--seed") && a + 1 < argc) smp.seed = strtoull(argv[++a], NULL, 10);
     else if (argv[a][0] == '-' && argv[a][1] == '-') { fprintf(stderr, "unknown option %s\n", argv[a]); usage(argv[0]); return 2; }
     else if (!dir) dir = argv[a];
     else if (nids < (int)(sizeof ids / sizeof *ids)) ids[nids++] = atoi(argv[a]);
@@ -110,6 +163,7 @@ int main(int argc, char **argv) {
   }
   if (!m) { fprintf(stderr, "llb-engine-b200: %s\n", llb_b200_last_error()); return 1; }
 
+  if (llb_spec_set_sampler(m, &smp)) { fprintf(stderr, "llb-engine-b200: %s\n", llb_b200_last_error()); return 1; }
   const double t0 = now_ms();
   float y[4];
   if (llb_spec_prefill(m, ids, nids) || llb_spec_pass(m, nids - 1, ids[nids - 1], y)) {

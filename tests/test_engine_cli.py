@@ -42,8 +42,12 @@ def test_usage_and_refusals_need_no_gpu():
         graft.load_package().llb.build()
     r = subprocess.run([EXE], capture_output=True, text=True)
     assert r.returncode == 2 and "usage:" in r.stderr and "LLB_SPEC" in r.stderr
-    r = subprocess.run([EXE, "/nonexistent", "1", "--temp", "0.7"], capture_output=True, text=True)
-    assert r.returncode == 2 and "sampling" in r.stderr
+    env = dict(os.environ, LLB_SAMPLE="temp=0.7,logprobs=3")
+    r = subprocess.run([EXE, "/nonexistent", "1"], capture_output=True, text=True, env=env)
+    assert r.returncode == 2 and "no key 'logprobs'" in r.stderr
+    env = dict(os.environ, LLB_SAMPLE="preset=nonsense")
+    r = subprocess.run([EXE, "/nonexistent", "1"], capture_output=True, text=True, env=env)
+    assert r.returncode == 2 and "unknown preset" in r.stderr
     r = subprocess.run([EXE, "/nonexistent", "1", "--bogus"], capture_output=True, text=True)
     assert r.returncode == 2 and "unknown option" in r.stderr
     env = dict(os.environ, LLB_SPEC="9")
@@ -85,3 +89,32 @@ def test_engine_process_matches_the_reference_process(packs, llb, tmp_path, mode
         m = RE_SPEC.match(spec[0])
         assert m and m.group(1) == mode and int(m.group(2)) == 3 and len(m.group(7).split()) == 3
         assert int(m.group(5)) >= len(ids) - 1 and int(m.group(3)) >= 1
+
+
+@pytest.mark.gpu
+def test_engine_process_samples_reproducibly(packs, llb, tmp_path):
+    """LLB_SAMPLE as the reference takes it (host/llb_host.c:1376-1380): the same seed gives the same stream, with or
+    without speculation (the verify rule is lossless per draw only in distribution, so the two need not be equal to each
+    other), another seed gives another stream, and a greedy spec leaves the greedy ids."""
+    cfg = packs.cfg_tiny()
+    pack = packs.build_pack(cfg)
+    pack.write(str(tmp_path))
+    (tmp_path / "mtp.bin").write_bytes(packs.aux1_bytes(packs.build_mtp(pack)))
+
+    def run(sample, spec):
+        env = dict(os.environ)
+        if sample:
+            env["LLB_SAMPLE"] = sample
+        if spec:
+            env["LLB_SPEC"], env["LLB_MTP"] = "3", str(tmp_path / "mtp.bin")
+        r = subprocess.run([EXE, str(tmp_path)] + GOLD["args"][:-2] + ["--steps", "24"], capture_output=True, text=True, env=env, timeout=300)
+        assert r.returncode == 0, r.stderr
+        return _parse(r.stdout.splitlines(), r.stderr.splitlines())[0]
+
+    greedy = run(None, True)
+    assert run("temp=0,top_k=5", True) == greedy
+    a = run("temp=1.0,top_k=40,top_p=0.95,seed=7", True)
+    assert a == run("temp=1.0,top_k=40,top_p=0.95,seed=7", True) and a != greedy
+    assert a != run("temp=1.0,top_k=40,top_p=0.95,seed=8", True)
+    b = run("preset=qwen_non_thinking,seed=7", False)
+    assert b == run("preset=qwen_non_thinking,seed=7", False) and len(b) == 24
