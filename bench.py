@@ -39,6 +39,7 @@ GEMM_DRAM_TRAFFIC = 106.4e6
 METRIC = "spec-decode tok/s per B200, 27B-shape Q4_K_M MTP k=3; verify-step HBM GB/s"
 WORKLOAD = "config 2: 27B-shape hybrid (d 5120, 64 layers, f 17408, V 151936), Q4_K_M, batch 1, MTP k=3 greedy, prompt 3011"
 PROMPT, GEN_CAP, K_DRAFT = 3011, 1200, 3
+DRAFT_VOCAB = 40960
 
 
 def peaks():
@@ -102,7 +103,9 @@ def build_model(device, layers=None):
     packs = load_package().packs
     cfg = packs.cfg_c2()
     pack = packs.build_pack(cfg, device=device, layers=layers)
-    mtp = packs.aux1_bytes(packs.build_mtp(pack))
+    # the drafter's head is the 40960-row draft-vocabulary slice of the reference's 27B drafter pack (tools/mtp27/mtp_pack.py:14-30:
+    # 172 MB a drafter pass instead of the whole head's 638 MB); on this synthetic model the slice is the first 40960 ids
+    mtp = packs.aux1_bytes(packs.build_mtp(pack, draft_vocab=DRAFT_VOCAB))
     prompt = packs.synth_prompt(3, PROMPT, cfg.vocab_size)
     return packs, pack, mtp, prompt
 
@@ -326,6 +329,59 @@ def run_streams(args, rank, world, local):
         dist.destroy_process_group()
 
 
+def run_gemm_case(args, local):
+    """The isolated verify-step GEMM (configuration 1: the 27B shapes with no model): `--rows` matrices of `--cols` columns in
+    format `--fmt` sharing T activation rows, launched over enough copies of the weights that every launch streams from HBM,
+    timed with CUDA events on the library's stream.  One JSON line; also the command the ncu summaries under profiles/ run."""
+    import numpy as np
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    llb, packs = pkg.llb, pkg.packs
+    torch.cuda.set_device(local)
+    llb.init(local)
+    L = llb.lib()
+    ty, K, T = args.fmt, args.cols, args.t
+    fmt = packs.FMT[ty]
+    rows = [int(r) for r in args.rows.split(",")]
+    g = torch.Generator(device=f"cuda:{local}").manual_seed(2)
+    per_copy = sum(r * packs.row_bytes(ty, K) for r in rows)
+    copies = max(2, int(400e6 // per_copy) + 1)              # more than the 126 MB L2 between two uses of a copy
+    sets = []
+    for c in range(copies):
+        ws = []
+        for r in rows:
+            w = torch.randn(r, K, device=f"cuda:{local}", generator=g) * 0.02
+            raw = packs.QUANT[ty](w).contiguous()
+            p = llb.alloc(L.llb_b200_weight_bytes(fmt, r, K))
+            llb.check(L.llb_b200_weight_upload(fmt, r, K, raw.data_ptr(), 1, p), "weight_upload")
+            ws.append(p)
+            del w, raw
+        sets.append(ws)
+    x = torch.randn(T, K, device=f"cuda:{local}", generator=g)
+    xp = llb.handle(L.llb_b200_xp_new(K, T, 2), "xp_new")
+    llb.check(L.llb_b200_xp_set_f32(xp, x.data_ptr()), "xp_set")
+    outs = [llb.alloc(T * r * 4 * 16) for r in rows]
+    st = torch.cuda.ExternalStream(L.llb_b200_stream())
+    for i in range(max(3, args.warmup)):
+        llb.gemm(fmt, sets[i % copies], rows, outs, K, xp, args.ksplit)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for i in range(args.steps):
+        llb.gemm(fmt, sets[i % copies], rows, outs, K, xp, args.ksplit)
+    e1.record(st)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / args.steps
+    peak, peak_src = peaks()
+    nc = 8 if T <= 4 else 16 if T <= 8 else 32
+    nbytes = per_copy + nc * K * 2 + sum(T * r * 4 for r in rows)
+    print(json.dumps({"case": "gemm", "kernel": f"k_gemm2<{ty}>", "rows": rows, "cols": K, "T": T, "plane_columns": nc, "launches": args.steps,
+                      "weight_copies": copies, "us_per_launch": us, "bytes_per_launch": nbytes, "GBs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
+                      "peak": peak, "peak_source": peak_src, "ksplit": L.llb_b200_gemm_ksplit(fmt, nc, sum((r + 15) // 16 for r in rows), K // 256, L.llb_b200_sm_count()) if args.ksplit == 0 else args.ksplit,
+                      "wait_errors": L.llb_b200_wait_errors()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -341,7 +397,13 @@ def main():
     ap.add_argument("--streams", type=int, default=0, help="several streams per GPU sharing one weight read (with --config; 0: the configuration's default)")
     ap.add_argument("--config", type=int, default=0, choices=[0, 2, 3, 4], help="a multi-stream line for configuration 2, 3 or 4 (extra lines; the default run is the headline)")
     ap.add_argument("--k", type=int, default=-1, help="drafts per cycle of a --config line")
-    ap.add_argument("--prompt", type=int, default=0, help="prompt length of a --config line")
+    ap.add_argument("--prompt", type=int, default=0, help="prompt length (of a --config line; of the default run: profiling only)")
+    ap.add_argument("--case", default="", choices=["", "gemm"], help="gemm: the isolated verify-step GEMM of configuration 1 (no model)")
+    ap.add_argument("--fmt", default="Q4_K", help="--case gemm: weight format (Q4_K, Q5_K, Q6_K, Q8_0)")
+    ap.add_argument("--rows", default="17408,17408", help="--case gemm: rows of the matrices that share the launch")
+    ap.add_argument("--cols", type=int, default=5120, help="--case gemm: columns (K)")
+    ap.add_argument("--t", type=int, default=4, help="--case gemm: activation rows (1..16)")
+    ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: K-slices (0: the library's choice)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -352,6 +414,10 @@ def main():
         run_reference(args, rank)
         return
 
+    if args.case == "gemm":
+        if rank == 0:
+            run_gemm_case(args, local)
+        return
     if args.tp and world > 1:
         run_tp(args, rank, world, local)
         return
@@ -370,6 +436,8 @@ def main():
     llb.init(local)
     t_build = time.time()
     packs, pack, mtp, prompt = build_model(f"cuda:{local}", layers=args.layers or None)
+    if args.prompt > 0:
+        prompt = prompt[:args.prompt]      # a shorter prompt (profiling only; the number is then not the headline)
     max_ctx = PROMPT + GEN_CAP + 64
     torch.cuda.synchronize()
     torch.cuda.empty_cache()   # the quantisers' temporaries go back to the driver before the engine allocates
@@ -455,6 +523,41 @@ def main():
         except Exception as ex:
             plain = {"value": None, "error": str(ex)}
 
+    # ---- a model on which drafts ARE accepted: config 0's shape (0.8B, Q8_0, the drafter a copy of the last attention block
+    # and the tied head) with every sublayer's output scaled by 0.001 (packs.ModelCfg.mix_gain), so that the next token
+    # depends mostly on the current one and a one-block drafter that sees the token (eh_proj = [I | 0]) predicts some of
+    # them: speculative cycles with partial acceptance, rollback and commit, timed, and plain decoding of the same model
+    accept_leg = None
+    if rank == 0 and not args.no_plain:
+        try:
+            cfg0 = packs.cfg_c0(mix_gain=0.001)
+            pack0 = packs.build_pack(cfg0, device=f"cuda:{local}")
+            mtp0 = packs.aux1_bytes(packs.build_mtp(pack0, eh="embed"))
+            prompt0 = packs.synth_prompt(1, 64, cfg0.vocab_size)
+            res = {}
+            for kk in (K_DRAFT, 0):
+                e0 = llb.SpecEngine(pack0, mtp0 if kk else None, k=kk, max_ctx=64 + 128 * (kk + 1) + 64)
+                e0.prefill(prompt0)
+                e0.run_cycles(3)
+                torch.cuda.synchronize()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(st)
+                _, tk = e0.run_cycles(96)
+                a1.record(st)
+                torch.cuda.synchronize()
+                res[kk] = (tk / (a0.elapsed_time(a1) / 1000.0), tk / 96.0, a0.elapsed_time(a1) / 96.0, e0.stats())
+                e0.close()
+            sst = res[K_DRAFT][3]
+            accept_leg = {"workload": "config 0's shape (0.8B: d 1024, 24 layers, V 32768, Q8_0) with sublayer outputs scaled by 0.001 so that drafts are accepted; "
+                                      "MTP k=3 greedy, prompt 64, 96 timed cycles",
+                          "spec_tok_s": res[K_DRAFT][0], "tokens_per_cycle": res[K_DRAFT][1], "cycle_ms": res[K_DRAFT][2],
+                          "accepted_by_position": [round(a / d, 4) if d else None for a, d in zip(sst["accepted"][1:4], sst["drafted"][1:4])],
+                          "plain_tok_s": res[0][0], "plain_ms_per_step": res[0][2], "speedup_over_plain": res[K_DRAFT][0] / res[0][0]}
+            del pack0
+            torch.cuda.empty_cache()
+        except Exception as ex:
+            accept_leg = {"error": str(ex)}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         try:
@@ -482,16 +585,16 @@ def main():
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "streams_per_gpu": 1, "parallelism": f"stream-dp{world}",
+            "config": {"workload": WORKLOAD, "streams_per_gpu": 1, "parallelism": f"stream-dp{world}", "draft_vocabulary": DRAFT_VOCAB,
                        "layers": args.layers or 64, "l2": "inputs larger than L2: a cycle streams >14 GB of weights",
                        "tokens_per_cycle": toks / (steps * world),
                        "accepted_by_position": [round(a / d, 4) if d else None for a, d in zip(stats["accepted"][1:4], stats["drafted"][1:4])],
                        "acceptance_note": "0 on this model by construction: with N(0, 0.02) weights at d 5120 every sublayer rewrites the residual "
                                           "stream, so no one-block drafter (whatever eh_proj) predicts the trunk; value is the cycle rate. "
                                           "plain_decode is k = 0 on the same engine, prompt and position",
-                       "prefill_s": round(t_pre, 3), "prefill_tok_s": round(PROMPT / t_pre, 1),
+                       "prompt": len(prompt), "prefill_s": round(t_pre, 3), "prefill_tok_s": round(len(prompt) / t_pre, 1),
                        "prefill": "8-row verify passes" if args.exact_prefill else "dense tcgen05 path, chunks of 128 rows (all but the last k + 1 rows)", "build_s": round(t_build, 2)},
-            "cycle_ms": ms / steps, "tokens_per_cycle": toks / (steps * world), "plain_decode": plain,
+            "cycle_ms": ms / steps, "tokens_per_cycle": toks / (steps * world), "plain_decode": plain, "with_acceptance": accept_leg,
             "wait_errors": llb.lib().llb_b200_wait_errors(),   # 1 if a bounded device-side wait ever ran out (results then invalid)
             "clocks": clocks,
             "e2e": {"value": n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 216,

@@ -13,8 +13,8 @@ static int g2_max_sb(int fmt, int NC) {
 static bool is_g3(int fmt, int NC) { return g_llb.gemm3 && fmt == LLB_FM_Q4_K && NC == 8; }
 static unsigned int *g_ffn_sync = nullptr;   // the fused FFN's grid barrier: two counters
 static unsigned int *g_g3_err = nullptr;   // device word: set when a bounded wait of k_gemm3 ran out
-static int g2_warps(int fmt) {
-  return fmt == LLB_FM_Q6_K ? (int)G2Traits<LLB_FM_Q6_K>::WARPS : fmt == LLB_FM_Q8_0 ? (int)G2Traits<LLB_FM_Q8_0>::WARPS : (int)G2Traits<LLB_FM_Q4_K>::WARPS;
+static int g2_warps_of(int fmt, int NC) {
+  return fmt == LLB_FM_Q6_K ? g2_warps<LLB_FM_Q6_K>(NC) : fmt == LLB_FM_Q8_0 ? g2_warps<LLB_FM_Q8_0>(NC) : g2_warps<LLB_FM_Q4_K>(NC);
 }
 
 template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs &a) {
@@ -22,7 +22,7 @@ template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs 
   int cps = g_llb.sms * G2_CPSM / a.ksplit;
   if (cps < 1) cps = 1;
   // every SM takes part as long as there is a tile for it: the tiles are dealt out one per CTA in turn
-  constexpr int G2_WARPS = G2Traits<FMT>::WARPS;
+  constexpr int G2_WARPS = g2_warps<FMT>(8 * NT);
   if (cps > a.tile0[a.nmat]) cps = a.tile0[a.nmat];
   const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>(NC);
   if (smem > G2_SMEM_MAX) return llb_fail("k_gemm2: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
@@ -155,7 +155,7 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
       continue;
     } else {
       const int cps = sms * G2_CPSM / ks > 0 ? sms * G2_CPSM / ks : 1;
-      rounds = (ntiles + (long long)cps * g2_warps(fmt) - 1) / ((long long)cps * g2_warps(fmt));
+      rounds = (ntiles + (long long)cps * g2_warps_of(fmt, NC) - 1) / ((long long)cps * g2_warps_of(fmt, NC));
     }
     const int slice = (nsb + ks - 1) / ks;
     const double cost = (double)rounds * slice * (1.0 + 0.02 * (ks - 1));

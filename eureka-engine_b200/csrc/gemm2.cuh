@@ -41,10 +41,14 @@ template <> struct G2Traits<LLB_FM_Q6_K> { enum { SB = 224, RS = 240, P = 14, QO
 // bytes further on in the row; piece 16 of a row-super-block is that scale piece (copy plan below).  AUX: 8 f32 sums of 32 columns.
 template <> struct G2Traits<LLB_FM_Q8_0> { enum { SB = 256, RS = 304, P = 17, QOFF = 0, WARPS = 8 / G2_CPSM, XPAD = 32, AUX = 32 }; };
 
-// ring depth: three stages; two for Q5_K and Q6_K at 32 plane columns (16 rows), whose 224- and 240-byte rows would
-// otherwise leave the activation slice too little shared memory for a K of 17408 to split 16 ways
-template <int FMT> __host__ __device__ constexpr int g2_stages(int NC) { return ((FMT == LLB_FM_Q6_K || FMT == LLB_FM_Q5_K) && NC >= 32) ? 2 : G2_STAGES; }
-template <int FMT> __host__ __device__ constexpr int g2_ring_bytes(int NC) { return G2Traits<FMT>::WARPS * g2_stages<FMT>(NC) * 16 * G2Traits<FMT>::RS; }
+// Warps of a CTA: the format's count, but eight at 32 plane columns (16 rows, four n-tiles).  Sixteen warps cap a thread
+// at 128 registers, and four n-tiles of accumulators, scale sums and min-term products do not fit in them: the 16-row
+// kernel spilled (40 bytes of stores, 120 of loads per thread and super-block) and spent its time waiting on local
+// memory (long-scoreboard stalls 1.3 per issue, 830 instructions per tile-super-block against 397 at 4 rows, tensor pipe
+// 34 % busy).  Eight warps get 255 registers and a ring half the size, which also leaves the activation slice more room.
+template <int FMT> __host__ __device__ constexpr int g2_warps(int NC) { return NC >= 32 && G2Traits<FMT>::WARPS > 8 ? 8 : G2Traits<FMT>::WARPS; }
+template <int FMT> __host__ __device__ constexpr int g2_stages(int NC) { return G2_STAGES; }
+template <int FMT> __host__ __device__ constexpr int g2_ring_bytes(int NC) { return g2_warps<FMT>(NC) * g2_stages<FMT>(NC) * 16 * G2Traits<FMT>::RS; }
 // bytes of shared memory a K-slice of nsl super-blocks needs for NC activation columns
 template <int FMT> __host__ __device__ inline int g2_xp_bytes(int nsl, int NC) {
   return NC * (nsl * 512 + G2Traits<FMT>::XPAD) + nsl * NC * G2Traits<FMT>::AUX;
@@ -96,7 +100,7 @@ template <int FMT> struct G2MatsPlain {
 template <int FMT, int NT, class Stage, class Mats>
 __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage, const Mats mats) {
   using TR = G2Traits<FMT>;
-  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = TR::WARPS, ST = g2_stages<FMT>(8 * NT);
+  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = g2_warps<FMT>(8 * NT), ST = g2_stages<FMT>(8 * NT);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
   const bool live = bid < cps * a.ksplit && warp < G2_WARPS;
   const int ks = bid % a.ksplit, ci = bid / a.ksplit;
@@ -363,7 +367,7 @@ template <int FMT, int NT> struct G2StagePlanes {
 };
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_gemm2(const GemmArgs a, const int cps) {
+__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT) * 32, G2_CPSM) k_gemm2(const GemmArgs a, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
   g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, G2MatsPlain<FMT>{a});
