@@ -40,7 +40,7 @@ struct LayerW { bool full = false; float *attn_norm = nullptr; AttnW at; DeltaW 
 struct TensorRec { uint64_t off, bytes; int rows, cols, fmt; bool blocked = false; };
 
 // Buffers of the prompt path (pf.cu), allocated at the first fast prefill: residual rows, fp16 activations in the
-// dense GEMM's k-group-major order, GEMM outputs as K-slice partial sums of PF_R rows, and the row sets of the chunk.
+// dense GEMM's k-group-major order, GEMM outputs as K-slice partial sums of PF_RMAX rows, and the row sets of the chunk.
 struct PfState {
   bool ready = false;
   float *x = nullptr, *x1 = nullptr, *hn = nullptr, *e = nullptr, *qn = nullptr, *y = nullptr, *beta = nullptr, *decay = nullptr, *o = nullptr;
@@ -979,25 +979,25 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   return 0;
 }
 
-// ---- the prompt path: chunks of up to PF_R rows through dense tcgen05 GEMMs (pf.cu) ----------------------------
-#define PF_GROUPS (PF_R + 1)
+// ---- the prompt path: chunks of up to PF_RMAX rows through dense tcgen05 GEMMs (pf.cu) ----------------------------
+#define PF_GROUPS (PF_RMAX + 1)
 static int pf_alloc(llb_spec *m) {
   PfState &f = m->pf;
   if (f.ready) return 0;
   CK(pf_setup());
   const int d = m->d, qa = m->H * m->hd;
-  auto kg = [&](int K) { return (__half *)dalloc(m, pf_kg_halves(K) * 2); };
-  f.x = falloc(m, (size_t)PF_R * d); f.x1 = falloc(m, (size_t)PF_R * d); f.hn = falloc(m, (size_t)(PF_R + 1) * d); f.e = falloc(m, (size_t)PF_R * d);
-  f.qn = falloc(m, (size_t)PF_R * qa); f.y = falloc(m, (size_t)PF_R * m->convd); f.beta = falloc(m, (size_t)PF_R * m->TR);
-  f.decay = falloc(m, (size_t)PF_R * m->TR); f.o = falloc(m, (size_t)PF_R * m->vdc);
+  auto kg = [&](int K) { return (__half *)dalloc(m, (PF_RMAX / PF_R) * pf_kg_halves(K) * 2); };   // the chunk's units one after the other
+  f.x = falloc(m, (size_t)PF_RMAX * d); f.x1 = falloc(m, (size_t)PF_RMAX * d); f.hn = falloc(m, (size_t)(PF_RMAX + 1) * d); f.e = falloc(m, (size_t)PF_RMAX * d);
+  f.qn = falloc(m, (size_t)PF_RMAX * qa); f.y = falloc(m, (size_t)PF_RMAX * m->convd); f.beta = falloc(m, (size_t)PF_RMAX * m->TR);
+  f.decay = falloc(m, (size_t)PF_RMAX * m->TR); f.o = falloc(m, (size_t)PF_RMAX * m->vdc);
   f.kg_d = kg(d); f.kg_f = kg(m->f); f.kg_qa = kg(qa); f.kg_v = kg(m->vdc); f.kg_2d = kg(2 * d);
   {
-    const size_t ng = (PF_R + m->Tpf - 1) / m->Tpf, per = (size_t)m->H * m->Tpf * m->att_split;
+    const size_t ng = (PF_RMAX + m->Tpf - 1) / m->Tpf, per = (size_t)m->H * m->Tpf * m->att_split;
     f.pm = falloc(m, ng * per); f.pl = falloc(m, ng * per); f.po = falloc(m, ng * per * m->hd);
     if (!f.pm || !f.pl || !f.po) return -1;
   }
   f.rs = (RowSet *)dalloc(m, sizeof(RowSet) * (1 + PF_GROUPS));
-  f.ids = (int *)dalloc(m, (size_t)(PF_R + 1) * 4);
+  f.ids = (int *)dalloc(m, (size_t)(PF_RMAX + 1) * 4);
   if (!f.x || !f.x1 || !f.hn || !f.e || !f.qn || !f.y || !f.beta || !f.decay || !f.o || !f.kg_d || !f.kg_f || !f.kg_qa || !f.kg_v || !f.kg_2d ||
       !f.rs || !f.ids) return -1;
   f.ready = true;
@@ -1051,13 +1051,13 @@ static int pf_site(llb_spec *m, std::vector<PfSiteMat> mats, const __half *kg, i
     for (size_t g = 0; g < grp.size(); g++) {
       const PfSiteMat &sm = mats[grp[g]];
       OutBuf &o = *sm.out;
-      const size_t need = (size_t)a.ksplit * PF_R * sm.w->rows;
+      const size_t need = (size_t)a.ksplit * PF_RMAX * sm.w->rows;
       if (!o.p || o.cap < need) {
         o.p = falloc(m, need);
         if (!o.p) return -1;
         o.cap = need;
       }
-      o.ns = a.ksplit; o.stride = (long long)PF_R * sm.w->rows;
+      o.ns = a.ksplit; o.stride = (long long)PF_RMAX * sm.w->rows;
       a.m[g].W = sm.w->w; a.m[g].rows = sm.w->rows; a.m[g].ostride = sm.w->rows; a.m[g].out = o.p; a.m[g].split_stride = o.stride;
       done[grp[g]] = true;
     }
@@ -1134,7 +1134,7 @@ static int pf_prefill(llb_spec *m, int b, const int *ids, int n_rows, int keep, 
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (pf_prof_on()) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, g_llb.stream); }
   while (n_rows - p > keep) {
-    const int R = n_rows - p - keep < PF_R ? n_rows - p - keep : PF_R;
+    const int R = n_rows - p - keep < PF_RMAX ? n_rows - p - keep : PF_RMAX;
     CK(pf_chunk(m, b, ids, p, R));
     p += R;
   }
@@ -1340,7 +1340,7 @@ static int prefill_stream(llb_spec *m, int b, const int *ids, int n) {
   for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
   CK(ctl_write(m, b, c));
   int p = 0;
-  // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_R rows through the dense path (dense FFN only)
+  // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_RMAX rows through the dense path (dense FFN only)
   if (m->prefill_mode == 1 && m->ne == 0 && m->tp.size <= 1 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, b, ids, n - 1, m->Tspec, &p));
   while (p < n - 1) {
     // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
@@ -1716,7 +1716,7 @@ LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il
     return (int)have;
   }
   else if (what == 4) { have = m->d; src = m->hn + (size_t)((m->B > 1 ? b * m->Tspec : 0) + pos) * m->d; }
-  else if (what == 6 && m->pf.ready && pos >= 0 && pos < PF_R) { have = m->d; src = m->pf.hn + (size_t)(pos + 1) * m->d; }   // dense path: normed hidden of row `pos` of its last chunk
+  else if (what == 6 && m->pf.ready && pos >= 0 && pos < PF_RMAX) { have = m->d; src = m->pf.hn + (size_t)(pos + 1) * m->d; }   // dense path: normed hidden of row `pos` of its last chunk
   else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
   if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
   CU_OK(cudaMemcpy(out, src, have * 4, cudaMemcpyDeviceToHost));

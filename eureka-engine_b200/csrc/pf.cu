@@ -1,4 +1,4 @@
-// pf.cu -- the prompt path: a chunk of up to PF_R = 256 prompt rows per pass, dense GEMMs on tcgen05 (pfmm.cuh) and
+// pf.cu -- the prompt path: a chunk of up to PF_RMAX = 256 prompt rows per pass, dense GEMMs on tcgen05 (pfmm.cuh) and
 // row-batched small ops.  It stands where the reference has its fast prefill tier (host/llb_pf.h:551 pf_take; kernels
 // tools/pf27/pfmm.cuh, host/llb_pf.cuh; hand-off into the speculative state host/llb_host.c:1831-1899 spec_pf /
 // spec_take): the trunk's K/V rows, conv history and DeltaNet state after the chunk, the drafter's K/V rows for the
@@ -51,7 +51,7 @@ int pf_pick_ksplit(int ntiles, int nsb, int sms) {
 int pf_gemm(cudaStream_t s, int fmt, PfArgs &a) {
   if (a.nmat < 1 || a.nmat > PF_MAXMAT) return llb_fail("pf gemm: nmat %d", a.nmat);
   if (a.K % 256 || a.ksplit < 1 || a.ksplit > a.K / 256) return llb_fail("pf gemm: K %d in %d slices", a.K, a.ksplit);
-  if (a.R < 1 || a.R > PF_R) return llb_fail("pf gemm: %d rows", a.R);
+  if (a.R < 1 || a.R > PF_RMAX) return llb_fail("pf gemm: %d rows", a.R);
   a.t128[0] = 0;
   for (int i = 0; i < PF_MAXMAT; i++) a.t128[i + 1] = a.t128[i] + (i < a.nmat ? (a.m[i].rows + 127) / 128 : 0);
   a.err = g_pf_err;
@@ -352,7 +352,7 @@ int op_pf_pack(cudaStream_t s, const float *x, int K, int R, __half *kg) {
 extern "C" __attribute__((visibility("default")))
 int llb_b200_pf_gemm(int fmt, unsigned long long w, int rows, int K, unsigned long long x_f32, int R, unsigned long long out_f32, int ksplit) {
   if (!g_llb.stream) return llb_fail("llb_b200_init has not been called");
-  if (K < 256 || K % 256 || rows < 1 || R < 1 || R > PF_R) return llb_fail("pf_gemm: rows %d, K %d, R %d (K a multiple of 256, R up to %d)", rows, K, R, PF_R);
+  if (K < 256 || K % 256 || rows < 1 || R < 1 || R > PF_RMAX) return llb_fail("pf_gemm: rows %d, K %d, R %d (K a multiple of 256, R up to %d)", rows, K, R, PF_RMAX);
   if (!dev_row_bytes(fmt, K) || fmt == LLB_FM_F32) return llb_fail("pf_gemm: format %d has no kernel", fmt);
   if (pf_setup()) return -1;
   const int nsb = K / 256;
@@ -360,8 +360,8 @@ int llb_b200_pf_gemm(int fmt, unsigned long long w, int rows, int K, unsigned lo
   if (ksplit > nsb) return llb_fail("pf_gemm: %d K-slices of %d super-blocks", ksplit, nsb);
   __half *kg = nullptr;
   float *parts = nullptr;
-  CU_OK(cudaMalloc(&kg, pf_kg_halves(K) * 2));
-  CU_OK(cudaMemsetAsync(kg, 0, pf_kg_halves(K) * 2, g_llb.stream));
+  CU_OK(cudaMalloc(&kg, 2 * pf_kg_halves(K) * 2));      // two units of 128 rows
+  CU_OK(cudaMemsetAsync(kg, 0, 2 * pf_kg_halves(K) * 2, g_llb.stream));
   if (ksplit > 1) CU_OK(cudaMalloc(&parts, (size_t)ksplit * R * rows * 4));
   int rc = op_pf_pack(g_llb.stream, (const float *)(uintptr_t)x_f32, K, R, kg);
   PfArgs a;

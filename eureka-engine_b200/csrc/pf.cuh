@@ -13,7 +13,7 @@ struct PfArgs {
   PfMat m[PF_MAXMAT];
   int nmat;
   int t128[PF_MAXMAT + 1];   // prefix sums of 128-row tiles
-  int K, ksplit, R;          // columns, K-slices, rows of the chunk in use (<= PF_R)
+  int K, ksplit, R;          // columns, K-slices, rows of the chunk in use (<= PF_RMAX)
   const __half *x;           // activations, k-group major
   unsigned int *err;
 };

@@ -1,23 +1,29 @@
 // pfmm.cuh -- the prompt path's dense GEMM on the fifth-generation tensor cores: Y[r][n] = sum_k W[n][k] X[r][k] for a
-// chunk of up to PF_R = 128 prompt rows against Q4_K / Q5_K / Q6_K / Q8_0 weights.  It replaces, for this library, the
+// chunk of up to PF_RMAX = 256 prompt rows (two units of PF_R = 128) against Q4_K / Q5_K / Q6_K / Q8_0 weights.  It replaces, for this library, the
 // reference's chunked tensor-core prefill GEMM (tools/pf27/pfmm.cuh:311-384: int8 mma.sync + cp.async on sm_86; its
 // caller host/llb_pf.h:551 pf_take) with a design for sm_100a:
 //
-//   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 128 prompt rows, K = 16 per instruction) issued
-//     by ONE thread, both operands in shared memory, fp32 accumulators in TENSOR MEMORY;
+//   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 128 prompt rows, K = 16 per instruction), both
+//     operands in shared memory, fp32 accumulators in TENSOR MEMORY;
 //   * BOTH operands are two fp16 planes, hi = fp16(v) and lo = fp16((v - hi) * 2048) (about 22 bits of v, as the T-row
-//     path's activation planes): a 16-column step is three MMAs, hi.hi, hi.lo and lo.hi, each into its own accumulator
-//     and each issued by its own thread; the epilogue adds the two cross terms divided by 2048 (lo.lo is below fp32
-//     resolution).  With one fp16 plane per operand every
-//     GEMM output carried a relative error of 4e-4, which a random 8-layer model amplified past the path's 2e-2 bar;
+//     path's activation planes): a 16-column step is three MMAs per unit of 128 rows, hi.hi into one accumulator and the
+//     two cross terms hi.lo and lo.hi into another; the epilogue adds the cross terms divided by 2048 (lo.lo is below
+//     fp32 resolution).  With one fp16 plane per operand every GEMM output carried a relative error of 4e-4, which a
+//     random 8-layer model amplified past the path's 2e-2 bar;
+//   * a weight stage is dequantised ONCE and multiplied against BOTH units of the chunk (four accumulators of 128
+//     columns: all 512 columns of tensor memory): the kernel is bound by turning codes into fp16 planes (14.5 thread
+//     instructions per weight, the tensor pipe 40 % busy with one unit), so the second unit's MMAs are nearly free;
 //   * the activation planes arrive by TMA: the chunk's activations are kept in global memory in the order the operand
 //     wants (k-group major, common.cuh), so a 64-column stage of one plane is ONE contiguous 16 KB cp.async.bulk that
 //     completes on an mbarrier (plain bulk copies of this GPU's own memory, no multicast);
 //   * the weight planes are made on the fly: eight warps read the packed super-blocks (each thread one row's 32 weights
 //     of a stage), dequantise in fp32 (the formulas of tools/qwen35_engine.c:233-307, one FMA per weight), split
 //     each weight into its two planes and store 16-byte core-matrix rows; stores of a warp are conflict-free;
-//   * a three-stage ring of (32 KB weights, 32 KB activations) with full / empty mbarriers decouples the roles, so
-//     loads and dequantisation run ahead while four more warps read a finished tile out with tcgen05.ld;
+//   * a two-stage ring of (32 KB weights, 2 x 32 KB activations) with full / empty mbarriers decouples the roles, so
+//     loads and dequantisation run ahead of the MMAs; four more warps read a finished tile out with tcgen05.ld.
+//     (Separate rings -- three weight stages and four half-stages of 32 activation columns, which fit the same shared
+//     memory -- were measured and dropped: the issuing threads then wait and commit twice as often, and a gate|up launch
+//     took 319 us against 262 us);
 //   * every wait is bounded: a wait that runs out sets *err, and all roles then run through without waiting, so the
 //     kernel returns, frees its tensor memory and leaves the context usable (llb_b200_wait_errors() reports it).
 #pragma once
@@ -26,12 +32,12 @@
 #include "pf.cuh"
 
 #define PF_KS 64              // columns per ring stage
-#define PF_STAGES 3
+#define PF_STAGES 2
 #define PF_A_BYTES (128 * PF_KS * 2)     // one plane of 128 weight rows
-#define PF_B_BYTES (PF_R * PF_KS * 2)    // one plane of the chunk's rows
-#define PF_STAGE_BYTES (2 * PF_A_BYTES + 2 * PF_B_BYTES)   // [A hi | A lo | B hi | B lo]
+#define PF_B_BYTES (PF_R * PF_KS * 2)    // one plane of one unit of the chunk's rows
+#define PF_STAGE_BYTES (2 * PF_A_BYTES + 4 * PF_B_BYTES)   // [A hi | A lo | unit 0: B hi | B lo | unit 1: B hi | B lo]
 #define PF_SMEM (1024 + PF_STAGES * PF_STAGE_BYTES)
-#define PF_THREADS 512        // warps 0-7 dequantise, 8 loads activations, 9 issues MMAs, 12-15 write results
+#define PF_THREADS 512        // warps 0-7 dequantise, 8 loads activations, 9-11 issue MMAs, 12-15 write results
 #define PF_IDESC 0x08200010u  // kind::f16: D f32, A / B f16 K-major, N = 128, M = 128
 
 
@@ -163,19 +169,20 @@ template <int FMT>
 __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // header: full_a[4] +0, full_b[4] +32, empty[4] +64, acc_full[2] +96, acc_empty[2] +112, tensor-memory address +128, dead +132
+  // header: full_a[4] +0, full_b[4] +32, empty[4] +64, acc_full +128, acc_empty +136, tensor-memory address +144, dead +148
   const uint32_t bar_s = smem_u32(smem);
   auto full_a = [&](int s) { return bar_s + 8u * (uint32_t)s; };
   auto full_b = [&](int s) { return bar_s + 32u + 8u * (uint32_t)s; };
   auto empty = [&](int s) { return bar_s + 64u + 8u * (uint32_t)s; };
-  auto acc_full = [&](int b) { return bar_s + 96u + 8u * (uint32_t)b; };
-  auto acc_empty = [&](int b) { return bar_s + 112u + 8u * (uint32_t)b; };
-  uint32_t *tmem_slot = (uint32_t *)(smem + 128);
-  volatile uint32_t *dead = (volatile uint32_t *)(smem + 132);
+  auto acc_full = [&](int b) { return bar_s + 128u + 8u * (uint32_t)b; };
+  auto acc_empty = [&](int b) { return bar_s + 136u + 8u * (uint32_t)b; };
+  uint32_t *tmem_slot = (uint32_t *)(smem + 144);
+  volatile uint32_t *dead = (volatile uint32_t *)(smem + 148);
   uint8_t *ring = smem + 1024;
   const uint32_t ring_s = smem_u32(ring);
   const int ntiles = a.t128[a.nmat], nunits = ntiles * a.ksplit;
   const size_t rb = dev_row_bytes(FMT, a.K);
+  const int nun = a.R > PF_R ? 2 : 1;   // units of 128 rows in this chunk
 
   pdl_trigger();
   if (tid == 0) {
@@ -252,7 +259,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
       }
     }
   } else if (warp == 8) {
-    // ---- activations: one 16 KB bulk copy per plane and stage ----
+    // ---- activations: one 16 KB bulk copy per unit, plane and stage ----
     if (lane == 0) {
       int it = 0;
       for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
@@ -264,21 +271,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
           if (*dead) continue;
           const __half *src = a.x + (size_t)((kbase + s * PF_KS) >> 3) * PF_R * 8;
           const uint32_t dst = ring_s + slot * PF_STAGE_BYTES + 2 * PF_A_BYTES;
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_b(slot)), "r"((uint32_t)(2 * PF_B_BYTES)) : "memory");
-          pf_bulk_copy(dst, src, PF_B_BYTES, full_b(slot));
-          pf_bulk_copy(dst + PF_B_BYTES, src + (size_t)a.K * PF_R, PF_B_BYTES, full_b(slot));
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_b(slot)), "r"((uint32_t)(nun * 2 * PF_B_BYTES)) : "memory");
+          for (int un = 0; un < nun; un++) {   // a unit's planes follow the previous unit's in global memory (common.cuh)
+            const __half *su = src + (size_t)un * pf_kg_halves(a.K);
+            pf_bulk_copy(dst + un * 2 * PF_B_BYTES, su, PF_B_BYTES, full_b(slot));
+            pf_bulk_copy(dst + un * 2 * PF_B_BYTES + PF_B_BYTES, su + (size_t)a.K * PF_R, PF_B_BYTES, full_b(slot));
+          }
         }
       }
     }
   } else if (warp >= 9 && warp < 12) {
     // ---- the tensor core.  Issuing one tcgen05.mma costs a thread 100 to 200 cycles, more than a 128 x 128 x 16 MMA
-    // takes to execute, so the three products of a step have a thread each, and an accumulator each (a thread's MMAs
-    // execute in its issue order; MMAs of different threads into one accumulator would not be ordered):
-    //   warp 9: hi.hi -> D1     warp 10: hi.lo -> D2     warp 11: lo.hi -> D3     result = D1 + (D2 + D3) / 2048
+    // takes to execute, so the products of a step are spread over three threads; MMAs into one accumulator come from
+    // one thread (a thread's MMAs execute in its issue order, MMAs of different threads would not be ordered):
+    //   warp 9:  hi.hi of unit 0 -> D1(0), hi.hi of unit 1 -> D1(1)
+    //   warp 10: hi.lo and lo.hi of unit 0 -> D23(0)        warp 11: hi.lo and lo.hi of unit 1 -> D23(1)
+    //   result of a unit = D1 + D23 / 2048; tensor-memory columns: D1(0) 0, D23(0) 128, D1(1) 256, D23(1) 384
     if (lane == 0) {
       const int which = warp - 9;
-      const uint32_t d = tmem_base + (uint32_t)(which * PF_R);
-      const uint32_t a_off = which == 2 ? PF_A_BYTES : 0, b_off = 2 * PF_A_BYTES + (which == 1 ? PF_B_BYTES : 0);
       int it = 0, i = 0;
       for (int u = blockIdx.x; u < nunits; u += gridDim.x, i++) {
         int kbase, nst;
@@ -290,11 +300,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
           wait(full_a(slot), (uint32_t)(it / PF_STAGES) & 1u);
           wait(full_b(slot), (uint32_t)(it / PF_STAGES) & 1u);
           t5_fence_after();
-          const uint64_t ad = g3_desc(ring_s + slot * PF_STAGE_BYTES + a_off, 2048, 128), bd = g3_desc(ring_s + slot * PF_STAGE_BYTES + b_off, PF_R * 16, 128);
+          const uint32_t st = ring_s + slot * PF_STAGE_BYTES, b0 = st + 2 * PF_A_BYTES;
+          const uint64_t a_hi = g3_desc(st, 2048, 128), a_lo = g3_desc(st + PF_A_BYTES, 2048, 128);
+          if (!*dead) {
 #pragma unroll
-          for (int k = 0; k < PF_KS / 16; k++)   // a step is two k-groups further on: the address field counts 16-byte units
-            pf_mma_ss(d, ad + (uint64_t)(k * 2 * 2048 / 16), bd + (uint64_t)(k * 2 * PF_R * 16 / 16), PF_IDESC, (s | k) != 0);
-          t5_commit(empty(slot));        // arrives when these MMAs have read the stage
+            for (int k = 0; k < PF_KS / 16; k++) {   // a step is two k-groups further on: the address field counts 16-byte units
+              const uint64_t ka = (uint64_t)(k * 2 * 2048 / 16), kb = (uint64_t)(k * 2 * PF_R * 16 / 16);
+              const uint32_t first = (s | k) != 0;
+              if (which == 0) {
+                for (int un = 0; un < nun; un++)
+                  pf_mma_ss(tmem_base + (uint32_t)(un * 2 * PF_R), a_hi + ka, g3_desc(b0 + un * 2 * PF_B_BYTES, PF_R * 16, 128) + kb, PF_IDESC, first);
+              } else if (which - 1 < nun) {
+                const int un = which - 1;
+                const uint32_t d = tmem_base + (uint32_t)(un * 2 * PF_R + PF_R);
+                const uint64_t b_hi = g3_desc(b0 + un * 2 * PF_B_BYTES, PF_R * 16, 128) + kb, b_lo = g3_desc(b0 + un * 2 * PF_B_BYTES + PF_B_BYTES, PF_R * 16, 128) + kb;
+                pf_mma_ss(d, a_hi + ka, b_lo, PF_IDESC, first);
+                pf_mma_ss(d, a_lo + ka, b_hi, PF_IDESC, 1u);
+              }
+            }
+          }
+          t5_commit(empty(slot));        // arrives when this thread's MMAs have read the stage
         }
         t5_commit(acc_full(0));          // ... and when this thread's share of the tile is in tensor memory
       }
@@ -314,16 +339,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
       wait(acc_full(0), (uint32_t)i & 1u);
       t5_fence_after();
       const uint32_t t0 = tmem_base + ((uint32_t)(32 * q) << 16);
-      for (int c = 0; c < a.R; c += 16) {
-        float v[16], v2[16], v3[16];
-        t5_ld16(t0 + c, v);
-        t5_ld16(t0 + PF_R + c, v2);
-        t5_ld16(t0 + 2 * PF_R + c, v3);
+      for (int c = 0; c < a.R; c += 16) {     // chunk rows c .. c + 15: unit c / 128, its columns c % 128 ..
+        float v[16], v2[16];
+        const uint32_t col = (uint32_t)((c / PF_R) * 2 * PF_R + (c % PF_R));
+        t5_ld16(t0 + col, v);
+        t5_ld16(t0 + col + PF_R, v2);
         t5_wait_ld();
         if (row < M.rows) {
 #pragma unroll
           for (int j = 0; j < 16; j++)
-            if (c + j < a.R) out[(size_t)(c + j) * M.ostride] = v[j] + (v2[j] + v3[j]) * XP_LO_INV;
+            if (c + j < a.R) out[(size_t)(c + j) * M.ostride] = v[j] + v2[j] * XP_LO_INV;
         }
       }
       t5_fence_before();

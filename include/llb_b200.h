@@ -123,7 +123,7 @@ LLB_API int llb_b200_gemm_host(int fmt, llb_b200_dptr w, int rows, int K, const 
                        llb_b200_dptr x_dev, llb_b200_dptr y_dev);
 
 /* The prompt path's dense GEMM alone (replaces the reference's chunked tensor-core prefill GEMM, tools/pf27/pfmm.cuh:311-384):
- * Y[r][n] = sum_c W[n][c] x[r][c] for R <= 128 rows of f32 activations x [R][K] against a weight matrix in the device
+ * Y[r][n] = sum_c W[n][c] x[r][c] for R <= 256 rows (two units of 128 against every dequantised weight stage) of f32 activations x [R][K] against a weight matrix in the device
  * layout, out f32 [R][rows]; tcgen05.mma with both operands as two fp16 planes (about 22 bits) and fp32 sums in tensor memory.  ksplit = 0
  * picks the K-split (at most K / 256 slices of whole super-blocks).  Synchronises; scratch is allocated and freed inside the call. */
 LLB_API int llb_b200_pf_gemm(int fmt, llb_b200_dptr w, int rows, int K, llb_b200_dptr x_f32, int R, llb_b200_dptr out_f32, int ksplit);

@@ -1,7 +1,8 @@
 """The prompt path's dense GEMM (tcgen05, both operands as two fp16 planes) against float64 dot products of the oracle's
 dequantised weights,
 through the C ABI: every weight format, ragged row counts (tiles of 128 with a partial last tile), partial chunks,
-several K-slices, and enough tiles that a CTA takes more than two (both accumulators of tensor memory in use)."""
+chunks of one and of two units of 128 rows (the second unit partial), several K-slices, and enough tiles that a CTA
+takes more than two."""
 import numpy as np
 import pytest
 import torch
@@ -35,6 +36,8 @@ def _case(llb, packs, oracle, dev, ty, rows, K, R, ksplit, seed):
 def test_dense_gemm_formats(llb, packs, oracle, dev, ty):
     _case(llb, packs, oracle, dev, ty, 200, 512, 128, 0, seed=1)        # a partial second tile
     _case(llb, packs, oracle, dev, ty, 128, 1024, 37, 2, seed=2)        # a partial chunk, two K-slices
+    _case(llb, packs, oracle, dev, ty, 300, 768, 256, 0, seed=6)        # two whole units of 128 rows
+    _case(llb, packs, oracle, dev, ty, 130, 512, 191, 2, seed=7)        # the second unit partial
 
 
 def test_dense_gemm_many_tiles_and_slices(llb, packs, oracle, dev):
@@ -43,3 +46,4 @@ def test_dense_gemm_many_tiles_and_slices(llb, packs, oracle, dev):
     _case(llb, packs, oracle, dev, "Q4_K", rows, 256, 128, 1, seed=3)
     _case(llb, packs, oracle, dev, "Q4_K", 640, 2048, 100, 4, seed=4)
     _case(llb, packs, oracle, dev, "Q6_K", 48, 1536, 128, 3, seed=5)    # fewer rows than a tile
+    _case(llb, packs, oracle, dev, "Q4_K", 128 * (sms + 9), 512, 256, 1, seed=8)   # two units, more than one tile per CTA
