@@ -160,17 +160,17 @@ __device__ __forceinline__ void xp_store4(const XPlanes &xp, int t, int planes, 
 }
 
 // ---- activations of a prompt chunk ----------------------------------------------------------------
-#define PF_R 128              // rows of one unit of a prompt chunk (= N of the dense GEMM's MMA, pfmm.cuh)
-#define PF_RMAX 256           // rows of a prompt chunk: two units, multiplied against the same dequantised weight stage
+#define PF_R 256              // rows of a prompt chunk (= N of the dense GEMM's MMA, pfmm.cuh)
+#define PF_RMAX 256           // ... of PF_RMAX / PF_R units multiplied against the same dequantised weight stage (one)
 // Activations of a chunk for the dense GEMM, "k-group major", as two fp16 planes like the T-row planes: hi = fp16(x),
 // lo = fp16((x - hi) * 2048), about 22 bits of x.  Element (row r, column k) of a [PF_R][K] matrix sits at half index
 // ((k >> 3) * PF_R + r) * 8 + (k & 7) of its plane; the lo plane follows the hi plane (K * PF_R halves further on).  Eight
 // consecutive columns of one row are one 16-byte core-matrix row, the PF_R rows of a k-group are contiguous (2 KB), and
-// a 64-column stage of one plane is one 16 KB run.  A chunk of more than PF_R rows is two such matrices one after the other.
+// a 64-column stage of one plane is one contiguous run (32 KB).  A chunk of more than PF_R rows is two such matrices one after the other.
 __host__ __device__ inline size_t pf_kg_halves(int K) { return (size_t)2 * K * PF_R; }
 // four consecutive columns k .. k+3 (k a multiple of 4) of row r into both planes
 __device__ __forceinline__ void pf_kg_store4(__half *x, int K, int r, int k, float v0, float v1, float v2, float v3) {
-  if (r >= PF_R) { x += pf_kg_halves(K); r -= PF_R; }   // the chunk's second unit of 128 rows follows the first
+  if (r >= PF_R) { x += pf_kg_halves(K); r -= PF_R; }   // a second unit of a chunk follows the first
   const size_t i = ((size_t)(k >> 3) * PF_R + r) * 8 + (k & 4);
   const __half2 a = __floats2half2_rn(v0, v1), b = __floats2half2_rn(v2, v3);
   const float2 af = __half22float2(a), bf = __half22float2(b);

@@ -1,25 +1,26 @@
 // pfmm.cuh -- the prompt path's dense GEMM on the fifth-generation tensor cores: Y[r][n] = sum_k W[n][k] X[r][k] for a
-// chunk of up to PF_RMAX = 256 prompt rows (two units of PF_R = 128) against Q4_K / Q5_K / Q6_K / Q8_0 weights.  It replaces, for this library, the
+// chunk of up to PF_R = 256 prompt rows against Q4_K / Q5_K / Q6_K / Q8_0 weights.  It replaces, for this library, the
 // reference's chunked tensor-core prefill GEMM (tools/pf27/pfmm.cuh:311-384: int8 mma.sync + cp.async on sm_86; its
 // caller host/llb_pf.h:551 pf_take) with a design for sm_100a:
 //
-//   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 128 prompt rows, K = 16 per instruction), both
+//   * the multiply is tcgen05.mma (kind::f16, M = 128 weight rows, N = 256 prompt rows, K = 16 per instruction), both
 //     operands in shared memory, fp32 accumulators in TENSOR MEMORY;
 //   * BOTH operands are two fp16 planes, hi = fp16(v) and lo = fp16((v - hi) * 2048) (about 22 bits of v, as the T-row
-//     path's activation planes): a 16-column step is three MMAs per unit of 128 rows, hi.hi into one accumulator and the
-//     two cross terms hi.lo and lo.hi into another; the epilogue adds the cross terms divided by 2048 (lo.lo is below
-//     fp32 resolution).  With one fp16 plane per operand every GEMM output carried a relative error of 4e-4, which a
+//     path's activation planes): a 16-column step is three MMAs, hi.hi into one accumulator of 256 columns and the
+//     two cross terms hi.lo and lo.hi into another (together all 512 columns of tensor memory); the epilogue adds the
+//     cross terms divided by 2048 (lo.lo is below fp32 resolution).  With one fp16 plane per operand every GEMM output carried a relative error of 4e-4, which a
 //     random 8-layer model amplified past the path's 2e-2 bar;
-//   * a weight stage is dequantised ONCE and multiplied against BOTH units of the chunk (four accumulators of 128
-//     columns: all 512 columns of tensor memory): the kernel is bound by turning codes into fp16 planes (14.5 thread
-//     instructions per weight, the tensor pipe 40 % busy with one unit), so the second unit's MMAs are nearly free;
+//   * N = 256 because the kernel is bound by turning codes into fp16 planes (14.5 thread instructions per weight; with
+//     N = 128 the tensor pipe was 40 % busy): a dequantised weight stage now serves twice the rows.  Measured on the
+//     27B shape's gate|up launch: N = 128, three stages, three accumulators 174 us per 128 rows; two units of N = 128
+//     per stage (four accumulators) 262 us per 256 rows; N = 256 238 us per 256 rows;
 //   * the activation planes arrive by TMA: the chunk's activations are kept in global memory in the order the operand
 //     wants (k-group major, common.cuh), so a 64-column stage of one plane is ONE contiguous 16 KB cp.async.bulk that
 //     completes on an mbarrier (plain bulk copies of this GPU's own memory, no multicast);
 //   * the weight planes are made on the fly: eight warps read the packed super-blocks (each thread one row's 32 weights
 //     of a stage), dequantise in fp32 (the formulas of tools/qwen35_engine.c:233-307, one FMA per weight), split
 //     each weight into its two planes and store 16-byte core-matrix rows; stores of a warp are conflict-free;
-//   * a two-stage ring of (32 KB weights, 2 x 32 KB activations) with full / empty mbarriers decouples the roles, so
+//   * a two-stage ring of (32 KB weights, 64 KB activations) with full / empty mbarriers decouples the roles, so
 //     loads and dequantisation run ahead of the MMAs; four more warps read a finished tile out with tcgen05.ld.
 //     (Separate rings -- three weight stages and four half-stages of 32 activation columns, which fit the same shared
 //     memory -- were measured and dropped: the issuing threads then wait and commit twice as often, and a gate|up launch
@@ -35,10 +36,11 @@
 #define PF_STAGES 2
 #define PF_A_BYTES (128 * PF_KS * 2)     // one plane of 128 weight rows
 #define PF_B_BYTES (PF_R * PF_KS * 2)    // one plane of one unit of the chunk's rows
-#define PF_STAGE_BYTES (2 * PF_A_BYTES + 4 * PF_B_BYTES)   // [A hi | A lo | unit 0: B hi | B lo | unit 1: B hi | B lo]
+#define PF_NUN (PF_RMAX / PF_R)   // units of a chunk
+#define PF_STAGE_BYTES (2 * PF_A_BYTES + 2 * PF_NUN * PF_B_BYTES)   // [A hi | A lo | per unit: B hi | B lo]
 #define PF_SMEM (1024 + PF_STAGES * PF_STAGE_BYTES)
 #define PF_THREADS 512        // warps 0-7 dequantise, 8 loads activations, 9-11 issue MMAs, 12-15 write results
-#define PF_IDESC 0x08200010u  // kind::f16: D f32, A / B f16 K-major, N = 128, M = 128
+#define PF_IDESC (0x08000010u | ((uint32_t)(PF_R >> 3) << 17))  // kind::f16: D f32, A / B f16 K-major, N = PF_R, M = 128
 
 
 __device__ __forceinline__ void pf_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
   const uint32_t ring_s = smem_u32(ring);
   const int ntiles = a.t128[a.nmat], nunits = ntiles * a.ksplit;
   const size_t rb = dev_row_bytes(FMT, a.K);
-  const int nun = a.R > PF_R ? 2 : 1;   // units of 128 rows in this chunk
+  const int nun = a.R > PF_R ? 2 : 1;   // units of PF_R rows in this chunk
 
   pdl_trigger();
   if (tid == 0) {
@@ -284,9 +286,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_pfmm(const PfArgs a) {
     // ---- the tensor core.  Issuing one tcgen05.mma costs a thread 100 to 200 cycles, more than a 128 x 128 x 16 MMA
     // takes to execute, so the products of a step are spread over three threads; MMAs into one accumulator come from
     // one thread (a thread's MMAs execute in its issue order, MMAs of different threads would not be ordered):
-    //   warp 9:  hi.hi of unit 0 -> D1(0), hi.hi of unit 1 -> D1(1)
-    //   warp 10: hi.lo and lo.hi of unit 0 -> D23(0)        warp 11: hi.lo and lo.hi of unit 1 -> D23(1)
-    //   result of a unit = D1 + D23 / 2048; tensor-memory columns: D1(0) 0, D23(0) 128, D1(1) 256, D23(1) 384
+    //   warp 9: hi.hi -> D1     warp 10: hi.lo and lo.hi -> D23     result = D1 + D23 / 2048
+    //   (tensor-memory columns: D1 at 0, D23 at PF_R.  The code is written for PF_RMAX / PF_R units of PF_R rows, unit un
+    //   with its pair of accumulators at 2 un PF_R and warp 10 + un issuing its cross terms; PF_R = 256 leaves one unit)
     if (lane == 0) {
       const int which = warp - 9;
       int it = 0, i = 0;
