@@ -1684,6 +1684,7 @@ LLB_API int llb_spec_read_state(llb_spec *m, int what, int il, int pos, float *o
 LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il, int pos, float *out, size_t n) {
   if (stream < 0 || stream >= m->B) return llb_fail("read_state: stream %d of %d", stream, m->B);
   const int b = stream;
+  if (il < 0 || pos < 0 || ((what == 1 || what == 2 || what == 5) && pos >= m->max_ctx)) return llb_fail("read_state: layer %d, position %d", il, pos);
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   const float *src = nullptr;
   size_t have = 0;
@@ -1715,7 +1716,7 @@ LLB_API int llb_spec_read_state_stream(llb_spec *m, int stream, int what, int il
     }
     return (int)have;
   }
-  else if (what == 4) { have = m->d; src = m->hn + (size_t)((m->B > 1 ? b * m->Tspec : 0) + pos) * m->d; }
+  else if (what == 4 && pos < (m->B > 1 ? m->Tspec : SPEC_MAXT)) { have = m->d; src = m->hn + (size_t)((m->B > 1 ? b * m->Tspec : 0) + pos) * m->d; }
   else if (what == 6 && m->pf.ready && pos >= 0 && pos < PF_RMAX) { have = m->d; src = m->pf.hn + (size_t)(pos + 1) * m->d; }   // dense path: normed hidden of row `pos` of its last chunk
   else return llb_fail("read_state: nothing of kind %d in layer %d", what, il);
   if (n < have) return llb_fail("read_state: buffer of %zu floats, %zu needed", n, have);
@@ -1754,6 +1755,7 @@ LLB_API int llb_spec_moe_ffn(llb_spec *m, int il, int T, const float *h2, float 
 }
 
 LLB_API int llb_spec_read_logits(llb_spec *m, int r, float *out) {
+  if (r < 0 || r >= m->Tmax || !m->b_lg.p) return llb_fail("read_logits: row %d of a pass of %d rows", r, m->Tmax);
   CU_OK(cudaStreamSynchronize(g_llb.stream));
   std::vector<float> tmp(m->V);
   for (int i = 0; i < m->V; i++) out[i] = 0.0f;
