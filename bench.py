@@ -261,7 +261,7 @@ def run_streams(args, rank, world, local):
     cfg = getattr(packs, builder)()
     pack = packs.build_pack(cfg, device=f"cuda:{local}", layers=args.layers or None)
     moe = bool(getattr(cfg, "n_experts", 0))
-    mtp = None if (moe or k == 0) else packs.aux1_bytes(packs.build_mtp(pack))
+    mtp = None if (moe or k == 0) else packs.aux1_bytes(packs.build_mtp(pack, draft_vocab=DRAFT_VOCAB))   # the drafter's head: the draft-vocabulary slice
     steps, warm = args.steps, max(args.warmup, 3)
     max_ctx = n_prompt + (steps + warm + 8) * (k + 1) + 64
     torch.cuda.synchronize()
