@@ -756,8 +756,8 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   if (nstreams < 1 || nstreams > 16) return llb_fail("streams: %d (1..16 per engine)", nstreams);
   m->B = nstreams;
   if (m->B > 1) {
-    // the rows of all streams go through every GEMM together: 16 rows at most (32 plane columns), 8 with routed experts
-    const int cap = m->ne > 0 ? 8 : 16;
+    // the rows of all streams go through every GEMM together: 16 rows at most (32 plane columns)
+    const int cap = 16;
     if (m->B * m->Tspec > cap) return llb_fail("streams: %d streams of k + 1 = %d rows are %d rows a pass, the limit is %d", m->B, m->Tspec, m->B * m->Tspec, cap);
     if (tp_on) return llb_fail("streams: a tensor-parallel engine runs one stream");
   }
@@ -1206,7 +1206,7 @@ LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, siz
   return open_any(index_text, pack, pack_bytes, pack_on_device, mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, tp_n, 1);
 }
 // The engine with `streams` independent sequences that share every weight read: a pass carries the k + 1 rows of every
-// stream through each GEMM together (streams x (k + 1) <= 16 rows; <= 8 with routed experts), attention, the DeltaNet
+// stream through each GEMM together (streams x (k + 1) <= 16 rows), attention, the DeltaNet
 // scan, the drafter and the accept step run per stream in the same launches.  A stream's tokens are those of the
 // same stream alone in such an engine, bit for bit (a row's GEMM result does not depend on its neighbours).
 LLB_API llb_spec *llb_spec_open_streams(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,

@@ -99,6 +99,8 @@ template <int FMT> static int setup_moe() {
   CU_OK(cudaFuncSetAttribute(k_moe_gu<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_moe_gu<FMT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
+  CU_OK(cudaFuncSetAttribute(k_moe_dn<FMT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   CU_OK(cudaFuncSetAttribute(k_moe_dn_silu<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_MAX));
   return 0;
 }
@@ -239,8 +241,8 @@ template <int FMT, int NT> static int launch_moe(cudaStream_t s, bool down, cons
     if constexpr (NT == 1) e = llb_launch(k_moe_dn_silu<FMT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, wt_silu, cps);
     else return llb_fail("moe gemm: the down launch builds its own activations for T <= 4 only");
   } else {
-    e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps)
-             : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, cps);
+    e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(g2_warps<FMT>(NC) * 32), smem, s, a, m, cps)
+             : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(g2_warps<FMT>(NC) * 32), smem, s, a, m, cps);
   }
   if (e != cudaSuccess) return llb_fail("moe gemm launch: %s", cudaGetErrorString(e));
   return 0;
@@ -254,7 +256,7 @@ int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeAr
   GemmArgs a;
   memset(&a, 0, sizeof a);
   a.K = down ? m.nslot * m.ef : m.d;
-  if (xp.K != a.K || (xp.NC != 8 && xp.NC != 16)) return llb_fail("moe gemm: planes of %d x %d columns, K is %d", xp.K, xp.NC, a.K);
+  if (xp.K != a.K || (xp.NC != 8 && xp.NC != 16 && xp.NC != 32)) return llb_fail("moe gemm: planes of %d x %d columns, K is %d", xp.K, xp.NC, a.K);
   a.nsb = a.K / 256; a.xp = xp; a.planes = 2; a.T = m.T; a.nmat = 0;
   const int ntiles = down ? m.T * (m.d / 16) : m.T * m.nslot * (m.ef / 8);
   int ks = 1;
@@ -264,8 +266,7 @@ int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeAr
   a.ksplit = ks;
   if (ksplit) *ksplit = ks;
   const int NT = xp.NC / 8;
-  if (NT > 2) return llb_fail("moe gemm: at most 8 rows per pass (%d plane columns asked for)", xp.NC);
-#define MOE_GO(F) return NT == 1 ? launch_moe<F, 1>(s, down, a, m, ntiles, wt_silu) : launch_moe<F, 2>(s, down, a, m, ntiles, wt_silu)
+#define MOE_GO(F) return NT == 1 ? launch_moe<F, 1>(s, down, a, m, ntiles, wt_silu) : NT == 2 ? launch_moe<F, 2>(s, down, a, m, ntiles, wt_silu) : launch_moe<F, 4>(s, down, a, m, ntiles, wt_silu)
   if (fmt == LLB_FM_Q4_K) MOE_GO(LLB_FM_Q4_K);
   if (fmt == LLB_FM_Q5_K) MOE_GO(LLB_FM_Q5_K);
   MOE_GO(LLB_FM_Q6_K);

@@ -97,7 +97,10 @@ template <int FMT> struct G2MatsPlain {
   }
 };
 
-template <int FMT, int NT, class Stage, class Mats>
+// NTC < NT (the routed-expert launches at 16 rows): a weight tile is multiplied with NTC = 2 of the NT staged n-tiles only,
+// the hi and lo tiles of the eight rows its own row is among (Mats::col0(tile) = first plane column of the hi tile; the
+// lo tile is NC / 2 columns on), since the epilogue keeps one row of the tile.
+template <int FMT, int NT, class Stage, class Mats, int NTC = NT>
 __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage, const Mats mats) {
   using TR = G2Traits<FMT>;
   constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = g2_warps<FMT>(8 * NT), ST = g2_stages<FMT>(8 * NT);
@@ -172,7 +175,10 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
   // warp again: ST-1 chunks are complete, none pending
   int pstage = ST - 1, cstage = 0;
   int c_tile = warp * cps + ci, c_c = 0;
-  float acc[NT][4];
+  static_assert(NTC == NT || NTC == 2, "a column selection computes one hi and one lo n-tile");
+  constexpr int NTS = NTC == NT ? 8 : NC / 2;            // plane columns from one computed n-tile to the next
+  int cb = 0;                                            // first plane column of the computed n-tiles
+  float acc[NTC][4];
   const uint8_t *xb = xh_s + gid * CS + 16 * j;          // B fragments of column gid (n-tile 0)
   const uint8_t *xfb = xsf_s + gid * 32 + 8 * j;
   const uint32_t mn_sel = (j & 1) ? 0x4342u : 0x4140u;
@@ -180,7 +186,8 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
   while (c_tile < ntiles) {
     if (c_c == 0) {
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+      for (int nt = 0; nt < NTC; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+      if constexpr (NTC != NT) cb = mats.col0(c_tile);
     }
     issue(pstage);                       // refill the stage consumed last iteration
     pstage = pstage + 1 == ST ? 0 : pstage + 1;
@@ -192,11 +199,11 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
       const uint8_t *b0 = ring + cstage * 16 * RS + gid * RS, *b1 = b0 + 8 * RS;
       const uint4 sw0 = *(const uint4 *)(b0 + 256), sw1 = *(const uint4 *)(b1 + 256);
       const uint32_t d0w[4] = {sw0.x, sw0.y, sw0.z, sw0.w}, d1w[4] = {sw1.x, sw1.y, sw1.z, sw1.w};
-      const uint8_t *xb8 = xh_s + gid * CS + 8 * j + (size_t)c_c * 512;
-      const float *xs8 = (const float *)xsf_s + (size_t)c_c * 8 * NC + 2 * j;
+      const uint8_t *xb8 = xh_s + (gid + cb) * CS + 8 * j + (size_t)c_c * 512;
+      const float *xs8 = (const float *)xsf_s + (size_t)c_c * 8 * NC + 2 * j + cb;
 #pragma unroll
       for (int blk = 0; blk < 8; blk++) {
-        float p[NT][4];
+        float p[NTC][4];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
           const int m = 2 * blk + u;
@@ -204,16 +211,16 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
           const uint32_t a0 = __byte_perm(w0, 0, 0x4240), a2 = __byte_perm(w0, 0, 0x4341);
           const uint32_t a1 = __byte_perm(w1, 0, 0x4240), a3 = __byte_perm(w1, 0, 0x4341);
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            const uint2 bx = *(const uint2 *)(xb8 + (size_t)nt * 8 * CS + 32 * m);
+          for (int nt = 0; nt < NTC; nt++) {
+            const uint2 bx = *(const uint2 *)(xb8 + (size_t)nt * NTS * CS + 32 * m);
             if (u == 0) mma16816_z(p[nt], a0, a1, a2, a3, bx.x, bx.y);
             else mma16816(p[nt], a0, a1, a2, a3, bx.x, bx.y);
           }
         }
         const float d0 = h2f_bits((d0w[blk >> 1] >> (16 * (blk & 1))) & 0xffffu), d1 = h2f_bits((d1w[blk >> 1] >> (16 * (blk & 1))) & 0xffffu);
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-          const float2 xs = *(const float2 *)(xs8 + (size_t)blk * NC + nt * 8);
+        for (int nt = 0; nt < NTC; nt++) {
+          const float2 xs = *(const float2 *)(xs8 + (size_t)blk * NC + nt * NTS);
           acc[nt][0] += d0 * (p[nt][0] * TWO24 - 128.0f * xs.x);
           acc[nt][1] += d0 * (p[nt][1] * TWO24 - 128.0f * xs.y);
           acc[nt][2] += d1 * (p[nt][2] * TWO24 - 128.0f * xs.x);
@@ -228,8 +235,8 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
       const uint4 sw0 = *(const uint4 *)(b0 + 192), sw1 = *(const uint4 *)(b1 + 192);
       const uint32_t sc0w[4] = {sw0.x ^ 0x80808080u, sw0.y ^ 0x80808080u, sw0.z ^ 0x80808080u, sw0.w ^ 0x80808080u};
       const uint32_t sc1w[4] = {sw1.x ^ 0x80808080u, sw1.y ^ 0x80808080u, sw1.z ^ 0x80808080u, sw1.w ^ 0x80808080u};
-      const uint8_t *xb6 = xh_s + gid * CS + 8 * j + (size_t)c_c * 512;
-      const float *xs6 = (const float *)xsf_s + (size_t)c_c * 16 * NC + 2 * j;
+      const uint8_t *xb6 = xh_s + (gid + cb) * CS + 8 * j + (size_t)c_c * 512;
+      const float *xs6 = (const float *)xsf_s + (size_t)c_c * 16 * NC + 2 * j + cb;
 #pragma unroll
       for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -253,11 +260,11 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
             const float s1 = d1 * (__uint_as_float(__byte_perm(sc1w[gi >> 2], 0x4B000000u, 0x7650u | (gi & 3))) - 8388736.0f);
             const int kl = 128 * hf + 32 * qd + 16 * u;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              const uint2 bx = *(const uint2 *)(xb6 + (size_t)nt * 8 * CS + kl * 2);
+            for (int nt = 0; nt < NTC; nt++) {
+              const uint2 bx = *(const uint2 *)(xb6 + (size_t)nt * NTS * CS + kl * 2);
               float p[4];
               mma16816_z(p, e0, e1, o0, o1, bx.x, bx.y);
-              const float2 xs = *(const float2 *)(xs6 + (size_t)(kl >> 4) * NC + nt * 8);
+              const float2 xs = *(const float2 *)(xs6 + (size_t)(kl >> 4) * NC + nt * NTS);
               acc[nt][0] += s0 * (p[0] * w - 32.0f * xs.x);
               acc[nt][1] += s0 * (p[1] * w - 32.0f * xs.y);
               acc[nt][2] += s1 * (p[2] * w - 32.0f * xs.x);
@@ -282,10 +289,10 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
         const uint2 t0 = *(const uint2 *)(b0 + 16 + 8 * j), t1 = *(const uint2 *)(b1 + 16 + 8 * j);
         qh0 = t0.x; qh0b = t0.y; qh1 = t1.x; qh1b = t1.y;
       }
-      float sS[NT][4], pm[NT][4];
+      float sS[NTC][4], pm[NTC][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        const uint2 xf = *(const uint2 *)(xfb + (size_t)c_c * NC * 32 + nt * 8 * 32);
+      for (int nt = 0; nt < NTC; nt++) {
+        const uint2 xf = *(const uint2 *)(xfb + (size_t)c_c * NC * 32 + (nt * NTS + cb) * 32);
         mma16816_z(pm[nt], am0, am1, al0, al1, xf.x, xf.y);
         sS[nt][0] = sS[nt][1] = sS[nt][2] = sS[nt][3] = 0.0f;
       }
@@ -304,8 +311,8 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
         const float sc1l = byte_f(s1, (2 * g) & 3), sc1h = byte_f_scaled(s1, (2 * g + 1) & 3, 0.0625f);
         const uint32_t a0x8 = a0.x >> 8, a0y8 = a0.y >> 8, a1x8 = a1.x >> 8, a1y8 = a1.y >> 8;
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-          const uint8_t *xr = xb + (size_t)nt * 8 * CS + ((size_t)c_c * 256 + 64 * g) * 2;
+        for (int nt = 0; nt < NTC; nt++) {
+          const uint8_t *xr = xb + (size_t)(nt * NTS + cb) * CS + ((size_t)c_c * 256 + 64 * g) * 2;
           const uint4 bl = *(const uint4 *)xr, bh = *(const uint4 *)(xr + 64);
           float pl[4], ph[4];
           mma16816_z(pl, (a0.x & 0x000f000fu) | ((f0l & 0x00010001u) << 4), (a1.x & 0x000f000fu) | ((f1l & 0x00010001u) << 4),
@@ -325,7 +332,7 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
       const float d0 = h2f_bits(h0.x & 0xffffu) * TWO24, dm0 = h2f_bits(h0.x >> 16) * 32.0f;
       const float d1 = h2f_bits(h1.x & 0xffffu) * TWO24, dm1 = h2f_bits(h1.x >> 16) * 32.0f;
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
+      for (int nt = 0; nt < NTC; nt++) {
         acc[nt][0] += d0 * sS[nt][0] - dm0 * pm[nt][0];
         acc[nt][1] += d0 * sS[nt][1] - dm0 * pm[nt][1];
         acc[nt][2] += d1 * sS[nt][2] - dm1 * pm[nt][2];
@@ -335,7 +342,7 @@ __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const
     __syncwarp();
     cstage = cstage + 1 == ST ? 0 : cstage + 1;
     if (++c_c == nsl) {
-      mats.template epilogue<NT>(ks, c_tile, acc, lane);
+      mats.template epilogue<NTC>(ks, c_tile, acc, lane);
       c_c = 0;
       c_tile += nws;
     }

@@ -1,6 +1,6 @@
 // moe.cuh -- the routed-expert FFN's two GEMMs (llb_moe_gu, llb_moe_dn of tools/payload-moeany.patch;
-// host side host/llb_host.c:622-724) for the T <= 8 rows of a verify pass, on the K-quant GEMM phase of
-// gemm2.cuh.
+// host side host/llb_host.c:622-724) for the T <= 16 rows of a verify pass (the rows of several streams), on the
+// K-quant GEMM phase of gemm2.cuh.
 //
 // Device layout of a layer's experts: two stacks of ne + 1 blocks, the shared expert being block ne,
 //   GU  block e = [ef gate rows][ef up rows] of d columns      (es_gu bytes per block)
@@ -24,19 +24,23 @@
 #include "ffn_fused.cuh"
 
 
-// column t of a finished tile: hi + lo / 2048, rows gid and gid + 8 (every lane takes part in the shuffles)
-template <int NT> __device__ __forceinline__ void moe_col(const float (&acc)[NT][4], int t, int lane, float &v0, float &v1, bool &mine) {
-  const int j = lane & 3;
+// A pass of 16 rows stages 32 plane columns but multiplies a weight tile with two n-tiles of them only: the hi and the
+// lo tile of the eight rows its own row t is among (columns 8 (t / 8) .. and 16 + 8 (t / 8) ..).
+template <int NT> constexpr int moe_ntc() { return NT > 2 ? 2 : NT; }
+// column t of a finished tile: hi + lo / 2048, rows gid and gid + 8 (every lane takes part in the shuffles); with two
+// n-tiles they are the hi and lo tiles of rows 8 (t / 8) ..
+template <int NTC> __device__ __forceinline__ void moe_col(const float (&acc)[NTC][4], int t, int lane, float &v0, float &v1, bool &mine) {
+  const int j = lane & 3, i = t & 1;
   float lo[4];
-  if constexpr (NT == 1) {
+  if constexpr (NTC == 1) {
 #pragma unroll
-    for (int i = 0; i < 4; i++) lo[i] = __shfl_xor_sync(0xffffffffu, acc[0][i], 2);
+    for (int q = 0; q < 4; q++) lo[q] = __shfl_xor_sync(0xffffffffu, acc[0][q], 2);
+    mine = j < 2 && (t >> 1) == j;
   } else {
 #pragma unroll
-    for (int i = 0; i < 4; i++) lo[i] = acc[NT - 1][i];
+    for (int q = 0; q < 4; q++) lo[q] = acc[1][q];
+    mine = ((t & 7) >> 1) == j;
   }
-  mine = (NT == 2 || j < 2) && (t >> 1) == j;
-  const int i = t & 1;
   v0 = acc[0][i] + lo[i] * XP_LO_INV;
   v1 = acc[0][i + 2] + lo[i + 2] * XP_LO_INV;
 }
@@ -54,6 +58,7 @@ template <int FMT> struct MoeGuMats {
     c.W = m.W + (size_t)e * m.es + (size_t)sb0 * G2Traits<FMT>::SB;
   }
   __device__ __forceinline__ const uint8_t *src(const Cur &c, int sb0, int pc) const { return c.W + (size_t)pc * G2Traits<FMT>::SB; }
+  __device__ __forceinline__ int col0(int tile) const { return ((tile / (m.ef >> 3)) / m.nslot) & ~7; }
   template <int NT> __device__ __forceinline__ void epilogue(int ks, int tile, float (&acc)[NT][4], int lane) const {
     const int tps = m.ef >> 3, slot = tile / tps, t = slot / m.nslot, jx = slot - t * m.nslot;
     float v0, v1;
@@ -82,6 +87,7 @@ template <int FMT> struct MoeDnMats {
     const int e = min(max(c.ids[g], 0), m.ne);
     return m.W + (size_t)e * m.es + (size_t)(sbi - g * eb) * G2Traits<FMT>::SB;
   }
+  __device__ __forceinline__ int col0(int tile) const { return (tile / (m.d >> 4)) & ~7; }
   template <int NT> __device__ __forceinline__ void epilogue(int ks, int tile, float (&acc)[NT][4], int lane) const {
     const int tpt = m.d >> 4, t = tile / tpt;
     float v0, v1;
@@ -94,10 +100,10 @@ template <int FMT> struct MoeDnMats {
 };
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_gu(const GemmArgs a, const MoeArgs m, const int cps) {
+__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT) * 32, G2_CPSM) k_moe_gu(const GemmArgs a, const MoeArgs m, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
-  g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeGuMats<FMT>{m});
+  g2_phase<FMT, NT, G2StagePlanes<FMT, NT>, MoeGuMats<FMT>, moe_ntc<NT>()>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeGuMats<FMT>{m});
 }
 // The down launch's activation slice built in shared memory from the gate|up outputs (T <= 4 rows): wt * silu(g) * u
 // of the CTA's K-slice, planes and side array exactly as k_silu_xp + G2StagePlanes would have left them, without the
@@ -145,8 +151,8 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_dn_s
 }
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_dn(const GemmArgs a, const MoeArgs m, const int cps) {
+__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT) * 32, G2_CPSM) k_moe_dn(const GemmArgs a, const MoeArgs m, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
-  g2_phase<FMT, NT>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeDnMats<FMT>{m});
+  g2_phase<FMT, NT, G2StagePlanes<FMT, NT>, MoeDnMats<FMT>, moe_ntc<NT>()>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeDnMats<FMT>{m});
 }

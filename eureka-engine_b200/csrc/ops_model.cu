@@ -230,12 +230,13 @@ template <int NQ> __device__ __forceinline__ void moe_route_row(const float *l, 
 // Router logits lg[t][r] = W[r] . h[t] for the ne router rows and the shared expert's gate row (row ne): F32
 // weights, a block per row (every load of the row in flight at once), all rows of the pass.  The block that
 // finishes last (a counter, no waiting) then routes: its warp t takes row t of the pass.
+#define MOE_MAXROWS 16   // rows of a pass the router takes (several streams of k + 1 rows)
 template <int NQ>
 __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int ne, int nk, float *__restrict__ lg,
                                                     int *__restrict__ ids, float *__restrict__ wt, unsigned int *__restrict__ ctr, const RowSet *rs, int n_all) {
   int rs_n, rs_p0;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.x, nrows = ne + 1;
-  __shared__ float red[8][SPEC_MAXT];
+  __shared__ float red[8][MOE_MAXROWS];
   __shared__ unsigned int last;
   // the row's weights depend on no kernel: fetched before the wait (two float4 per thread cover d <= 2048)
   const float4 *wr = (const float4 *)(W + (size_t)r * d);
@@ -244,9 +245,9 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
   const float4 w0 = c0 < nc ? __ldg(wr + c0) : z4, w1 = c1 < nc ? __ldg(wr + c1) : z4;
   rs = rs_begin(rs, rs_n, rs_p0);
   if (n_all > 0) rs_n = n_all;   // a pass over several streams: every row of the pass (a stream's idle rows cost nothing that matters)
-  float acc[SPEC_MAXT];
+  float acc[MOE_MAXROWS];
 #pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++) {
+  for (int t = 0; t < MOE_MAXROWS; t++) {
     acc[t] = 0.0f;
     if (t < rs_n) {
       const float4 *x = (const float4 *)(h + (size_t)t * d);
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
     }
   }
 #pragma unroll
-  for (int t = 0; t < SPEC_MAXT; t++) {
+  for (int t = 0; t < MOE_MAXROWS; t++) {
     const float v = warp_sum(acc[t]);
     if (lane == 0) red[warp][t] = v;
   }
@@ -282,7 +283,7 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
 static unsigned int *g_moe_ctr = nullptr;
 int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne, int nk, float *lg, int *ids, float *wt, const RowSet *rs, int Tmax) {
   const int n_all = g_streams.stride ? Tmax : 0;
-  if (Tmax > SPEC_MAXT) return llb_fail("moe route: %d rows in a pass (at most %d)", Tmax, SPEC_MAXT);
+  if (Tmax > MOE_MAXROWS) return llb_fail("moe route: %d rows in a pass (at most %d)", Tmax, MOE_MAXROWS);
   if (ne < 1 || ne > 1024 || nk < 1 || nk > 32 || nk > ne || d % 4) return llb_fail("moe route: %d experts, top %d, d %d", ne, nk, d);
   if (!g_moe_ctr) {
     CU_OK(cudaMalloc(&g_moe_ctr, 4));

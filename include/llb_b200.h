@@ -210,7 +210,7 @@ LLB_API int llb_b200_smp_rows(const llb_smp_params *p, llb_b200_dptr logits, int
 
 /* Several streams per engine (multi-stream batching inside one GPU; the reference's analogue is its prefill-only
  * LLB_BATCH, host/llb_host.c:2151-2793).  `streams` independent sequences share every weight read: a pass carries the k + 1
- * rows of each stream through every GEMM together (streams x (k + 1) <= 16 rows; <= 8 with routed experts), while attention,
+ * rows of each stream through every GEMM together (streams x (k + 1) <= 16 rows), while attention,
  * the DeltaNet scan, the drafter and the accept step run per stream inside the same launches, each stream on its own KV
  * cache, conv ring, state ring, control block and result ring.  A stream's tokens do not depend on what the other
  * streams do (a row's GEMM result does not depend on its neighbours).  Prompts go in per stream, at any time; a cycle

@@ -136,10 +136,11 @@ def test_streams_with_the_prompt_lookup_drafter(pkg, packs, oracle, llb):
         eng.close()
 
 
-@pytest.mark.parametrize("k,B", [(3, 2), (1, 4), (0, 8)])
+@pytest.mark.parametrize("k,B", [(3, 2), (1, 4), (0, 8), (3, 4), (1, 8), (0, 16)])
 def test_streams_of_a_routed_expert_model(pkg, packs, oracle, llb, k, B):
     """Routed experts: the router runs over every row of the pass and the expert launches take each row's own experts;
-    at most eight rows a pass.  Plain decoding of eight streams, and the prompt-lookup drafter on two and four."""
+    up to sixteen rows a pass.  Plain decoding of eight and sixteen streams, and the prompt-lookup drafter on two, four
+    and eight."""
     cfg = packs.cfg_tiny_moe()
     pack = packs.build_pack(cfg)
     base = [packs.synth_prompt(50 + b, 6, cfg.vocab_size) for b in range(B)]
