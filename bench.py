@@ -268,10 +268,10 @@ def run_streams(args, rank, world, local):
     torch.cuda.empty_cache()
     eng = llb.SpecEngine(pack, mtp, k=k, max_ctx=max_ctx, streams=B)
     eng.set_prefill(True)
+    prompts = [packs.synth_prompt(100 * rank + b + 3, n_prompt, cfg.vocab_size) for b in range(B)]
     torch.cuda.synchronize()
     t_pre = time.time()
-    for b in range(B):
-        eng.prefill_stream(b, packs.synth_prompt(100 * rank + b + 3, n_prompt, cfg.vocab_size))
+    eng.prefill_streams(prompts)          # the prompts' rows share the prompt passes
     torch.cuda.synchronize()
     t_pre = time.time() - t_pre
     st = torch.cuda.ExternalStream(llb.lib().llb_b200_stream())

@@ -1310,72 +1310,109 @@ LLB_API int llb_spec_reset(llb_spec *m) {
   return 0;
 }
 
-static int prefill_stream(llb_spec *m, int b, const int *ids, int n) {
-  if (b < 0 || b >= m->B) return llb_fail("prefill: stream %d of %d", b, m->B);
-  if (n < 1) return llb_fail("prefill: empty prompt");
-  if (n + m->Tpf + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
-  for (int i = 0; i < n; i++) if (ids[i] < 0 || ids[i] >= m->V) return llb_fail("prefill: token %d out of range", ids[i]);
-  CK(reset_stream(m, b));
+// The prompts of nb streams (bs[i] gets ids[i][0 .. ns[i]-1]) through the same prompt passes: every stream feeds its own
+// rows of a pass, so prompts that arrive together share each pass's weight read; a stream whose prompt is through sits
+// the remaining passes out.
+static int prefill_many(llb_spec *m, int nb, const int *bs, const int *const *ids, const int *ns) {
+  if (nb < 1 || nb > m->B) return llb_fail("prefill: %d prompts for %d streams", nb, m->B);
+  std::vector<char> in_set(m->B, 0);
+  for (int i = 0; i < nb; i++) {
+    const int b = bs[i], n = ns[i];
+    if (b < 0 || b >= m->B) return llb_fail("prefill: stream %d of %d", b, m->B);
+    if (in_set[b]) return llb_fail("prefill: stream %d given twice", b);
+    in_set[b] = 1;
+    if (n < 1) return llb_fail("prefill: empty prompt");
+    if (n + m->Tpf + 1 > m->max_ctx) return llb_fail("prefill: %d tokens do not fit a context of %d", n, m->max_ctx);
+    for (int j = 0; j < n; j++) if (ids[i][j] < 0 || ids[i][j] >= m->V) return llb_fail("prefill: token %d out of range", ids[i][j]);
+  }
+  for (int i = 0; i < nb; i++) CK(reset_stream(m, bs[i]));
   if (m->tp.size > 1) CK(tp_host_barrier());
-  // the other streams sit this out: with no rows in their control blocks every kernel skips them, and the accept
-  // kernel neither decides nor reports for them; their blocks are put back afterwards
-  std::vector<SpecCtl> keep;
-  bool parked = false;
-  for (int o = 0; o < m->B; o++) parked = parked || (o != b && m->sq[o].primed);
-  if (parked) {
-    keep.resize(m->B);
-    CU_OK(cudaMemcpy(keep.data(), m->ctl, sizeof(SpecCtl) * m->B, cudaMemcpyDeviceToHost));
-    for (int o = 0; o < m->B; o++) if (o != b) {
-      SpecCtl c = keep[o];
-      c.verify.n = 0; c.catchup.n = 0; c.chain.n = 0;
-      CK(ctl_write(m, o, c));
+  // a stream that takes no part in a pass sits it out: with no rows in its control block every kernel skips it, and the
+  // accept kernel neither decides nor reports for it; its block is put back at the end
+  std::vector<SpecCtl> keep(m->B);
+  std::vector<char> kept(m->B, 0);
+  auto park = [&](int o) -> int {
+    CU_OK(cudaMemcpy(&keep[o], ctl_of(m, o), sizeof(SpecCtl), cudaMemcpyDeviceToHost));
+    kept[o] = 1;
+    SpecCtl c = keep[o];
+    c.verify.n = 0; c.catchup.n = 0; c.chain.n = 0;
+    return ctl_write(m, o, c);
+  };
+  for (int o = 0; o < m->B; o++) if (!in_set[o] && m->sq[o].primed) CK(park(o));
+  std::vector<int> p(nb, 0);
+  for (int i = 0; i < nb; i++) {
+    const int b = bs[i];
+    SpecCtl c = ctl_fresh(m, b);
+    CU_OK(cudaMemcpyAsync(hist_of(m, b), ids[i], (size_t)ns[i] * 4, cudaMemcpyHostToDevice, g_llb.stream));
+    // the drafter's row for position 0 pairs token 0 with a zero hidden (host/llb_host.c:1815-1817)
+    c.catchup.n = 1; c.catchup.pos0 = 0; c.catchup.tok[0] = ids[i][0];
+    c.verify.n = m->lookup ? 1 : m->per;   // nothing to look up at position 0
+    c.verify.pos0 = 0; c.verify.tok[0] = ids[i][0];
+    for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
+    CK(ctl_write(m, b, c));
+  }
+  // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_RMAX rows through the dense path (dense FFN only),
+  // one stream after the other (a chunk fills the tensor cores by itself)
+  for (int i = 0; i < nb; i++)
+    if (m->prefill_mode == 1 && m->ne == 0 && m->tp.size <= 1 && ns[i] - 1 >= m->Tspec + 32) CK(pf_prefill(m, bs[i], ids[i], ns[i] - 1, m->Tspec, &p[i]));
+  for (int i = 0; i < nb; i++) if (nb > 1 && p[i] >= ns[i] - 1) CK(park(bs[i]));   // a one-token prompt: nothing to run
+  for (;;) {
+    std::vector<int> rows_of(nb, 0);
+    int live = 0;
+    for (int i = 0; i < nb; i++) {
+      const int b = bs[i], n = ns[i];
+      if (p[i] >= n - 1) continue;
+      live++;
+      // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
+      // over the rows of the last chunk, and that cycle's kernels cover k + 1 rows
+      const int rem = n - 1 - p[i];
+      const int rows = rem <= m->Tspec ? rem : (rem - m->Tspec < m->Tpf ? rem - m->Tspec : m->Tpf);
+      rows_of[i] = rows;
+      // rows and their successors are given; only these fields of the control block change
+      struct { int n, pos0, tok[SPEC_MAXT], slot[SPEC_MAXT]; } v;
+      v.n = rows; v.pos0 = p[i];
+      for (int r = 0; r < SPEC_MAXT; r++) { v.tok[r] = r < rows ? ids[i][p[i] + r] : 0; v.slot[r] = (p[i] + r) & (CONV_RING - 1); }
+      int tail[1 + SPEC_MAXT];
+      tail[0] = rows;  // forced
+      for (int r = 0; r < SPEC_MAXT; r++) tail[1 + r] = r < rows ? ids[i][p[i] + r + 1] : 0;
+      // pageable sources: the copies have taken their bytes when the calls return
+      CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->verify, &v, sizeof v, cudaMemcpyHostToDevice, g_llb.stream));
+      CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->forced, tail, sizeof tail, cudaMemcpyHostToDevice, g_llb.stream));
+    }
+    if (!live) break;
+    CU_OK(cudaGraphLaunch(m->g_prefill, g_llb.stream));
+    for (int i = 0; i < nb; i++) {
+      if (!rows_of[i]) continue;
+      SpecResult r;
+      CK(wait_result(m, bs[i], &r));
+      if (r.served != rows_of[i]) return llb_fail("prefill: chunk at %d of stream %d served %d of %d rows", p[i], bs[i], r.served, rows_of[i]);
+      p[i] += rows_of[i];
+      if (p[i] >= ns[i] - 1 && live > 1) CK(park(bs[i]));   // through, while others still have rows to feed
     }
   }
-  SpecCtl c = ctl_fresh(m, b);
-  CU_OK(cudaMemcpyAsync(hist_of(m, b), ids, (size_t)n * 4, cudaMemcpyHostToDevice, g_llb.stream));
-  // the drafter's row for position 0 pairs token 0 with a zero hidden (host/llb_host.c:1815-1817)
-  c.catchup.n = 1; c.catchup.pos0 = 0; c.catchup.tok[0] = ids[0];
-  c.verify.n = m->lookup ? 1 : m->per;   // nothing to look up at position 0
-  c.verify.pos0 = 0; c.verify.tok[0] = ids[0];
-  for (int r = 0; r < SPEC_MAXT; r++) c.verify.slot[r] = r & (CONV_RING - 1);
-  CK(ctl_write(m, b, c));
-  int p = 0;
-  // LLB_PREFILL=fast: everything but the last k + 1 rows in chunks of PF_RMAX rows through the dense path (dense FFN only)
-  if (m->prefill_mode == 1 && m->ne == 0 && m->tp.size <= 1 && n - 1 >= m->Tspec + 32) CK(pf_prefill(m, b, ids, n - 1, m->Tspec, &p));
-  while (p < n - 1) {
-    // wide chunks, except that the last one has at most k + 1 rows: the first speculative cycle's drafter catches up
-    // over the rows of the last chunk, and that cycle's kernels cover k + 1 rows
-    const int rem = n - 1 - p;
-    const int rows = rem <= m->Tspec ? rem : (rem - m->Tspec < m->Tpf ? rem - m->Tspec : m->Tpf);
-    // rows and their successors are given; only these fields of the control block change
-    struct { int n, pos0, tok[SPEC_MAXT], slot[SPEC_MAXT]; } v;
-    v.n = rows; v.pos0 = p;
-    for (int r = 0; r < SPEC_MAXT; r++) { v.tok[r] = r < rows ? ids[p + r] : 0; v.slot[r] = (p + r) & (CONV_RING - 1); }
-    int tail[1 + SPEC_MAXT];
-    tail[0] = rows;  // forced
-    for (int r = 0; r < SPEC_MAXT; r++) tail[1 + r] = r < rows ? ids[p + r + 1] : 0;
-    CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->verify, &v, sizeof v, cudaMemcpyHostToDevice, g_llb.stream));
-    CU_OK(cudaMemcpyAsync(&ctl_of(m, b)->forced, tail, sizeof tail, cudaMemcpyHostToDevice, g_llb.stream));
-    CU_OK(cudaGraphLaunch(m->g_prefill, g_llb.stream));
-    SpecResult r;
-    CK(wait_result(m, b, &r));
-    if (r.served != rows) return llb_fail("prefill: chunk at %d served %d of %d rows", p, r.served, rows);
-    p += rows;
+  for (int o = 0; o < m->B; o++) if (kept[o]) CK(ctl_write(m, o, keep[o]));
+  for (int i = 0; i < nb; i++) {
+    SeqHost &q = m->sq[bs[i]];
+    q.pos = ns[i] - 1;        // n == 1: nothing ran, the first cycle starts at position 0 with the single prompt token
+    q.last_tok = ids[i][ns[i] - 1];
+    q.primed = true;
+    q.have_last = false;
   }
-  if (parked) for (int o = 0; o < m->B; o++) if (o != b) CK(ctl_write(m, o, keep[o]));
-  SeqHost &q = m->sq[b];
-  q.pos = n - 1;        // n == 1: nothing ran, the first cycle starts at position 0 with the single prompt token
-  q.last_tok = ids[n - 1];
-  q.primed = true;
-  q.have_last = false;
   return 0;
 }
+static int prefill_stream(llb_spec *m, int b, const int *ids, int n) { return prefill_many(m, 1, &b, &ids, &n); }
 // Feed the prompt.  Positions 0 .. n-2 run through the verify pass in chunks of given rows (or, for long prompts with
 // LLB_PREFILL=fast, through the dense path); the last prompt token becomes the first speculative cycle's committed
 // input, exactly where the reference's first cycle after a prompt starts (host/llb_host.c:1911, pos = n-1).
 LLB_API int llb_spec_prefill(llb_spec *m, const int *ids, int n) { return prefill_stream(m, 0, ids, n); }
 // The same for stream b of an engine opened with llb_spec_open_streams; the other streams keep their state.
 LLB_API int llb_spec_prefill_stream(llb_spec *m, int stream, const int *ids, int n) { return prefill_stream(m, stream, ids, n); }
+// Several streams' prompts at once (streams[i] gets ids[i][0 .. n[i]-1]): the prompts' rows share the prompt passes, each
+// stream feeding its own k + 1 rows of a pass; results are those of llb_spec_prefill_stream on each stream in turn.
+LLB_API int llb_spec_prefill_streams(llb_spec *m, int n_prompts, const int *streams, const int *const *ids, const int *n) {
+  if (!m || !streams || !ids || !n) return llb_fail("llb_spec_prefill_streams: null argument");
+  return prefill_many(m, n_prompts, streams, ids, n);
+}
 
 // One speculative cycle.  ids_out[0..*n_out-1] are the emitted tokens; top2_out (may be null) gets
 // [id1, bits1, id2, bits2] of each emitted row.

@@ -77,6 +77,7 @@ def lib() -> C.CDLL:
             "llb_b200_smp_rows": (i32, [vp, u64, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
             "llb_spec_open_streams": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
             "llb_spec_streams": (i32, [vp]), "llb_spec_prefill_stream": (i32, [vp, i32, vp, i32]),
+            "llb_spec_prefill_streams": (i32, [vp, i32, vp, vp, vp]),
             "llb_spec_cycle_streams": (i32, [vp, vp, vp, vp]), "llb_spec_run_cycles_streams": (i32, [vp, i32, vp]),
             "llb_spec_position_stream": (i32, [vp, i32]), "llb_spec_stats_stream": (i32, [vp, i32, vp]),
             "llb_spec_read_state_stream": (i32, [vp, i32, i32, i32, i32, vp, sz]),
@@ -299,6 +300,17 @@ class SpecEngine:
         import numpy as np
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         check(self.L.llb_spec_prefill_stream(self.h, b, ids.ctypes.data, len(ids)), "llb_spec_prefill_stream")
+
+    def prefill_streams(self, prompts, streams=None):
+        """{stream: ids}, or a list of prompts for `streams` (default: stream i gets prompts[i]), through shared prompt passes."""
+        import numpy as np
+        items = sorted(prompts.items()) if isinstance(prompts, dict) else list(zip(streams if streams is not None else range(len(prompts)), prompts))
+        arrs = [np.ascontiguousarray(p, dtype=np.int32) for _, p in items]
+        n = len(items)
+        bs = (C.c_int * n)(*[int(b) for b, _ in items])
+        ptrs = (C.c_void_p * n)(*[a.ctypes.data for a in arrs])
+        ns = (C.c_int * n)(*[len(a) for a in arrs])
+        check(self.L.llb_spec_prefill_streams(self.h, n, bs, ptrs, ns), "llb_spec_prefill_streams")
 
     def cycle_streams(self):
         """One cycle of every stream with a prompt: [(ids, top2) per stream] (empty arrays for an idle stream)."""

@@ -220,6 +220,10 @@ LLB_API llb_spec *llb_spec_open_streams(const char *index_text, const void *pack
                                         size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int streams);
 LLB_API int llb_spec_streams(const llb_spec *m);
 LLB_API int llb_spec_prefill_stream(llb_spec *m, int stream, const int *ids, int n);
+/* The prompts of several streams at once: streams[i] gets ids[i][0 .. n[i]-1].  The prompts' rows share the prompt passes
+ * (every stream feeds its own k + 1 rows of a pass), so n_prompts prompts take about the passes of the longest one; each
+ * stream ends in the state llb_spec_prefill_stream would have left it in.  A stream named twice is refused. */
+LLB_API int llb_spec_prefill_streams(llb_spec *m, int n_prompts, const int *streams, const int *const *ids, const int *n);
 /* One cycle of every stream that has a prompt, as one graph launch: ids_out[stream * 8 + i], i < n_out[stream], are that
  * stream's emitted tokens (n_out = 0 for a stream without a prompt); top2_out (may be NULL) [stream][8][4] words. */
 LLB_API int llb_spec_cycle_streams(llb_spec *m, int *ids_out, int *n_out, uint32_t *top2_out);

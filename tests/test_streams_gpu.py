@@ -116,6 +116,59 @@ def test_a_stream_does_not_see_its_neighbours(pkg, packs, oracle, llb):
     assert b[5]["accepted"][1] > 0        # and it was speculating
 
 
+@pytest.mark.parametrize("model,k,B", [("tiny", 3, 4), ("moe", 1, 8), ("moe", 0, 16), ("c2", 3, 4)])
+def test_prompts_fed_together_equal_prompts_fed_in_turn(pkg, packs, oracle, llb, model, k, B):
+    """llb_spec_prefill_streams on prompts of different lengths (one of a single token, two of equal length; on the 27B
+    layer shapes one long enough for the dense prompt path) against llb_spec_prefill_stream stream by stream: every
+    stream's ids, top-2 words, position, DeltaNet state and K rows are bit-identical.  A prompt fed later, while the
+    others are in flight, joins the same way."""
+    if model == "c2":
+        cfg = packs.cfg_c2(n_layers=4, vocab_size=2048, mix_gain=0.001)
+        pack = packs.build_pack(cfg, device="cuda:0")
+        mtp = packs.aux1_bytes(packs.build_mtp(pack, eh="embed"))
+        lens = [9, 150, 1, 9]
+    else:
+        cfg = packs.cfg_tiny_moe() if model == "moe" else packs.cfg_tiny()
+        pack = packs.build_pack(cfg)
+        mtp = packs.aux1_bytes(packs.build_mtp(pack)) if model == "tiny" else None
+        lens = [(1, 7, 23, 7, 12, 4, 30, 2)[b % 8] + b // 8 for b in range(B)]
+    prompts = [packs.synth_prompt(70 + b, n, cfg.vocab_size) for b, n in enumerate(lens)]
+    late = B - 1
+    steps = 12
+    runs = []
+    for together in (False, True):
+        eng = pkg.llb.SpecEngine(pack, mtp, k=k, max_ctx=256, streams=B)
+        try:
+            eng.set_prefill(True)
+            if together:
+                eng.prefill_streams({b: prompts[b] for b in range(B) if b != late})
+            else:
+                for b in range(B):
+                    if b != late:
+                        eng.prefill_stream(b, prompts[b])
+            first = eng.cycle_streams()
+            if together:
+                eng.prefill_streams({late: prompts[late]})
+            else:
+                eng.prefill_stream(late, prompts[late])
+            ids, t2 = _drive(eng, steps, range(B))
+            for b in range(B):
+                if b != late:
+                    ids[b] = np.concatenate([first[b][0], ids[b]])
+            pos = [eng.position_stream(b) for b in range(B)]
+            states = [eng.read_state_stream(b, 0, il) for b in range(B) for il in range(cfg.n_layers) if not cfg.is_full(il)]
+            krows = [eng.read_state_stream(b, 1, il, pos[b] - 1) for b in range(B) for il in range(cfg.n_layers) if cfg.is_full(il)]
+            runs.append((ids, t2, pos, states + krows))
+        finally:
+            eng.close()
+    a, b_ = runs
+    assert a[2] == b_[2]
+    for b in range(B):
+        assert np.array_equal(a[0][b], b_[0][b]) and np.array_equal(a[1][b], b_[1][b]), b
+    for x, y in zip(a[3], b_[3]):
+        assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+
 def test_streams_with_the_prompt_lookup_drafter(pkg, packs, oracle, llb):
     """No drafter image: every stream drafts from its own token history (a separate history per stream)."""
     cfg = packs.cfg_tiny()
@@ -201,5 +254,7 @@ def test_stream_limits_are_refused_by_name(pkg, packs, llb):
             eng.cycle()
         with pytest.raises(pkg.llb.LlbError, match="stream 2 of 2"):
             eng.prefill_stream(2, [1, 2, 3])
+        with pytest.raises(pkg.llb.LlbError, match="given twice"):
+            eng.prefill_streams([[1, 2, 3], [4, 5]], streams=[1, 1])
     finally:
         eng.close()
