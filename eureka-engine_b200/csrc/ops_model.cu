@@ -231,12 +231,12 @@ template <int NQ> __device__ __forceinline__ void moe_route_row(const float *l, 
 // weights, a block per row (every load of the row in flight at once), all rows of the pass.  The block that
 // finishes last (a counter, no waiting) then routes: its warp t takes row t of the pass.
 #define MOE_MAXROWS 16   // rows of a pass the router takes (several streams of k + 1 rows)
-template <int NQ>
-__global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int ne, int nk, float *__restrict__ lg,
+template <int NQ, int MR>   // MR: the most rows of a pass (8 or 16); two resident blocks a multiprocessor, so that the ne + 1 blocks are one wave
+__global__ void __launch_bounds__(256, 2) k_moe_router(const float *__restrict__ W, const float *__restrict__ h, int d, int ne, int nk, float *__restrict__ lg,
                                                     int *__restrict__ ids, float *__restrict__ wt, unsigned int *__restrict__ ctr, const RowSet *rs, int n_all) {
   int rs_n, rs_p0;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.x, nrows = ne + 1;
-  __shared__ float red[8][MOE_MAXROWS];
+  __shared__ float red[8][MR];
   __shared__ unsigned int last;
   // the row's weights depend on no kernel: fetched before the wait (two float4 per thread cover d <= 2048)
   const float4 *wr = (const float4 *)(W + (size_t)r * d);
@@ -245,9 +245,9 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
   const float4 w0 = c0 < nc ? __ldg(wr + c0) : z4, w1 = c1 < nc ? __ldg(wr + c1) : z4;
   rs = rs_begin(rs, rs_n, rs_p0);
   if (n_all > 0) rs_n = n_all;   // a pass over several streams: every row of the pass (a stream's idle rows cost nothing that matters)
-  float acc[MOE_MAXROWS];
+  float acc[MR];
 #pragma unroll
-  for (int t = 0; t < MOE_MAXROWS; t++) {
+  for (int t = 0; t < MR; t++) {
     acc[t] = 0.0f;
     if (t < rs_n) {
       const float4 *x = (const float4 *)(h + (size_t)t * d);
@@ -260,9 +260,11 @@ __global__ void __launch_bounds__(256) k_moe_router(const float *__restrict__ W,
     }
   }
 #pragma unroll
-  for (int t = 0; t < MOE_MAXROWS; t++) {
-    const float v = warp_sum(acc[t]);
-    if (lane == 0) red[warp][t] = v;
+  for (int t = 0; t < MR; t++) {
+    if (t < rs_n) {   // the same for every thread of the launch
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) red[warp][t] = v;
+    }
   }
   __syncthreads();
   if (threadIdx.x < rs_n) {
@@ -289,8 +291,10 @@ int op_moe_route(cudaStream_t s, const float *Wr, const float *h, int d, int ne,
     CU_OK(cudaMalloc(&g_moe_ctr, 4));
     CU_OK(cudaMemset(g_moe_ctr, 0, 4));
   }
-  if (ne <= 256) CU_OK(llb_launch(k_moe_router<8>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs, n_all));
-  else CU_OK(llb_launch(k_moe_router<32>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs, n_all));
+#define ROUTE_GO(NQ, MR) CU_OK(llb_launch(k_moe_router<NQ, MR>, dim3(ne + 1), dim3(256), (size_t)(0), s, Wr, h, d, ne, nk, lg, ids, wt, g_moe_ctr, rs, n_all))
+  if (ne <= 256) { if (Tmax <= 8) ROUTE_GO(8, 8); else ROUTE_GO(8, MOE_MAXROWS); }
+  else { if (Tmax <= 8) ROUTE_GO(32, 8); else ROUTE_GO(32, MOE_MAXROWS); }
+#undef ROUTE_GO
   CU_OK(cudaGetLastError());
   return 0;
 }
