@@ -1769,10 +1769,13 @@ LLB_API int llb_spec_moe_ffn(llb_spec *m, int il, int T, const float *h2, float 
   if (il < 0 || il >= m->L || !m->layer[il].ffn.moe) return llb_fail("moe_ffn: layer %d has no routed experts", il);
   if (T < 1 || T > m->Tmax) return llb_fail("moe_ffn: %d rows, the engine was opened for %d", T, m->Tmax);
   CK(llb_spec_reset(m));
-  if (m->B > 1) return llb_fail("moe_ffn: a test entry of one-stream engines");
-  SpecCtl c = ctl_fresh(m, 0);
-  c.verify.n = T;
-  CK(ctl_write(m, 0, c));
+  // rows in pass order: with several streams, row t is row t % (k + 1) of stream t / (k + 1)
+  for (int b = 0; b < m->B; b++) {
+    SpecCtl c = ctl_fresh(m, b);
+    const int left = T - b * m->per;
+    c.verify.n = left < 0 ? 0 : left > m->per ? m->per : left;
+    CK(ctl_write(m, b, c));
+  }
   StreamScope scope(m);
   cudaStream_t s = g_llb.stream;
   CU_OK(cudaMemcpyAsync(m->hn2, h2, (size_t)T * m->d * 4, cudaMemcpyHostToDevice, s));

@@ -79,6 +79,34 @@ def test_moe_ffn_rows_vs_oracle_and_row_independence(pkg, packs, oracle, llb, T,
         orc.close()
 
 
+@pytest.mark.parametrize("T,k,B", [(16, 3, 4), (16, 0, 16), (11, 1, 8)])
+def test_moe_ffn_sixteen_rows_of_several_streams(pkg, packs, oracle, llb, T, k, B):
+    """The pass of a several-stream engine (32 plane columns staged, an expert tile multiplied with its own row group's
+    two n-tiles): every row against the oracle, and bit for bit the same row alone in the pass, where it is row 0 of the
+    first row group (between engines of different widths the K-slices of the down launch differ, and with them the order
+    of the fp32 sums)."""
+    cfg = packs.cfg_tiny_moe(n_layers=8, d_expert=512, d_shared=512)
+    pack = packs.build_pack(cfg)
+    orc = oracle.Oracle(pack.index_text(), pack.data.numpy(), cap=8)
+    eng = pkg.llb.SpecEngine(pack, None, k=k, max_ctx=64, streams=B)
+    try:
+        rng = np.random.default_rng(300 + T + B)
+        h2 = rng.standard_normal((T, cfg.d_model)).astype(np.float32)
+        for il in (0, 2):      # Q5_K and Q4_K down stacks
+            out, ids, wt = eng.moe_ffn(il, h2)
+            for t in range(T):
+                ro, rid, rw = orc.moe_ffn(il, h2[t])
+                assert list(ids[t, :-1]) == list(rid)
+                assert np.abs(wt[t] - rw).max() < 1e-6
+                assert np.linalg.norm(out[t] - ro) / np.linalg.norm(ro) < 2e-5
+            for t in (0, 7, 8, T - 1):
+                alone, _, _ = eng.moe_ffn(il, h2[t:t + 1])
+                assert np.array_equal(alone[0].view(np.uint32), out[t].view(np.uint32)), t
+    finally:
+        eng.close()
+        orc.close()
+
+
 @pytest.mark.parametrize("k", [0, 3])
 def test_tiny_moe_model_ids_match_oracle(pkg, packs, oracle, llb, k):
     """A hybrid model whose every FFN is routed: plain greedy (k = 0) and the prompt-lookup speculative loop."""
