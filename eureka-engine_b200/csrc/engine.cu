@@ -89,6 +89,19 @@ struct llb_spec {
   XPlanes xpv[3][6];   // [NC 8 / 16 / 32][xp_d, xp_f, xp_qa, xp_v, xp_2d, xp_e]
   // weights
   std::vector<void *> allocs;
+  // An engine opened by llb_spec_open_sibling uses the weights of the engine it names (`share`) and owns only its
+  // sequence state: its open replays the first engine's, taking that engine's weight allocations (wlist, in order)
+  // where the first one allocated and uploaded.  What the replay needs is kept by the first engine: the index text, the
+  // drafter image's header and size, the layer count asked for.
+  llb_spec *share = nullptr;
+  int sharers = 0;         // siblings open on this engine's weights
+  bool closed = false;     // closed by its owner while siblings were open: freed with the last of them
+  std::vector<std::pair<void *, size_t>> wlist;
+  size_t wnext = 0;
+  std::string index_copy;
+  std::vector<uint8_t> mtp_hdr;
+  size_t mtp_total = 0;
+  int layers_arg = 0;
   std::vector<LayerW> layer;
   DevMat embd, head;
   float *out_norm = nullptr;
@@ -180,6 +193,22 @@ static void *dalloc(llb_spec *m, size_t bytes) {
   return p;
 }
 static float *falloc(llb_spec *m, size_t n) { return (float *)dalloc(m, n * 4); }
+// storage of a weight: allocated (fresh: the caller uploads into it), or, in a sibling, the first engine's
+static void *walloc(llb_spec *m, size_t bytes, bool *fresh) {
+  if (!m->share) {
+    void *p = dalloc(m, bytes);
+    if (p) m->wlist.push_back({p, bytes});
+    *fresh = true;
+    return p;
+  }
+  *fresh = false;
+  const std::vector<std::pair<void *, size_t>> &wl = m->share->wlist;
+  if (m->wnext >= wl.size() || wl[m->wnext].second != bytes) {
+    llb_fail("sibling: weight %zu of %zu bytes is not what the first engine loaded there (a drafter it was opened without?)", m->wnext, bytes);
+    return nullptr;
+  }
+  return wl[m->wnext++].first;
+}
 // plane columns of a pass of T rows (hi and lo halves): 8, 16 or 32
 static int nc_of(int T) { return T <= 4 ? 8 : T <= 8 ? 16 : 32; }
 static int rows_cap(const llb_spec *m) { const int a = m->B * m->Tspec, b = m->Tpf; return a > b ? a : b; }
@@ -291,8 +320,10 @@ static int load_tensor(llb_spec *m, const TensorRec &t, const uint8_t *pack, siz
                                        (unsigned long long)t.bytes, want);
   if (!in_range(t.off, t.bytes, src_bytes)) return llb_fail("index: tensor at %llu (%llu bytes) reaches past the end of its source (%zu bytes)",
                                                              (unsigned long long)t.off, (unsigned long long)t.bytes, src_bytes);
-  void *dst = dalloc(m, (size_t)t.rows * dev_row_bytes(t.fmt, t.cols));
+  bool fresh;
+  void *dst = walloc(m, (size_t)t.rows * dev_row_bytes(t.fmt, t.cols), &fresh);
   if (!dst) return -1;
+  if (!fresh) { dedupe[t.off] = dst; *out = dst; return 0; }
   if (t.blocked) {
     // [f16 d][32 q] x cols/32 per row -> [cols q][cols/32 f16 d] per row (tools/gguf2pack.c:25-27), 4096 rows at a time
     if (on_device) return llb_fail("index: blocked Q8_0 tensors are read from host memory only");
@@ -326,6 +357,7 @@ static int load_sliced(llb_spec *m, const TensorRec &t, const uint8_t *pack, siz
   void *full = nullptr;
   CK(load_tensor(m, t, pack, src_bytes, on_device, &full, none));
   m->allocs.pop_back();                                    // the temporary is freed below, not at close
+  m->wlist.pop_back();
   TpSel allr, allc;
   allr.add(0, t.rows); allc.add(0, t.cols);
   if (!rows) rows = &allr;
@@ -402,16 +434,24 @@ static int load_moe(llb_spec *m, FfnW &w, const std::string &p, const std::unord
   for (int fm : {eg.fmt, ed.fmt})
     if (fm != LLB_FM_Q4_K && fm != LLB_FM_Q5_K && fm != LLB_FM_Q6_K) return llb_fail("%s: expert stacks of format %d have no kernel (Q4_K, Q5_K, Q6_K do)", p.c_str(), fm);
   w.moe = true; w.fmt_gu = eg.fmt; w.fmt_dn = ed.fmt;
-  w.router = falloc(m, (size_t)(ne + 1) * d);
+  bool fresh;
+  w.router = (float *)walloc(m, (size_t)(ne + 1) * d * 4, &fresh);
   if (!w.router) return -1;
+  const size_t rb_gu0 = dev_row_bytes(eg.fmt, d), rb_dn0 = dev_row_bytes(ed.fmt, ef);
+  if (!fresh) {
+    w.es_gu = (long long)(2 * ef * rb_gu0); w.es_dn = (long long)(d * rb_dn0);
+    w.gu = (uint8_t *)walloc(m, (size_t)(ne + 1) * w.es_gu, &fresh);
+    w.dn = (uint8_t *)walloc(m, (size_t)(ne + 1) * w.es_dn, &fresh);
+    return w.gu && w.dn ? 0 : -1;
+  }
   const cudaMemcpyKind kind = on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
   CU_OK(cudaMemcpyAsync(w.router, pack + r_in.off, (size_t)ne * d * 4, kind, g_llb.stream));
   CU_OK(cudaMemcpyAsync(w.router + (size_t)ne * d, pack + r_sh.off, (size_t)d * 4, kind, g_llb.stream));
   const size_t rb_gu = dev_row_bytes(eg.fmt, d), rb_dn = dev_row_bytes(ed.fmt, ef);
   const size_t pb_gu = pack_row_bytes(eg.fmt, d), pb_dn = pack_row_bytes(ed.fmt, ef);
   w.es_gu = (long long)(2 * ef * rb_gu); w.es_dn = (long long)(d * rb_dn);
-  w.gu = (uint8_t *)dalloc(m, (size_t)(ne + 1) * w.es_gu);
-  w.dn = (uint8_t *)dalloc(m, (size_t)(ne + 1) * w.es_dn);
+  w.gu = (uint8_t *)walloc(m, (size_t)(ne + 1) * w.es_gu, &fresh);
+  w.dn = (uint8_t *)walloc(m, (size_t)(ne + 1) * w.es_dn, &fresh);
   if (!w.gu || !w.dn) return -1;
   for (int e = 0; e <= ne; e++) {
     const uint8_t *g = e < ne ? pack + eg.off + (size_t)e * gu_stride * pb_gu : pack + sg.off;
@@ -690,6 +730,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   std::unordered_map<std::string, TensorRec> tab;
   CK(parse_index(m, index_text, tab));
   CK(validate_index(m, tab, m->pack_bytes));
+  if (!m->share) { m->index_copy = index_text; m->layers_arg = layers; }
   const int L_index = m->L;   // the trunk's length in the index: a nextn (MTP) block, if the index has one, is block L_index
   if (layers > 0 && layers < m->L) m->L = layers;
   if (k < 0 || k > 7) return llb_fail("k = %d: the path takes 0..7 drafts (host/llb_host.c:1608)", k);
@@ -863,6 +904,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
     std::vector<uint8_t> hdr(16 + 72 * 64);
     size_t hb = mtp_bytes < hdr.size() ? mtp_bytes : hdr.size();
     if (mtp_on_device) CU_OK(cudaMemcpy(hdr.data(), mtp, hb, cudaMemcpyDeviceToHost)); else memcpy(hdr.data(), mtp, hb);
+    if (!m->share) { m->mtp_hdr.assign(hdr.begin(), hdr.begin() + hb); m->mtp_total = mtp_bytes; }
     uint64_t off[17], nb[17];
     int fm[17];
     bool got[17] = {false};
@@ -1201,6 +1243,7 @@ LLB_API llb_spec *llb_spec_open(const char *index_text, const void *pack, size_t
 // in the same order (the collectives inside a cycle pair up across the ranks); all of them return the same tokens.
 static llb_spec *open_any(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp, size_t mtp_bytes,
                           int mtp_on_device, int k, int max_ctx, int layers, int tp_n, int nstreams);
+static llb_spec *open_finish(llb_spec *m);
 LLB_API llb_spec *llb_spec_open_tp(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                    size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int tp_n) {
   return open_any(index_text, pack, pack_bytes, pack_on_device, mtp, mtp_bytes, mtp_on_device, k, max_ctx, layers, tp_n, 1);
@@ -1223,6 +1266,35 @@ static llb_spec *open_any(const char *index_text, const void *pack, size_t pack_
     llb_spec_close(m);
     return nullptr;
   }
+  return open_finish(m);
+}
+// Another engine on the weights `first` has on the device: its own k, context, streams, sequence state and graphs, no
+// second copy of the model.  Streams beyond the 16 rows of a pass go into siblings: their passes run one after the
+// other, each streaming the weights once.  Tokens are those of an engine opened the usual way with the same k and
+// streams, bit for bit.  `first` may be closed before its siblings; the weights are freed with the last of them.
+// Refused: tensor-parallel engines; k > 0 with a drafter the first engine did not load.
+LLB_API llb_spec *llb_spec_open_sibling(llb_spec *first, int k, int max_ctx, int streams) {
+  if (!first) { llb_fail("llb_spec_open_sibling: no engine"); return nullptr; }
+  if (first->share) first = first->share;
+  if (first->tp.size > 1) { llb_fail("llb_spec_open_sibling: a tensor-parallel engine has no siblings"); return nullptr; }
+  llb_spec *m = new llb_spec();
+  m->pack_bytes = first->pack_bytes;
+  m->share = first;
+  first->sharers += 1;
+  const uint8_t *mtp = first->mtp_hdr.empty() ? nullptr : first->mtp_hdr.data();
+  if (open_impl(m, first->index_copy.c_str(), nullptr, 0, mtp, first->mtp_total, 0, k, max_ctx, first->layers_arg, 1, streams)) {
+    llb_spec_close(m);
+    return nullptr;
+  }
+  return open_finish(m);
+}
+// bytes of weights this engine allocated itself: 0 for a sibling
+LLB_API size_t llb_spec_weight_bytes(const llb_spec *m) {
+  size_t n = 0;
+  if (m && !m->share) for (const auto &w : m->wlist) n += w.second;
+  return n;
+}
+static llb_spec *open_finish(llb_spec *m) {
   // One eager pass with empty row sets sizes and allocates every partial-sum buffer, so that the
   // captures below allocate nothing.  Then the graphs are captured once; everything that changes
   // between cycles lives in device memory.
@@ -1280,6 +1352,12 @@ LLB_API int llb_b200_gguf_index(const char *path, char *buf, int cap) {
 LLB_API void llb_spec_close(llb_spec *m) {
   if (!m) return;
   cudaStreamSynchronize(g_llb.stream);
+  if (m->sharers > 0) { m->closed = true; return; }   // its weights are in use: freed when the last sibling closes
+  if (llb_spec *first = m->share) {
+    m->share = nullptr;
+    first->sharers -= 1;
+    if (first->sharers == 0 && first->closed) llb_spec_close(first);
+  }
   if (m->g_spec) cudaGraphExecDestroy(m->g_spec);
   if (m->g_prefill) cudaGraphExecDestroy(m->g_prefill);
   if (m->g_verify) cudaGraphExecDestroy(m->g_verify);

@@ -78,6 +78,7 @@ def lib() -> C.CDLL:
             "llb_spec_open_streams": (vp, [C.c_char_p, vp, sz, i32, vp, sz, i32, i32, i32, i32, i32]),
             "llb_spec_streams": (i32, [vp]), "llb_spec_prefill_stream": (i32, [vp, i32, vp, i32]),
             "llb_spec_prefill_streams": (i32, [vp, i32, vp, vp, vp]),
+            "llb_spec_open_sibling": (vp, [vp, i32, i32, i32]), "llb_spec_weight_bytes": (sz, [vp]),
             "llb_spec_cycle_streams": (i32, [vp, vp, vp, vp]), "llb_spec_run_cycles_streams": (i32, [vp, i32, vp]),
             "llb_spec_position_stream": (i32, [vp, i32]), "llb_spec_stats_stream": (i32, [vp, i32, vp]),
             "llb_spec_read_state_stream": (i32, [vp, i32, i32, i32, i32, vp, sz]),
@@ -265,6 +266,19 @@ class SpecEngine:
         self.h = handle(self.L.llb_spec_open_gguf(path.encode(), mptr, mbytes, 0, k, max_ctx, layers), "llb_spec_open_gguf")
         self.k, self.vocab, self.d, self.cfg = k, cfg.vocab_size, cfg.d_model, cfg
         return self
+
+    def sibling(self, k: int = None, max_ctx: int = 4096, streams: int = None) -> "SpecEngine":
+        """Another engine on this one's weights (llb_spec_open_sibling): its own k, context, streams and sequence state."""
+        o = SpecEngine.__new__(SpecEngine)
+        o.L = self.L
+        o.k = self.k if k is None else k
+        o.streams = getattr(self, "streams", 1) if streams is None else streams
+        o.h = handle(self.L.llb_spec_open_sibling(self.h, o.k, max_ctx, o.streams), "llb_spec_open_sibling")
+        o.vocab, o.d, o.cfg = self.vocab, self.d, self.cfg
+        return o
+
+    def weight_bytes(self) -> int:
+        return int(self.L.llb_spec_weight_bytes(self.h))
 
     def close(self):
         if getattr(self, "h", None):

@@ -219,6 +219,14 @@ LLB_API int llb_b200_smp_rows(const llb_smp_params *p, llb_b200_dptr logits, int
 LLB_API llb_spec *llb_spec_open_streams(const char *index_text, const void *pack, size_t pack_bytes, int pack_on_device, const void *mtp,
                                         size_t mtp_bytes, int mtp_on_device, int k, int max_ctx, int layers, int streams);
 LLB_API int llb_spec_streams(const llb_spec *m);
+/* Another engine on the weights `first` has on the device: its own k, context, streams, sequence state and graphs, no
+ * second copy of the model.  Streams beyond the 16 rows of one pass go into siblings, whose passes run one after the other
+ * (each streams the weights once).  Its tokens are those of an engine opened the usual way with the same k and streams, bit
+ * for bit.  `first` may be closed before its siblings: the weights are freed with the last engine that uses them.
+ * Refused: a tensor-parallel `first`; k > 0 where `first` was opened without the drafter the sibling would load. */
+LLB_API llb_spec *llb_spec_open_sibling(llb_spec *first, int k, int max_ctx, int streams);
+/* Bytes of weights the engine allocated itself (0 for a sibling). */
+LLB_API size_t llb_spec_weight_bytes(const llb_spec *m);
 LLB_API int llb_spec_prefill_stream(llb_spec *m, int stream, const int *ids, int n);
 /* The prompts of several streams at once: streams[i] gets ids[i][0 .. n[i]-1].  The prompts' rows share the prompt passes
  * (every stream feeds its own k + 1 rows of a pass), so n_prompts prompts take about the passes of the longest one; each

@@ -169,6 +169,75 @@ def test_prompts_fed_together_equal_prompts_fed_in_turn(pkg, packs, oracle, llb,
         assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
 
 
+@pytest.mark.parametrize("model", ["tiny", "moe"])
+def test_a_sibling_engine_uses_the_first_ones_weights(pkg, packs, oracle, llb, model):
+    """llb_spec_open_sibling: a second engine (other k, other streams) on the first one's weights.  Both engines, cycled in
+    turn, give the ids, top-2 words and DeltaNet state of engines opened the usual way, bit for bit; the sibling allocates
+    no weights; the first engine may be closed while the sibling runs on."""
+    moe = model == "moe"
+    cfg = packs.cfg_tiny_moe() if moe else packs.cfg_tiny()
+    pack = packs.build_pack(cfg)
+    mtp = None if moe else packs.aux1_bytes(packs.build_mtp(pack))
+    shapes = [(3, 2), (1, 4)]                # (k, streams) of the first engine and of its sibling
+    prompts = [packs.synth_prompt(90 + b, 5 + 4 * b, cfg.vocab_size) for b in range(6)]
+    if moe:
+        prompts = [np.concatenate([p, p, p[:2]]).astype(np.int32) for p in prompts]
+    mine = [prompts[:2], prompts[2:]]
+    steps = 14
+
+    def one_cycle(eng, out):
+        for b, (i, t) in enumerate(eng.cycle_streams()):
+            out[b] += [(int(v), tuple(int(x) for x in row)) for v, row in zip(i, t)]
+
+    def snapshot(eng, B):
+        pos = [eng.position_stream(b) for b in range(B)]
+        return pos, [eng.read_state_stream(b, 0, il).view(np.uint32) for b in range(B) for il in range(cfg.n_layers) if not cfg.is_full(il)]
+
+    alone = []
+    for (k, B), ps in zip(shapes, mine):
+        eng = pkg.llb.SpecEngine(pack, mtp, k=k, max_ctx=128, streams=B)
+        try:
+            assert eng.weight_bytes() > 0
+            eng.prefill_streams(ps)
+            out = {b: [] for b in range(B)}
+            for _ in range(steps):
+                one_cycle(eng, out)
+            alone.append((out,) + snapshot(eng, B))
+        finally:
+            eng.close()
+    first = pkg.llb.SpecEngine(pack, mtp, k=shapes[0][0], max_ctx=128, streams=shapes[0][1])
+    sib = first.sibling(k=shapes[1][0], max_ctx=128, streams=shapes[1][1])
+    try:
+        assert sib.weight_bytes() == 0 and first.weight_bytes() > 0
+        engs = [first, sib]
+        got = [{b: [] for b in range(B)} for _, B in shapes]
+        for e, ps in zip(engs, mine):
+            e.prefill_streams(ps)
+        for _ in range(steps):                # the two engines' cycles in turn
+            for e, out in zip(engs, got):
+                one_cycle(e, out)
+        for e, out, ref, (_, B) in zip(engs, got, alone, shapes):
+            assert out == ref[0]
+            pos, states = snapshot(e, B)
+            assert pos == ref[1]
+            for x, y in zip(states, ref[2]):
+                assert np.array_equal(x, y)
+        # the first engine closed under the sibling: the weights stay until the sibling closes
+        first.close()
+        more = sib.cycle_streams()
+        assert all(len(i) >= 1 for i, _ in more)
+    finally:
+        first.close()
+        sib.close()
+    # and the device still opens and runs an engine of its own afterwards
+    eng = pkg.llb.SpecEngine(pack, mtp, k=1, max_ctx=64)
+    try:
+        eng.prefill(prompts[0])
+        assert len(eng.generate(4)[0]) == 4
+    finally:
+        eng.close()
+
+
 def test_streams_with_the_prompt_lookup_drafter(pkg, packs, oracle, llb):
     """No drafter image: every stream drafts from its own token history (a separate history per stream)."""
     cfg = packs.cfg_tiny()
