@@ -216,7 +216,7 @@ STREAM_CASES = {
     2: ("cfg_c2", "config 2: 27B-shape hybrid (d 5120, 64 layers, f 17408, V 151936), Q4_K_M, MTP k=%d greedy, prompt %d, %d streams per GPU",
         3011, 3, 4),
     3: ("cfg_c3", "config 3: 35B-A3B-shape MoE hybrid (d 2048, 40 layers, 256 experts top 8 + shared, V 151936), Q4_K_S, prompt-lookup k=%d "
-        "greedy, prompt %d, %d streams per GPU", 512, 1, 4),
+        "greedy, prompt %d, %d streams per GPU", 512, 3, 8),
     4: ("cfg_c4", "config 4: 9B-shape hybrid (d 4096, 32 layers, f 12288, V 151936), Q8_0, MTP k=%d greedy, prompt %d, %d streams per GPU",
         32768, 3, 4),
 }
@@ -266,49 +266,59 @@ def run_streams(args, rank, world, local):
     max_ctx = n_prompt + (steps + warm + 8) * (k + 1) + 64
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
-    eng = llb.SpecEngine(pack, mtp, k=k, max_ctx=max_ctx, streams=B)
-    eng.set_prefill(True)
+    # a pass takes 16 rows: more streams than that go into sibling engines on the same weights, whose passes run in turn
+    per_eng = max(1, 16 // (k + 1))
+    E = -(-B // per_eng)
+    if B % E:
+        raise SystemExit(f"--streams {B} at k = {k}: {E} engines of at most {per_eng} streams need a stream count they divide")
+    Be = B // E
+    eng = llb.SpecEngine(pack, mtp, k=k, max_ctx=max_ctx, streams=Be)
+    engs = [eng] + [eng.sibling(k=k, max_ctx=max_ctx, streams=Be) for _ in range(E - 1)]
+    for e in engs:
+        e.set_prefill(True)
     prompts = [packs.synth_prompt(100 * rank + b + 3, n_prompt, cfg.vocab_size) for b in range(B)]
     torch.cuda.synchronize()
     t_pre = time.time()
-    eng.prefill_streams(prompts)          # the prompts' rows share the prompt passes
+    for i, e in enumerate(engs):
+        e.prefill_streams(prompts[i * Be:(i + 1) * Be])          # the prompts' rows share the prompt passes
     torch.cuda.synchronize()
     t_pre = time.time() - t_pre
     st = torch.cuda.ExternalStream(llb.lib().llb_b200_stream())
     sampler = ClockSampler(local)
     sampler.start()
-    eng.run_cycles_streams(warm)
+    for e in engs:
+        e.run_cycles_streams(warm)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(st)
-    toks = int(eng.run_cycles_streams(steps).sum())
+    toks = sum(int(e.run_cycles_streams(steps).sum()) for e in engs)
     e1.record(st)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    # end to end: one graph launch and B result records per cycle, the host reading every stream's tokens
+    # end to end: one graph launch and a result record per stream per cycle, the host reading every stream's tokens
     t0 = time.perf_counter()
     n_e2e = 0
     for _ in range(steps):
-        n_e2e += sum(len(i) for i, _ in eng.cycle_streams())
+        for e in engs:
+            n_e2e += sum(len(i) for i, _ in e.cycle_streams())
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop()
-    ver_ms = eng.time_verify(10)
-    positions = [eng.position_stream(b) + k + 1 for b in range(B)]
-    vbytes = streams_bytes(packs, pack, positions, B * (k + 1))
+    ver_ms = sum(e.time_verify(10) for e in engs)          # every engine's pass streams the weights once
+    vbytes = sum(streams_bytes(packs, pack, [e.position_stream(b) + k + 1 for b in range(Be)], Be * (k + 1)) for e in engs)
     peak, peak_src = peaks()
     (ms, e2e_s), (toks, n_e2e) = pkg.dp.aggregate([ms, e2e_s], [float(toks), float(n_e2e)], device=f"cuda:{local}")
     if rank == 0:
-        acc = [eng.stats_stream(b) for b in range(B)]
+        acc = [e.stats_stream(b) for e in engs for b in range(Be)]
         line = {
             "metric": "spec-decode tok/s per B200 over all of its streams; verify-step HBM GB/s", "value": toks / (ms / 1000.0), "unit": "tok/s",
             "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": words % (k, n_prompt, B), "streams_per_gpu": B, "rows_per_pass": B * (k + 1), "parallelism": f"stream-dp{world}",
+            "config": {"workload": words % (k, n_prompt, B), "streams_per_gpu": B, "rows_per_pass": Be * (k + 1), "engines_per_gpu": E, "parallelism": f"stream-dp{world}",
                        "layers": args.layers or cfg.n_layers, "l2": "inputs larger than L2: a cycle streams the whole model",
                        "drafter": "prompt lookup" if mtp is None and k > 0 else ("MTP" if k > 0 else "none"),
                        "tokens_per_cycle_per_stream": toks / (steps * world * B),
@@ -318,13 +328,14 @@ def run_streams(args, rank, world, local):
             "wait_errors": llb.lib().llb_b200_wait_errors(), "clocks": clocks,
             "e2e": {"value": n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 216 * B,
                     "api": "llb_spec_cycle_streams: one graph launch, one result record per stream read back per cycle"},
-            "gpu_launches": eng.graph_nodes(0) * steps,
+            "gpu_launches": eng.graph_nodes(0) * steps * E,
             "verify_step": {"bytes": vbytes, "ms": ver_ms, "GBs": vbytes / ver_ms / 1e6, "frac": vbytes / ver_ms / 1e6 / peak, "peak": peak,
                             "peak_source": peak_src, "kernels": eng.graph_nodes(2),
                             "what": "dense weights and head once, KV of every stream, one expert block per (row, slot)"},
         }
         print(json.dumps(line), flush=True)
-    eng.close()
+    for e in engs:
+        e.close()
     if world > 1:
         dist.destroy_process_group()
 
