@@ -588,7 +588,8 @@ static int enq_moe_core(llb_spec *m, const FfnW &w, const RowSet *rs) {
   PK("moe gate|up", gemm_launch_moe(s, w.fmt_gu, false, m->xp_d, a, &one, nullptr));
   const bool silu_in_down = m->NC == 8;
   if (!silu_in_down) PK("moe silu", op_silu_scaled_xp(s, PartIn{m->moe_g, 1, 0}, PartIn{m->moe_u, 1, 0}, fe, m->xp_e, rs, m->Tmax, m->moe_wt, m->ef));
-  int ks = gemm_fix_ksplit(w.fmt_dn, m->NC, fe / 256, gemm_pick_ksplit(w.fmt_dn, m->NC, m->Tmax * (m->d / 16), fe / 256, g_llb.sms));
+  const bool sel = m->NC >= 32;
+  int ks = gemm_fix_ksplit(w.fmt_dn, m->NC, fe / 256, gemm_pick_ksplit(w.fmt_dn, m->NC, m->Tmax * (m->d / 16), fe / 256, g_llb.sms, sel), sel);
   CK(out_prepare(m, m->b_dn, m->d, ks));
   a.W = w.dn; a.es = w.es_dn; a.out = m->b_dn.p; a.split_stride = m->b_dn.stride;
   PK("moe down", gemm_launch_moe(s, w.fmt_dn, true, m->xp_e, a, &ks, silu_in_down ? m->moe_wt : nullptr));

@@ -5,16 +5,17 @@
 #include "moe.cuh"
 #include "host.cuh"
 
-static int g2_max_sb(int fmt, int NC) {
-  return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC)
-       : fmt == LLB_FM_Q8_0 ? g2_max_slice_sb<LLB_FM_Q8_0>(NC) : g2_max_slice_sb<LLB_FM_Q6_K>(NC);
+static int g2_max_sb(int fmt, int NC, bool sel = false) {
+  return fmt == LLB_FM_Q4_K ? g2_max_slice_sb<LLB_FM_Q4_K>(NC, sel) : fmt == LLB_FM_Q5_K ? g2_max_slice_sb<LLB_FM_Q5_K>(NC, sel)
+       : fmt == LLB_FM_Q8_0 ? g2_max_slice_sb<LLB_FM_Q8_0>(NC, sel) : g2_max_slice_sb<LLB_FM_Q6_K>(NC, sel);
 }
 // the tcgen05 kernel takes Q4_K with T <= 4 (8 plane columns)
 static bool is_g3(int fmt, int NC) { return g_llb.gemm3 && fmt == LLB_FM_Q4_K && NC == 8; }
 static unsigned int *g_ffn_sync = nullptr;   // the fused FFN's grid barrier: two counters
 static unsigned int *g_g3_err = nullptr;   // device word: set when a bounded wait of k_gemm3 ran out
-static int g2_warps_of(int fmt, int NC) {
-  return fmt == LLB_FM_Q6_K ? g2_warps<LLB_FM_Q6_K>(NC) : fmt == LLB_FM_Q8_0 ? g2_warps<LLB_FM_Q8_0>(NC) : g2_warps<LLB_FM_Q4_K>(NC);
+static int g2_warps_of(int fmt, int NC, bool sel = false) {
+  return fmt == LLB_FM_Q6_K ? g2_warps<LLB_FM_Q6_K>(NC, sel) : fmt == LLB_FM_Q8_0 ? g2_warps<LLB_FM_Q8_0>(NC, sel)
+       : fmt == LLB_FM_Q5_K ? g2_warps<LLB_FM_Q5_K>(NC, sel) : g2_warps<LLB_FM_Q4_K>(NC, sel);
 }
 
 template <int FMT, int NT> static int launch_two(cudaStream_t s, const GemmArgs &a) {
@@ -123,14 +124,15 @@ int gemm_setup(void) {
   return 0;
 }
 
-int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks) {
+// sel: a routed-expert launch (its own warp count and ring depth at 32 plane columns)
+int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks, bool sel) {
   if (ks < 1) ks = 1;
-  if (is_g3(fmt, NC)) {
+  if (!sel && is_g3(fmt, NC)) {
     const int mx = g3_max_slice_sb();
     const int lo = (nsb + mx - 1) / mx;
     if (ks < lo) ks = lo;
   } else {
-    const int mx = g2_max_sb(fmt, NC);
+    const int mx = g2_max_sb(fmt, NC, sel);
     const int lo = (nsb + mx - 1) / mx;       // the activation slice of a CTA has to fit in shared memory
     if (ks < lo) ks = lo;
   }
@@ -141,13 +143,13 @@ int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks) {
 
 // K-slices per row tile: the longest chain of work of any warp (tiles per warp x super-blocks per
 // slice), with a small charge per slice for the partial sums the consumer has to add.
-int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
+int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms, bool sel) {
   int best = 1;
   double best_cost = 1e30;
   for (int ks = 1; ks <= GEMM_MAXSPLIT && ks <= nsb; ks++) {
-    if (gemm_fix_ksplit(fmt, NC, nsb, ks) != ks) continue;
+    if (gemm_fix_ksplit(fmt, NC, nsb, ks, sel) != ks) continue;
     long long rounds;
-    if (is_g3(fmt, NC)) {
+    if (!sel && is_g3(fmt, NC)) {
       // 128-row tiles, one CTA per (tile, slice) at a time; 1.5 super-blocks of pipeline fill per tile
       const int cps = sms / ks > 0 ? sms / ks : 1, nt128 = (ntiles + 7) / 8;
       rounds = (nt128 + cps - 1) / cps;
@@ -157,13 +159,13 @@ int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms) {
       continue;
     } else {
       const int cps = sms * G2_CPSM / ks > 0 ? sms * G2_CPSM / ks : 1;
-      rounds = (ntiles + (long long)cps * g2_warps_of(fmt, NC) - 1) / ((long long)cps * g2_warps_of(fmt, NC));
+      rounds = (ntiles + (long long)cps * g2_warps_of(fmt, NC, sel) - 1) / ((long long)cps * g2_warps_of(fmt, NC, sel));
     }
     const int slice = (nsb + ks - 1) / ks;
     const double cost = (double)rounds * slice * (1.0 + 0.02 * (ks - 1));
     if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
   }
-  return gemm_fix_ksplit(fmt, NC, nsb, best);
+  return gemm_fix_ksplit(fmt, NC, nsb, best, sel);
 }
 
 // One K-split for a launch whose partial sums outlive the pass (attn_qkv into the conv ring): valid at both
@@ -234,15 +236,16 @@ template <int FMT, int NT> static int launch_moe(cudaStream_t s, bool down, cons
   int cps = g_llb.sms * G2_CPSM / a.ksplit;
   if (cps < 1) cps = 1;
   if (cps > ntiles) cps = ntiles;
-  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>(NC);
+  constexpr bool sel = moe_ntc<NT>() != NT;
+  const size_t smem = (size_t)g2_xp_bytes<FMT>(nsl, NC) + g2_ring_bytes<FMT>(NC, sel);
   if (smem > G2_SMEM_MAX) return llb_fail("moe gemm: a K-slice of %d super-blocks needs %zu bytes of shared memory", nsl, smem);
   cudaError_t e;
   if (down && wt_silu) {
     if constexpr (NT == 1) e = llb_launch(k_moe_dn_silu<FMT>, dim3(cps * a.ksplit), dim3(G2Traits<FMT>::WARPS * 32), smem, s, a, m, wt_silu, cps);
     else return llb_fail("moe gemm: the down launch builds its own activations for T <= 4 only");
   } else {
-    e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(g2_warps<FMT>(NC) * 32), smem, s, a, m, cps)
-             : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(g2_warps<FMT>(NC) * 32), smem, s, a, m, cps);
+    e = down ? llb_launch(k_moe_dn<FMT, NT>, dim3(cps * a.ksplit), dim3(g2_warps<FMT>(NC, sel) * 32), smem, s, a, m, cps)
+             : llb_launch(k_moe_gu<FMT, NT>, dim3(cps * a.ksplit), dim3(g2_warps<FMT>(NC, sel) * 32), smem, s, a, m, cps);
   }
   if (e != cudaSuccess) return llb_fail("moe gemm launch: %s", cudaGetErrorString(e));
   return 0;
@@ -260,8 +263,9 @@ int gemm_launch_moe(cudaStream_t s, int fmt, bool down, const XPlanes &xp, MoeAr
   a.nsb = a.K / 256; a.xp = xp; a.planes = 2; a.T = m.T; a.nmat = 0;
   const int ntiles = down ? m.T * (m.d / 16) : m.T * m.nslot * (m.ef / 8);
   int ks = 1;
-  if (down) ks = *ksplit > 0 ? *ksplit : gemm_pick_ksplit(fmt, xp.NC, ntiles, a.nsb, g_llb.sms);
-  ks = gemm_fix_ksplit(fmt, xp.NC, a.nsb, ks);
+  const bool sel = xp.NC >= 32;
+  if (down) ks = *ksplit > 0 ? *ksplit : gemm_pick_ksplit(fmt, xp.NC, ntiles, a.nsb, g_llb.sms, sel);
+  ks = gemm_fix_ksplit(fmt, xp.NC, a.nsb, ks, sel);
   if (!down && ks != 1) return llb_fail("moe gemm: %d columns do not fit one K-slice", a.K);
   a.ksplit = ks;
   if (ksplit) *ksplit = ks;

@@ -46,15 +46,24 @@ template <> struct G2Traits<LLB_FM_Q8_0> { enum { SB = 256, RS = 304, P = 17, QO
 // kernel spilled (40 bytes of stores, 120 of loads per thread and super-block) and spent its time waiting on local
 // memory (long-scoreboard stalls 1.3 per issue, 830 instructions per tile-super-block against 397 at 4 rows, tensor pipe
 // 34 % busy).  Eight warps get 255 registers and a ring half the size, which also leaves the activation slice more room.
-template <int FMT> __host__ __device__ constexpr int g2_warps(int NC) { return NC >= 32 && G2Traits<FMT>::WARPS > 8 ? 8 : G2Traits<FMT>::WARPS; }
-template <int FMT> __host__ __device__ constexpr int g2_stages(int NC) { return G2_STAGES; }
-template <int FMT> __host__ __device__ constexpr int g2_ring_bytes(int NC) { return g2_warps<FMT>(NC) * g2_stages<FMT>(NC) * 16 * G2Traits<FMT>::RS; }
+// sel: the routed-expert launches at 32 plane columns, which multiply a weight tile with two of the four staged n-tiles
+// (g2_phase's NTC = 2) and so need the registers of the two-n-tile kernel only: more warps (the eight-warp launch left its
+// schedulers two warps each and half their issue slots empty), two-deep rings so that the 32 staged columns of a whole
+// d = 2048 K-slice (139 KB) still fit beside them.
+template <int FMT> __host__ __device__ constexpr int g2_warps(int NC, bool sel = false) {
+  if (sel && NC >= 32 && G2_CPSM == 1) return FMT == LLB_FM_Q4_K ? 16 : FMT == LLB_FM_Q5_K ? 12 : 8;
+  return NC >= 32 && G2Traits<FMT>::WARPS > 8 ? 8 : G2Traits<FMT>::WARPS;
+}
+template <int FMT> __host__ __device__ constexpr int g2_stages(int NC, bool sel = false) { return sel && NC >= 32 && G2_CPSM == 1 ? 2 : G2_STAGES; }
+template <int FMT> __host__ __device__ constexpr int g2_ring_bytes(int NC, bool sel = false) {
+  return g2_warps<FMT>(NC, sel) * g2_stages<FMT>(NC, sel) * 16 * G2Traits<FMT>::RS;
+}
 // bytes of shared memory a K-slice of nsl super-blocks needs for NC activation columns
 template <int FMT> __host__ __device__ inline int g2_xp_bytes(int nsl, int NC) {
   return NC * (nsl * 512 + G2Traits<FMT>::XPAD) + nsl * NC * G2Traits<FMT>::AUX;
 }
-template <int FMT> inline int g2_max_slice_sb(int NC) {
-  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>(NC) - NC * G2Traits<FMT>::XPAD;
+template <int FMT> inline int g2_max_slice_sb(int NC, bool sel = false) {
+  int left = G2_SMEM_MAX - g2_ring_bytes<FMT>(NC, sel) - NC * G2Traits<FMT>::XPAD;
   return left / (NC * 512 + NC * G2Traits<FMT>::AUX);
 }
 
@@ -103,7 +112,7 @@ template <int FMT> struct G2MatsPlain {
 template <int FMT, int NT, class Stage, class Mats, int NTC = NT>
 __device__ __forceinline__ void g2_phase(const GemmArgs &a, const int cps, const int bid, uint8_t *smem, Stage stage, const Mats mats) {
   using TR = G2Traits<FMT>;
-  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = g2_warps<FMT>(8 * NT), ST = g2_stages<FMT>(8 * NT);
+  constexpr int NC = 8 * NT, RS = TR::RS, SB = TR::SB, P = TR::P, NIT = (16 * P + 31) / 32, G2_WARPS = g2_warps<FMT>(8 * NT, NTC != NT), ST = g2_stages<FMT>(8 * NT, NTC != NT);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, j = lane & 3;
   const bool live = bid < cps * a.ksplit && warp < G2_WARPS;
   const int ks = bid % a.ksplit, ci = bid / a.ksplit;

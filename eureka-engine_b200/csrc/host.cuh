@@ -46,8 +46,8 @@ inline cudaError_t llb_launch(void (*k)(KArgs...), dim3 grid, dim3 block, size_t
 }
 
 // gemm.cu
-int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms);
-int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks);   // clamps a requested K-split to what the format's kernel can take
+int gemm_pick_ksplit(int fmt, int NC, int ntiles, int nsb, int sms, bool sel = false);   // sel: for a routed-expert launch
+int gemm_fix_ksplit(int fmt, int NC, int nsb, int ks, bool sel = false);   // clamps a requested K-split to what the format's kernel can take
 int gemm_ring_ksplit(int fmt, int nsb, int ntiles, int nc_spec, int nc_pf, int sms, int cap);
 int gemm_launch(cudaStream_t s, int fmt, GemmArgs &a);   // fills tile0 / nsb, picks NT from xp.NC
 int gemm_setup(void);

@@ -100,7 +100,7 @@ template <int FMT> struct MoeDnMats {
 };
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT) * 32, G2_CPSM) k_moe_gu(const GemmArgs a, const MoeArgs m, const int cps) {
+__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT, moe_ntc<NT>() != NT) * 32, G2_CPSM) k_moe_gu(const GemmArgs a, const MoeArgs m, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
   g2_phase<FMT, NT, G2StagePlanes<FMT, NT>, MoeGuMats<FMT>, moe_ntc<NT>()>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeGuMats<FMT>{m});
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(G2Traits<FMT>::WARPS * 32, G2_CPSM) k_moe_dn_s
 }
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT) * 32, G2_CPSM) k_moe_dn(const GemmArgs a, const MoeArgs m, const int cps) {
+__global__ void __launch_bounds__(g2_warps<FMT>(8 * NT, moe_ntc<NT>() != NT) * 32, G2_CPSM) k_moe_dn(const GemmArgs a, const MoeArgs m, const int cps) {
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_trigger();
   g2_phase<FMT, NT, G2StagePlanes<FMT, NT>, MoeDnMats<FMT>, moe_ntc<NT>()>(a, cps, (int)blockIdx.x, smem, G2StagePlanes<FMT, NT>{a}, MoeDnMats<FMT>{m});
