@@ -735,6 +735,7 @@ static int open_impl(llb_spec *m, const char *index_text, const uint8_t *pack, i
   const int L_index = m->L;   // the trunk's length in the index: a nextn (MTP) block, if the index has one, is block L_index
   if (layers > 0 && layers < m->L) m->L = layers;
   if (k < 0 || k > 7) return llb_fail("k = %d: the path takes 0..7 drafts (host/llb_host.c:1608)", k);
+  if (max_ctx < 1 || max_ctx > (1 << 24)) return llb_fail("max_ctx = %d: a context of 1 .. 16777216 positions", max_ctx);
   if (m->SZ != 128 || m->KC < 2) return llb_fail("ssm_state_size %d / conv kernel %d unsupported", m->SZ, m->KC);
   if (m->hd != 128 && m->hd != 256) return llb_fail("head_dim %d unsupported", m->hd);
   if (m->ne > 0 && (m->sf != m->ef || m->ef % 256 || m->nk < 1 || m->nk > 32 || m->nk > m->ne || m->ne > 1024))

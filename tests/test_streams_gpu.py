@@ -315,6 +315,8 @@ def test_stream_limits_are_refused_by_name(pkg, packs, llb):
     mtp = packs.aux1_bytes(packs.build_mtp(pack))
     with pytest.raises(pkg.llb.LlbError, match="rows a pass"):
         pkg.llb.SpecEngine(pack, mtp, k=3, max_ctx=64, streams=5)          # 20 rows
+    with pytest.raises(pkg.llb.LlbError, match="max_ctx = 0"):
+        pkg.llb.SpecEngine(pack, mtp, k=3, max_ctx=0)
     eng = pkg.llb.SpecEngine(pack, mtp, k=1, max_ctx=64, streams=2)
     try:
         with pytest.raises(pkg.llb.LlbError, match="no stream has a prompt"):
